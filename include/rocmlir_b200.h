@@ -1,0 +1,123 @@
+/* rocmlir_b200 — C ABI of the B200 (sm_100a) contraction-kernel library.
+ *
+ * The library stands behind the boundary that rocMLIR offers to MIGraphX / MIOpen-style clients:
+ * where the reference lowers one fused kernel function to an AMD code object and hands back
+ * {binary, block size, grid size}, this library selects a hand-written sm_100a kernel and either
+ * launches it (rb* entry points below) or describes it (miir* entry points, Miir-compatible).
+ *
+ * Plain C: pointers and sizes only. Device pointers are ordinary CUDA device addresses; `stream`
+ * is a cudaStream_t passed as void* (NULL = default stream). Nothing here allocates device memory
+ * on the caller's behalf except where a function says so.
+ */
+#ifndef ROCMLIR_B200_H
+#define ROCMLIR_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define RB_API_VERSION 1
+
+#if defined(__GNUC__)
+#define RB_EXPORT __attribute__((visibility("default")))
+#else
+#define RB_EXPORT
+#endif
+
+/* Element types. Mirrors the type names rocmlir-gen accepts for -t / -out_datatype
+ * (mlir/tools/rocmlir-gen/rocmlir-gen.cpp:432-458): f32 f16 bf16 i8 i32 fp8 (OCP e4m3fn). */
+typedef enum RbDType {
+  RB_F32 = 0,
+  RB_F16 = 1,
+  RB_BF16 = 2,
+  RB_I8 = 3,
+  RB_I32 = 4,
+  RB_F8E4M3 = 5
+} RbDType;
+
+typedef enum RbStatus {
+  RB_SUCCESS = 0,
+  RB_INVALID_PARAM = 1,   /* malformed problem (sizes <= 0, unknown dtype, NULL pointer) */
+  RB_UNSUPPORTED = 2,     /* well-formed, but no kernel for it: the "applicability" failure of
+                             mlirMIGraphXAddApplicabilityPipeline (mlir-c/Dialect/MIGraphX.h:66-73) */
+  RB_WORKSPACE_TOO_SMALL = 3,
+  RB_CUDA_ERROR = 4,
+  RB_KERNEL_TIMEOUT = 5   /* a bounded device-side wait ran out; see rbReadKernelStatus */
+} RbStatus;
+
+/* Fused elementwise epilogue applied to the accumulator tile before the single global store.
+ * Replaces the linalg.generic readers that rocMLIR re-tiles onto the accumulator registers
+ * (mlir/lib/Dialect/Rock/Transforms/AlignTiling.cpp:903-1049) for the forms MIGraphX emits:
+ * dequantizelinear / quantizelinear / add(broadcast bias) / relu / convert
+ * (mlir/lib/Conversion/MIGraphXToTosa/MIGraphXToTosa.cpp:876-1018).
+ *
+ * Order of evaluation, each step an individually rounded f32 (or `mid_type`) operation:
+ *   x = acc                       (f32, or i32 -> f32 round-to-nearest-even when any float step is on)
+ *   x = round_to(mid_type, x)     if RB_EPI_ROUND_MID  (the GEMM's declared result type)
+ *   x = x * alpha                 if RB_EPI_ALPHA      (per-tensor scale product, fp8)
+ *   x = x * col_scale[n]          if RB_EPI_COL_SCALE  (per-column dequantisation scale, f32)
+ *   x = x + bias[n]               if RB_EPI_BIAS       (then round_to(mid_type) if ROUND_MID)
+ *   x = max(x, 0)                 if RB_EPI_RELU
+ *   x = x * out_recip             if RB_EPI_REQUANT    (out_recip = 1/scale computed by the caller in f32)
+ *   store: convert x to the C type (floats: RNE, fp8 saturating; integers: RNE then saturate). */
+enum {
+  RB_EPI_ALPHA = 1,
+  RB_EPI_COL_SCALE = 2,
+  RB_EPI_BIAS = 4,
+  RB_EPI_RELU = 8,
+  RB_EPI_REQUANT = 16,
+  RB_EPI_ROUND_MID = 32
+};
+
+typedef struct RbEpilogue {
+  uint32_t flags;
+  float alpha;
+  float out_recip;
+  int32_t mid_type;        /* RbDType used by RB_EPI_ROUND_MID */
+  int32_t bias_type;       /* RbDType of bias[]: RB_F32, RB_F16 or RB_BF16 */
+  const float *col_scale;  /* device, [n] */
+  const void *bias;        /* device, [n] */
+} RbEpilogue;
+
+/* rock.gemm (mlir/include/mlir/Dialect/Rock/IR/RockOps.td:136-181):
+ *   C[g,m,n] = sum_k A[g,m,k] * B[g,k,n]
+ * A is stored G x M x K (trans_a: G x K x M), B is G x K x N (trans_b: G x N x K), C is G x M x N
+ * (trans_c: G x N x M); every matrix row-major and contiguous, exactly the flat buffers that
+ * rocmlir-gen's kernels take (rocmlir-gen.cpp:2094-2124). Accumulation is f32 for float inputs
+ * and i32 for i8 (mlir/lib/Dialect/Rock/Transforms/GemmToGridwise.cpp:93-109). */
+typedef struct RbGemmProblem {
+  int32_t g, m, n, k;
+  int32_t trans_a, trans_b, trans_c;
+  int32_t ab_type; /* RbDType of A and B */
+  int32_t c_type;  /* RbDType of C */
+  int32_t f32_mode; /* for ab_type RB_F32: 0 = 3xTF32 split (fp32-class accuracy), 1 = single TF32 pass */
+} RbGemmProblem;
+
+/* Bytes of caller-provided device workspace rbGemm needs for this problem (0 for most). */
+RB_EXPORT size_t rbGemmWorkspaceSize(const RbGemmProblem *p);
+
+/* Runs the GEMM on `stream`. Returns RB_UNSUPPORTED for problems outside the kernel's reach. */
+RB_EXPORT RbStatus rbGemm(const RbGemmProblem *p, const RbEpilogue *epi /* may be NULL */, const void *a, const void *b,
+                void *c, void *workspace, size_t workspace_bytes, void *stream);
+
+/* Kernel-selection knob for tuning/experiments: tile variant used by subsequent rbGemm calls on this
+ * thread's library state. 0 = automatic (measured table). Mirrors the role of rocMLIR's perf_config
+ * (mlir/include/mlir/Dialect/Rock/Tuning/GridwiseGemmParams.h:138-194). */
+RB_EXPORT void rbSetGemmVariant(int variant);
+
+/* Device status word: 0 when every bounded wait completed. Synchronises the device. */
+RB_EXPORT RbStatus rbReadKernelStatus(uint32_t *status_out, int clear);
+
+/* Number of kernel launches this library issued since load (a monotone counter). */
+RB_EXPORT uint64_t rbLaunchCount(void);
+
+/* Last error text for this thread (never NULL). */
+RB_EXPORT const char *rbGetLastError(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ROCMLIR_B200_H */

@@ -1,0 +1,81 @@
+"""ctypes binding of librocmlir_b200.so (the C ABI declared in include/rocmlir_b200.h).
+
+There is no CPU path: importing works anywhere, but every compute call needs the built
+library and an sm_100 GPU and raises otherwise.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "librocmlir_b200.so")
+
+# RbDType
+F32, F16, BF16, I8, I32, F8E4M3 = 0, 1, 2, 3, 4, 5
+DTYPE_NAMES = {F32: "f32", F16: "f16", BF16: "bf16", I8: "i8", I32: "i32", F8E4M3: "fp8"}
+DTYPE_BYTES = {F32: 4, F16: 2, BF16: 2, I8: 1, I32: 4, F8E4M3: 1}
+
+# RbStatus
+SUCCESS, INVALID_PARAM, UNSUPPORTED, WORKSPACE_TOO_SMALL, CUDA_ERROR, KERNEL_TIMEOUT = range(6)
+STATUS_NAMES = ["RB_SUCCESS", "RB_INVALID_PARAM", "RB_UNSUPPORTED", "RB_WORKSPACE_TOO_SMALL", "RB_CUDA_ERROR",
+                "RB_KERNEL_TIMEOUT"]
+
+EPI_ALPHA, EPI_COL_SCALE, EPI_BIAS, EPI_RELU, EPI_REQUANT, EPI_ROUND_MID = 1, 2, 4, 8, 16, 32
+
+
+class RbEpilogue(C.Structure):
+    _fields_ = [("flags", C.c_uint32), ("alpha", C.c_float), ("out_recip", C.c_float), ("mid_type", C.c_int32),
+                ("bias_type", C.c_int32), ("col_scale", C.c_void_p), ("bias", C.c_void_p)]
+
+
+class RbGemmProblem(C.Structure):
+    _fields_ = [("g", C.c_int32), ("m", C.c_int32), ("n", C.c_int32), ("k", C.c_int32), ("trans_a", C.c_int32),
+                ("trans_b", C.c_int32), ("trans_c", C.c_int32), ("ab_type", C.c_int32), ("c_type", C.c_int32),
+                ("f32_mode", C.c_int32)]
+
+
+class RbError(RuntimeError):
+    def __init__(self, status: int, msg: str):
+        super().__init__(f"{STATUS_NAMES[status] if 0 <= status < len(STATUS_NAMES) else status}: {msg}")
+        self.status = status
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """Loads the shared library once; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(f"{LIB_PATH} is missing: run `python -m rocmlir_b200.build` (no CPU fallback exists)")
+        l = C.CDLL(LIB_PATH)
+        l.rbGemmWorkspaceSize.restype = C.c_size_t
+        l.rbGemmWorkspaceSize.argtypes = [C.POINTER(RbGemmProblem)]
+        l.rbGemm.restype = C.c_int
+        l.rbGemm.argtypes = [C.POINTER(RbGemmProblem), C.POINTER(RbEpilogue), C.c_void_p, C.c_void_p, C.c_void_p,
+                             C.c_void_p, C.c_size_t, C.c_void_p]
+        l.rbSetGemmVariant.restype = None
+        l.rbSetGemmVariant.argtypes = [C.c_int]
+        l.rbReadKernelStatus.restype = C.c_int
+        l.rbReadKernelStatus.argtypes = [C.POINTER(C.c_uint32), C.c_int]
+        l.rbLaunchCount.restype = C.c_uint64
+        l.rbGetLastError.restype = C.c_char_p
+        _lib = l
+    return _lib
+
+
+def check(status: int) -> None:
+    if status != SUCCESS:
+        raise RbError(status, lib().rbGetLastError().decode())
+
+
+def kernel_status(clear: bool = True) -> int:
+    v = C.c_uint32(0)
+    check(lib().rbReadKernelStatus(C.byref(v), 1 if clear else 0))
+    return v.value
+
+
+def launch_count() -> int:
+    return int(lib().rbLaunchCount())

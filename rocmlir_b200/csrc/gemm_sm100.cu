@@ -1,0 +1,299 @@
+// Host side of rbGemm: validates a rock.gemm problem, prepares operands that TMA cannot address
+// directly (row pitch not a multiple of 16 bytes -> padded copy in the caller's workspace; f32 ->
+// TF32 hi/lo split), encodes the tensor maps and launches the persistent tcgen05 kernel.
+#include "gemm_sm100.cuh"
+
+#include <mutex>
+
+#include "lib_state.h"
+
+namespace rb {
+namespace {
+
+thread_local int t_variant = 0;
+
+// ---- auxiliary kernels ---------------------------------------------------------------------------
+// Copies `rows` rows of `row_bytes` bytes into rows of `pitch_bytes` bytes, zero-filling the pad.
+__global__ void pad_rows_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, long long rows,
+                                int row_bytes, int pitch_bytes) {
+  const long long total = rows * pitch_bytes;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / pitch_bytes;
+    const int c = (int)(i - r * pitch_bytes);
+    dst[i] = c < row_bytes ? src[r * row_bytes + c] : (uint8_t)0;
+  }
+}
+
+// x = hi + lo (+ O(2^-22 |x|)), hi and lo both exactly representable in TF32 (low 13 bits zero).
+// Rows are re-pitched at the same time (pitch in elements).
+__global__ void split_tf32_kernel(const float* __restrict__ src, float* __restrict__ hi, float* __restrict__ lo,
+                                  long long rows, int cols, int pitch) {
+  const long long total = rows * pitch;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / pitch;
+    const int c = (int)(i - r * pitch);
+    float h = 0.f, l = 0.f;
+    if (c < cols) {
+      const float x = src[r * cols + c];
+      const uint32_t xb = __float_as_uint(x);
+      // round-to-nearest (ties away) onto 10 mantissa bits; inf/nan pass through the mask unchanged
+      const uint32_t hb = ((xb & 0x7F800000u) == 0x7F800000u) ? xb : ((xb + 0x1000u) & 0xFFFFE000u);
+      h = __uint_as_float(hb);
+      const float rem = x - h;
+      const uint32_t rb_ = __float_as_uint(rem);
+      l = __uint_as_float(((rb_ & 0x7F800000u) == 0x7F800000u) ? 0u : ((rb_ + 0x1000u) & 0xFFFFE000u));
+      if ((xb & 0x7F800000u) == 0x7F800000u) l = 0.f;
+    }
+    hi[i] = h;
+    lo[i] = l;
+  }
+}
+
+// ---- dispatch ----------------------------------------------------------------------------------------
+typedef void (*GemmKernel)(const GemmTensorMaps, const GemmParams);
+
+template <int KIND, int CTAS>
+GemmKernel pick_major(bool a_mn, bool b_mn) {
+  if (!a_mn && !b_mn) return gemm_tcgen05_kernel<KIND, false, false, CTAS>;
+  if (!a_mn && b_mn) return gemm_tcgen05_kernel<KIND, false, true, CTAS>;
+  if (a_mn && !b_mn) return gemm_tcgen05_kernel<KIND, true, false, CTAS>;
+  return gemm_tcgen05_kernel<KIND, true, true, CTAS>;
+}
+template <int CTAS>
+GemmKernel pick_kernel(int kind, bool a_mn, bool b_mn) {
+  switch (kind) {
+    case kKindF16: return pick_major<kKindF16, CTAS>(a_mn, b_mn);
+    case kKindTF32: return pick_major<kKindTF32, CTAS>(a_mn, b_mn);
+    case kKindI8: return pick_major<kKindI8, CTAS>(a_mn, b_mn);
+    default: return pick_major<kKindF8, CTAS>(a_mn, b_mn);
+  }
+}
+
+struct OperandPlan {
+  bool mn_major;        // contiguous dimension is M/N (not K)
+  long long rows;       // rows per batch of the stored matrix
+  int cols;             // contiguous extent
+  int pitch;            // elements per row after padding
+  bool needs_copy;      // pitch != cols or split required
+};
+
+size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+OperandPlan plan_operand(bool mn_major, int mn, int k, size_t es) {
+  OperandPlan o;
+  o.mn_major = mn_major;
+  o.rows = mn_major ? k : mn;
+  o.cols = mn_major ? mn : k;
+  const int elems16 = (int)(16 / es);
+  o.pitch = (o.cols + elems16 - 1) / elems16 * elems16;
+  o.needs_copy = o.pitch != o.cols;
+  return o;
+}
+
+bool valid_ab(int t) { return t == RB_F32 || t == RB_F16 || t == RB_BF16 || t == RB_I8 || t == RB_F8E4M3; }
+bool valid_c(int t) { return t >= RB_F32 && t <= RB_F8E4M3; }
+
+RbStatus check_problem(const RbGemmProblem* p) {
+  if (!p) return fail(RB_INVALID_PARAM, "problem is NULL");
+  if (p->g <= 0 || p->m <= 0 || p->n <= 0 || p->k <= 0) return fail(RB_INVALID_PARAM, "g, m, n, k must be positive");
+  if (!valid_ab(p->ab_type) || !valid_c(p->c_type)) return fail(RB_INVALID_PARAM, "unknown element type");
+  return RB_SUCCESS;
+}
+
+struct Workspace {
+  size_t a_off[2], b_off[2];  // [0] = copy / hi, [1] = lo
+  size_t total;
+};
+
+Workspace plan_workspace(const RbGemmProblem* p, const OperandPlan& oa, const OperandPlan& ob) {
+  Workspace w{};
+  const size_t es = dtype_bytes(p->ab_type);
+  const bool split = p->ab_type == RB_F32 && p->f32_mode == 0;
+  size_t off = 0;
+  const size_t a_bytes = align_up((size_t)p->g * oa.rows * oa.pitch * es, 256);
+  const size_t b_bytes = align_up((size_t)p->g * ob.rows * ob.pitch * es, 256);
+  if (split || oa.needs_copy) { w.a_off[0] = off; off += a_bytes; }
+  if (split) { w.a_off[1] = off; off += a_bytes; }
+  if (split || ob.needs_copy) { w.b_off[0] = off; off += b_bytes; }
+  if (split) { w.b_off[1] = off; off += b_bytes; }
+  w.total = off;
+  return w;
+}
+
+std::once_flag g_attr_once;
+int g_max_pairs_2cta = -1;
+
+}  // namespace
+}  // namespace rb
+
+using namespace rb;
+
+extern "C" void rbSetGemmVariant(int variant) { t_variant = variant; }
+
+extern "C" size_t rbGemmWorkspaceSize(const RbGemmProblem* p) {
+  if (check_problem(p) != RB_SUCCESS) return 0;
+  const size_t es = dtype_bytes(p->ab_type);
+  const OperandPlan oa = plan_operand(p->trans_a != 0, p->m, p->k, es);
+  const OperandPlan ob = plan_operand(p->trans_b == 0, p->n, p->k, es);
+  return plan_workspace(p, oa, ob).total;
+}
+
+extern "C" RbStatus rbGemm(const RbGemmProblem* p, const RbEpilogue* epi, const void* a, const void* b, void* c,
+                           void* workspace, size_t workspace_bytes, void* stream_v) {
+  RbStatus st = check_problem(p);
+  if (st != RB_SUCCESS) return st;
+  if (!a || !b || !c) return fail(RB_INVALID_PARAM, "a, b and c must be device pointers");
+  const DeviceInfo* dev = device_info();
+  if (!dev) return RB_CUDA_ERROR;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+
+  const int abt = p->ab_type;
+  const size_t es = dtype_bytes(abt);
+  const bool is_int = abt == RB_I8;
+  const uint32_t flags = epi ? epi->flags : 0u;
+  if (is_int && flags == 0 && p->c_type != RB_I32)
+    return fail(RB_UNSUPPORTED, "i8 x i8 without an epilogue produces i32 (rocmlir-gen: -t i8 implies an i32 result)");
+  if (!is_int && p->c_type == RB_I32) return fail(RB_UNSUPPORTED, "float inputs cannot produce an i32 result");
+  if (epi) {
+    if ((flags & RB_EPI_COL_SCALE) && !epi->col_scale) return fail(RB_INVALID_PARAM, "col_scale is NULL");
+    if ((flags & RB_EPI_BIAS) && !epi->bias) return fail(RB_INVALID_PARAM, "bias is NULL");
+    if ((flags & RB_EPI_BIAS) && !(epi->bias_type == RB_F32 || epi->bias_type == RB_F16 || epi->bias_type == RB_BF16))
+      return fail(RB_INVALID_PARAM, "bias_type must be f32, f16 or bf16");
+  }
+
+  int kind;
+  uint32_t fmt, cfmt = 1;
+  switch (abt) {
+    case RB_F16: kind = kKindF16; fmt = 0; break;
+    case RB_BF16: kind = kKindF16; fmt = 1; break;
+    case RB_F32: kind = kKindTF32; fmt = 2; break;
+    case RB_I8: kind = kKindI8; fmt = 1; cfmt = 2; break;
+    default: kind = kKindF8; fmt = 0; break;
+  }
+
+  const bool a_mn = p->trans_a != 0;  // A stored G x K x M
+  const bool b_mn = p->trans_b == 0;  // B stored G x K x N
+  const OperandPlan oa = plan_operand(a_mn, p->m, p->k, es);
+  const OperandPlan ob = plan_operand(b_mn, p->n, p->k, es);
+  const Workspace ws = plan_workspace(p, oa, ob);
+  if (ws.total > 0) {
+    if (!workspace || workspace_bytes < ws.total)
+      return fail(RB_WORKSPACE_TOO_SMALL, "workspace of " + std::to_string(ws.total) + " bytes required");
+    if (reinterpret_cast<uintptr_t>(workspace) % 16) return fail(RB_INVALID_PARAM, "workspace must be 16-byte aligned");
+  }
+  if ((reinterpret_cast<uintptr_t>(a) % 16 && !(oa.needs_copy || (abt == RB_F32 && p->f32_mode == 0))) ||
+      (reinterpret_cast<uintptr_t>(b) % 16 && !(ob.needs_copy || (abt == RB_F32 && p->f32_mode == 0))))
+    return fail(RB_UNSUPPORTED, "operand base addresses must be 16-byte aligned");
+
+  const bool split = abt == RB_F32 && p->f32_mode == 0;
+  uint8_t* wsb = static_cast<uint8_t*>(workspace);
+  const void* a_src[2] = {a, nullptr};
+  const void* b_src[2] = {b, nullptr};
+  if (split) {
+    float* ahi = reinterpret_cast<float*>(wsb + ws.a_off[0]);
+    float* alo = reinterpret_cast<float*>(wsb + ws.a_off[1]);
+    float* bhi = reinterpret_cast<float*>(wsb + ws.b_off[0]);
+    float* blo = reinterpret_cast<float*>(wsb + ws.b_off[1]);
+    split_tf32_kernel<<<dev->sm_count * 4, 256, 0, stream>>>(static_cast<const float*>(a), ahi, alo,
+                                                             (long long)p->g * oa.rows, oa.cols, oa.pitch);
+    split_tf32_kernel<<<dev->sm_count * 4, 256, 0, stream>>>(static_cast<const float*>(b), bhi, blo,
+                                                             (long long)p->g * ob.rows, ob.cols, ob.pitch);
+    count_launch(2);
+    a_src[0] = ahi; a_src[1] = alo;
+    b_src[0] = bhi; b_src[1] = blo;
+  } else {
+    if (oa.needs_copy) {
+      pad_rows_kernel<<<dev->sm_count * 4, 256, 0, stream>>>(static_cast<const uint8_t*>(a), wsb + ws.a_off[0],
+                                                           (long long)p->g * oa.rows, (int)(oa.cols * es),
+                                                           (int)(oa.pitch * es));
+      count_launch();
+      a_src[0] = wsb + ws.a_off[0];
+    }
+    if (ob.needs_copy) {
+      pad_rows_kernel<<<dev->sm_count * 4, 256, 0, stream>>>(static_cast<const uint8_t*>(b), wsb + ws.b_off[0],
+                                                           (long long)p->g * ob.rows, (int)(ob.cols * es),
+                                                           (int)(ob.pitch * es));
+      count_launch();
+      b_src[0] = wsb + ws.b_off[0];
+    }
+  }
+
+  // Variant: 1 = one CTA per 128x256 tile, 2 = CTA pair per 256x256 tile.
+  int ctas = (t_variant == 2) ? 2 : 1;
+
+  const int bke = (int)(kRowBytes / es);
+  GemmTensorMaps maps;
+  memset(&maps, 0, sizeof(maps));
+  CUtensorMapDataType dt = abt == RB_F16   ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                           : abt == RB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                           : abt == RB_F32  ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                            : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  auto encode_operand = [&](CUtensorMap* m, const void* base, const OperandPlan& o, int box_rows_kmajor,
+                            std::string* err) {
+    const uint64_t dims[3] = {(uint64_t)o.cols, (uint64_t)o.rows, (uint64_t)p->g};
+    const uint64_t strides[2] = {(uint64_t)o.pitch * es, (uint64_t)o.rows * o.pitch * es};
+    // K-major: box = BKE k-elements x tile rows. MN-major: box = one 128-byte chunk of MN x BKE k-rows.
+    const uint32_t box[3] = {(uint32_t)bke, (uint32_t)(o.mn_major ? bke : box_rows_kmajor), 1u};
+    return encode_tiled(m, dt, 3, base, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, err);
+  };
+  std::string err;
+  // Segment order for the split: (lo,hi), (hi,lo), (hi,hi) so that the small terms are summed first.
+  const int nseg = split ? 3 : 1;
+  const int seg_a[3] = {split ? 1 : 0, 0, 0};
+  const int seg_b[3] = {0, 1, 0};
+  for (int s = 0; s < nseg; ++s) {
+    if (!encode_operand(&maps.a[s], a_src[seg_a[s]], oa, kBM, &err)) return fail(RB_UNSUPPORTED, "A: " + err);
+    if (!encode_operand(&maps.b[s], b_src[seg_b[s]], ob, kBN / ctas, &err)) return fail(RB_UNSUPPORTED, "B: " + err);
+  }
+
+  GemmParams kp;
+  memset(&kp, 0, sizeof(kp));
+  kp.G = p->g; kp.M = p->m; kp.N = p->n; kp.K = p->k;
+  kp.tiles_m = (p->m + kBM * ctas - 1) / (kBM * ctas);
+  kp.tiles_n = (p->n + kBN - 1) / kBN;
+  kp.kblocks = (p->k + bke - 1) / bke;
+  kp.nseg = nseg;
+  kp.idesc = make_idesc(cfmt, fmt, fmt, a_mn ? 1u : 0u, b_mn ? 1u : 0u, (uint32_t)(kBM * ctas), (uint32_t)kBN);
+  kp.acc_is_int = is_int ? 1 : 0;
+  kp.c = c;
+  kp.c_type = p->c_type;
+  const size_t es_c = dtype_bytes(p->c_type);
+  if (p->trans_c) { kp.c_stride_m = 1; kp.c_stride_n = p->m; } else { kp.c_stride_m = p->n; kp.c_stride_n = 1; }
+  kp.c_stride_g = (long long)p->m * p->n;
+  kp.vec_ok = (!p->trans_c && ((size_t)p->n * es_c) % 16 == 0 && reinterpret_cast<uintptr_t>(c) % 16 == 0) ? 1 : 0;
+  if (epi) {
+    kp.epi.flags = epi->flags; kp.epi.alpha = epi->alpha; kp.epi.out_recip = epi->out_recip;
+    kp.epi.mid_type = epi->mid_type; kp.epi.bias_type = epi->bias_type;
+    kp.epi.col_scale = epi->col_scale; kp.epi.bias = epi->bias;
+  }
+  kp.status = dev->status_word;
+
+  const long long num_tiles = (long long)kp.G * kp.tiles_m * kp.tiles_n;
+  if (num_tiles > 0x7fffffffLL) return fail(RB_UNSUPPORTED, "too many tiles");
+
+  GemmKernel kern = ctas == 2 ? pick_kernel<2>(kind, a_mn, b_mn) : pick_kernel<1>(kind, a_mn, b_mn);
+  const int smem = ctas == 2 ? GemmSmemLayout<2>::kTotal : GemmSmemLayout<1>::kTotal;
+  RB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.blockDim = dim3(kGemmThreads, 1, 1);
+  cfg.dynamicSmemBytes = (size_t)smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if (ctas == 2) {
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int pairs = dev->sm_count / 2;
+    cfg.gridDim = dim3((unsigned)(2 * (int)std::min<long long>(num_tiles, pairs)), 1, 1);
+  } else {
+    cfg.gridDim = dim3((unsigned)std::min<long long>(num_tiles, dev->sm_count), 1, 1);
+  }
+  RB_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, maps, kp));
+  count_launch();
+  return RB_SUCCESS;
+}

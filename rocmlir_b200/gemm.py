@@ -1,0 +1,130 @@
+"""Host-side mirror of rock.gemm (mlir/include/mlir/Dialect/Rock/IR/RockOps.td:136-181) over the C ABI.
+
+Operands are CUDA torch tensors used only as device buffers: A is G x M x K (trans_a: G x K x M),
+B is G x K x N (trans_b: G x N x K), C is G x M x N (trans_c: G x N x M) — the flat row-major
+buffers rocmlir-gen's kernels take. 2-D tensors are treated as G = 1.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Optional
+
+import numpy as np
+import torch
+
+from . import _lib as L
+
+_TORCH2RB = {torch.float32: L.F32, torch.float16: L.F16, torch.bfloat16: L.BF16, torch.int8: L.I8,
+             torch.int32: L.I32, torch.float8_e4m3fn: L.F8E4M3}
+_RB2TORCH = {v: k for k, v in _TORCH2RB.items()}
+
+
+def rb_dtype(t: torch.dtype) -> int:
+    if t not in _TORCH2RB:
+        raise L.RbError(L.INVALID_PARAM, f"unsupported element type {t}")
+    return _TORCH2RB[t]
+
+
+def torch_dtype(t: int) -> torch.dtype:
+    return _RB2TORCH[t]
+
+
+@dataclass
+class Epilogue:
+    """Fused elementwise tail of the GEMM; fields map one-to-one onto RbEpilogue."""
+    alpha: Optional[float] = None               # per-tensor scale product (fp8 dequantisation)
+    col_scale: Optional[torch.Tensor] = None    # f32 [N], dequantizelinear scale per output column
+    bias: Optional[torch.Tensor] = None         # [N], f32 / f16 / bf16
+    relu: bool = False
+    requant_scale: Optional[float] = None       # quantizelinear scale; the kernel multiplies by fl32(1/scale)
+    mid_type: Optional[int] = None              # declared GEMM result type: round to it before/after the bias add
+
+    def to_c(self) -> L.RbEpilogue:
+        e = L.RbEpilogue()
+        flags = 0
+        if self.alpha is not None:
+            flags |= L.EPI_ALPHA
+            e.alpha = float(np.float32(self.alpha))
+        if self.col_scale is not None:
+            assert self.col_scale.dtype == torch.float32 and self.col_scale.is_cuda and self.col_scale.is_contiguous()
+            flags |= L.EPI_COL_SCALE
+            e.col_scale = self.col_scale.data_ptr()
+        if self.bias is not None:
+            assert self.bias.is_cuda and self.bias.is_contiguous()
+            flags |= L.EPI_BIAS
+            e.bias = self.bias.data_ptr()
+            e.bias_type = rb_dtype(self.bias.dtype)
+        if self.relu:
+            flags |= L.EPI_RELU
+        if self.requant_scale is not None:
+            flags |= L.EPI_REQUANT
+            e.out_recip = float(np.float32(1.0) / np.float32(self.requant_scale))
+        if self.mid_type is not None:
+            flags |= L.EPI_ROUND_MID
+            e.mid_type = int(self.mid_type)
+        e.flags = flags
+        return e
+
+
+def _as3d(t: torch.Tensor) -> torch.Tensor:
+    return t.unsqueeze(0) if t.dim() == 2 else t
+
+
+def problem(a: torch.Tensor, b: torch.Tensor, trans_a: bool, trans_b: bool, trans_c: bool, out_dtype: torch.dtype,
+            f32_mode: int = 0) -> L.RbGemmProblem:
+    a3, b3 = _as3d(a), _as3d(b)
+    g = a3.shape[0]
+    m, k = (a3.shape[2], a3.shape[1]) if trans_a else (a3.shape[1], a3.shape[2])
+    kb, n = (b3.shape[2], b3.shape[1]) if trans_b else (b3.shape[1], b3.shape[2])
+    if kb != k or b3.shape[0] != g:
+        raise L.RbError(L.INVALID_PARAM, f"shape mismatch: A {tuple(a.shape)} B {tuple(b.shape)}")
+    if a.dtype != b.dtype:
+        raise L.RbError(L.UNSUPPORTED, "mixed A/B element types are not supported")
+    return L.RbGemmProblem(g, m, n, k, int(trans_a), int(trans_b), int(trans_c), rb_dtype(a.dtype),
+                           rb_dtype(out_dtype), int(f32_mode))
+
+
+def default_out_dtype(ab: torch.dtype) -> torch.dtype:
+    # rocmlir-gen: -t i8 => i32 result, -t fp8 => f32 result (rocmlir-gen.cpp:432-458)
+    if ab == torch.int8:
+        return torch.int32
+    if ab == torch.float8_e4m3fn:
+        return torch.float32
+    return ab
+
+
+def workspace_size(p: L.RbGemmProblem) -> int:
+    return int(L.lib().rbGemmWorkspaceSize(C.byref(p)))
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bool = False, trans_c: bool = False,
+         out_dtype: Optional[torch.dtype] = None, epilogue: Optional[Epilogue] = None,
+         out: Optional[torch.Tensor] = None, workspace: Optional[torch.Tensor] = None, f32_mode: int = 0,
+         variant: Optional[int] = None) -> torch.Tensor:
+    if not (a.is_cuda and b.is_cuda):
+        raise L.RbError(L.CUDA_ERROR, "operands must be CUDA tensors (the library has no CPU path)")
+    if not (a.is_contiguous() and b.is_contiguous()):
+        raise L.RbError(L.INVALID_PARAM, "operands must be contiguous")
+    out_dtype = out_dtype or default_out_dtype(a.dtype)
+    p = problem(a, b, trans_a, trans_b, trans_c, out_dtype, f32_mode)
+    shape = (p.g, p.n, p.m) if trans_c else (p.g, p.m, p.n)
+    if out is None:
+        out = torch.empty(shape, dtype=out_dtype, device=a.device)
+    else:
+        assert out.is_contiguous() and out.dtype == out_dtype and out.numel() == p.g * p.m * p.n
+    ws_bytes = workspace_size(p)
+    if ws_bytes and (workspace is None or workspace.numel() * workspace.element_size() < ws_bytes):
+        workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=a.device)
+    e = epilogue.to_c() if epilogue is not None else None
+    lib = L.lib()
+    if variant is not None:
+        lib.rbSetGemmVariant(int(variant))
+    stream = torch.cuda.current_stream(a.device).cuda_stream
+    st = lib.rbGemm(C.byref(p), C.byref(e) if e is not None else None, a.data_ptr(), b.data_ptr(), out.data_ptr(),
+                    workspace.data_ptr() if workspace is not None else None,
+                    workspace.numel() * workspace.element_size() if workspace is not None else 0, stream)
+    L.check(st)
+    if a.dim() == 2 and b.dim() == 2:
+        out = out.view(shape[1], shape[2])
+    return out
