@@ -1,0 +1,286 @@
+#!/usr/bin/env python
+"""Benchmark of the contraction hot path on B200.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (N = 1 and per rank for N > 1): the fp16 GEMM of the headline configuration,
+C = A.B with M = N = K = 4096, A and B row-major, f32 accumulate, f16 output, A,B ~ 0.1 * N(0,1) from
+a seed. One step = one pass over a batch of `--sets` independent operand sets (distinct A, B, C buffers,
+8 by default = 805 MB, larger than the 126 MB L2, so every GEMM of a step reads cold operands).
+Ranks hold independent batches (no data-path collective): weak scaling.
+
+Prints ONE JSON line (rank 0): device-resident throughput (`value`), the same metric through the
+host-buffer entry point with the copies timed (`e2e`), the roofline of the GEMM kernel, the clocks seen
+under load, and a CPU baseline (the reference's validation loop nest restated in oracle/, timed on a
+bounded sample of the same workload).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+M = N = K = 4096
+FLOPS_PER_GEMM = 2.0 * M * N * K                      # perfRunner.py:627-630 convention: 2*g*m*k*n
+BYTES_PER_GEMM = 3 * M * N * 2                        # each operand read once, C written once, f16
+METRIC = "TFLOP/s, fp16 GEMM M=N=K=4096 (rock.gemm, f32 accumulate, f16 out)"
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of gemm_tcgen05_kernel on this workload, from the
+# ncu capture summarised in profiles/gemm_f16_4096_ncu.md (None until a capture exists).
+NCU_DRAM_BYTES_PER_LAUNCH = None
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            d = json.load(open(path))
+            return {"burst": float(d["bf16_tflops"]), "sustained": float(d["bf16_tflops_sustained"]),
+                    "hbm": float(d["hbm_gbs"]), "source": "measured"}
+        except Exception:
+            pass
+    return {"burst": 1590.0, "sustained": 1400.0, "hbm": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.samples, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "50"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            f = [x.strip() for x in s.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx = float(f[1])
+            except ValueError:
+                continue
+            for nm, v in zip(names, f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def make_operands(sets: int, seed: int, device):
+    """A, B ~ 0.1 * N(0,1) rounded to f16; generated on the host from a seeded stream, then copied."""
+    import numpy as np
+    import torch
+    out = []
+    rng = np.random.Generator(np.random.PCG64(seed))
+    for _ in range(sets):
+        a = (rng.standard_normal((M, K), dtype=np.float32) * np.float32(0.1)).astype(np.float16)
+        b = (rng.standard_normal((K, N), dtype=np.float32) * np.float32(0.1)).astype(np.float16)
+        out.append((torch.from_numpy(a).pin_memory(), torch.from_numpy(b).pin_memory()))
+    return out
+
+
+def cpu_reference_sample(seconds_target: float, threads: int):
+    """Times the oracle's rock.gemm loop nest (the reference's CPU validation path) on a row sample of the
+    4096^3 problem and returns (TFLOP/s, description)."""
+    import numpy as np
+    import oracle
+    rng = np.random.Generator(np.random.PCG64(1))
+    b = oracle.round_to((rng.standard_normal((1, K, N), dtype=np.float32) * np.float32(0.1)), oracle.F16)
+    rows = max(threads, 8)
+    a = oracle.round_to((rng.standard_normal((1, rows, K), dtype=np.float32) * np.float32(0.1)), oracle.F16)
+    t0 = time.perf_counter()
+    oracle.gemm_f32(a, b, 1, rows, N, K, threads=threads)
+    dt = time.perf_counter() - t0
+    # scale the sample so that it takes about seconds_target, then time that
+    rows2 = int(min(M, max(rows, rows * seconds_target / max(dt, 1e-6))))
+    rows2 = max(threads, rows2 // threads * threads)
+    a = oracle.round_to((rng.standard_normal((1, rows2, K), dtype=np.float32) * np.float32(0.1)), oracle.F16)
+    t0 = time.perf_counter()
+    oracle.gemm_f32(a, b, 1, rows2, N, K, threads=threads)
+    dt = time.perf_counter() - t0
+    tflops = 2.0 * rows2 * N * K / dt / 1e12
+    return tflops, dt, f"{rows2} of {M} rows of one 4096^3 GEMM (f32-widened operands, k innermost), {dt:.1f} s"
+
+
+def run_reference(args, rank: int, world: int):
+    """--impl reference: the reference's own CPU implementation of the path. Its validator is generated MLIR
+    that needs mlir-cpu-runner (not buildable here), so the timed code is the oracle port of that loop nest."""
+    if rank != 0:
+        return
+    import oracle
+    threads = oracle.max_threads()
+    vals = []
+    per_step = max(2.0, min(20.0, 120.0 / max(1, args.steps + args.warmup)))
+    for i in range(args.warmup + args.steps):
+        tf, dt, desc = cpu_reference_sample(per_step, threads)
+        if i >= args.warmup:
+            vals.append((tf, dt))
+    tflops = sum(v[0] for v in vals) / len(vals)
+    ms = 1e3 * sum(v[1] for v in vals) / len(vals)
+    line = {"impl": "reference", "metric": METRIC, "value": tflops, "unit": "TFLOP/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": "fp16 GEMM 4096x4096x4096, A,B ~ 0.1*N(0,1)", "sample_per_step": desc},
+            "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": desc},
+            "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--sets", type=int, default=8, help="independent operand sets per step")
+    ap.add_argument("--variant", type=int, default=0)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (used for ncu captures)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import torch
+    import torch.distributed as dist
+    from rocmlir_b200 import _lib as L
+    from rocmlir_b200.gemm import gemm, gemm_host
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    distributed = world > 1
+    if distributed:
+        dist.init_process_group("nccl", device_id=dev)
+
+    host_sets = make_operands(args.sets, seed=1 + rank, device=dev)
+    dev_sets = [(a.to(dev), b.to(dev), torch.empty((M, N), dtype=torch.float16, device=dev)) for a, b in host_sets]
+    variant = args.variant if args.variant else None
+
+    def step_device():
+        for a, b, c in dev_sets:
+            gemm(a, b, out=c, variant=variant)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if distributed:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step_device()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = L.launch_count()
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step_device()
+    e1.record()
+    barrier()
+    launches = L.launch_count() - launches0
+    ms_total = e0.elapsed_time(e1)
+    status = L.kernel_status()
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- end to end: host buffers in, host result out, through rbGemmHost (copies inside the timed region) ----
+    host_out = torch.empty((M, N), dtype=torch.float16).pin_memory()
+    e2e_steps = max(2, min(args.steps, 5))
+    e2e_ms_total = float("nan")
+    if not args.no_e2e:
+        for a, b in host_sets[:2]:
+            gemm_host(a, b, host_out, variant=variant)
+        barrier()
+        e0.record()
+        for _ in range(e2e_steps):
+            for a, b in host_sets:
+                gemm_host(a, b, host_out, variant=variant)
+        e1.record()
+        barrier()
+        e2e_ms_total = e0.elapsed_time(e1)
+
+    t = torch.tensor([ms_total, e2e_ms_total], dtype=torch.float64, device=dev)
+    if distributed:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total, e2e_ms_total = t.tolist()
+
+    if rank == 0:
+        peaks = measured_peaks()
+        ms_per_step = ms_total / args.steps
+        total_flops = FLOPS_PER_GEMM * args.sets * args.steps * world
+        value = total_flops / (ms_total * 1e-3) / 1e12
+        e2e_value = FLOPS_PER_GEMM * args.sets * e2e_steps * world / (e2e_ms_total * 1e-3) / 1e12
+        per_launch_ms = ms_total / max(1, launches)
+        achieved = FLOPS_PER_GEMM / (per_launch_ms * 1e-3) / 1e12
+        peak_kind = "burst" if ms_total < 1000.0 else "sustained"
+        peak = peaks[peak_kind]
+        line = {
+            "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": "fp16 GEMM 4096x4096x4096, A,B row-major, f32 accumulate, f16 out, A,B ~ 0.1*N(0,1)",
+                       "gemms_per_step": args.sets,
+                       "l2": f"inputs larger than L2: {args.sets} operand sets = {args.sets * BYTES_PER_GEMM / 1e6:.0f} MB per step",
+                       "parallelism": f"{world} independent replicas of the batch (weak scaling, no collective)",
+                       "kernel_variant": args.variant, "kernel_status": status},
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                         "frac": achieved / peak,
+                         "peak_source": f"{peaks['source']} cuBLAS bf16 {peak_kind} (timed region {ms_total:.0f} ms)",
+                         "frac_of_nominal_2250": achieved / 2250.0,
+                         "traffic": NCU_DRAM_BYTES_PER_LAUNCH, "algorithmic_bytes": BYTES_PER_GEMM,
+                         "kernel": "gemm_tcgen05_kernel", "avg_launch_ms": per_launch_ms},
+            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": args.sets * 2 * M * K * 2,
+                    "d2h_bytes_per_step": args.sets * M * N * 2, "steps": e2e_steps,
+                    "api": "rbGemmHost (pinned host A, B -> device, GEMM, C -> host, stream sync)"},
+            "gpu_launches": int(launches), "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            import oracle
+            threads = oracle.max_threads()
+            tf, dt, desc = cpu_reference_sample(12.0, threads)
+            line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": desc}
+        print(json.dumps(line), flush=True)
+    if distributed:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

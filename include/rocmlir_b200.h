@@ -103,6 +103,13 @@ RB_EXPORT size_t rbGemmWorkspaceSize(const RbGemmProblem *p);
 RB_EXPORT RbStatus rbGemm(const RbGemmProblem *p, const RbEpilogue *epi /* may be NULL */, const void *a, const void *b,
                 void *c, void *workspace, size_t workspace_bytes, void *stream);
 
+/* Same operation on HOST buffers: copies A and B (and the epilogue vectors, whose pointers are host
+ * pointers here) to the device, runs rbGemm, copies C back and waits for `stream`. Counterpart of the
+ * `<kernel>_gpu` wrapper of rocmlir-gen's host harness (mlir/tools/rocmlir-gen/rocmlir-gen.cpp:1211-1283).
+ * Device staging memory is a grow-only arena owned by the calling thread (cudaMalloc on first use or growth). */
+RB_EXPORT RbStatus rbGemmHost(const RbGemmProblem *p, const RbEpilogue *epi_host /* may be NULL */, const void *a_host,
+                              const void *b_host, void *c_host, void *stream);
+
 /* Kernel-selection knob for tuning/experiments: tile variant used by subsequent rbGemm calls on this
  * thread's library state. 0 = automatic (measured table). Mirrors the role of rocMLIR's perf_config
  * (mlir/include/mlir/Dialect/Rock/Tuning/GridwiseGemmParams.h:138-194). */

@@ -25,29 +25,59 @@ __global__ void pad_rows_kernel(const uint8_t* __restrict__ src, uint8_t* __rest
   }
 }
 
-// x = hi + lo (+ O(2^-22 |x|)), hi and lo both exactly representable in TF32 (low 13 bits zero).
-// Rows are re-pitched at the same time (pitch in elements).
-__global__ void split_tf32_kernel(const float* __restrict__ src, float* __restrict__ hi, float* __restrict__ lo,
-                                  long long rows, int cols, int pitch) {
-  const long long total = rows * pitch;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
-       i += (long long)gridDim.x * blockDim.x) {
-    const long long r = i / pitch;
-    const int c = (int)(i - r * pitch);
-    float h = 0.f, l = 0.f;
-    if (c < cols) {
-      const float x = src[r * cols + c];
-      const uint32_t xb = __float_as_uint(x);
-      // round-to-nearest (ties away) onto 10 mantissa bits; inf/nan pass through the mask unchanged
-      const uint32_t hb = ((xb & 0x7F800000u) == 0x7F800000u) ? xb : ((xb + 0x1000u) & 0xFFFFE000u);
-      h = __uint_as_float(hb);
-      const float rem = x - h;
-      const uint32_t rb_ = __float_as_uint(rem);
-      l = __uint_as_float(((rb_ & 0x7F800000u) == 0x7F800000u) ? 0u : ((rb_ + 0x1000u) & 0xFFFFE000u));
-      if ((xb & 0x7F800000u) == 0x7F800000u) l = 0.f;
+// f32 operands are re-laid into K-major planes in the workspace before the TF32 MMA: an MN-major
+// operand is transposed (the 32-bit MN-major shared-memory layout needs a different swizzle mode, so
+// the kernel keeps a single K-major path for TF32), rows are pitched to a multiple of 16 bytes, and with
+// SPLIT the value is separated into x = hi + lo (+ O(2^-22 |x|)) with hi and lo both exactly
+// representable in TF32 (low 13 mantissa bits zero), so that hi*hi + hi*lo + lo*hi carries fp32-class
+// accuracy whatever the tensor core does with the low bits.
+//   src: [G][R][C] row-major.  TRANSPOSE = false: out [G][R][pitch] (pitch >= C)
+//                              TRANSPOSE = true : out [G][C][pitch] (pitch >= R)
+__device__ __forceinline__ float tf32_round(float x) {
+  const uint32_t xb = __float_as_uint(x);
+  if ((xb & 0x7F800000u) == 0x7F800000u) return x;  // inf / nan
+  return __uint_as_float((xb + 0x1000u) & 0xFFFFE000u);
+}
+template <bool TRANSPOSE, bool SPLIT>
+__global__ void f32_prepare_kernel(const float* __restrict__ src, float* __restrict__ hi, float* __restrict__ lo,
+                                   int R, int C, int pitch) {
+  __shared__ float tile[32][33];
+  const long long g = blockIdx.z;
+  const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  const float* s = src + g * (long long)R * C;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = r0 + threadIdx.y + 8 * i, c = c0 + threadIdx.x;
+    tile[threadIdx.y + 8 * i][threadIdx.x] = (r < R && c < C) ? s[(long long)r * C + c] : 0.0f;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float x;
+    long long o;
+    bool ok;
+    if (TRANSPOSE) {
+      const int oc = c0 + threadIdx.y + 8 * i;  // output row = source column
+      const int orr = r0 + threadIdx.x;         // output column = source row
+      x = tile[threadIdx.x][threadIdx.y + 8 * i];
+      ok = oc < C && orr < pitch;
+      o = (g * C + oc) * (long long)pitch + orr;
+    } else {
+      const int r = r0 + threadIdx.y + 8 * i, c = c0 + threadIdx.x;
+      x = tile[threadIdx.y + 8 * i][threadIdx.x];
+      ok = r < R && c < pitch;
+      o = (g * R + r) * (long long)pitch + c;
     }
-    hi[i] = h;
-    lo[i] = l;
+    if (ok) {
+      if (SPLIT) {
+        const float h = tf32_round(x);
+        const float l = isfinite(h) ? tf32_round(x - h) : 0.0f;
+        hi[o] = h;
+        lo[o] = l;
+      } else {
+        hi[o] = x;
+      }
+    }
   }
 }
 
@@ -65,30 +95,35 @@ template <int CTAS>
 GemmKernel pick_kernel(int kind, bool a_mn, bool b_mn) {
   switch (kind) {
     case kKindF16: return pick_major<kKindF16, CTAS>(a_mn, b_mn);
-    case kKindTF32: return pick_major<kKindTF32, CTAS>(a_mn, b_mn);
+    case kKindTF32: return gemm_tcgen05_kernel<kKindTF32, false, false, CTAS>;  // f32 operands are made K-major first
     case kKindI8: return pick_major<kKindI8, CTAS>(a_mn, b_mn);
     default: return pick_major<kKindF8, CTAS>(a_mn, b_mn);
   }
 }
 
 struct OperandPlan {
-  bool mn_major;        // contiguous dimension is M/N (not K)
-  long long rows;       // rows per batch of the stored matrix
-  int cols;             // contiguous extent
-  int pitch;            // elements per row after padding
-  bool needs_copy;      // pitch != cols or split required
+  bool src_mn_major;    // as stored by the caller: contiguous dimension is M/N (not K)
+  bool mn_major;        // as the kernel sees it (after a transposing copy, if any)
+  int src_rows, src_cols;  // stored matrix per batch
+  long long rows;       // rows per batch as the kernel sees it
+  int cols;             // contiguous extent as the kernel sees it
+  int pitch;            // elements per row as the kernel sees it
+  bool needs_copy;      // operand goes through the workspace
 };
 
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
-OperandPlan plan_operand(bool mn_major, int mn, int k, size_t es) {
+OperandPlan plan_operand(bool mn_major, int mn, int k, size_t es, bool is_f32, bool split) {
   OperandPlan o;
-  o.mn_major = mn_major;
-  o.rows = mn_major ? k : mn;
-  o.cols = mn_major ? mn : k;
+  o.src_mn_major = mn_major;
+  o.src_rows = mn_major ? k : mn;
+  o.src_cols = mn_major ? mn : k;
+  o.mn_major = is_f32 ? false : mn_major;
+  o.rows = o.mn_major ? k : mn;
+  o.cols = o.mn_major ? mn : k;
   const int elems16 = (int)(16 / es);
   o.pitch = (o.cols + elems16 - 1) / elems16 * elems16;
-  o.needs_copy = o.pitch != o.cols;
+  o.needs_copy = o.pitch != o.cols || (is_f32 && (split || mn_major));
   return o;
 }
 
@@ -114,16 +149,14 @@ Workspace plan_workspace(const RbGemmProblem* p, const OperandPlan& oa, const Op
   size_t off = 0;
   const size_t a_bytes = align_up((size_t)p->g * oa.rows * oa.pitch * es, 256);
   const size_t b_bytes = align_up((size_t)p->g * ob.rows * ob.pitch * es, 256);
-  if (split || oa.needs_copy) { w.a_off[0] = off; off += a_bytes; }
+  if (oa.needs_copy) { w.a_off[0] = off; off += a_bytes; }
   if (split) { w.a_off[1] = off; off += a_bytes; }
-  if (split || ob.needs_copy) { w.b_off[0] = off; off += b_bytes; }
+  if (ob.needs_copy) { w.b_off[0] = off; off += b_bytes; }
   if (split) { w.b_off[1] = off; off += b_bytes; }
   w.total = off;
   return w;
 }
 
-std::once_flag g_attr_once;
-int g_max_pairs_2cta = -1;
 
 }  // namespace
 }  // namespace rb
@@ -135,8 +168,9 @@ extern "C" void rbSetGemmVariant(int variant) { t_variant = variant; }
 extern "C" size_t rbGemmWorkspaceSize(const RbGemmProblem* p) {
   if (check_problem(p) != RB_SUCCESS) return 0;
   const size_t es = dtype_bytes(p->ab_type);
-  const OperandPlan oa = plan_operand(p->trans_a != 0, p->m, p->k, es);
-  const OperandPlan ob = plan_operand(p->trans_b == 0, p->n, p->k, es);
+  const bool f32 = p->ab_type == RB_F32, split = f32 && p->f32_mode == 0;
+  const OperandPlan oa = plan_operand(p->trans_a != 0, p->m, p->k, es, f32, split);
+  const OperandPlan ob = plan_operand(p->trans_b == 0, p->n, p->k, es, f32, split);
   return plan_workspace(p, oa, ob).total;
 }
 
@@ -173,36 +207,51 @@ extern "C" RbStatus rbGemm(const RbGemmProblem* p, const RbEpilogue* epi, const 
     default: kind = kKindF8; fmt = 0; break;
   }
 
-  const bool a_mn = p->trans_a != 0;  // A stored G x K x M
-  const bool b_mn = p->trans_b == 0;  // B stored G x K x N
-  const OperandPlan oa = plan_operand(a_mn, p->m, p->k, es);
-  const OperandPlan ob = plan_operand(b_mn, p->n, p->k, es);
+  const bool is_f32 = abt == RB_F32;
+  const bool split = is_f32 && p->f32_mode == 0;
+  const OperandPlan oa = plan_operand(p->trans_a != 0 /* A stored G x K x M */, p->m, p->k, es, is_f32, split);
+  const OperandPlan ob = plan_operand(p->trans_b == 0 /* B stored G x K x N */, p->n, p->k, es, is_f32, split);
+  const bool a_mn = oa.mn_major, b_mn = ob.mn_major;
   const Workspace ws = plan_workspace(p, oa, ob);
   if (ws.total > 0) {
     if (!workspace || workspace_bytes < ws.total)
       return fail(RB_WORKSPACE_TOO_SMALL, "workspace of " + std::to_string(ws.total) + " bytes required");
     if (reinterpret_cast<uintptr_t>(workspace) % 16) return fail(RB_INVALID_PARAM, "workspace must be 16-byte aligned");
   }
-  if ((reinterpret_cast<uintptr_t>(a) % 16 && !(oa.needs_copy || (abt == RB_F32 && p->f32_mode == 0))) ||
-      (reinterpret_cast<uintptr_t>(b) % 16 && !(ob.needs_copy || (abt == RB_F32 && p->f32_mode == 0))))
+  if ((reinterpret_cast<uintptr_t>(a) % 16 && !oa.needs_copy) || (reinterpret_cast<uintptr_t>(b) % 16 && !ob.needs_copy))
     return fail(RB_UNSUPPORTED, "operand base addresses must be 16-byte aligned");
 
-  const bool split = abt == RB_F32 && p->f32_mode == 0;
   uint8_t* wsb = static_cast<uint8_t*>(workspace);
   const void* a_src[2] = {a, nullptr};
   const void* b_src[2] = {b, nullptr};
-  if (split) {
-    float* ahi = reinterpret_cast<float*>(wsb + ws.a_off[0]);
-    float* alo = reinterpret_cast<float*>(wsb + ws.a_off[1]);
-    float* bhi = reinterpret_cast<float*>(wsb + ws.b_off[0]);
-    float* blo = reinterpret_cast<float*>(wsb + ws.b_off[1]);
-    split_tf32_kernel<<<dev->sm_count * 4, 256, 0, stream>>>(static_cast<const float*>(a), ahi, alo,
-                                                             (long long)p->g * oa.rows, oa.cols, oa.pitch);
-    split_tf32_kernel<<<dev->sm_count * 4, 256, 0, stream>>>(static_cast<const float*>(b), bhi, blo,
-                                                             (long long)p->g * ob.rows, ob.cols, ob.pitch);
-    count_launch(2);
-    a_src[0] = ahi; a_src[1] = alo;
-    b_src[0] = bhi; b_src[1] = blo;
+  auto prepare_f32 = [&](const void* src, const OperandPlan& o, float* hi, float* lo) {
+    const dim3 blk(32, 8, 1);
+    // the grid covers the padded extent of whichever dimension becomes the output row pitch
+    const int cx = o.src_mn_major ? o.src_cols : o.pitch, ry = o.src_mn_major ? o.pitch : o.src_rows;
+    const dim3 grd((cx + 31) / 32, (ry + 31) / 32, p->g);
+    const float* s = static_cast<const float*>(src);
+    if (o.src_mn_major) {
+      if (split) f32_prepare_kernel<true, true><<<grd, blk, 0, stream>>>(s, hi, lo, o.src_rows, o.src_cols, o.pitch);
+      else f32_prepare_kernel<true, false><<<grd, blk, 0, stream>>>(s, hi, lo, o.src_rows, o.src_cols, o.pitch);
+    } else {
+      if (split) f32_prepare_kernel<false, true><<<grd, blk, 0, stream>>>(s, hi, lo, o.src_rows, o.src_cols, o.pitch);
+      else f32_prepare_kernel<false, false><<<grd, blk, 0, stream>>>(s, hi, lo, o.src_rows, o.src_cols, o.pitch);
+    }
+    count_launch();
+  };
+  if (is_f32) {
+    if (oa.needs_copy) {
+      float* hi = reinterpret_cast<float*>(wsb + ws.a_off[0]);
+      float* lo = split ? reinterpret_cast<float*>(wsb + ws.a_off[1]) : nullptr;
+      prepare_f32(a, oa, hi, lo);
+      a_src[0] = hi; a_src[1] = lo;
+    }
+    if (ob.needs_copy) {
+      float* hi = reinterpret_cast<float*>(wsb + ws.b_off[0]);
+      float* lo = split ? reinterpret_cast<float*>(wsb + ws.b_off[1]) : nullptr;
+      prepare_f32(b, ob, hi, lo);
+      b_src[0] = hi; b_src[1] = lo;
+    }
   } else {
     if (oa.needs_copy) {
       pad_rows_kernel<<<dev->sm_count * 4, 256, 0, stream>>>(static_cast<const uint8_t*>(a), wsb + ws.a_off[0],

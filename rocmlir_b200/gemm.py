@@ -128,3 +128,41 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bo
     if a.dim() == 2 and b.dim() == 2:
         out = out.view(shape[1], shape[2])
     return out
+
+
+def gemm_host(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, trans_a: bool = False, trans_b: bool = False,
+              trans_c: bool = False, epilogue: Optional[Epilogue] = None, f32_mode: int = 0,
+              variant: Optional[int] = None, device: Optional[torch.device] = None) -> torch.Tensor:
+    """rbGemmHost: A, B and the result are HOST tensors (pinned memory makes the copies asynchronous); the
+    call returns when the result is in `out`. Epilogue vectors, if any, are host tensors too."""
+    if a.is_cuda or b.is_cuda or out.is_cuda:
+        raise L.RbError(L.INVALID_PARAM, "gemm_host takes host tensors")
+    p = problem(a, b, trans_a, trans_b, trans_c, out.dtype, f32_mode)
+    assert out.is_contiguous() and out.numel() == p.g * p.m * p.n
+    e = None
+    if epilogue is not None:
+        # build the struct from host pointers
+        cs, bs = epilogue.col_scale, epilogue.bias
+        e = L.RbEpilogue()
+        tmp = Epilogue(alpha=epilogue.alpha, relu=epilogue.relu, requant_scale=epilogue.requant_scale,
+                       mid_type=epilogue.mid_type).to_c()
+        e.flags, e.alpha, e.out_recip, e.mid_type = tmp.flags, tmp.alpha, tmp.out_recip, tmp.mid_type
+        if cs is not None:
+            assert not cs.is_cuda and cs.dtype == torch.float32
+            e.flags |= L.EPI_COL_SCALE
+            e.col_scale = cs.data_ptr()
+        if bs is not None:
+            assert not bs.is_cuda
+            e.flags |= L.EPI_BIAS
+            e.bias = bs.data_ptr()
+            e.bias_type = rb_dtype(bs.dtype)
+    lib = L.lib()
+    if variant is not None:
+        lib.rbSetGemmVariant(int(variant))
+    dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+    with torch.cuda.device(dev):
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        st = lib.rbGemmHost(C.byref(p), C.byref(e) if e is not None else None, a.data_ptr(), b.data_ptr(),
+                            out.data_ptr(), stream)
+    L.check(st)
+    return out
