@@ -61,6 +61,8 @@ def lib() -> C.CDLL:
                                  C.c_void_p]
         l.rbSetGemmVariant.restype = None
         l.rbSetGemmVariant.argtypes = [C.c_int]
+        l.rbSetTraceBuffer.restype = None
+        l.rbSetTraceBuffer.argtypes = [C.c_void_p, C.c_size_t]
         l.rbReadKernelStatus.restype = C.c_int
         l.rbReadKernelStatus.argtypes = [C.POINTER(C.c_uint32), C.c_int]
         l.rbLaunchCount.restype = C.c_uint64

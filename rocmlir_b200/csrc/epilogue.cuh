@@ -78,23 +78,26 @@ __device__ __forceinline__ void store_elem(void* base, long long idx, float x, i
   }
 }
 
-// Pack 32 consecutive f32 values into the C type and write them with 16-byte stores.
-// `dst` must be 16-byte aligned.
-__device__ __forceinline__ void store_row32_vec(void* dst, const float* x, int t) {
-  uint4* d = reinterpret_cast<uint4*>(dst);
+// Packs 32 consecutive f32 values into the C type: 8 (4-byte types), 4 (2-byte) or 2 (1-byte) 16-byte
+// words in `out`; returns that count.
+__device__ __forceinline__ int pack_row32(const float* x, int t, uint4* out) {
   if (t == RB_F32) {
 #pragma unroll
     for (int i = 0; i < 8; ++i)
-      d[i] = make_uint4(__float_as_uint(x[4 * i]), __float_as_uint(x[4 * i + 1]), __float_as_uint(x[4 * i + 2]),
-                        __float_as_uint(x[4 * i + 3]));
-  } else if (t == RB_I32) {
+      out[i] = make_uint4(__float_as_uint(x[4 * i]), __float_as_uint(x[4 * i + 1]), __float_as_uint(x[4 * i + 2]),
+                          __float_as_uint(x[4 * i + 3]));
+    return 8;
+  }
+  if (t == RB_I32) {
 #pragma unroll
     for (int i = 0; i < 8; ++i)
-      d[i] = make_uint4((uint32_t)f32_to_int_sat(x[4 * i], INT32_MIN, INT32_MAX),
-                        (uint32_t)f32_to_int_sat(x[4 * i + 1], INT32_MIN, INT32_MAX),
-                        (uint32_t)f32_to_int_sat(x[4 * i + 2], INT32_MIN, INT32_MAX),
-                        (uint32_t)f32_to_int_sat(x[4 * i + 3], INT32_MIN, INT32_MAX));
-  } else if (t == RB_F16) {
+      out[i] = make_uint4((uint32_t)f32_to_int_sat(x[4 * i], INT32_MIN, INT32_MAX),
+                          (uint32_t)f32_to_int_sat(x[4 * i + 1], INT32_MIN, INT32_MAX),
+                          (uint32_t)f32_to_int_sat(x[4 * i + 2], INT32_MIN, INT32_MAX),
+                          (uint32_t)f32_to_int_sat(x[4 * i + 3], INT32_MIN, INT32_MAX));
+    return 8;
+  }
+  if (t == RB_F16) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       uint32_t w[4];
@@ -103,9 +106,11 @@ __device__ __forceinline__ void store_row32_vec(void* dst, const float* x, int t
         __half2 h = __floats2half2_rn(x[8 * i + 2 * j], x[8 * i + 2 * j + 1]);
         w[j] = *reinterpret_cast<uint32_t*>(&h);
       }
-      d[i] = make_uint4(w[0], w[1], w[2], w[3]);
+      out[i] = make_uint4(w[0], w[1], w[2], w[3]);
     }
-  } else if (t == RB_BF16) {
+    return 4;
+  }
+  if (t == RB_BF16) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       uint32_t w[4];
@@ -114,26 +119,28 @@ __device__ __forceinline__ void store_row32_vec(void* dst, const float* x, int t
         __nv_bfloat162 h = __floats2bfloat162_rn(x[8 * i + 2 * j], x[8 * i + 2 * j + 1]);
         w[j] = *reinterpret_cast<uint32_t*>(&h);
       }
-      d[i] = make_uint4(w[0], w[1], w[2], w[3]);
+      out[i] = make_uint4(w[0], w[1], w[2], w[3]);
     }
-  } else {  // 8-bit outputs
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      uint32_t w[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        uint32_t b = 0;
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          float v = x[16 * i + 4 * j + k];
-          uint32_t byte = (t == RB_I8) ? (uint32_t)(uint8_t)(int8_t)f32_to_int_sat(v, -128, 127) : (uint32_t)f32_to_e4m3(v);
-          b |= byte << (8 * k);
-        }
-        w[j] = b;
-      }
-      d[i] = make_uint4(w[0], w[1], w[2], w[3]);
-    }
+    return 4;
   }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {  // 8-bit outputs
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint32_t b = 0;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float v = x[16 * i + 4 * j + k];
+        const uint32_t byte =
+            (t == RB_I8) ? (uint32_t)(uint8_t)(int8_t)f32_to_int_sat(v, -128, 127) : (uint32_t)f32_to_e4m3(v);
+        b |= byte << (8 * k);
+      }
+      w[j] = b;
+    }
+    out[i] = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+  return 2;
 }
 
 }  // namespace rb

@@ -11,6 +11,8 @@ namespace rb {
 namespace {
 
 thread_local int t_variant = 0;
+thread_local unsigned long long* t_trace = nullptr;
+thread_local size_t t_trace_len = 0;
 
 // ---- auxiliary kernels ---------------------------------------------------------------------------
 // Copies `rows` rows of `row_bytes` bytes into rows of `pitch_bytes` bytes, zero-filling the pad.
@@ -164,6 +166,7 @@ Workspace plan_workspace(const RbGemmProblem* p, const OperandPlan& oa, const Op
 using namespace rb;
 
 extern "C" void rbSetGemmVariant(int variant) { t_variant = variant; }
+extern "C" void rbSetTraceBuffer(unsigned long long* device_buf, size_t n_u64) { t_trace = device_buf; t_trace_len = n_u64; }
 
 extern "C" size_t rbGemmWorkspaceSize(const RbGemmProblem* p) {
   if (check_problem(p) != RB_SUCCESS) return 0;
@@ -269,8 +272,12 @@ extern "C" RbStatus rbGemm(const RbGemmProblem* p, const RbEpilogue* epi, const 
     }
   }
 
-  // Variant: 1 = one CTA per 128x256 tile, 2 = CTA pair per 256x256 tile.
-  int ctas = (t_variant == 2) ? 2 : 1;
+  // Variant word: bits 0-3: 1 = one CTA per 128x256 tile, 2 = CTA pair per 256x256 tile (0 = automatic);
+  // bits 4-7: ring depth (0 = deepest that fits); bit 8: write C with plain stores instead of TMA stores.
+  int ctas = ((t_variant & 0xF) == 1) ? 1 : 2;
+  int stages = (t_variant >> 4) & 0xF;
+  const int max_stages = ctas == 2 ? GemmSmemLayout<2>::kMaxStages : GemmSmemLayout<1>::kMaxStages;
+  if (stages <= 0 || stages > max_stages) stages = max_stages;
 
   const int bke = (int)(kRowBytes / es);
   GemmTensorMaps maps;
@@ -312,18 +319,32 @@ extern "C" RbStatus rbGemm(const RbGemmProblem* p, const RbEpilogue* epi, const 
   if (p->trans_c) { kp.c_stride_m = 1; kp.c_stride_n = p->m; } else { kp.c_stride_m = p->n; kp.c_stride_n = 1; }
   kp.c_stride_g = (long long)p->m * p->n;
   kp.vec_ok = (!p->trans_c && ((size_t)p->n * es_c) % 16 == 0 && reinterpret_cast<uintptr_t>(c) % 16 == 0) ? 1 : 0;
+  kp.c_tma = (kp.vec_ok && !((t_variant >> 8) & 1)) ? 1 : 0;
+  if (kp.c_tma) {
+    const CUtensorMapDataType cdt = p->c_type == RB_F16    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                    : p->c_type == RB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                    : p->c_type == RB_F32  ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                    : p->c_type == RB_I32  ? CU_TENSOR_MAP_DATA_TYPE_INT32
+                                                           : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+    const uint64_t cdims[3] = {(uint64_t)p->n, (uint64_t)p->m, (uint64_t)p->g};
+    const uint64_t cstrides[2] = {(uint64_t)p->n * es_c, (uint64_t)p->m * p->n * es_c};
+    const uint32_t cbox[3] = {(uint32_t)(kRowBytes / es_c), 32u, 1u};
+    if (!encode_tiled(&maps.c, cdt, 3, c, cdims, cstrides, cbox, CU_TENSOR_MAP_SWIZZLE_128B, &err))
+      return fail(RB_UNSUPPORTED, "C: " + err);
+  }
   if (epi) {
     kp.epi.flags = epi->flags; kp.epi.alpha = epi->alpha; kp.epi.out_recip = epi->out_recip;
     kp.epi.mid_type = epi->mid_type; kp.epi.bias_type = epi->bias_type;
     kp.epi.col_scale = epi->col_scale; kp.epi.bias = epi->bias;
   }
   kp.status = dev->status_word;
+  kp.stages = stages;
 
   const long long num_tiles = (long long)kp.G * kp.tiles_m * kp.tiles_n;
   if (num_tiles > 0x7fffffffLL) return fail(RB_UNSUPPORTED, "too many tiles");
 
   GemmKernel kern = ctas == 2 ? pick_kernel<2>(kind, a_mn, b_mn) : pick_kernel<1>(kind, a_mn, b_mn);
-  const int smem = ctas == 2 ? GemmSmemLayout<2>::kTotal : GemmSmemLayout<1>::kTotal;
+  const int smem = ctas == 2 ? GemmSmemLayout<2>::total(stages) : GemmSmemLayout<1>::total(stages);
   RB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
 
   cudaLaunchConfig_t cfg;
@@ -342,6 +363,7 @@ extern "C" RbStatus rbGemm(const RbGemmProblem* p, const RbEpilogue* epi, const 
   } else {
     cfg.gridDim = dim3((unsigned)std::min<long long>(num_tiles, dev->sm_count), 1, 1);
   }
+  kp.trace = (t_trace && t_trace_len >= (size_t)cfg.gridDim.x * 16) ? t_trace : nullptr;
   RB_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, maps, kp));
   count_launch();
   return RB_SUCCESS;

@@ -48,6 +48,7 @@ constexpr int kMaxSeg = 3;
 struct GemmTensorMaps {
   CUtensorMap a[kMaxSeg];
   CUtensorMap b[kMaxSeg];
+  CUtensorMap c;  // store map of C (box: 128 bytes of a row x 32 rows); valid when GemmParams::c_tma != 0
 };
 
 struct GemmParams {
@@ -61,8 +62,11 @@ struct GemmParams {
   long long c_stride_g, c_stride_m, c_stride_n;  // in elements
   int c_type;
   int vec_ok;                 // rows of C start 16-byte aligned and c_stride_n == 1
+  int c_tma;                  // C is written by TMA stores from a shared-memory staging tile
   EpiParams epi;
   uint32_t* status;
+  unsigned long long* trace;  // optional [gridDim.x][16] cycle counters per CTA (see rbSetTraceBuffer), or NULL
+  int stages;                 // shared-memory ring depth (<= GemmSmemLayout::kMaxStages)
 };
 
 template <int CTAS>
@@ -70,9 +74,14 @@ struct GemmSmemLayout {
   static constexpr int kABytes = kBM * kRowBytes;
   static constexpr int kBBytes = (kBN / CTAS) * kRowBytes;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = (CTAS == 1) ? 4 : 6;
+  static constexpr int kMaxStages = (CTAS == 1) ? 4 : 6;
+  // Epilogue staging: per epilogue warp two 32-row x 128-byte tiles (double buffered TMA stores).
+  static constexpr int kStoreTileBytes = 32 * kRowBytes;
+  static constexpr int kStagingBytes = 4 * 2 * kStoreTileBytes;
   static constexpr int kBarBytes = 512;
-  static constexpr int kTotal = kStages * kStageBytes + kBarBytes + 1024;  // + alignment slack
+  static constexpr int total(int stages) {
+    return stages * kStageBytes + kStagingBytes + kBarBytes + 1024;  // + alignment slack
+  }
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& g, int& mb, int& nb) {
@@ -102,12 +111,14 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kStages * L::kStageBytes);
-  uint64_t* full_bar = bars;                       // [kStages]
-  uint64_t* empty_bar = bars + L::kStages;         // [kStages]
-  uint64_t* tfull_bar = bars + 2 * L::kStages;     // [2]
-  uint64_t* tempty_bar = bars + 2 * L::kStages + 2;  // [2]
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * L::kStages + 4);
+  const int stages = p.stages;
+  uint8_t* staging = smem + stages * L::kStageBytes;  // 1024-byte aligned (stage sizes are multiples of 1024)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + L::kStagingBytes);
+  uint64_t* full_bar = bars;                       // [stages]
+  uint64_t* empty_bar = bars + stages;             // [stages]
+  uint64_t* tfull_bar = bars + 2 * stages;         // [2]
+  uint64_t* tempty_bar = bars + 2 * stages + 2;    // [2]
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * stages + 4);
 
   const int warp = threadIdx.x >> 5;
   const uint32_t rank = (CTAS == 2) ? cluster_ctarank() : 0u;
@@ -116,7 +127,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
   const int num_tiles = p.G * p.tiles_m * p.tiles_n;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < L::kStages; ++s) {
+    for (int s = 0; s < stages; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
@@ -135,6 +146,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
       prefetch_tmap(&maps.a[s]);
       prefetch_tmap(&maps.b[s]);
     }
+    if (p.c_tma) prefetch_tmap(&maps.c);
   }
   tc_fence_before();
   __syncthreads();
@@ -147,20 +159,19 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
   if (warp == 0) {
     // ------------------------------ producer ------------------------------
     if (lane_id() == 0) {
-      uint32_t it = 0;
+      uint32_t s = 0, ph = 0;
       bool ok = true;
-      // Completion of this CTA's loads is counted on the leader CTA's barrier.
+      long long w_empty = 0;
       for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
         int g, mb, nb;
         tile_coords(tile, p.tiles_m, p.tiles_n, g, mb, nb);
         const int m0 = (mb * CTAS + (int)rank) * kBM;
         const int n0 = nb * kBN + (int)rank * BN_CTA;
-        for (int kk = 0; kk < ktotal; ++kk, ++it) {
-          const int seg = kk / p.kblocks;
-          const int kb = kk - seg * p.kblocks;
-          const uint32_t s = it % L::kStages;
-          const uint32_t ph = (it / L::kStages) & 1u;
+        int seg = 0, kb = 0;
+        for (int kk = 0; kk < ktotal; ++kk) {
+          const long long tw = p.trace ? clock64() : 0;
           if (!mbar_wait(&empty_bar[s], ph ^ 1u, p.status, kStatusTimeoutProducer + s)) { ok = false; break; }
+          if (p.trace) w_empty += clock64() - tw;
           uint8_t* sa = smem + s * L::kStageBytes;
           uint8_t* sb = sa + L::kABytes;
           const int k0 = kb * BKE;
@@ -181,6 +192,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
                 tma_load_3d(sb + c * CHUNK_BYTES, &maps.b[seg], &full_bar[s], n0 + c * CHE, k0, g);
             }
           } else {
+            // Completion of this CTA's loads is counted on the leader CTA's barrier.
             const uint32_t lead_full = mapa_u32(smem_u32(&full_bar[s]), 0);
             if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * L::kStageBytes);
             if constexpr (!A_MN) {
@@ -198,44 +210,74 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
                 tma_load_3d_bar(sb + c * CHUNK_BYTES, &maps.b[seg], lead_full, n0 + c * CHE, k0, g);
             }
           }
+          if (++kb == p.kblocks) { kb = 0; ++seg; }
+          if (++s == (uint32_t)stages) { s = 0; ph ^= 1u; }
         }
       }
+      if (p.trace) p.trace[blockIdx.x * 16 + 1] = (unsigned long long)w_empty;
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer (leader CTA only) ------------------------------
+    // The tensor pipe accepts few MMAs ahead of the one it executes, so whatever the issuing thread does
+    // between two MMAs is a bubble. The full-barrier test of the NEXT stage is therefore issued before
+    // the MMAs of the current one and its result is consumed after them (its latency hides behind them).
     if (lane_id() == 0 && rank == 0) {
-      uint32_t it = 0, t = 0;
+      uint32_t s = 0, ph = 0, t = 0;
       bool ok = true;
+      long long w_full = 0, w_tempty = 0;
+      const long long t_begin = p.trace ? clock64() : 0;
+      bool ready = false;
+      // Descriptor halves: constant high word; low word of stage 0, advanced by adds only.
+      const uint32_t desc_hi = smem_desc_hi(1024);
+      const uint32_t a_lo0 = smem_desc_lo(smem_u32(smem), A_MN ? CHUNK_BYTES : 16);
+      const uint32_t b_lo0 = smem_desc_lo(smem_u32(smem) + L::kABytes, B_MN ? CHUNK_BYTES : 16);
+      constexpr uint32_t kStageStep = L::kStageBytes >> 4;
+      constexpr uint32_t kAStep = (A_MN ? KT::UMMA_K * kRowBytes : KT::UMMA_K * ES) >> 4;
+      constexpr uint32_t kBStep = (B_MN ? KT::UMMA_K * kRowBytes : KT::UMMA_K * ES) >> 4;
+      const uint32_t full0 = smem_u32(&full_bar[0]);
+      const uint32_t empty0 = smem_u32(&empty_bar[0]);
+      const uint32_t peer_off = (CTAS == 2) ? (mapa_u32(empty0, 1) - mapa_u32(empty0, 0)) : 0u;
+      const uint32_t self_off = (CTAS == 2) ? (mapa_u32(empty0, 0) - empty0) : 0u;
       for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs, ++t) {
         const uint32_t buf = t & 1u;
         const uint32_t bph = (t >> 1) & 1u;
+        const long long tw0 = p.trace ? clock64() : 0;
         if (!mbar_wait(&tempty_bar[buf], bph ^ 1u, p.status, kStatusTimeoutMma + 0x10 + buf)) { ok = false; break; }
+        if (p.trace) w_tempty += clock64() - tw0;
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + buf * kBN;
-        for (int kk = 0; kk < ktotal; ++kk, ++it) {
-          const uint32_t s = it % L::kStages;
-          const uint32_t ph = (it / L::kStages) & 1u;
-          if (!mbar_wait(&full_bar[s], ph, p.status, kStatusTimeoutMma + s)) { ok = false; break; }
+        uint32_t accum = 0;
+        for (int kk = 0; kk < ktotal; ++kk) {
+          if (!ready) {
+            const long long tw = p.trace ? clock64() : 0;
+            if (!mbar_wait(&full_bar[s], ph, p.status, kStatusTimeoutMma + s)) { ok = false; break; }
+            if (p.trace) w_full += clock64() - tw;
+          }
           tc_fence_after();
-          const uint32_t sa = smem_u32(smem + s * L::kStageBytes);
-          const uint32_t sb = sa + L::kABytes;
+          uint32_t ns = s + 1, nph = ph;
+          if (ns == (uint32_t)stages) { ns = 0; nph ^= 1u; }
+          const bool next_ready = mbar_test_wait_addr(full0 + ns * 8, nph);  // consumed after the MMAs below
+          const uint32_t a_lo = a_lo0 + s * kStageStep;
+          const uint32_t b_lo = b_lo0 + s * kStageStep;
 #pragma unroll
           for (int k = 0; k < KSTEPS; ++k) {
-            const uint64_t adesc = A_MN ? make_smem_desc(sa + k * KT::UMMA_K * kRowBytes, CHUNK_BYTES, 1024)
-                                        : make_smem_desc(sa + k * KT::UMMA_K * ES, 16, 1024);
-            const uint64_t bdesc = B_MN ? make_smem_desc(sb + k * KT::UMMA_K * kRowBytes, CHUNK_BYTES, 1024)
-                                        : make_smem_desc(sb + k * KT::UMMA_K * ES, 16, 1024);
-            umma_ss<KIND, CTAS>(tmem_d, adesc, bdesc, p.idesc, (kk | k) != 0 ? 1u : 0u);
+            umma_ss<KIND, CTAS>(tmem_d, desc64(a_lo + k * kAStep, desc_hi), desc64(b_lo + k * kBStep, desc_hi), p.idesc,
+                                accum);
+            accum = 1;
           }
           // Free the stage in every CTA of the pair once these MMAs have read it.
           if constexpr (CTAS == 1) {
-            tc_commit<1>(&empty_bar[s]);
+            tc_commit_addr1(empty0 + s * 8);
           } else {
-            tc_commit_addr2(mapa_u32(smem_u32(&empty_bar[s]), 0));
-            tc_commit_addr2(mapa_u32(smem_u32(&empty_bar[s]), 1));
+            tc_commit_addr2(empty0 + s * 8 + self_off);
+            tc_commit_addr2(empty0 + s * 8 + self_off + peer_off);
           }
+          s = ns;
+          ph = nph;
+          ready = next_ready;
         }
         if (!ok) break;
+        if (p.trace && t < 8) p.trace[blockIdx.x * 16 + 8 + t] = (unsigned long long)w_full;  // cumulative, per tile
         if constexpr (CTAS == 1) {
           tc_commit<1>(&tfull_bar[buf]);
         } else {
@@ -243,22 +285,37 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
           tc_commit_addr2(mapa_u32(smem_u32(&tfull_bar[buf]), 1));
         }
       }
+      if (p.trace) {
+        p.trace[blockIdx.x * 16 + 2] = (unsigned long long)w_full;
+        p.trace[blockIdx.x * 16 + 3] = (unsigned long long)w_tempty;
+        p.trace[blockIdx.x * 16 + 4] = (unsigned long long)(clock64() - t_begin);  // MMA issue loop, total
+        p.trace[blockIdx.x * 16 + 5] = t;
+      }
     }
   } else if (warp >= 4) {
     // ------------------------------ epilogue ------------------------------
     const int q = warp & 3;
     const int lane = lane_id();
-    uint32_t t = 0;
+    const int es_c = dtype_size(p.c_type);
+    const int cols_per_store = kRowBytes / es_c;          // columns covered by one 128-byte staging row
+    const int groups_per_store = cols_per_store / 32;     // 32-column TMEM loads per staging row: 1, 2 or 4
+    const bool raw_i32 = p.acc_is_int && p.c_type == RB_I32 && p.epi.flags == 0;
+    uint8_t* my_staging = staging + q * 2 * L::kStoreTileBytes;
+    uint32_t t = 0, nstores = 0;
+    long long w_tfull = 0, e_work = 0;
     for (int tile = pair_id; tile < num_tiles; tile += num_pairs, ++t) {
       int g, mb, nb;
       tile_coords(tile, p.tiles_m, p.tiles_n, g, mb, nb);
       const uint32_t buf = t & 1u;
       const uint32_t bph = (t >> 1) & 1u;
+      const long long tw = p.trace ? clock64() : 0;
       if (!mbar_wait(&tfull_bar[buf], bph, p.status, kStatusTimeoutEpilogue + buf)) break;
+      const long long te = p.trace ? clock64() : 0;
+      w_tfull += te - tw;
       tc_fence_after();
-      const long long row = (long long)(mb * CTAS + (int)rank) * kBM + q * 32 + lane;
+      const long long row0 = (long long)(mb * CTAS + (int)rank) * kBM + q * 32;
+      const long long row = row0 + lane;
       const bool row_ok = row < p.M;
-      const int es_c = dtype_size(p.c_type);
       const long long c_row_off = (long long)g * p.c_stride_g + row * p.c_stride_m;
 #pragma unroll 1
       for (int c = 0; c < kBN / 32; ++c) {
@@ -267,37 +324,72 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
         uint32_t v[32];
         tmem_ld32(tmem_base + (uint32_t(q * 32) << 16) + buf * kBN + c * 32, v);
         tmem_ld_wait();
-        const bool raw_i32 = p.acc_is_int && p.c_type == RB_I32 && p.epi.flags == 0;
-        const bool full = (n0 + 32 <= p.N);
+        uint4 w[8];
+        int nw;
         if (raw_i32) {
-          if (row_ok) {
-            int32_t* dst = reinterpret_cast<int32_t*>(p.c);
-            if (full && p.vec_ok) {
-              uint4* d = reinterpret_cast<uint4*>(dst + c_row_off + n0);
 #pragma unroll
-              for (int i = 0; i < 8; ++i) d[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (n0 + j < p.N) dst[c_row_off + (long long)(n0 + j) * p.c_stride_n] = (int32_t)v[j];
-            }
-          }
+          for (int i = 0; i < 8; ++i) w[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+          nw = 8;
         } else {
           float x[32];
+          if (p.epi.flags == 0) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            float a = p.acc_is_int ? __int2float_rn((int)v[j]) : __uint_as_float(v[j]);
-            const long long n = min((long long)(n0 + j), (long long)p.N - 1);
-            x[j] = (p.epi.flags != 0) ? epi_apply(a, p.epi, n) : a;
+            for (int j = 0; j < 32; ++j) x[j] = p.acc_is_int ? __int2float_rn((int)v[j]) : __uint_as_float(v[j]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float a = p.acc_is_int ? __int2float_rn((int)v[j]) : __uint_as_float(v[j]);
+              x[j] = epi_apply(a, p.epi, min(n0 + j, p.N - 1));
+            }
           }
-          if (row_ok) {
-            if (full && p.vec_ok) {
-              store_row32_vec(reinterpret_cast<uint8_t*>(p.c) + (c_row_off + n0) * es_c, x, p.c_type);
-            } else {
+          if (p.c_tma || (p.vec_ok && n0 + 32 <= p.N)) {
+            nw = pack_row32(x, p.c_type, w);
+          } else {
+            nw = 0;
+            if (row_ok) {
 #pragma unroll
               for (int j = 0; j < 32; ++j)
                 if (n0 + j < p.N) store_elem(p.c, c_row_off + (long long)(n0 + j) * p.c_stride_n, x[j], p.c_type);
             }
+          }
+        }
+        if (p.c_tma) {
+          // Stage 32 rows x 128 bytes per store: row `lane` at lane * 128, its 16-byte pieces XOR-swizzled with
+          // (lane & 7) exactly as the 128-byte-swizzled store map expects (also free of bank conflicts).
+          const int sub = c % groups_per_store;
+          uint8_t* stg = my_staging + (nstores & 1u) * L::kStoreTileBytes;
+          if (sub == 0) {
+            if (lane == 0 && nstores >= 2) bulk_wait_read<1>();  // the store that last used this buffer has read it
+            __syncwarp();
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            if (i < nw) {
+              const int piece = sub * nw + i;
+              *reinterpret_cast<uint4*>(stg + lane * kRowBytes + ((piece ^ (lane & 7)) << 4)) = w[i];
+            }
+          }
+          const bool last_group = (sub == groups_per_store - 1) || (n0 + 32 >= p.N) || (c == kBN / 32 - 1);
+          if (last_group) {
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0 && row0 < p.M) {
+              tma_store_3d(&maps.c, stg, n0 - sub * 32, (int)row0, g);
+              bulk_commit();
+            }
+            ++nstores;
+          }
+        } else if (nw > 0 && row_ok) {
+          if (p.vec_ok && n0 + 32 <= p.N) {
+            uint4* d = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.c) + (c_row_off + n0) * es_c);
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              if (i < nw) d[i] = w[i];
+          } else {  // raw i32 with a ragged or strided destination
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (n0 + j < p.N)
+                reinterpret_cast<int32_t*>(p.c)[c_row_off + (long long)(n0 + j) * p.c_stride_n] = (int32_t)v[j];
           }
         }
       }
@@ -308,6 +400,12 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
         if constexpr (CTAS == 1) mbar_arrive(&tempty_bar[buf]);
         else mbar_arrive_cluster(&tempty_bar[buf], 0);
       }
+      if (p.trace) e_work += clock64() - te;
+    }
+    if (p.c_tma && lane == 0) bulk_wait<0>();  // every store of this thread has completed before the CTA exits
+    if (p.trace && warp == 4 && lane == 0) {
+      p.trace[blockIdx.x * 16 + 6] = (unsigned long long)w_tfull;
+      p.trace[blockIdx.x * 16 + 7] = (unsigned long long)e_work;
     }
   }
 
