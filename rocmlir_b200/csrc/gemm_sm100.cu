@@ -103,6 +103,84 @@ GemmKernel pick_kernel(int kind, bool a_mn, bool b_mn) {
   }
 }
 
+// ---- tile configuration -----------------------------------------------------------------------
+// The measured tile-shape table of this library, in the role of rocMLIR's perf_config heuristics
+// (mlir/lib/Dialect/Rock/Tuning/GridwiseGemmParams.cpp:384-417): tile width from N, CTA pairs whenever
+// the operand layout allows them, the deepest ring that fits, and a K split when the output has too few
+// tiles to fill the GPU (the role of split-K in mlir/lib/Dialect/Rock/Transforms/GemmToGridwise.cpp:268-394,
+// here with f32 partial planes and a fixed-order reduction instead of atomics).
+constexpr int kAssumedSMs = 148;  // B200
+
+struct GemmConfig {
+  int ctas, bn, stages, splits;
+  bool plain_stores;
+};
+
+GemmConfig choose_config(const RbGemmProblem* p, int variant) {
+  GemmConfig c;
+  const int es = (int)dtype_bytes(p->ab_type);
+  const bool b_mn = p->ab_type != RB_F32 && p->trans_b == 0;
+  const int che = kRowBytes / es;
+  const int bn_code = (variant >> 12) & 0xF;
+  c.bn = bn_code == 1 ? 64 : bn_code == 2 ? 128 : bn_code == 3 ? 256 : (p->n <= 64 ? 64 : p->n <= 128 ? 128 : 256);
+  if (b_mn && c.bn < che) c.bn = che;                       // an MN-major B tile is loaded in whole 128-byte chunks
+  c.ctas = ((variant & 0xF) == 1) ? 1 : 2;
+  if (b_mn && (c.bn / 2) % che != 0) c.ctas = 1;
+  if (p->m <= kBM && (variant & 0xF) != 2) c.ctas = 1;      // a pair would compute 128 empty rows
+  c.stages = (variant >> 4) & 0xF;
+  const int max_stages = c.ctas == 2 ? GemmSmemLayout<2>::max_stages(c.bn) : GemmSmemLayout<1>::max_stages(c.bn);
+  if (c.stages <= 0 || c.stages > max_stages) c.stages = max_stages;
+  c.plain_stores = ((variant >> 8) & 1) != 0;
+  const int bke = kRowBytes / es;
+  const long long kblocks = (p->k + bke - 1) / bke;
+  const long long tiles = (long long)p->g * ((p->m + kBM * c.ctas - 1) / (kBM * c.ctas)) * ((p->n + c.bn - 1) / c.bn);
+  const long long units = kAssumedSMs / c.ctas;
+  c.splits = (variant >> 16) & 0xFF;
+  if (c.splits == 0) {
+    c.splits = 1;
+    if (tiles * 2 <= units && kblocks >= 16) {
+      long long want = units / tiles;
+      long long cap = kblocks / 8;  // at least 8 K blocks per range
+      c.splits = (int)std::max<long long>(1, std::min<long long>(std::min(want, cap), 128));
+    }
+  }
+  if (c.splits > kblocks) c.splits = (int)kblocks;
+  // every range must be non-empty with ceil-division ranges
+  while (c.splits > 1 && (long long)(c.splits - 1) * ((kblocks + c.splits - 1) / c.splits) >= kblocks) --c.splits;
+  return c;
+}
+
+// Sums the partial planes of a K split in a fixed order (range 0, 1, 2, ...), applies the epilogue and
+// writes C. One thread per output element; consecutive threads walk consecutive columns.
+__global__ void splitk_reduce_kernel(const void* __restrict__ partial, int splits, long long plane, int G, int M, int N,
+                                     void* __restrict__ c, int c_type, int trans_c, int acc_is_int, EpiParams epi) {
+  const long long total = (long long)G * M * N;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int n = (int)(i % N);
+    const long long gm = i / N;
+    const int m = (int)(gm % M);
+    const long long g = gm / M;
+    const long long o = trans_c ? (g * N + n) * (long long)M + m : i;
+    if (acc_is_int) {
+      int acc = 0;
+      for (int s = 0; s < splits; ++s) acc += reinterpret_cast<const int*>(partial)[s * plane + i];
+      if (c_type == RB_I32 && epi.flags == 0) {
+        reinterpret_cast<int*>(c)[o] = acc;
+      } else {
+        float x = __int2float_rn(acc);
+        if (epi.flags) x = epi_apply(x, epi, n);
+        store_elem(c, o, x, c_type);
+      }
+    } else {
+      float acc = 0.0f;
+      for (int s = 0; s < splits; ++s) acc = __fadd_rn(acc, reinterpret_cast<const float*>(partial)[s * plane + i]);
+      if (epi.flags) acc = epi_apply(acc, epi, n);
+      store_elem(c, o, acc, c_type);
+    }
+  }
+}
+
 struct OperandPlan {
   bool src_mn_major;    // as stored by the caller: contiguous dimension is M/N (not K)
   bool mn_major;        // as the kernel sees it (after a transposing copy, if any)
@@ -141,10 +219,11 @@ RbStatus check_problem(const RbGemmProblem* p) {
 
 struct Workspace {
   size_t a_off[2], b_off[2];  // [0] = copy / hi, [1] = lo
+  size_t partial_off;         // K-split partial planes
   size_t total;
 };
 
-Workspace plan_workspace(const RbGemmProblem* p, const OperandPlan& oa, const OperandPlan& ob) {
+Workspace plan_workspace(const RbGemmProblem* p, const OperandPlan& oa, const OperandPlan& ob, const GemmConfig& cfg) {
   Workspace w{};
   const size_t es = dtype_bytes(p->ab_type);
   const bool split = p->ab_type == RB_F32 && p->f32_mode == 0;
@@ -155,6 +234,10 @@ Workspace plan_workspace(const RbGemmProblem* p, const OperandPlan& oa, const Op
   if (split) { w.a_off[1] = off; off += a_bytes; }
   if (ob.needs_copy) { w.b_off[0] = off; off += b_bytes; }
   if (split) { w.b_off[1] = off; off += b_bytes; }
+  if (cfg.splits > 1) {
+    w.partial_off = off;
+    off += align_up((size_t)cfg.splits * p->g * p->m * p->n * 4, 256);
+  }
   w.total = off;
   return w;
 }
@@ -174,7 +257,7 @@ extern "C" size_t rbGemmWorkspaceSize(const RbGemmProblem* p) {
   const bool f32 = p->ab_type == RB_F32, split = f32 && p->f32_mode == 0;
   const OperandPlan oa = plan_operand(p->trans_a != 0, p->m, p->k, es, f32, split);
   const OperandPlan ob = plan_operand(p->trans_b == 0, p->n, p->k, es, f32, split);
-  return plan_workspace(p, oa, ob).total;
+  return plan_workspace(p, oa, ob, choose_config(p, t_variant)).total;
 }
 
 extern "C" RbStatus rbGemm(const RbGemmProblem* p, const RbEpilogue* epi, const void* a, const void* b, void* c,
@@ -215,7 +298,8 @@ extern "C" RbStatus rbGemm(const RbGemmProblem* p, const RbEpilogue* epi, const 
   const OperandPlan oa = plan_operand(p->trans_a != 0 /* A stored G x K x M */, p->m, p->k, es, is_f32, split);
   const OperandPlan ob = plan_operand(p->trans_b == 0 /* B stored G x K x N */, p->n, p->k, es, is_f32, split);
   const bool a_mn = oa.mn_major, b_mn = ob.mn_major;
-  const Workspace ws = plan_workspace(p, oa, ob);
+  const GemmConfig cfg = choose_config(p, t_variant);
+  const Workspace ws = plan_workspace(p, oa, ob, cfg);
   if (ws.total > 0) {
     if (!workspace || workspace_bytes < ws.total)
       return fail(RB_WORKSPACE_TOO_SMALL, "workspace of " + std::to_string(ws.total) + " bytes required");
@@ -272,12 +356,10 @@ extern "C" RbStatus rbGemm(const RbGemmProblem* p, const RbEpilogue* epi, const 
     }
   }
 
-  // Variant word: bits 0-3: 1 = one CTA per 128x256 tile, 2 = CTA pair per 256x256 tile (0 = automatic);
-  // bits 4-7: ring depth (0 = deepest that fits); bit 8: write C with plain stores instead of TMA stores.
-  int ctas = ((t_variant & 0xF) == 1) ? 1 : 2;
-  int stages = (t_variant >> 4) & 0xF;
-  const int max_stages = ctas == 2 ? GemmSmemLayout<2>::kMaxStages : GemmSmemLayout<1>::kMaxStages;
-  if (stages <= 0 || stages > max_stages) stages = max_stages;
+  // Variant word (rbSetGemmVariant): bits 0-3: 1 = single CTA per tile, 2 = CTA pair (0 = automatic);
+  // bits 4-7 ring depth; bit 8 plain stores instead of TMA stores; bits 12-15 tile width code (1 = 64,
+  // 2 = 128, 3 = 256); bits 16-23 K-split count. Zero fields mean "choose" (see choose_config).
+  const int ctas = cfg.ctas, bn = cfg.bn, stages = cfg.stages, splits = cfg.splits;
 
   const int bke = (int)(kRowBytes / es);
   GemmTensorMaps maps;
@@ -301,25 +383,47 @@ extern "C" RbStatus rbGemm(const RbGemmProblem* p, const RbEpilogue* epi, const 
   const int seg_b[3] = {0, 1, 0};
   for (int s = 0; s < nseg; ++s) {
     if (!encode_operand(&maps.a[s], a_src[seg_a[s]], oa, kBM, &err)) return fail(RB_UNSUPPORTED, "A: " + err);
-    if (!encode_operand(&maps.b[s], b_src[seg_b[s]], ob, kBN / ctas, &err)) return fail(RB_UNSUPPORTED, "B: " + err);
+    if (!encode_operand(&maps.b[s], b_src[seg_b[s]], ob, bn / ctas, &err)) return fail(RB_UNSUPPORTED, "B: " + err);
   }
 
   GemmParams kp;
   memset(&kp, 0, sizeof(kp));
   kp.G = p->g; kp.M = p->m; kp.N = p->n; kp.K = p->k;
+  kp.bn = bn;
+  kp.splits = splits;
   kp.tiles_m = (p->m + kBM * ctas - 1) / (kBM * ctas);
-  kp.tiles_n = (p->n + kBN - 1) / kBN;
+  kp.tiles_n = (p->n + bn - 1) / bn;
   kp.kblocks = (p->k + bke - 1) / bke;
   kp.nseg = nseg;
-  kp.idesc = make_idesc(cfmt, fmt, fmt, a_mn ? 1u : 0u, b_mn ? 1u : 0u, (uint32_t)(kBM * ctas), (uint32_t)kBN);
+  kp.idesc = make_idesc(cfmt, fmt, fmt, a_mn ? 1u : 0u, b_mn ? 1u : 0u, (uint32_t)(kBM * ctas), (uint32_t)bn);
   kp.acc_is_int = is_int ? 1 : 0;
-  kp.c = c;
-  kp.c_type = p->c_type;
+  EpiParams ep;
+  memset(&ep, 0, sizeof(ep));
+  if (epi) {
+    ep.flags = epi->flags; ep.alpha = epi->alpha; ep.out_recip = epi->out_recip;
+    ep.mid_type = epi->mid_type; ep.bias_type = epi->bias_type;
+    ep.col_scale = epi->col_scale; ep.bias = epi->bias;
+  }
   const size_t es_c = dtype_bytes(p->c_type);
-  if (p->trans_c) { kp.c_stride_m = 1; kp.c_stride_n = p->m; } else { kp.c_stride_m = p->n; kp.c_stride_n = 1; }
-  kp.c_stride_g = (long long)p->m * p->n;
-  kp.vec_ok = (!p->trans_c && ((size_t)p->n * es_c) % 16 == 0 && reinterpret_cast<uintptr_t>(c) % 16 == 0) ? 1 : 0;
-  kp.c_tma = (kp.vec_ok && !((t_variant >> 8) & 1)) ? 1 : 0;
+  void* partial = splits > 1 ? static_cast<void*>(wsb + ws.partial_off) : nullptr;
+  if (splits > 1) {
+    // every K range writes raw accumulators into its own plane; the reduction applies the epilogue
+    kp.c = partial;
+    kp.c_type = is_int ? RB_I32 : RB_F32;
+    kp.c_stride_m = p->n; kp.c_stride_n = 1;
+    kp.c_stride_g = (long long)p->m * p->n;
+    kp.split_stride = (long long)p->g * p->m * p->n;
+    kp.vec_ok = (p->n % 4 == 0) ? 1 : 0;
+    kp.c_tma = 0;
+  } else {
+    kp.c = c;
+    kp.c_type = p->c_type;
+    if (p->trans_c) { kp.c_stride_m = 1; kp.c_stride_n = p->m; } else { kp.c_stride_m = p->n; kp.c_stride_n = 1; }
+    kp.c_stride_g = (long long)p->m * p->n;
+    kp.vec_ok = (!p->trans_c && ((size_t)p->n * es_c) % 16 == 0 && reinterpret_cast<uintptr_t>(c) % 16 == 0) ? 1 : 0;
+    kp.c_tma = (kp.vec_ok && !cfg.plain_stores) ? 1 : 0;
+    kp.epi = ep;
+  }
   if (kp.c_tma) {
     const CUtensorMapDataType cdt = p->c_type == RB_F16    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
                                     : p->c_type == RB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
@@ -332,39 +436,41 @@ extern "C" RbStatus rbGemm(const RbGemmProblem* p, const RbEpilogue* epi, const 
     if (!encode_tiled(&maps.c, cdt, 3, c, cdims, cstrides, cbox, CU_TENSOR_MAP_SWIZZLE_128B, &err))
       return fail(RB_UNSUPPORTED, "C: " + err);
   }
-  if (epi) {
-    kp.epi.flags = epi->flags; kp.epi.alpha = epi->alpha; kp.epi.out_recip = epi->out_recip;
-    kp.epi.mid_type = epi->mid_type; kp.epi.bias_type = epi->bias_type;
-    kp.epi.col_scale = epi->col_scale; kp.epi.bias = epi->bias;
-  }
   kp.status = dev->status_word;
   kp.stages = stages;
 
-  const long long num_tiles = (long long)kp.G * kp.tiles_m * kp.tiles_n;
-  if (num_tiles > 0x7fffffffLL) return fail(RB_UNSUPPORTED, "too many tiles");
+  const long long num_items = (long long)kp.G * kp.tiles_m * kp.tiles_n * splits;
+  if (num_items > 0x7fffffffLL) return fail(RB_UNSUPPORTED, "too many tiles");
 
   GemmKernel kern = ctas == 2 ? pick_kernel<2>(kind, a_mn, b_mn) : pick_kernel<1>(kind, a_mn, b_mn);
-  const int smem = ctas == 2 ? GemmSmemLayout<2>::total(stages) : GemmSmemLayout<1>::total(stages);
+  const int smem = ctas == 2 ? GemmSmemLayout<2>::total(stages, bn) : GemmSmemLayout<1>::total(stages, bn);
   RB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
 
-  cudaLaunchConfig_t cfg;
-  memset(&cfg, 0, sizeof(cfg));
-  cfg.blockDim = dim3(kGemmThreads, 1, 1);
-  cfg.dynamicSmemBytes = (size_t)smem;
-  cfg.stream = stream;
+  cudaLaunchConfig_t lc;
+  memset(&lc, 0, sizeof(lc));
+  lc.blockDim = dim3(kGemmThreads, 1, 1);
+  lc.dynamicSmemBytes = (size_t)smem;
+  lc.stream = stream;
   cudaLaunchAttribute attr[1];
   if (ctas == 2) {
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    int pairs = dev->sm_count / 2;
-    cfg.gridDim = dim3((unsigned)(2 * (int)std::min<long long>(num_tiles, pairs)), 1, 1);
+    lc.attrs = attr;
+    lc.numAttrs = 1;
+    const int pairs = dev->sm_count / 2;
+    lc.gridDim = dim3((unsigned)(2 * (int)std::min<long long>(num_items, pairs)), 1, 1);
   } else {
-    cfg.gridDim = dim3((unsigned)std::min<long long>(num_tiles, dev->sm_count), 1, 1);
+    lc.gridDim = dim3((unsigned)std::min<long long>(num_items, dev->sm_count), 1, 1);
   }
-  kp.trace = (t_trace && t_trace_len >= (size_t)cfg.gridDim.x * 16) ? t_trace : nullptr;
-  RB_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, maps, kp));
+  kp.trace = (t_trace && t_trace_len >= (size_t)lc.gridDim.x * 16) ? t_trace : nullptr;
+  RB_CUDA_TRY(cudaLaunchKernelEx(&lc, kern, maps, kp));
   count_launch();
+  if (splits > 1) {
+    const long long total = (long long)p->g * p->m * p->n;
+    const int blocks = (int)std::min<long long>((total + 255) / 256, (long long)dev->sm_count * 8);
+    splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(partial, splits, total, p->g, p->m, p->n, c, p->c_type,
+                                                     p->trans_c ? 1 : 0, is_int ? 1 : 0, ep);
+    count_launch();
+  }
   return RB_SUCCESS;
 }

@@ -24,7 +24,7 @@
 namespace rb {
 
 constexpr int kBM = 128;          // rows of C per CTA
-constexpr int kBN = 256;          // columns of C per tile
+constexpr int kMaxBN = 256;       // widest tile: columns of C per tile (GemmParams::bn selects 64, 128 or 256)
 constexpr int kRowBytes = 128;    // bytes of the contiguous dimension per shared-memory row (swizzle span)
 constexpr int kGemmThreads = 256;
 constexpr int kTmemCols = 512;
@@ -53,6 +53,9 @@ struct GemmTensorMaps {
 
 struct GemmParams {
   int G, M, N, K;
+  int bn;                     // tile width in columns of C: UMMA N (a multiple of 32 * CTAS)
+  int splits;                 // K is cut into `splits` ranges; with splits > 1 every range writes raw partial sums
+  long long split_stride;     // elements between the partial planes of consecutive ranges (splits > 1)
   int tiles_m, tiles_n;       // tiles_m counts (kBM * CTAS)-row blocks
   int kblocks;                // K blocks per segment
   int nseg;
@@ -72,15 +75,19 @@ struct GemmParams {
 template <int CTAS>
 struct GemmSmemLayout {
   static constexpr int kABytes = kBM * kRowBytes;
-  static constexpr int kBBytes = (kBN / CTAS) * kRowBytes;
-  static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kMaxStages = (CTAS == 1) ? 4 : 6;
+  static constexpr int kMaxStages = 8;
+  static constexpr int kSmemBudget = 232448;  // opt-in shared memory per CTA on sm_100
+  static constexpr int stage_bytes(int bn) { return kABytes + (bn / CTAS) * kRowBytes; }
   // Epilogue staging: per epilogue warp two 32-row x 128-byte tiles (double buffered TMA stores).
   static constexpr int kStoreTileBytes = 32 * kRowBytes;
   static constexpr int kStagingBytes = 4 * 2 * kStoreTileBytes;
   static constexpr int kBarBytes = 512;
-  static constexpr int total(int stages) {
-    return stages * kStageBytes + kStagingBytes + kBarBytes + 1024;  // + alignment slack
+  static constexpr int total(int stages, int bn) {
+    return stages * stage_bytes(bn) + kStagingBytes + kBarBytes + 1024;  // + alignment slack
+  }
+  static constexpr int max_stages(int bn) {
+    int s = (kSmemBudget - kStagingBytes - kBarBytes - 1024) / stage_bytes(bn);
+    return s > kMaxStages ? kMaxStages : s;
   }
 };
 
@@ -106,13 +113,14 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
   constexpr int BKE = kRowBytes / ES;          // K elements per stage
   constexpr int CHE = kRowBytes / ES;          // MN elements per MN-major chunk
   constexpr int KSTEPS = BKE / KT::UMMA_K;     // MMAs per stage (always 4)
-  constexpr int BN_CTA = kBN / CTAS;           // columns of B this CTA loads
   constexpr int CHUNK_BYTES = BKE * kRowBytes; // one MN-major chunk: BKE k-rows of 128 B
+  const int bn_cta = p.bn / CTAS;              // columns of B this CTA loads
+  const int stage_bytes = L::stage_bytes(p.bn);
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int stages = p.stages;
-  uint8_t* staging = smem + stages * L::kStageBytes;  // 1024-byte aligned (stage sizes are multiples of 1024)
+  uint8_t* staging = smem + stages * stage_bytes;  // 1024-byte aligned (stage sizes are multiples of 1024)
   uint64_t* bars = reinterpret_cast<uint64_t*>(staging + L::kStagingBytes);
   uint64_t* full_bar = bars;                       // [stages]
   uint64_t* empty_bar = bars + stages;             // [stages]
@@ -124,7 +132,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
   const uint32_t rank = (CTAS == 2) ? cluster_ctarank() : 0u;
   const int pair_id = blockIdx.x / CTAS;
   const int num_pairs = gridDim.x / CTAS;
-  const int num_tiles = p.G * p.tiles_m * p.tiles_n;
+  const int num_tiles = p.G * p.tiles_m * p.tiles_n * p.splits;  // work items
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
@@ -154,7 +162,8 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
-  const int ktotal = p.kblocks * p.nseg;
+  // K blocks per work item: the K range of a segment is cut into p.splits nearly equal parts.
+  const int kb_per_split = (p.kblocks + p.splits - 1) / p.splits;
 
   if (warp == 0) {
     // ------------------------------ producer ------------------------------
@@ -164,19 +173,23 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
       long long w_empty = 0;
       for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
         int g, mb, nb;
-        tile_coords(tile, p.tiles_m, p.tiles_n, g, mb, nb);
+        const int split = tile % p.splits;
+        tile_coords(tile / p.splits, p.tiles_m, p.tiles_n, g, mb, nb);
         const int m0 = (mb * CTAS + (int)rank) * kBM;
-        const int n0 = nb * kBN + (int)rank * BN_CTA;
-        int seg = 0, kb = 0;
+        const int n0 = nb * p.bn + (int)rank * bn_cta;
+        const int kb_begin = split * kb_per_split;
+        const int kb_end = min(p.kblocks, kb_begin + kb_per_split);
+        const int ktotal = (kb_end - kb_begin) * p.nseg;
+        int seg = 0, kb = kb_begin;
         for (int kk = 0; kk < ktotal; ++kk) {
           const long long tw = p.trace ? clock64() : 0;
           if (!mbar_wait(&empty_bar[s], ph ^ 1u, p.status, kStatusTimeoutProducer + s)) { ok = false; break; }
           if (p.trace) w_empty += clock64() - tw;
-          uint8_t* sa = smem + s * L::kStageBytes;
+          uint8_t* sa = smem + s * stage_bytes;
           uint8_t* sb = sa + L::kABytes;
           const int k0 = kb * BKE;
           if constexpr (CTAS == 1) {
-            mbar_expect_tx(&full_bar[s], L::kStageBytes);
+            mbar_expect_tx(&full_bar[s], stage_bytes);
             if constexpr (!A_MN) {
               tma_load_3d(sa, &maps.a[seg], &full_bar[s], k0, m0, g);
             } else {
@@ -187,14 +200,13 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
             if constexpr (!B_MN) {
               tma_load_3d(sb, &maps.b[seg], &full_bar[s], k0, n0, g);
             } else {
-#pragma unroll
-              for (int c = 0; c < BN_CTA / CHE; ++c)
+              for (int c = 0; c < bn_cta / CHE; ++c)
                 tma_load_3d(sb + c * CHUNK_BYTES, &maps.b[seg], &full_bar[s], n0 + c * CHE, k0, g);
             }
           } else {
             // Completion of this CTA's loads is counted on the leader CTA's barrier.
             const uint32_t lead_full = mapa_u32(smem_u32(&full_bar[s]), 0);
-            if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * L::kStageBytes);
+            if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * stage_bytes);
             if constexpr (!A_MN) {
               tma_load_3d_bar(sa, &maps.a[seg], lead_full, k0, m0, g);
             } else {
@@ -205,12 +217,11 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
             if constexpr (!B_MN) {
               tma_load_3d_bar(sb, &maps.b[seg], lead_full, k0, n0, g);
             } else {
-#pragma unroll
-              for (int c = 0; c < BN_CTA / CHE; ++c)
+              for (int c = 0; c < bn_cta / CHE; ++c)
                 tma_load_3d_bar(sb + c * CHUNK_BYTES, &maps.b[seg], lead_full, n0 + c * CHE, k0, g);
             }
           }
-          if (++kb == p.kblocks) { kb = 0; ++seg; }
+          if (++kb == kb_end) { kb = kb_begin; ++seg; }
           if (++s == (uint32_t)stages) { s = 0; ph ^= 1u; }
         }
       }
@@ -231,7 +242,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
       const uint32_t desc_hi = smem_desc_hi(1024);
       const uint32_t a_lo0 = smem_desc_lo(smem_u32(smem), A_MN ? CHUNK_BYTES : 16);
       const uint32_t b_lo0 = smem_desc_lo(smem_u32(smem) + L::kABytes, B_MN ? CHUNK_BYTES : 16);
-      constexpr uint32_t kStageStep = L::kStageBytes >> 4;
+      const uint32_t kStageStep = (uint32_t)stage_bytes >> 4;
       constexpr uint32_t kAStep = (A_MN ? KT::UMMA_K * kRowBytes : KT::UMMA_K * ES) >> 4;
       constexpr uint32_t kBStep = (B_MN ? KT::UMMA_K * kRowBytes : KT::UMMA_K * ES) >> 4;
       const uint32_t full0 = smem_u32(&full_bar[0]);
@@ -245,8 +256,10 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
         if (!mbar_wait(&tempty_bar[buf], bph ^ 1u, p.status, kStatusTimeoutMma + 0x10 + buf)) { ok = false; break; }
         if (p.trace) w_tempty += clock64() - tw0;
         tc_fence_after();
-        const uint32_t tmem_d = tmem_base + buf * kBN;
+        const uint32_t tmem_d = tmem_base + buf * kMaxBN;
         uint32_t accum = 0;
+        const int kb_begin = (tile % p.splits) * kb_per_split;
+        const int ktotal = (min(p.kblocks, kb_begin + kb_per_split) - kb_begin) * p.nseg;
         for (int kk = 0; kk < ktotal; ++kk) {
           if (!ready) {
             const long long tw = p.trace ? clock64() : 0;
@@ -305,7 +318,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
     long long w_tfull = 0, e_work = 0;
     for (int tile = pair_id; tile < num_tiles; tile += num_pairs, ++t) {
       int g, mb, nb;
-      tile_coords(tile, p.tiles_m, p.tiles_n, g, mb, nb);
+      tile_coords(tile / p.splits, p.tiles_m, p.tiles_n, g, mb, nb);
       const uint32_t buf = t & 1u;
       const uint32_t bph = (t >> 1) & 1u;
       const long long tw = p.trace ? clock64() : 0;
@@ -316,13 +329,15 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
       const long long row0 = (long long)(mb * CTAS + (int)rank) * kBM + q * 32;
       const long long row = row0 + lane;
       const bool row_ok = row < p.M;
-      const long long c_row_off = (long long)g * p.c_stride_g + row * p.c_stride_m;
+      const long long c_row_off =
+          (long long)(tile % p.splits) * p.split_stride + (long long)g * p.c_stride_g + row * p.c_stride_m;
+      const int ngroups = p.bn / 32;
 #pragma unroll 1
-      for (int c = 0; c < kBN / 32; ++c) {
-        const int n0 = nb * kBN + c * 32;
+      for (int c = 0; c < ngroups; ++c) {
+        const int n0 = nb * p.bn + c * 32;
         if (n0 >= p.N) break;  // warp-uniform
         uint32_t v[32];
-        tmem_ld32(tmem_base + (uint32_t(q * 32) << 16) + buf * kBN + c * 32, v);
+        tmem_ld32(tmem_base + (uint32_t(q * 32) << 16) + buf * kMaxBN + c * 32, v);
         tmem_ld_wait();
         uint4 w[8];
         int nw;
@@ -369,7 +384,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
               *reinterpret_cast<uint4*>(stg + lane * kRowBytes + ((piece ^ (lane & 7)) << 4)) = w[i];
             }
           }
-          const bool last_group = (sub == groups_per_store - 1) || (n0 + 32 >= p.N) || (c == kBN / 32 - 1);
+          const bool last_group = (sub == groups_per_store - 1) || (n0 + 32 >= p.N) || (c == ngroups - 1);
           if (last_group) {
             fence_proxy_async();
             __syncwarp();

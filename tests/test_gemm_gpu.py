@@ -69,6 +69,30 @@ def test_int8_gemm_bit_exact(cuda_device, g, m, n, k, ta, tb, tc, variant):
     assert info["overflows"] == 0
 
 
+# Few output tiles and a long reduction: the library cuts K into ranges (partial planes + fixed-order reduction),
+# and narrow N selects the 64- and 128-column tiles. Shapes of the ResNet bwd-weight GEMMs in miniature.
+SPLITK_SHAPES = [(1, 64, 576, 8192), (1, 200, 64, 4096), (2, 130, 100, 2048), (1, 576, 64, 6272)]
+
+
+@pytest.mark.parametrize("ta,tb,tc", [(0, 0, 0), (1, 0, 1), (0, 1, 0)])
+@pytest.mark.parametrize("g,m,n,k", SPLITK_SHAPES)
+def test_split_k_and_narrow_tiles_exact(cuda_device, g, m, n, k, ta, tb, tc):
+    from rocmlir_b200 import _lib as L
+    import ctypes as C
+    prob = L.RbGemmProblem(g, m, n, k, ta, tb, tc, L.F16, L.F16, 0)
+    assert L.lib().rbGemmWorkspaceSize(C.byref(prob)) > 0, "expected a K split (workspace for partial planes)"
+    (af, araw), (bf, braw) = reference_random([(g, m, k), (g, k, n)], oracle.F16, seed=1)
+    ref = oracle.from_f32(oracle.gemm_f32(stored(af, ta), stored(bf, tb), g, m, n, k, ta, tb, tc,
+                                          threads=oracle.max_threads()), oracle.F16)
+    got = run_gemm(stored(araw, ta), stored(braw, tb), oracle.F16, oracle.F16, ta, tb, tc)
+    np.testing.assert_array_equal(got.reshape(ref.shape), ref)
+    a = uniform_int8((g, m, k), seed=41)
+    b = uniform_int8((g, k, n), seed=42)
+    refi = oracle.gemm_i8(stored(a, ta), stored(b, tb), g, m, n, k, ta, tb, tc, threads=oracle.max_threads())
+    goti = run_gemm(stored(a, ta), stored(b, tb), oracle.I8, oracle.I32, ta, tb, tc)
+    assert oracle.verify_int(goti, refi)[0] == [1, 1, 1]
+
+
 @pytest.mark.parametrize("code,scale", [(oracle.F16, 0.1), (oracle.BF16, 0.1), (oracle.F32, 1.0)])
 @pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0)])
 def test_float_gemm_normal_data_reference_verifier(cuda_device, code, scale, ta, tb):
