@@ -110,6 +110,40 @@ RB_EXPORT RbStatus rbGemm(const RbGemmProblem *p, const RbEpilogue *epi /* may b
 RB_EXPORT RbStatus rbGemmHost(const RbGemmProblem *p, const RbEpilogue *epi_host /* may be NULL */, const void *a_host,
                               const void *b_host, void *c_host, void *stream);
 
+/* rock.conv / rock.conv_bwd_data / rock.conv_bwd_weight
+ * (mlir/include/mlir/Dialect/Rock/IR/RockOps.td:87-134). Tensors are 5-D with an explicit group dimension,
+ * each stored in the order its layout string spells, as ConvGenerator canonicalises them
+ * (mlir/lib/Dialect/Rock/Generator/ConvGenerator.cpp:487-668): filter letters g k c y x, input n g c h w,
+ * output n g k h w (e.g. "gkyxc" / "nhwgc" / "nhwgk" for NHWC, "gkcyx" / "ngchw" / "ngkhw" for NCHW).
+ * c and k count channels PER GROUP. in_h = ho * stride_h + y * dil_h - pad_h, and ho, wo must equal
+ * (in + pad + pad_r - (fil - 1) * dil - 1) / stride + 1 (ConvGenerator.h:98-104).
+ * Argument order is (filter, input, output) for all three directions, as in the reference's kernels
+ * (ConvGenerator.cpp:825-830); the direction decides which one is written:
+ *   0 forward: output; 1 backward data: input; 2 backward weight: filter.
+ * i8 (forward only) produces an i32 output, like rocmlir-gen's -t i8. */
+typedef struct RbConvProblem {
+  int32_t n, g, c, k;
+  int32_t h, w, y, x;
+  int32_t stride_h, stride_w, dil_h, dil_w;
+  int32_t pad_h, pad_w, pad_h_r, pad_w_r;
+  int32_t ho, wo;
+  int32_t data_type; /* RbDType of filter, input and output (i8: output is i32) */
+  int32_t direction;
+  int32_t f32_mode;  /* as in RbGemmProblem */
+  char fil_layout[8], in_layout[8], out_layout[8];
+} RbConvProblem;
+
+/* Bytes of device workspace rbConv needs (gathered operand matrices, split-K planes); the counterpart of
+ * miirGetWorkspaceSize (mlir/tools/rocmlir-lib/Miir.h:60-66). 0 also for an invalid problem. */
+RB_EXPORT size_t rbConvWorkspaceSize(const RbConvProblem *p);
+
+/* Number of kernels one rbConv call launches besides those inside its GEMM (counterpart of
+ * miirGetKernelCount, Miir.h:54-58); -1 for an invalid problem. */
+RB_EXPORT int rbConvKernelCount(const RbConvProblem *p);
+
+RB_EXPORT RbStatus rbConv(const RbConvProblem *p, void *filter, void *input, void *output, void *workspace,
+                          size_t workspace_bytes, void *stream);
+
 /* Kernel-selection knob for tuning/experiments: tile variant used by subsequent rbGemm calls on this
  * thread's library state. 0 = automatic (measured table). Mirrors the role of rocMLIR's perf_config
  * (mlir/include/mlir/Dialect/Rock/Tuning/GridwiseGemmParams.h:138-194). */

@@ -35,6 +35,13 @@ class RbGemmProblem(C.Structure):
                 ("f32_mode", C.c_int32)]
 
 
+class RbConvProblem(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("n", "g", "c", "k", "h", "w", "y", "x", "stride_h", "stride_w", "dil_h",
+                                         "dil_w", "pad_h", "pad_w", "pad_h_r", "pad_w_r", "ho", "wo", "data_type",
+                                         "direction", "f32_mode")] + \
+               [("fil_layout", C.c_char * 8), ("in_layout", C.c_char * 8), ("out_layout", C.c_char * 8)]
+
+
 class RbError(RuntimeError):
     def __init__(self, status: int, msg: str):
         super().__init__(f"{STATUS_NAMES[status] if 0 <= status < len(STATUS_NAMES) else status}: {msg}")
@@ -59,6 +66,13 @@ def lib() -> C.CDLL:
         l.rbGemmHost.restype = C.c_int
         l.rbGemmHost.argtypes = [C.POINTER(RbGemmProblem), C.POINTER(RbEpilogue), C.c_void_p, C.c_void_p, C.c_void_p,
                                  C.c_void_p]
+        l.rbConvWorkspaceSize.restype = C.c_size_t
+        l.rbConvWorkspaceSize.argtypes = [C.POINTER(RbConvProblem)]
+        l.rbConvKernelCount.restype = C.c_int
+        l.rbConvKernelCount.argtypes = [C.POINTER(RbConvProblem)]
+        l.rbConv.restype = C.c_int
+        l.rbConv.argtypes = [C.POINTER(RbConvProblem), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t,
+                             C.c_void_p]
         l.rbSetGemmVariant.restype = None
         l.rbSetGemmVariant.argtypes = [C.c_int]
         l.rbSetTraceBuffer.restype = None

@@ -1,0 +1,328 @@
+// rock.conv / rock.conv_bwd_data / rock.conv_bwd_weight as GEMMs on the tcgen05 kernel.
+//
+// rocMLIR views the three tensors of a convolution as matrices through coordinate maps and runs its GEMM
+// kernel on the views (mlir/lib/Dialect/Rock/Transforms/ConvToGemm.cpp:1133-1400 forward / backward weight,
+// :770-1131 backward data; sizes in mlir/lib/Dialect/Rock/IR/RockDialect.cpp:509-533). This file does the same
+// with explicit matrices: an operand that already is a row-major matrix in its storage layout (NHWC activations
+// of a 1x1 stride-1 convolution, a KYXC filter, an NHWK output) is handed to the GEMM as it lies; anything else
+// is gathered into (or scattered from) a matrix in the caller's workspace by the kernels below.
+//
+//   forward      out[(n,ho,wo), k]   = sum_{y,x,c} im2col(in)[(n,ho,wo), (y,x,c)] * fil[k, (y,x,c)]
+//   backward wt  fil[k, (y,x,c)]     = sum_{n,ho,wo} out[(n,ho,wo), k] * im2col(in)[(n,ho,wo), (y,x,c)]
+//   backward dat in[(n,h,w), c]      = sum_{y,x,k} col2im(out)[(n,h,w), (y,x,k)] * fil[(y,x,k), c]
+// Groups are the GEMM batch dimension. Index relation and output-size rule are the reference's
+// (in_h = ho*stride + y*dil - pad; mlir/include/mlir/Dialect/Rock/Generator/ConvGenerator.h:98-104).
+#include <cuda_runtime.h>
+#include <string.h>
+
+#include <algorithm>
+#include <string>
+
+#include "lib_state.h"
+
+namespace rb {
+namespace {
+
+struct Dims5 {
+  long long size[5];
+  long long stride[5];
+};
+
+// Copies a 5-D tensor between a strided layout and the dense row-major layout of `size`.
+// to_dense: dst[dense] = src[strided]; else dst[strided] = src[dense]. ES = element bytes.
+template <int ES>
+__global__ void permute5_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, Dims5 d, int to_dense) {
+  const long long total = d.size[0] * d.size[1] * d.size[2] * d.size[3] * d.size[4];
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    long long r = i, off = 0;
+#pragma unroll
+    for (int k = 4; k >= 0; --k) {
+      const long long q = r / d.size[k];
+      off += (r - q * d.size[k]) * d.stride[k];
+      r = q;
+    }
+    const long long s = to_dense ? off : i, t = to_dense ? i : off;
+    if (ES == 1) dst[t] = src[s];
+    if (ES == 2) reinterpret_cast<uint16_t*>(dst)[t] = reinterpret_cast<const uint16_t*>(src)[s];
+    if (ES == 4) reinterpret_cast<uint32_t*>(dst)[t] = reinterpret_cast<const uint32_t*>(src)[s];
+  }
+}
+
+struct GatherParams {
+  // matrix: [G][rows = N * P * Q][cols = Y * X * CH], dense, row pitch `pitch` elements
+  long long N, G, P, Q, Y, X, CH;
+  long long pitch;
+  // source tensor (n, g, ch, a, b) strides in elements and image extent
+  long long s_n, s_g, s_ch, s_a, s_b;
+  long long A, B;
+  // index relation
+  long long stride_h, stride_w, dil_h, dil_w, pad_h, pad_w;
+  int transposed;  // 0: a = p*stride + y*dil - pad (im2col); 1: a = (p + pad - y*dil) / stride when divisible (col2im)
+};
+
+template <int ES>
+__global__ void conv_gather_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, GatherParams g) {
+  const long long cols = g.Y * g.X * g.CH;
+  const long long rows = g.N * g.P * g.Q;
+  const long long total = g.G * rows * g.pitch;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long col = i % g.pitch;
+    long long r = i / g.pitch;
+    const long long row = r % rows;
+    const long long grp = r / rows;
+    bool ok = col < cols;
+    long long off = 0;
+    if (ok) {
+      const long long ch = col % g.CH;
+      const long long t = col / g.CH;
+      const long long x = t % g.X, y = t / g.X;
+      const long long q = row % g.Q;
+      const long long t2 = row / g.Q;
+      const long long pp = t2 % g.P, n = t2 / g.P;
+      long long a, b;
+      if (!g.transposed) {
+        a = pp * g.stride_h + y * g.dil_h - g.pad_h;
+        b = q * g.stride_w + x * g.dil_w - g.pad_w;
+      } else {
+        const long long ta = pp + g.pad_h - y * g.dil_h, tb = q + g.pad_w - x * g.dil_w;
+        ok = ta >= 0 && tb >= 0 && ta % g.stride_h == 0 && tb % g.stride_w == 0;
+        a = ta / g.stride_h;
+        b = tb / g.stride_w;
+      }
+      ok = ok && a >= 0 && a < g.A && b >= 0 && b < g.B;
+      off = n * g.s_n + grp * g.s_g + ch * g.s_ch + a * g.s_a + b * g.s_b;
+    }
+    if (ES == 1) dst[i] = ok ? src[off] : (uint8_t)0;
+    if (ES == 2) reinterpret_cast<uint16_t*>(dst)[i] = ok ? reinterpret_cast<const uint16_t*>(src)[off] : (uint16_t)0;
+    if (ES == 4) reinterpret_cast<uint32_t*>(dst)[i] = ok ? reinterpret_cast<const uint32_t*>(src)[off] : 0u;
+  }
+}
+
+size_t up256(size_t x) { return (x + 255) / 256 * 256; }
+
+// Named-dimension strides of a tensor stored in `layout` order (row-major over the letters).
+bool layout_strides(const char* layout, const char* letters, const long long* sizes, long long* strides,
+                    std::string* canon) {
+  if (!layout || strlen(layout) != 5) return false;
+  long long acc = 1;
+  bool seen[5] = {false, false, false, false, false};
+  for (int pos = 4; pos >= 0; --pos) {
+    const char* f = strchr(letters, layout[pos]);
+    if (!f) return false;
+    const int idx = (int)(f - letters);
+    if (seen[idx]) return false;
+    seen[idx] = true;
+    strides[idx] = acc;
+    acc *= sizes[idx];
+  }
+  if (canon) *canon = layout;
+  return true;
+}
+
+struct ConvPlan {
+  // tensors: strides for fil (g,k,c,y,x), in (n,g,c,h,w), out (n,g,k,h,w)
+  long long fs[5], is[5], os[5];
+  RbGemmProblem gemm;
+  // matrices: element counts (0 = operand used as it lies)
+  bool a_direct, b_direct, c_direct;
+  size_t a_bytes, b_bytes, c_bytes, gemm_ws;
+  size_t a_off, b_off, c_off, gemm_off, total;
+};
+
+bool is_dense_in_order(const long long* strides, const long long* sizes, const int* order, int n) {
+  long long acc = 1;
+  for (int i = n - 1; i >= 0; --i) {
+    const int d = order[i];
+    if (sizes[d] != 1 && strides[d] != acc) return false;
+    acc *= sizes[d];
+  }
+  return true;
+}
+
+RbStatus make_plan(const RbConvProblem* p, ConvPlan* pl) {
+  if (!p) return fail(RB_INVALID_PARAM, "problem is NULL");
+  if (p->n <= 0 || p->g <= 0 || p->c <= 0 || p->k <= 0 || p->h <= 0 || p->w <= 0 || p->y <= 0 || p->x <= 0 ||
+      p->stride_h <= 0 || p->stride_w <= 0 || p->dil_h <= 0 || p->dil_w <= 0 || p->pad_h < 0 || p->pad_w < 0 ||
+      p->pad_h_r < 0 || p->pad_w_r < 0)
+    return fail(RB_INVALID_PARAM, "convolution sizes must be positive (paddings non-negative)");
+  if (p->direction < 0 || p->direction > 2) return fail(RB_INVALID_PARAM, "direction must be 0 (fwd), 1 (bwd data), 2 (bwd weight)");
+  const long long ho = ((long long)p->h + p->pad_h + p->pad_h_r - (long long)(p->y - 1) * p->dil_h - 1) / p->stride_h + 1;
+  const long long wo = ((long long)p->w + p->pad_w + p->pad_w_r - (long long)(p->x - 1) * p->dil_w - 1) / p->stride_w + 1;
+  if (ho <= 0 || wo <= 0) return fail(RB_INVALID_PARAM, "the filter does not fit the padded image");
+  if (p->ho != ho || p->wo != wo)
+    return fail(RB_INVALID_PARAM, "ho/wo must equal (in + padL + padR - (fil-1)*dil - 1)/stride + 1 = " +
+                                      std::to_string(ho) + " x " + std::to_string(wo));
+  const int t = p->data_type;
+  if (!(t == RB_F32 || t == RB_F16 || t == RB_BF16 || t == RB_I8)) return fail(RB_INVALID_PARAM, "unsupported element type");
+  if (t == RB_I8 && p->direction != 0)
+    return fail(RB_UNSUPPORTED, "i8 convolution exists in the forward direction only (RockOps.td:101-134)");
+  const long long fsz[5] = {p->g, p->k, p->c, p->y, p->x};
+  const long long isz[5] = {p->n, p->g, p->c, p->h, p->w};
+  const long long osz[5] = {p->n, p->g, p->k, ho, wo};
+  if (!layout_strides(p->fil_layout, "gkcyx", fsz, pl->fs, nullptr)) return fail(RB_INVALID_PARAM, "fil_layout must be a permutation of gkcyx");
+  if (!layout_strides(p->in_layout, "ngchw", isz, pl->is, nullptr)) return fail(RB_INVALID_PARAM, "in_layout must be a permutation of ngchw");
+  if (!layout_strides(p->out_layout, "ngkhw", osz, pl->os, nullptr)) return fail(RB_INVALID_PARAM, "out_layout must be a permutation of ngkhw");
+
+  const size_t es = dtype_bytes(t);
+  const int out_t = (t == RB_I8) ? RB_I32 : t;  // rocmlir-gen: -t i8 => i32 output
+  const size_t es_o = dtype_bytes(out_t);
+  const long long G = p->g;
+  const long long pix_o = (long long)p->n * ho * wo, pix_i = (long long)p->n * p->h * p->w;
+  const long long yxc = (long long)p->y * p->x * p->c, yxk = (long long)p->y * p->x * p->k;
+  const bool pointwise = p->y == 1 && p->x == 1 && p->stride_h == 1 && p->stride_w == 1 && p->pad_h == 0 &&
+                         p->pad_w == 0 && p->pad_h_r == 0 && p->pad_w_r == 0;
+  RbGemmProblem& gp = pl->gemm;
+  memset(&gp, 0, sizeof(gp));
+  gp.g = (int)G;
+  gp.ab_type = t;
+  gp.f32_mode = p->f32_mode;
+  // dense-order tests: index orders into (n,g,c/k,h,w) and (g,k,c,y,x)
+  const int act_gmat[5] = {1, 0, 3, 4, 2};   // g, n, h, w, c : the [G][pixels][channels] matrix order
+  const int fil_kyxc[5] = {0, 1, 3, 4, 2};   // g, k, y, x, c : the [G][k][(y,x,c)] matrix order
+  const bool in_is_mat = is_dense_in_order(pl->is, isz, act_gmat, 5);
+  const bool out_is_mat = is_dense_in_order(pl->os, osz, act_gmat, 5);
+  const bool fil_is_mat = is_dense_in_order(pl->fs, fsz, fil_kyxc, 5);
+  if (p->direction == 0) {
+    gp.m = (int)pix_o; gp.n = p->k; gp.k = (int)yxc;
+    gp.trans_a = 0; gp.trans_b = 1; gp.trans_c = 0;       // A [M][K], B [N][K], C [M][N]
+    gp.c_type = out_t;
+    pl->a_direct = pointwise && in_is_mat;
+    pl->b_direct = fil_is_mat;
+    pl->c_direct = out_is_mat;
+    pl->a_bytes = pl->a_direct ? 0 : (size_t)G * pix_o * yxc * es;
+    pl->b_bytes = pl->b_direct ? 0 : (size_t)G * p->k * yxc * es;
+    pl->c_bytes = pl->c_direct ? 0 : (size_t)G * pix_o * p->k * es_o;
+  } else if (p->direction == 2) {
+    gp.m = p->k; gp.n = (int)yxc; gp.k = (int)pix_o;
+    gp.trans_a = 1; gp.trans_b = 0; gp.trans_c = 0;       // A stored [K][M] = out matrix, B [K][N] = im2col, C [M][N]
+    gp.c_type = t;
+    pl->a_direct = out_is_mat;
+    pl->b_direct = pointwise && in_is_mat;
+    pl->c_direct = fil_is_mat;
+    pl->a_bytes = pl->a_direct ? 0 : (size_t)G * pix_o * p->k * es;
+    pl->b_bytes = pl->b_direct ? 0 : (size_t)G * pix_o * yxc * es;
+    pl->c_bytes = pl->c_direct ? 0 : (size_t)G * p->k * yxc * es;
+  } else {
+    gp.m = (int)pix_i; gp.n = p->c; gp.k = (int)yxk;
+    gp.trans_a = 0; gp.trans_b = 0; gp.trans_c = 0;       // A [M][K] = col2im(out), B [K][N] = filter as (y,x,k) x c
+    gp.c_type = t;
+    pl->a_direct = pointwise && out_is_mat;
+    // a 1x1 filter stored (g,k,c) row-major already is the [K][N] matrix
+    const int fil_yxkc[5] = {0, 3, 4, 1, 2};
+    pl->b_direct = is_dense_in_order(pl->fs, fsz, fil_yxkc, 5);
+    pl->c_direct = in_is_mat;
+    pl->a_bytes = pl->a_direct ? 0 : (size_t)G * pix_i * yxk * es;
+    pl->b_bytes = pl->b_direct ? 0 : (size_t)G * yxk * p->c * es;
+    pl->c_bytes = pl->c_direct ? 0 : (size_t)G * pix_i * p->c * es;
+  }
+  if ((long long)gp.m != (p->direction == 0 ? pix_o : p->direction == 2 ? (long long)p->k : pix_i) ||
+      pix_o > 0x7fffffffLL || pix_i > 0x7fffffffLL || yxc > 0x7fffffffLL || yxk > 0x7fffffffLL)
+    return fail(RB_UNSUPPORTED, "GEMM extent exceeds 2^31");
+  pl->gemm_ws = rbGemmWorkspaceSize(&gp);
+  size_t off = 0;
+  pl->a_off = off; off += up256(pl->a_bytes);
+  pl->b_off = off; off += up256(pl->b_bytes);
+  pl->c_off = off; off += up256(pl->c_bytes);
+  pl->gemm_off = off; off += up256(pl->gemm_ws);
+  pl->total = off;
+  return RB_SUCCESS;
+}
+
+template <typename K, typename... Args>
+void launch_es(size_t es, int blocks, cudaStream_t st, K k1, K k2, K k4, Args... args) {
+  if (es == 1) k1<<<blocks, 256, 0, st>>>(args...);
+  else if (es == 2) k2<<<blocks, 256, 0, st>>>(args...);
+  else k4<<<blocks, 256, 0, st>>>(args...);
+}
+
+}  // namespace
+}  // namespace rb
+
+using namespace rb;
+
+extern "C" size_t rbConvWorkspaceSize(const RbConvProblem* p) {
+  ConvPlan pl;
+  if (make_plan(p, &pl) != RB_SUCCESS) return 0;
+  return pl.total;
+}
+
+extern "C" int rbConvKernelCount(const RbConvProblem* p) {
+  ConvPlan pl;
+  if (make_plan(p, &pl) != RB_SUCCESS) return -1;
+  return 1 + (pl.a_direct ? 0 : 1) + (pl.b_direct ? 0 : 1) + (pl.c_direct ? 0 : 1);
+}
+
+extern "C" RbStatus rbConv(const RbConvProblem* p, void* filter, void* input, void* output, void* workspace,
+                           size_t workspace_bytes, void* stream_v) {
+  ConvPlan pl;
+  RbStatus st = make_plan(p, &pl);
+  if (st != RB_SUCCESS) return st;
+  if (!filter || !input || !output) return fail(RB_INVALID_PARAM, "filter, input and output must be device pointers");
+  if (pl.total > 0 && (!workspace || workspace_bytes < pl.total))
+    return fail(RB_WORKSPACE_TOO_SMALL, "workspace of " + std::to_string(pl.total) + " bytes required");
+  const DeviceInfo* dev = device_info();
+  if (!dev) return RB_CUDA_ERROR;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  const size_t es = dtype_bytes(p->data_type);
+  const int blocks = dev->sm_count * 8;
+  const long long ho = p->ho, wo = p->wo;
+
+  auto gather = [&](const void* src, uint8_t* dst, bool from_out, bool transposed, long long P, long long Q,
+                    long long CH) {
+    GatherParams g;
+    g.N = p->n; g.G = p->g; g.P = P; g.Q = Q; g.Y = p->y; g.X = p->x; g.CH = CH;
+    g.pitch = g.Y * g.X * g.CH;
+    const long long* s = from_out ? pl.os : pl.is;
+    g.s_n = s[0]; g.s_g = s[1]; g.s_ch = s[2]; g.s_a = s[3]; g.s_b = s[4];
+    g.A = from_out ? ho : p->h; g.B = from_out ? wo : p->w;
+    g.stride_h = p->stride_h; g.stride_w = p->stride_w; g.dil_h = p->dil_h; g.dil_w = p->dil_w;
+    g.pad_h = p->pad_h; g.pad_w = p->pad_w;
+    g.transposed = transposed ? 1 : 0;
+    launch_es(es, blocks, stream, conv_gather_kernel<1>, conv_gather_kernel<2>, conv_gather_kernel<4>,
+              static_cast<const uint8_t*>(src), dst, g);
+    count_launch();
+  };
+  auto permute = [&](const void* src, void* dst, const long long* sizes, const long long* strides, const int* order,
+                     bool to_dense, size_t esz) {
+    Dims5 d;
+    for (int i = 0; i < 5; ++i) { d.size[i] = sizes[order[i]]; d.stride[i] = strides[order[i]]; }
+    launch_es(esz, blocks, stream, permute5_kernel<1>, permute5_kernel<2>, permute5_kernel<4>,
+              static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst), d, to_dense ? 1 : 0);
+    count_launch();
+  };
+  const long long fsz[5] = {p->g, p->k, p->c, p->y, p->x};
+  const long long isz[5] = {p->n, p->g, p->c, p->h, p->w};
+  const long long osz[5] = {p->n, p->g, p->k, ho, wo};
+  const int act_gmat[5] = {1, 0, 3, 4, 2};
+  const int fil_kyxc[5] = {0, 1, 3, 4, 2};
+  const int fil_yxkc[5] = {0, 3, 4, 1, 2};
+  const size_t es_c = dtype_bytes(pl.gemm.c_type);
+
+  const void* A;
+  const void* B;
+  void* C;
+  if (p->direction == 0) {
+    if (pl.a_direct) A = input; else { gather(input, ws + pl.a_off, false, false, ho, wo, p->c); A = ws + pl.a_off; }
+    if (pl.b_direct) B = filter; else { permute(filter, ws + pl.b_off, fsz, pl.fs, fil_kyxc, true, es); B = ws + pl.b_off; }
+    C = pl.c_direct ? output : static_cast<void*>(ws + pl.c_off);
+  } else if (p->direction == 2) {
+    if (pl.a_direct) A = output; else { permute(output, ws + pl.a_off, osz, pl.os, act_gmat, true, es); A = ws + pl.a_off; }
+    if (pl.b_direct) B = input; else { gather(input, ws + pl.b_off, false, false, ho, wo, p->c); B = ws + pl.b_off; }
+    C = pl.c_direct ? filter : static_cast<void*>(ws + pl.c_off);
+  } else {
+    if (pl.a_direct) A = output; else { gather(output, ws + pl.a_off, true, true, p->h, p->w, p->k); A = ws + pl.a_off; }
+    if (pl.b_direct) B = filter; else { permute(filter, ws + pl.b_off, fsz, pl.fs, fil_yxkc, true, es); B = ws + pl.b_off; }
+    C = pl.c_direct ? input : static_cast<void*>(ws + pl.c_off);
+  }
+  st = rbGemm(&pl.gemm, nullptr, A, B, C, pl.gemm_ws ? ws + pl.gemm_off : nullptr, pl.gemm_ws, stream_v);
+  if (st != RB_SUCCESS) return st;
+  if (!pl.c_direct) {
+    if (p->direction == 0) permute(C, output, osz, pl.os, act_gmat, false, es_c);
+    else if (p->direction == 2) permute(C, filter, fsz, pl.fs, fil_kyxc, false, es_c);
+    else permute(C, input, isz, pl.is, act_gmat, false, es_c);
+  }
+  return RB_SUCCESS;
+}
