@@ -39,8 +39,9 @@ def test_library_exports_every_declared_symbol(lib):
 
 def test_workspace_size_needs_no_device(lib):
     from rocmlir_b200 import _lib as L
-    # aligned f16 problem: no workspace; K = 769 (odd, reference default gemm K): padded copies of A only
-    p = L.RbGemmProblem(1, 1024, 512, 4096, 0, 0, 0, L.F16, L.F16, 0)
+    # aligned f16 problem with enough tiles to fill the GPU: no workspace; K = 769 (odd, the reference's default
+    # gemm K): a pitched copy of A
+    p = L.RbGemmProblem(1, 4096, 4096, 4096, 0, 0, 0, L.F16, L.F16, 0)
     assert lib.rbGemmWorkspaceSize(C.byref(p)) == 0
     p = L.RbGemmProblem(1, 1024, 512, 769, 0, 0, 0, L.F16, L.F16, 0)
     assert lib.rbGemmWorkspaceSize(C.byref(p)) >= 1024 * 776 * 2
