@@ -103,6 +103,29 @@ RB_EXPORT size_t rbGemmWorkspaceSize(const RbGemmProblem *p);
 RB_EXPORT RbStatus rbGemm(const RbGemmProblem *p, const RbEpilogue *epi /* may be NULL */, const void *a, const void *b,
                 void *c, void *workspace, size_t workspace_bytes, void *stream);
 
+/* rbGemm for callers that cannot allocate device memory. (No counterpart in the reference: there the client
+ * owns every buffer, workspace included.)
+ *
+ * Some hosts of this library are not allowed to call cudaMalloc at the point where they need a GEMM: code that
+ * runs inside a memory-pool or allocator callback, a plugin that is handed its buffers by a framework and must
+ * not grow the process's device footprint, a real-time loop that may not take the allocator's lock. rbGemm asks
+ * such callers for a workspace whenever it pads an operand whose row pitch is not a multiple of 16 bytes,
+ * splits f32 operands into TF32 planes, or cuts K into ranges; this entry point takes no workspace and uses a
+ * fixed RB_NO_ALLOC_SCRATCH_BYTES array inside the library image instead. It calls no cudaMalloc, cudaFree or
+ * allocating library routine. The inputs and the output are still the caller's.
+ *
+ *  - Problems whose scratch need (rbGemmWorkspaceSize) exceeds RB_NO_ALLOC_SCRATCH_BYTES are rejected with
+ *    RB_WORKSPACE_TOO_SMALL and a message naming both sizes; nothing is launched.
+ *  - The first call on each device looks up the scratch array's device address (cudaGetSymbolAddress, with that
+ *    device current). Make that first call before any stream capture begins.
+ *  - All calls on a device share the one array and it keeps the previous call's contents. The kernels overwrite
+ *    every byte they later read, so nothing has to be cleared; but two calls whose kernels overlap on the GPU
+ *    (different streams, or different host threads) race on it. Serialise such calls on one stream.
+ *  - Every GPU that loads the library holds the array until the process exits. */
+#define RB_NO_ALLOC_SCRATCH_BYTES (16u << 20)
+RB_EXPORT RbStatus rbGemmNoAlloc(const RbGemmProblem *p, const RbEpilogue *epi /* may be NULL */, const void *a,
+                                 const void *b, void *c, void *stream);
+
 /* Same operation on HOST buffers: copies A and B (and the epilogue vectors, whose pointers are host
  * pointers here) to the device, runs rbGemm, copies C back and waits for `stream`. Counterpart of the
  * `<kernel>_gpu` wrapper of rocmlir-gen's host harness (mlir/tools/rocmlir-gen/rocmlir-gen.cpp:1211-1283).

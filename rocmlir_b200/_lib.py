@@ -63,6 +63,9 @@ def lib() -> C.CDLL:
         l.rbGemm.restype = C.c_int
         l.rbGemm.argtypes = [C.POINTER(RbGemmProblem), C.POINTER(RbEpilogue), C.c_void_p, C.c_void_p, C.c_void_p,
                              C.c_void_p, C.c_size_t, C.c_void_p]
+        l.rbGemmNoAlloc.restype = C.c_int
+        l.rbGemmNoAlloc.argtypes = [C.POINTER(RbGemmProblem), C.POINTER(RbEpilogue), C.c_void_p, C.c_void_p, C.c_void_p,
+                                    C.c_void_p]
         l.rbGemmHost.restype = C.c_int
         l.rbGemmHost.argtypes = [C.POINTER(RbGemmProblem), C.POINTER(RbEpilogue), C.c_void_p, C.c_void_p, C.c_void_p,
                                  C.c_void_p]

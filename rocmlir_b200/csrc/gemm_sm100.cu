@@ -474,3 +474,40 @@ extern "C" RbStatus rbGemm(const RbGemmProblem* p, const RbEpilogue* epi, const 
   }
   return RB_SUCCESS;
 }
+
+// ---- rbGemmNoAlloc ------------------------------------------------------------------------------------
+// Scratch for callers that may not allocate device memory: one fixed array inside the library image. Every GPU
+// that loads the library carries it until the process exits; all calls share it.
+namespace {
+constexpr size_t kNoAllocScratchBytes = RB_NO_ALLOC_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+constexpr int kNoAllocMaxDevices = 16;
+void* g_noalloc_ptr[kNoAllocMaxDevices];
+cudaError_t g_noalloc_err[kNoAllocMaxDevices];
+std::once_flag g_noalloc_once[kNoAllocMaxDevices];
+}  // namespace
+
+extern "C" RbStatus rbGemmNoAlloc(const RbGemmProblem* p, const RbEpilogue* epi, const void* a, const void* b, void* c,
+                                  void* stream) {
+  RbStatus st = rb::check_problem(p);
+  if (st != RB_SUCCESS) return st;
+  const size_t need = rbGemmWorkspaceSize(p);
+  if (need > kNoAllocScratchBytes)
+    return rb::fail(RB_WORKSPACE_TOO_SMALL,
+                    "rbGemmNoAlloc: this problem needs " + std::to_string(need) + " bytes of scratch, the built-in "
+                    "scratch holds " + std::to_string(kNoAllocScratchBytes) + "; use rbGemm with a caller workspace");
+  int dev = 0;
+  RB_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kNoAllocMaxDevices) return rb::fail(RB_CUDA_ERROR, "device index out of range");
+  // In host code the array's name is only a handle for the runtime, not a device address: the address the kernels
+  // get is looked up once per device, with that device current.
+  std::call_once(g_noalloc_once[dev], [dev] {
+    void* ptr = nullptr;
+    g_noalloc_err[dev] = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+    g_noalloc_ptr[dev] = g_noalloc_err[dev] == cudaSuccess ? ptr : nullptr;
+  });
+  if (g_noalloc_err[dev] != cudaSuccess || !g_noalloc_ptr[dev])
+    return rb::fail(RB_CUDA_ERROR, std::string("cudaGetSymbolAddress(scratch): ") + cudaGetErrorString(g_noalloc_err[dev]));
+  return rbGemm(p, epi, a, b, c, need ? g_noalloc_ptr[dev] : nullptr, need ? kNoAllocScratchBytes : 0, stream);
+}
