@@ -167,6 +167,29 @@ RB_EXPORT int rbConvKernelCount(const RbConvProblem *p);
 RB_EXPORT RbStatus rbConv(const RbConvProblem *p, void *filter, void *input, void *output, void *workspace,
                           size_t workspace_bytes, void *stream);
 
+/* rock.attention (mlir/include/mlir/Dialect/Rock/IR/RockOps.td:208-254): per group g
+ *   O = softmax_k( f(Q . K) ) . V      Q [G][Sq][D], K [G][D][Sk] (trans_k: [G][Sk][D]), V [G][Sk][Dv], O [G][Sq][Dv]
+ * the buffers of rocmlir-gen's rock_attention kernel (rocmlir-gen.cpp:2149-2200, 2264-2328). The reference has no
+ * 1/sqrt(d) and no mask inside the op: callers put them into the elementwise region f between the two products
+ * (TosaToRock.cpp:779-1074). Here f is:  s*scale (has_scale: the MIGraphX scalar-literal form)  + bias[g][q][k]
+ * (optional, element type)  then  where(mask[g][q][k] != 0, s, mask_fill) (optional, i8: the mixr-attn-where form)
+ * then, with `causal`, keys k > q are dropped analytically (equal to a lower-triangular mask with fill -inf, without
+ * reading a [G][Sq][Sk] tensor). Row statistics are f32. f16 and bf16; head dimensions 64 or 128. */
+typedef struct RbAttentionProblem {
+  int32_t g, seq_q, seq_k, head_qk, head_v;
+  int32_t trans_q, trans_k, trans_v, trans_o;
+  int32_t data_type;
+  int32_t has_scale;
+  float scale;
+  int32_t causal;
+  float mask_fill;
+  const void *bias;
+  const int8_t *mask;
+} RbAttentionProblem;
+
+RB_EXPORT RbStatus rbAttention(const RbAttentionProblem *p, const void *q, const void *k, const void *v, void *o,
+                               void *stream);
+
 /* Kernel-selection knob for tuning/experiments: tile variant used by subsequent rbGemm calls on this
  * thread's library state. 0 = automatic (measured table). Mirrors the role of rocMLIR's perf_config
  * (mlir/include/mlir/Dialect/Rock/Tuning/GridwiseGemmParams.h:138-194). */

@@ -42,6 +42,13 @@ class RbConvProblem(C.Structure):
                [("fil_layout", C.c_char * 8), ("in_layout", C.c_char * 8), ("out_layout", C.c_char * 8)]
 
 
+class RbAttentionProblem(C.Structure):
+    _fields_ = [("g", C.c_int32), ("seq_q", C.c_int32), ("seq_k", C.c_int32), ("head_qk", C.c_int32),
+                ("head_v", C.c_int32), ("trans_q", C.c_int32), ("trans_k", C.c_int32), ("trans_v", C.c_int32),
+                ("trans_o", C.c_int32), ("data_type", C.c_int32), ("has_scale", C.c_int32), ("scale", C.c_float),
+                ("causal", C.c_int32), ("mask_fill", C.c_float), ("bias", C.c_void_p), ("mask", C.c_void_p)]
+
+
 class RbError(RuntimeError):
     def __init__(self, status: int, msg: str):
         super().__init__(f"{STATUS_NAMES[status] if 0 <= status < len(STATUS_NAMES) else status}: {msg}")
@@ -76,6 +83,9 @@ def lib() -> C.CDLL:
         l.rbConv.restype = C.c_int
         l.rbConv.argtypes = [C.POINTER(RbConvProblem), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t,
                              C.c_void_p]
+        l.rbAttention.restype = C.c_int
+        l.rbAttention.argtypes = [C.POINTER(RbAttentionProblem), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                  C.c_void_p]
         l.rbSetGemmVariant.restype = None
         l.rbSetGemmVariant.argtypes = [C.c_int]
         l.rbSetTraceBuffer.restype = None

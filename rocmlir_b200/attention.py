@@ -1,0 +1,48 @@
+"""Host-side mirror of rock.attention (mlir/include/mlir/Dialect/Rock/IR/RockOps.td:208-254) over the C ABI.
+
+Q [G,Sq,D], K [G,D,Sk] (trans_k: [G,Sk,D]), V [G,Sk,Dv] -> O [G,Sq,Dv]; argument names follow rocmlir-gen's
+attention flags (-seq_len_q, -seq_len_k, -head_dim_qk, -head_dim_v, -transK, --with-attn-scale, --with-attn-bias).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from . import _lib as L
+from .gemm import rb_dtype
+
+
+def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, trans_k: bool = False,
+              scale: Optional[float] = None, bias: Optional[torch.Tensor] = None,
+              mask: Optional[torch.Tensor] = None, mask_fill: float = float("-inf"), causal: bool = False,
+              out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    for t in (q, k, v):
+        if not t.is_cuda or not t.is_contiguous():
+            raise L.RbError(L.INVALID_PARAM, "q, k, v must be contiguous CUDA tensors (the library has no CPU path)")
+    g, sq, d = q.shape
+    sk, dv = v.shape[1], v.shape[2]
+    kshape = (g, sk, d) if trans_k else (g, d, sk)
+    if tuple(k.shape) != kshape or v.shape[0] != g:
+        raise L.RbError(L.INVALID_PARAM, f"shape mismatch: Q {tuple(q.shape)} K {tuple(k.shape)} V {tuple(v.shape)}")
+    if out is None:
+        out = torch.empty((g, sq, dv), dtype=q.dtype, device=q.device)
+    p = L.RbAttentionProblem(g, sq, sk, d, dv, 0, int(trans_k), 0, 0, rb_dtype(q.dtype), int(scale is not None),
+                             float(scale or 0.0), int(causal), float(mask_fill), None, None)
+    if bias is not None:
+        assert bias.is_cuda and bias.is_contiguous() and bias.dtype == q.dtype and tuple(bias.shape) == (g, sq, sk)
+        p.bias = bias.data_ptr()
+    if mask is not None:
+        assert mask.is_cuda and mask.is_contiguous() and mask.dtype == torch.int8 and tuple(mask.shape) == (g, sq, sk)
+        p.mask = mask.data_ptr()
+    stream = torch.cuda.current_stream(q.device).cuda_stream
+    L.check(L.lib().rbAttention(C.byref(p), q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), stream))
+    return out
+
+
+def flops(g: int, sq: int, sk: int, d: int, dv: int, causal: bool = False) -> float:
+    """perfRunner.py:759-777: matmul FLOPs only; under a causal mask only unmasked score entries count."""
+    if causal:
+        return 2.0 * g * (d + dv) * sq * (sk + 1) / 2
+    return 2.0 * g * sq * sk * d + 2.0 * g * sq * sk * dv
