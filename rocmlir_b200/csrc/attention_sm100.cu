@@ -13,10 +13,13 @@
 //   warp 0   producer: TMA loads of Q (once) and of the K and V tiles of each key block (2-deep rings)
 //   warp 1   MMA issuer: S_j = Q.K_j^T into one of two TMEM score buffers, O += P_j.V_j
 //   warp 2   TMEM allocator
-//   warps 4-7 softmax: thread = query row (TMEM lane). Two passes over the score tile in TMEM (row max, then
-//            exp2 / row sum / P in f16 written to 128-byte-swizzled shared memory as the A operand of P.V),
-//            rescale of O in TMEM when a row maximum moved, final O / l and TMA store.
+//   warps 4-7 softmax: thread = query row (TMEM lane). The 128 scores of the row are read from TMEM once, P = exp2(x - m)
+//            is written back over the score buffer in the element type (two values per 32-bit column) and is the
+//            A operand of P.V straight from TMEM; O is rescaled in TMEM only when the running maximum has grown by
+//            more than 2^8 since the reference maximum was last moved (exp2 stays in range, the final O / l
+//            cancels the stale reference); final O / l and TMA store.
 // S_{j+1} is issued before P_j is awaited, so the score MMA of the next block overlaps the softmax of this one.
+// MMAs of one issuing thread execute in order, which is what makes P_j safe in the buffer S_{j+2} will overwrite.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -56,12 +59,11 @@ struct AttSmem {
   static constexpr int kQBytes = kQT * 256;        // up to D = 128 f16
   static constexpr int kKBytes = kKT * 256;
   static constexpr int kVBytes = kKT * 256;
-  static constexpr int kPBytes = kQT * kKT * 2;
-  static constexpr int kQ = 0;
-  static constexpr int kK = kQ + kQBytes;          // 2 stages
-  static constexpr int kV = kK + 2 * kKBytes;      // 2 stages
-  static constexpr int kP = kV + 2 * kVBytes;
-  static constexpr int kBars = kP + kPBytes;
+  static constexpr int kStages = 3;
+  static constexpr int kQ = 0;                     // reused as the store staging area at the end
+  static constexpr int kK = kQ + kQBytes;
+  static constexpr int kV = kK + kStages * kKBytes;
+  static constexpr int kBars = kV + kStages * kVBytes;
   static constexpr int kTotal = kBars + 256 + 1024;
 };
 
@@ -78,21 +80,27 @@ __device__ __forceinline__ uint32_t pack2(float a, float b, int is_bf16) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 __global__ void __launch_bounds__(kAttThreads, 1) attention_fwd_kernel(const __grid_constant__ AttMaps maps,
                                                                         const AttParams p) {
+  constexpr int NS = AttSmem::kStages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + AttSmem::kBars);
   uint64_t* q_full = bars + 0;
-  uint64_t* k_full = bars + 1;    // [2]
-  uint64_t* k_empty = bars + 3;   // [2]
-  uint64_t* v_full = bars + 5;    // [2]
-  uint64_t* v_empty = bars + 7;   // [2]
-  uint64_t* s_full = bars + 9;    // [2]
-  uint64_t* s_free = bars + 11;   // [2]
-  uint64_t* p_full = bars + 13;
-  uint64_t* pv_done = bars + 14;
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 16);
+  uint64_t* k_full = bars + 1;             // [NS]
+  uint64_t* k_empty = k_full + NS;         // [NS]
+  uint64_t* v_full = k_empty + NS;         // [NS]
+  uint64_t* v_empty = v_full + NS;         // [NS]
+  uint64_t* s_full = v_empty + NS;         // [2]
+  uint64_t* p_full = s_full + 2;
+  uint64_t* pv_done = p_full + 1;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(pv_done + 1);
 
   const int warp = threadIdx.x >> 5;
   const int lane = lane_id();
@@ -105,14 +113,14 @@ __global__ void __launch_bounds__(kAttThreads, 1) attention_fwd_kernel(const __g
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < NS; ++i) {
       mbar_init(&k_full[i], 1);
       mbar_init(&k_empty[i], 1);
       mbar_init(&v_full[i], 1);
       mbar_init(&v_empty[i], 1);
-      mbar_init(&s_full[i], 1);
-      mbar_init(&s_free[i], 4);
     }
+    mbar_init(&s_full[0], 1);
+    mbar_init(&s_full[1], 1);
     mbar_init(p_full, 4);
     mbar_init(pv_done, 1);
     fence_mbar_init();
@@ -131,7 +139,7 @@ __global__ void __launch_bounds__(kAttThreads, 1) attention_fwd_kernel(const __g
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
-  const uint32_t tmem_o = tmem_base + 256;
+  const uint32_t tmem_o = tmem_base + 256;   // S buffers at columns 0 and 128, O at 256
 
   const int d_atoms = p.D / 64, dv_chunks = p.Dv / 64;
   const uint32_t q_bytes = (uint32_t)kQT * p.D * 2, k_bytes = (uint32_t)kKT * p.D * 2, v_bytes = (uint32_t)kKT * p.Dv * 2;
@@ -141,9 +149,9 @@ __global__ void __launch_bounds__(kAttThreads, 1) attention_fwd_kernel(const __g
     if (lane == 0) {
       mbar_expect_tx(q_full, q_bytes);
       for (int a = 0; a < d_atoms; ++a) tma_load_3d(smem + AttSmem::kQ + a * (kQT * 128), &maps.q, q_full, a * 64, q0, g);
+      int s = 0;
+      uint32_t par = 0;
       for (int j = 0; j < nb; ++j) {
-        const int s = j & 1;
-        const uint32_t par = (uint32_t)(j >> 1) & 1u;
         if (!mbar_wait(&k_empty[s], par ^ 1u, p.status, kStatusTimeoutProducer + s)) break;
         uint8_t* ks = smem + AttSmem::kK + s * AttSmem::kKBytes;
         mbar_expect_tx(&k_full[s], k_bytes);
@@ -152,51 +160,57 @@ __global__ void __launch_bounds__(kAttThreads, 1) attention_fwd_kernel(const __g
         } else {
           for (int c = 0; c < kKT / 64; ++c) tma_load_3d(ks + c * (p.D * 128), &maps.k, &k_full[s], j * kKT + c * 64, 0, g);
         }
-        if (!mbar_wait(&v_empty[s], par ^ 1u, p.status, kStatusTimeoutProducer + 2 + s)) break;
+        if (!mbar_wait(&v_empty[s], par ^ 1u, p.status, kStatusTimeoutProducer + 4 + s)) break;
         uint8_t* vs = smem + AttSmem::kV + s * AttSmem::kVBytes;
         mbar_expect_tx(&v_full[s], v_bytes);
         for (int c = 0; c < dv_chunks; ++c) tma_load_3d(vs + c * (kKT * 128), &maps.v, &v_full[s], c * 64, j * kKT, g);
+        if (++s == NS) { s = 0; par ^= 1u; }
       }
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
     if (lane == 0) {
       const uint32_t hi = smem_desc_hi(1024);
-      const uint32_t q_addr = smem_u32(smem + AttSmem::kQ), p_addr = smem_u32(smem + AttSmem::kP);
+      const uint32_t q_addr = smem_u32(smem + AttSmem::kQ);
+      int ks_stage = 0;        // ring position of the next K tile to consume
+      uint32_t ks_par = 0;
       auto issue_s = [&](int j) -> bool {
-        const int s = j & 1;
-        if (!mbar_wait(&k_full[s], (uint32_t)(j >> 1) & 1u, p.status, kStatusTimeoutMma + s)) return false;
-        if (!mbar_wait(&s_free[s], ((uint32_t)(j >> 1) & 1u) ^ 1u, p.status, kStatusTimeoutMma + 4 + s)) return false;
+        if (!mbar_wait(&k_full[ks_stage], ks_par, p.status, kStatusTimeoutMma + ks_stage)) return false;
         tc_fence_after();
-        const uint32_t k_addr = smem_u32(smem + AttSmem::kK + s * AttSmem::kKBytes);
+        const uint32_t k_addr = smem_u32(smem + AttSmem::kK + ks_stage * AttSmem::kKBytes);
         const int ksteps = p.D / 16;
         for (int kk = 0; kk < ksteps; ++kk) {
           const uint32_t a_lo = smem_desc_lo(q_addr + (kk >> 2) * (kQT * 128) + (kk & 3) * 32, 16);
           const uint32_t b_lo = p.trans_k ? smem_desc_lo(k_addr + (kk >> 2) * (kKT * 128) + (kk & 3) * 32, 16)
                                           : smem_desc_lo(k_addr + kk * 2048, (uint32_t)p.D * 128);
-          umma_ss<kKindF16, 1>(tmem_base + s * 128, desc64(a_lo, hi), desc64(b_lo, hi), p.idesc_s, kk ? 1u : 0u);
+          umma_ss<kKindF16, 1>(tmem_base + (j & 1) * 128, desc64(a_lo, hi), desc64(b_lo, hi), p.idesc_s, kk ? 1u : 0u);
         }
-        tc_commit<1>(&s_full[s]);
-        tc_commit<1>(&k_empty[s]);
+        tc_commit<1>(&s_full[j & 1]);
+        tc_commit<1>(&k_empty[ks_stage]);
+        if (++ks_stage == NS) { ks_stage = 0; ks_par ^= 1u; }
         return true;
       };
       bool ok = mbar_wait(q_full, 0, p.status, kStatusTimeoutMma + 8);
       if (ok) ok = issue_s(0);
+      int vs_stage = 0;
+      uint32_t vs_par = 0;
       for (int j = 0; j < nb && ok; ++j) {
+        // S_{j+1} goes into the buffer that held S_{j-1} / P_{j-1}; P_{j-1}.V_{j-1} was issued before it and MMAs
+        // execute in issue order.
         if (j + 1 < nb) ok = issue_s(j + 1);
         if (!ok) break;
-        const int s = j & 1;
         if (!mbar_wait(p_full, (uint32_t)j & 1u, p.status, kStatusTimeoutMma + 9)) break;
-        if (!mbar_wait(&v_full[s], (uint32_t)(j >> 1) & 1u, p.status, kStatusTimeoutMma + 10 + s)) break;
+        if (!mbar_wait(&v_full[vs_stage], vs_par, p.status, kStatusTimeoutMma + 10 + vs_stage)) break;
         tc_fence_after();
-        const uint32_t v_addr = smem_u32(smem + AttSmem::kV + s * AttSmem::kVBytes);
+        const uint32_t v_addr = smem_u32(smem + AttSmem::kV + vs_stage * AttSmem::kVBytes);
+        const uint32_t tmem_p = tmem_base + (j & 1) * 128;   // P_j: 128 lanes x 64 columns, two values per column
         for (int kk = 0; kk < kKT / 16; ++kk) {
-          const uint32_t a_lo = smem_desc_lo(p_addr + (kk >> 2) * (kQT * 128) + (kk & 3) * 32, 16);
           const uint32_t b_lo = smem_desc_lo(v_addr + kk * 2048, kKT * 128);
-          umma_ss<kKindF16, 1>(tmem_o, desc64(a_lo, hi), desc64(b_lo, hi), p.idesc_pv, (j | kk) ? 1u : 0u);
+          umma_ts<kKindF16>(tmem_o, tmem_p + kk * 8, desc64(b_lo, hi), p.idesc_pv, (j | kk) ? 1u : 0u);
         }
         tc_commit<1>(pv_done);
-        tc_commit<1>(&v_empty[s]);
+        tc_commit<1>(&v_empty[vs_stage]);
+        if (++vs_stage == NS) { vs_stage = 0; vs_par ^= 1u; }
       }
     }
   } else if (warp >= 4) {
@@ -205,22 +219,49 @@ __global__ void __launch_bounds__(kAttThreads, 1) attention_fwd_kernel(const __g
     const int r = wq * 32 + lane;          // row within the tile == TMEM lane
     const long long row = (long long)q0 + r;
     const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
-    uint8_t* p_smem = smem + AttSmem::kP;
-    float m = -INFINITY, l = 0.0f;
+    float m_ref = -INFINITY;   // maximum the exponentials are taken against
+    float l = 0.0f;
     bool ok = true;
     for (int j = 0; j < nb && ok; ++j) {
-      const int s = j & 1;
-      if (!mbar_wait(&s_full[s], (uint32_t)(j >> 1) & 1u, p.status, kStatusTimeoutEpilogue + s)) { ok = false; break; }
+      const int sb = j & 1;
+      if (!mbar_wait(&s_full[sb], (uint32_t)(j >> 1) & 1u, p.status, kStatusTimeoutEpilogue + sb)) { ok = false; break; }
       tc_fence_after();
-      const uint32_t tmem_s = tmem_base + lane_base + s * 128;
+      const uint32_t tmem_s = tmem_base + lane_base + sb * 128;
       const int key0 = j * kKT;
-      const bool need_mask = (key0 + kKT > p.Sk) || (p.causal && key0 + kKT - 1 > q0) || p.bias || p.mask;
-      const long long side_off = ((long long)g * p.Sq + min(row, (long long)p.Sq - 1)) * p.Sk;
-      // f(S): scale, bias, masks; returns the score in the log2 domain
-      auto score = [&](uint32_t raw, int col) -> float {
-        float x = __uint_as_float(raw) * p.scale_log2;
-        if (need_mask) {
-          const int key = key0 + col;
+      const bool side_inputs = p.bias || p.mask;                       // per-element tensors: general path
+      const bool edge = (key0 + kKT > p.Sk) || (p.causal && key0 + kKT - 1 > q0);  // key tail or diagonal block
+      uint32_t v[128];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld32(tmem_s + c * 32, v + c * 32);
+      tmem_ld_wait();
+      // f(S) in the log2 domain: scale, bias, masks
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+      if (!side_inputs && !edge) {
+#pragma unroll
+        for (int i = 0; i < 128; i += 4) {
+          const float x0 = __uint_as_float(v[i]) * p.scale_log2, x1 = __uint_as_float(v[i + 1]) * p.scale_log2;
+          const float x2 = __uint_as_float(v[i + 2]) * p.scale_log2, x3 = __uint_as_float(v[i + 3]) * p.scale_log2;
+          v[i] = __float_as_uint(x0); v[i + 1] = __float_as_uint(x1); v[i + 2] = __float_as_uint(x2); v[i + 3] = __float_as_uint(x3);
+          mx0 = fmaxf(mx0, x0); mx1 = fmaxf(mx1, x1); mx2 = fmaxf(mx2, x2); mx3 = fmaxf(mx3, x3);
+        }
+      } else if (!side_inputs) {
+        // keys past the end of the sequence or above the diagonal are dropped with a select
+        const int limit = min(p.Sk - key0, p.causal ? (int)min(row - key0 + 1, (long long)kKT) : kKT);
+#pragma unroll
+        for (int i = 0; i < 128; i += 4) {
+          const float x0 = (i < limit) ? __uint_as_float(v[i]) * p.scale_log2 : -INFINITY;
+          const float x1 = (i + 1 < limit) ? __uint_as_float(v[i + 1]) * p.scale_log2 : -INFINITY;
+          const float x2 = (i + 2 < limit) ? __uint_as_float(v[i + 2]) * p.scale_log2 : -INFINITY;
+          const float x3 = (i + 3 < limit) ? __uint_as_float(v[i + 3]) * p.scale_log2 : -INFINITY;
+          v[i] = __float_as_uint(x0); v[i + 1] = __float_as_uint(x1); v[i + 2] = __float_as_uint(x2); v[i + 3] = __float_as_uint(x3);
+          mx0 = fmaxf(mx0, x0); mx1 = fmaxf(mx1, x1); mx2 = fmaxf(mx2, x2); mx3 = fmaxf(mx3, x3);
+        }
+      } else {
+        const long long side_off = ((long long)g * p.Sq + min(row, (long long)p.Sq - 1)) * p.Sk;
+#pragma unroll
+        for (int i = 0; i < 128; ++i) {  // fully unrolled: v[] must stay in registers
+          float x = __uint_as_float(v[i]) * p.scale_log2;
+          const int key = key0 + i;
           if (key < p.Sk) {
             if (p.bias) x = fmaf(load_elem(p.bias, side_off + key, p.is_bf16), kLog2e, x);
             if (p.mask && p.mask[side_off + key] == 0) x = p.mask_fill * kLog2e;
@@ -228,85 +269,64 @@ __global__ void __launch_bounds__(kAttThreads, 1) attention_fwd_kernel(const __g
           } else {
             x = -INFINITY;
           }
-        }
-        return x;
-      };
-      // pass 1: row maximum
-      float mx = m;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld32(tmem_s + c * 32, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, score(v[i], c * 32 + i));
-      }
-      const float m_use = (mx == -INFINITY) ? 0.0f : mx;   // a fully masked row keeps exp2 finite
-      const float alpha = exp2f(m - m_use);                  // m = -inf on the first block -> 0
-      // the P buffer and O are free once P_{j-1}.V_{j-1} has completed
-      if (j > 0 && !mbar_wait(pv_done, (uint32_t)(j - 1) & 1u, p.status, kStatusTimeoutEpilogue + 4)) { ok = false; break; }
-      // pass 2: p = exp2(x - m), row sum, P (element type) into the swizzled A-operand tile
-      float lsum = 0.0f;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld32(tmem_s + c * 32, v);
-        tmem_ld_wait();
-        uint32_t w[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float p0 = exp2f(score(v[2 * i], c * 32 + 2 * i) - m_use);
-          const float p1 = exp2f(score(v[2 * i + 1], c * 32 + 2 * i + 1) - m_use);
-          lsum += p0 + p1;
-          w[i] = pack2(p0, p1, p.is_bf16);
-        }
-        // 32 keys = 64 bytes = 4 pieces of 16 bytes; atom = 64 keys
-        uint8_t* rowp = p_smem + (c >> 1) * (kQT * 128) + r * 128;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int piece = (c & 1) * 4 + i;
-          *reinterpret_cast<uint4*>(rowp + ((piece ^ (r & 7)) << 4)) = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+          v[i] = __float_as_uint(x);
+          mx0 = fmaxf(mx0, x);
         }
       }
-      // the score buffer may be overwritten by S_{j+2}
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s_free[s]);
-      l = l * alpha + lsum;
-      m = mx;
-      // rescale O where a row maximum moved (whole warp takes part: TMEM access is warp-collective)
+      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+      // Move the reference maximum only when it is first set or the row maximum has outgrown it by more than 2^8.
+      float alpha = 1.0f;
+      if (mx > m_ref + 8.0f || (m_ref == -INFINITY && mx > -INFINITY)) {
+        alpha = ex2(m_ref - mx);   // 0 when the reference was -inf
+        m_ref = mx;
+      }
+      const float m_use = (m_ref == -INFINITY) ? 0.0f : m_ref;   // a row masked so far keeps exp2 finite (p = 0)
+      float l0 = 0.0f, l1 = 0.0f, l2 = 0.0f, l3 = 0.0f;
+#pragma unroll
+      for (int i = 0; i < 64; i += 2) {
+        const float p0 = ex2(__uint_as_float(v[2 * i]) - m_use), p1 = ex2(__uint_as_float(v[2 * i + 1]) - m_use);
+        const float p2 = ex2(__uint_as_float(v[2 * i + 2]) - m_use), p3 = ex2(__uint_as_float(v[2 * i + 3]) - m_use);
+        l0 += p0; l1 += p1; l2 += p2; l3 += p3;
+        v[i] = pack2(p0, p1, p.is_bf16);
+        v[i + 1] = pack2(p2, p3, p.is_bf16);
+      }
+      l = l * alpha + ((l0 + l1) + (l2 + l3));
+      // P_j over the first 64 columns of the score buffer
+      tmem_st32(tmem_s, v);
+      tmem_st32(tmem_s + 32, v + 32);
+      // rescale O where a reference maximum moved (whole warp takes part: TMEM access is warp-collective)
       if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
+        if (!mbar_wait(pv_done, (uint32_t)(j - 1) & 1u, p.status, kStatusTimeoutEpilogue + 4)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll 1
         for (int c = 0; c < p.Dv / 32; ++c) {
-          uint32_t v[32];
-          tmem_ld32(tmem_o + lane_base + c * 32, v);
+          uint32_t o[32];
+          tmem_ld32(tmem_o + lane_base + c * 32, o);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-          tmem_st32(tmem_o + lane_base + c * 32, v);
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st32(tmem_o + lane_base + c * 32, o);
         }
-        tmem_st_wait();
       }
-      fence_proxy_async();   // P written through the generic proxy, read by the MMA through the async proxy
+      tmem_st_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);
     }
-    // ---- epilogue: O / l -> element type -> staging (the P tile is free now) -> TMA store ----
+    // ---- epilogue: O / l -> element type -> staging (the Q tile is no longer needed) -> TMA store ----
     if (ok && mbar_wait(pv_done, (uint32_t)(nb - 1) & 1u, p.status, kStatusTimeoutEpilogue + 5)) {
       tc_fence_after();
       const float inv = (l > 0.0f) ? 1.0f / l : 0.0f;
-      uint8_t* stg = p_smem + wq * (2 * 32 * 128);   // per warp: Dv/64 tiles of 32 rows x 128 bytes
+      uint8_t* stg = smem + AttSmem::kQ + wq * (2 * 32 * 128);   // per warp: Dv/64 tiles of 32 rows x 128 bytes
 #pragma unroll 1
       for (int c = 0; c < p.Dv / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld32(tmem_o + lane_base + c * 32, v);
+        uint32_t o[32];
+        tmem_ld32(tmem_o + lane_base + c * 32, o);
         tmem_ld_wait();
         uint32_t w[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i)
-          w[i] = pack2(__uint_as_float(v[2 * i]) * inv, __uint_as_float(v[2 * i + 1]) * inv, p.is_bf16);
+          w[i] = pack2(__uint_as_float(o[2 * i]) * inv, __uint_as_float(o[2 * i + 1]) * inv, p.is_bf16);
         uint8_t* rowp = stg + (c >> 1) * (32 * 128) + lane * 128;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
