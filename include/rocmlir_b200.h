@@ -190,6 +190,15 @@ typedef struct RbAttentionProblem {
 RB_EXPORT RbStatus rbAttention(const RbAttentionProblem *p, const void *q, const void *k, const void *v, void *o,
                                void *stream);
 
+/* GEMM + GEMM: O[g] = (A[g] . B1[g]) . B2[g], A G x M x K1, B1 G x K1 x N1, B2 G x N1 x N2, O G x M x N2, the
+ * intermediate rounded to the element type, both products accumulated in f32 — the attention skeleton of the
+ * reference with the softmax removed (mlir/include/mlir/Dialect/Rock/IR/Rock.h:52-56,
+ * mlir/lib/Dialect/Rock/Transforms/GridwiseGemmToBlockwise.cpp:1790-1813). The intermediate is kept in `workspace`. */
+RB_EXPORT size_t rbGemmGemmWorkspaceSize(int32_t g, int32_t m, int32_t k1, int32_t n1, int32_t n2, int32_t data_type);
+RB_EXPORT RbStatus rbGemmGemm(int32_t g, int32_t m, int32_t k1, int32_t n1, int32_t n2, int32_t data_type, const void *a,
+                              const void *b1, const void *b2, void *o, void *workspace, size_t workspace_bytes,
+                              void *stream);
+
 /* Kernel-selection knob for tuning/experiments: tile variant used by subsequent rbGemm calls on this
  * thread's library state. 0 = automatic (measured table). Mirrors the role of rocMLIR's perf_config
  * (mlir/include/mlir/Dialect/Rock/Tuning/GridwiseGemmParams.h:138-194). */

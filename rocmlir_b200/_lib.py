@@ -86,6 +86,10 @@ def lib() -> C.CDLL:
         l.rbAttention.restype = C.c_int
         l.rbAttention.argtypes = [C.POINTER(RbAttentionProblem), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                   C.c_void_p]
+        l.rbGemmGemmWorkspaceSize.restype = C.c_size_t
+        l.rbGemmGemmWorkspaceSize.argtypes = [C.c_int32] * 6
+        l.rbGemmGemm.restype = C.c_int
+        l.rbGemmGemm.argtypes = [C.c_int32] * 6 + [C.c_void_p] * 5 + [C.c_size_t, C.c_void_p]
         l.rbSetGemmVariant.restype = None
         l.rbSetGemmVariant.argtypes = [C.c_int]
         l.rbSetTraceBuffer.restype = None

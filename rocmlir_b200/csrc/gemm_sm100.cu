@@ -511,3 +511,34 @@ extern "C" RbStatus rbGemmNoAlloc(const RbGemmProblem* p, const RbEpilogue* epi,
     return rb::fail(RB_CUDA_ERROR, std::string("cudaGetSymbolAddress(scratch): ") + cudaGetErrorString(g_noalloc_err[dev]));
   return rbGemm(p, epi, a, b, c, need ? g_noalloc_ptr[dev] : nullptr, need ? kNoAllocScratchBytes : 0, stream);
 }
+
+// ---- rbGemmGemm -------------------------------------------------------------------------------------------
+// O = (A . B1) . B2 with the intermediate rounded to the element type: what rocMLIR's attention skeleton computes
+// with the softmax removed (mlir/lib/Dialect/Rock/Transforms/GridwiseGemmToBlockwise.cpp:1790-1813, 2162-2165).
+// Two launches of the GEMM kernel; the intermediate (M x N1, element type) lives in the caller's workspace and
+// is small enough to stay in L2 between them for the shapes this op is used with.
+extern "C" size_t rbGemmGemmWorkspaceSize(int32_t g, int32_t m, int32_t k1, int32_t n1, int32_t n2, int32_t data_type) {
+  if (g <= 0 || m <= 0 || k1 <= 0 || n1 <= 0 || n2 <= 0 || !rb::dtype_bytes(data_type)) return 0;
+  RbGemmProblem p1 = {g, m, n1, k1, 0, 0, 0, data_type, data_type, 0};
+  RbGemmProblem p2 = {g, m, n2, n1, 0, 0, 0, data_type, data_type, 0};
+  const size_t mid = rb::align_up((size_t)g * m * n1 * rb::dtype_bytes(data_type), 256);
+  return mid + std::max(rbGemmWorkspaceSize(&p1), rbGemmWorkspaceSize(&p2));
+}
+
+extern "C" RbStatus rbGemmGemm(int32_t g, int32_t m, int32_t k1, int32_t n1, int32_t n2, int32_t data_type,
+                               const void* a, const void* b1, const void* b2, void* o, void* workspace,
+                               size_t workspace_bytes, void* stream) {
+  if (!(data_type == RB_F16 || data_type == RB_BF16 || data_type == RB_F32))
+    return rb::fail(RB_UNSUPPORTED, "gemm+gemm exists for f16, bf16 and f32");
+  const size_t need = rbGemmGemmWorkspaceSize(g, m, k1, n1, n2, data_type);
+  if (need == 0) return rb::fail(RB_INVALID_PARAM, "sizes must be positive");
+  if (!workspace || workspace_bytes < need)
+    return rb::fail(RB_WORKSPACE_TOO_SMALL, "workspace of " + std::to_string(need) + " bytes required");
+  RbGemmProblem p1 = {g, m, n1, k1, 0, 0, 0, data_type, data_type, 0};
+  RbGemmProblem p2 = {g, m, n2, n1, 0, 0, 0, data_type, data_type, 0};
+  const size_t mid = rb::align_up((size_t)g * m * n1 * rb::dtype_bytes(data_type), 256);
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  RbStatus st = rbGemm(&p1, nullptr, a, b1, ws, ws + mid, workspace_bytes - mid, stream);
+  if (st != RB_SUCCESS) return st;
+  return rbGemm(&p2, nullptr, ws, b2, o, ws + mid, workspace_bytes - mid, stream);
+}

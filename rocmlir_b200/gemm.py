@@ -166,3 +166,26 @@ def gemm_host(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, trans_a: b
                             out.data_ptr(), stream)
     L.check(st)
     return out
+
+
+def gemm_gemm(a: torch.Tensor, b1: torch.Tensor, b2: torch.Tensor, *, out: Optional[torch.Tensor] = None,
+              workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """O = (A . B1) . B2 with the intermediate rounded to the element type (rbGemmGemm)."""
+    a3, b13, b23 = _as3d(a), _as3d(b1), _as3d(b2)
+    g, m, k1 = a3.shape
+    n1, n2 = b13.shape[2], b23.shape[2]
+    assert b13.shape == (g, k1, n1) and b23.shape == (g, n1, n2)
+    for t in (a, b1, b2):
+        if not t.is_cuda or not t.is_contiguous():
+            raise L.RbError(L.INVALID_PARAM, "operands must be contiguous CUDA tensors")
+    dt = rb_dtype(a.dtype)
+    lib = L.lib()
+    need = int(lib.rbGemmGemmWorkspaceSize(g, m, k1, n1, n2, dt))
+    if workspace is None or workspace.numel() * workspace.element_size() < need:
+        workspace = torch.empty(need, dtype=torch.uint8, device=a.device)
+    if out is None:
+        out = torch.empty((g, m, n2), dtype=a.dtype, device=a.device)
+    stream = torch.cuda.current_stream(a.device).cuda_stream
+    L.check(lib.rbGemmGemm(g, m, k1, n1, n2, dt, a.data_ptr(), b1.data_ptr(), b2.data_ptr(), out.data_ptr(),
+                           workspace.data_ptr(), workspace.numel() * workspace.element_size(), stream))
+    return out.view(m, n2) if a.dim() == 2 else out

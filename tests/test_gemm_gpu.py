@@ -215,3 +215,23 @@ def test_fp16_gemm_4096_cubed_sampled_rows_and_linearity(cuda_device):
     colsum = got.astype(np.float64).sum(0)
     tol = 4096 * 2.0 ** -11 * np.abs(got).max()
     assert np.abs(colsum - colsum_ref).max() < tol
+
+
+@pytest.mark.parametrize("m,k1,n1,n2", [(256, 192, 320, 128), (4096, 1024, 1024, 1024)])
+def test_gemm_gemm_matches_oracle(cuda_device, m, k1, n1, n2):
+    """O = (A.B1).B2, intermediate rounded to f16 (BASELINE config 5b at full size: M 4096, K1 = N1 = N2 = 1024).
+    The full-size oracle is evaluated on a seeded sample of rows (rows are independent)."""
+    import torch
+    from rocmlir_b200 import _lib as L
+    from rocmlir_b200.gemm import gemm_gemm
+    af, araw = normal_data((m, k1), oracle.F16, seed=51, scale=0.1)
+    b1f, b1raw = normal_data((k1, n1), oracle.F16, seed=52, scale=0.1)
+    b2f, b2raw = normal_data((n1, n2), oracle.F16, seed=53, scale=0.1)
+    out = gemm_gemm(to_device(araw, oracle.F16), to_device(b1raw, oracle.F16), to_device(b2raw, oracle.F16))
+    torch.cuda.synchronize()
+    assert L.kernel_status() == 0
+    got = oracle.to_f32(from_device(out, oracle.F16), oracle.F16)
+    rows = np.arange(m) if m <= 256 else np.random.Generator(np.random.PCG64(5)).choice(m, 64, replace=False)
+    ref = oracle.round_to(oracle.gemm_gemm(af[rows], b1f, b2f, oracle.F16, threads=oracle.max_threads()), oracle.F16)
+    verdict, info = oracle.verify_float(got[rows], ref, 1e-3, 100.0, 1e30)
+    assert verdict == [1, 1, 1], info
