@@ -207,7 +207,7 @@ RB_EXPORT void rbSetGemmVariant(int variant);
 /* Tracing: when a device buffer of at least 16 * (CTAs of the launch) 64-bit words is set, the GEMM kernel
  * writes per-CTA SM-cycle counters into it: [1] producer waited for a free stage, [2] MMA thread waited for
  * loaded data, [3] MMA thread waited for a free accumulator, [4] MMA loop total, [5] tiles, [6] epilogue
- * waited for a tile, [7] epilogue busy, [8..15] cumulative [2] after each of the first 8 tiles. NULL switches tracing off. Thread-local, like the variant knob.
+ * waited for a tile, [7] epilogue busy, [8..14] cumulative [2] after each of the first 7 tiles, [15] the MMA loop in nanoseconds. NULL switches tracing off. Thread-local, like the variant knob.
  * The reference's counterpart is external profiling (rocprof) around mlir-cpu-runner
  * (mlir/utils/performance/perfRunner.py:131-150). */
 RB_EXPORT void rbSetTraceBuffer(unsigned long long *device_buf, size_t n_u64);

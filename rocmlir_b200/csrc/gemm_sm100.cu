@@ -368,8 +368,19 @@ extern "C" RbStatus rbGemm(const RbGemmProblem* p, const RbEpilogue* epi, const 
                            : abt == RB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                            : abt == RB_F32  ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                                             : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  // An MN-major tile is 128-byte chunks of M/N x K rows; when the extent is a whole number of chunks the chunk
+  // index becomes a tensor dimension of its own and one 4-D box fetches the whole tile of a stage.
+  const bool a_fused = oa.mn_major && oa.cols % bke == 0 && oa.pitch == oa.cols;
+  const bool b_fused = ob.mn_major && ob.cols % bke == 0 && ob.pitch == ob.cols;
   auto encode_operand = [&](CUtensorMap* m, const void* base, const OperandPlan& o, int box_rows_kmajor,
                             std::string* err) {
+    const bool fused = (&o == &oa) ? a_fused : b_fused;
+    if (fused) {
+      const uint64_t dims[4] = {(uint64_t)bke, (uint64_t)o.rows, (uint64_t)(o.cols / bke), (uint64_t)p->g};
+      const uint64_t strides[3] = {(uint64_t)o.pitch * es, (uint64_t)kRowBytes, (uint64_t)o.rows * o.pitch * es};
+      const uint32_t box[4] = {(uint32_t)bke, (uint32_t)bke, (uint32_t)(box_rows_kmajor / bke), 1u};
+      return encode_tiled(m, dt, 4, base, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, err);
+    }
     const uint64_t dims[3] = {(uint64_t)o.cols, (uint64_t)o.rows, (uint64_t)p->g};
     const uint64_t strides[2] = {(uint64_t)o.pitch * es, (uint64_t)o.rows * o.pitch * es};
     // K-major: box = BKE k-elements x tile rows. MN-major: box = one 128-byte chunk of MN x BKE k-rows.
@@ -438,6 +449,9 @@ extern "C" RbStatus rbGemm(const RbGemmProblem* p, const RbEpilogue* epi, const 
   }
   kp.status = dev->status_word;
   kp.stages = stages;
+  kp.probe = (t_variant >> 24) & 3;
+  kp.a_fused = a_fused ? 1 : 0;
+  kp.b_fused = b_fused ? 1 : 0;
 
   const long long num_items = (long long)kp.G * kp.tiles_m * kp.tiles_n * splits;
   if (num_items > 0x7fffffffLL) return fail(RB_UNSUPPORTED, "too many tiles");

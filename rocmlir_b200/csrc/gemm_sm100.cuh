@@ -69,6 +69,8 @@ struct GemmParams {
   EpiParams epi;
   uint32_t* status;
   unsigned long long* trace;  // optional [gridDim.x][16] cycle counters per CTA (see rbSetTraceBuffer), or NULL
+  int a_fused, b_fused;       // MN-major operand loaded with one 4-D box per stage (extent a multiple of the chunk)
+  int probe;                  // instrumentation (results become meaningless): bit0 = no loads, bit1 = no epilogue work
   int stages;                 // shared-memory ring depth (<= GemmSmemLayout::kMaxStages)
 };
 
@@ -188,10 +190,14 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
           uint8_t* sa = smem + s * stage_bytes;
           uint8_t* sb = sa + L::kABytes;
           const int k0 = kb * BKE;
-          if constexpr (CTAS == 1) {
+          if (p.probe & 1) {
+            if (CTAS == 1 || rank == 0) mbar_arrive(&full_bar[s]);
+          } else if constexpr (CTAS == 1) {
             mbar_expect_tx(&full_bar[s], stage_bytes);
             if constexpr (!A_MN) {
               tma_load_3d(sa, &maps.a[seg], &full_bar[s], k0, m0, g);
+            } else if (p.a_fused) {
+              tma_load_4d(sa, &maps.a[seg], &full_bar[s], 0, k0, m0 / CHE, g);
             } else {
 #pragma unroll
               for (int c = 0; c < kBM / CHE; ++c)
@@ -199,6 +205,8 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
             }
             if constexpr (!B_MN) {
               tma_load_3d(sb, &maps.b[seg], &full_bar[s], k0, n0, g);
+            } else if (p.b_fused) {
+              tma_load_4d(sb, &maps.b[seg], &full_bar[s], 0, k0, n0 / CHE, g);
             } else {
               for (int c = 0; c < bn_cta / CHE; ++c)
                 tma_load_3d(sb + c * CHUNK_BYTES, &maps.b[seg], &full_bar[s], n0 + c * CHE, k0, g);
@@ -209,6 +217,8 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
             if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * stage_bytes);
             if constexpr (!A_MN) {
               tma_load_3d_bar(sa, &maps.a[seg], lead_full, k0, m0, g);
+            } else if (p.a_fused) {
+              tma_load_4d_bar(sa, &maps.a[seg], lead_full, 0, k0, m0 / CHE, g);
             } else {
 #pragma unroll
               for (int c = 0; c < kBM / CHE; ++c)
@@ -216,6 +226,8 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
             }
             if constexpr (!B_MN) {
               tma_load_3d_bar(sb, &maps.b[seg], lead_full, k0, n0, g);
+            } else if (p.b_fused) {
+              tma_load_4d_bar(sb, &maps.b[seg], lead_full, 0, k0, n0 / CHE, g);
             } else {
               for (int c = 0; c < bn_cta / CHE; ++c)
                 tma_load_3d_bar(sb + c * CHUNK_BYTES, &maps.b[seg], lead_full, n0 + c * CHE, k0, g);
@@ -237,6 +249,8 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
       bool ok = true;
       long long w_full = 0, w_tempty = 0;
       const long long t_begin = p.trace ? clock64() : 0;
+      unsigned long long ns_begin = 0;
+      if (p.trace) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns_begin));
       bool ready = false;
       // Descriptor halves: constant high word; low word of stage 0, advanced by adds only.
       const uint32_t desc_hi = smem_desc_hi(1024);
@@ -247,8 +261,6 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
       constexpr uint32_t kBStep = (B_MN ? KT::UMMA_K * kRowBytes : KT::UMMA_K * ES) >> 4;
       const uint32_t full0 = smem_u32(&full_bar[0]);
       const uint32_t empty0 = smem_u32(&empty_bar[0]);
-      const uint32_t peer_off = (CTAS == 2) ? (mapa_u32(empty0, 1) - mapa_u32(empty0, 0)) : 0u;
-      const uint32_t self_off = (CTAS == 2) ? (mapa_u32(empty0, 0) - empty0) : 0u;
       for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs, ++t) {
         const uint32_t buf = t & 1u;
         const uint32_t bph = (t >> 1) & 1u;
@@ -282,20 +294,18 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
           if constexpr (CTAS == 1) {
             tc_commit_addr1(empty0 + s * 8);
           } else {
-            tc_commit_addr2(empty0 + s * 8 + self_off);
-            tc_commit_addr2(empty0 + s * 8 + self_off + peer_off);
+            tc_commit_mask2(empty0 + s * 8, 3);
           }
           s = ns;
           ph = nph;
           ready = next_ready;
         }
         if (!ok) break;
-        if (p.trace && t < 8) p.trace[blockIdx.x * 16 + 8 + t] = (unsigned long long)w_full;  // cumulative, per tile
+        if (p.trace && t < 7) p.trace[blockIdx.x * 16 + 8 + t] = (unsigned long long)w_full;  // cumulative, per tile
         if constexpr (CTAS == 1) {
           tc_commit<1>(&tfull_bar[buf]);
         } else {
-          tc_commit_addr2(mapa_u32(smem_u32(&tfull_bar[buf]), 0));
-          tc_commit_addr2(mapa_u32(smem_u32(&tfull_bar[buf]), 1));
+          tc_commit_mask2(smem_u32(&tfull_bar[buf]), 3);
         }
       }
       if (p.trace) {
@@ -303,6 +313,9 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
         p.trace[blockIdx.x * 16 + 3] = (unsigned long long)w_tempty;
         p.trace[blockIdx.x * 16 + 4] = (unsigned long long)(clock64() - t_begin);  // MMA issue loop, total
         p.trace[blockIdx.x * 16 + 5] = t;
+        unsigned long long ns_end;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns_end));
+        p.trace[blockIdx.x * 16 + 15] = ns_end - ns_begin;  // the same loop in nanoseconds (gives the SM clock)
       }
     }
   } else if (warp >= 4) {
@@ -336,6 +349,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
       for (int c = 0; c < ngroups; ++c) {
         const int n0 = nb * p.bn + c * 32;
         if (n0 >= p.N) break;  // warp-uniform
+        if (p.probe & 2) break;
         uint32_t v[32];
         tmem_ld32(tmem_base + (uint32_t(q * 32) << 16) + buf * kMaxBN + c * 32, v);
         tmem_ld_wait();

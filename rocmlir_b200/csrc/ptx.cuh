@@ -131,6 +131,15 @@ __device__ __forceinline__ void tma_load_3d_bar(void* dst, const CUtensorMap* m,
       "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
 }
+// 4-D variant of tma_load_3d_bar (completion on a barrier that may live in the pair's leader CTA).
+__device__ __forceinline__ void tma_load_4d_bar(void* dst, const CUtensorMap* m, uint32_t bar_cluster_addr, int c0,
+                                                int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(smem_u32(dst)),
+      "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
 __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* m, uint64_t* bar, int c0,
                                             int c1, int c2, int c3) {
   asm volatile(
@@ -216,6 +225,14 @@ __device__ __forceinline__ void tc_commit_addr1(uint32_t bar_addr) {
 // (own CTA or the peer, see mapa_u32). Two of these, one per CTA, signal both halves of a pair.
 __device__ __forceinline__ void tc_commit_addr2(uint32_t bar_cluster_addr) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr)
+               : "memory");
+}
+// One commit that arrives on the barrier at this shared-memory offset in every CTA of `cta_mask`
+// (an mbarrier arrival broadcast inside the cluster; no data moves).
+__device__ __forceinline__ void tc_commit_mask2(uint32_t bar_addr, uint16_t cta_mask) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+                   bar_addr),
+               "h"(cta_mask)
                : "memory");
 }
 __device__ __forceinline__ uint32_t mapa_u32(uint32_t cta_smem_addr, uint32_t cta_rank) {
