@@ -191,10 +191,15 @@ def main():
     host_sets = make_operands(args.sets, seed=1 + rank, device=dev)
     dev_sets = [(a.to(dev), b.to(dev), torch.empty((M, N), dtype=torch.float16, device=dev)) for a, b in host_sets]
     variant = args.variant if args.variant else None
+    from rocmlir_b200.gemm import problem, workspace_size
+    if variant is not None:
+        L.lib().rbSetGemmVariant(int(variant))
+    ws_bytes = workspace_size(problem(dev_sets[0][0], dev_sets[0][1], False, False, False, torch.float16))
+    workspace = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
 
     def step_device():
         for a, b, c in dev_sets:
-            gemm(a, b, out=c, variant=variant)
+            gemm(a, b, out=c, variant=variant, workspace=workspace)
 
     def barrier():
         torch.cuda.synchronize()

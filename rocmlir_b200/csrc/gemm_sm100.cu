@@ -3,6 +3,7 @@
 // TF32 hi/lo split), encodes the tensor maps and launches the persistent tcgen05 kernel.
 #include "gemm_sm100.cuh"
 
+#include <atomic>
 #include <mutex>
 
 #include "lib_state.h"
@@ -114,6 +115,7 @@ constexpr int kAssumedSMs = 148;  // B200
 struct GemmConfig {
   int ctas, bn, stages, splits;
   bool plain_stores;
+  int dp_tiles, sk_tiles;  // stream-K tail (see GemmParams); sk_tiles == 0: every tile is computed whole
 };
 
 GemmConfig choose_config(const RbGemmProblem* p, int variant) {
@@ -147,6 +149,21 @@ GemmConfig choose_config(const RbGemmProblem* p, int variant) {
   if (c.splits > kblocks) c.splits = (int)kblocks;
   // every range must be non-empty with ceil-division ranges
   while (c.splits > 1 && (long long)(c.splits - 1) * ((kblocks + c.splits - 1) / c.splits) >= kblocks) --c.splits;
+  // Stream-K tail (variant bit 9 switches it ON): when the last wave of whole tiles would leave more than 5 % of the
+  // GPU idle, the tiles of the last full wave plus the remainder are dealt out by K blocks instead. Measured on
+  // B200 it does not pay for the shapes tried (4096^3 f16: 1090 vs 1120 TFLOP/s sustained; 2048x11008x4096 i8:
+  // 2000 vs 2300 TOP/s): the GPU runs at its power cap, idle SMs in the last wave let the busy ones clock higher,
+  // and the short partial items expose their epilogues. It stays available for tuning.
+  c.dp_tiles = (int)tiles;
+  c.sk_tiles = 0;
+  if (c.splits == 1 && tiles > units && ((variant >> 9) & 1) && kblocks >= 8) {
+    const long long rem = tiles % units;
+    const long long waves = (tiles + units - 1) / units;
+    if (rem != 0 && (double)(units - rem) / (double)(waves * units) > 0.05) {
+      c.sk_tiles = (int)(rem + units);
+      c.dp_tiles = (int)(tiles - c.sk_tiles);
+    }
+  }
   return c;
 }
 
@@ -220,6 +237,7 @@ RbStatus check_problem(const RbGemmProblem* p) {
 struct Workspace {
   size_t a_off[2], b_off[2];  // [0] = copy / hi, [1] = lo
   size_t partial_off;         // K-split partial planes
+  size_t sk_off, sk_flags_off;  // stream-K partial tiles and their arrival counters
   size_t total;
 };
 
@@ -237,6 +255,13 @@ Workspace plan_workspace(const RbGemmProblem* p, const OperandPlan& oa, const Op
   if (cfg.splits > 1) {
     w.partial_off = off;
     off += align_up((size_t)cfg.splits * p->g * p->m * p->n * 4, 256);
+  }
+  if (cfg.sk_tiles > 0) {
+    const size_t units = kAssumedSMs / cfg.ctas;
+    w.sk_off = off;
+    off += align_up(units * (size_t)(kBM * cfg.ctas) * cfg.bn * 4, 256);
+    w.sk_flags_off = off;
+    off += align_up(units * 8 * sizeof(unsigned int), 256);
   }
   w.total = off;
   return w;
@@ -298,8 +323,13 @@ extern "C" RbStatus rbGemm(const RbGemmProblem* p, const RbEpilogue* epi, const 
   const OperandPlan oa = plan_operand(p->trans_a != 0 /* A stored G x K x M */, p->m, p->k, es, is_f32, split);
   const OperandPlan ob = plan_operand(p->trans_b == 0 /* B stored G x K x N */, p->n, p->k, es, is_f32, split);
   const bool a_mn = oa.mn_major, b_mn = ob.mn_major;
-  const GemmConfig cfg = choose_config(p, t_variant);
-  const Workspace ws = plan_workspace(p, oa, ob, cfg);
+  GemmConfig cfg = choose_config(p, t_variant);
+  Workspace ws = plan_workspace(p, oa, ob, cfg);
+  if (cfg.sk_tiles > 0 && (!workspace || workspace_bytes < ws.total)) {
+    // the stream-K tail is an optimisation: without room for its partial tiles every tile is computed whole
+    cfg.sk_tiles = 0;
+    ws = plan_workspace(p, oa, ob, cfg);
+  }
   if (ws.total > 0) {
     if (!workspace || workspace_bytes < ws.total)
       return fail(RB_WORKSPACE_TOO_SMALL, "workspace of " + std::to_string(ws.total) + " bytes required");
@@ -453,8 +483,19 @@ extern "C" RbStatus rbGemm(const RbGemmProblem* p, const RbEpilogue* epi, const 
   kp.a_fused = a_fused ? 1 : 0;
   kp.b_fused = b_fused ? 1 : 0;
 
-  const long long num_items = (long long)kp.G * kp.tiles_m * kp.tiles_n * splits;
+  const long long num_tiles = (long long)kp.G * kp.tiles_m * kp.tiles_n;
+  const long long num_items = num_tiles * splits;
   if (num_items > 0x7fffffffLL) return fail(RB_UNSUPPORTED, "too many tiles");
+  // the stream-K split was planned for a B200's SM count; on anything else every tile is computed whole
+  const bool use_sk = cfg.sk_tiles > 0 && dev->sm_count == kAssumedSMs;
+  kp.dp_tiles = use_sk ? cfg.dp_tiles : (int)num_tiles;
+  kp.sk_tiles = use_sk ? cfg.sk_tiles : 0;
+  if (use_sk) {
+    kp.sk_partial = wsb + ws.sk_off;
+    kp.sk_flags = reinterpret_cast<unsigned int*>(wsb + ws.sk_flags_off);
+    static std::atomic<unsigned int> next_token{0x5eed0001u};
+    kp.sk_token = next_token.fetch_add(1, std::memory_order_relaxed);
+  }
 
   GemmKernel kern = ctas == 2 ? pick_kernel<2>(kind, a_mn, b_mn) : pick_kernel<1>(kind, a_mn, b_mn);
   const int smem = ctas == 2 ? GemmSmemLayout<2>::total(stages, bn) : GemmSmemLayout<1>::total(stages, bn);

@@ -69,6 +69,16 @@ struct GemmParams {
   EpiParams epi;
   uint32_t* status;
   unsigned long long* trace;  // optional [gridDim.x][16] cycle counters per CTA (see rbSetTraceBuffer), or NULL
+  // Stream-K tail (only with splits == 1): the first dp_tiles tiles are computed whole, round-robin over the
+  // persistent CTAs (pairs); the K blocks of the remaining sk_tiles tiles are dealt out evenly and contiguously,
+  // so a CTA may compute only part of a tile's K range. The CTA that holds a tile's first K blocks owns the tile:
+  // the others write f32/i32 partial tiles to sk_partial[unit] and raise sk_flags[unit]; the owner adds them in
+  // unit order in its epilogue. Partial work comes first in every CTA's range and owned work last, so an owner
+  // never waits for work that has not started.
+  int dp_tiles, sk_tiles;
+  void* sk_partial;            // [units][bn / 32][8][kBM * CTAS] 16-byte words of raw accumulators (row fastest: coalesced)
+  unsigned int* sk_flags;      // [units][8]: one word per (CTA of the pair, epilogue warp), set to sk_token when written
+  unsigned int sk_token;       // unique per launch, so stale words of earlier launches never match
   int a_fused, b_fused;       // MN-major operand loaded with one 4-D box per stage (extent a multiple of the chunk)
   int probe;                  // instrumentation (results become meaningless): bit0 = no loads, bit1 = no epilogue work
   int stages;                 // shared-memory ring depth (<= GemmSmemLayout::kMaxStages)
@@ -106,6 +116,55 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
   nb = t / gsz;
 }
 
+// Work items of one persistent CTA (or CTA pair) `unit` out of `units`. All roles of a CTA walk the same sequence.
+struct WorkItem {
+  int tile;            // linear tile index (g, m block, n block)
+  int split;           // uniform K split: index of the K range (0 otherwise)
+  int kb_begin, kb_end;
+  int kind;            // 0 whole result, 1 owner of a tile whose tail other units compute, 2 contributor
+  int first_contrib, n_contrib;  // owner: units first_contrib .. first_contrib + n_contrib - 1 hold the rest
+};
+struct WorkIter {
+  int unit, units, splits, kblocks, kb_per_split, dp_items, dp_tiles;
+  int i;               // next data-parallel item
+  long long cur, end;  // stream-K range of this unit in K blocks over the sk tiles
+  long long q, r;      // every unit gets q blocks, the first r units one more
+  __device__ WorkIter(const GemmParams& p, int unit_, int units_) {
+    unit = unit_; units = units_; splits = p.splits; kblocks = p.kblocks;
+    kb_per_split = (p.kblocks + p.splits - 1) / p.splits;
+    dp_tiles = p.dp_tiles;
+    dp_items = p.dp_tiles * p.splits;
+    i = unit;
+    const long long total = (long long)p.sk_tiles * p.kblocks;
+    q = total / units; r = total % units;
+    cur = unit * q + min((long long)unit, r);
+    end = cur + q + (unit < r ? 1 : 0);
+  }
+  __device__ bool next(WorkItem& w) {
+    if (i < dp_items) {
+      w.tile = i / splits; w.split = i - w.tile * splits;
+      w.kb_begin = w.split * kb_per_split; w.kb_end = min(kblocks, w.kb_begin + kb_per_split);
+      w.kind = 0; w.first_contrib = 0; w.n_contrib = 0;
+      i += units;
+      return true;
+    }
+    if (cur >= end) return false;
+    const int t = (int)(cur / kblocks);
+    w.tile = dp_tiles + t; w.split = 0;
+    w.kb_begin = (int)(cur - (long long)t * kblocks);
+    w.kb_end = (int)min((long long)kblocks, w.kb_begin + (end - cur));
+    cur += w.kb_end - w.kb_begin;
+    w.first_contrib = 0; w.n_contrib = 0;
+    if (w.kb_begin != 0) { w.kind = 2; return true; }
+    if (w.kb_end == kblocks) { w.kind = 0; return true; }
+    w.kind = 1;
+    w.first_contrib = unit + 1;
+    long long remaining = kblocks - w.kb_end;
+    for (int u = unit + 1; remaining > 0 && u < units; ++u) { remaining -= q + (u < r ? 1 : 0); ++w.n_contrib; }
+    return true;
+  }
+};
+
 template <int KIND, bool A_MN, bool B_MN, int CTAS>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParams p) {
@@ -134,7 +193,6 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
   const uint32_t rank = (CTAS == 2) ? cluster_ctarank() : 0u;
   const int pair_id = blockIdx.x / CTAS;
   const int num_pairs = gridDim.x / CTAS;
-  const int num_tiles = p.G * p.tiles_m * p.tiles_n * p.splits;  // work items
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
@@ -164,8 +222,6 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
-  // K blocks per work item: the K range of a segment is cut into p.splits nearly equal parts.
-  const int kb_per_split = (p.kblocks + p.splits - 1) / p.splits;
 
   if (warp == 0) {
     // ------------------------------ producer ------------------------------
@@ -173,14 +229,14 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
       uint32_t s = 0, ph = 0;
       bool ok = true;
       long long w_empty = 0;
-      for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
+      WorkIter it(p, pair_id, num_pairs);
+      WorkItem w;
+      while (ok && it.next(w)) {
         int g, mb, nb;
-        const int split = tile % p.splits;
-        tile_coords(tile / p.splits, p.tiles_m, p.tiles_n, g, mb, nb);
+        tile_coords(w.tile, p.tiles_m, p.tiles_n, g, mb, nb);
         const int m0 = (mb * CTAS + (int)rank) * kBM;
         const int n0 = nb * p.bn + (int)rank * bn_cta;
-        const int kb_begin = split * kb_per_split;
-        const int kb_end = min(p.kblocks, kb_begin + kb_per_split);
+        const int kb_begin = w.kb_begin, kb_end = w.kb_end;
         const int ktotal = (kb_end - kb_begin) * p.nseg;
         int seg = 0, kb = kb_begin;
         for (int kk = 0; kk < ktotal; ++kk) {
@@ -261,7 +317,9 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
       constexpr uint32_t kBStep = (B_MN ? KT::UMMA_K * kRowBytes : KT::UMMA_K * ES) >> 4;
       const uint32_t full0 = smem_u32(&full_bar[0]);
       const uint32_t empty0 = smem_u32(&empty_bar[0]);
-      for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs, ++t) {
+      WorkIter it(p, pair_id, num_pairs);
+      WorkItem w;
+      for (; ok && it.next(w); ++t) {
         const uint32_t buf = t & 1u;
         const uint32_t bph = (t >> 1) & 1u;
         const long long tw0 = p.trace ? clock64() : 0;
@@ -270,8 +328,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + buf * kMaxBN;
         uint32_t accum = 0;
-        const int kb_begin = (tile % p.splits) * kb_per_split;
-        const int ktotal = (min(p.kblocks, kb_begin + kb_per_split) - kb_begin) * p.nseg;
+        const int ktotal = (w.kb_end - w.kb_begin) * p.nseg;
         for (int kk = 0; kk < ktotal; ++kk) {
           if (!ready) {
             const long long tw = p.trace ? clock64() : 0;
@@ -329,9 +386,11 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
     uint8_t* my_staging = staging + q * 2 * L::kStoreTileBytes;
     uint32_t t = 0, nstores = 0;
     long long w_tfull = 0, e_work = 0;
-    for (int tile = pair_id; tile < num_tiles; tile += num_pairs, ++t) {
+    WorkIter it(p, pair_id, num_pairs);
+    WorkItem w;
+    for (; it.next(w); ++t) {
       int g, mb, nb;
-      tile_coords(tile / p.splits, p.tiles_m, p.tiles_n, g, mb, nb);
+      tile_coords(w.tile, p.tiles_m, p.tiles_n, g, mb, nb);
       const uint32_t buf = t & 1u;
       const uint32_t bph = (t >> 1) & 1u;
       const long long tw = p.trace ? clock64() : 0;
@@ -342,9 +401,29 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
       const long long row0 = (long long)(mb * CTAS + (int)rank) * kBM + q * 32;
       const long long row = row0 + lane;
       const bool row_ok = row < p.M;
-      const long long c_row_off =
-          (long long)(tile % p.splits) * p.split_stride + (long long)g * p.c_stride_g + row * p.c_stride_m;
       const int ngroups = p.bn / 32;
+      const long long c_row_off =
+          (long long)w.split * p.split_stride + (long long)g * p.c_stride_g + row * p.c_stride_m;
+      // stream-K: 16-byte word i of column group c of this thread's row in the partial tile of unit u
+      const int tile_row = (int)rank * kBM + q * 32 + lane;
+      auto sk_word = [&](int u, int c, int i) -> uint4* {
+        return reinterpret_cast<uint4*>(p.sk_partial) +
+               (((size_t)u * ngroups + c) * 8 + i) * (size_t)(kBM * CTAS) + tile_row;
+      };
+      if (w.kind == 1) {
+        // owner: the partial tiles it needs were produced at the start of the other units' ranges; this warp only
+        // needs the rows written by the same warp of the same CTA of each contributing unit
+        bool got = true;
+        for (int u = w.first_contrib; u < w.first_contrib + w.n_contrib && got; ++u) {
+          const volatile unsigned int* flag = p.sk_flags + u * 8 + (int)rank * 4 + q;
+          const long long t0 = clock64();
+          while (*flag != p.sk_token) {
+            if (clock64() - t0 > kWaitCycles) { atomicCAS(p.status, 0u, kStatusTimeoutAux + 1); got = false; break; }
+          }
+        }
+        __threadfence();
+        if (!got) break;
+      }
 #pragma unroll 1
       for (int c = 0; c < ngroups; ++c) {
         const int n0 = nb * p.bn + c * 32;
@@ -353,11 +432,32 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
         uint32_t v[32];
         tmem_ld32(tmem_base + (uint32_t(q * 32) << 16) + buf * kMaxBN + c * 32, v);
         tmem_ld_wait();
-        uint4 w[8];
+        if (w.kind == 2) {  // contributor: raw accumulators to this unit's partial tile
+#pragma unroll
+          for (int i = 0; i < 8; ++i) *sk_word(pair_id, c, i) = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+          continue;
+        }
+        if (w.kind == 1) {  // owner: add the other units' partial tiles in unit order
+          for (int u = w.first_contrib; u < w.first_contrib + w.n_contrib; ++u) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const uint4 x4 = __ldcg(sk_word(u, c, i));
+              if (p.acc_is_int) {
+                v[4 * i] += x4.x; v[4 * i + 1] += x4.y; v[4 * i + 2] += x4.z; v[4 * i + 3] += x4.w;
+              } else {
+                v[4 * i] = __float_as_uint(__fadd_rn(__uint_as_float(v[4 * i]), __uint_as_float(x4.x)));
+                v[4 * i + 1] = __float_as_uint(__fadd_rn(__uint_as_float(v[4 * i + 1]), __uint_as_float(x4.y)));
+                v[4 * i + 2] = __float_as_uint(__fadd_rn(__uint_as_float(v[4 * i + 2]), __uint_as_float(x4.z)));
+                v[4 * i + 3] = __float_as_uint(__fadd_rn(__uint_as_float(v[4 * i + 3]), __uint_as_float(x4.w)));
+              }
+            }
+          }
+        }
+        uint4 w4[8];
         int nw;
         if (raw_i32) {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) w[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+          for (int i = 0; i < 8; ++i) w4[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
           nw = 8;
         } else {
           float x[32];
@@ -372,7 +472,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
             }
           }
           if (p.c_tma || (p.vec_ok && n0 + 32 <= p.N)) {
-            nw = pack_row32(x, p.c_type, w);
+            nw = pack_row32(x, p.c_type, w4);
           } else {
             nw = 0;
             if (row_ok) {
@@ -395,7 +495,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
           for (int i = 0; i < 8; ++i) {
             if (i < nw) {
               const int piece = sub * nw + i;
-              *reinterpret_cast<uint4*>(stg + lane * kRowBytes + ((piece ^ (lane & 7)) << 4)) = w[i];
+              *reinterpret_cast<uint4*>(stg + lane * kRowBytes + ((piece ^ (lane & 7)) << 4)) = w4[i];
             }
           }
           const bool last_group = (sub == groups_per_store - 1) || (n0 + 32 >= p.N) || (c == ngroups - 1);
@@ -413,7 +513,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
             uint4* d = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.c) + (c_row_off + n0) * es_c);
 #pragma unroll
             for (int i = 0; i < 8; ++i)
-              if (i < nw) d[i] = w[i];
+              if (i < nw) d[i] = w4[i];
           } else {  // raw i32 with a ragged or strided destination
 #pragma unroll
             for (int j = 0; j < 32; ++j)
@@ -425,6 +525,11 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
       // This warp has drained its quarter of the accumulator buffer.
       tc_fence_before();
       __syncwarp();
+      if (w.kind == 2) {
+        __threadfence();          // the partial tile is visible before the flag
+        __syncwarp();
+        if (lane == 0) *reinterpret_cast<volatile unsigned int*>(p.sk_flags + pair_id * 8 + (int)rank * 4 + q) = p.sk_token;
+      }
       if (lane == 0) {
         if constexpr (CTAS == 1) mbar_arrive(&tempty_bar[buf]);
         else mbar_arrive_cluster(&tempty_bar[buf], 0);

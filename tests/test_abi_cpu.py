@@ -43,6 +43,9 @@ def test_workspace_size_needs_no_device(lib):
     # gemm K): a pitched copy of A
     p = L.RbGemmProblem(1, 4096, 4096, 4096, 0, 0, 0, L.F16, L.F16, 0)
     assert lib.rbGemmWorkspaceSize(C.byref(p)) == 0
+    lib.rbSetGemmVariant(0x200)          # opt-in stream-K tail: one f32 partial tile per CTA pair plus arrival words
+    assert lib.rbGemmWorkspaceSize(C.byref(p)) == 74 * 256 * 256 * 4 + 74 * 8 * 4 + 192  # words rounded up to 256 B
+    lib.rbSetGemmVariant(0)
     p = L.RbGemmProblem(1, 1024, 512, 769, 0, 0, 0, L.F16, L.F16, 0)
     assert lib.rbGemmWorkspaceSize(C.byref(p)) >= 1024 * 776 * 2
     # f32 accurate mode needs hi/lo planes of both operands

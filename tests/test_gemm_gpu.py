@@ -235,3 +235,30 @@ def test_gemm_gemm_matches_oracle(cuda_device, m, k1, n1, n2):
     ref = oracle.round_to(oracle.gemm_gemm(af[rows], b1f, b2f, oracle.F16, threads=oracle.max_threads()), oracle.F16)
     verdict, info = oracle.verify_float(got[rows], ref, 1e-3, 100.0, 1e30)
     assert verdict == [1, 1, 1], info
+
+
+@pytest.mark.parametrize("code,shape", [(oracle.F16, (1, 2304, 2560, 1024)), (oracle.I8, (1, 1300, 3000, 2048)),
+                                        (oracle.F16, (2, 1200, 1100, 640))])
+@pytest.mark.parametrize("ctas", [1, 2])
+def test_stream_k_tail_exact(cuda_device, code, shape, ctas):
+    """Opt-in stream-K tail (variant bit 9): tiles of the last waves are dealt out by K blocks, partial tiles are
+    summed by the owning CTA in unit order. Integer-valued data: must equal the oracle (and the plain schedule) exactly."""
+    import ctypes as C
+    from rocmlir_b200 import _lib as L
+    g, m, n, k = shape
+    variant = 0x200 | ctas
+    L.lib().rbSetGemmVariant(variant)
+    prob = L.RbGemmProblem(g, m, n, k, 0, 0, 0, code, oracle.I32 if code == oracle.I8 else code, 0)
+    assert L.lib().rbGemmWorkspaceSize(C.byref(prob)) > 0, "the shape must trigger the stream-K tail"
+    L.lib().rbSetGemmVariant(0)
+    if code == oracle.I8:
+        a = uniform_int8((g, m, k), seed=61)
+        b = uniform_int8((g, k, n), seed=62)
+        ref = oracle.gemm_i8(a, b, g, m, n, k, threads=oracle.max_threads())
+        got = run_gemm(a, b, oracle.I8, oracle.I32, variant=variant)
+        assert oracle.verify_int(got, ref)[0] == [1, 1, 1]
+    else:
+        (af, araw), (bf, braw) = reference_random([(g, m, k), (g, k, n)], code, seed=1)
+        ref = oracle.from_f32(oracle.gemm_f32(af, bf, g, m, n, k, threads=oracle.max_threads()), code)
+        got = run_gemm(araw, braw, code, code, variant=variant)
+        np.testing.assert_array_equal(got.reshape(ref.shape), ref)
