@@ -155,8 +155,157 @@ def run_reference(args, rank: int, world: int):
     print(json.dumps(line), flush=True)
 
 
+# ---------------------------------------------------------------------------------------------------------
+# Secondary workloads (--workload NAME): the other configurations of the baseline, one JSON line each with the
+# same keys (device-resident throughput + roofline; no end-to-end or CPU leg). The headline stays gemm_f16.
+# ---------------------------------------------------------------------------------------------------------
+RESNET = {"a": dict(c=64, k=64, h=56, w=56, y=3, x=3, pad_h=1, pad_w=1),
+          "b": dict(c=256, k=64, h=56, w=56, y=1, x=1),
+          "c": dict(c=128, k=128, h=28, w=28, y=3, x=3, stride_h=2, stride_w=2, pad_h=1, pad_w=1),
+          "d": dict(c=512, k=2048, h=7, w=7, y=1, x=1)}
+
+
+def build_workload(name, dev, sets):
+    """Returns (step_fn, work_per_step, unit, algorithmic_bytes_per_step, bound, dtype, description, kernel)."""
+    import math
+    import torch
+    from rocmlir_b200.gemm import Epilogue, gemm, gemm_gemm, problem, workspace_size
+    from rocmlir_b200 import _lib as L
+    g = torch.Generator(device="cpu").manual_seed(1)
+
+    def randn(shape, scale, dtype):
+        return (torch.randn(shape, generator=g) * scale).to(dtype).to(dev)
+
+    if name.startswith("gemm_"):
+        kind = name[5:]
+        if kind in ("f16", "bf16", "f16_bias_relu"):
+            dt = torch.bfloat16 if kind == "bf16" else torch.float16
+            m = n = k = 4096
+            ops = [(randn((m, k), 0.1, dt), randn((k, n), 0.1, dt), torch.empty((m, n), dtype=dt, device=dev)) for _ in range(sets)]
+            epi = None
+            if kind == "f16_bias_relu":
+                epi = Epilogue(bias=randn((n,), 0.1, dt), relu=True, mid_type=L.F16)
+            ws = torch.empty(max(16, workspace_size(problem(ops[0][0], ops[0][1], False, False, False, dt))), dtype=torch.uint8, device=dev)
+            step = lambda: [gemm(a, b, out=c, epilogue=epi, workspace=ws) for a, b, c in ops]
+            return step, 2.0 * m * n * k * sets, "TFLOP/s", 3.0 * m * n * 2 * sets, "tensor", kind.split("_")[0], \
+                f"{kind} GEMM 4096^3, A,B row-major, f32 accumulate" + (", C' = relu(C + bias[N])" if epi else ""), "gemm_tcgen05_kernel"
+        m, n, k = 2048, 11008, 4096
+        if kind.startswith("i8"):
+            ops = [(torch.randint(-127, 128, (m, k), generator=g, dtype=torch.int8).to(dev),
+                    torch.randint(-127, 128, (n, k), generator=g, dtype=torch.int8).to(dev)) for _ in range(sets)]
+            requant = kind == "i8_requant"
+            odt = torch.int8 if requant else torch.int32
+            outs = [torch.empty((m, n), dtype=odt, device=dev) for _ in range(sets)]
+            epi = Epilogue(col_scale=(torch.rand(n, generator=g) * 0.009 + 0.001).to(dev), requant_scale=12.0) if requant else None
+            step = lambda: [gemm(a, b, trans_b=True, out=c, out_dtype=odt, epilogue=epi) for (a, b), c in zip(ops, outs)]
+            obytes = 1 if requant else 4
+            return step, 2.0 * m * n * k * sets, "TOP/s", (m * k + n * k + m * n * obytes) * sets, "tensor", "i8", \
+                f"int8 GEMM 2048x11008x4096 (B stored N x K), i32 accumulate" + (", dequant x s_col[n], requant to i8 (RNE, saturate)" if requant else ", i32 out"), "gemm_tcgen05_kernel"
+        if kind == "fp8":
+            ops = [(randn((m, k), 1.0, torch.float8_e4m3fn), randn((n, k), 1.0, torch.float8_e4m3fn)) for _ in range(sets)]
+            outs = [torch.empty((m, n), dtype=torch.bfloat16, device=dev) for _ in range(sets)]
+            epi = Epilogue(alpha=0.25 * 0.5)
+            step = lambda: [gemm(a, b, trans_b=True, out=c, out_dtype=torch.bfloat16, epilogue=epi) for (a, b), c in zip(ops, outs)]
+            return step, 2.0 * m * n * k * sets, "TFLOP/s", (m * k + n * k + m * n * 2) * sets, "tensor", "fp8", \
+                "fp8-e4m3 GEMM 2048x11008x4096 (B stored N x K), f32 accumulate, x sA*sB, bf16 out", "gemm_tcgen05_kernel"
+    if name == "gemm_gemm_f16":
+        m, k1, n1, n2 = 4096, 1024, 1024, 1024
+        ops = [(randn((m, k1), 0.1, torch.float16), randn((k1, n1), 0.1, torch.float16), randn((n1, n2), 0.1, torch.float16),
+                torch.empty((m, n2), dtype=torch.float16, device=dev)) for _ in range(sets)]
+        ws = torch.empty(64 << 20, dtype=torch.uint8, device=dev)
+        step = lambda: [gemm_gemm(a, b1, b2, out=o, workspace=ws) for a, b1, b2, o in ops]
+        return step, (2.0 * m * k1 * n1 + 2.0 * m * n1 * n2) * sets, "TFLOP/s", 2.0 * (m * k1 + k1 * n1 + n1 * n2 + m * n2) * sets, \
+            "tensor", "f16", "fp16 GEMM+GEMM M4096 K1 1024 N1 1024 N2 1024 (two launches, intermediate in L2)", "gemm_tcgen05_kernel x2"
+    if name.startswith("conv_"):
+        from rocmlir_b200.conv import ConvConfig, conv, workspace_size as conv_ws
+        if name == "conv_f32_nchw":
+            cfg = ConvConfig(n=16, c=64, k=64, h=56, w=56, y=3, x=3, pad_h=1, pad_w=1, fil_layout="kcyx", in_layout="nchw", out_layout="nkhw")
+            dt, direction, scale, lo = torch.float32, 0, None, True
+            desc = "fp32 conv2d forward NCHW/KCYX N16 C64 56x56 K64 3x3 s1 p1, uniform[-1,1)"
+        else:
+            _, _, _, shape, dirname = name.split("_", 4)  # conv_f16_nhwc_<a-d>_<fwd|bwd_data|bwd_weight>
+            direction = {"fwd": 0, "bwd_data": 1, "bwd_weight": 2}[dirname]
+            cfg = ConvConfig(n=256, **RESNET[shape])
+            dt = torch.float16
+            desc = f"fp16 NHWC conv N256 {RESNET[shape]} {dirname}, tensors ~ 0.05*N(0,1)"
+        nsets = max(1, min(sets, 2))
+        ts = []
+        for _ in range(nsets):
+            if dt == torch.float32:
+                mk = lambda nel: (torch.rand(nel, generator=g) * 2 - 1).to(dev)
+            else:
+                mk = lambda nel: (torch.randn(nel, generator=g) * 0.05).to(dt).to(dev)
+            ts.append((mk(cfg.numel("fil")), mk(cfg.numel("in")), mk(cfg.numel("out"))))
+        ws = torch.empty(max(16, conv_ws(cfg, dt, direction)), dtype=torch.uint8, device=dev)
+        step = lambda: [conv(cfg, direction, f, i, o, workspace=ws) for f, i, o in ts]
+        es = 4 if dt == torch.float32 else 2
+        abytes = (cfg.numel("fil") + cfg.numel("in") + cfg.numel("out")) * es * nsets
+        ai = cfg.flops() / (abytes / nsets)
+        return step, cfg.flops() * nsets, "TFLOP/s", abytes, ("tensor" if ai > 281 else "hbm"), ("f32" if es == 4 else "f16"), desc, \
+            "conv_gather / permute5 + gemm_tcgen05_kernel"
+    if name.startswith("attention_f16"):
+        from rocmlir_b200.attention import attention, flops
+        causal = name.endswith("causal")
+        G, S, D = 512, 2048, 128
+        q = randn((G, S, D), 1.0, torch.float16); kk = randn((G, D, S), 1.0, torch.float16); v = randn((G, S, D), 1.0, torch.float16)
+        o = torch.empty_like(q)
+        step = lambda: attention(q, kk, v, scale=1.0 / math.sqrt(D), causal=causal, out=o)
+        return step, flops(G, S, S, D, D, causal), "TFLOP/s", 4.0 * G * S * D * 2, "tensor", "f16", \
+            f"fp16 attention batch 16 x 32 heads, S 2048, D 128, {'causal' if causal else 'non-causal'}, Q/K/V ~ N(0,1)", "attention_fwd_kernel"
+    raise SystemExit(f"unknown workload {name}")
+
+
+WORKLOADS = (["gemm_f16", "gemm_bf16", "gemm_f16_bias_relu", "gemm_i8", "gemm_i8_requant", "gemm_fp8", "gemm_gemm_f16",
+              "conv_f32_nchw", "attention_f16", "attention_f16_causal"] +
+             [f"conv_f16_nhwc_{s}_{d}" for s in "abcd" for d in ("fwd", "bwd_data", "bwd_weight")])
+
+
+def run_secondary(args, name, rank, world, local_rank):
+    import torch
+    from rocmlir_b200 import _lib as L
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    step, work, unit, abytes, bound, dtype, desc, kernel = build_workload(name, dev, args.sets)
+    for _ in range(max(3, args.warmup)):
+        step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    l0 = L.launch_count()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    launches = L.launch_count() - l0
+    clocks = sampler.stop()
+    peaks = measured_peaks()
+    value = work * args.steps / (ms * 1e-3) / 1e12
+    kind = "burst" if ms < 1000.0 else "sustained"
+    if bound == "tensor":
+        # the measured tensor peak is a bf16 figure; 8-bit kinds are held against twice it, f32 (3xTF32) against a sixth
+        mult = {"i8": 2.0, "fp8": 2.0, "f32": 1.0 / 6.0}.get(dtype, 1.0)
+        peak, achieved, runit = peaks[kind] * mult, value, unit
+    else:
+        peak, achieved, runit = peaks["hbm"], abytes * args.steps / (ms * 1e-3) / 1e9, "GB/s"
+    line = {"metric": f"{unit}, {desc}", "value": value, "unit": unit, "n_gpus": 1, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": dtype, "data": "synthetic",
+            "config": {"workload": desc, "kernel_status": L.kernel_status(),
+                       "l2": "operand sets rotate / tensors exceed L2" if abytes > 126e6 else "working set fits L2 (stated)"},
+            "roofline": {"bound": bound, "achieved": achieved, "peak": peak, "unit": runit, "frac": achieved / peak,
+                         "peak_source": f"{peaks['source']} ({kind}; {'HBM copy' if bound == 'hbm' else 'cuBLAS bf16 x type factor'})",
+                         "traffic": None, "algorithmic_bytes": abytes, "kernel": kernel,
+                         "avg_launch_ms": ms / max(1, launches)},
+            "e2e": None, "gpu_launches": int(launches), "clocks": clocks}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--workload", default="gemm_f16", help="gemm_f16 (headline) or one of bench.WORKLOADS / 'all'")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=3)
@@ -173,6 +322,11 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank, world)
+        return
+    if args.workload != "gemm_f16":
+        if rank == 0:
+            for name in (WORKLOADS[1:] if args.workload == "all" else [args.workload]):
+                run_secondary(args, name, rank, world, local_rank)
         return
 
     import torch

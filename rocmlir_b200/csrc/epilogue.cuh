@@ -50,6 +50,47 @@ __device__ __forceinline__ float epi_apply(float x, const EpiParams& e, long lon
   return x;
 }
 
+// The same steps on 32 consecutive columns held in registers, one uniform branch per step instead of per element.
+// `cs` / `bs` point at the 32 per-column scales / biases of these columns, already converted to f32 (shared memory).
+__device__ __forceinline__ void epi_apply32(float* x, const EpiParams& e, const float* cs, const float* bs) {
+  if (e.flags & RB_EPI_ROUND_MID) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) x[j] = round_to_type(x[j], e.mid_type);
+  }
+  if (e.flags & RB_EPI_ALPHA) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) x[j] = __fmul_rn(x[j], e.alpha);
+  }
+  if (e.flags & RB_EPI_COL_SCALE) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+      const float4 s4 = *reinterpret_cast<const float4*>(cs + j);
+      x[j] = __fmul_rn(x[j], s4.x); x[j + 1] = __fmul_rn(x[j + 1], s4.y);
+      x[j + 2] = __fmul_rn(x[j + 2], s4.z); x[j + 3] = __fmul_rn(x[j + 3], s4.w);
+    }
+  }
+  if (e.flags & RB_EPI_BIAS) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+      const float4 b4 = *reinterpret_cast<const float4*>(bs + j);
+      x[j] = __fadd_rn(x[j], b4.x); x[j + 1] = __fadd_rn(x[j + 1], b4.y);
+      x[j + 2] = __fadd_rn(x[j + 2], b4.z); x[j + 3] = __fadd_rn(x[j + 3], b4.w);
+    }
+    if (e.flags & RB_EPI_ROUND_MID) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) x[j] = round_to_type(x[j], e.mid_type);
+    }
+  }
+  if (e.flags & RB_EPI_RELU) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) x[j] = fmaxf(x[j], 0.0f);
+  }
+  if (e.flags & RB_EPI_REQUANT) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) x[j] = __fmul_rn(x[j], e.out_recip);
+  }
+}
+
 // float -> integer cast of tosa.cast: round half to even, then saturate
 // (external/llvm-project/mlir/lib/Conversion/TosaToLinalg/TosaToLinalg.cpp:497-555).
 __device__ __forceinline__ int f32_to_int_sat(float x, int lo, int hi) {

@@ -118,7 +118,7 @@ struct GemmConfig {
   int dp_tiles, sk_tiles;  // stream-K tail (see GemmParams); sk_tiles == 0: every tile is computed whole
 };
 
-GemmConfig choose_config(const RbGemmProblem* p, int variant) {
+GemmConfig choose_config(const RbGemmProblem* p, int variant, bool epi_vec = false) {
   GemmConfig c;
   const int es = (int)dtype_bytes(p->ab_type);
   const bool b_mn = p->ab_type != RB_F32 && p->trans_b == 0;
@@ -130,7 +130,7 @@ GemmConfig choose_config(const RbGemmProblem* p, int variant) {
   if (b_mn && (c.bn / 2) % che != 0) c.ctas = 1;
   if (p->m <= kBM && (variant & 0xF) != 2) c.ctas = 1;      // a pair would compute 128 empty rows
   c.stages = (variant >> 4) & 0xF;
-  const int max_stages = c.ctas == 2 ? GemmSmemLayout<2>::max_stages(c.bn) : GemmSmemLayout<1>::max_stages(c.bn);
+  const int max_stages = c.ctas == 2 ? GemmSmemLayout<2>::max_stages(c.bn, epi_vec) : GemmSmemLayout<1>::max_stages(c.bn, epi_vec);
   if (c.stages <= 0 || c.stages > max_stages) c.stages = max_stages;
   c.plain_stores = ((variant >> 8) & 1) != 0;
   const int bke = kRowBytes / es;
@@ -323,7 +323,8 @@ extern "C" RbStatus rbGemm(const RbGemmProblem* p, const RbEpilogue* epi, const 
   const OperandPlan oa = plan_operand(p->trans_a != 0 /* A stored G x K x M */, p->m, p->k, es, is_f32, split);
   const OperandPlan ob = plan_operand(p->trans_b == 0 /* B stored G x K x N */, p->n, p->k, es, is_f32, split);
   const bool a_mn = oa.mn_major, b_mn = ob.mn_major;
-  GemmConfig cfg = choose_config(p, t_variant);
+  const bool epi_vec = (flags & (RB_EPI_COL_SCALE | RB_EPI_BIAS)) != 0;
+  GemmConfig cfg = choose_config(p, t_variant, epi_vec);
   Workspace ws = plan_workspace(p, oa, ob, cfg);
   if (cfg.sk_tiles > 0 && (!workspace || workspace_bytes < ws.total)) {
     // the stream-K tail is an optimisation: without room for its partial tiles every tile is computed whole
@@ -498,7 +499,8 @@ extern "C" RbStatus rbGemm(const RbGemmProblem* p, const RbEpilogue* epi, const 
   }
 
   GemmKernel kern = ctas == 2 ? pick_kernel<2>(kind, a_mn, b_mn) : pick_kernel<1>(kind, a_mn, b_mn);
-  const int smem = ctas == 2 ? GemmSmemLayout<2>::total(stages, bn) : GemmSmemLayout<1>::total(stages, bn);
+  const bool kernel_epi_vec = splits == 1 && epi_vec;  // with a K split the reduction kernel applies the epilogue
+  const int smem = ctas == 2 ? GemmSmemLayout<2>::total(stages, bn, kernel_epi_vec) : GemmSmemLayout<1>::total(stages, bn, kernel_epi_vec);
   RB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
 
   cudaLaunchConfig_t lc;

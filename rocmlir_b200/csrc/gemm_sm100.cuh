@@ -94,11 +94,14 @@ struct GemmSmemLayout {
   static constexpr int kStoreTileBytes = 32 * kRowBytes;
   static constexpr int kStagingBytes = 4 * 2 * kStoreTileBytes;
   static constexpr int kBarBytes = 512;
-  static constexpr int total(int stages, int bn) {
-    return stages * stage_bytes(bn) + kStagingBytes + kBarBytes + 1024;  // + alignment slack
+  // Per-column epilogue vectors of the current tile as f32, one private copy per epilogue warp (no cross-warp
+  // barrier is needed that way): [4 warps][scale[kMaxBN], bias[kMaxBN]].
+  static constexpr int kEpiVecBytes = 4 * 2 * kMaxBN * 4;
+  static constexpr int total(int stages, int bn, bool epi_vec) {
+    return stages * stage_bytes(bn) + kStagingBytes + (epi_vec ? kEpiVecBytes : 0) + kBarBytes + 1024;  // + alignment slack
   }
-  static constexpr int max_stages(int bn) {
-    int s = (kSmemBudget - kStagingBytes - kBarBytes - 1024) / stage_bytes(bn);
+  static constexpr int max_stages(int bn, bool epi_vec) {
+    int s = (kSmemBudget - kStagingBytes - (epi_vec ? kEpiVecBytes : 0) - kBarBytes - 1024) / stage_bytes(bn);
     return s > kMaxStages ? kMaxStages : s;
   }
 };
@@ -182,7 +185,9 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int stages = p.stages;
   uint8_t* staging = smem + stages * stage_bytes;  // 1024-byte aligned (stage sizes are multiples of 1024)
-  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + L::kStagingBytes);
+  const bool epi_vec = (p.epi.flags & (RB_EPI_COL_SCALE | RB_EPI_BIAS)) != 0;
+  float* epi_vecs = reinterpret_cast<float*>(staging + L::kStagingBytes);   // present only when epi_vec
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + L::kStagingBytes + (epi_vec ? L::kEpiVecBytes : 0));
   uint64_t* full_bar = bars;                       // [stages]
   uint64_t* empty_bar = bars + stages;             // [stages]
   uint64_t* tfull_bar = bars + 2 * stages;         // [2]
@@ -402,6 +407,18 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
       const long long row = row0 + lane;
       const bool row_ok = row < p.M;
       const int ngroups = p.bn / 32;
+      // Per-column scales / biases of this tile, converted to f32, in this warp's private copy.
+      float* vec_scale = epi_vecs + q * (2 * kMaxBN);
+      float* vec_bias = vec_scale + kMaxBN;
+      if (epi_vec) {
+        __syncwarp();  // the previous tile's reads of the copy are done
+        for (int j = lane; j < p.bn; j += 32) {
+          const int n = min(nb * p.bn + j, p.N - 1);
+          if (p.epi.flags & RB_EPI_COL_SCALE) vec_scale[j] = __ldg(p.epi.col_scale + n);
+          if (p.epi.flags & RB_EPI_BIAS) vec_bias[j] = load_bias(p.epi.bias, p.epi.bias_type, n);
+        }
+        __syncwarp();
+      }
       const long long c_row_off =
           (long long)w.split * p.split_stride + (long long)g * p.c_stride_g + row * p.c_stride_m;
       // stream-K: 16-byte word i of column group c of this thread's row in the partial tile of unit u
@@ -466,10 +483,8 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
             for (int j = 0; j < 32; ++j) x[j] = p.acc_is_int ? __int2float_rn((int)v[j]) : __uint_as_float(v[j]);
           } else {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const float a = p.acc_is_int ? __int2float_rn((int)v[j]) : __uint_as_float(v[j]);
-              x[j] = epi_apply(a, p.epi, min(n0 + j, p.N - 1));
-            }
+            for (int j = 0; j < 32; ++j) x[j] = p.acc_is_int ? __int2float_rn((int)v[j]) : __uint_as_float(v[j]);
+            epi_apply32(x, p.epi, vec_scale + c * 32, vec_bias + c * 32);
           }
           if (p.c_tma || (p.vec_ok && n0 + 32 <= p.N)) {
             nw = pack_row32(x, p.c_type, w4);
