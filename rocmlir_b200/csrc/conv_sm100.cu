@@ -127,6 +127,7 @@ struct ConvPlan {
   RbGemmProblem gemm;
   // matrices: element counts (0 = operand used as it lies)
   bool a_direct, b_direct, c_direct;
+  bool a_implicit;   // forward: the A matrix is never built; the GEMM producer loads it from the NHWC input (TMA im2col)
   size_t a_bytes, b_bytes, c_bytes, gemm_ws;
   size_t a_off, b_off, c_off, gemm_off, total;
 };
@@ -175,6 +176,7 @@ RbStatus make_plan(const RbConvProblem* p, ConvPlan* pl) {
                          p->pad_w == 0 && p->pad_h_r == 0 && p->pad_w_r == 0;
   RbGemmProblem& gp = pl->gemm;
   memset(&gp, 0, sizeof(gp));
+  pl->a_implicit = false;
   gp.g = (int)G;
   gp.ab_type = t;
   gp.f32_mode = p->f32_mode;
@@ -191,6 +193,12 @@ RbStatus make_plan(const RbConvProblem* p, ConvPlan* pl) {
     pl->a_direct = pointwise && in_is_mat;
     pl->b_direct = fil_is_mat;
     pl->c_direct = out_is_mat;
+    // NHWC input, one group, channels a multiple of the 128-byte K block, 8/16-bit types: implicit GEMM.
+    // Corner / offset fields of the im2col descriptor are small signed integers; stay well inside them.
+    pl->a_implicit = !pl->a_direct && in_is_mat && G == 1 && t != RB_F32 && (p->c * es) % 128 == 0 &&
+                     p->pad_h < 64 && p->pad_w < 64 && (p->y - 1) * p->dil_h < 256 && (p->x - 1) * p->dil_w < 256 &&
+                     p->stride_h <= 8 && p->stride_w <= 8;
+    if (pl->a_implicit) pl->a_direct = true;   // nothing to gather
     pl->a_bytes = pl->a_direct ? 0 : (size_t)G * pix_o * yxc * es;
     pl->b_bytes = pl->b_direct ? 0 : (size_t)G * p->k * yxc * es;
     pl->c_bytes = pl->c_direct ? 0 : (size_t)G * pix_o * p->k * es_o;
@@ -317,7 +325,17 @@ extern "C" RbStatus rbConv(const RbConvProblem* p, void* filter, void* input, vo
     if (pl.b_direct) B = filter; else { permute(filter, ws + pl.b_off, fsz, pl.fs, fil_yxkc, true, es); B = ws + pl.b_off; }
     C = pl.c_direct ? input : static_cast<void*>(ws + pl.c_off);
   }
-  st = rbGemm(&pl.gemm, nullptr, A, B, C, pl.gemm_ws ? ws + pl.gemm_off : nullptr, pl.gemm_ws, stream_v);
+  if (pl.a_implicit) {
+    ConvAOperand cv;
+    cv.tensor = input;
+    cv.N = p->n; cv.H = p->h; cv.W = p->w; cv.C = p->c;
+    cv.P = (int)ho; cv.Q = (int)wo; cv.Y = p->y; cv.X = p->x;
+    cv.stride_h = p->stride_h; cv.stride_w = p->stride_w; cv.dil_h = p->dil_h; cv.dil_w = p->dil_w;
+    cv.pad_h = p->pad_h; cv.pad_w = p->pad_w; cv.pad_h_hi = p->pad_h_r; cv.pad_w_hi = p->pad_w_r;
+    st = gemm_run(&pl.gemm, nullptr, nullptr, B, C, pl.gemm_ws ? ws + pl.gemm_off : nullptr, pl.gemm_ws, stream_v, &cv);
+  } else {
+    st = rbGemm(&pl.gemm, nullptr, A, B, C, pl.gemm_ws ? ws + pl.gemm_off : nullptr, pl.gemm_ws, stream_v);
+  }
   if (st != RB_SUCCESS) return st;
   if (!pl.c_direct) {
     if (p->direction == 0) permute(C, output, osz, pl.os, act_gmat, false, es_c);

@@ -287,8 +287,18 @@ extern "C" size_t rbGemmWorkspaceSize(const RbGemmProblem* p) {
 
 extern "C" RbStatus rbGemm(const RbGemmProblem* p, const RbEpilogue* epi, const void* a, const void* b, void* c,
                            void* workspace, size_t workspace_bytes, void* stream_v) {
+  return rb::gemm_run(p, epi, a, b, c, workspace, workspace_bytes, stream_v, nullptr);
+}
+
+RbStatus rb::gemm_run(const RbGemmProblem* p, const RbEpilogue* epi, const void* a, const void* b, void* c,
+                      void* workspace, size_t workspace_bytes, void* stream_v, const ConvAOperand* conva) {
   RbStatus st = check_problem(p);
   if (st != RB_SUCCESS) return st;
+  if (conva) {
+    if (p->g != 1 || p->trans_a || p->ab_type == RB_F32 || !conva->tensor)
+      return fail(RB_UNSUPPORTED, "implicit A operand: one group, K-major, 8/16-bit element types");
+    a = conva->tensor;
+  }
   if (!a || !b || !c) return fail(RB_INVALID_PARAM, "a, b and c must be device pointers");
   const DeviceInfo* dev = device_info();
   if (!dev) return RB_CUDA_ERROR;
@@ -320,7 +330,11 @@ extern "C" RbStatus rbGemm(const RbGemmProblem* p, const RbEpilogue* epi, const 
 
   const bool is_f32 = abt == RB_F32;
   const bool split = is_f32 && p->f32_mode == 0;
-  const OperandPlan oa = plan_operand(p->trans_a != 0 /* A stored G x K x M */, p->m, p->k, es, is_f32, split);
+  OperandPlan oa = plan_operand(p->trans_a != 0 /* A stored G x K x M */, p->m, p->k, es, is_f32, split);
+  if (conva) {  // fetched in place by im2col loads: never copied, never padded
+    oa.needs_copy = false;
+    oa.pitch = oa.cols;
+  }
   const OperandPlan ob = plan_operand(p->trans_b == 0 /* B stored G x K x N */, p->n, p->k, es, is_f32, split);
   const bool a_mn = oa.mn_major, b_mn = ob.mn_major;
   const bool epi_vec = (flags & (RB_EPI_COL_SCALE | RB_EPI_BIAS)) != 0;
@@ -423,8 +437,23 @@ extern "C" RbStatus rbGemm(const RbGemmProblem* p, const RbEpilogue* epi, const 
   const int nseg = split ? 3 : 1;
   const int seg_a[3] = {split ? 1 : 0, 0, 0};
   const int seg_b[3] = {0, 1, 0};
+  if (conva) {
+    const ConvAOperand& cv = *conva;
+    if (cv.C % bke != 0) return fail(RB_UNSUPPORTED, "implicit A operand: channels must be a multiple of the 128-byte K block");
+    if ((long long)cv.N * cv.P * cv.Q != p->m || (long long)cv.Y * cv.X * cv.C != p->k)
+      return fail(RB_INVALID_PARAM, "implicit A operand does not match the GEMM extents");
+    const uint64_t dims[4] = {(uint64_t)cv.C, (uint64_t)cv.W, (uint64_t)cv.H, (uint64_t)cv.N};
+    const uint64_t strides[3] = {(uint64_t)cv.C * es, (uint64_t)cv.W * cv.C * es, (uint64_t)cv.H * cv.W * cv.C * es};
+    // bounding box of the base pixel: from -pad to (extent - 1) + upper corner, so that stepping by the stride
+    // visits exactly P x Q positions (CUTLASS states the same rule for its fprop maps)
+    const int lower[2] = {-cv.pad_w, -cv.pad_h};
+    const int upper[2] = {cv.pad_w_hi - (cv.X - 1) * cv.dil_w, cv.pad_h_hi - (cv.Y - 1) * cv.dil_h};
+    const uint32_t trav[2] = {(uint32_t)cv.stride_w, (uint32_t)cv.stride_h};
+    if (!encode_im2col_nhwc(&maps.a[0], dt, cv.tensor, dims, strides, lower, upper, (uint32_t)bke, (uint32_t)kBM, trav, &err))
+      return fail(RB_UNSUPPORTED, "A (im2col): " + err);
+  }
   for (int s = 0; s < nseg; ++s) {
-    if (!encode_operand(&maps.a[s], a_src[seg_a[s]], oa, kBM, &err)) return fail(RB_UNSUPPORTED, "A: " + err);
+    if (!conva && !encode_operand(&maps.a[s], a_src[seg_a[s]], oa, kBM, &err)) return fail(RB_UNSUPPORTED, "A: " + err);
     if (!encode_operand(&maps.b[s], b_src[seg_b[s]], ob, bn / ctas, &err)) return fail(RB_UNSUPPORTED, "B: " + err);
   }
 
@@ -481,6 +510,12 @@ extern "C" RbStatus rbGemm(const RbGemmProblem* p, const RbEpilogue* epi, const 
   kp.status = dev->status_word;
   kp.stages = stages;
   kp.probe = (t_variant >> 24) & 3;
+  if (conva) {
+    kp.conva.enabled = 1; kp.conva.P = conva->P; kp.conva.Q = conva->Q; kp.conva.X = conva->X;
+    kp.conva.cchunks = conva->C / bke;
+    kp.conva.stride_h = conva->stride_h; kp.conva.stride_w = conva->stride_w;
+    kp.conva.dil_h = conva->dil_h; kp.conva.dil_w = conva->dil_w; kp.conva.pad_h = conva->pad_h; kp.conva.pad_w = conva->pad_w;
+  }
   kp.a_fused = a_fused ? 1 : 0;
   kp.b_fused = b_fused ? 1 : 0;
 

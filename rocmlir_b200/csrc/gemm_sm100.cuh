@@ -51,6 +51,17 @@ struct GemmTensorMaps {
   CUtensorMap c;  // store map of C (box: 128 bytes of a row x 32 rows); valid when GemmParams::c_tma != 0
 };
 
+// A operand fetched straight from an NHWC activation tensor (implicit GEMM): row m of A is output pixel m
+// (n, p, q in row-major order), column (y, x, c) is in[n][p*stride + y*dil - pad][q*stride + x*dil - pad][c].
+// One K block = one 128-byte run of channels of one filter tap.
+struct ConvAParams {
+  int enabled;
+  int P, Q;             // output image
+  int X;                // filter width (tap index = y * X + x)
+  int cchunks;          // channel chunks (K blocks) per tap
+  int stride_h, stride_w, dil_h, dil_w, pad_h, pad_w;
+};
+
 struct GemmParams {
   int G, M, N, K;
   int bn;                     // tile width in columns of C: UMMA N (a multiple of 32 * CTAS)
@@ -79,6 +90,7 @@ struct GemmParams {
   void* sk_partial;            // [units][bn / 32][8][kBM * CTAS] 16-byte words of raw accumulators (row fastest: coalesced)
   unsigned int* sk_flags;      // [units][8]: one word per (CTA of the pair, epilogue warp), set to sk_token when written
   unsigned int sk_token;       // unique per launch, so stale words of earlier launches never match
+  ConvAParams conva;
   int a_fused, b_fused;       // MN-major operand loaded with one 4-D box per stage (extent a multiple of the chunk)
   int probe;                  // instrumentation (results become meaningless): bit0 = no loads, bit1 = no epilogue work
   int stages;                 // shared-memory ring depth (<= GemmSmemLayout::kMaxStages)
@@ -243,6 +255,15 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
         const int n0 = nb * p.bn + (int)rank * bn_cta;
         const int kb_begin = w.kb_begin, kb_end = w.kb_end;
         const int ktotal = (kb_end - kb_begin) * p.nseg;
+        int img = 0, base_h = 0, base_w = 0;
+        if (p.conva.enabled) {
+          const int pq = p.conva.P * p.conva.Q;
+          img = m0 / pq;
+          const int rem = m0 - img * pq;
+          const int op = rem / p.conva.Q;
+          base_h = op * p.conva.stride_h - p.conva.pad_h;
+          base_w = (rem - op * p.conva.Q) * p.conva.stride_w - p.conva.pad_w;
+        }
         int seg = 0, kb = kb_begin;
         for (int kk = 0; kk < ktotal; ++kk) {
           const long long tw = p.trace ? clock64() : 0;
@@ -255,7 +276,12 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
             if (CTAS == 1 || rank == 0) mbar_arrive(&full_bar[s]);
           } else if constexpr (CTAS == 1) {
             mbar_expect_tx(&full_bar[s], stage_bytes);
-            if constexpr (!A_MN) {
+            if (!A_MN && p.conva.enabled) {
+              const int tap = kb / p.conva.cchunks, cc = kb - tap * p.conva.cchunks;
+              const int fy = tap / p.conva.X, fx = tap - fy * p.conva.X;
+              tma_load_im2col_4d(sa, &maps.a[seg], &full_bar[s], cc * BKE, base_w, base_h, img,
+                                 (uint16_t)(fx * p.conva.dil_w), (uint16_t)(fy * p.conva.dil_h));
+            } else if constexpr (!A_MN) {
               tma_load_3d(sa, &maps.a[seg], &full_bar[s], k0, m0, g);
             } else if (p.a_fused) {
               tma_load_4d(sa, &maps.a[seg], &full_bar[s], 0, k0, m0 / CHE, g);
@@ -276,7 +302,12 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
             // Completion of this CTA's loads is counted on the leader CTA's barrier.
             const uint32_t lead_full = mapa_u32(smem_u32(&full_bar[s]), 0);
             if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * stage_bytes);
-            if constexpr (!A_MN) {
+            if (!A_MN && p.conva.enabled) {
+              const int tap = kb / p.conva.cchunks, cc = kb - tap * p.conva.cchunks;
+              const int fy = tap / p.conva.X, fx = tap - fy * p.conva.X;
+              tma_load_im2col_4d_bar(sa, &maps.a[seg], lead_full, cc * BKE, base_w, base_h, img,
+                                     (uint16_t)(fx * p.conva.dil_w), (uint16_t)(fy * p.conva.dil_h));
+            } else if constexpr (!A_MN) {
               tma_load_3d_bar(sa, &maps.a[seg], lead_full, k0, m0, g);
             } else if (p.a_fused) {
               tma_load_4d_bar(sa, &maps.a[seg], lead_full, 0, k0, m0 / CHE, g);

@@ -19,6 +19,12 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeTiledFn g_encode = nullptr;
 std::once_flag g_encode_once;
+typedef CUresult (*EncodeIm2colFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const int*, const int*, cuuint32_t, cuuint32_t, const cuuint32_t*,
+                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                   CUtensorMapFloatOOBfill);
+EncodeIm2colFn g_encode_im2col = nullptr;
+std::once_flag g_encode_im2col_once;
 }  // namespace
 
 RbStatus fail(RbStatus st, const std::string& msg) {
@@ -90,6 +96,38 @@ bool encode_tiled(CUtensorMap* out, CUtensorMapDataType dt, int rank, const void
       for (int i = 0; i < rank; ++i) *err += " " + std::to_string(box[i]);
       *err += ")";
     }
+    return false;
+  }
+  return true;
+}
+
+bool encode_im2col_nhwc(CUtensorMap* out, CUtensorMapDataType dt, const void* base, const uint64_t dims[4],
+                        const uint64_t strides_bytes[3], const int lower_corner[2], const int upper_corner[2],
+                        uint32_t channels_per_pixel, uint32_t pixels_per_column, const uint32_t traversal_stride[2],
+                        std::string* err) {
+  std::call_once(g_encode_im2col_once, [] {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &fn, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      g_encode_im2col = reinterpret_cast<EncodeIm2colFn>(fn);
+  });
+  if (!g_encode_im2col) {
+    if (err) *err = "cuTensorMapEncodeIm2col is not available from the driver";
+    return false;
+  }
+  cuuint64_t d[4] = {dims[0], dims[1], dims[2], dims[3]};
+  cuuint64_t s[3] = {strides_bytes[0], strides_bytes[1], strides_bytes[2]};
+  cuuint32_t es[4] = {1, traversal_stride[0], traversal_stride[1], 1};
+  CUresult r = g_encode_im2col(out, dt, 4, const_cast<void*>(base), d, s, lower_corner, upper_corner,
+                               channels_per_pixel, pixels_per_column, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    if (err)
+      *err = "cuTensorMapEncodeIm2col failed with CUresult " + std::to_string((int)r) + " (corners " +
+             std::to_string(lower_corner[0]) + "," + std::to_string(lower_corner[1]) + " / " +
+             std::to_string(upper_corner[0]) + "," + std::to_string(upper_corner[1]) + ")";
     return false;
   }
   return true;

@@ -30,6 +30,26 @@ bool encode_tiled(CUtensorMap* out, CUtensorMapDataType dt, int rank, const void
                   const uint64_t* strides_bytes, const uint32_t* box, CUtensorMapSwizzle swizzle,
                   std::string* err);
 
+// im2col-mode map of an NHWC tensor: dims/strides innermost-first {C, W, H, N}; box = channels x pixels.
+bool encode_im2col_nhwc(CUtensorMap* out, CUtensorMapDataType dt, const void* base, const uint64_t dims[4],
+                        const uint64_t strides_bytes[3], const int lower_corner[2], const int upper_corner[2],
+                        uint32_t channels_per_pixel, uint32_t pixels_per_column, const uint32_t traversal_stride[2],
+                        std::string* err);
+
+// Implicit-GEMM description of the A operand for gemm_run: the activation tensor of a convolution.
+struct ConvAOperand {
+  const void* tensor;        // NHWC (dense), element type = the GEMM's ab_type
+  int N, H, W, C;            // tensor extents
+  int P, Q;                  // output image (GEMM M = N * P * Q)
+  int Y, X;                  // filter (GEMM K = Y * X * C)
+  int stride_h, stride_w, dil_h, dil_w;
+  int pad_h, pad_w;          // base pixel of output (p, q) = (p*stride_h - pad_h, q*stride_w - pad_w); may be negative pads
+  int pad_h_hi, pad_w_hi;    // upper paddings (bounding box of the base pixel)
+};
+// rbGemm with an optional implicit A operand (then `a` is ignored, trans_a must be 0, g must be 1).
+RbStatus gemm_run(const RbGemmProblem* p, const RbEpilogue* epi, const void* a, const void* b, void* c, void* workspace,
+                  size_t workspace_bytes, void* stream, const ConvAOperand* conva);
+
 inline size_t dtype_bytes(int t) {
   switch (t) {
     case RB_F32: case RB_I32: return 4;
