@@ -221,6 +221,18 @@ RbStatus make_plan(const RbConvProblem* p, ConvPlan* pl) {
     const int fil_yxkc[5] = {0, 3, 4, 1, 2};
     pl->b_direct = is_dense_in_order(pl->fs, fsz, fil_yxkc, 5);
     pl->c_direct = in_is_mat;
+    // Unit stride: the input gradient is a forward convolution of the output gradient with the filter taps
+    // mirrored, so the same implicit-GEMM path applies (A = NHWK output gradient read through im2col loads with
+    // padding (fil-1)*dil - pad; B = the filter rearranged to c x (y', x', k) with y' = Y-1-y, x' = X-1-x).
+    const long long bpad_h = (long long)(p->y - 1) * p->dil_h - p->pad_h, bpad_w = (long long)(p->x - 1) * p->dil_w - p->pad_w;
+    pl->a_implicit = !pl->a_direct && out_is_mat && G == 1 && t != RB_F32 && (p->k * es) % 128 == 0 &&
+                     p->stride_h == 1 && p->stride_w == 1 && bpad_h >= 0 && bpad_w >= 0 && bpad_h < 64 && bpad_w < 64 &&
+                     (p->y - 1) * p->dil_h < 256 && (p->x - 1) * p->dil_w < 256;
+    if (pl->a_implicit) {
+      pl->a_direct = true;
+      pl->b_direct = false;     // the mirrored c x (y',x',k) matrix is always built (it is filter-sized)
+      gp.trans_b = 1;           // B stored [N = c][K = (y',x',k)]
+    }
     pl->a_bytes = pl->a_direct ? 0 : (size_t)G * pix_i * yxk * es;
     pl->b_bytes = pl->b_direct ? 0 : (size_t)G * yxk * p->c * es;
     pl->c_bytes = pl->c_direct ? 0 : (size_t)G * pix_i * p->c * es;
@@ -322,16 +334,35 @@ extern "C" RbStatus rbConv(const RbConvProblem* p, void* filter, void* input, vo
     C = pl.c_direct ? filter : static_cast<void*>(ws + pl.c_off);
   } else {
     if (pl.a_direct) A = output; else { gather(output, ws + pl.a_off, true, true, p->h, p->w, p->k); A = ws + pl.a_off; }
-    if (pl.b_direct) B = filter; else { permute(filter, ws + pl.b_off, fsz, pl.fs, fil_yxkc, true, es); B = ws + pl.b_off; }
+    if (pl.a_implicit) {
+      // B[c][(y',x',k)] = fil[k][c][Y-1-y'][X-1-x']: walk y and x backwards from the last tap
+      long long mfs[5] = {pl.fs[0], pl.fs[1], pl.fs[2], -pl.fs[3], -pl.fs[4]};
+      const int fil_cyxk[5] = {0, 2, 3, 4, 1};
+      const uint8_t* last_tap = static_cast<const uint8_t*>(filter) + ((p->y - 1) * pl.fs[3] + (p->x - 1) * pl.fs[4]) * (long long)es;
+      permute(last_tap, ws + pl.b_off, fsz, mfs, fil_cyxk, true, es);
+      B = ws + pl.b_off;
+    } else if (pl.b_direct) B = filter; else { permute(filter, ws + pl.b_off, fsz, pl.fs, fil_yxkc, true, es); B = ws + pl.b_off; }
     C = pl.c_direct ? input : static_cast<void*>(ws + pl.c_off);
   }
   if (pl.a_implicit) {
     ConvAOperand cv;
-    cv.tensor = input;
-    cv.N = p->n; cv.H = p->h; cv.W = p->w; cv.C = p->c;
-    cv.P = (int)ho; cv.Q = (int)wo; cv.Y = p->y; cv.X = p->x;
-    cv.stride_h = p->stride_h; cv.stride_w = p->stride_w; cv.dil_h = p->dil_h; cv.dil_w = p->dil_w;
-    cv.pad_h = p->pad_h; cv.pad_w = p->pad_w; cv.pad_h_hi = p->pad_h_r; cv.pad_w_hi = p->pad_w_r;
+    if (p->direction == 0) {
+      cv.tensor = input;
+      cv.N = p->n; cv.H = p->h; cv.W = p->w; cv.C = p->c;
+      cv.P = (int)ho; cv.Q = (int)wo; cv.Y = p->y; cv.X = p->x;
+      cv.stride_h = p->stride_h; cv.stride_w = p->stride_w; cv.dil_h = p->dil_h; cv.dil_w = p->dil_w;
+      cv.pad_h = p->pad_h; cv.pad_w = p->pad_w; cv.pad_h_hi = p->pad_h_r; cv.pad_w_hi = p->pad_w_r;
+    } else {
+      // backward data, unit stride: "image" = output gradient (ho x wo x k), "output pixels" = input pixels (h x w)
+      cv.tensor = output;
+      cv.N = p->n; cv.H = (int)ho; cv.W = (int)wo; cv.C = p->k;
+      cv.P = p->h; cv.Q = p->w; cv.Y = p->y; cv.X = p->x;
+      cv.stride_h = 1; cv.stride_w = 1; cv.dil_h = p->dil_h; cv.dil_w = p->dil_w;
+      cv.pad_h = (p->y - 1) * p->dil_h - p->pad_h; cv.pad_w = (p->x - 1) * p->dil_w - p->pad_w;
+      // upper padding such that the base pixel takes exactly h (w) positions: h = ho + pad + pad_hi - (Y-1)*dil
+      cv.pad_h_hi = p->h - (int)ho - cv.pad_h + (p->y - 1) * p->dil_h;
+      cv.pad_w_hi = p->w - (int)wo - cv.pad_w + (p->x - 1) * p->dil_w;
+    }
     st = gemm_run(&pl.gemm, nullptr, nullptr, B, C, pl.gemm_ws ? ws + pl.gemm_off : nullptr, pl.gemm_ws, stream_v, &cv);
   } else {
     st = rbGemm(&pl.gemm, nullptr, A, B, C, pl.gemm_ws ? ws + pl.gemm_off : nullptr, pl.gemm_ws, stream_v);
