@@ -32,8 +32,8 @@ FLOPS_PER_GEMM = 2.0 * M * N * K                      # perfRunner.py:627-630 co
 BYTES_PER_GEMM = 3 * M * N * 2                        # each operand read once, C written once, f16
 METRIC = "TFLOP/s, fp16 GEMM M=N=K=4096 (rock.gemm, f32 accumulate, f16 out)"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of gemm_tcgen05_kernel on this workload, from the
-# ncu capture summarised in profiles/gemm_f16_4096_ncu.md (None until a capture exists).
-NCU_DRAM_BYTES_PER_LAUNCH = None
+# ncu capture summarised in profiles/gemm_f16_4096_ncu.md (89.3 MB read + 15.6 MB written).
+NCU_DRAM_BYTES_PER_LAUNCH = 104.97e6
 
 
 def measured_peaks():
