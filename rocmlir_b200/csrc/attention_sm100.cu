@@ -352,6 +352,343 @@ __global__ void __launch_bounds__(kAttThreads, 1) attention_fwd_kernel(const __g
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Two query tiles per CTA. One softmax group alone leaves the tensor pipe idle while it works: P_j.V_j has to wait
+// for softmax(j). With two 128-row query tiles (A, B) that share every K/V tile, the products of one tile run while
+// the other tile's softmax group computes:   ... PV_A(j)  S_A(j+1)  PV_B(j)  S_B(j+1) ...
+// 384 threads: warp 0 producer, warp 1 MMA issuer, warp 2 TMEM allocator, warps 4-7 softmax of tile A, warps 8-11
+// softmax of tile B. TMEM: S_A, S_B (P aliases their first 64 columns), O_A, O_B = 512 columns. The 128 scores of a
+// row are read in two halves (row maximum first, then exponentials) so that 384 threads fit the register file.
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int kAtt2Threads = 384;
+
+struct Att2Smem {
+  static constexpr int kQBytes = kQT * 256;        // one query tile, up to D = 128
+  static constexpr int kKBytes = kKT * 256;
+  static constexpr int kVBytes = kKT * 256;
+  static constexpr int kStages = 2;
+  static constexpr int kQ = 0;                     // two query tiles; each is reused as its tile's store staging
+  static constexpr int kK = kQ + 2 * kQBytes;
+  static constexpr int kV = kK + kStages * kKBytes;
+  static constexpr int kBars = kV + kStages * kVBytes;
+  static constexpr int kTotal = kBars + 256 + 1024;
+};
+
+__device__ __forceinline__ void tmem_ld64(uint32_t taddr, uint32_t* r) {
+  tmem_ld32(taddr, r);
+  tmem_ld32(taddr + 32, r + 32);
+}
+
+__global__ void __launch_bounds__(kAtt2Threads, 1) attention_fwd2_kernel(const __grid_constant__ AttMaps maps,
+                                                                          const AttParams p) {
+  constexpr int NS = Att2Smem::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Att2Smem::kBars);
+  uint64_t* q_full = bars + 0;
+  uint64_t* k_full = bars + 1;             // [NS]
+  uint64_t* k_empty = k_full + NS;         // [NS]
+  uint64_t* v_full = k_empty + NS;         // [NS]
+  uint64_t* v_empty = v_full + NS;         // [NS]
+  uint64_t* s_full = v_empty + NS;         // [2 tiles]
+  uint64_t* p_full = s_full + 2;           // [2 tiles]
+  uint64_t* pv_done = p_full + 2;          // [2 tiles]
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(pv_done + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = lane_id();
+  const int pair_tiles = (p.q_tiles + 1) / 2;            // CTAs per group
+  const int g = blockIdx.x / pair_tiles;
+  const int pt = p.causal ? (pair_tiles - 1 - blockIdx.x % pair_tiles) : (blockIdx.x % pair_tiles);
+  const int q0 = pt * (2 * kQT);
+  // key blocks each tile needs
+  const int nb_all = (p.Sk + kKT - 1) / kKT;
+  int nbt[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int tq0 = q0 + t * kQT;
+    if (tq0 >= p.Sq) nbt[t] = 0;
+    else nbt[t] = p.causal ? min(nb_all, (min(tq0 + kQT, p.Sq) - 1) / kKT + 1) : nb_all;
+  }
+  const int jmax = max(nbt[0], nbt[1]);
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < NS; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_empty[i], 1);
+    }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(&s_full[t], 1);
+      mbar_init(&p_full[t], 4);
+      mbar_init(&pv_done[t], 1);
+    }
+    fence_mbar_init();
+  }
+  if (warp == 2) {
+    tmem_alloc<1>(tmem_holder, 512);
+    tmem_relinquish<1>();
+  }
+  if (warp == 0 && lane == 0) {
+    prefetch_tmap(&maps.q);
+    prefetch_tmap(&maps.k);
+    prefetch_tmap(&maps.v);
+    prefetch_tmap(&maps.o);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;   // S_A 0, S_B 128, O_A 256, O_B 384
+
+  const int d_atoms = p.D / 64, dv_chunks = p.Dv / 64;
+  const uint32_t q_bytes = (uint32_t)kQT * p.D * 2, k_bytes = (uint32_t)kKT * p.D * 2, v_bytes = (uint32_t)kKT * p.Dv * 2;
+
+  if (warp == 0) {
+    // ------------------------------ producer ------------------------------
+    if (lane == 0) {
+      mbar_expect_tx(q_full, 2 * q_bytes);   // rows past the end of the sequence arrive as zeros
+      for (int t = 0; t < 2; ++t)
+        for (int a = 0; a < d_atoms; ++a)
+          tma_load_3d(smem + Att2Smem::kQ + t * Att2Smem::kQBytes + a * (kQT * 128), &maps.q, q_full, a * 64, q0 + t * kQT, g);
+      int s = 0;
+      uint32_t par = 0;
+      for (int j = 0; j < jmax; ++j) {
+        if (!mbar_wait(&k_empty[s], par ^ 1u, p.status, kStatusTimeoutProducer + s)) break;
+        uint8_t* ks = smem + Att2Smem::kK + s * Att2Smem::kKBytes;
+        mbar_expect_tx(&k_full[s], k_bytes);
+        if (p.trans_k) {
+          for (int a = 0; a < d_atoms; ++a) tma_load_3d(ks + a * (kKT * 128), &maps.k, &k_full[s], a * 64, j * kKT, g);
+        } else {
+          for (int c = 0; c < kKT / 64; ++c) tma_load_3d(ks + c * (p.D * 128), &maps.k, &k_full[s], j * kKT + c * 64, 0, g);
+        }
+        if (!mbar_wait(&v_empty[s], par ^ 1u, p.status, kStatusTimeoutProducer + 4 + s)) break;
+        uint8_t* vs = smem + Att2Smem::kV + s * Att2Smem::kVBytes;
+        mbar_expect_tx(&v_full[s], v_bytes);
+        for (int c = 0; c < dv_chunks; ++c) tma_load_3d(vs + c * (kKT * 128), &maps.v, &v_full[s], c * 64, j * kKT, g);
+        if (++s == NS) { s = 0; par ^= 1u; }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      const uint32_t hi = smem_desc_hi(1024);
+      const int ksteps = p.D / 16;
+      auto issue_s = [&](int t, int stage) {
+        const uint32_t q_addr = smem_u32(smem + Att2Smem::kQ + t * Att2Smem::kQBytes);
+        const uint32_t k_addr = smem_u32(smem + Att2Smem::kK + stage * Att2Smem::kKBytes);
+        for (int kk = 0; kk < ksteps; ++kk) {
+          const uint32_t a_lo = smem_desc_lo(q_addr + (kk >> 2) * (kQT * 128) + (kk & 3) * 32, 16);
+          const uint32_t b_lo = p.trans_k ? smem_desc_lo(k_addr + (kk >> 2) * (kKT * 128) + (kk & 3) * 32, 16)
+                                          : smem_desc_lo(k_addr + kk * 2048, (uint32_t)p.D * 128);
+          umma_ss<kKindF16, 1>(tmem_base + t * 128, desc64(a_lo, hi), desc64(b_lo, hi), p.idesc_s, kk ? 1u : 0u);
+        }
+        tc_commit<1>(&s_full[t]);
+      };
+      auto issue_pv = [&](int t, int stage, int j) {
+        const uint32_t v_addr = smem_u32(smem + Att2Smem::kV + stage * Att2Smem::kVBytes);
+        const uint32_t tmem_p = tmem_base + t * 128;
+        for (int kk = 0; kk < kKT / 16; ++kk) {
+          const uint32_t b_lo = smem_desc_lo(v_addr + kk * 2048, kKT * 128);
+          umma_ts<kKindF16>(tmem_base + 256 + t * 128, tmem_p + kk * 8, desc64(b_lo, hi), p.idesc_pv, (j | kk) ? 1u : 0u);
+        }
+        tc_commit<1>(&pv_done[t]);
+      };
+      bool ok = mbar_wait(q_full, 0, p.status, kStatusTimeoutMma + 8);
+      if (ok && jmax > 0) {
+        ok = mbar_wait(&k_full[0], 0, p.status, kStatusTimeoutMma + 0);
+        if (ok) {
+          tc_fence_after();
+          if (0 < nbt[0]) issue_s(0, 0);
+          if (0 < nbt[1]) issue_s(1, 0);
+          tc_commit<1>(&k_empty[0]);
+        }
+      }
+      int st = 0;          // ring stage of block j
+      uint32_t par = 0;
+      for (int j = 0; j < jmax && ok; ++j) {
+        const int nst = (st + 1 == NS) ? 0 : st + 1;
+        const uint32_t npar = (st + 1 == NS) ? (par ^ 1u) : par;
+        const bool more = j + 1 < jmax;
+        if (!mbar_wait(&v_full[st], par, p.status, kStatusTimeoutMma + 10 + st)) break;
+        if (j < nbt[0]) {
+          if (!mbar_wait(&p_full[0], (uint32_t)j & 1u, p.status, kStatusTimeoutMma + 20)) break;
+          tc_fence_after();
+          issue_pv(0, st, j);
+        }
+        if (more && !mbar_wait(&k_full[nst], npar, p.status, kStatusTimeoutMma + nst)) break;
+        if (more) tc_fence_after();
+        if (j + 1 < nbt[0]) issue_s(0, nst);      // S_A(j+1) overwrites S_A / P_A(j) after PV_A(j): issue order
+        if (j < nbt[1]) {
+          if (!mbar_wait(&p_full[1], (uint32_t)j & 1u, p.status, kStatusTimeoutMma + 21)) break;
+          tc_fence_after();
+          issue_pv(1, st, j);
+        }
+        tc_commit<1>(&v_empty[st]);
+        if (j + 1 < nbt[1]) issue_s(1, nst);
+        if (more) tc_commit<1>(&k_empty[nst]);
+        st = nst;
+        par = npar;
+      }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------ softmax / correction / epilogue of one tile ------------------------------
+    const int t = (warp - 4) >> 2;          // tile A or B
+    const int wq = warp & 3;
+    const int nb = nbt[t];
+    const int tq0 = q0 + t * kQT;
+    const int r = wq * 32 + lane;
+    const long long row = (long long)tq0 + r;
+    const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
+    const uint32_t tmem_s = tmem_base + lane_base + t * 128;
+    const uint32_t tmem_o = tmem_base + lane_base + 256 + t * 128;
+    float m_ref = -INFINITY, l = 0.0f;
+    bool ok = true;
+    for (int j = 0; j < nb && ok; ++j) {
+      if (!mbar_wait(&s_full[t], (uint32_t)j & 1u, p.status, kStatusTimeoutEpilogue + t)) { ok = false; break; }
+      tc_fence_after();
+      const int key0 = j * kKT;
+      const bool side_inputs = p.bias || p.mask;
+      const bool edge = (key0 + kKT > p.Sk) || (p.causal && key0 + kKT - 1 > tq0);
+      const int limit = min(p.Sk - key0, p.causal ? (int)min(row - key0 + 1, (long long)kKT) : kKT);
+      const long long side_off = ((long long)g * p.Sq + min(row, (long long)p.Sq - 1)) * p.Sk + key0;
+      // x(i): score of key key0 + i in the log2 domain after scale, bias and masks
+      auto fx = [&](uint32_t raw, int i) -> float {
+        float x = __uint_as_float(raw) * p.scale_log2;
+        if (side_inputs && i < p.Sk - key0) {
+          if (p.bias) x = fmaf(load_elem(p.bias, side_off + i, p.is_bf16), kLog2e, x);
+          if (p.mask && p.mask[side_off + i] == 0) x = p.mask_fill * kLog2e;
+        }
+        return x;
+      };
+      // pass 1: row maximum over both halves
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+      float m_use = 0.0f;
+      // exponent argument x(i) - m; without a bias it is the same single fused multiply-add as on the fast path, so
+      // that a mask tensor and the analytic causal mask give bit-identical results
+      auto fe = [&](uint32_t raw, int i) -> float {
+        float a = p.bias ? fx(raw, i) - m_use : fmaf(__uint_as_float(raw), p.scale_log2, -m_use);
+        if (p.mask && i < p.Sk - key0 && p.mask[side_off + i] == 0) a = p.mask_fill * kLog2e - m_use;
+        return a;
+      };
+#pragma unroll 1
+      for (int h = 0; h < 2; ++h) {
+        uint32_t v[64];
+        tmem_ld64(tmem_s + h * 64, v);
+        tmem_ld_wait();
+        if (!side_inputs && !edge) {
+#pragma unroll
+          for (int i = 0; i < 64; i += 4) {
+            mx0 = fmaxf(mx0, __uint_as_float(v[i])); mx1 = fmaxf(mx1, __uint_as_float(v[i + 1]));
+            mx2 = fmaxf(mx2, __uint_as_float(v[i + 2])); mx3 = fmaxf(mx3, __uint_as_float(v[i + 3]));
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 64; ++i) {
+            const float x = (h * 64 + i < limit) ? fx(v[i], h * 64 + i) : -INFINITY;
+            mx0 = fmaxf(mx0, x);
+          }
+        }
+      }
+      float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+      if (!side_inputs && !edge) mx *= p.scale_log2;   // the scale is positive: max commutes with it
+      float alpha = 1.0f;
+      if (mx > m_ref + 8.0f || (m_ref == -INFINITY && mx > -INFINITY)) {
+        alpha = ex2(m_ref - mx);
+        m_ref = mx;
+      }
+      m_use = (m_ref == -INFINITY) ? 0.0f : m_ref;
+      // pass 2: exponentials, row sum, P over the first 64 columns of the score buffer
+      float l0 = 0.0f, l1 = 0.0f, l2 = 0.0f, l3 = 0.0f;
+#pragma unroll 1
+      for (int h = 0; h < 2; ++h) {
+        uint32_t v[64];
+        tmem_ld64(tmem_s + h * 64, v);
+        tmem_ld_wait();
+        uint32_t w[32];
+        if (!side_inputs && !edge) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float p0 = ex2(fmaf(__uint_as_float(v[2 * i]), p.scale_log2, -m_use));
+            const float p1 = ex2(fmaf(__uint_as_float(v[2 * i + 1]), p.scale_log2, -m_use));
+            const float p2 = ex2(fmaf(__uint_as_float(v[2 * i + 2]), p.scale_log2, -m_use));
+            const float p3 = ex2(fmaf(__uint_as_float(v[2 * i + 3]), p.scale_log2, -m_use));
+            l0 += p0; l1 += p1; l2 += p2; l3 += p3;
+            w[i] = pack2(p0, p1, p.is_bf16);
+            w[i + 1] = pack2(p2, p3, p.is_bf16);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int c0 = h * 64 + 2 * i;
+            const float p0 = (c0 < limit) ? ex2(fe(v[2 * i], c0)) : 0.0f;
+            const float p1 = (c0 + 1 < limit) ? ex2(fe(v[2 * i + 1], c0 + 1)) : 0.0f;
+            if (i & 1) { l2 += p0; l3 += p1; } else { l0 += p0; l1 += p1; }   // same summation order as the fast path
+            w[i] = pack2(p0, p1, p.is_bf16);
+          }
+        }
+        // half h of P -> columns 32h .. 32h+31 (both halves of S are in registers or consumed by now only for
+        // h = 1; for h = 0 the columns 0..31 written here belong to the half already read)
+        tmem_st32(tmem_s + h * 32, w);
+      }
+      l = l * alpha + ((l0 + l1) + (l2 + l3));
+      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
+        if (!mbar_wait(&pv_done[t], (uint32_t)(j - 1) & 1u, p.status, kStatusTimeoutEpilogue + 4 + t)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll 1
+        for (int c = 0; c < p.Dv / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld32(tmem_o + c * 32, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st32(tmem_o + c * 32, o);
+        }
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[t]);
+    }
+    if (ok && nb > 0 && mbar_wait(&pv_done[t], (uint32_t)(nb - 1) & 1u, p.status, kStatusTimeoutEpilogue + 6 + t)) {
+      tc_fence_after();
+      const float inv = (l > 0.0f) ? 1.0f / l : 0.0f;
+      uint8_t* stg = smem + Att2Smem::kQ + t * Att2Smem::kQBytes + wq * (2 * 32 * 128);
+#pragma unroll 1
+      for (int c = 0; c < p.Dv / 32; ++c) {
+        uint32_t o[32];
+        tmem_ld32(tmem_o + c * 32, o);
+        tmem_ld_wait();
+        uint32_t w[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          w[i] = pack2(__uint_as_float(o[2 * i]) * inv, __uint_as_float(o[2 * i + 1]) * inv, p.is_bf16);
+        uint8_t* rowp = stg + (c >> 1) * (32 * 128) + lane * 128;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int piece = (c & 1) * 4 + i;
+          *reinterpret_cast<uint4*>(rowp + ((piece ^ (lane & 7)) << 4)) = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+        }
+      }
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0 && tq0 + wq * 32 < p.Sq) {
+        for (int c = 0; c < p.Dv / 64; ++c) tma_store_3d(&maps.o, stg + c * (32 * 128), c * 64, tq0 + wq * 32, g);
+        bulk_commit();
+        bulk_wait<0>();
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc<1>(tmem_base, 512);
+  }
+}
+
 }  // namespace
 }  // namespace rb
 
@@ -424,8 +761,15 @@ extern "C" RbStatus rbAttention(const RbAttentionProblem* p, const void* q, cons
   kp.status = dev->status_word;
   const long long ctas = (long long)p->g * kp.q_tiles;
   if (ctas > 0x7fffffffLL) return fail(RB_UNSUPPORTED, "too many query tiles");
-  RB_CUDA_TRY(cudaFuncSetAttribute(attention_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AttSmem::kTotal));
-  attention_fwd_kernel<<<(unsigned)ctas, kAttThreads, AttSmem::kTotal, stream>>>(maps, kp);
+  if (p->seq_q > kQT && p->scale >= 0.0f) {
+    // two query tiles per CTA (the fast path folds the scale into the row maximum, which needs scale >= 0)
+    const long long ctas2 = (long long)p->g * ((kp.q_tiles + 1) / 2);
+    RB_CUDA_TRY(cudaFuncSetAttribute(attention_fwd2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Att2Smem::kTotal));
+    attention_fwd2_kernel<<<(unsigned)ctas2, kAtt2Threads, Att2Smem::kTotal, stream>>>(maps, kp);
+  } else {
+    RB_CUDA_TRY(cudaFuncSetAttribute(attention_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AttSmem::kTotal));
+    attention_fwd_kernel<<<(unsigned)ctas, kAttThreads, AttSmem::kTotal, stream>>>(maps, kp);
+  }
   RB_CUDA_TRY(cudaGetLastError());
   count_launch();
   return RB_SUCCESS;
