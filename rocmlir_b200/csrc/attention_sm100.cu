@@ -53,6 +53,7 @@ struct AttParams {
   float mask_fill;
   uint32_t idesc_s, idesc_pv;
   uint32_t* status;
+  unsigned long long* trace;   // optional [CTAs][16] cycle counters (two-tile kernel), see rbSetTraceBuffer
 };
 
 struct AttSmem {
@@ -475,27 +476,47 @@ __global__ void __launch_bounds__(kAtt2Threads, 1) attention_fwd2_kernel(const _
     if (lane == 0) {
       const uint32_t hi = smem_desc_hi(1024);
       const int ksteps = p.D / 16;
+      // The issuing thread must spend well under 64 cycles per 128x128x16 MMA, so every descriptor is a base
+      // computed once plus a compile-time offset (loops fully unrolled, unused steps predicated off).
+      const uint32_t q_lo0 = smem_desc_lo(smem_u32(smem + Att2Smem::kQ), 16);
+      const uint32_t k_lo0 = p.trans_k ? smem_desc_lo(smem_u32(smem + Att2Smem::kK), 16)
+                                       : smem_desc_lo(smem_u32(smem + Att2Smem::kK), (uint32_t)p.D * 128);
+      const uint32_t v_lo0 = smem_desc_lo(smem_u32(smem + Att2Smem::kV), kKT * 128);
+      const uint32_t idesc_s = p.idesc_s, idesc_pv = p.idesc_pv;
+      const bool trans_k = p.trans_k != 0;
       auto issue_s = [&](int t, int stage) {
-        const uint32_t q_addr = smem_u32(smem + Att2Smem::kQ + t * Att2Smem::kQBytes);
-        const uint32_t k_addr = smem_u32(smem + Att2Smem::kK + stage * Att2Smem::kKBytes);
-        for (int kk = 0; kk < ksteps; ++kk) {
-          const uint32_t a_lo = smem_desc_lo(q_addr + (kk >> 2) * (kQT * 128) + (kk & 3) * 32, 16);
-          const uint32_t b_lo = p.trans_k ? smem_desc_lo(k_addr + (kk >> 2) * (kKT * 128) + (kk & 3) * 32, 16)
-                                          : smem_desc_lo(k_addr + kk * 2048, (uint32_t)p.D * 128);
-          umma_ss<kKindF16, 1>(tmem_base + t * 128, desc64(a_lo, hi), desc64(b_lo, hi), p.idesc_s, kk ? 1u : 0u);
+        const uint32_t a_lo = q_lo0 + t * (Att2Smem::kQBytes >> 4);
+        const uint32_t b_lo = k_lo0 + stage * (Att2Smem::kKBytes >> 4);
+        const uint32_t d = tmem_base + t * 128;
+        if (trans_k) {
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk)
+            if (kk < ksteps)
+              umma_ss<kKindF16, 1>(d, desc64(a_lo + (((kk >> 2) * (kQT * 128) + (kk & 3) * 32) >> 4), hi),
+                                   desc64(b_lo + (((kk >> 2) * (kKT * 128) + (kk & 3) * 32) >> 4), hi), idesc_s, kk ? 1u : 0u);
+        } else {
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk)
+            if (kk < ksteps)
+              umma_ss<kKindF16, 1>(d, desc64(a_lo + (((kk >> 2) * (kQT * 128) + (kk & 3) * 32) >> 4), hi),
+                                   desc64(b_lo + ((kk * 2048) >> 4), hi), idesc_s, kk ? 1u : 0u);
         }
         tc_commit<1>(&s_full[t]);
       };
       auto issue_pv = [&](int t, int stage, int j) {
-        const uint32_t v_addr = smem_u32(smem + Att2Smem::kV + stage * Att2Smem::kVBytes);
+        const uint32_t b_lo = v_lo0 + stage * (Att2Smem::kVBytes >> 4);
         const uint32_t tmem_p = tmem_base + t * 128;
-        for (int kk = 0; kk < kKT / 16; ++kk) {
-          const uint32_t b_lo = smem_desc_lo(v_addr + kk * 2048, kKT * 128);
-          umma_ts<kKindF16>(tmem_base + 256 + t * 128, tmem_p + kk * 8, desc64(b_lo, hi), p.idesc_pv, (j | kk) ? 1u : 0u);
-        }
+        const uint32_t d = tmem_base + 256 + t * 128;
+        const uint32_t acc0 = j ? 1u : 0u;
+#pragma unroll
+        for (int kk = 0; kk < kKT / 16; ++kk)
+          umma_ts<kKindF16>(d, tmem_p + kk * 8, desc64(b_lo + ((kk * 2048) >> 4), hi), idesc_pv, kk ? 1u : acc0);
         tc_commit<1>(&pv_done[t]);
       };
+      long long w_p[2] = {0, 0}, w_v = 0, w_k = 0;
+      const long long t_begin = p.trace ? clock64() : 0;
       bool ok = mbar_wait(q_full, 0, p.status, kStatusTimeoutMma + 8);
+      const long long t_q = p.trace ? clock64() : 0;
       if (ok && jmax > 0) {
         ok = mbar_wait(&k_full[0], 0, p.status, kStatusTimeoutMma + 0);
         if (ok) {
@@ -511,17 +532,24 @@ __global__ void __launch_bounds__(kAtt2Threads, 1) attention_fwd2_kernel(const _
         const int nst = (st + 1 == NS) ? 0 : st + 1;
         const uint32_t npar = (st + 1 == NS) ? (par ^ 1u) : par;
         const bool more = j + 1 < jmax;
+        long long tc = p.trace ? clock64() : 0;
         if (!mbar_wait(&v_full[st], par, p.status, kStatusTimeoutMma + 10 + st)) break;
+        if (p.trace) { const long long n = clock64(); w_v += n - tc; tc = n; }
         if (j < nbt[0]) {
           if (!mbar_wait(&p_full[0], (uint32_t)j & 1u, p.status, kStatusTimeoutMma + 20)) break;
+          if (p.trace) { const long long n = clock64(); w_p[0] += n - tc; tc = n; }
           tc_fence_after();
           issue_pv(0, st, j);
         }
+        if (p.trace) tc = clock64();
         if (more && !mbar_wait(&k_full[nst], npar, p.status, kStatusTimeoutMma + nst)) break;
+        if (p.trace) { const long long n = clock64(); w_k += n - tc; tc = n; }
         if (more) tc_fence_after();
         if (j + 1 < nbt[0]) issue_s(0, nst);      // S_A(j+1) overwrites S_A / P_A(j) after PV_A(j): issue order
         if (j < nbt[1]) {
+          if (p.trace) tc = clock64();
           if (!mbar_wait(&p_full[1], (uint32_t)j & 1u, p.status, kStatusTimeoutMma + 21)) break;
+          if (p.trace) w_p[1] += clock64() - tc;
           tc_fence_after();
           issue_pv(1, st, j);
         }
@@ -530,6 +558,16 @@ __global__ void __launch_bounds__(kAtt2Threads, 1) attention_fwd2_kernel(const _
         if (more) tc_commit<1>(&k_empty[nst]);
         st = nst;
         par = npar;
+      }
+      if (p.trace) {
+        unsigned long long* tr = p.trace + (size_t)blockIdx.x * 16;
+        tr[0] = (unsigned long long)(clock64() - t_begin);   // MMA thread: total
+        tr[1] = (unsigned long long)(t_q - t_begin);         //   waiting for Q
+        tr[2] = (unsigned long long)w_p[0];                  //   waiting for P of tile A
+        tr[3] = (unsigned long long)w_p[1];                  //   waiting for P of tile B
+        tr[4] = (unsigned long long)w_v;                     //   waiting for V tiles
+        tr[5] = (unsigned long long)w_k;                     //   waiting for K tiles
+        tr[6] = (unsigned long long)jmax;
       }
     }
   } else if (warp >= 4) {
@@ -545,8 +583,12 @@ __global__ void __launch_bounds__(kAtt2Threads, 1) attention_fwd2_kernel(const _
     const uint32_t tmem_o = tmem_base + lane_base + 256 + t * 128;
     float m_ref = -INFINITY, l = 0.0f;
     bool ok = true;
+    long long sm_wait = 0, sm_busy = 0;
     for (int j = 0; j < nb && ok; ++j) {
+      const long long ts0 = p.trace ? clock64() : 0;
       if (!mbar_wait(&s_full[t], (uint32_t)j & 1u, p.status, kStatusTimeoutEpilogue + t)) { ok = false; break; }
+      const long long ts1 = p.trace ? clock64() : 0;
+      sm_wait += ts1 - ts0;
       tc_fence_after();
       const int key0 = j * kKT;
       const bool side_inputs = p.bias || p.mask;
@@ -583,6 +625,16 @@ __global__ void __launch_bounds__(kAtt2Threads, 1) attention_fwd2_kernel(const _
             mx0 = fmaxf(mx0, __uint_as_float(v[i])); mx1 = fmaxf(mx1, __uint_as_float(v[i + 1]));
             mx2 = fmaxf(mx2, __uint_as_float(v[i + 2])); mx3 = fmaxf(mx3, __uint_as_float(v[i + 3]));
           }
+        } else if (!side_inputs) {
+          // key tail / diagonal block: keys at or past `limit` are dropped with a select
+#pragma unroll
+          for (int i = 0; i < 64; i += 4) {
+            const int c0 = h * 64 + i;
+            mx0 = fmaxf(mx0, (c0 < limit) ? __uint_as_float(v[i]) : -INFINITY);
+            mx1 = fmaxf(mx1, (c0 + 1 < limit) ? __uint_as_float(v[i + 1]) : -INFINITY);
+            mx2 = fmaxf(mx2, (c0 + 2 < limit) ? __uint_as_float(v[i + 2]) : -INFINITY);
+            mx3 = fmaxf(mx3, (c0 + 3 < limit) ? __uint_as_float(v[i + 3]) : -INFINITY);
+          }
         } else {
 #pragma unroll
           for (int i = 0; i < 64; ++i) {
@@ -592,7 +644,7 @@ __global__ void __launch_bounds__(kAtt2Threads, 1) attention_fwd2_kernel(const _
         }
       }
       float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-      if (!side_inputs && !edge) mx *= p.scale_log2;   // the scale is positive: max commutes with it
+      if (!side_inputs) mx *= p.scale_log2;   // the scale is positive: max commutes with it (-inf stays -inf)
       float alpha = 1.0f;
       if (mx > m_ref + 8.0f || (m_ref == -INFINITY && mx > -INFINITY)) {
         alpha = ex2(m_ref - mx);
@@ -614,6 +666,18 @@ __global__ void __launch_bounds__(kAtt2Threads, 1) attention_fwd2_kernel(const _
             const float p1 = ex2(fmaf(__uint_as_float(v[2 * i + 1]), p.scale_log2, -m_use));
             const float p2 = ex2(fmaf(__uint_as_float(v[2 * i + 2]), p.scale_log2, -m_use));
             const float p3 = ex2(fmaf(__uint_as_float(v[2 * i + 3]), p.scale_log2, -m_use));
+            l0 += p0; l1 += p1; l2 += p2; l3 += p3;
+            w[i] = pack2(p0, p1, p.is_bf16);
+            w[i + 1] = pack2(p2, p3, p.is_bf16);
+          }
+        } else if (!side_inputs) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const int c0 = h * 64 + 2 * i;
+            const float p0 = (c0 < limit) ? ex2(fmaf(__uint_as_float(v[2 * i]), p.scale_log2, -m_use)) : 0.0f;
+            const float p1 = (c0 + 1 < limit) ? ex2(fmaf(__uint_as_float(v[2 * i + 1]), p.scale_log2, -m_use)) : 0.0f;
+            const float p2 = (c0 + 2 < limit) ? ex2(fmaf(__uint_as_float(v[2 * i + 2]), p.scale_log2, -m_use)) : 0.0f;
+            const float p3 = (c0 + 3 < limit) ? ex2(fmaf(__uint_as_float(v[2 * i + 3]), p.scale_log2, -m_use)) : 0.0f;
             l0 += p0; l1 += p1; l2 += p2; l3 += p3;
             w[i] = pack2(p0, p1, p.is_bf16);
             w[i + 1] = pack2(p2, p3, p.is_bf16);
@@ -650,6 +714,11 @@ __global__ void __launch_bounds__(kAtt2Threads, 1) attention_fwd2_kernel(const _
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[t]);
+      if (p.trace) sm_busy += clock64() - ts1;
+    }
+    if (p.trace && wq == 0 && lane == 0) {
+      p.trace[(size_t)blockIdx.x * 16 + 8 + 2 * t] = (unsigned long long)sm_wait;   // softmax group t: waiting for S
+      p.trace[(size_t)blockIdx.x * 16 + 9 + 2 * t] = (unsigned long long)sm_busy;   //   busy (incl. rescale)
     }
     if (ok && nb > 0 && mbar_wait(&pv_done[t], (uint32_t)(nb - 1) & 1u, p.status, kStatusTimeoutEpilogue + 6 + t)) {
       tc_fence_after();
@@ -759,6 +828,7 @@ extern "C" RbStatus rbAttention(const RbAttentionProblem* p, const void* q, cons
   kp.idesc_s = make_idesc(1, fmt, fmt, 0, p->trans_k ? 0u : 1u, kQT, kKT);
   kp.idesc_pv = make_idesc(1, fmt, fmt, 0, 1u, kQT, (uint32_t)p->head_v);
   kp.status = dev->status_word;
+  kp.trace = trace_buffer((size_t)p->g * ((kp.q_tiles + 1) / 2) * 16);
   const long long ctas = (long long)p->g * kp.q_tiles;
   if (ctas > 0x7fffffffLL) return fail(RB_UNSUPPORTED, "too many query tiles");
   if (p->seq_q > kQT && p->scale >= 0.0f) {

@@ -12,8 +12,6 @@ namespace rb {
 namespace {
 
 thread_local int t_variant = 0;
-thread_local unsigned long long* t_trace = nullptr;
-thread_local size_t t_trace_len = 0;
 
 // ---- auxiliary kernels ---------------------------------------------------------------------------
 // Copies `rows` rows of `row_bytes` bytes into rows of `pitch_bytes` bytes, zero-filling the pad.
@@ -274,7 +272,6 @@ Workspace plan_workspace(const RbGemmProblem* p, const OperandPlan& oa, const Op
 using namespace rb;
 
 extern "C" void rbSetGemmVariant(int variant) { t_variant = variant; }
-extern "C" void rbSetTraceBuffer(unsigned long long* device_buf, size_t n_u64) { t_trace = device_buf; t_trace_len = n_u64; }
 
 extern "C" size_t rbGemmWorkspaceSize(const RbGemmProblem* p) {
   if (check_problem(p) != RB_SUCCESS) return 0;
@@ -554,7 +551,7 @@ RbStatus rb::gemm_run(const RbGemmProblem* p, const RbEpilogue* epi, const void*
   } else {
     lc.gridDim = dim3((unsigned)std::min<long long>(num_items, dev->sm_count), 1, 1);
   }
-  kp.trace = (t_trace && t_trace_len >= (size_t)lc.gridDim.x * 16) ? t_trace : nullptr;
+  kp.trace = trace_buffer((size_t)lc.gridDim.x * 16);
   RB_CUDA_TRY(cudaLaunchKernelEx(&lc, kern, maps, kp));
   count_launch();
   if (splits > 1) {

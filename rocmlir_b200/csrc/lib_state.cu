@@ -7,6 +7,8 @@ namespace rb {
 
 namespace {
 thread_local std::string t_last_error;
+thread_local unsigned long long* t_trace = nullptr;
+thread_local size_t t_trace_len = 0;
 std::atomic<uint64_t> g_launches{0};
 __device__ uint32_t g_status_word;  // written by kernels whose bounded waits run out
 
@@ -31,6 +33,8 @@ RbStatus fail(RbStatus st, const std::string& msg) {
   t_last_error = msg;
   return st;
 }
+
+unsigned long long* trace_buffer(size_t need_u64) { return (t_trace && t_trace_len >= need_u64) ? t_trace : nullptr; }
 
 void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
 
@@ -145,6 +149,11 @@ RbStatus rbReadKernelStatus(uint32_t* status_out, int clear) {
   RB_CUDA_TRY(cudaMemcpy(status_out, d->status_word, sizeof(uint32_t), cudaMemcpyDeviceToHost));
   if (clear) RB_CUDA_TRY(cudaMemset(d->status_word, 0, sizeof(uint32_t)));
   return RB_SUCCESS;
+}
+
+void rbSetTraceBuffer(unsigned long long* device_buf, size_t n_u64) {
+  rb::t_trace = device_buf;
+  rb::t_trace_len = n_u64;
 }
 
 uint64_t rbLaunchCount(void) { return rb::g_launches.load(std::memory_order_relaxed); }

@@ -50,6 +50,9 @@ struct ConvAOperand {
 RbStatus gemm_run(const RbGemmProblem* p, const RbEpilogue* epi, const void* a, const void* b, void* c, void* workspace,
                   size_t workspace_bytes, void* stream, const ConvAOperand* conva);
 
+// Device trace buffer set with rbSetTraceBuffer for the calling thread (nullptr when `need` words do not fit).
+unsigned long long* trace_buffer(size_t need_u64);
+
 inline size_t dtype_bytes(int t) {
   switch (t) {
     case RB_F32: case RB_I32: return 4;
