@@ -332,6 +332,7 @@ def main():
     import torch
     import torch.distributed as dist
     from rocmlir_b200 import _lib as L
+    from rocmlir_b200 import sharding
     from rocmlir_b200.gemm import gemm, gemm_host
 
     if not torch.cuda.is_available():
@@ -396,10 +397,9 @@ def main():
         barrier()
         e2e_ms_total = e0.elapsed_time(e1)
 
-    t = torch.tensor([ms_total, e2e_ms_total], dtype=torch.float64, device=dev)
-    if distributed:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_total, e2e_ms_total = t.tolist()
+    # a multi-rank job takes as long as its slowest rank
+    ms_total = sharding.job_time_ms(ms_total, device=dev)
+    e2e_ms_total = sharding.job_time_ms(e2e_ms_total, device=dev)
 
     if rank == 0:
         peaks = measured_peaks()
