@@ -164,6 +164,11 @@ RB_EXPORT size_t rbConvWorkspaceSize(const RbConvProblem *p);
  * miirGetKernelCount, Miir.h:54-58); -1 for an invalid problem. */
 RB_EXPORT int rbConvKernelCount(const RbConvProblem *p);
 
+/* The GEMM a convolution is computed as (the reference's GemmSize::fromConvolution and the backward variants,
+ * mlir/lib/Dialect/Rock/IR/RockDialect.cpp:509-533,671-749): forward M = N*Ho*Wo, N = K, K = Y*X*C; backward
+ * data M = N*H*W, N = C, K = Y*X*K; backward weight M = K, N = Y*X*C, K = N*Ho*Wo (per group). */
+RB_EXPORT RbStatus rbConvGetGemmProblem(const RbConvProblem *p, RbGemmProblem *out);
+
 RB_EXPORT RbStatus rbConv(const RbConvProblem *p, void *filter, void *input, void *output, void *workspace,
                           size_t workspace_bytes, void *stream);
 
@@ -203,6 +208,24 @@ RB_EXPORT RbStatus rbGemmGemm(int32_t g, int32_t m, int32_t k1, int32_t n1, int3
  * thread's library state. 0 = automatic (measured table). Mirrors the role of rocMLIR's perf_config
  * (mlir/include/mlir/Dialect/Rock/Tuning/GridwiseGemmParams.h:138-194). */
 RB_EXPORT void rbSetGemmVariant(int variant);
+RB_EXPORT int rbGetGemmVariant(void);
+
+/* The tile configuration the library would launch for `p` under the calling thread's variant word (on a
+ * 148-SM B200): the information rocMLIR attaches to a lowered kernel as block_size / grid_size attributes
+ * (mlir/lib/Dialect/Rock/Transforms/AffixTuningParameters.cpp:69-87) plus what a 1-D launch cannot carry on
+ * this hardware (dynamic shared memory, CTAs per cluster). `variant` is the explicit variant word that
+ * reproduces the configuration. */
+typedef struct RbGemmConfigInfo {
+  int32_t tile_m, tile_n, tile_k; /* output tile of one CTA group; K elements per pipeline stage */
+  int32_t ctas;                   /* CTAs per cluster (1, or 2 = cta_group::2 pair) */
+  int32_t stages;                 /* depth of the shared-memory ring */
+  int32_t splits;                 /* K ranges (1 = no split) */
+  int32_t stream_k;               /* 1 when the stream-K tail is active */
+  uint32_t grid, block;           /* 1-D launch: CTAs and threads per CTA */
+  uint32_t dynamic_smem;          /* bytes */
+  uint32_t variant;
+} RbGemmConfigInfo;
+RB_EXPORT RbStatus rbGemmGetConfig(const RbGemmProblem *p, RbGemmConfigInfo *out);
 
 /* Tracing: when a device buffer of at least 16 * (CTAs of the launch) 64-bit words is set, the GEMM kernel
  * writes per-CTA SM-cycle counters into it: [1] producer waited for a free stage, [2] MMA thread waited for

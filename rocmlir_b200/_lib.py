@@ -49,6 +49,16 @@ class RbAttentionProblem(C.Structure):
                 ("causal", C.c_int32), ("mask_fill", C.c_float), ("bias", C.c_void_p), ("mask", C.c_void_p)]
 
 
+class RbGemmConfigInfo(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("tile_m", "tile_n", "tile_k", "ctas", "stages", "splits", "stream_k")] + \
+               [(n, C.c_uint32) for n in ("grid", "block", "dynamic_smem", "variant")]
+
+
+class _Handle(C.Structure):
+    """The one-pointer opaque structs of the tuning API (RbProblem, RbTuningSpace, RbTuningParam, RbTuningTable)."""
+    _fields_ = [("ptr", C.c_void_p)]
+
+
 class RbError(RuntimeError):
     def __init__(self, status: int, msg: str):
         super().__init__(f"{STATUS_NAMES[status] if 0 <= status < len(STATUS_NAMES) else status}: {msg}")
@@ -92,6 +102,80 @@ def lib() -> C.CDLL:
         l.rbGemmGemm.argtypes = [C.c_int32] * 6 + [C.c_void_p] * 5 + [C.c_size_t, C.c_void_p]
         l.rbSetGemmVariant.restype = None
         l.rbSetGemmVariant.argtypes = [C.c_int]
+        l.rbGetGemmVariant.restype = C.c_int
+        l.rbGetGemmVariant.argtypes = []
+        l.rbGemmGetConfig.restype = C.c_int
+        l.rbGemmGetConfig.argtypes = [C.POINTER(RbGemmProblem), C.POINTER(RbGemmConfigInfo)]
+        l.rbConvGetGemmProblem.restype = C.c_int
+        l.rbConvGetGemmProblem.argtypes = [C.POINTER(RbConvProblem), C.POINTER(RbGemmProblem)]
+        # include/miir_b200.h
+        l.miirCreateHandle.restype = C.c_void_p
+        l.miirCreateHandle.argtypes = [C.c_char_p]
+        for name in ("miirGetKernelCount", "miirGetWorkspaceSize", "miirLowerTuningParams", "miirLowerBin",
+                     "miirDestroyHandle"):
+            getattr(l, name).restype = C.c_int
+            getattr(l, name).argtypes = [C.c_void_p]
+        l.miirBufferGet.restype = C.c_int
+        l.miirBufferGet.argtypes = [C.c_void_p, C.c_char_p, C.POINTER(C.c_size_t)]
+        l.miirGetExecutionDims.restype = C.c_int
+        l.miirGetExecutionDims.argtypes = [C.c_void_p, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]
+        l.miirLaunch.restype = C.c_int
+        l.miirLaunch.argtypes = [C.c_void_p] * 6 + [C.c_size_t, C.c_void_p]
+        l.miirLaunchFromBuffer.restype = C.c_int
+        l.miirLaunchFromBuffer.argtypes = [C.c_char_p, C.c_size_t] + [C.c_void_p] * 5 + [C.c_size_t, C.c_void_p]
+        # include/rocmlir_b200_tuning.h
+        l.rbProblemCreate.restype = _Handle
+        l.rbProblemCreate.argtypes = [C.c_char_p]
+        l.rbProblemFromGemm.restype = _Handle
+        l.rbProblemFromGemm.argtypes = [C.POINTER(RbGemmProblem)]
+        l.rbProblemFromConv.restype = _Handle
+        l.rbProblemFromConv.argtypes = [C.POINTER(RbConvProblem)]
+        l.rbProblemFromAttention.restype = _Handle
+        l.rbProblemFromAttention.argtypes = [C.POINTER(RbAttentionProblem)]
+        l.rbProblemDestroy.restype = None
+        l.rbProblemDestroy.argtypes = [_Handle]
+        l.rbProblemGetPerfConfig.restype = C.c_size_t
+        l.rbProblemGetPerfConfig.argtypes = [_Handle, C.c_char_p, C.c_size_t]
+        l.rbProblemGetVariant.restype = C.c_uint32
+        l.rbProblemGetVariant.argtypes = [_Handle]
+        l.rbTuningSpaceCreate.restype = _Handle
+        l.rbTuningSpaceCreate.argtypes = [_Handle, C.c_int]
+        l.rbTuningGetNumParams.restype = C.c_uint
+        l.rbTuningGetNumParams.argtypes = [_Handle]
+        l.rbTuningParamCreate.restype = _Handle
+        l.rbTuningParamCreate.argtypes = []
+        l.rbTuningParamDestroy.restype = None
+        l.rbTuningParamDestroy.argtypes = [_Handle]
+        l.rbTuningSpaceDestroy.restype = None
+        l.rbTuningSpaceDestroy.argtypes = [_Handle]
+        l.rbTuningParamGet.restype = C.c_bool
+        l.rbTuningParamGet.argtypes = [_Handle, C.c_uint, _Handle]
+        l.rbTuningParamGetQuick.restype = C.c_bool
+        l.rbTuningParamGetQuick.argtypes = [_Handle, C.c_uint, _Handle]
+        l.rbTuningParamToString.restype = C.c_size_t
+        l.rbTuningParamToString.argtypes = [_Handle, C.c_char_p, C.c_size_t]
+        l.rbTuningSetParam.restype = C.c_bool
+        l.rbTuningSetParam.argtypes = [_Handle, _Handle]
+        l.rbTuningSetFromStr.restype = C.c_bool
+        l.rbTuningSetFromStr.argtypes = [_Handle, C.c_char_p, C.c_size_t]
+        l.rbTuningTableCreate.restype = _Handle
+        l.rbTuningTableCreate.argtypes = []
+        l.rbTuningTableDestroy.restype = None
+        l.rbTuningTableDestroy.argtypes = [_Handle]
+        l.rbTuningUpdateTable.restype = C.c_bool
+        l.rbTuningUpdateTable.argtypes = [_Handle, C.c_char_p, C.c_size_t, C.c_char_p, C.c_size_t, C.c_float]
+        l.rbTuningSetFromTable.restype = C.c_bool
+        l.rbTuningSetFromTable.argtypes = [_Handle, _Handle]
+        l.rbTuningGetKey.restype = C.c_size_t
+        l.rbTuningGetKey.argtypes = [_Handle, C.c_char_p, C.c_size_t]
+        l.rbIsSplitKFaster.restype = C.c_int
+        l.rbIsSplitKFaster.argtypes = [C.c_int64] * 5 + [C.c_int]
+        l.rbIsProblemFusible.restype = C.c_bool
+        l.rbIsProblemFusible.argtypes = [_Handle, C.c_char_p, C.c_size_t]
+        l.rbGetNumPrefillArgs.restype = C.c_size_t
+        l.rbGetNumPrefillArgs.argtypes = [_Handle]
+        l.rbGetNumAuxBuffers.restype = C.c_size_t
+        l.rbGetNumAuxBuffers.argtypes = [_Handle]
         l.rbSetTraceBuffer.restype = None
         l.rbSetTraceBuffer.argtypes = [C.c_void_p, C.c_size_t]
         l.rbReadKernelStatus.restype = C.c_int

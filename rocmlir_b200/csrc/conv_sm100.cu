@@ -268,6 +268,15 @@ extern "C" size_t rbConvWorkspaceSize(const RbConvProblem* p) {
   return pl.total;
 }
 
+extern "C" RbStatus rbConvGetGemmProblem(const RbConvProblem* p, RbGemmProblem* out) {
+  ConvPlan pl;
+  RbStatus st = make_plan(p, &pl);
+  if (st != RB_SUCCESS) return st;
+  if (!out) return fail(RB_INVALID_PARAM, "out is NULL");
+  *out = pl.gemm;
+  return RB_SUCCESS;
+}
+
 extern "C" int rbConvKernelCount(const RbConvProblem* p) {
   ConvPlan pl;
   if (make_plan(p, &pl) != RB_SUCCESS) return -1;

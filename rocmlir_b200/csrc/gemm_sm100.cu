@@ -272,6 +272,7 @@ Workspace plan_workspace(const RbGemmProblem* p, const OperandPlan& oa, const Op
 using namespace rb;
 
 extern "C" void rbSetGemmVariant(int variant) { t_variant = variant; }
+extern "C" int rbGetGemmVariant(void) { return t_variant; }
 
 extern "C" size_t rbGemmWorkspaceSize(const RbGemmProblem* p) {
   if (check_problem(p) != RB_SUCCESS) return 0;
@@ -280,6 +281,33 @@ extern "C" size_t rbGemmWorkspaceSize(const RbGemmProblem* p) {
   const OperandPlan oa = plan_operand(p->trans_a != 0, p->m, p->k, es, f32, split);
   const OperandPlan ob = plan_operand(p->trans_b == 0, p->n, p->k, es, f32, split);
   return plan_workspace(p, oa, ob, choose_config(p, t_variant)).total;
+}
+
+extern "C" RbStatus rbGemmGetConfig(const RbGemmProblem* p, RbGemmConfigInfo* out) {
+  RbStatus st = check_problem(p);
+  if (st != RB_SUCCESS) return st;
+  if (!out) return fail(RB_INVALID_PARAM, "out is NULL");
+  const GemmConfig c = choose_config(p, t_variant);
+  const int es = (int)dtype_bytes(p->ab_type);
+  const long long tiles = (long long)p->g * ((p->m + kBM * c.ctas - 1) / (kBM * c.ctas)) * ((p->n + c.bn - 1) / c.bn);
+  const long long items = tiles * c.splits;
+  const long long units = kAssumedSMs / c.ctas;
+  memset(out, 0, sizeof(*out));
+  out->tile_m = kBM * c.ctas;
+  out->tile_n = c.bn;
+  out->tile_k = kRowBytes / es;
+  out->ctas = c.ctas;
+  out->stages = c.stages;
+  out->splits = c.splits;
+  out->stream_k = c.sk_tiles > 0 ? 1 : 0;
+  out->grid = (uint32_t)(c.ctas * std::min<long long>(items, units));
+  out->block = kGemmThreads;
+  out->dynamic_smem = (uint32_t)(c.ctas == 2 ? GemmSmemLayout<2>::total(c.stages, c.bn, false)
+                                              : GemmSmemLayout<1>::total(c.stages, c.bn, false));
+  const int bn_code = c.bn == 64 ? 1 : c.bn == 128 ? 2 : 3;
+  out->variant = (uint32_t)c.ctas | ((uint32_t)c.stages << 4) | (c.plain_stores ? 1u << 8 : 0u) |
+                 (c.sk_tiles > 0 ? 1u << 9 : 0u) | ((uint32_t)bn_code << 12) | ((uint32_t)c.splits << 16);
+  return RB_SUCCESS;
 }
 
 extern "C" RbStatus rbGemm(const RbGemmProblem* p, const RbEpilogue* epi, const void* a, const void* b, void* c,

@@ -1,0 +1,456 @@
+// Tuning surface (include/rocmlir_b200_tuning.h): problem handles, tuning spaces over the GEMM kernel's tile
+// configurations, the best-entry table, problem keys in the reference's text format and the split-K likelihood
+// rule. Counterpart of mlir/lib/CAPI/Dialect/Rock.cpp:31-205 and mlir/lib/Dialect/Rock/Tuning/RockTuningImpl.cpp.
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <limits>
+#include <mutex>
+#include <map>
+#include <set>
+#include <shared_mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/rocmlir_b200_tuning.h"
+#include "lib_state.h"
+#include "problem.h"
+
+namespace rb {
+namespace {
+
+constexpr int kDefaultNumCU = 148;   // SMs of a B200: the "minNumCU" of this architecture (AmdArchDb.cpp:19-127)
+
+struct Param {
+  uint32_t variant = 0;
+  std::string text;   // perf_config string
+};
+
+struct Space {
+  std::vector<Param> params, quick;
+};
+
+struct Table {
+  std::shared_mutex lock;
+  std::map<std::string, std::pair<std::string, float>> best;
+};
+
+size_t copy_out(const std::string& s, char* buf, size_t len) {
+  if (buf && len) strncpy(buf, s.c_str(), len);   // strncpy semantics: no terminator when the buffer is too small
+  return s.size();
+}
+
+bool gemm_of(const ProblemDesc& d, RbGemmProblem* gp) {
+  if (d.kind == kGemm) {
+    *gp = d.gemm;
+    return true;
+  }
+  if (d.kind == kConv) return rbConvGetGemmProblem(&d.conv, gp) == RB_SUCCESS;
+  return false;
+}
+
+// Is `variant` honoured as asked for this GEMM (the library silently adjusts requests it cannot satisfy)?
+bool variant_valid(const RbGemmProblem& gp, uint32_t variant, RbGemmConfigInfo* info) {
+  const int saved = rbGetGemmVariant();
+  rbSetGemmVariant((int)variant);
+  const RbStatus st = rbGemmGetConfig(&gp, info);
+  rbSetGemmVariant(saved);
+  if (st != RB_SUCCESS) return false;
+  const int want_ctas = (variant & 0xF) == 1 ? 1 : 2;
+  const int bn_code = (variant >> 12) & 0xF;
+  const int want_bn = bn_code == 1 ? 64 : bn_code == 2 ? 128 : 256;
+  const int want_stages = (variant >> 4) & 0xF;
+  const int want_splits = (variant >> 16) & 0xFF;
+  const int want_sk = (variant >> 9) & 1;
+  if (info->ctas != want_ctas || info->tile_n != want_bn) return false;
+  if (want_stages && info->stages != want_stages) return false;
+  if (want_splits && info->splits != want_splits) return false;
+  if (want_sk != info->stream_k) return false;
+  return true;
+}
+
+uint32_t make_variant(int ctas, int bn, int stages, int splits, int sk) {
+  const uint32_t bn_code = bn == 64 ? 1u : bn == 128 ? 2u : 3u;
+  return (uint32_t)ctas | ((uint32_t)stages << 4) | ((uint32_t)sk << 9) | (bn_code << 12) | ((uint32_t)splits << 16);
+}
+
+void add_param(std::vector<Param>* out, std::set<uint32_t>* seen, const RbGemmProblem& gp, uint32_t v) {
+  RbGemmConfigInfo info;
+  if (!variant_valid(gp, v, &info)) return;
+  if (!seen->insert(v).second) return;
+  Param p;
+  p.variant = v;
+  p.text = variant_to_perf_config(v);
+  out->push_back(p);
+}
+
+void build_space(const ProblemDesc& d, RbTuningParamSetKind kind, Space* sp) {
+  RbGemmProblem gp;
+  if (!gemm_of(d, &gp)) {
+    // attention has one kernel configuration
+    Param p;
+    p.variant = 0;
+    p.text = "v1:attention";
+    sp->params.push_back(p);
+    sp->quick.push_back(p);
+    return;
+  }
+  // the library's own choice first
+  const int saved = rbGetGemmVariant();
+  rbSetGemmVariant(0);
+  RbGemmConfigInfo own;
+  const bool have_own = rbGemmGetConfig(&gp, &own) == RB_SUCCESS;
+  rbSetGemmVariant(saved);
+  std::set<uint32_t> seen_q, seen;
+  if (have_own) {
+    const uint32_t v = make_variant(own.ctas, own.tile_n, 0, own.splits, own.stream_k);
+    add_param(&sp->quick, &seen_q, gp, v);
+    // nearest alternatives: the other CTA grouping, the neighbouring tile widths, one more / one fewer K range
+    add_param(&sp->quick, &seen_q, gp, make_variant(own.ctas == 2 ? 1 : 2, own.tile_n, 0, own.splits, 0));
+    if (own.tile_n > 64) add_param(&sp->quick, &seen_q, gp, make_variant(own.ctas, own.tile_n / 2, 0, own.splits, 0));
+    if (own.tile_n < 256) add_param(&sp->quick, &seen_q, gp, make_variant(own.ctas, own.tile_n * 2, 0, own.splits, 0));
+    if (own.splits > 1) add_param(&sp->quick, &seen_q, gp, make_variant(own.ctas, own.tile_n, 0, 1, 0));
+    add_param(&sp->quick, &seen_q, gp, make_variant(own.ctas, own.tile_n, 0, own.splits * 2, 0));
+  }
+  if (kind == RbTuningParamSetKindQuick) {
+    sp->params = sp->quick;
+    return;
+  }
+  static const int split_set[] = {1, 2, 3, 4, 6, 8, 12, 16, 24, 32, 48, 64};
+  for (int ctas = 1; ctas <= 2; ++ctas)
+    for (int bn : {64, 128, 256})
+      for (int splits : split_set)
+        for (int sk = 0; sk <= 1; ++sk) {
+          if (sk && splits != 1) continue;
+          // tiles that would be at least half empty are legal but never worth measuring
+          if ((ctas == 2 && gp.m <= 128) || (bn > 64 && bn / 2 >= gp.n)) continue;
+          if (kind == RbTuningParamSetKindExhaustive) {
+            for (int stages = 2; stages <= 8; ++stages) add_param(&sp->params, &seen, gp, make_variant(ctas, bn, stages, splits, sk));
+          } else {
+            add_param(&sp->params, &seen, gp, make_variant(ctas, bn, 0, splits, sk));
+          }
+        }
+}
+
+const char* bool_str(int v) { return v ? "true" : "false"; }
+
+const char* type_name(int t) {
+  switch (t) {
+    case RB_F32: return "f32";
+    case RB_F16: return "f16";
+    case RB_BF16: return "bf16";
+    case RB_I8: return "i8";
+    case RB_I32: return "i32";
+    case RB_F8E4M3: return "fp8";
+    default: return nullptr;
+  }
+}
+
+// RockTuningImpl.cpp:550-876
+bool problem_key(const ProblemDesc& d, std::string* out) {
+  const int num_cu = d.num_cu > 0 ? d.num_cu : kDefaultNumCU;
+  std::string s = (d.arch.empty() ? std::string("sm_100a") : d.arch) + "\t" + std::to_string(num_cu) + "\t";
+  if (d.kind == kAttention) {
+    const RbAttentionProblem& a = d.att;
+    const char* t = type_name(a.data_type);
+    if (!t) return false;
+    s += std::string("-t ") + t + " -transQ " + bool_str(a.trans_q) + " -transK " + bool_str(a.trans_k) + " -transV " +
+         bool_str(a.trans_v) + " -transO " + bool_str(a.trans_o) + " -g " + std::to_string(a.g) + " -seq_len_q " +
+         std::to_string(a.seq_q) + " -seq_len_k " + std::to_string(a.seq_k) + " -head_dim_qk " + std::to_string(a.head_qk) +
+         " -head_dim_v " + std::to_string(a.head_v);
+  } else if (d.kind == kGemm) {
+    const RbGemmProblem& g = d.gemm;
+    const char* t = type_name(g.ab_type);
+    const char* ot = type_name(g.c_type);
+    if (!t || !ot || g.ab_type == RB_I32) return false;
+    s += std::string("-t ") + (g.ab_type == RB_F8E4M3 ? "fp8_fp8" : t) + " -out_datatype " + ot + " -transA " +
+         bool_str(g.trans_a) + " -transB " + bool_str(g.trans_b) + " -g " + std::to_string(g.g) + " -m " +
+         std::to_string(g.m) + " -n " + std::to_string(g.n) + " -k " + std::to_string(g.k);
+  } else if (d.kind == kConv) {
+    const RbConvProblem& c = d.conv;
+    switch (c.data_type) {
+      case RB_F32: s += "conv "; break;
+      case RB_F16: s += "convfp16 "; break;
+      case RB_BF16: s += "convbfp16 "; break;
+      case RB_I8: s += "convint8 "; break;
+      case RB_F8E4M3: s += "convfp8_fp8 "; break;
+      default: return false;
+    }
+    s += c.direction == 0 ? "-F 1 " : c.direction == 1 ? "-F 2 " : "-F 4 ";
+    auto upper = [](const char* layout, int which) {
+      std::string o;
+      for (int i = 0; i < 5; ++i) {
+        const char ch = layout[i];
+        char u = '#';
+        if (ch == 'g') u = 'G';
+        else if (ch == 'n') u = 'N';
+        else if (ch == 'k') u = which == 0 ? 'N' : 'C';
+        else if (ch == 'c') u = 'C';
+        else if (ch == 'y' || ch == 'h') u = '0';
+        else if (ch == 'x' || ch == 'w') u = '1';
+        o.push_back(u);
+      }
+      return o;
+    };
+    s += "-f " + upper(c.fil_layout, 0) + " -I " + upper(c.in_layout, 1) + " -O " + upper(c.out_layout, 2);
+    s += " -n " + std::to_string(c.n) + " -c " + std::to_string(c.c) + " -H " + std::to_string(c.h) + " -W " +
+         std::to_string(c.w) + " -k " + std::to_string(c.k) + " -y " + std::to_string(c.y) + " -x " + std::to_string(c.x) +
+         " -p " + std::to_string(c.pad_h) + " -q " + std::to_string(c.pad_w) + " -u " + std::to_string(c.stride_h) + " -v " +
+         std::to_string(c.stride_w) + " -l " + std::to_string(c.dil_h) + " -j " + std::to_string(c.dil_w) + " -g " +
+         std::to_string(c.g);
+  } else {
+    return false;
+  }
+  *out = s;
+  return true;
+}
+
+// RockTuningImpl.cpp:98-113: max work per compute unit / average work per compute unit
+double work_imbalance(int64_t g, int64_t m, int64_t n, int64_t tile_m, int64_t tile_n, int64_t num_cu, int64_t split = 1) {
+  const double groups = (double)g * (double)((m + tile_m - 1) / tile_m) * (double)((n + tile_n - 1) / tile_n) * (double)split;
+  const double per_cu = std::ceil(groups / (double)num_cu);
+  return per_cu * (double)num_cu / groups;
+}
+
+bool set_variant(ProblemDesc* d, uint32_t variant, const std::string& text) {
+  if (d->kind == kAttention) {
+    if (text != "v1:attention") return false;
+    d->perf_config = text;
+    return true;
+  }
+  RbGemmProblem gp;
+  RbGemmConfigInfo info;
+  if (!gemm_of(*d, &gp) || !variant_valid(gp, variant, &info)) return false;
+  const uint32_t old_v = d->variant;
+  d->variant = variant;
+  if (!refresh_problem(d)) {
+    d->variant = old_v;
+    refresh_problem(d);
+    return false;
+  }
+  d->perf_config = text;
+  return true;
+}
+
+RbProblem make_problem(ProblemDesc* d) {
+  RbProblem p;
+  if (!refresh_problem(d)) {
+    delete d;
+    p.ptr = nullptr;
+  } else {
+    p.ptr = d;
+  }
+  return p;
+}
+
+}  // namespace
+}  // namespace rb
+
+using namespace rb;
+
+extern "C" {
+
+RbProblem rbProblemCreate(const char* options) {
+  RbProblem p;
+  ProblemDesc* d = new ProblemDesc;
+  if (!parse_problem(options, d)) {
+    delete d;
+    d = nullptr;
+  }
+  p.ptr = d;
+  return p;
+}
+
+RbProblem rbProblemFromGemm(const RbGemmProblem* gp) {
+  if (!gp) return RbProblem{nullptr};
+  ProblemDesc* d = new ProblemDesc;
+  memset(&d->conv, 0, sizeof(d->conv));
+  memset(&d->att, 0, sizeof(d->att));
+  d->kind = kGemm;
+  d->gemm = *gp;
+  d->arch = "sm_100a";
+  return make_problem(d);
+}
+
+RbProblem rbProblemFromConv(const RbConvProblem* cp) {
+  if (!cp) return RbProblem{nullptr};
+  ProblemDesc* d = new ProblemDesc;
+  memset(&d->gemm, 0, sizeof(d->gemm));
+  memset(&d->att, 0, sizeof(d->att));
+  d->kind = kConv;
+  d->conv = *cp;
+  d->arch = "sm_100a";
+  return make_problem(d);
+}
+
+RbProblem rbProblemFromAttention(const RbAttentionProblem* ap) {
+  if (!ap) return RbProblem{nullptr};
+  ProblemDesc* d = new ProblemDesc;
+  memset(&d->gemm, 0, sizeof(d->gemm));
+  memset(&d->conv, 0, sizeof(d->conv));
+  d->kind = kAttention;
+  d->att = *ap;
+  d->arch = "sm_100a";
+  return make_problem(d);
+}
+
+void rbProblemDestroy(RbProblem problem) { delete static_cast<ProblemDesc*>(problem.ptr); }
+
+size_t rbProblemGetPerfConfig(RbProblem problem, char* buf, size_t bufLen) {
+  if (!problem.ptr) return (size_t)-1;
+  return copy_out(static_cast<ProblemDesc*>(problem.ptr)->perf_config, buf, bufLen);
+}
+
+uint32_t rbProblemGetVariant(RbProblem problem) {
+  return problem.ptr ? static_cast<ProblemDesc*>(problem.ptr)->variant : 0u;
+}
+
+RbTuningSpace rbTuningSpaceCreate(RbProblem problem, RbTuningParamSetKind kind) {
+  RbTuningSpace s;
+  s.ptr = nullptr;
+  if (!problem.ptr) return s;
+  Space* sp = new Space;
+  build_space(*static_cast<ProblemDesc*>(problem.ptr), kind, sp);
+  s.ptr = sp;
+  return s;
+}
+
+unsigned rbTuningGetNumParams(RbTuningSpace space) {
+  return space.ptr ? (unsigned)static_cast<Space*>(space.ptr)->params.size() : 0u;
+}
+
+RbTuningParam rbTuningParamCreate(void) {
+  RbTuningParam p;
+  p.ptr = new Param;
+  return p;
+}
+
+void rbTuningParamDestroy(RbTuningParam param) { delete static_cast<Param*>(param.ptr); }
+
+void rbTuningSpaceDestroy(RbTuningSpace space) { delete static_cast<Space*>(space.ptr); }
+
+bool rbTuningParamGet(RbTuningSpace space, unsigned pos, RbTuningParam param) {
+  if (!space.ptr || !param.ptr) return false;
+  const Space* sp = static_cast<Space*>(space.ptr);
+  if (pos >= sp->params.size()) return false;
+  *static_cast<Param*>(param.ptr) = sp->params[pos];
+  return true;
+}
+
+bool rbTuningParamGetQuick(RbTuningSpace space, unsigned pos, RbTuningParam param) {
+  if (!space.ptr || !param.ptr) return false;
+  const Space* sp = static_cast<Space*>(space.ptr);
+  if (pos >= sp->quick.size()) return false;
+  *static_cast<Param*>(param.ptr) = sp->quick[pos];
+  return true;
+}
+
+size_t rbTuningParamToString(RbTuningParam param, char* buf, size_t bufLen) {
+  if (!param.ptr) return (size_t)-1;
+  return copy_out(static_cast<Param*>(param.ptr)->text, buf, bufLen);
+}
+
+bool rbTuningSetParam(RbProblem problem, RbTuningParam param) {
+  if (!problem.ptr || !param.ptr) return false;
+  const Param* p = static_cast<Param*>(param.ptr);
+  return set_variant(static_cast<ProblemDesc*>(problem.ptr), p->variant, p->text);
+}
+
+bool rbTuningSetFromStr(RbProblem problem, const char* perfStr, size_t perfLen) {
+  if (!problem.ptr || !perfStr) return false;
+  const std::string text(perfStr, perfLen);
+  ProblemDesc* d = static_cast<ProblemDesc*>(problem.ptr);
+  if (d->kind == kAttention) return set_variant(d, 0, text);
+  uint32_t v = 0;
+  if (!perf_config_to_variant(text.c_str(), &v)) return false;
+  return set_variant(d, v, text);
+}
+
+RbTuningTable rbTuningTableCreate(void) {
+  RbTuningTable t;
+  t.ptr = new Table;
+  return t;
+}
+
+void rbTuningTableDestroy(RbTuningTable table) { delete static_cast<Table*>(table.ptr); }
+
+bool rbTuningUpdateTable(RbTuningTable table, const char* problemKey, size_t keyLen, const char* perfStr, size_t perfLen,
+                         float time) {
+  if (!table.ptr || !problemKey || !perfStr) return false;
+  Table* t = static_cast<Table*>(table.ptr);
+  const std::string key(problemKey, keyLen), perf(perfStr, perfLen);
+  std::unique_lock<std::shared_mutex> guard(t->lock);
+  auto it = t->best.find(key);
+  if (it != t->best.end() && it->second.second <= time) return false;   // a better-performing entry exists
+  t->best[key] = std::make_pair(perf, time);
+  return true;
+}
+
+bool rbTuningSetFromTable(RbTuningTable table, RbProblem problem) {
+  if (!table.ptr || !problem.ptr) return false;
+  Table* t = static_cast<Table*>(table.ptr);
+  std::string key;
+  if (!problem_key(*static_cast<ProblemDesc*>(problem.ptr), &key)) return false;
+  std::string perf;
+  {
+    std::shared_lock<std::shared_mutex> guard(t->lock);
+    auto it = t->best.find(key);
+    if (it == t->best.end()) return false;
+    perf = it->second.first;
+  }
+  return rbTuningSetFromStr(problem, perf.c_str(), perf.size());
+}
+
+size_t rbTuningGetKey(RbProblem problem, char* buf, size_t bufLen) {
+  if (!problem.ptr) return (size_t)-1;
+  std::string key;
+  if (!problem_key(*static_cast<ProblemDesc*>(problem.ptr), &key)) return (size_t)-1;
+  return copy_out(key, buf, bufLen);
+}
+
+RbSplitKSelectionLikelihood rbIsSplitKFaster(int64_t gDim, int64_t mDim, int64_t nDim, int64_t kDim, int64_t numCUs,
+                                             RbTuningParamSetKind tuningLevel) {
+  (void)kDim;   // the reference's rule looks at the output tiling only
+  // Rock.cpp (mlirIsSplitKFaster): the quick set never contains a split
+  if (tuningLevel == RbTuningParamSetKindQuick) return RbSplitKNever;
+  if (gDim <= 0 || mDim <= 0 || nDim <= 0 || numCUs <= 0) return RbSplitKNever;
+  static const int64_t tiles_m[] = {128, 256};
+  static const int64_t tiles_n[] = {64, 128, 256};
+  std::set<int64_t> split_values;
+  double min_imbalance = std::numeric_limits<double>::max();
+  for (int64_t tm : tiles_m)
+    for (int64_t tn : tiles_n) {
+      const double dp = work_imbalance(gDim, mDim, nDim, tm, tn, numCUs);
+      min_imbalance = std::min(min_imbalance, dp);
+      split_values.insert(1);
+      if (dp < 1.20) continue;                       // imbalance threshold (RockTuningImpl.cpp:124-127)
+      for (int64_t f : {(int64_t)3, (int64_t)4}) {   // factors 3 and 4 only (:135-146)
+        const double gain = dp / work_imbalance(gDim, mDim, nDim, tm, tn, numCUs, f);
+        if (gain > 1.30) split_values.insert(f);
+      }
+    }
+  if (split_values.size() == 1) return RbSplitKNever;
+  if (min_imbalance > 1.8) return RbSplitKAlways;
+  return RbSplitKMaybe;
+}
+
+bool rbIsProblemFusible(RbProblem problem, const char* perfStr, size_t perfLen) {
+  if (!problem.ptr || !perfStr) return false;
+  const ProblemDesc* d = static_cast<ProblemDesc*>(problem.ptr);
+  const std::string text(perfStr, perfLen);
+  if (d->kind == kAttention) return text == "v1:attention";
+  uint32_t v = 0;
+  return perf_config_to_variant(text.c_str(), &v);
+}
+
+size_t rbGetNumPrefillArgs(RbProblem problem) {
+  (void)problem;
+  return 0;
+}
+
+size_t rbGetNumAuxBuffers(RbProblem problem) {
+  (void)problem;
+  return 0;
+}
+
+}  // extern "C"

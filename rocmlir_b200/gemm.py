@@ -113,13 +113,13 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bo
         out = torch.empty(shape, dtype=out_dtype, device=a.device)
     else:
         assert out.is_contiguous() and out.dtype == out_dtype and out.numel() == p.g * p.m * p.n
+    lib = L.lib()
+    if variant is not None:   # before the workspace query: a K split or a stream-K tail changes what is needed
+        lib.rbSetGemmVariant(int(variant))
     ws_bytes = workspace_size(p)
     if ws_bytes and (workspace is None or workspace.numel() * workspace.element_size() < ws_bytes):
         workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=a.device)
     e = epilogue.to_c() if epilogue is not None else None
-    lib = L.lib()
-    if variant is not None:
-        lib.rbSetGemmVariant(int(variant))
     stream = torch.cuda.current_stream(a.device).cuda_stream
     st = lib.rbGemm(C.byref(p), C.byref(e) if e is not None else None, a.data_ptr(), b.data_ptr(), out.data_ptr(),
                     workspace.data_ptr() if workspace is not None else None,

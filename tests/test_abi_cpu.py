@@ -14,7 +14,7 @@ def declared_symbols():
     names = []
     for h in glob.glob(os.path.join(ROOT, "include", "*.h")):
         src = open(h).read()
-        names += [n for n in re.findall(r"^RB_EXPORT[^;(]*?\b(\w+)\s*\(", src, re.M)]
+        names += [n for n in re.findall(r"^(?:RB|MIIR)_EXPORT[^;(]*?\b(\w+)\s*\(", src, re.M)]
     return sorted(set(names))
 
 
