@@ -35,7 +35,12 @@ typedef enum RbDType {
   RB_BF16 = 2,
   RB_I8 = 3,
   RB_I32 = 4,
-  RB_F8E4M3 = 5
+  RB_F8E4M3 = 5,
+  /* GEMM inputs only (results are f32 / f16 / bf16): OCP e5m2 ("bf8"), and the two mixed pairs rocmlir-gen spells
+   * fp8_bf8 (A e4m3, B e5m2) and bf8_fp8 (A e5m2, B e4m3). */
+  RB_F8E5M2 = 6,
+  RB_F8E4M3_E5M2 = 7,
+  RB_F8E5M2_E4M3 = 8
 } RbDType;
 
 typedef enum RbStatus {
@@ -176,7 +181,8 @@ RB_EXPORT RbStatus rbConv(const RbConvProblem *p, void *filter, void *input, voi
  *   O = softmax_k( f(Q . K) ) . V      Q [G][Sq][D], K [G][D][Sk] (trans_k: [G][Sk][D]), V [G][Sk][Dv], O [G][Sq][Dv]
  * the buffers of rocmlir-gen's rock_attention kernel (rocmlir-gen.cpp:2149-2200, 2264-2328). The reference has no
  * 1/sqrt(d) and no mask inside the op: callers put them into the elementwise region f between the two products
- * (TosaToRock.cpp:779-1074). Here f is:  s*scale (has_scale: the MIGraphX scalar-literal form)  + bias[g][q][k]
+ * (TosaToRock.cpp:779-1074). Here f is:  s*scale (has_scale: the MIGraphX scalar-literal form)  * scale_tensor[g][q][k]
+ * (optional)  + bias[g][q][k]
  * (optional, element type)  then  where(mask[g][q][k] != 0, s, mask_fill) (optional, i8: the mixr-attn-where form)
  * then, with `causal`, keys k > q are dropped analytically (equal to a lower-triangular mask with fill -inf, without
  * reading a [G][Sq][Sk] tensor). Row statistics are f32. f16 and bf16; head dimensions 64 or 128. */
@@ -190,6 +196,8 @@ typedef struct RbAttentionProblem {
   float mask_fill;
   const void *bias;
   const int8_t *mask;
+  const void *scale_tensor; /* optional [G][Sq][Sk] of the element type: s * scale_tensor[g][q][k] before the bias
+                               (rocmlir-gen's --with-attn-scale operand, rocmlir-gen.cpp:2338-2391) */
 } RbAttentionProblem;
 
 RB_EXPORT RbStatus rbAttention(const RbAttentionProblem *p, const void *q, const void *k, const void *v, void *o,

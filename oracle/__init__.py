@@ -17,8 +17,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "_build", "liboracle.so")
 REF_LIB_PATH = os.path.join(HERE, "_ref", "libconv-validation-wrappers.so")
 
-F32, F16, BF16, I8, I32, F8E4M3, I64, F64 = range(8)
-_STORAGE = {F32: np.float32, F16: np.uint16, BF16: np.uint16, I8: np.int8, I32: np.int32, F8E4M3: np.uint8,
+F32, F16, BF16, I8, I32, F8E4M3, I64, F64, F8E5M2 = range(9)
+_STORAGE = {F32: np.float32, F16: np.uint16, BF16: np.uint16, I8: np.int8, I32: np.int32, F8E4M3: np.uint8, F8E5M2: np.uint8,
             I64: np.int64}
 
 _lib = None

@@ -29,7 +29,7 @@
 #define ORC_API extern "C" __attribute__((visibility("default")))
 
 // Element types; numbering shared with RbDType in include/rocmlir_b200.h (plus i64 for references).
-enum { ORC_F32 = 0, ORC_F16 = 1, ORC_BF16 = 2, ORC_I8 = 3, ORC_I32 = 4, ORC_F8E4M3 = 5, ORC_I64 = 6, ORC_F64 = 7 };
+enum { ORC_F32 = 0, ORC_F16 = 1, ORC_BF16 = 2, ORC_I8 = 3, ORC_I32 = 4, ORC_F8E4M3 = 5, ORC_I64 = 6, ORC_F64 = 7, ORC_F8E5M2 = 8 };
 
 // ------------------------------------------------------------------------------------------------
 // Scalar conversions (arith.truncf / arith.extf semantics: round to nearest even)
@@ -108,11 +108,34 @@ static inline uint8_t f32_to_e4m3_bits(float f) {
   return sign | (uint8_t)((be << 3) | (qi - 8));
 }
 
+// OCP e5m2: the upper byte of an IEEE half (bias 15, inf and NaN exist, max finite 57344). f32 -> e5m2 is
+// round-to-nearest-even on the 2-bit mantissa, then saturation to +-57344 like the e4m3 truncation above.
+static inline float e5m2_bits_to_f32(uint8_t v) { return f16_bits_to_f32((uint16_t)((uint16_t)v << 8)); }
+static inline uint8_t f32_to_e5m2_bits(float f) {
+  const uint8_t sign = std::signbit(f) ? 0x80 : 0;
+  if (std::isnan(f)) return sign | 0x7F;
+  const float a = std::fabs(f);
+  if (a >= 57344.0f) return sign | 0x7B;        // max finite (everything at or above it, inf included, saturates)
+  if (a < std::ldexp(1.0f, -17)) return sign;   // below half of the smallest subnormal (2^-16)
+  int e;
+  std::frexp(a, &e);
+  int ue = e - 1;
+  if (ue < -14) ue = -14;                       // subnormals share the scale 2^-14 * 2^-2
+  const float scaled = std::ldexp(a, 2 - ue);   // in units of the last mantissa bit
+  int qi = (int)std::nearbyint(scaled);         // ties to even
+  int be = ue + 15;
+  if (ue == -14 && qi < 4) return sign | (uint8_t)qi;
+  if (qi == 8) { qi = 4; be += 1; }
+  if (be >= 31) return sign | 0x7B;
+  return sign | (uint8_t)((be << 2) | (qi - 4));
+}
+
 static inline float round_to(float x, int t) {
   switch (t) {
     case ORC_F16: return f16_bits_to_f32(f32_to_f16_bits(x));
     case ORC_BF16: return bf16_bits_to_f32(f32_to_bf16_bits(x));
     case ORC_F8E4M3: return e4m3_bits_to_f32(f32_to_e4m3_bits(x));
+    case ORC_F8E5M2: return e5m2_bits_to_f32(f32_to_e5m2_bits(x));
     default: return x;
   }
 }
@@ -126,6 +149,7 @@ ORC_API void orc_convert_to_f32(const void* src, int dtype, float* dst, int64_t 
       case ORC_I8: dst[i] = (float)((const int8_t*)src)[i]; break;
       case ORC_I32: dst[i] = (float)((const int32_t*)src)[i]; break;
       case ORC_F8E4M3: dst[i] = e4m3_bits_to_f32(((const uint8_t*)src)[i]); break;
+      case ORC_F8E5M2: dst[i] = e5m2_bits_to_f32(((const uint8_t*)src)[i]); break;
       case ORC_I64: dst[i] = (float)((const int64_t*)src)[i]; break;
       default: dst[i] = 0; break;
     }
@@ -154,6 +178,7 @@ ORC_API void orc_convert_from_f32(const float* src, void* dst, int dtype, int64_
       case ORC_I8: ((int8_t*)dst)[i] = sat_int ? (int8_t)f32_to_int_sat(x, -128, 127) : (int8_t)(int32_t)x; break;
       case ORC_I32: ((int32_t*)dst)[i] = sat_int ? (int32_t)f32_to_int_sat(x, INT32_MIN, INT32_MAX) : (int32_t)x; break;
       case ORC_F8E4M3: ((uint8_t*)dst)[i] = f32_to_e4m3_bits(x); break;
+      case ORC_F8E5M2: ((uint8_t*)dst)[i] = f32_to_e5m2_bits(x); break;
       default: break;
     }
   }

@@ -12,9 +12,10 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "librocmlir_b200.so")
 
 # RbDType
-F32, F16, BF16, I8, I32, F8E4M3 = 0, 1, 2, 3, 4, 5
-DTYPE_NAMES = {F32: "f32", F16: "f16", BF16: "bf16", I8: "i8", I32: "i32", F8E4M3: "fp8"}
-DTYPE_BYTES = {F32: 4, F16: 2, BF16: 2, I8: 1, I32: 4, F8E4M3: 1}
+F32, F16, BF16, I8, I32, F8E4M3, F8E5M2, F8E4M3_E5M2, F8E5M2_E4M3 = range(9)
+DTYPE_NAMES = {F32: "f32", F16: "f16", BF16: "bf16", I8: "i8", I32: "i32", F8E4M3: "fp8", F8E5M2: "bf8", F8E4M3_E5M2: "fp8_bf8",
+               F8E5M2_E4M3: "bf8_fp8"}
+DTYPE_BYTES = {F32: 4, F16: 2, BF16: 2, I8: 1, I32: 4, F8E4M3: 1, F8E5M2: 1, F8E4M3_E5M2: 1, F8E5M2_E4M3: 1}
 
 # RbStatus
 SUCCESS, INVALID_PARAM, UNSUPPORTED, WORKSPACE_TOO_SMALL, CUDA_ERROR, KERNEL_TIMEOUT = range(6)
@@ -46,7 +47,8 @@ class RbAttentionProblem(C.Structure):
     _fields_ = [("g", C.c_int32), ("seq_q", C.c_int32), ("seq_k", C.c_int32), ("head_qk", C.c_int32),
                 ("head_v", C.c_int32), ("trans_q", C.c_int32), ("trans_k", C.c_int32), ("trans_v", C.c_int32),
                 ("trans_o", C.c_int32), ("data_type", C.c_int32), ("has_scale", C.c_int32), ("scale", C.c_float),
-                ("causal", C.c_int32), ("mask_fill", C.c_float), ("bias", C.c_void_p), ("mask", C.c_void_p)]
+                ("causal", C.c_int32), ("mask_fill", C.c_float), ("bias", C.c_void_p), ("mask", C.c_void_p),
+                ("scale_tensor", C.c_void_p)]
 
 
 class RbGemmConfigInfo(C.Structure):

@@ -17,7 +17,7 @@ from .gemm import rb_dtype
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, trans_k: bool = False,
               scale: Optional[float] = None, bias: Optional[torch.Tensor] = None,
               mask: Optional[torch.Tensor] = None, mask_fill: float = float("-inf"), causal: bool = False,
-              out: Optional[torch.Tensor] = None) -> torch.Tensor:
+              out: Optional[torch.Tensor] = None, scale_tensor: Optional[torch.Tensor] = None) -> torch.Tensor:
     for t in (q, k, v):
         if not t.is_cuda or not t.is_contiguous():
             raise L.RbError(L.INVALID_PARAM, "q, k, v must be contiguous CUDA tensors (the library has no CPU path)")
@@ -29,7 +29,11 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, trans_k: boo
     if out is None:
         out = torch.empty((g, sq, dv), dtype=q.dtype, device=q.device)
     p = L.RbAttentionProblem(g, sq, sk, d, dv, 0, int(trans_k), 0, 0, rb_dtype(q.dtype), int(scale is not None),
-                             float(scale or 0.0), int(causal), float(mask_fill), None, None)
+                             float(scale or 0.0), int(causal), float(mask_fill), None, None, None)
+    if scale_tensor is not None:
+        assert scale_tensor.is_cuda and scale_tensor.is_contiguous() and scale_tensor.dtype == q.dtype and \
+            tuple(scale_tensor.shape) == (g, sq, sk)
+        p.scale_tensor = scale_tensor.data_ptr()
     if bias is not None:
         assert bias.is_cuda and bias.is_contiguous() and bias.dtype == q.dtype and tuple(bias.shape) == (g, sq, sk)
         p.bias = bias.data_ptr()

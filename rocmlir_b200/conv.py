@@ -61,6 +61,12 @@ class ConvConfig:
     out_layout: str = "nhwgk"
 
     def __post_init__(self):
+        # an unknown letter names the output-channel dimension (ConvGenerator.cpp:706-716): "nchw" for the output
+        # tensor and "nchw" (GNCHW) for the filter are accepted spellings
+        if "k" not in self.out_layout:
+            self.out_layout = self.out_layout.replace("c", "k")
+        if "k" not in self.fil_layout:
+            self.fil_layout = self.fil_layout.replace("n", "k")
         self.fil_layout = add_group(self.fil_layout, "f")
         self.in_layout = add_group(self.in_layout, "c")
         self.out_layout = add_group(self.out_layout, "k")

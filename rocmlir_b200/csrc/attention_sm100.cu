@@ -49,6 +49,7 @@ struct AttParams {
   int q_tiles;
   float scale_log2;  // scale * log2(e)
   const void* bias;  // optional additive [G][Sq][Sk], element type
+  const void* scale_t;  // optional multiplicative [G][Sq][Sk], element type (applied before the bias)
   const int8_t* mask;  // optional [G][Sq][Sk]: score kept where mask != 0, else mask_fill
   float mask_fill;
   uint32_t idesc_s, idesc_pv;
@@ -229,7 +230,7 @@ __global__ void __launch_bounds__(kAttThreads, 1) attention_fwd_kernel(const __g
       tc_fence_after();
       const uint32_t tmem_s = tmem_base + lane_base + sb * 128;
       const int key0 = j * kKT;
-      const bool side_inputs = p.bias || p.mask;                       // per-element tensors: general path
+      const bool side_inputs = p.bias || p.mask || p.scale_t;          // per-element tensors: general path
       const bool edge = (key0 + kKT > p.Sk) || (p.causal && key0 + kKT - 1 > q0);  // key tail or diagonal block
       uint32_t v[128];
 #pragma unroll
@@ -264,6 +265,7 @@ __global__ void __launch_bounds__(kAttThreads, 1) attention_fwd_kernel(const __g
           float x = __uint_as_float(v[i]) * p.scale_log2;
           const int key = key0 + i;
           if (key < p.Sk) {
+            if (p.scale_t) x *= load_elem(p.scale_t, side_off + key, p.is_bf16);
             if (p.bias) x = fmaf(load_elem(p.bias, side_off + key, p.is_bf16), kLog2e, x);
             if (p.mask && p.mask[side_off + key] == 0) x = p.mask_fill * kLog2e;
             if (p.causal && key > row) x = -INFINITY;
@@ -591,7 +593,7 @@ __global__ void __launch_bounds__(kAtt2Threads, 1) attention_fwd2_kernel(const _
       sm_wait += ts1 - ts0;
       tc_fence_after();
       const int key0 = j * kKT;
-      const bool side_inputs = p.bias || p.mask;
+      const bool side_inputs = p.bias || p.mask || p.scale_t;
       const bool edge = (key0 + kKT > p.Sk) || (p.causal && key0 + kKT - 1 > tq0);
       const int limit = min(p.Sk - key0, p.causal ? (int)min(row - key0 + 1, (long long)kKT) : kKT);
       const long long side_off = ((long long)g * p.Sq + min(row, (long long)p.Sq - 1)) * p.Sk + key0;
@@ -599,6 +601,7 @@ __global__ void __launch_bounds__(kAtt2Threads, 1) attention_fwd2_kernel(const _
       auto fx = [&](uint32_t raw, int i) -> float {
         float x = __uint_as_float(raw) * p.scale_log2;
         if (side_inputs && i < p.Sk - key0) {
+          if (p.scale_t) x *= load_elem(p.scale_t, side_off + i, p.is_bf16);
           if (p.bias) x = fmaf(load_elem(p.bias, side_off + i, p.is_bf16), kLog2e, x);
           if (p.mask && p.mask[side_off + i] == 0) x = p.mask_fill * kLog2e;
         }
@@ -610,7 +613,7 @@ __global__ void __launch_bounds__(kAtt2Threads, 1) attention_fwd2_kernel(const _
       // exponent argument x(i) - m; without a bias it is the same single fused multiply-add as on the fast path, so
       // that a mask tensor and the analytic causal mask give bit-identical results
       auto fe = [&](uint32_t raw, int i) -> float {
-        float a = p.bias ? fx(raw, i) - m_use : fmaf(__uint_as_float(raw), p.scale_log2, -m_use);
+        float a = (p.bias || p.scale_t) ? fx(raw, i) - m_use : fmaf(__uint_as_float(raw), p.scale_log2, -m_use);
         if (p.mask && i < p.Sk - key0 && p.mask[side_off + i] == 0) a = p.mask_fill * kLog2e - m_use;
         return a;
       };
@@ -822,6 +825,7 @@ extern "C" RbStatus rbAttention(const RbAttentionProblem* p, const void* q, cons
   kp.q_tiles = (p->seq_q + kQT - 1) / kQT;
   kp.scale_log2 = (p->has_scale ? p->scale : 1.0f) * kLog2e;
   kp.bias = p->bias;
+  kp.scale_t = p->scale_tensor;
   kp.mask = p->mask;
   kp.mask_fill = p->mask_fill;
   const uint32_t fmt = kp.is_bf16 ? 1u : 0u;

@@ -41,44 +41,49 @@ __device__ __forceinline__ float tf32_round(float x) {
 }
 template <bool TRANSPOSE, bool SPLIT>
 __global__ void f32_prepare_kernel(const float* __restrict__ src, float* __restrict__ hi, float* __restrict__ lo,
-                                   int R, int C, int pitch) {
+                                   int R, int C, int pitch, int tiles_x, int tiles_y, long long total_tiles) {
   __shared__ float tile[32][33];
-  const long long g = blockIdx.z;
-  const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
-  const float* s = src + g * (long long)R * C;
+  // 32 x 32 tiles dealt out over a 1-D grid: row counts of several million (im2col matrices) exceed gridDim.y
+  for (long long t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+    const long long g = t / ((long long)tiles_x * tiles_y);
+    const long long rem = t - g * (long long)tiles_x * tiles_y;
+    const int c0 = (int)(rem % tiles_x) * 32, r0 = (int)(rem / tiles_x) * 32;
+    const float* s = src + g * (long long)R * C;
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int r = r0 + threadIdx.y + 8 * i, c = c0 + threadIdx.x;
-    tile[threadIdx.y + 8 * i][threadIdx.x] = (r < R && c < C) ? s[(long long)r * C + c] : 0.0f;
-  }
-  __syncthreads();
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    float x;
-    long long o;
-    bool ok;
-    if (TRANSPOSE) {
-      const int oc = c0 + threadIdx.y + 8 * i;  // output row = source column
-      const int orr = r0 + threadIdx.x;         // output column = source row
-      x = tile[threadIdx.x][threadIdx.y + 8 * i];
-      ok = oc < C && orr < pitch;
-      o = (g * C + oc) * (long long)pitch + orr;
-    } else {
+    for (int i = 0; i < 4; ++i) {
       const int r = r0 + threadIdx.y + 8 * i, c = c0 + threadIdx.x;
-      x = tile[threadIdx.y + 8 * i][threadIdx.x];
-      ok = r < R && c < pitch;
-      o = (g * R + r) * (long long)pitch + c;
+      tile[threadIdx.y + 8 * i][threadIdx.x] = (r < R && c < C) ? s[(long long)r * C + c] : 0.0f;
     }
-    if (ok) {
-      if (SPLIT) {
-        const float h = tf32_round(x);
-        const float l = isfinite(h) ? tf32_round(x - h) : 0.0f;
-        hi[o] = h;
-        lo[o] = l;
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float x;
+      long long o;
+      bool ok;
+      if (TRANSPOSE) {
+        const int oc = c0 + threadIdx.y + 8 * i;  // output row = source column
+        const int orr = r0 + threadIdx.x;         // output column = source row
+        x = tile[threadIdx.x][threadIdx.y + 8 * i];
+        ok = oc < C && orr < pitch;
+        o = (g * C + oc) * (long long)pitch + orr;
       } else {
-        hi[o] = x;
+        const int r = r0 + threadIdx.y + 8 * i, c = c0 + threadIdx.x;
+        x = tile[threadIdx.y + 8 * i][threadIdx.x];
+        ok = r < R && c < pitch;
+        o = (g * R + r) * (long long)pitch + c;
+      }
+      if (ok) {
+        if (SPLIT) {
+          const float h = tf32_round(x);
+          const float l = isfinite(h) ? tf32_round(x - h) : 0.0f;
+          hi[o] = h;
+          lo[o] = l;
+        } else {
+          hi[o] = x;
+        }
       }
     }
+    __syncthreads();
   }
 }
 
@@ -143,6 +148,14 @@ GemmConfig choose_config(const RbGemmProblem* p, int variant, bool epi_vec = fal
       long long cap = kblocks / 8;  // at least 8 K blocks per range
       c.splits = (int)std::max<long long>(1, std::min<long long>(std::min(want, cap), 128));
     }
+  }
+  // f32 in accurate mode: the tensor core adds each MMA's products into the f32 accumulator with truncation, a bias
+  // of about -2^-24 per 8-element step that grows linearly with the length of one accumulation chain (measured:
+  // relative error 7.5e-9 x K on same-sign data; 1.9e-4 at K = 25088, where the sequential f32 loop of the reference
+  // has 1e-5). Chains are therefore kept to 2048 elements; the partial planes are added with round-to-nearest.
+  if (p->ab_type == RB_F32 && p->f32_mode == 0) {   // also under an explicit variant: shorter chains only
+    const long long need = std::min<long long>(((long long)p->k + 2047) / 2048, 255);
+    if (need > c.splits) c.splits = (int)need;
   }
   if (c.splits > kblocks) c.splits = (int)kblocks;
   // every range must be non-empty with ceil-division ranges
@@ -222,7 +235,9 @@ OperandPlan plan_operand(bool mn_major, int mn, int k, size_t es, bool is_f32, b
   return o;
 }
 
-bool valid_ab(int t) { return t == RB_F32 || t == RB_F16 || t == RB_BF16 || t == RB_I8 || t == RB_F8E4M3; }
+bool valid_ab(int t) {
+  return t == RB_F32 || t == RB_F16 || t == RB_BF16 || t == RB_I8 || (t >= RB_F8E4M3 && t <= RB_F8E5M2_E4M3);
+}
 bool valid_c(int t) { return t >= RB_F32 && t <= RB_F8E4M3; }
 
 RbStatus check_problem(const RbGemmProblem* p) {
@@ -344,12 +359,15 @@ RbStatus rb::gemm_run(const RbGemmProblem* p, const RbEpilogue* epi, const void*
   }
 
   int kind;
-  uint32_t fmt, cfmt = 1;
+  uint32_t fmt, fmt_b = 0xffffffffu, cfmt = 1;   // fmt_b: B's format when it differs from A's
   switch (abt) {
     case RB_F16: kind = kKindF16; fmt = 0; break;
     case RB_BF16: kind = kKindF16; fmt = 1; break;
     case RB_F32: kind = kKindTF32; fmt = 2; break;
     case RB_I8: kind = kKindI8; fmt = 1; cfmt = 2; break;
+    case RB_F8E5M2: kind = kKindF8; fmt = 1; break;               // f8f6f4 kind: 0 = e4m3, 1 = e5m2
+    case RB_F8E4M3_E5M2: kind = kKindF8; fmt = 0; fmt_b = 1; break;
+    case RB_F8E5M2_E4M3: kind = kKindF8; fmt = 1; fmt_b = 0; break;
     default: kind = kKindF8; fmt = 0; break;
   }
 
@@ -385,14 +403,16 @@ RbStatus rb::gemm_run(const RbGemmProblem* p, const RbEpilogue* epi, const void*
     const dim3 blk(32, 8, 1);
     // the grid covers the padded extent of whichever dimension becomes the output row pitch
     const int cx = o.src_mn_major ? o.src_cols : o.pitch, ry = o.src_mn_major ? o.pitch : o.src_rows;
-    const dim3 grd((cx + 31) / 32, (ry + 31) / 32, p->g);
+    const int tiles_x = (cx + 31) / 32, tiles_y = (ry + 31) / 32;
+    const long long total_tiles = (long long)tiles_x * tiles_y * p->g;
+    const dim3 grd((unsigned)std::min<long long>(total_tiles, (long long)dev->sm_count * 64), 1, 1);
     const float* s = static_cast<const float*>(src);
     if (o.src_mn_major) {
-      if (split) f32_prepare_kernel<true, true><<<grd, blk, 0, stream>>>(s, hi, lo, o.src_rows, o.src_cols, o.pitch);
-      else f32_prepare_kernel<true, false><<<grd, blk, 0, stream>>>(s, hi, lo, o.src_rows, o.src_cols, o.pitch);
+      if (split) f32_prepare_kernel<true, true><<<grd, blk, 0, stream>>>(s, hi, lo, o.src_rows, o.src_cols, o.pitch, tiles_x, tiles_y, total_tiles);
+      else f32_prepare_kernel<true, false><<<grd, blk, 0, stream>>>(s, hi, lo, o.src_rows, o.src_cols, o.pitch, tiles_x, tiles_y, total_tiles);
     } else {
-      if (split) f32_prepare_kernel<false, true><<<grd, blk, 0, stream>>>(s, hi, lo, o.src_rows, o.src_cols, o.pitch);
-      else f32_prepare_kernel<false, false><<<grd, blk, 0, stream>>>(s, hi, lo, o.src_rows, o.src_cols, o.pitch);
+      if (split) f32_prepare_kernel<false, true><<<grd, blk, 0, stream>>>(s, hi, lo, o.src_rows, o.src_cols, o.pitch, tiles_x, tiles_y, total_tiles);
+      else f32_prepare_kernel<false, false><<<grd, blk, 0, stream>>>(s, hi, lo, o.src_rows, o.src_cols, o.pitch, tiles_x, tiles_y, total_tiles);
     }
     count_launch();
   };
@@ -425,6 +445,7 @@ RbStatus rb::gemm_run(const RbGemmProblem* p, const RbEpilogue* epi, const void*
       b_src[0] = wsb + ws.b_off[0];
     }
   }
+  RB_CUDA_TRY(cudaGetLastError());   // launch errors of the preparation kernels
 
   // Variant word (rbSetGemmVariant): bits 0-3: 1 = single CTA per tile, 2 = CTA pair (0 = automatic);
   // bits 4-7 ring depth; bit 8 plain stores instead of TMA stores; bits 12-15 tile width code (1 = 64,
@@ -491,7 +512,7 @@ RbStatus rb::gemm_run(const RbGemmProblem* p, const RbEpilogue* epi, const void*
   kp.tiles_n = (p->n + bn - 1) / bn;
   kp.kblocks = (p->k + bke - 1) / bke;
   kp.nseg = nseg;
-  kp.idesc = make_idesc(cfmt, fmt, fmt, a_mn ? 1u : 0u, b_mn ? 1u : 0u, (uint32_t)(kBM * ctas), (uint32_t)bn);
+  kp.idesc = make_idesc(cfmt, fmt, fmt_b == 0xffffffffu ? fmt : fmt_b, a_mn ? 1u : 0u, b_mn ? 1u : 0u, (uint32_t)(kBM * ctas), (uint32_t)bn);
   kp.acc_is_int = is_int ? 1 : 0;
   EpiParams ep;
   memset(&ep, 0, sizeof(ep));

@@ -57,7 +57,7 @@ inline size_t dtype_bytes(int t) {
   switch (t) {
     case RB_F32: case RB_I32: return 4;
     case RB_F16: case RB_BF16: return 2;
-    case RB_I8: case RB_F8E4M3: return 1;
+    case RB_I8: case RB_F8E4M3: case RB_F8E5M2: case RB_F8E4M3_E5M2: case RB_F8E5M2_E4M3: return 1;
     default: return 0;
   }
 }

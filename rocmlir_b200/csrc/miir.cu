@@ -27,7 +27,7 @@ struct LaunchDescriptor {
   uint32_t workspace;  // bytes
   RbConvProblem conv;
   RbGemmProblem gemm;
-  RbAttentionProblem att;   // bias / mask pointers are always NULL in a descriptor
+  RbAttentionProblem att;   // bias / mask / scale tensor pointers are always NULL in a descriptor
 };
 constexpr char kMagic[8] = {'R', 'B', '2', 'K', 'D', 'S', 'C', '\0'};
 constexpr uint32_t kDescVersion = 1;
@@ -187,5 +187,6 @@ extern "C" MiirStatus miirLaunchFromBuffer(const char* buffer, size_t size, void
   if (memcmp(d.magic, kMagic, 8) != 0 || d.version != kDescVersion) return MIIR_INVALID_MODULE;
   d.att.bias = nullptr;
   d.att.mask = nullptr;
+  d.att.scale_tensor = nullptr;
   return launch_descriptor(d, arg0, arg1, arg2, extra, workspace, workspace_bytes, stream);
 }

@@ -76,6 +76,9 @@ int parse_type(const std::string& t) {
   if (t == "i8") return RB_I8;
   if (t == "i32") return RB_I32;
   if (t == "fp8" || t == "f8E4M3FN" || t == "fp8_fp8") return RB_F8E4M3;
+  if (t == "bf8" || t == "f8E5M2" || t == "bf8_bf8") return RB_F8E5M2;
+  if (t == "fp8_bf8") return RB_F8E4M3_E5M2;
+  if (t == "bf8_fp8") return RB_F8E5M2_E4M3;
   return -1;
 }
 
@@ -127,7 +130,7 @@ bool parse_conv(const std::map<std::string, std::string>& m, int direction, Prob
   RbConvProblem& c = h->conv;
   memset(&c, 0, sizeof(c));
   const int in_t = parse_type(m.at("in_type")), fil_t = parse_type(m.at("fil_type")), out_t = parse_type(m.at("out_type"));
-  if (in_t < 0 || fil_t < 0 || out_t < 0 || in_t == RB_I32 || in_t != fil_t) return false;
+  if (in_t < 0 || fil_t < 0 || out_t < 0 || in_t == RB_I32 || in_t != fil_t || in_t >= RB_F8E4M3) return false;
   if (in_t == RB_I8) {
     if (out_t != RB_I32) return false;   // i8 x i8 accumulates and stores i32
   } else if (out_t != in_t) {
@@ -176,9 +179,10 @@ bool parse_gemm(const std::map<std::string, std::string>& m, ProblemDesc* h) {
   if (!m.count("t") || !m.count("m") || !m.count("n") || !m.count("k")) return false;
   const int t = parse_type(m.at("t"));
   if (t < 0 || t == RB_I32) return false;
-  int out_t = (t == RB_I8) ? RB_I32 : t;   // rocmlir-gen.cpp:3709-3729: -t i8 defaults to an i32 result
+  // rocmlir-gen.cpp:430-455: -t i8 defaults to an i32 result, 8-bit floats to an f32 result
+  int out_t = (t == RB_I8) ? RB_I32 : (t >= RB_F8E4M3 ? RB_F32 : t);
   if (m.count("out_datatype")) out_t = parse_type(m.at("out_datatype"));
-  if (out_t < 0) return false;
+  if (out_t < 0 || out_t > RB_F8E4M3) return false;
   p.g = 1;
   if (!opt_int(m, "g", &p.g) || !opt_int(m, "m", &p.m) || !opt_int(m, "n", &p.n) || !opt_int(m, "k", &p.k)) return false;
   if (!opt_bool(m, "transA", &p.trans_a) || !opt_bool(m, "transB", &p.trans_b) || !opt_bool(m, "transC", &p.trans_c))

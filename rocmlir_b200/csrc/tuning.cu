@@ -142,6 +142,9 @@ const char* type_name(int t) {
     case RB_I8: return "i8";
     case RB_I32: return "i32";
     case RB_F8E4M3: return "fp8";
+    case RB_F8E5M2: return "bf8";
+    case RB_F8E4M3_E5M2: return "fp8_bf8";
+    case RB_F8E5M2_E4M3: return "bf8_fp8";
     default: return nullptr;
   }
 }
@@ -163,7 +166,7 @@ bool problem_key(const ProblemDesc& d, std::string* out) {
     const char* t = type_name(g.ab_type);
     const char* ot = type_name(g.c_type);
     if (!t || !ot || g.ab_type == RB_I32) return false;
-    s += std::string("-t ") + (g.ab_type == RB_F8E4M3 ? "fp8_fp8" : t) + " -out_datatype " + ot + " -transA " +
+    s += std::string("-t ") + (g.ab_type == RB_F8E4M3 ? "fp8_fp8" : g.ab_type == RB_F8E5M2 ? "bf8_bf8" : t) + " -out_datatype " + ot + " -transA " +
          bool_str(g.trans_a) + " -transB " + bool_str(g.trans_b) + " -g " + std::to_string(g.g) + " -m " +
          std::to_string(g.m) + " -n " + std::to_string(g.n) + " -k " + std::to_string(g.k);
   } else if (d.kind == kConv) {

@@ -16,7 +16,7 @@ import torch
 from . import _lib as L
 
 _TORCH2RB = {torch.float32: L.F32, torch.float16: L.F16, torch.bfloat16: L.BF16, torch.int8: L.I8,
-             torch.int32: L.I32, torch.float8_e4m3fn: L.F8E4M3}
+             torch.int32: L.I32, torch.float8_e4m3fn: L.F8E4M3, torch.float8_e5m2: L.F8E5M2}
 _RB2TORCH = {v: k for k, v in _TORCH2RB.items()}
 
 
@@ -79,17 +79,22 @@ def problem(a: torch.Tensor, b: torch.Tensor, trans_a: bool, trans_b: bool, tran
     kb, n = (b3.shape[2], b3.shape[1]) if trans_b else (b3.shape[1], b3.shape[2])
     if kb != k or b3.shape[0] != g:
         raise L.RbError(L.INVALID_PARAM, f"shape mismatch: A {tuple(a.shape)} B {tuple(b.shape)}")
-    if a.dtype != b.dtype:
-        raise L.RbError(L.UNSUPPORTED, "mixed A/B element types are not supported")
-    return L.RbGemmProblem(g, m, n, k, int(trans_a), int(trans_b), int(trans_c), rb_dtype(a.dtype),
-                           rb_dtype(out_dtype), int(f32_mode))
+    if a.dtype == b.dtype:
+        ab = rb_dtype(a.dtype)
+    elif (a.dtype, b.dtype) == (torch.float8_e4m3fn, torch.float8_e5m2):
+        ab = L.F8E4M3_E5M2      # rocmlir-gen's -t fp8_bf8
+    elif (a.dtype, b.dtype) == (torch.float8_e5m2, torch.float8_e4m3fn):
+        ab = L.F8E5M2_E4M3      # -t bf8_fp8
+    else:
+        raise L.RbError(L.UNSUPPORTED, "mixed A/B element types exist for the two 8-bit float formats only")
+    return L.RbGemmProblem(g, m, n, k, int(trans_a), int(trans_b), int(trans_c), ab, rb_dtype(out_dtype), int(f32_mode))
 
 
 def default_out_dtype(ab: torch.dtype) -> torch.dtype:
     # rocmlir-gen: -t i8 => i32 result, -t fp8 => f32 result (rocmlir-gen.cpp:432-458)
     if ab == torch.int8:
         return torch.int32
-    if ab == torch.float8_e4m3fn:
+    if ab in (torch.float8_e4m3fn, torch.float8_e5m2):
         return torch.float32
     return ab
 

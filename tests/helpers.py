@@ -7,13 +7,13 @@ import numpy as np
 import oracle
 
 NP_STORAGE = {oracle.F32: np.float32, oracle.F16: np.uint16, oracle.BF16: np.uint16, oracle.I8: np.int8,
-              oracle.I32: np.int32, oracle.F8E4M3: np.uint8}
+              oracle.I32: np.int32, oracle.F8E4M3: np.uint8, oracle.F8E5M2: np.uint8}
 
 
 def torch_dtype(code):
     import torch
     return {oracle.F32: torch.float32, oracle.F16: torch.float16, oracle.BF16: torch.bfloat16, oracle.I8: torch.int8,
-            oracle.I32: torch.int32, oracle.F8E4M3: torch.float8_e4m3fn}[code]
+            oracle.I32: torch.int32, oracle.F8E4M3: torch.float8_e4m3fn, oracle.F8E5M2: torch.float8_e5m2}[code]
 
 
 def to_device(raw: np.ndarray, code: int, device="cuda"):
@@ -28,7 +28,7 @@ def from_device(t, code: int) -> np.ndarray:
     import torch
     if code in (oracle.F16, oracle.BF16):
         return t.contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
-    if code == oracle.F8E4M3:
+    if code in (oracle.F8E4M3, oracle.F8E5M2):
         return t.contiguous().view(torch.uint8).cpu().numpy()
     return t.contiguous().cpu().numpy()
 

@@ -1,0 +1,371 @@
+"""A test driver with rocmlir-gen's command line: generate the inputs the way `rocmlir-gen -ph -pv -rand N` does,
+run the operation on the GPU through the library, run the CPU restatement of the reference's validator, compare
+with the reference's verifier and thresholds, and print the verdict line `[1 1 1]`
+(mlir/tools/rocmlir-gen/rocmlir-gen.cpp:73-785 flags, :996-1092 defaults, :837-972 layout and padding fix-ups,
+:1325-1486 data fill, :2696-2886 verification). It replaces the reference's pipeline
+`rocmlir-gen ... -pv | rocmlir-driver -c | mlir-cpu-runner` for the tests of this repository.
+
+    python tests/rocmlir_gen.py --operation gemm -t f16 -g 3 -m 1024 -k 769 -n 1024 --arch sm_100a -pv -rand 1
+
+This file is test infrastructure: it is the only place where the library and the oracle meet.
+"""
+from __future__ import annotations
+
+import os
+import sys
+from dataclasses import dataclass
+from typing import Dict, List, Optional
+
+import numpy as np
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+import oracle  # noqa: E402
+from helpers import from_device, to_device  # noqa: E402
+
+
+class Unsupported(Exception):
+    """The flags describe something this library has no kernel for (the reason says what)."""
+
+
+# flags that take no value (cl::opt<bool> given bare); `-flag=true|false` also works for them
+BOOL_FLAGS = {"p", "pv", "ph", "pr", "pi", "pv_with_gpu", "pv_with_mlir", "prc", "reverse_grid", "with-attn-scale",
+              "with-attn-bias", "transA", "transB", "transC", "transQ", "transK", "transV", "transO", "emit-tuning-key",
+              "host-harness", "verifier-keep-perf-config", "disable-split-k-for-tuning", "print-results"}
+
+
+def parse_flags(text: str) -> Dict[str, str]:
+    """-k v | -k=v | --k v | --k=v | bare boolean flags. Later occurrences overwrite earlier ones."""
+    toks = text.split()
+    out: Dict[str, str] = {}
+    i = 0
+    while i < len(toks):
+        t = toks[i]
+        if not t.startswith("-") or t.lstrip("-") == "" or t.lstrip("-")[0].isdigit():
+            raise ValueError(f"unexpected token {t!r}")
+        key = t.lstrip("-")
+        if "=" in key:
+            key, val = key.split("=", 1)
+            out[key] = val
+            i += 1
+        elif key in BOOL_FLAGS:
+            out[key] = "true"
+            i += 1
+        else:
+            if i + 1 >= len(toks):
+                raise ValueError(f"flag {t!r} needs a value")
+            out[key] = toks[i + 1]
+            i += 2
+    return out
+
+
+TYPE_CODES = {"f32": oracle.F32, "f16": oracle.F16, "bf16": oracle.BF16, "i8": oracle.I8, "i32": oracle.I32,
+              "fp8": oracle.F8E4M3, "f8E4M3FN": oracle.F8E4M3, "bf8": oracle.F8E5M2, "f8E5M2": oracle.F8E5M2}
+
+
+@dataclass
+class Types:
+    a: int
+    b: int
+    out: int
+
+
+def resolve_types(f: Dict[str, str]) -> Types:
+    """The -t callback and its defaults (rocmlir-gen.cpp:430-455, 1000-1008)."""
+    fil = f.get("fil_dtype", "f32")
+    inp = f.get("in_dtype", "f32")
+    out = f.get("out_dtype", f.get("out_datatype", ""))
+    t = f.get("t", f.get("dtype"))
+    if t is not None:
+        if "_" in t:
+            fil, inp = t.split("_", 1)
+        else:
+            fil = inp = t
+        if out == "":
+            if t == "i8":
+                out = "i32"
+            elif t.startswith(("f8", "fp8", "bf8")):
+                out = "f32"
+            elif fil == inp:
+                out = t
+    if out == "":
+        out = "f32"
+    for name in (fil, inp, out):
+        if name not in TYPE_CODES:
+            raise Unsupported(f"element type {name}")
+    if fil != inp and not {fil, inp} <= {"fp8", "bf8", "f8E4M3FN", "f8E5M2"}:
+        raise Unsupported("mixed input types other than the two 8-bit float formats")
+    return Types(TYPE_CODES[fil], TYPE_CODES[inp], TYPE_CODES[out])
+
+
+class Filler:
+    """Tensors filled in kernel-argument order (rocmlir-gen.cpp:3157-3218): one libc rand() per element with
+    `-rand N`, the fixed pattern or all-ones otherwise."""
+
+    def __init__(self, f: Dict[str, str]):
+        self.mode = f.get("rand", "fixed")
+        self.rand_float = f.get("rand_type", "int") == "float"
+        self.mn = int(f.get("rand_min", 0))
+        self.mx = int(f.get("rand_max", 1))
+        self.random = self.mode not in ("fixed", "none")
+        if self.random:
+            seed = int(self.mode)
+            if seed == 0:
+                raise Unsupported("-rand 0 seeds from the clock: not reproducible")
+            oracle.seed(seed)
+        # -rand_side: only that tensor (argument index 0 filter, 1 input, 2 output) is random; the others get the
+        # degenerate range [1, 1] (rocmlir-gen.cpp:1325-1357), i.e. the constant 1 (0.1 in float mode)
+        side = f.get("rand_side", "both")[0]
+        self.only = {"f": 0, "i": 1, "o": 2}.get(side, -1)
+        self.index = 0
+
+    def tensor(self, n: int, code: int):
+        """-> (values as f32 after rounding to the element type, raw storage bits)"""
+        is_int = code in (oracle.I8, oracle.I32)
+        idx = self.index
+        self.index += 1
+        if self.random:
+            if self.only >= 0 and self.only != idx:
+                vals = oracle.fill_random(n, self.rand_float, 1, 1)
+            elif self.rand_float:
+                vals = oracle.fill_random(n, True, self.mn, self.mx)
+            else:
+                vals = oracle.fill_random(n, False, -5, 5)
+        elif self.mode == "none":
+            vals = np.full(n, 0.1 if self.rand_float else 1.0, np.float32)
+        else:
+            vals = oracle.fill_pattern(n, [1.0, -1.0, 2.0] if is_int else [0.5, -1.0, 0.75])
+        if code == oracle.I32:
+            raw = vals.astype(np.int32)
+            return raw.astype(np.float32), raw
+        raw = oracle.from_f32(vals, code)
+        return oracle.to_f32(raw, code), raw
+
+
+def thresholds(f: Dict[str, str], test_code: int):
+    """rocmlir-gen.cpp:2850-2861"""
+    rms = 0.001 if test_code == oracle.F16 else 0.00003
+    if "RMS_threshold" in f:
+        rms = float(f["RMS_threshold"])
+    abs_thr = float(f.get("absDiff_threshold", 100.0))
+    rel_thr = float(f.get("relDiff_threshold", 0.000001))
+    if test_code == oracle.F16:
+        rel_thr = 100.0
+    return rms, abs_thr, rel_thr
+
+
+def verdict_for(got_raw: np.ndarray, want: np.ndarray, code: int, f: Dict[str, str]) -> List[int]:
+    if code in (oracle.I8, oracle.I32):
+        v, _ = oracle.verify_int(got_raw, want.astype(np.int64))
+        return v
+    got = oracle.to_f32(got_raw, code) if code != oracle.F32 else got_raw
+    want = oracle.round_to(want, code)       # the validation result is truncated to the kernel's type (:2822-2839)
+    rms, a, r = thresholds(f, code)
+    v, _ = oracle.verify_float(got, want, rms, a, r)
+    return v
+
+
+def as_bool(f: Dict[str, str], key: str) -> bool:
+    return f.get(key, "false").lower() in ("true", "1")
+
+
+def translate_perf_config(f: Dict[str, str]) -> Optional[int]:
+    """The reference's perf strings name AMD tile parameters; the only field with a meaning here is the split-K
+    factor of a `v2:` GEMM string (7th field), which selects the same number of K ranges."""
+    pc = f.get("perf_config", "")
+    if pc.startswith("v2:"):
+        parts = pc[3:].split(",")
+        if len(parts) >= 7 and int(parts[6]) > 1:
+            return int(parts[6]) << 16
+    return None
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+def run_gemm(f: Dict[str, str]) -> List[int]:
+    from rocmlir_b200.gemm import gemm
+    ty = resolve_types(f)
+    if as_bool(f, "p"):
+        g, m, k, n = 1, 1024, 769, 512
+    else:
+        g, m, k, n = int(f.get("g", 1)), int(f["m"]), int(f["k"]), int(f["n"])
+    ta, tb, tc = as_bool(f, "transA"), as_bool(f, "transB"), as_bool(f, "transC")
+    if (g * m * n) > (1 << 29):
+        raise Unsupported("result larger than 2 GiB elements: the CPU validator alone would take the test budget")
+    fill = Filler(f)
+    a_shape = (g, k, m) if ta else (g, m, k)
+    b_shape = (g, n, k) if tb else (g, k, n)
+    c_shape = (g, n, m) if tc else (g, m, n)
+    a_f, a_r = fill.tensor(int(np.prod(a_shape)), ty.a)
+    b_f, b_r = fill.tensor(int(np.prod(b_shape)), ty.b)
+    fill.tensor(int(np.prod(c_shape)), ty.out)        # the output buffer is an argument too: it consumes rand() calls
+    is_int = ty.a == oracle.I8
+    if is_int and ty.out not in (oracle.I32,):
+        raise Unsupported("i8 GEMM with a non-i32 result needs an epilogue")
+    threads = oracle.max_threads()
+    if is_int:
+        want = oracle.gemm_i8(a_r.reshape(a_shape), b_r.reshape(b_shape), g, m, n, k, ta, tb, tc, threads=threads)
+    else:
+        want = oracle.gemm_f32(a_f.reshape(a_shape), b_f.reshape(b_shape), g, m, n, k, ta, tb, tc, threads=threads)
+    from helpers import torch_dtype
+    a_d = to_device(a_r.reshape(a_shape), ty.a)
+    b_d = to_device(b_r.reshape(b_shape), ty.b)
+    out = gemm(a_d, b_d, trans_a=ta, trans_b=tb, trans_c=tc, out_dtype=torch_dtype(ty.out),
+               variant=translate_perf_config(f) or 0)
+    got = from_device(out, ty.out)
+    return verdict_for(got.reshape(c_shape), want, ty.out, f)
+
+
+def conv_config(f: Dict[str, str]):
+    from rocmlir_b200.conv import ConvConfig
+    if as_bool(f, "p"):
+        d = dict(g=1, n=128, c=8, k=128, h=32, w=32, y=3, x=3)   # rocmlir-gen.cpp:1023-1046 (no mfma forced)
+        f = {**{"dilation_h": "1", "dilation_w": "1", "conv_stride_h": "1", "conv_stride_w": "1"}, **f}
+    else:
+        g = int(f.get("groupsize", 1))
+        ci, co = int(f["in_channels"]), int(f["out_channels"])
+        if ci % g or co % g:
+            raise ValueError("channels must be divisible by the group count")
+        d = dict(g=g, n=int(f["batchsize"]), c=ci // g, k=co // g, h=int(f["in_h"]), w=int(f["in_w"]),
+                 y=int(f["fil_h"]), x=int(f["fil_w"]))
+    if any(k in f for k in ("in_d", "fil_d", "out_d")):
+        raise Unsupported("3-D convolution")
+    pad = {}
+    for ax in ("h", "w"):
+        combined = int(f.get(f"padding_{ax}", 0))
+        left, right = int(f.get(f"padding_{ax}_l", 0)), int(f.get(f"padding_{ax}_r", 0))
+        if combined > 0 and left == 0 and right == 0:      # rocmlir-gen.cpp:880-897
+            left = right = combined
+        pad[ax] = (left, right)
+    sh, sw = int(f.get("conv_stride_h", 1)), int(f.get("conv_stride_w", 1))
+    dh, dw = int(f.get("dilation_h", 1)), int(f.get("dilation_w", 1))
+
+    def fix_right(inp, fil, pl, pr, stride, dil):              # rocmlir-gen.cpp:905-971
+        out = (inp + pl + pr - (fil - 1) * dil - 1) // stride + 1
+        need = 1 + (fil - 1) * dil + (out - 1) * stride
+        return pr + max(0, need - (inp + pl + pr))
+    pr_h = fix_right(d["h"], d["y"], pad["h"][0], pad["h"][1], sh, dh)
+    pr_w = fix_right(d["w"], d["x"], pad["w"][0], pad["w"][1], sw, dw)
+    fl, il, ol = f.get("fil_layout", "gkcyx"), f.get("in_layout", "ngchw"), f.get("out_layout", "ngkhw")
+    for name, lay in (("filter", fl), ("input", il)):          # verifyConvLayout, rocmlir-gen.cpp:974-994
+        pair = [c for c in lay if c in ("yx01" if name == "filter" else "hw01")]
+        pos = [lay.index(c) for c in pair]
+        if len(pos) != 2 or abs(pos[0] - pos[1]) != 1:
+            raise ValueError(f"unsupported {name} layout: disjointed image dimensions")
+    if len(fl.replace("g", "")) != 4:
+        raise Unsupported("3-D convolution layout")
+    cfg = ConvConfig(stride_h=sh, stride_w=sw, dil_h=dh, dil_w=dw, pad_h=pad["h"][0], pad_w=pad["w"][0], pad_h_r=pr_h,
+                     pad_w_r=pr_w, fil_layout=fl, in_layout=il, out_layout=ol, **d)
+    if "out_h" in f and int(f["out_h"]) != cfg.ho or "out_w" in f and int(f["out_w"]) != cfg.wo:
+        raise ValueError("out_h / out_w do not follow from the other sizes")
+    return cfg
+
+
+def run_conv(f: Dict[str, str], direction: int) -> List[int]:
+    from rocmlir_b200.conv import conv
+    ty = resolve_types(f)
+    cfg = conv_config(f)
+    code = ty.a
+    if code in (oracle.F8E4M3, oracle.F8E5M2) or ty.b != ty.a:
+        raise Unsupported("8-bit float convolution")
+    if code == oracle.I8 and direction != 0:
+        raise ValueError("i8 convolution is forward only")
+    out_code = oracle.I32 if code == oracle.I8 else code
+    if ty.out != out_code:
+        raise Unsupported("convolution output type differs from the input type")
+    ocfg = oracle.Conv(n=cfg.n, c=cfg.c, k=cfg.k, h=cfg.h, w=cfg.w, y=cfg.y, x=cfg.x, g=cfg.g, stride_h=cfg.stride_h,
+                       stride_w=cfg.stride_w, dil_h=cfg.dil_h, dil_w=cfg.dil_w, pad_h=cfg.pad_h, pad_w=cfg.pad_w,
+                       pad_h_r=cfg.pad_h_r, pad_w_r=cfg.pad_w_r, fil_layout=cfg.fil_layout, in_layout=cfg.in_layout,
+                       out_layout=cfg.out_layout)
+    fill = Filler(f)
+    fil_f, fil_r = fill.tensor(ocfg.numel("fil"), code)
+    in_f, in_r = fill.tensor(ocfg.numel("in"), code)
+    out_f, out_r = fill.tensor(ocfg.numel("out"), out_code)
+    threads = oracle.max_threads()
+    if code == oracle.I8:
+        want = oracle.conv_i8(ocfg, fil_r, in_r, threads=threads)
+    else:
+        want = oracle.conv_f32(ocfg, direction, fil_f, in_f, out_f, threads=threads)
+    t = {"fil": to_device(fil_r, code), "in": to_device(in_r, code), "out": to_device(out_r, out_code)}
+    res = conv(cfg, direction, t["fil"], t["in"], t["out"])
+    res_code = out_code if direction == 0 else code
+    return verdict_for(from_device(res, res_code).ravel(), want.ravel(), res_code, f)
+
+
+def run_attention(f: Dict[str, str]) -> List[int]:
+    from rocmlir_b200.attention import attention
+    ty = resolve_types(f)
+    code = ty.a
+    if code not in (oracle.F16, oracle.BF16):
+        raise Unsupported("attention kernels exist for f16 and bf16")
+    if as_bool(f, "p"):
+        g, sq, sk, d, dv = 1, 1024, 1024, 32, 32
+    else:
+        g = int(f.get("g", 1))
+        sq, sk, d, dv = int(f["seq_len_q"]), int(f["seq_len_k"]), int(f["head_dim_qk"]), int(f["head_dim_v"])
+    if d not in (64, 128) or dv not in (64, 128):
+        raise Unsupported("head dimensions other than 64 and 128")
+    if as_bool(f, "transQ") or as_bool(f, "transV") or as_bool(f, "transO"):
+        raise Unsupported("transQ / transV / transO")
+    tk = as_bool(f, "transK")
+    if not tk and sk % 8:
+        raise Unsupported("K stored G x D x Sk needs seq_len_k % 8 == 0")
+    fill = Filler(f)
+    q_f, q_r = fill.tensor(g * sq * d, code)
+    k_f, k_r = fill.tensor(g * sk * d, code)
+    v_f, v_r = fill.tensor(g * sk * dv, code)
+    sc = bi = None
+    if as_bool(f, "with-attn-scale"):
+        sc = fill.tensor(g * sq * sk, code)
+    if as_bool(f, "with-attn-bias"):
+        bi = fill.tensor(g * sq * sk, code)
+    fill.tensor(g * sq * dv, code)
+    k_shape = (g, sk, d) if tk else (g, d, sk)
+    k_log = k_f.reshape(k_shape).transpose(0, 2, 1) if tk else k_f.reshape(k_shape)   # oracle wants [G, D, Sk]
+    want = oracle.attention(q_f.reshape(g, sq, d), np.ascontiguousarray(k_log), v_f.reshape(g, sk, dv), elem_type=code,
+                            scale=None if sc is None else sc[0].reshape(g, sq, sk),
+                            bias=None if bi is None else bi[0].reshape(g, sq, sk), threads=oracle.max_threads())
+    o = attention(to_device(q_r.reshape(g, sq, d), code), to_device(k_r.reshape(k_shape), code),
+                  to_device(v_r.reshape(g, sk, dv), code), trans_k=tk,
+                  scale_tensor=None if sc is None else to_device(sc[1].reshape(g, sq, sk), code),
+                  bias=None if bi is None else to_device(bi[1].reshape(g, sq, sk), code))
+    return verdict_for(from_device(o, code).ravel(), want.ravel(), code, f)
+
+
+def run(flags: str) -> List[int]:
+    """Runs one rocmlir-gen command line; returns the verdict triple. Raises Unsupported / ValueError."""
+    import torch
+    from rocmlir_b200 import _lib as L
+    f = parse_flags(flags.replace("%arch", "sm_100a"))
+    arch = f.get("arch", "sm_100a")
+    if arch not in ("sm_100a", "sm_100"):
+        raise ValueError(f"architecture {arch} is not this hardware")
+    if "pv_with_gpu" in f or "pv_with_mlir" in f:
+        raise Unsupported("validation against a second GPU kernel: the CPU validator is the oracle here")
+    op = f.get("operation", "conv")
+    if op == "gemm":
+        v = run_gemm(f)
+    elif op in ("conv", "conv_bwd_data", "conv_bwd_weight"):
+        v = run_conv(f, {"conv": 0, "conv_bwd_data": 1, "conv_bwd_weight": 2}[op])
+    elif op == "attention":
+        v = run_attention(f)
+    else:
+        raise ValueError(f"unknown operation {op}")
+    torch.cuda.synchronize()
+    if L.kernel_status() != 0:
+        raise RuntimeError("a kernel reported a bounded-wait timeout")
+    return v
+
+
+def main(argv: List[str]) -> int:
+    try:
+        v = run(" ".join(argv))
+    except Unsupported as e:
+        print(f"unsupported: {e}", file=sys.stderr)
+        return 2
+    print("[" + " ".join(str(x) for x in v) + "]")
+    return 0 if v == [1, 1, 1] else 1
+
+
+if __name__ == "__main__":
+    sys.exit(main(sys.argv[1:]))
