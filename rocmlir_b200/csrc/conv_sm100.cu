@@ -128,6 +128,7 @@ struct ConvPlan {
   // matrices: element counts (0 = operand used as it lies)
   bool a_direct, b_direct, c_direct;
   bool a_implicit;   // forward: the A matrix is never built; the GEMM producer loads it from the NHWC input (TMA im2col)
+  bool b_implicit;   // backward weight: the same for the B matrix (K = pixels, N = (y,x,c))
   size_t a_bytes, b_bytes, c_bytes, gemm_ws;
   size_t a_off, b_off, c_off, gemm_off, total;
 };
@@ -177,6 +178,7 @@ RbStatus make_plan(const RbConvProblem* p, ConvPlan* pl) {
   RbGemmProblem& gp = pl->gemm;
   memset(&gp, 0, sizeof(gp));
   pl->a_implicit = false;
+  pl->b_implicit = false;
   gp.g = (int)G;
   gp.ab_type = t;
   gp.f32_mode = p->f32_mode;
@@ -209,6 +211,12 @@ RbStatus make_plan(const RbConvProblem* p, ConvPlan* pl) {
     pl->a_direct = out_is_mat;
     pl->b_direct = pointwise && in_is_mat;
     pl->c_direct = fil_is_mat;
+    // NHWC input, one group, 16-bit types: the im2col matrix is never built; the producer fetches its tiles from the
+    // input tensor (one im2col load per 64-channel chunk of a tile, K index = output pixel)
+    pl->b_implicit = !pl->b_direct && in_is_mat && G == 1 && t != RB_F32 && (p->c * es) % 128 == 0 &&
+                     p->pad_h < 64 && p->pad_w < 64 && (p->y - 1) * p->dil_h < 256 && (p->x - 1) * p->dil_w < 256 &&
+                     p->stride_h <= 8 && p->stride_w <= 8;
+    if (pl->b_implicit) pl->b_direct = true;
     pl->a_bytes = pl->a_direct ? 0 : (size_t)G * pix_o * p->k * es;
     pl->b_bytes = pl->b_direct ? 0 : (size_t)G * pix_o * yxc * es;
     pl->c_bytes = pl->c_direct ? 0 : (size_t)G * p->k * yxc * es;
@@ -341,6 +349,19 @@ extern "C" RbStatus rbConv(const RbConvProblem* p, void* filter, void* input, vo
     if (pl.a_direct) A = output; else { permute(output, ws + pl.a_off, osz, pl.os, act_gmat, true, es); A = ws + pl.a_off; }
     if (pl.b_direct) B = input; else { gather(input, ws + pl.b_off, false, false, ho, wo, p->c); B = ws + pl.b_off; }
     C = pl.c_direct ? filter : static_cast<void*>(ws + pl.c_off);
+    if (pl.b_implicit) {
+      ConvAOperand cv;
+      cv.operand = 1;
+      cv.tensor = input;
+      cv.N = p->n; cv.H = p->h; cv.W = p->w; cv.C = p->c;
+      cv.P = (int)ho; cv.Q = (int)wo; cv.Y = p->y; cv.X = p->x;
+      cv.stride_h = p->stride_h; cv.stride_w = p->stride_w; cv.dil_h = p->dil_h; cv.dil_w = p->dil_w;
+      cv.pad_h = p->pad_h; cv.pad_w = p->pad_w; cv.pad_h_hi = p->pad_h_r; cv.pad_w_hi = p->pad_w_r;
+      st = gemm_run(&pl.gemm, nullptr, A, nullptr, C, pl.gemm_ws ? ws + pl.gemm_off : nullptr, pl.gemm_ws, stream_v, &cv);
+      if (st != RB_SUCCESS) return st;
+      if (!pl.c_direct) permute(C, filter, fsz, pl.fs, fil_kyxc, false, es_c);
+      return RB_SUCCESS;
+    }
   } else {
     if (pl.a_direct) A = output; else { gather(output, ws + pl.a_off, true, true, p->h, p->w, p->k); A = ws + pl.a_off; }
     if (pl.a_implicit) {

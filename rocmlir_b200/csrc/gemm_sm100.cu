@@ -334,10 +334,12 @@ RbStatus rb::gemm_run(const RbGemmProblem* p, const RbEpilogue* epi, const void*
                       void* workspace, size_t workspace_bytes, void* stream_v, const ConvAOperand* conva) {
   RbStatus st = check_problem(p);
   if (st != RB_SUCCESS) return st;
+  const bool conv_a = conva && conva->operand == 0, conv_b = conva && conva->operand == 1;
   if (conva) {
-    if (p->g != 1 || p->trans_a || p->ab_type == RB_F32 || !conva->tensor)
-      return fail(RB_UNSUPPORTED, "implicit A operand: one group, K-major, 8/16-bit element types");
-    a = conva->tensor;
+    if (p->g != 1 || (conv_a && p->trans_a) || (conv_b && p->trans_b) || p->ab_type == RB_F32 || !conva->tensor)
+      return fail(RB_UNSUPPORTED, "implicit operand: one group, 8/16-bit element types, A K-major or B stored K x N");
+    if (conv_a) a = conva->tensor;
+    else b = conva->tensor;
   }
   if (!a || !b || !c) return fail(RB_INVALID_PARAM, "a, b and c must be device pointers");
   const DeviceInfo* dev = device_info();
@@ -374,11 +376,15 @@ RbStatus rb::gemm_run(const RbGemmProblem* p, const RbEpilogue* epi, const void*
   const bool is_f32 = abt == RB_F32;
   const bool split = is_f32 && p->f32_mode == 0;
   OperandPlan oa = plan_operand(p->trans_a != 0 /* A stored G x K x M */, p->m, p->k, es, is_f32, split);
-  if (conva) {  // fetched in place by im2col loads: never copied, never padded
+  if (conv_a) {  // fetched in place by im2col loads: never copied, never padded
     oa.needs_copy = false;
     oa.pitch = oa.cols;
   }
-  const OperandPlan ob = plan_operand(p->trans_b == 0 /* B stored G x K x N */, p->n, p->k, es, is_f32, split);
+  OperandPlan ob = plan_operand(p->trans_b == 0 /* B stored G x K x N */, p->n, p->k, es, is_f32, split);
+  if (conv_b) {
+    ob.needs_copy = false;
+    ob.pitch = ob.cols;
+  }
   const bool a_mn = oa.mn_major, b_mn = ob.mn_major;
   const bool epi_vec = (flags & (RB_EPI_COL_SCALE | RB_EPI_BIAS)) != 0;
   GemmConfig cfg = choose_config(p, t_variant, epi_vec);
@@ -485,9 +491,11 @@ RbStatus rb::gemm_run(const RbGemmProblem* p, const RbEpilogue* epi, const void*
   const int seg_b[3] = {0, 1, 0};
   if (conva) {
     const ConvAOperand& cv = *conva;
-    if (cv.C % bke != 0) return fail(RB_UNSUPPORTED, "implicit A operand: channels must be a multiple of the 128-byte K block");
-    if ((long long)cv.N * cv.P * cv.Q != p->m || (long long)cv.Y * cv.X * cv.C != p->k)
-      return fail(RB_INVALID_PARAM, "implicit A operand does not match the GEMM extents");
+    const int che = kRowBytes / (int)es;   // elements per 128-byte run of channels
+    if (cv.C % che != 0) return fail(RB_UNSUPPORTED, "implicit operand: channels must be a multiple of 128 bytes");
+    const long long pixels = (long long)cv.N * cv.P * cv.Q, taps = (long long)cv.Y * cv.X * cv.C;
+    if (conv_a ? (pixels != p->m || taps != p->k) : (pixels != p->k || taps != p->n))
+      return fail(RB_INVALID_PARAM, "implicit operand does not match the GEMM extents");
     const uint64_t dims[4] = {(uint64_t)cv.C, (uint64_t)cv.W, (uint64_t)cv.H, (uint64_t)cv.N};
     const uint64_t strides[3] = {(uint64_t)cv.C * es, (uint64_t)cv.W * cv.C * es, (uint64_t)cv.H * cv.W * cv.C * es};
     // bounding box of the base pixel: from -pad to (extent - 1) + upper corner, so that stepping by the stride
@@ -495,12 +503,14 @@ RbStatus rb::gemm_run(const RbGemmProblem* p, const RbEpilogue* epi, const void*
     const int lower[2] = {-cv.pad_w, -cv.pad_h};
     const int upper[2] = {cv.pad_w_hi - (cv.X - 1) * cv.dil_w, cv.pad_h_hi - (cv.Y - 1) * cv.dil_h};
     const uint32_t trav[2] = {(uint32_t)cv.stride_w, (uint32_t)cv.stride_h};
-    if (!encode_im2col_nhwc(&maps.a[0], dt, cv.tensor, dims, strides, lower, upper, (uint32_t)bke, (uint32_t)kBM, trav, &err))
-      return fail(RB_UNSUPPORTED, "A (im2col): " + err);
+    // A: a tile is 128 pixels (rows) x one K block of channels. B: a chunk is one K block of pixels x 64 channels.
+    if (!encode_im2col_nhwc(conv_a ? &maps.a[0] : &maps.b[0], dt, cv.tensor, dims, strides, lower, upper, (uint32_t)che,
+                            (uint32_t)(conv_a ? kBM : bke), trav, &err))
+      return fail(RB_UNSUPPORTED, "implicit operand (im2col): " + err);
   }
   for (int s = 0; s < nseg; ++s) {
-    if (!conva && !encode_operand(&maps.a[s], a_src[seg_a[s]], oa, kBM, &err)) return fail(RB_UNSUPPORTED, "A: " + err);
-    if (!encode_operand(&maps.b[s], b_src[seg_b[s]], ob, bn / ctas, &err)) return fail(RB_UNSUPPORTED, "B: " + err);
+    if (!conv_a && !encode_operand(&maps.a[s], a_src[seg_a[s]], oa, kBM, &err)) return fail(RB_UNSUPPORTED, "A: " + err);
+    if (!conv_b && !encode_operand(&maps.b[s], b_src[seg_b[s]], ob, bn / ctas, &err)) return fail(RB_UNSUPPORTED, "B: " + err);
   }
 
   GemmParams kp;
@@ -557,7 +567,7 @@ RbStatus rb::gemm_run(const RbGemmProblem* p, const RbEpilogue* epi, const void*
   kp.stages = stages;
   kp.probe = (t_variant >> 24) & 3;
   if (conva) {
-    kp.conva.enabled = 1; kp.conva.P = conva->P; kp.conva.Q = conva->Q; kp.conva.X = conva->X;
+    kp.conva.enabled = conv_a ? 1 : 2; kp.conva.P = conva->P; kp.conva.Q = conva->Q; kp.conva.X = conva->X;
     kp.conva.cchunks = conva->C / bke;
     kp.conva.stride_h = conva->stride_h; kp.conva.stride_w = conva->stride_w;
     kp.conva.dil_h = conva->dil_h; kp.conva.dil_w = conva->dil_w; kp.conva.pad_h = conva->pad_h; kp.conva.pad_w = conva->pad_w;

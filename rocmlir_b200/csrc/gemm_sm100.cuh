@@ -54,6 +54,8 @@ struct GemmTensorMaps {
 // A operand fetched straight from an NHWC activation tensor (implicit GEMM): row m of A is output pixel m
 // (n, p, q in row-major order), column (y, x, c) is in[n][p*stride + y*dil - pad][q*stride + x*dil - pad][c].
 // One K block = one 128-byte run of channels of one filter tap.
+// enabled == 2: the same for the B operand of a backward-weight convolution: K index = output pixel, column
+// (y, x, c) = N index; one 64-element chunk of an MN-major B tile = one 128-byte run of channels of one tap.
 struct ConvAParams {
   int enabled;
   int P, Q;             // output image
@@ -95,6 +97,24 @@ struct GemmParams {
   int probe;                  // instrumentation (results become meaningless): bit0 = no loads, bit1 = no epilogue work
   int stages;                 // shared-memory ring depth (<= GemmSmemLayout::kMaxStages)
 };
+
+// Implicit B operand: base coordinates of output pixel `pix` (row-major n, p, q) and the tap / channel chunk of
+// column `col`. Columns past the end of the matrix fetch tap 0 (their results are never stored).
+__device__ __forceinline__ void convb_pixel(const ConvAParams& cv, int pix, int& img, int& base_h, int& base_w) {
+  const int pq = cv.P * cv.Q;
+  img = pix / pq;
+  const int rem = pix - img * pq;
+  const int op = rem / cv.Q;
+  base_h = op * cv.stride_h - cv.pad_h;
+  base_w = (rem - op * cv.Q) * cv.stride_w - cv.pad_w;
+}
+__device__ __forceinline__ void convb_tap(const ConvAParams& cv, int col, int ncols, int che, int& cc, int& fy, int& fx) {
+  const int chunk = (col < ncols) ? col / che : 0;
+  const int tap = chunk / cv.cchunks;
+  cc = chunk - tap * cv.cchunks;
+  fy = tap / cv.X;
+  fx = tap - fy * cv.X;
+}
 
 template <int CTAS>
 struct GemmSmemLayout {
@@ -256,7 +276,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
         const int kb_begin = w.kb_begin, kb_end = w.kb_end;
         const int ktotal = (kb_end - kb_begin) * p.nseg;
         int img = 0, base_h = 0, base_w = 0;
-        if (p.conva.enabled) {
+        if (p.conva.enabled == 1) {
           const int pq = p.conva.P * p.conva.Q;
           img = m0 / pq;
           const int rem = m0 - img * pq;
@@ -276,7 +296,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
             if (CTAS == 1 || rank == 0) mbar_arrive(&full_bar[s]);
           } else if constexpr (CTAS == 1) {
             mbar_expect_tx(&full_bar[s], stage_bytes);
-            if (!A_MN && p.conva.enabled) {
+            if (!A_MN && p.conva.enabled == 1) {
               const int tap = kb / p.conva.cchunks, cc = kb - tap * p.conva.cchunks;
               const int fy = tap / p.conva.X, fx = tap - fy * p.conva.X;
               tma_load_im2col_4d(sa, &maps.a[seg], &full_bar[s], cc * BKE, base_w, base_h, img,
@@ -292,6 +312,15 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
             }
             if constexpr (!B_MN) {
               tma_load_3d(sb, &maps.b[seg], &full_bar[s], k0, n0, g);
+            } else if (p.conva.enabled == 2) {
+              int bi, bh, bw;
+              convb_pixel(p.conva, k0, bi, bh, bw);
+              for (int c = 0; c < bn_cta / CHE; ++c) {
+                int cc, fy, fx;
+                convb_tap(p.conva, n0 + c * CHE, p.N, CHE, cc, fy, fx);
+                tma_load_im2col_4d(sb + c * CHUNK_BYTES, &maps.b[seg], &full_bar[s], cc * CHE, bw, bh, bi,
+                                   (uint16_t)(fx * p.conva.dil_w), (uint16_t)(fy * p.conva.dil_h));
+              }
             } else if (p.b_fused) {
               tma_load_4d(sb, &maps.b[seg], &full_bar[s], 0, k0, n0 / CHE, g);
             } else {
@@ -302,7 +331,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
             // Completion of this CTA's loads is counted on the leader CTA's barrier.
             const uint32_t lead_full = mapa_u32(smem_u32(&full_bar[s]), 0);
             if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * stage_bytes);
-            if (!A_MN && p.conva.enabled) {
+            if (!A_MN && p.conva.enabled == 1) {
               const int tap = kb / p.conva.cchunks, cc = kb - tap * p.conva.cchunks;
               const int fy = tap / p.conva.X, fx = tap - fy * p.conva.X;
               tma_load_im2col_4d_bar(sa, &maps.a[seg], lead_full, cc * BKE, base_w, base_h, img,
@@ -318,6 +347,15 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
             }
             if constexpr (!B_MN) {
               tma_load_3d_bar(sb, &maps.b[seg], lead_full, k0, n0, g);
+            } else if (p.conva.enabled == 2) {
+              int bi, bh, bw;
+              convb_pixel(p.conva, k0, bi, bh, bw);
+              for (int c = 0; c < bn_cta / CHE; ++c) {
+                int cc, fy, fx;
+                convb_tap(p.conva, n0 + c * CHE, p.N, CHE, cc, fy, fx);
+                tma_load_im2col_4d_bar(sb + c * CHUNK_BYTES, &maps.b[seg], lead_full, cc * CHE, bw, bh, bi,
+                                       (uint16_t)(fx * p.conva.dil_w), (uint16_t)(fy * p.conva.dil_h));
+              }
             } else if (p.b_fused) {
               tma_load_4d_bar(sb, &maps.b[seg], lead_full, 0, k0, n0 / CHE, g);
             } else {

@@ -38,6 +38,8 @@ bool encode_im2col_nhwc(CUtensorMap* out, CUtensorMapDataType dt, const void* ba
 
 // Implicit-GEMM description of the A operand for gemm_run: the activation tensor of a convolution.
 struct ConvAOperand {
+  int operand = 0;           // 0: the A operand (GEMM M = N*P*Q, K = Y*X*C). 1: the B operand of a backward-weight
+                             // convolution (GEMM K = N*P*Q, N = Y*X*C; B stored K x N, i.e. trans_b = 0)
   const void* tensor;        // NHWC (dense), element type = the GEMM's ab_type
   int N, H, W, C;            // tensor extents
   int P, Q;                  // output image (GEMM M = N * P * Q)
@@ -46,7 +48,7 @@ struct ConvAOperand {
   int pad_h, pad_w;          // base pixel of output (p, q) = (p*stride_h - pad_h, q*stride_w - pad_w); may be negative pads
   int pad_h_hi, pad_w_hi;    // upper paddings (bounding box of the base pixel)
 };
-// rbGemm with an optional implicit A operand (then `a` is ignored, trans_a must be 0, g must be 1).
+// rbGemm with an optional implicit operand (then `a` (or `b`) is ignored, trans_a (trans_b) must be 0, g must be 1).
 RbStatus gemm_run(const RbGemmProblem* p, const RbEpilogue* epi, const void* a, const void* b, void* c, void* workspace,
                   size_t workspace_bytes, void* stream, const ConvAOperand* conva);
 
