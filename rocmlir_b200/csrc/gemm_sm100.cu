@@ -541,7 +541,7 @@ RbStatus rb::gemm_run(const RbGemmProblem* p, const RbEpilogue* epi, const void*
     kp.c_stride_g = (long long)p->m * p->n;
     kp.split_stride = (long long)p->g * p->m * p->n;
     kp.vec_ok = (p->n % 4 == 0) ? 1 : 0;
-    kp.c_tma = 0;
+    kp.c_tma = (kp.vec_ok && !cfg.plain_stores) ? 1 : 0;   // planes are stored like a C of splits * g groups
   } else {
     kp.c = c;
     kp.c_type = p->c_type;
@@ -552,20 +552,22 @@ RbStatus rb::gemm_run(const RbGemmProblem* p, const RbEpilogue* epi, const void*
     kp.epi = ep;
   }
   if (kp.c_tma) {
-    const CUtensorMapDataType cdt = p->c_type == RB_F16    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
-                                    : p->c_type == RB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
-                                    : p->c_type == RB_F32  ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
-                                    : p->c_type == RB_I32  ? CU_TENSOR_MAP_DATA_TYPE_INT32
-                                                           : CU_TENSOR_MAP_DATA_TYPE_UINT8;
-    const uint64_t cdims[3] = {(uint64_t)p->n, (uint64_t)p->m, (uint64_t)p->g};
-    const uint64_t cstrides[2] = {(uint64_t)p->n * es_c, (uint64_t)p->m * p->n * es_c};
-    const uint32_t cbox[3] = {(uint32_t)(kRowBytes / es_c), 32u, 1u};
-    if (!encode_tiled(&maps.c, cdt, 3, c, cdims, cstrides, cbox, CU_TENSOR_MAP_SWIZZLE_128B, &err))
+    const int st_type = kp.c_type;                      // what the kernel stores: C's type, or raw planes
+    const size_t es_st = dtype_bytes(st_type);
+    const CUtensorMapDataType cdt = st_type == RB_F16    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                    : st_type == RB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                    : st_type == RB_F32  ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                    : st_type == RB_I32  ? CU_TENSOR_MAP_DATA_TYPE_INT32
+                                                         : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+    const uint64_t cdims[3] = {(uint64_t)p->n, (uint64_t)p->m, (uint64_t)p->g * splits};
+    const uint64_t cstrides[2] = {(uint64_t)p->n * es_st, (uint64_t)p->m * p->n * es_st};
+    const uint32_t cbox[3] = {(uint32_t)(kRowBytes / es_st), 32u, 1u};
+    if (!encode_tiled(&maps.c, cdt, 3, kp.c, cdims, cstrides, cbox, CU_TENSOR_MAP_SWIZZLE_128B, &err))
       return fail(RB_UNSUPPORTED, "C: " + err);
   }
   kp.status = dev->status_word;
   kp.stages = stages;
-  kp.probe = (t_variant >> 24) & 3;
+  kp.probe = (t_variant >> 24) & 7;
   if (conva) {
     kp.conva.enabled = conv_a ? 1 : 2; kp.conva.P = conva->P; kp.conva.Q = conva->Q; kp.conva.X = conva->X;
     kp.conva.cchunks = conva->C / bke;

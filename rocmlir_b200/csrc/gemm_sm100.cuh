@@ -94,7 +94,8 @@ struct GemmParams {
   unsigned int sk_token;       // unique per launch, so stale words of earlier launches never match
   ConvAParams conva;
   int a_fused, b_fused;       // MN-major operand loaded with one 4-D box per stage (extent a multiple of the chunk)
-  int probe;                  // instrumentation (results become meaningless): bit0 = no loads, bit1 = no epilogue work
+  int probe;                  // instrumentation (results become meaningless): bit0 = no loads, bit1 = no epilogue work,
+                              // bit2 = epilogue without its global stores
   int stages;                 // shared-memory ring depth (<= GemmSmemLayout::kMaxStages)
 };
 
@@ -432,7 +433,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
           ready = next_ready;
         }
         if (!ok) break;
-        if (p.trace && t < 7) p.trace[blockIdx.x * 16 + 8 + t] = (unsigned long long)w_full;  // cumulative, per tile
+        if (p.trace && t < 5) p.trace[blockIdx.x * 16 + 8 + t] = (unsigned long long)w_full;  // cumulative, per tile
         if constexpr (CTAS == 1) {
           tc_commit<1>(&tfull_bar[buf]);
         } else {
@@ -459,7 +460,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
     const bool raw_i32 = p.acc_is_int && p.c_type == RB_I32 && p.epi.flags == 0;
     uint8_t* my_staging = staging + q * 2 * L::kStoreTileBytes;
     uint32_t t = 0, nstores = 0;
-    long long w_tfull = 0, e_work = 0;
+    long long w_tfull = 0, e_work = 0, e_ld = 0, e_cv = 0;
     WorkIter it(p, pair_id, num_pairs);
     WorkItem w;
     for (; it.next(w); ++t) {
@@ -476,6 +477,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
       const long long row = row0 + lane;
       const bool row_ok = row < p.M;
       const int ngroups = p.bn / 32;
+      const int gz = w.split * p.G + g;   // group coordinate of the store map (K-split planes are stacked groups)
       // Per-column scales / biases of this tile, converted to f32, in this warp's private copy.
       float* vec_scale = epi_vecs + q * (2 * kMaxBN);
       float* vec_bias = vec_scale + kMaxBN;
@@ -510,14 +512,97 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
         __threadfence();
         if (!got) break;
       }
+      // Fast path (whole tiles, float accumulators, no fused elementwise work, 16-bit C through TMA stores): a
+      // compact loop - 64 columns = one 128-byte staging row per step. The general loop below handles every other
+      // case; keeping this one small matters because the general loop's code is far larger than the instruction
+      // cache and ran at about 1400 cycles per 32 columns where this one needs about 150.
+      const bool fast16 = w.kind == 0 && p.c_tma && p.epi.flags == 0 && !p.acc_is_int && !p.probe &&
+                          (p.c_type == RB_F16 || p.c_type == RB_BF16);
+      // 4-byte C (f32 results, raw i32 results, the raw planes of a K split): 32 columns = one staging row per step
+      const bool fast32 = w.kind == 0 && p.c_tma && !p.probe &&
+                          ((p.epi.flags == 0 && !p.acc_is_int && p.c_type == RB_F32) || raw_i32);
+      if (fast16) {
+        const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + buf * kMaxBN;
+        const int nsteps = p.bn / 64;
 #pragma unroll 1
-      for (int c = 0; c < ngroups; ++c) {
+        for (int cp = 0; cp < nsteps; ++cp) {
+          const int n0 = nb * p.bn + cp * 64;
+          if (n0 >= p.N) break;  // warp-uniform
+          uint32_t v[64];
+          tmem_ld32(taddr + cp * 64, v);
+          tmem_ld32(taddr + cp * 64 + 32, v + 32);
+          uint8_t* stg = my_staging + (nstores & 1u) * L::kStoreTileBytes;
+          if (lane == 0 && nstores >= 2) bulk_wait_read<1>();  // the store that last used this buffer has read it
+          __syncwarp();
+          tmem_ld_wait();
+          uint8_t* rowp = stg + lane * kRowBytes;
+          if (p.c_type == RB_F16) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              uint32_t h[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                __half2 t2 = __floats2half2_rn(__uint_as_float(v[8 * i + 2 * j]), __uint_as_float(v[8 * i + 2 * j + 1]));
+                h[j] = *reinterpret_cast<uint32_t*>(&t2);
+              }
+              *reinterpret_cast<uint4*>(rowp + ((i ^ (lane & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              uint32_t h[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                __nv_bfloat162 t2 = __floats2bfloat162_rn(__uint_as_float(v[8 * i + 2 * j]), __uint_as_float(v[8 * i + 2 * j + 1]));
+                h[j] = *reinterpret_cast<uint32_t*>(&t2);
+              }
+              *reinterpret_cast<uint4*>(rowp + ((i ^ (lane & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
+            }
+          }
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0 && row0 < p.M) {
+            tma_store_3d(&maps.c, stg, n0, (int)row0, gz);
+            bulk_commit();
+          }
+          ++nstores;
+        }
+      } else if (fast32) {
+        const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + buf * kMaxBN;
+#pragma unroll 1
+        for (int c = 0; c < ngroups; ++c) {
+          const int n0 = nb * p.bn + c * 32;
+          if (n0 >= p.N) break;  // warp-uniform
+          uint32_t v[32];
+          tmem_ld32(taddr + c * 32, v);
+          uint8_t* stg = my_staging + (nstores & 1u) * L::kStoreTileBytes;
+          if (lane == 0 && nstores >= 2) bulk_wait_read<1>();
+          __syncwarp();
+          tmem_ld_wait();
+          uint8_t* rowp = stg + lane * kRowBytes;
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            *reinterpret_cast<uint4*>(rowp + ((i ^ (lane & 7)) << 4)) = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0 && row0 < p.M) {
+            tma_store_3d(&maps.c, stg, n0, (int)row0, gz);
+            bulk_commit();
+          }
+          ++nstores;
+        }
+      }
+#pragma unroll 1
+      for (int c = 0; c < ngroups && !fast16 && !fast32; ++c) {
         const int n0 = nb * p.bn + c * 32;
         if (n0 >= p.N) break;  // warp-uniform
         if (p.probe & 2) break;
         uint32_t v[32];
+        const long long tl0 = p.trace ? clock64() : 0;
         tmem_ld32(tmem_base + (uint32_t(q * 32) << 16) + buf * kMaxBN + c * 32, v);
         tmem_ld_wait();
+        const long long tl1 = p.trace ? clock64() : 0;
+        e_ld += tl1 - tl0;
         if (w.kind == 2) {  // contributor: raw accumulators to this unit's partial tile
 #pragma unroll
           for (int i = 0; i < 8; ++i) *sk_word(pair_id, c, i) = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
@@ -566,6 +651,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
             }
           }
         }
+        if (p.trace) e_cv += clock64() - tl1;
         if (p.c_tma) {
           // Stage 32 rows x 128 bytes per store: row `lane` at lane * 128, its 16-byte pieces XOR-swizzled with
           // (lane & 7) exactly as the 128-byte-swizzled store map expects (also free of bank conflicts).
@@ -586,13 +672,13 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
           if (last_group) {
             fence_proxy_async();
             __syncwarp();
-            if (lane == 0 && row0 < p.M) {
-              tma_store_3d(&maps.c, stg, n0 - sub * 32, (int)row0, g);
+            if (lane == 0 && row0 < p.M && !(p.probe & 4)) {
+              tma_store_3d(&maps.c, stg, n0 - sub * 32, (int)row0, gz);
               bulk_commit();
             }
             ++nstores;
           }
-        } else if (nw > 0 && row_ok) {
+        } else if (nw > 0 && row_ok && !(p.probe & 4)) {
           if (p.vec_ok && n0 + 32 <= p.N) {
             uint4* d = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.c) + (c_row_off + n0) * es_c);
 #pragma unroll
@@ -624,6 +710,8 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
     if (p.trace && warp == 4 && lane == 0) {
       p.trace[blockIdx.x * 16 + 6] = (unsigned long long)w_tfull;
       p.trace[blockIdx.x * 16 + 7] = (unsigned long long)e_work;
+      p.trace[blockIdx.x * 16 + 13] = (unsigned long long)e_ld;   // of e_work: TMEM loads
+      p.trace[blockIdx.x * 16 + 14] = (unsigned long long)e_cv;   //            conversion / fused elementwise / packing
     }
   }
 
