@@ -592,8 +592,51 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
           ++nstores;
         }
       }
+      // Fused elementwise work (or 1-byte / converted outputs) on whole tiles through TMA stores: the general loop's
+      // body without its stream-K and plain-store branches.
+      const bool fast_epi = !fast16 && !fast32 && w.kind == 0 && p.c_tma && !p.probe && !raw_i32;
+      if (fast_epi) {
+        const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + buf * kMaxBN;
 #pragma unroll 1
-      for (int c = 0; c < ngroups && !fast16 && !fast32; ++c) {
+        for (int c = 0; c < ngroups; ++c) {
+          const int n0 = nb * p.bn + c * 32;
+          if (n0 >= p.N) break;  // warp-uniform
+          uint32_t v[32];
+          tmem_ld32(taddr + c * 32, v);
+          const int sub = c % groups_per_store;
+          uint8_t* stg = my_staging + (nstores & 1u) * L::kStoreTileBytes;
+          if (sub == 0) {
+            if (lane == 0 && nstores >= 2) bulk_wait_read<1>();
+            __syncwarp();
+          }
+          tmem_ld_wait();
+          float x[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) x[j] = p.acc_is_int ? __int2float_rn((int)v[j]) : __uint_as_float(v[j]);
+          if (p.epi.flags) epi_apply32(x, p.epi, vec_scale + c * 32, vec_bias + c * 32);
+          uint4 w4[8];
+          const int nw = pack_row32(x, p.c_type, w4);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            if (i < nw) {
+              const int piece = sub * nw + i;
+              *reinterpret_cast<uint4*>(stg + lane * kRowBytes + ((piece ^ (lane & 7)) << 4)) = w4[i];
+            }
+          }
+          const bool last_group = (sub == groups_per_store - 1) || (n0 + 32 >= p.N) || (c == ngroups - 1);
+          if (last_group) {
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0 && row0 < p.M) {
+              tma_store_3d(&maps.c, stg, n0 - sub * 32, (int)row0, gz);
+              bulk_commit();
+            }
+            ++nstores;
+          }
+        }
+      }
+#pragma unroll 1
+      for (int c = 0; c < ngroups && !fast16 && !fast32 && !fast_epi; ++c) {
         const int n0 = nb * p.bn + c * 32;
         if (n0 >= p.N) break;  // warp-uniform
         if (p.probe & 2) break;
