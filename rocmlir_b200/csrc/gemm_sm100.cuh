@@ -378,7 +378,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
     if (lane_id() == 0 && rank == 0) {
       uint32_t s = 0, ph = 0, t = 0;
       bool ok = true;
-      long long w_full = 0, w_tempty = 0;
+      long long w_full = 0, w_tempty = 0, t_kloop = 0;
       const long long t_begin = p.trace ? clock64() : 0;
       unsigned long long ns_begin = 0;
       if (p.trace) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns_begin));
@@ -404,13 +404,15 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
         const uint32_t tmem_d = tmem_base + buf * kMaxBN;
         uint32_t accum = 0;
         const int ktotal = (w.kb_end - w.kb_begin) * p.nseg;
+        const long long tk0 = p.trace ? clock64() : 0;
         for (int kk = 0; kk < ktotal; ++kk) {
           if (!ready) {
             const long long tw = p.trace ? clock64() : 0;
             if (!mbar_wait(&full_bar[s], ph, p.status, kStatusTimeoutMma + s)) { ok = false; break; }
             if (p.trace) w_full += clock64() - tw;
           }
-          tc_fence_after();
+          // no tcgen05 fence here: the operands arrive through the async proxy (TMA) and are ordered by the
+          // barrier itself; the fence after the accumulator-buffer wait above orders the TMEM accesses
           uint32_t ns = s + 1, nph = ph;
           if (ns == (uint32_t)stages) { ns = 0; nph ^= 1u; }
           const bool next_ready = mbar_test_wait_addr(full0 + ns * 8, nph);  // consumed after the MMAs below
@@ -433,7 +435,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
           ready = next_ready;
         }
         if (!ok) break;
-        if (p.trace && t < 5) p.trace[blockIdx.x * 16 + 8 + t] = (unsigned long long)w_full;  // cumulative, per tile
+        if (p.trace) t_kloop += clock64() - tk0;
         if constexpr (CTAS == 1) {
           tc_commit<1>(&tfull_bar[buf]);
         } else {
@@ -445,6 +447,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
         p.trace[blockIdx.x * 16 + 3] = (unsigned long long)w_tempty;
         p.trace[blockIdx.x * 16 + 4] = (unsigned long long)(clock64() - t_begin);  // MMA issue loop, total
         p.trace[blockIdx.x * 16 + 5] = t;
+        p.trace[blockIdx.x * 16 + 8] = (unsigned long long)t_kloop;   // of the total: inside the K loops
         unsigned long long ns_end;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns_end));
         p.trace[blockIdx.x * 16 + 15] = ns_end - ns_begin;  // the same loop in nanoseconds (gives the SM clock)
