@@ -33,7 +33,7 @@ BYTES_PER_GEMM = 3 * M * N * 2                        # each operand read once, 
 METRIC = "TFLOP/s, fp16 GEMM M=N=K=4096 (rock.gemm, f32 accumulate, f16 out)"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of gemm_tcgen05_kernel on this workload, from the
 # ncu capture summarised in profiles/gemm_f16_4096_ncu.md (89.3 MB read + 15.6 MB written).
-NCU_DRAM_BYTES_PER_LAUNCH = 104.97e6
+NCU_DRAM_BYTES_PER_LAUNCH = 104.32e6
 
 
 def measured_peaks():
