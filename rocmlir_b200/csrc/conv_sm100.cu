@@ -63,40 +63,82 @@ struct GatherParams {
 
 template <int ES>
 __global__ void conv_gather_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, GatherParams g) {
-  const long long cols = g.Y * g.X * g.CH;
-  const long long rows = g.N * g.P * g.Q;
-  const long long total = g.G * rows * g.pitch;
+  // Rows, columns and every per-tensor extent fit 32 bits (checked by the plan); only the flat index is 64-bit, so
+  // all but the first division are 32-bit.
+  const unsigned cols = (unsigned)(g.Y * g.X * g.CH), pitch = (unsigned)g.pitch;
+  const unsigned rows = (unsigned)(g.N * g.P * g.Q);
+  const unsigned CH = (unsigned)g.CH, X = (unsigned)g.X, Q = (unsigned)g.Q, P = (unsigned)g.P;
+  const long long total = g.G * (long long)rows * pitch;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
-    const long long col = i % g.pitch;
-    long long r = i / g.pitch;
-    const long long row = r % rows;
-    const long long grp = r / rows;
+    const unsigned col = (unsigned)(i % pitch);
+    const unsigned long long r = (unsigned long long)(i / pitch);
+    const unsigned row = (unsigned)(r % rows);
+    const unsigned grp = (unsigned)(r / rows);
     bool ok = col < cols;
     long long off = 0;
     if (ok) {
-      const long long ch = col % g.CH;
-      const long long t = col / g.CH;
-      const long long x = t % g.X, y = t / g.X;
-      const long long q = row % g.Q;
-      const long long t2 = row / g.Q;
-      const long long pp = t2 % g.P, n = t2 / g.P;
-      long long a, b;
+      const unsigned ch = col % CH, t = col / CH;
+      const unsigned x = t % X, y = t / X;
+      const unsigned q = row % Q, t2 = row / Q;
+      const unsigned pp = t2 % P, n = t2 / P;
+      int a, b;
       if (!g.transposed) {
-        a = pp * g.stride_h + y * g.dil_h - g.pad_h;
-        b = q * g.stride_w + x * g.dil_w - g.pad_w;
+        a = (int)(pp * (unsigned)g.stride_h + y * (unsigned)g.dil_h) - (int)g.pad_h;
+        b = (int)(q * (unsigned)g.stride_w + x * (unsigned)g.dil_w) - (int)g.pad_w;
       } else {
-        const long long ta = pp + g.pad_h - y * g.dil_h, tb = q + g.pad_w - x * g.dil_w;
-        ok = ta >= 0 && tb >= 0 && ta % g.stride_h == 0 && tb % g.stride_w == 0;
-        a = ta / g.stride_h;
-        b = tb / g.stride_w;
+        const int ta = (int)pp + (int)g.pad_h - (int)(y * (unsigned)g.dil_h), tb = (int)q + (int)g.pad_w - (int)(x * (unsigned)g.dil_w);
+        ok = ta >= 0 && tb >= 0 && ta % (int)g.stride_h == 0 && tb % (int)g.stride_w == 0;
+        a = ta / (int)g.stride_h;
+        b = tb / (int)g.stride_w;
       }
-      ok = ok && a >= 0 && a < g.A && b >= 0 && b < g.B;
-      off = n * g.s_n + grp * g.s_g + ch * g.s_ch + a * g.s_a + b * g.s_b;
+      ok = ok && a >= 0 && a < (int)g.A && b >= 0 && b < (int)g.B;
+      off = (long long)n * g.s_n + (long long)grp * g.s_g + (long long)ch * g.s_ch + (long long)a * g.s_a + (long long)b * g.s_b;
     }
     if (ES == 1) dst[i] = ok ? src[off] : (uint8_t)0;
     if (ES == 2) reinterpret_cast<uint16_t*>(dst)[i] = ok ? reinterpret_cast<const uint16_t*>(src)[off] : (uint16_t)0;
     if (ES == 4) reinterpret_cast<uint32_t*>(dst)[i] = ok ? reinterpret_cast<const uint32_t*>(src)[off] : 0u;
+  }
+}
+
+// The same gather for channel-contiguous sources (NHWC-like: s_ch == 1): one 16-byte vector of channels per thread
+// and iteration, index arithmetic once per vector and in 32 bits after the first division. Requires CH * ES and the
+// row pitch to be multiples of 16 bytes and 16-byte aligned buffers.
+template <int ES>
+__global__ void conv_gather_vec_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, GatherParams g) {
+  constexpr int VE = 16 / ES;                      // elements per vector
+  const unsigned pitch_v = (unsigned)(g.pitch / VE), chv = (unsigned)(g.CH / VE);
+  const unsigned rows = (unsigned)(g.N * g.P * g.Q);
+  const unsigned X = (unsigned)g.X, Q = (unsigned)g.Q, P = (unsigned)g.P;
+  const long long total = g.G * (long long)rows * pitch_v;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const unsigned colv = (unsigned)(i % pitch_v);
+    const unsigned long long r = (unsigned long long)(i / pitch_v);
+    const unsigned row = (unsigned)(r % rows);
+    const unsigned grp = (unsigned)(r / rows);
+    const unsigned cv = colv % chv, t = colv / chv;
+    const unsigned x = t % X, y = t / X;
+    const unsigned q = row % Q, t2 = row / Q;
+    const unsigned pp = t2 % P, n = t2 / P;
+    int a, b;
+    bool ok = true;
+    if (!g.transposed) {
+      a = (int)(pp * (unsigned)g.stride_h + y * (unsigned)g.dil_h) - (int)g.pad_h;
+      b = (int)(q * (unsigned)g.stride_w + x * (unsigned)g.dil_w) - (int)g.pad_w;
+    } else {
+      const int ta = (int)pp + (int)g.pad_h - (int)(y * (unsigned)g.dil_h), tb = (int)q + (int)g.pad_w - (int)(x * (unsigned)g.dil_w);
+      ok = ta >= 0 && tb >= 0 && ta % (int)g.stride_h == 0 && tb % (int)g.stride_w == 0;
+      a = ta / (int)g.stride_h;
+      b = tb / (int)g.stride_w;
+    }
+    ok = ok && a >= 0 && a < (int)g.A && b >= 0 && b < (int)g.B;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (ok) {
+      const long long off = (long long)n * g.s_n + (long long)grp * g.s_g + (long long)cv * VE + (long long)a * g.s_a + (long long)b * g.s_b;
+      v = __ldg(reinterpret_cast<const uint4*>(src + off * ES));
+    }
+    reinterpret_cast<uint4*>(dst)[i] = v;
   }
 }
 
@@ -318,8 +360,17 @@ extern "C" RbStatus rbConv(const RbConvProblem* p, void* filter, void* input, vo
     g.stride_h = p->stride_h; g.stride_w = p->stride_w; g.dil_h = p->dil_h; g.dil_w = p->dil_w;
     g.pad_h = p->pad_h; g.pad_w = p->pad_w;
     g.transposed = transposed ? 1 : 0;
-    launch_es(es, blocks, stream, conv_gather_kernel<1>, conv_gather_kernel<2>, conv_gather_kernel<4>,
-              static_cast<const uint8_t*>(src), dst, g);
+    const bool vec = g.s_ch == 1 && (g.CH * (long long)es) % 16 == 0 && (g.pitch * (long long)es) % 16 == 0 &&
+                     (g.s_n * (long long)es) % 16 == 0 && (g.s_g * (long long)es) % 16 == 0 &&
+                     (g.s_a * (long long)es) % 16 == 0 && (g.s_b * (long long)es) % 16 == 0 &&
+                     reinterpret_cast<uintptr_t>(src) % 16 == 0 && reinterpret_cast<uintptr_t>(dst) % 16 == 0 &&
+                     g.N * g.P * g.Q < 0x7fffffffLL && g.pitch < 0x7fffffffLL;
+    if (vec)
+      launch_es(es, blocks, stream, conv_gather_vec_kernel<1>, conv_gather_vec_kernel<2>, conv_gather_vec_kernel<4>,
+                static_cast<const uint8_t*>(src), dst, g);
+    else
+      launch_es(es, blocks, stream, conv_gather_kernel<1>, conv_gather_kernel<2>, conv_gather_kernel<4>,
+                static_cast<const uint8_t*>(src), dst, g);
     count_launch();
   };
   auto permute = [&](const void* src, void* dst, const long long* sizes, const long long* strides, const int* order,
