@@ -33,6 +33,29 @@ struct Dims5 {
 template <int ES>
 __global__ void permute5_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, Dims5 d, int to_dense) {
   const long long total = d.size[0] * d.size[1] * d.size[2] * d.size[3] * d.size[4];
+  if (total <= 0xffffffffLL) {
+    // the usual case: 32-bit index arithmetic (64-bit divisions cost an order of magnitude more)
+    const unsigned n = (unsigned)total;
+    const unsigned s0 = (unsigned)d.size[0], s1 = (unsigned)d.size[1], s2 = (unsigned)d.size[2], s3 = (unsigned)d.size[3],
+                   s4 = (unsigned)d.size[4];
+    (void)s0;
+    for (unsigned long long i64 = blockIdx.x * (unsigned long long)blockDim.x + threadIdx.x; i64 < n;
+         i64 += (unsigned long long)gridDim.x * blockDim.x) {
+      const unsigned i = (unsigned)i64;
+      unsigned r = i;
+      const unsigned i4 = r % s4; r /= s4;
+      const unsigned i3 = r % s3; r /= s3;
+      const unsigned i2 = r % s2; r /= s2;
+      const unsigned i1 = r % s1; r /= s1;
+      const long long off = (long long)r * d.stride[0] + (long long)i1 * d.stride[1] + (long long)i2 * d.stride[2] +
+                            (long long)i3 * d.stride[3] + (long long)i4 * d.stride[4];
+      const long long s = to_dense ? off : (long long)i, t = to_dense ? (long long)i : off;
+      if (ES == 1) dst[t] = src[s];
+      if (ES == 2) reinterpret_cast<uint16_t*>(dst)[t] = reinterpret_cast<const uint16_t*>(src)[s];
+      if (ES == 4) reinterpret_cast<uint32_t*>(dst)[t] = reinterpret_cast<const uint32_t*>(src)[s];
+    }
+    return;
+  }
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
     long long r = i, off = 0;
@@ -171,6 +194,8 @@ struct ConvPlan {
   bool a_direct, b_direct, c_direct;
   bool a_implicit;   // forward: the A matrix is never built; the GEMM producer loads it from the NHWC input (TMA im2col)
   bool b_implicit;   // backward weight: the same for the B matrix (K = pixels, N = (y,x,c))
+  int a_planes;      // f32 forward implicit GEMM: TF32 planes of the input kept in the workspace (0, 1 or 2)
+  bool a_nchw;       //   the input is NCHW: the plane pass transposes it to NHWC
   size_t a_bytes, b_bytes, c_bytes, gemm_ws;
   size_t a_off, b_off, c_off, gemm_off, total;
 };
@@ -239,11 +264,23 @@ RbStatus make_plan(const RbConvProblem* p, ConvPlan* pl) {
     pl->c_direct = out_is_mat;
     // NHWC input, one group, channels a multiple of the 128-byte K block, 8/16-bit types: implicit GEMM.
     // Corner / offset fields of the im2col descriptor are small signed integers; stay well inside them.
-    pl->a_implicit = !pl->a_direct && in_is_mat && G == 1 && t != RB_F32 && (p->c * es) % 128 == 0 &&
+    // f32: the same over TF32 planes of the input (hi, and lo in accurate mode) in NHWC order, built by one pass
+    // over the input - a transposing pass when the input is NCHW - instead of an im2col matrix Y*X times its size.
+    const int act_nchw[5] = {0, 1, 2, 3, 4};
+    const bool in_is_nchw = is_dense_in_order(pl->is, isz, act_nchw, 5);
+    const bool in_ok = (t != RB_F32) ? in_is_mat : (in_is_mat || in_is_nchw);
+    pl->a_implicit = !pl->a_direct && in_ok && G == 1 && (p->c * es) % 128 == 0 &&
                      p->pad_h < 64 && p->pad_w < 64 && (p->y - 1) * p->dil_h < 256 && (p->x - 1) * p->dil_w < 256 &&
-                     p->stride_h <= 8 && p->stride_w <= 8;
+                     p->stride_h <= 8 && p->stride_w <= 8 && pix_i < 0x7fffffffLL;
+    pl->a_planes = 0;
+    pl->a_nchw = false;
+    if (pl->a_implicit && t == RB_F32) {
+      pl->a_nchw = !in_is_mat;
+      pl->a_planes = p->f32_mode == 0 ? 2 : (in_is_mat ? 0 : 1);
+    }
     if (pl->a_implicit) pl->a_direct = true;   // nothing to gather
-    pl->a_bytes = pl->a_direct ? 0 : (size_t)G * pix_o * yxc * es;
+    pl->a_bytes = pl->a_implicit ? (size_t)pl->a_planes * up256((size_t)pix_i * p->c * es)
+                                 : (pl->a_direct ? 0 : (size_t)G * pix_o * yxc * es);
     pl->b_bytes = pl->b_direct ? 0 : (size_t)G * p->k * yxc * es;
     pl->c_bytes = pl->c_direct ? 0 : (size_t)G * pix_o * p->k * es_o;
   } else if (p->direction == 2) {
@@ -290,7 +327,7 @@ RbStatus make_plan(const RbConvProblem* p, ConvPlan* pl) {
   if ((long long)gp.m != (p->direction == 0 ? pix_o : p->direction == 2 ? (long long)p->k : pix_i) ||
       pix_o > 0x7fffffffLL || pix_i > 0x7fffffffLL || yxc > 0x7fffffffLL || yxk > 0x7fffffffLL)
     return fail(RB_UNSUPPORTED, "GEMM extent exceeds 2^31");
-  pl->gemm_ws = rbGemmWorkspaceSize(&gp);
+  pl->gemm_ws = gemm_workspace_bytes(&gp, pl->a_implicit ? 0 : pl->b_implicit ? 1 : -1);
   size_t off = 0;
   pl->a_off = off; off += up256(pl->a_bytes);
   pl->b_off = off; off += up256(pl->b_bytes);
@@ -392,6 +429,20 @@ extern "C" RbStatus rbConv(const RbConvProblem* p, void* filter, void* input, vo
   const void* A;
   const void* B;
   void* C;
+  const void* a_hi = input;
+  const void* a_lo = nullptr;
+  if (p->direction == 0 && pl.a_implicit && pl.a_planes > 0) {
+    float* hi = reinterpret_cast<float*>(ws + pl.a_off);
+    float* lo = pl.a_planes == 2 ? reinterpret_cast<float*>(ws + pl.a_off + pl.a_bytes / 2) : nullptr;
+    const long long pix = (long long)p->n * p->h * p->w;
+    if (pl.a_nchw)   // per image: [C][H*W] -> [H*W][C]
+      st = f32_planes(static_cast<const float*>(input), hi, lo, p->n, p->c, p->h * p->w, p->c, true, lo != nullptr, stream_v);
+    else
+      st = f32_planes(static_cast<const float*>(input), hi, lo, 1, (int)pix, p->c, p->c, false, lo != nullptr, stream_v);
+    if (st != RB_SUCCESS) return st;
+    a_hi = hi;
+    a_lo = lo;
+  }
   if (p->direction == 0) {
     if (pl.a_direct) A = input; else { gather(input, ws + pl.a_off, false, false, ho, wo, p->c); A = ws + pl.a_off; }
     if (pl.b_direct) B = filter; else { permute(filter, ws + pl.b_off, fsz, pl.fs, fil_kyxc, true, es); B = ws + pl.b_off; }
@@ -428,7 +479,8 @@ extern "C" RbStatus rbConv(const RbConvProblem* p, void* filter, void* input, vo
   if (pl.a_implicit) {
     ConvAOperand cv;
     if (p->direction == 0) {
-      cv.tensor = input;
+      cv.tensor = a_hi;
+      cv.tensor_lo = a_lo;
       cv.N = p->n; cv.H = p->h; cv.W = p->w; cv.C = p->c;
       cv.P = (int)ho; cv.Q = (int)wo; cv.Y = p->y; cv.X = p->x;
       cv.stride_h = p->stride_h; cv.stride_w = p->stride_w; cv.dil_h = p->dil_h; cv.dil_w = p->dil_w;

@@ -262,9 +262,9 @@ Workspace plan_workspace(const RbGemmProblem* p, const OperandPlan& oa, const Op
   const size_t a_bytes = align_up((size_t)p->g * oa.rows * oa.pitch * es, 256);
   const size_t b_bytes = align_up((size_t)p->g * ob.rows * ob.pitch * es, 256);
   if (oa.needs_copy) { w.a_off[0] = off; off += a_bytes; }
-  if (split) { w.a_off[1] = off; off += a_bytes; }
+  if (split && oa.needs_copy) { w.a_off[1] = off; off += a_bytes; }
   if (ob.needs_copy) { w.b_off[0] = off; off += b_bytes; }
-  if (split) { w.b_off[1] = off; off += b_bytes; }
+  if (split && ob.needs_copy) { w.b_off[1] = off; off += b_bytes; }
   if (cfg.splits > 1) {
     w.partial_off = off;
     off += align_up((size_t)cfg.splits * p->g * p->m * p->n * 4, 256);
@@ -289,13 +289,39 @@ using namespace rb;
 extern "C" void rbSetGemmVariant(int variant) { t_variant = variant; }
 extern "C" int rbGetGemmVariant(void) { return t_variant; }
 
-extern "C" size_t rbGemmWorkspaceSize(const RbGemmProblem* p) {
+size_t rb::gemm_workspace_bytes(const RbGemmProblem* p, int implicit_operand) {
   if (check_problem(p) != RB_SUCCESS) return 0;
   const size_t es = dtype_bytes(p->ab_type);
   const bool f32 = p->ab_type == RB_F32, split = f32 && p->f32_mode == 0;
-  const OperandPlan oa = plan_operand(p->trans_a != 0, p->m, p->k, es, f32, split);
-  const OperandPlan ob = plan_operand(p->trans_b == 0, p->n, p->k, es, f32, split);
+  OperandPlan oa = plan_operand(p->trans_a != 0, p->m, p->k, es, f32, split);
+  OperandPlan ob = plan_operand(p->trans_b == 0, p->n, p->k, es, f32, split);
+  if (implicit_operand == 0) oa.needs_copy = false;
+  if (implicit_operand == 1) ob.needs_copy = false;
   return plan_workspace(p, oa, ob, choose_config(p, t_variant)).total;
+}
+
+extern "C" size_t rbGemmWorkspaceSize(const RbGemmProblem* p) { return rb::gemm_workspace_bytes(p, -1); }
+
+RbStatus rb::f32_planes(const float* src, float* hi, float* lo, int groups, int R, int C, int pitch, bool transpose,
+                        bool split, void* stream_v) {
+  const DeviceInfo* dev = device_info();
+  if (!dev) return RB_CUDA_ERROR;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  const dim3 blk(32, 8, 1);
+  const int cx = transpose ? C : pitch, ry = transpose ? pitch : R;
+  const int tiles_x = (cx + 31) / 32, tiles_y = (ry + 31) / 32;
+  const long long total_tiles = (long long)tiles_x * tiles_y * groups;
+  const dim3 grd((unsigned)std::min<long long>(total_tiles, (long long)dev->sm_count * 64), 1, 1);
+  if (transpose) {
+    if (split) f32_prepare_kernel<true, true><<<grd, blk, 0, stream>>>(src, hi, lo, R, C, pitch, tiles_x, tiles_y, total_tiles);
+    else f32_prepare_kernel<true, false><<<grd, blk, 0, stream>>>(src, hi, lo, R, C, pitch, tiles_x, tiles_y, total_tiles);
+  } else {
+    if (split) f32_prepare_kernel<false, true><<<grd, blk, 0, stream>>>(src, hi, lo, R, C, pitch, tiles_x, tiles_y, total_tiles);
+    else f32_prepare_kernel<false, false><<<grd, blk, 0, stream>>>(src, hi, lo, R, C, pitch, tiles_x, tiles_y, total_tiles);
+  }
+  count_launch();
+  RB_CUDA_TRY(cudaGetLastError());
+  return RB_SUCCESS;
 }
 
 extern "C" RbStatus rbGemmGetConfig(const RbGemmProblem* p, RbGemmConfigInfo* out) {
@@ -336,8 +362,9 @@ RbStatus rb::gemm_run(const RbGemmProblem* p, const RbEpilogue* epi, const void*
   if (st != RB_SUCCESS) return st;
   const bool conv_a = conva && conva->operand == 0, conv_b = conva && conva->operand == 1;
   if (conva) {
-    if (p->g != 1 || (conv_a && p->trans_a) || (conv_b && p->trans_b) || p->ab_type == RB_F32 || !conva->tensor)
-      return fail(RB_UNSUPPORTED, "implicit operand: one group, 8/16-bit element types, A K-major or B stored K x N");
+    const bool f32_ok = conv_a && (p->f32_mode != 0 || conva->tensor_lo);   // TF32 planes prepared by the caller
+    if (p->g != 1 || (conv_a && p->trans_a) || (conv_b && p->trans_b) || (p->ab_type == RB_F32 && !f32_ok) || !conva->tensor)
+      return fail(RB_UNSUPPORTED, "implicit operand: one group, A K-major or B stored K x N (f32: A only, as TF32 planes)");
     if (conv_a) a = conva->tensor;
     else b = conva->tensor;
   }
@@ -504,9 +531,13 @@ RbStatus rb::gemm_run(const RbGemmProblem* p, const RbEpilogue* epi, const void*
     const int upper[2] = {cv.pad_w_hi - (cv.X - 1) * cv.dil_w, cv.pad_h_hi - (cv.Y - 1) * cv.dil_h};
     const uint32_t trav[2] = {(uint32_t)cv.stride_w, (uint32_t)cv.stride_h};
     // A: a tile is 128 pixels (rows) x one K block of channels. B: a chunk is one K block of pixels x 64 channels.
-    if (!encode_im2col_nhwc(conv_a ? &maps.a[0] : &maps.b[0], dt, cv.tensor, dims, strides, lower, upper, (uint32_t)che,
-                            (uint32_t)(conv_a ? kBM : bke), trav, &err))
-      return fail(RB_UNSUPPORTED, "implicit operand (im2col): " + err);
+    for (int sg = 0; sg < (conv_a ? nseg : 1); ++sg) {
+      // f32 accurate mode: segment sg of A reads the lo or the hi plane (same order as the copied-operand path)
+      const void* plane = (conv_a && seg_a[sg] == 1) ? cv.tensor_lo : cv.tensor;
+      if (!encode_im2col_nhwc(conv_a ? &maps.a[sg] : &maps.b[0], dt, plane, dims, strides, lower, upper, (uint32_t)che,
+                              (uint32_t)(conv_a ? kBM : bke), trav, &err))
+        return fail(RB_UNSUPPORTED, "implicit operand (im2col): " + err);
+    }
   }
   for (int s = 0; s < nseg; ++s) {
     if (!conv_a && !encode_operand(&maps.a[s], a_src[seg_a[s]], oa, kBM, &err)) return fail(RB_UNSUPPORTED, "A: " + err);

@@ -40,7 +40,8 @@ bool encode_im2col_nhwc(CUtensorMap* out, CUtensorMapDataType dt, const void* ba
 struct ConvAOperand {
   int operand = 0;           // 0: the A operand (GEMM M = N*P*Q, K = Y*X*C). 1: the B operand of a backward-weight
                              // convolution (GEMM K = N*P*Q, N = Y*X*C; B stored K x N, i.e. trans_b = 0)
-  const void* tensor;        // NHWC (dense), element type = the GEMM's ab_type
+  const void* tensor;        // NHWC (dense), element type = the GEMM's ab_type (f32: the hi TF32 plane)
+  const void* tensor_lo = nullptr;  // f32 in accurate mode: the lo TF32 plane of the same tensor (see f32_planes)
   int N, H, W, C;            // tensor extents
   int P, Q;                  // output image (GEMM M = N * P * Q)
   int Y, X;                  // filter (GEMM K = Y * X * C)
@@ -51,6 +52,14 @@ struct ConvAOperand {
 // rbGemm with an optional implicit operand (then `a` (or `b`) is ignored, trans_a (trans_b) must be 0, g must be 1).
 RbStatus gemm_run(const RbGemmProblem* p, const RbEpilogue* epi, const void* a, const void* b, void* c, void* workspace,
                   size_t workspace_bytes, void* stream, const ConvAOperand* conva);
+
+// rbGemmWorkspaceSize when operand `implicit_operand` (0 = A, 1 = B, -1 = none) is fetched in place by im2col loads
+// and therefore needs neither a pitched copy nor TF32 planes inside the GEMM's own workspace.
+size_t gemm_workspace_bytes(const RbGemmProblem* p, int implicit_operand);
+// TF32 planes of an f32 matrix stack [groups][R][C]: hi (and lo when `split`) with row pitch `pitch` elements;
+// with `transpose` the output is [groups][C][pitch >= R]. x = hi + lo, both exactly representable in TF32.
+RbStatus f32_planes(const float* src, float* hi, float* lo, int groups, int R, int C, int pitch, bool transpose,
+                    bool split, void* stream);
 
 // Device trace buffer set with rbSetTraceBuffer for the calling thread (nullptr when `need` words do not fit).
 unsigned long long* trace_buffer(size_t need_u64);
