@@ -117,6 +117,7 @@ constexpr int kAssumedSMs = 148;  // B200
 
 struct GemmConfig {
   int ctas, bn, stages, splits;
+  int kpr;                 // K blocks per barrier round (see GemmParams::kpr)
   bool plain_stores;
   int dp_tiles, sk_tiles;  // stream-K tail (see GemmParams); sk_tiles == 0: every tile is computed whole
 };
@@ -132,9 +133,18 @@ GemmConfig choose_config(const RbGemmProblem* p, int variant, bool epi_vec = fal
   c.ctas = ((variant & 0xF) == 1) ? 1 : 2;
   if (b_mn && (c.bn / 2) % che != 0) c.ctas = 1;
   if (p->m <= kBM && (variant & 0xF) != 2) c.ctas = 1;      // a pair would compute 128 empty rows
+  if (c.bn == 64 && (variant & 0xF) != 2) c.ctas = 1;        // measured: 64-column tiles run faster unpaired (345 vs 324 TFLOP/s)
   c.stages = (variant >> 4) & 0xF;
   const int max_stages = c.ctas == 2 ? GemmSmemLayout<2>::max_stages(c.bn, epi_vec) : GemmSmemLayout<1>::max_stages(c.bn, epi_vec);
   if (c.stages <= 0 || c.stages > max_stages) c.stages = max_stages;
+  // K blocks per barrier round. One round costs the issuing thread about 310 + 44 n cycles for n MMAs (measured),
+  // which four 128x256x16 MMAs (512 cycles) barely hide and four narrower ones do not. Measured: two blocks per
+  // round at 256 columns (4096^3 f16 1100 -> 1290 TFLOP/s with this producer loop), four at 128 and 64 columns.
+  // Variant bits 28-29: 1, 2, 3 = 1, 2, 4 blocks; 0 = this rule.
+  const int kpr_code = (variant >> 28) & 3;
+  c.kpr = kpr_code == 1 ? 1 : kpr_code == 2 ? 2 : kpr_code == 3 ? 4 : (c.bn <= 128 ? 4 : 2);
+  while (c.kpr > 1 && c.stages < 2 * c.kpr) c.kpr /= 2;   // at least two rounds in flight
+  c.stages = c.stages / c.kpr * c.kpr;
   c.plain_stores = ((variant >> 8) & 1) != 0;
   const int bke = kRowBytes / es;
   const long long kblocks = (p->k + bke - 1) / bke;
@@ -598,6 +608,7 @@ RbStatus rb::gemm_run(const RbGemmProblem* p, const RbEpilogue* epi, const void*
   }
   kp.status = dev->status_word;
   kp.stages = stages;
+  kp.kpr = cfg.kpr;
   kp.probe = (t_variant >> 24) & 7;
   if (conva) {
     kp.conva.enabled = conv_a ? 1 : 2; kp.conva.P = conva->P; kp.conva.Q = conva->Q; kp.conva.X = conva->X;

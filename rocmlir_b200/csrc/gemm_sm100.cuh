@@ -96,7 +96,8 @@ struct GemmParams {
   int a_fused, b_fused;       // MN-major operand loaded with one 4-D box per stage (extent a multiple of the chunk)
   int probe;                  // instrumentation (results become meaningless): bit0 = no loads, bit1 = no epilogue work,
                               // bit2 = epilogue without its global stores
-  int stages;                 // shared-memory ring depth (<= GemmSmemLayout::kMaxStages)
+  int stages;                 // shared-memory ring depth (<= GemmSmemLayout::kMaxStages), a multiple of kpr
+  int kpr;                    // K blocks per barrier round (1, 2 or 4): one full/empty barrier pair serves kpr ring slots
 };
 
 // Implicit B operand: base coordinates of output pixel `pix` (row-major n, p, q) and the tap / channel chunk of
@@ -126,15 +127,18 @@ struct GemmSmemLayout {
   // Epilogue staging: per epilogue warp two 32-row x 128-byte tiles (double buffered TMA stores).
   static constexpr int kStoreTileBytes = 32 * kRowBytes;
   static constexpr int kStagingBytes = 4 * 2 * kStoreTileBytes;
+  // With per-column epilogue vectors the staging is single-buffered: the 16 KB saved keep the ring at six 32 KB
+  // stages (three rounds of two K blocks) beside the vectors, which matters more than overlapping the stores.
+  static constexpr int staging_bytes(bool epi_vec) { return epi_vec ? kStagingBytes / 2 : kStagingBytes; }
   static constexpr int kBarBytes = 512;
   // Per-column epilogue vectors of the current tile as f32, one private copy per epilogue warp (no cross-warp
   // barrier is needed that way): [4 warps][scale[kMaxBN], bias[kMaxBN]].
   static constexpr int kEpiVecBytes = 4 * 2 * kMaxBN * 4;
   static constexpr int total(int stages, int bn, bool epi_vec) {
-    return stages * stage_bytes(bn) + kStagingBytes + (epi_vec ? kEpiVecBytes : 0) + kBarBytes + 1024;  // + alignment slack
+    return stages * stage_bytes(bn) + staging_bytes(epi_vec) + (epi_vec ? kEpiVecBytes : 0) + kBarBytes + 1024;  // + alignment slack
   }
   static constexpr int max_stages(int bn, bool epi_vec) {
-    int s = (kSmemBudget - kStagingBytes - (epi_vec ? kEpiVecBytes : 0) - kBarBytes - 1024) / stage_bytes(bn);
+    int s = (kSmemBudget - staging_bytes(epi_vec) - (epi_vec ? kEpiVecBytes : 0) - kBarBytes - 1024) / stage_bytes(bn);
     return s > kMaxStages ? kMaxStages : s;
   }
 };
@@ -217,10 +221,12 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int stages = p.stages;
+  const int kpr = p.kpr;               // K blocks per barrier round
+  const int rounds = stages / kpr;     // barrier pairs in use
   uint8_t* staging = smem + stages * stage_bytes;  // 1024-byte aligned (stage sizes are multiples of 1024)
   const bool epi_vec = (p.epi.flags & (RB_EPI_COL_SCALE | RB_EPI_BIAS)) != 0;
-  float* epi_vecs = reinterpret_cast<float*>(staging + L::kStagingBytes);   // present only when epi_vec
-  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + L::kStagingBytes + (epi_vec ? L::kEpiVecBytes : 0));
+  float* epi_vecs = reinterpret_cast<float*>(staging + L::staging_bytes(epi_vec));   // present only when epi_vec
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + L::staging_bytes(epi_vec) + (epi_vec ? L::kEpiVecBytes : 0));
   uint64_t* full_bar = bars;                       // [stages]
   uint64_t* empty_bar = bars + stages;             // [stages]
   uint64_t* tfull_bar = bars + 2 * stages;         // [2]
@@ -286,17 +292,26 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
           base_w = (rem - op * p.conva.Q) * p.conva.stride_w - p.conva.pad_w;
         }
         int seg = 0, kb = kb_begin;
-        for (int kk = 0; kk < ktotal; ++kk) {
+        // One barrier round covers up to kpr consecutive K blocks in ring slots s * kpr ... (s indexes rounds):
+        // the barrier work of the issuing threads is per round, which is what bounds narrow tiles.
+        for (int kk0 = 0; kk0 < ktotal; kk0 += kpr) {
+          const int nblk = min(kpr, ktotal - kk0);
           const long long tw = p.trace ? clock64() : 0;
           if (!mbar_wait(&empty_bar[s], ph ^ 1u, p.status, kStatusTimeoutProducer + s)) { ok = false; break; }
           if (p.trace) w_empty += clock64() - tw;
-          uint8_t* sa = smem + s * stage_bytes;
-          uint8_t* sb = sa + L::kABytes;
-          const int k0 = kb * BKE;
           if (p.probe & 1) {
             if (CTAS == 1 || rank == 0) mbar_arrive(&full_bar[s]);
           } else if constexpr (CTAS == 1) {
-            mbar_expect_tx(&full_bar[s], stage_bytes);
+            mbar_expect_tx(&full_bar[s], nblk * stage_bytes);
+          } else {
+            if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * nblk * stage_bytes);
+          }
+          for (int j = 0; j < nblk; ++j) {
+          uint8_t* sa = smem + (s * kpr + j) * stage_bytes;
+          uint8_t* sb = sa + L::kABytes;
+          const int k0 = kb * BKE;
+          if (p.probe & 1) {
+          } else if constexpr (CTAS == 1) {
             if (!A_MN && p.conva.enabled == 1) {
               const int tap = kb / p.conva.cchunks, cc = kb - tap * p.conva.cchunks;
               const int fy = tap / p.conva.X, fx = tap - fy * p.conva.X;
@@ -331,7 +346,6 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
           } else {
             // Completion of this CTA's loads is counted on the leader CTA's barrier.
             const uint32_t lead_full = mapa_u32(smem_u32(&full_bar[s]), 0);
-            if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * stage_bytes);
             if (!A_MN && p.conva.enabled == 1) {
               const int tap = kb / p.conva.cchunks, cc = kb - tap * p.conva.cchunks;
               const int fy = tap / p.conva.X, fx = tap - fy * p.conva.X;
@@ -365,7 +379,8 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
             }
           }
           if (++kb == kb_end) { kb = kb_begin; ++seg; }
-          if (++s == (uint32_t)stages) { s = 0; ph ^= 1u; }
+          }
+          if (++s == (uint32_t)rounds) { s = 0; ph ^= 1u; }
         }
       }
       if (p.trace) p.trace[blockIdx.x * 16 + 1] = (unsigned long long)w_empty;
@@ -405,34 +420,70 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
         uint32_t accum = 0;
         const int ktotal = (w.kb_end - w.kb_begin) * p.nseg;
         const long long tk0 = p.trace ? clock64() : 0;
-        for (int kk = 0; kk < ktotal; ++kk) {
-          if (!ready) {
-            const long long tw = p.trace ? clock64() : 0;
-            if (!mbar_wait(&full_bar[s], ph, p.status, kStatusTimeoutMma + s)) { ok = false; break; }
-            if (p.trace) w_full += clock64() - tw;
-          }
-          // no tcgen05 fence here: the operands arrive through the async proxy (TMA) and are ordered by the
-          // barrier itself; the fence after the accumulator-buffer wait above orders the TMEM accesses
-          uint32_t ns = s + 1, nph = ph;
-          if (ns == (uint32_t)stages) { ns = 0; nph ^= 1u; }
-          const bool next_ready = mbar_test_wait_addr(full0 + ns * 8, nph);  // consumed after the MMAs below
-          const uint32_t a_lo = a_lo0 + s * kStageStep;
-          const uint32_t b_lo = b_lo0 + s * kStageStep;
+        if (kpr == 1) {
+          // one K block per round: the tight loop (at 256-column tiles the four MMAs of a block execute for 512
+          // cycles and the loop below must issue them in less)
+          for (int kk = 0; kk < ktotal; ++kk) {
+            if (!ready) {
+              const long long tw = p.trace ? clock64() : 0;
+              if (!mbar_wait(&full_bar[s], ph, p.status, kStatusTimeoutMma + s)) { ok = false; break; }
+              if (p.trace) w_full += clock64() - tw;
+            }
+            uint32_t ns = s + 1, nph = ph;
+            if (ns == (uint32_t)stages) { ns = 0; nph ^= 1u; }
+            const bool next_ready = mbar_test_wait_addr(full0 + ns * 8, nph);  // consumed after the MMAs below
+            const uint32_t a_lo = a_lo0 + s * kStageStep;
+            const uint32_t b_lo = b_lo0 + s * kStageStep;
 #pragma unroll
-          for (int k = 0; k < KSTEPS; ++k) {
-            umma_ss<KIND, CTAS>(tmem_d, desc64(a_lo + k * kAStep, desc_hi), desc64(b_lo + k * kBStep, desc_hi), p.idesc,
-                                accum);
-            accum = 1;
+            for (int k = 0; k < KSTEPS; ++k) {
+              umma_ss<KIND, CTAS>(tmem_d, desc64(a_lo + k * kAStep, desc_hi), desc64(b_lo + k * kBStep, desc_hi), p.idesc,
+                                  accum);
+              accum = 1;
+            }
+            if constexpr (CTAS == 1) {
+              tc_commit_addr1(empty0 + s * 8);
+            } else {
+              tc_commit_mask2(empty0 + s * 8, 3);
+            }
+            s = ns;
+            ph = nph;
+            ready = next_ready;
           }
-          // Free the stage in every CTA of the pair once these MMAs have read it.
-          if constexpr (CTAS == 1) {
-            tc_commit_addr1(empty0 + s * 8);
-          } else {
-            tc_commit_mask2(empty0 + s * 8, 3);
+        } else {
+          for (int kk0 = 0; kk0 < ktotal; kk0 += kpr) {
+            const int nblk = min(kpr, ktotal - kk0);
+            if (!ready) {
+              const long long tw = p.trace ? clock64() : 0;
+              if (!mbar_wait(&full_bar[s], ph, p.status, kStatusTimeoutMma + s)) { ok = false; break; }
+              if (p.trace) w_full += clock64() - tw;
+            }
+            // no tcgen05 fence here: the operands arrive through the async proxy (TMA) and are ordered by the
+            // barrier itself; the fence after the accumulator-buffer wait above orders the TMEM accesses
+            uint32_t ns = s + 1, nph = ph;
+            if (ns == (uint32_t)rounds) { ns = 0; nph ^= 1u; }
+            const bool next_ready = mbar_test_wait_addr(full0 + ns * 8, nph);  // consumed after the MMAs below
+            uint32_t a_lo = a_lo0 + s * kpr * kStageStep;
+            uint32_t b_lo = b_lo0 + s * kpr * kStageStep;
+            for (int j = 0; j < nblk; ++j) {
+  #pragma unroll
+              for (int k = 0; k < KSTEPS; ++k) {
+                umma_ss<KIND, CTAS>(tmem_d, desc64(a_lo + k * kAStep, desc_hi), desc64(b_lo + k * kBStep, desc_hi), p.idesc,
+                                    accum);
+                accum = 1;
+              }
+              a_lo += kStageStep;
+              b_lo += kStageStep;
+            }
+            // Free the round's slots in every CTA of the pair once these MMAs have read them.
+            if constexpr (CTAS == 1) {
+              tc_commit_addr1(empty0 + s * 8);
+            } else {
+              tc_commit_mask2(empty0 + s * 8, 3);
+            }
+            s = ns;
+            ph = nph;
+            ready = next_ready;
           }
-          s = ns;
-          ph = nph;
-          ready = next_ready;
         }
         if (!ok) break;
         if (p.trace) t_kloop += clock64() - tk0;
@@ -461,7 +512,8 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
     const int cols_per_store = kRowBytes / es_c;          // columns covered by one 128-byte staging row
     const int groups_per_store = cols_per_store / 32;     // 32-column TMEM loads per staging row: 1, 2 or 4
     const bool raw_i32 = p.acc_is_int && p.c_type == RB_I32 && p.epi.flags == 0;
-    uint8_t* my_staging = staging + q * 2 * L::kStoreTileBytes;
+    const uint32_t stg_bufs = epi_vec ? 1u : 2u;   // staging buffers per warp
+    uint8_t* my_staging = staging + q * stg_bufs * L::kStoreTileBytes;
     uint32_t t = 0, nstores = 0;
     long long w_tfull = 0, e_work = 0, e_ld = 0, e_cv = 0;
     WorkIter it(p, pair_id, num_pairs);
@@ -607,9 +659,9 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
           uint32_t v[32];
           tmem_ld32(taddr + c * 32, v);
           const int sub = c % groups_per_store;
-          uint8_t* stg = my_staging + (nstores & 1u) * L::kStoreTileBytes;
+          uint8_t* stg = my_staging + (stg_bufs == 2 ? (nstores & 1u) : 0u) * L::kStoreTileBytes;
           if (sub == 0) {
-            if (lane == 0 && nstores >= 2) bulk_wait_read<1>();
+            if (lane == 0 && nstores >= stg_bufs) { if (stg_bufs == 2) bulk_wait_read<1>(); else bulk_wait_read<0>(); }
             __syncwarp();
           }
           tmem_ld_wait();
@@ -702,9 +754,10 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
           // Stage 32 rows x 128 bytes per store: row `lane` at lane * 128, its 16-byte pieces XOR-swizzled with
           // (lane & 7) exactly as the 128-byte-swizzled store map expects (also free of bank conflicts).
           const int sub = c % groups_per_store;
-          uint8_t* stg = my_staging + (nstores & 1u) * L::kStoreTileBytes;
+          uint8_t* stg = my_staging + (stg_bufs == 2 ? (nstores & 1u) : 0u) * L::kStoreTileBytes;
           if (sub == 0) {
-            if (lane == 0 && nstores >= 2) bulk_wait_read<1>();  // the store that last used this buffer has read it
+            // the store that last used this buffer has read it
+            if (lane == 0 && nstores >= stg_bufs) { if (stg_bufs == 2) bulk_wait_read<1>(); else bulk_wait_read<0>(); }
             __syncwarp();
           }
 #pragma unroll
