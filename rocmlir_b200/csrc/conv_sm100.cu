@@ -165,6 +165,25 @@ __global__ void conv_gather_vec_kernel(const uint8_t* __restrict__ src, uint8_t*
   }
 }
 
+// Zero-upsampling of an NHWK tensor for a strided backward-data convolution: out[n][p*sh][q*sw][:] = in[n][p][q][:],
+// zeros elsewhere (out is N x ((P-1)*sh+1) x ((Q-1)*sw+1) x CH). One 16-byte vector of channels per thread and step.
+__global__ void upsample_nhwc_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, int N, int P, int Q, int UP,
+                                     int UQ, int chv, int sh, int sw) {
+  const long long total = (long long)N * UP * UQ * chv;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const unsigned cv = (unsigned)(i % chv);
+    const unsigned long long r = (unsigned long long)(i / chv);
+    const unsigned uq = (unsigned)(r % UQ);
+    const unsigned r2 = (unsigned)(r / UQ);
+    const unsigned up = r2 % UP, n = r2 / UP;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (up % sh == 0 && uq % sw == 0)
+      v = __ldg(in + (((long long)n * P + up / sh) * Q + uq / sw) * chv + cv);
+    out[i] = v;
+  }
+}
+
 size_t up256(size_t x) { return (x + 255) / 256 * 256; }
 
 // Named-dimension strides of a tensor stored in `layout` order (row-major over the letters).
@@ -194,6 +213,7 @@ struct ConvPlan {
   bool a_direct, b_direct, c_direct;
   bool a_implicit;   // forward: the A matrix is never built; the GEMM producer loads it from the NHWC input (TMA im2col)
   bool b_implicit;   // backward weight: the same for the B matrix (K = pixels, N = (y,x,c))
+  bool a_up;         // backward data with a stride: the output gradient is zero-upsampled into the workspace first
   int a_planes;      // f32 forward implicit GEMM: TF32 planes of the input kept in the workspace (0, 1 or 2)
   bool a_nchw;       //   the input is NCHW: the plane pass transposes it to NHWC
   size_t a_bytes, b_bytes, c_bytes, gemm_ws;
@@ -246,6 +266,7 @@ RbStatus make_plan(const RbConvProblem* p, ConvPlan* pl) {
   memset(&gp, 0, sizeof(gp));
   pl->a_implicit = false;
   pl->b_implicit = false;
+  pl->a_up = false;
   gp.g = (int)G;
   gp.ab_type = t;
   gp.f32_mode = p->f32_mode;
@@ -312,15 +333,25 @@ RbStatus make_plan(const RbConvProblem* p, ConvPlan* pl) {
     // mirrored, so the same implicit-GEMM path applies (A = NHWK output gradient read through im2col loads with
     // padding (fil-1)*dil - pad; B = the filter rearranged to c x (y', x', k) with y' = Y-1-y, x' = X-1-x).
     const long long bpad_h = (long long)(p->y - 1) * p->dil_h - p->pad_h, bpad_w = (long long)(p->x - 1) * p->dil_w - p->pad_w;
-    pl->a_implicit = !pl->a_direct && out_is_mat && G == 1 && t != RB_F32 && (p->k * es) % 128 == 0 &&
-                     p->stride_h == 1 && p->stride_w == 1 && bpad_h >= 0 && bpad_w >= 0 && bpad_h < 64 && bpad_w < 64 &&
-                     (p->y - 1) * p->dil_h < 256 && (p->x - 1) * p->dil_w < 256;
+    // A stride is handled by zero-upsampling the output gradient first ((Ho-1)*stride+1 rows with the gradient on
+    // every stride-th position): the same unit-stride formulation then applies. It computes stride_h*stride_w times
+    // the useful products, and still beats the col2im gather it replaces.
+    const long long uh = (ho - 1) * p->stride_h + 1, uw = (wo - 1) * p->stride_w + 1;
+    const long long bpad_h_hi = p->h - uh - bpad_h + (long long)(p->y - 1) * p->dil_h;
+    const long long bpad_w_hi = p->w - uw - bpad_w + (long long)(p->x - 1) * p->dil_w;
+    pl->a_up = p->stride_h > 1 || p->stride_w > 1;
+    pl->a_implicit = (!pl->a_direct || pl->a_up) && out_is_mat && G == 1 && t != RB_F32 && (p->k * es) % 128 == 0 &&
+                     bpad_h >= 0 && bpad_w >= 0 && bpad_h < 64 && bpad_w < 64 && bpad_h_hi >= 0 && bpad_w_hi >= 0 &&
+                     bpad_h_hi < 64 && bpad_w_hi < 64 && p->stride_h <= 4 && p->stride_w <= 4 &&
+                     (p->y - 1) * p->dil_h < 256 && (p->x - 1) * p->dil_w < 256 &&
+                     (long long)p->n * uh * uw < 0x7fffffffLL;
+    if (!pl->a_implicit) pl->a_up = false;
     if (pl->a_implicit) {
       pl->a_direct = true;
       pl->b_direct = false;     // the mirrored c x (y',x',k) matrix is always built (it is filter-sized)
       gp.trans_b = 1;           // B stored [N = c][K = (y',x',k)]
     }
-    pl->a_bytes = pl->a_direct ? 0 : (size_t)G * pix_i * yxk * es;
+    pl->a_bytes = pl->a_up ? (size_t)p->n * uh * uw * p->k * es : (pl->a_direct ? 0 : (size_t)G * pix_i * yxk * es);
     pl->b_bytes = pl->b_direct ? 0 : (size_t)G * yxk * p->c * es;
     pl->c_bytes = pl->c_direct ? 0 : (size_t)G * pix_i * p->c * es;
   }
@@ -487,14 +518,22 @@ extern "C" RbStatus rbConv(const RbConvProblem* p, void* filter, void* input, vo
       cv.pad_h = p->pad_h; cv.pad_w = p->pad_w; cv.pad_h_hi = p->pad_h_r; cv.pad_w_hi = p->pad_w_r;
     } else {
       // backward data, unit stride: "image" = output gradient (ho x wo x k), "output pixels" = input pixels (h x w)
+      const int uh = ((int)ho - 1) * p->stride_h + 1, uw = ((int)wo - 1) * p->stride_w + 1;   // = ho, wo at unit stride
       cv.tensor = output;
-      cv.N = p->n; cv.H = (int)ho; cv.W = (int)wo; cv.C = p->k;
+      if (pl.a_up) {
+        const int chv = (int)((size_t)p->k * es / 16);
+        upsample_nhwc_kernel<<<blocks, 256, 0, stream>>>(static_cast<const uint4*>(output), reinterpret_cast<uint4*>(ws + pl.a_off),
+                                                          p->n, (int)ho, (int)wo, uh, uw, chv, p->stride_h, p->stride_w);
+        count_launch();
+        cv.tensor = ws + pl.a_off;
+      }
+      cv.N = p->n; cv.H = uh; cv.W = uw; cv.C = p->k;
       cv.P = p->h; cv.Q = p->w; cv.Y = p->y; cv.X = p->x;
       cv.stride_h = 1; cv.stride_w = 1; cv.dil_h = p->dil_h; cv.dil_w = p->dil_w;
       cv.pad_h = (p->y - 1) * p->dil_h - p->pad_h; cv.pad_w = (p->x - 1) * p->dil_w - p->pad_w;
       // upper padding such that the base pixel takes exactly h (w) positions: h = ho + pad + pad_hi - (Y-1)*dil
-      cv.pad_h_hi = p->h - (int)ho - cv.pad_h + (p->y - 1) * p->dil_h;
-      cv.pad_w_hi = p->w - (int)wo - cv.pad_w + (p->x - 1) * p->dil_w;
+      cv.pad_h_hi = p->h - uh - cv.pad_h + (p->y - 1) * p->dil_h;
+      cv.pad_w_hi = p->w - uw - cv.pad_w + (p->x - 1) * p->dil_w;
     }
     st = gemm_run(&pl.gemm, nullptr, nullptr, B, C, pl.gemm_ws ? ws + pl.gemm_off : nullptr, pl.gemm_ws, stream_v, &cv);
   } else {

@@ -69,6 +69,26 @@ def test_int8_gemm_bit_exact(cuda_device, g, m, n, k, ta, tb, tc, variant):
     assert info["overflows"] == 0
 
 
+# K blocks per barrier round (variant bits 28-29: 1, 2, 4 blocks) x tile width x CTA grouping, with a K that leaves
+# a partial last round (7 or 13 blocks) and ragged M, N: every configuration must give the same exact result.
+@pytest.mark.parametrize("kpr", [1, 2, 3])
+@pytest.mark.parametrize("bn", [1, 2, 3])
+@pytest.mark.parametrize("ctas", [1, 2])
+def test_k_blocks_per_round_configurations_exact(cuda_device, kpr, bn, ctas):
+    variant = ctas | (bn << 12) | (kpr << 28)
+    g, m, n, k = 2, 300, 200, 64 * 7 + 8
+    (af, araw), (bf, braw) = reference_random([(g, m, k), (g, k, n)], oracle.F16, seed=1)
+    ref = oracle.from_f32(oracle.gemm_f32(af, bf, g, m, n, k, threads=oracle.max_threads()), oracle.F16)
+    got = run_gemm(araw, braw, oracle.F16, oracle.F16, variant=variant)
+    np.testing.assert_array_equal(got.reshape(ref.shape), ref)
+    k = 128 * 13
+    a = uniform_int8((g, m, k), seed=21)
+    b = uniform_int8((g, n, k), seed=22)
+    refi = oracle.gemm_i8(a, b, g, m, n, k, False, True, False, threads=oracle.max_threads())
+    goti = run_gemm(a, b, oracle.I8, oracle.I32, tb=True, variant=variant)
+    assert oracle.verify_int(goti, refi)[0] == [1, 1, 1]
+
+
 # Few output tiles and a long reduction: the library cuts K into ranges (partial planes + fixed-order reduction),
 # and narrow N selects the 64- and 128-column tiles. Shapes of the ResNet bwd-weight GEMMs in miniature.
 SPLITK_SHAPES = [(1, 64, 576, 8192), (1, 200, 64, 4096), (2, 130, 100, 2048), (1, 576, 64, 6272)]
