@@ -133,6 +133,12 @@ GemmConfig choose_config(const RbGemmProblem* p, int variant, bool epi_vec = fal
   c.ctas = ((variant & 0xF) == 1) ? 1 : 2;
   if (b_mn && (c.bn / 2) % che != 0) c.ctas = 1;
   if (p->m <= kBM && (variant & 0xF) != 2) c.ctas = 1;      // a pair would compute 128 empty rows
+  {
+    // a main loop of one or two K blocks leaves the epilogue exposed, and the epilogue of a pair is the slower one
+    // (measured at K = 64, 256 columns: 134 us paired, 86 us unpaired, the HBM floor being 79 us)
+    const long long kb = (p->k + kRowBytes / es - 1) / (kRowBytes / es);
+    if (kb <= 2 && (variant & 0xF) != 2) c.ctas = 1;
+  }
   if (c.bn == 64 && (variant & 0xF) != 2) c.ctas = 1;        // measured: 64-column tiles run faster unpaired (345 vs 324 TFLOP/s)
   c.stages = (variant >> 4) & 0xF;
   const int max_stages = c.ctas == 2 ? GemmSmemLayout<2>::max_stages(c.bn, epi_vec) : GemmSmemLayout<1>::max_stages(c.bn, epi_vec);
