@@ -15,6 +15,11 @@
 // tile i+1. With CTAS == 2 two CTAs of a cluster form a pair that computes a 256 x 256 tile with
 // tcgen05.mma.cta_group::2: each CTA loads its own 128 rows of A and its own 128 columns of B.
 //
+// The ring is walked in rounds of kpr K blocks (1, 2 or 4) that share one full / empty barrier pair: the barrier
+// work of the single issuing threads is per round, and it is what bounds tiles whose MMAs are short.
+// The epilogue has compact loops for the common cases (16-bit C, 4-byte C, fused elementwise work) beside a general
+// one: the general body exceeds the instruction cache and runs an order of magnitude slower.
+//
 // Tile scheduler: static persistent loop with M-grouped rasterisation for L2 reuse, the same idea as
 // rocMLIR's grouped grid layout (mlir/lib/Dialect/Rock/utility/GridLayoutEmitter.cpp:61-109).
 #pragma once
@@ -307,78 +312,79 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
             if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * nblk * stage_bytes);
           }
           for (int j = 0; j < nblk; ++j) {
-          uint8_t* sa = smem + (s * kpr + j) * stage_bytes;
-          uint8_t* sb = sa + L::kABytes;
-          const int k0 = kb * BKE;
-          if (p.probe & 1) {
-          } else if constexpr (CTAS == 1) {
-            if (!A_MN && p.conva.enabled == 1) {
-              const int tap = kb / p.conva.cchunks, cc = kb - tap * p.conva.cchunks;
-              const int fy = tap / p.conva.X, fx = tap - fy * p.conva.X;
-              tma_load_im2col_4d(sa, &maps.a[seg], &full_bar[s], cc * BKE, base_w, base_h, img,
-                                 (uint16_t)(fx * p.conva.dil_w), (uint16_t)(fy * p.conva.dil_h));
-            } else if constexpr (!A_MN) {
-              tma_load_3d(sa, &maps.a[seg], &full_bar[s], k0, m0, g);
-            } else if (p.a_fused) {
-              tma_load_4d(sa, &maps.a[seg], &full_bar[s], 0, k0, m0 / CHE, g);
-            } else {
-#pragma unroll
-              for (int c = 0; c < kBM / CHE; ++c)
-                tma_load_3d(sa + c * CHUNK_BYTES, &maps.a[seg], &full_bar[s], m0 + c * CHE, k0, g);
-            }
-            if constexpr (!B_MN) {
-              tma_load_3d(sb, &maps.b[seg], &full_bar[s], k0, n0, g);
-            } else if (p.conva.enabled == 2) {
-              int bi, bh, bw;
-              convb_pixel(p.conva, k0, bi, bh, bw);
-              for (int c = 0; c < bn_cta / CHE; ++c) {
-                int cc, fy, fx;
-                convb_tap(p.conva, n0 + c * CHE, p.N, CHE, cc, fy, fx);
-                tma_load_im2col_4d(sb + c * CHUNK_BYTES, &maps.b[seg], &full_bar[s], cc * CHE, bw, bh, bi,
+            uint8_t* sa = smem + (s * kpr + j) * stage_bytes;
+            uint8_t* sb = sa + L::kABytes;
+            const int k0 = kb * BKE;
+            if (p.probe & 1) {
+              // loads switched off: the round's barrier was completed above
+            } else if constexpr (CTAS == 1) {
+              if (!A_MN && p.conva.enabled == 1) {
+                const int tap = kb / p.conva.cchunks, cc = kb - tap * p.conva.cchunks;
+                const int fy = tap / p.conva.X, fx = tap - fy * p.conva.X;
+                tma_load_im2col_4d(sa, &maps.a[seg], &full_bar[s], cc * BKE, base_w, base_h, img,
                                    (uint16_t)(fx * p.conva.dil_w), (uint16_t)(fy * p.conva.dil_h));
+              } else if constexpr (!A_MN) {
+                tma_load_3d(sa, &maps.a[seg], &full_bar[s], k0, m0, g);
+              } else if (p.a_fused) {
+                tma_load_4d(sa, &maps.a[seg], &full_bar[s], 0, k0, m0 / CHE, g);
+              } else {
+  #pragma unroll
+                for (int c = 0; c < kBM / CHE; ++c)
+                  tma_load_3d(sa + c * CHUNK_BYTES, &maps.a[seg], &full_bar[s], m0 + c * CHE, k0, g);
               }
-            } else if (p.b_fused) {
-              tma_load_4d(sb, &maps.b[seg], &full_bar[s], 0, k0, n0 / CHE, g);
-            } else {
-              for (int c = 0; c < bn_cta / CHE; ++c)
-                tma_load_3d(sb + c * CHUNK_BYTES, &maps.b[seg], &full_bar[s], n0 + c * CHE, k0, g);
-            }
-          } else {
-            // Completion of this CTA's loads is counted on the leader CTA's barrier.
-            const uint32_t lead_full = mapa_u32(smem_u32(&full_bar[s]), 0);
-            if (!A_MN && p.conva.enabled == 1) {
-              const int tap = kb / p.conva.cchunks, cc = kb - tap * p.conva.cchunks;
-              const int fy = tap / p.conva.X, fx = tap - fy * p.conva.X;
-              tma_load_im2col_4d_bar(sa, &maps.a[seg], lead_full, cc * BKE, base_w, base_h, img,
+              if constexpr (!B_MN) {
+                tma_load_3d(sb, &maps.b[seg], &full_bar[s], k0, n0, g);
+              } else if (p.conva.enabled == 2) {
+                int bi, bh, bw;
+                convb_pixel(p.conva, k0, bi, bh, bw);
+                for (int c = 0; c < bn_cta / CHE; ++c) {
+                  int cc, fy, fx;
+                  convb_tap(p.conva, n0 + c * CHE, p.N, CHE, cc, fy, fx);
+                  tma_load_im2col_4d(sb + c * CHUNK_BYTES, &maps.b[seg], &full_bar[s], cc * CHE, bw, bh, bi,
                                      (uint16_t)(fx * p.conva.dil_w), (uint16_t)(fy * p.conva.dil_h));
-            } else if constexpr (!A_MN) {
-              tma_load_3d_bar(sa, &maps.a[seg], lead_full, k0, m0, g);
-            } else if (p.a_fused) {
-              tma_load_4d_bar(sa, &maps.a[seg], lead_full, 0, k0, m0 / CHE, g);
-            } else {
-#pragma unroll
-              for (int c = 0; c < kBM / CHE; ++c)
-                tma_load_3d_bar(sa + c * CHUNK_BYTES, &maps.a[seg], lead_full, m0 + c * CHE, k0, g);
-            }
-            if constexpr (!B_MN) {
-              tma_load_3d_bar(sb, &maps.b[seg], lead_full, k0, n0, g);
-            } else if (p.conva.enabled == 2) {
-              int bi, bh, bw;
-              convb_pixel(p.conva, k0, bi, bh, bw);
-              for (int c = 0; c < bn_cta / CHE; ++c) {
-                int cc, fy, fx;
-                convb_tap(p.conva, n0 + c * CHE, p.N, CHE, cc, fy, fx);
-                tma_load_im2col_4d_bar(sb + c * CHUNK_BYTES, &maps.b[seg], lead_full, cc * CHE, bw, bh, bi,
-                                       (uint16_t)(fx * p.conva.dil_w), (uint16_t)(fy * p.conva.dil_h));
+                }
+              } else if (p.b_fused) {
+                tma_load_4d(sb, &maps.b[seg], &full_bar[s], 0, k0, n0 / CHE, g);
+              } else {
+                for (int c = 0; c < bn_cta / CHE; ++c)
+                  tma_load_3d(sb + c * CHUNK_BYTES, &maps.b[seg], &full_bar[s], n0 + c * CHE, k0, g);
               }
-            } else if (p.b_fused) {
-              tma_load_4d_bar(sb, &maps.b[seg], lead_full, 0, k0, n0 / CHE, g);
             } else {
-              for (int c = 0; c < bn_cta / CHE; ++c)
-                tma_load_3d_bar(sb + c * CHUNK_BYTES, &maps.b[seg], lead_full, n0 + c * CHE, k0, g);
+              // Completion of this CTA's loads is counted on the leader CTA's barrier.
+              const uint32_t lead_full = mapa_u32(smem_u32(&full_bar[s]), 0);
+              if (!A_MN && p.conva.enabled == 1) {
+                const int tap = kb / p.conva.cchunks, cc = kb - tap * p.conva.cchunks;
+                const int fy = tap / p.conva.X, fx = tap - fy * p.conva.X;
+                tma_load_im2col_4d_bar(sa, &maps.a[seg], lead_full, cc * BKE, base_w, base_h, img,
+                                       (uint16_t)(fx * p.conva.dil_w), (uint16_t)(fy * p.conva.dil_h));
+              } else if constexpr (!A_MN) {
+                tma_load_3d_bar(sa, &maps.a[seg], lead_full, k0, m0, g);
+              } else if (p.a_fused) {
+                tma_load_4d_bar(sa, &maps.a[seg], lead_full, 0, k0, m0 / CHE, g);
+              } else {
+  #pragma unroll
+                for (int c = 0; c < kBM / CHE; ++c)
+                  tma_load_3d_bar(sa + c * CHUNK_BYTES, &maps.a[seg], lead_full, m0 + c * CHE, k0, g);
+              }
+              if constexpr (!B_MN) {
+                tma_load_3d_bar(sb, &maps.b[seg], lead_full, k0, n0, g);
+              } else if (p.conva.enabled == 2) {
+                int bi, bh, bw;
+                convb_pixel(p.conva, k0, bi, bh, bw);
+                for (int c = 0; c < bn_cta / CHE; ++c) {
+                  int cc, fy, fx;
+                  convb_tap(p.conva, n0 + c * CHE, p.N, CHE, cc, fy, fx);
+                  tma_load_im2col_4d_bar(sb + c * CHUNK_BYTES, &maps.b[seg], lead_full, cc * CHE, bw, bh, bi,
+                                         (uint16_t)(fx * p.conva.dil_w), (uint16_t)(fy * p.conva.dil_h));
+                }
+              } else if (p.b_fused) {
+                tma_load_4d_bar(sb, &maps.b[seg], lead_full, 0, k0, n0 / CHE, g);
+              } else {
+                for (int c = 0; c < bn_cta / CHE; ++c)
+                  tma_load_3d_bar(sb + c * CHUNK_BYTES, &maps.b[seg], lead_full, n0 + c * CHE, k0, g);
+              }
             }
-          }
-          if (++kb == kb_end) { kb = kb_begin; ++seg; }
+            if (++kb == kb_end) { kb = kb_begin; ++seg; }
           }
           if (++s == (uint32_t)rounds) { s = 0; ph ^= 1u; }
         }
