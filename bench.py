@@ -165,13 +165,17 @@ RESNET = {"a": dict(c=64, k=64, h=56, w=56, y=3, x=3, pad_h=1, pad_w=1),
           "d": dict(c=512, k=2048, h=7, w=7, y=1, x=1)}
 
 
-def build_workload(name, dev, sets):
-    """Returns (step_fn, work_per_step, unit, algorithmic_bytes_per_step, bound, dtype, description, kernel)."""
+def build_workload(name, dev, sets, rank=0, world=1):
+    """Returns (step_fn, work_per_step, unit, algorithmic_bytes_per_step, bound, dtype, description, kernel) for this
+    rank's shard of the configuration (rocmlir_b200.sharding: GEMM by columns of B and C, GEMM+GEMM by rows,
+    convolution by batch - backward weight with an all-reduce of the partial gradients -, attention by group)."""
     import math
     import torch
+    import torch.distributed as dist
+    from rocmlir_b200 import sharding
     from rocmlir_b200.gemm import Epilogue, gemm, gemm_gemm, problem, workspace_size
     from rocmlir_b200 import _lib as L
-    g = torch.Generator(device="cpu").manual_seed(1)
+    g = torch.Generator(device="cpu").manual_seed(1 + rank)
 
     def randn(shape, scale, dtype):
         return (torch.randn(shape, generator=g) * scale).to(dtype).to(dev)
@@ -180,16 +184,18 @@ def build_workload(name, dev, sets):
         kind = name[5:]
         if kind in ("f16", "bf16", "f16_bias_relu"):
             dt = torch.bfloat16 if kind == "bf16" else torch.float16
-            m = n = k = 4096
+            m = k = 4096
+            n = sharding.gemm_column_shard(4096, rank, world).size
             ops = [(randn((m, k), 0.1, dt), randn((k, n), 0.1, dt), torch.empty((m, n), dtype=dt, device=dev)) for _ in range(sets)]
             epi = None
             if kind == "f16_bias_relu":
                 epi = Epilogue(bias=randn((n,), 0.1, dt), relu=True, mid_type=L.F16)
             ws = torch.empty(max(16, workspace_size(problem(ops[0][0], ops[0][1], False, False, False, dt))), dtype=torch.uint8, device=dev)
             step = lambda: [gemm(a, b, out=c, epilogue=epi, workspace=ws) for a, b, c in ops]
-            return step, 2.0 * m * n * k * sets, "TFLOP/s", 3.0 * m * n * 2 * sets, "tensor", kind.split("_")[0], \
+            return step, 2.0 * m * n * k * sets, "TFLOP/s", (m * k + k * n + m * n) * 2.0 * sets, "tensor", kind.split("_")[0], \
                 f"{kind} GEMM 4096^3, A,B row-major, f32 accumulate" + (", C' = relu(C + bias[N])" if epi else ""), "gemm_tcgen05_kernel"
-        m, n, k = 2048, 11008, 4096
+        m, k = 2048, 4096
+        n = sharding.gemm_column_shard(11008, rank, world).size
         if kind.startswith("i8"):
             ops = [(torch.randint(-127, 128, (m, k), generator=g, dtype=torch.int8).to(dev),
                     torch.randint(-127, 128, (n, k), generator=g, dtype=torch.int8).to(dev)) for _ in range(sets)]
@@ -209,7 +215,8 @@ def build_workload(name, dev, sets):
             return step, 2.0 * m * n * k * sets, "TFLOP/s", (m * k + n * k + m * n * 2) * sets, "tensor", "fp8", \
                 "fp8-e4m3 GEMM 2048x11008x4096 (B stored N x K), f32 accumulate, x sA*sB, bf16 out", "gemm_tcgen05_kernel"
     if name == "gemm_gemm_f16":
-        m, k1, n1, n2 = 4096, 1024, 1024, 1024
+        k1, n1, n2 = 1024, 1024, 1024
+        m = sharding.shard_range(4096, rank, world, granule=128).size
         ops = [(randn((m, k1), 0.1, torch.float16), randn((k1, n1), 0.1, torch.float16), randn((n1, n2), 0.1, torch.float16),
                 torch.empty((m, n2), dtype=torch.float16, device=dev)) for _ in range(sets)]
         ws = torch.empty(64 << 20, dtype=torch.uint8, device=dev)
@@ -219,25 +226,34 @@ def build_workload(name, dev, sets):
     if name.startswith("conv_"):
         from rocmlir_b200.conv import ConvConfig, conv, workspace_size as conv_ws
         if name == "conv_f32_nchw":
-            cfg = ConvConfig(n=16, c=64, k=64, h=56, w=56, y=3, x=3, pad_h=1, pad_w=1, fil_layout="kcyx", in_layout="nchw", out_layout="nkhw")
+            cfg = ConvConfig(n=sharding.conv_batch_shard(16, rank, world).size, c=64, k=64, h=56, w=56, y=3, x=3, pad_h=1, pad_w=1,
+                             fil_layout="kcyx", in_layout="nchw", out_layout="nkhw")
             dt, direction, scale, lo = torch.float32, 0, None, True
             desc = "fp32 conv2d forward NCHW/KCYX N16 C64 56x56 K64 3x3 s1 p1, uniform[-1,1)"
         else:
             _, _, _, shape, dirname = name.split("_", 4)  # conv_f16_nhwc_<a-d>_<fwd|bwd_data|bwd_weight>
             direction = {"fwd": 0, "bwd_data": 1, "bwd_weight": 2}[dirname]
-            cfg = ConvConfig(n=256, **RESNET[shape])
+            cfg = ConvConfig(n=sharding.conv_batch_shard(256, rank, world).size, **RESNET[shape])
             dt = torch.float16
             desc = f"fp16 NHWC conv N256 {RESNET[shape]} {dirname}, tensors ~ 0.05*N(0,1)"
         nsets = max(1, min(sets, 2))
         ts = []
-        for _ in range(nsets):
-            if dt == torch.float32:
-                mk = lambda nel: (torch.rand(nel, generator=g) * 2 - 1).to(dev)
-            else:
-                mk = lambda nel: (torch.randn(nel, generator=g) * 0.05).to(dt).to(dev)
-            ts.append((mk(cfg.numel("fil")), mk(cfg.numel("in")), mk(cfg.numel("out"))))
+        if dt == torch.float32:
+            mk = lambda nel: (torch.rand(nel, generator=g) * 2 - 1).to(dev)
+        else:
+            mk = lambda nel: (torch.randn(nel, generator=g) * 0.05).to(dt).to(dev)
+        # the filter (gradient) tensors of all sets live in one flat bucket, so that a batch-sharded backward-weight
+        # step needs one all-reduce (gradient bucketing), not one per convolution
+        bucket = mk(cfg.numel("fil") * nsets)
+        for i_set in range(nsets):
+            ts.append((bucket[i_set * cfg.numel("fil"):(i_set + 1) * cfg.numel("fil")], mk(cfg.numel("in")), mk(cfg.numel("out"))))
         ws = torch.empty(max(16, conv_ws(cfg, dt, direction)), dtype=torch.uint8, device=dev)
-        step = lambda: [conv(cfg, direction, f, i, o, workspace=ws) for f, i, o in ts]
+
+        def step():
+            for f, i, o in ts:
+                conv(cfg, direction, f, i, o, workspace=ws)
+            if direction == 2 and world > 1:
+                sharding.allreduce_weight_gradient(bucket)   # the one exchange of the path
         es = 4 if dt == torch.float32 else 2
         abytes = (cfg.numel("fil") + cfg.numel("in") + cfg.numel("out")) * es * nsets
         ai = cfg.flops() / (abytes / nsets)
@@ -246,7 +262,8 @@ def build_workload(name, dev, sets):
     if name.startswith("attention_f16"):
         from rocmlir_b200.attention import attention, flops
         causal = name.endswith("causal")
-        G, S, D = 512, 2048, 128
+        S, D = 2048, 128
+        G = sharding.attention_group_shard(512, rank, world).size
         q = randn((G, S, D), 1.0, torch.float16); kk = randn((G, D, S), 1.0, torch.float16); v = randn((G, S, D), 1.0, torch.float16)
         o = torch.empty_like(q)
         step = lambda: attention(q, kk, v, scale=1.0 / math.sqrt(D), causal=causal, out=o)
@@ -262,25 +279,41 @@ WORKLOADS = (["gemm_f16", "gemm_bf16", "gemm_f16_bias_relu", "gemm_i8", "gemm_i8
 
 def run_secondary(args, name, rank, world, local_rank):
     import torch
+    import torch.distributed as dist
     from rocmlir_b200 import _lib as L
+    from rocmlir_b200 import sharding
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    step, work, unit, abytes, bound, dtype, desc, kernel = build_workload(name, dev, args.sets)
+    step, work, unit, abytes, bound, dtype, desc, kernel = build_workload(name, dev, args.sets, rank, world)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
     for _ in range(max(3, args.warmup)):
         step()
-    torch.cuda.synchronize()
+    barrier()
     sampler = ClockSampler(local_rank)
-    sampler.start()
+    if rank == 0:
+        sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     l0 = L.launch_count()
     e0.record()
     for _ in range(args.steps):
         step()
     e1.record()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1)
+    barrier()
+    ms = sharding.job_time_ms(e0.elapsed_time(e1), device=dev)     # slowest rank
     launches = L.launch_count() - l0
-    clocks = sampler.stop()
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:   # whole-job work: the shards need not be equal
+        t = torch.tensor([float(work), float(abytes)], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        work, abytes = t.tolist()
+    if rank != 0:
+        return
     peaks = measured_peaks()
     value = work * args.steps / (ms * 1e-3) / 1e12
     capped = bool(clocks) and "sw_power_cap" in (clocks.get("reasons") or [])
@@ -288,16 +321,20 @@ def run_secondary(args, name, rank, world, local_rank):
     if bound == "tensor":
         # the measured tensor peak is a bf16 figure; 8-bit kinds are held against twice it, f32 (3xTF32) against a sixth
         mult = {"i8": 2.0, "fp8": 2.0, "f32": 1.0 / 6.0}.get(dtype, 1.0)
-        peak, achieved, runit = peaks[kind] * mult, value, unit
+        peak, achieved, runit = peaks[kind] * mult * world, value, unit
     else:
-        peak, achieved, runit = peaks["hbm"], abytes * args.steps / (ms * 1e-3) / 1e9, "GB/s"
-    line = {"metric": f"{unit}, {desc}", "value": value, "unit": unit, "n_gpus": 1, "steps": args.steps,
-            "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+        peak, achieved, runit = peaks["hbm"] * world, abytes * args.steps / (ms * 1e-3) / 1e9, "GB/s"
+    line = {"metric": f"{unit}, {desc}", "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "weak" if world == 1 else "strong",
             "vs_baseline": None, "dtype": dtype, "data": "synthetic",
             "config": {"workload": desc, "kernel_status": L.kernel_status(),
-                       "l2": "operand sets rotate / tensors exceed L2" if abytes > 126e6 else "working set fits L2 (stated)"},
+                       "parallelism": "one GPU" if world == 1 else f"the configuration sharded over {world} GPUs "
+                                      "(GEMM: columns; convolution: batch; attention: groups)",
+                       "l2": "operand sets rotate / tensors exceed L2" if abytes > 126e6 * world else "working set fits L2 (stated)"},
             "roofline": {"bound": bound, "achieved": achieved, "peak": peak, "unit": runit, "frac": achieved / peak,
-                         "peak_source": f"{peaks['source']} ({kind}; {'HBM copy' if bound == 'hbm' else 'cuBLAS bf16 x type factor'})",
+                         "peak_source": f"{peaks['source']} ({kind}; {'HBM copy' if bound == 'hbm' else 'cuBLAS bf16 x type factor'}"
+                                        + (f" x {world} GPUs)" if world > 1 else ")"),
                          "traffic": None, "algorithmic_bytes": abytes, "kernel": kernel,
                          "avg_launch_ms": ms / max(1, launches)},
             "e2e": None, "gpu_launches": int(launches), "clocks": clocks}
@@ -325,9 +362,15 @@ def main():
         run_reference(args, rank, world)
         return
     if args.workload != "gemm_f16":
-        if rank == 0:
-            for name in (WORKLOADS[1:] if args.workload == "all" else [args.workload]):
-                run_secondary(args, name, rank, world, local_rank)
+        if world > 1:
+            import torch
+            import torch.distributed as dist
+            torch.cuda.set_device(local_rank)
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        for name in (WORKLOADS[1:] if args.workload == "all" else [args.workload]):
+            run_secondary(args, name, rank, world, local_rank)
+        if world > 1:
+            dist.destroy_process_group()
         return
 
     import torch

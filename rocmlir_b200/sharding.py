@@ -71,12 +71,15 @@ def job_time_ms(local_ms: float, group: Optional[dist.ProcessGroup] = None, devi
     return float(t.item())
 
 
-def allreduce_weight_gradient(partial: torch.Tensor, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
+def allreduce_weight_gradient(partial: torch.Tensor, group: Optional[dist.ProcessGroup] = None, async_op: bool = False):
     """Sums the per-rank partial filter gradients of a batch-split backward-weight convolution in place.
-    The partials should be f32 so that the sum over ranks rounds once at the caller's final conversion."""
+    The partials should be f32 so that the sum over ranks rounds once at the caller's final conversion.
+    With `async_op` the collective runs on the communication stream while the caller launches the next layer's
+    kernels; the returned handle's wait() orders the caller's stream after it (None when there is nothing to do)."""
     if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
-        dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=group)
-    return partial
+        work = dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=group, async_op=async_op)
+        return work if async_op else partial
+    return None if async_op else partial
 
 
 def gather_columns(c_local: torch.Tensor, n: int, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
