@@ -295,6 +295,27 @@ def run_secondary(args, name, rank, world, local_rank):
     for _ in range(max(3, args.warmup)):
         step()
     barrier()
+    # A step of small kernels is bound by the host's launch path (about 11 us per library call, 18 us through the
+    # Python mirror), so the step is captured once into a CUDA graph and replayed: the library allocates nothing and
+    # its launches are capturable. Not under torchrun (the NCCL all-reduce of a step stays outside graphs here).
+    run, per_step_launches, graphed = step, None, False
+    if not args.no_graph and world == 1:
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                graph = torch.cuda.CUDAGraph()
+                l0 = L.launch_count()
+                with torch.cuda.graph(graph, stream=side):
+                    step()
+                per_step_launches = L.launch_count() - l0
+            torch.cuda.current_stream().wait_stream(side)
+            graph.replay()
+            torch.cuda.synchronize()
+            run, graphed = graph.replay, True
+        except Exception as e:   # capture refused: time the plain step
+            print(f"[bench] graph capture failed ({e}); timing direct launches", file=sys.stderr)
+            torch.cuda.synchronize()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
@@ -302,11 +323,11 @@ def run_secondary(args, name, rank, world, local_rank):
     l0 = L.launch_count()
     e0.record()
     for _ in range(args.steps):
-        step()
+        run()
     e1.record()
     barrier()
     ms = sharding.job_time_ms(e0.elapsed_time(e1), device=dev)     # slowest rank
-    launches = L.launch_count() - l0
+    launches = per_step_launches * args.steps if graphed else L.launch_count() - l0
     clocks = sampler.stop() if rank == 0 else None
     if world > 1:   # whole-job work: the shards need not be equal
         t = torch.tensor([float(work), float(abytes)], dtype=torch.float64, device=dev)
@@ -329,6 +350,7 @@ def run_secondary(args, name, rank, world, local_rank):
             "scaling": "weak" if world == 1 else "strong",
             "vs_baseline": None, "dtype": dtype, "data": "synthetic",
             "config": {"workload": desc, "kernel_status": L.kernel_status(),
+                       "launch": "CUDA graph replay of one captured step" if graphed else "direct launches",
                        "parallelism": "one GPU" if world == 1 else f"the configuration sharded over {world} GPUs "
                                       "(GEMM: columns; convolution: batch; attention: groups)",
                        "l2": "operand sets rotate / tensors exceed L2" if abytes > 126e6 * world else "working set fits L2 (stated)"},
@@ -352,6 +374,7 @@ def main():
     ap.add_argument("--variant", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (used for ncu captures)")
+    ap.add_argument("--no-graph", action="store_true", help="secondary workloads: direct launches instead of a CUDA graph")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 

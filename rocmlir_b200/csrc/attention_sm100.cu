@@ -838,10 +838,10 @@ extern "C" RbStatus rbAttention(const RbAttentionProblem* p, const void* q, cons
   if (p->seq_q > kQT && p->scale >= 0.0f) {
     // two query tiles per CTA (the fast path folds the scale into the row maximum, which needs scale >= 0)
     const long long ctas2 = (long long)p->g * ((kp.q_tiles + 1) / 2);
-    RB_CUDA_TRY(cudaFuncSetAttribute(attention_fwd2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Att2Smem::kTotal));
+    if (ensure_dynamic_smem(reinterpret_cast<const void*>(attention_fwd2_kernel), Att2Smem::kTotal) != RB_SUCCESS) return RB_CUDA_ERROR;
     attention_fwd2_kernel<<<(unsigned)ctas2, kAtt2Threads, Att2Smem::kTotal, stream>>>(maps, kp);
   } else {
-    RB_CUDA_TRY(cudaFuncSetAttribute(attention_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AttSmem::kTotal));
+    if (ensure_dynamic_smem(reinterpret_cast<const void*>(attention_fwd_kernel), AttSmem::kTotal) != RB_SUCCESS) return RB_CUDA_ERROR;
     attention_fwd_kernel<<<(unsigned)ctas, kAttThreads, AttSmem::kTotal, stream>>>(maps, kp);
   }
   RB_CUDA_TRY(cudaGetLastError());

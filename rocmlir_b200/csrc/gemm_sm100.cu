@@ -642,7 +642,10 @@ RbStatus rb::gemm_run(const RbGemmProblem* p, const RbEpilogue* epi, const void*
   GemmKernel kern = ctas == 2 ? pick_kernel<2>(kind, a_mn, b_mn) : pick_kernel<1>(kind, a_mn, b_mn);
   const bool kernel_epi_vec = splits == 1 && epi_vec;  // with a K split the reduction kernel applies the epilogue
   const int smem = ctas == 2 ? GemmSmemLayout<2>::total(stages, bn, kernel_epi_vec) : GemmSmemLayout<1>::total(stages, bn, kernel_epi_vec);
-  RB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  {
+    const RbStatus sst = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem);
+    if (sst != RB_SUCCESS) return sst;
+  }
 
   cudaLaunchConfig_t lc;
   memset(&lc, 0, sizeof(lc));

@@ -1,7 +1,9 @@
 #include "lib_state.h"
 
 #include <atomic>
+#include <map>
 #include <mutex>
+#include <utility>
 
 namespace rb {
 
@@ -35,6 +37,19 @@ RbStatus fail(RbStatus st, const std::string& msg) {
 }
 
 unsigned long long* trace_buffer(size_t need_u64) { return (t_trace && t_trace_len >= need_u64) ? t_trace : nullptr; }
+
+RbStatus ensure_dynamic_smem(const void* kernel, int bytes) {
+  static std::mutex mu;
+  static std::map<std::pair<int, const void*>, int> granted;   // largest size set so far
+  int dev = 0;
+  RB_CUDA_TRY(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lock(mu);
+  int& have = granted[std::make_pair(dev, kernel)];
+  if (bytes <= have) return RB_SUCCESS;
+  RB_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  have = bytes;
+  return RB_SUCCESS;
+}
 
 void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
 

@@ -61,6 +61,10 @@ size_t gemm_workspace_bytes(const RbGemmProblem* p, int implicit_operand);
 RbStatus f32_planes(const float* src, float* hi, float* lo, int groups, int R, int C, int pitch, bool transpose,
                     bool split, void* stream);
 
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per (device, kernel, size): the call costs microseconds and
+// small problems are bound by the host's launch path.
+RbStatus ensure_dynamic_smem(const void* kernel, int bytes);
+
 // Device trace buffer set with rbSetTraceBuffer for the calling thread (nullptr when `need` words do not fit).
 unsigned long long* trace_buffer(size_t need_u64);
 
