@@ -12,6 +12,14 @@
 //   backward dat in[(n,h,w), c]      = sum_{y,x,k} col2im(out)[(n,h,w), (y,x,k)] * fil[(y,x,k), c]
 // Groups are the GEMM batch dimension. Index relation and output-size rule are the reference's
 // (in_h = ho*stride + y*dil - pad; mlir/include/mlir/Dialect/Rock/Generator/ConvGenerator.h:98-104).
+//
+// Implicit GEMM (no im2col matrix in memory) for dense NHWC tensors of one group whose channel count is a multiple
+// of 128 bytes: the GEMM producer fetches the im2col tiles itself with TMA im2col descriptors -
+//   forward       A from the input (16-bit and 8-bit types; f32 through TF32 planes of the input, hi and lo, which
+//                 one pass builds and, for an NCHW input, transposes)
+//   backward data A from the output gradient with padding (fil-1)*dil - pad and the filter taps mirrored; with a
+//                 stride the gradient is zero-upsampled into the workspace first
+//   backward wt   B from the input (K index = output pixel), A = the NHWK output gradient in place.
 #include <cuda_runtime.h>
 #include <string.h>
 
