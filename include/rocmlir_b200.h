@@ -177,6 +177,30 @@ RB_EXPORT RbStatus rbConvGetGemmProblem(const RbConvProblem *p, RbGemmProblem *o
 RB_EXPORT RbStatus rbConv(const RbConvProblem *p, void *filter, void *input, void *output, void *workspace,
                           size_t workspace_bytes, void *stream);
 
+/* The same three operations with a third image dimension (depth), as rocmlir-gen builds them for layouts with
+ * three image letters (mlir/tools/rocmlir-gen/rocmlir-gen.cpp:3545-3581; letters and their digit aliases in
+ * mlir/lib/Dialect/Rock/Generator/ConvGenerator.cpp:622-627): filter letters g k c z y x, input n g c d h w,
+ * output n g k d h w, each a 6-letter permutation. Index relation and size rule per dimension are rbConv's.
+ * A problem whose depths are all 1 is the 2-D problem on the same bytes and runs as such. Otherwise the depth is
+ * folded: the filter depth taps become extra input channels of a 2-D convolution over N * Do images
+ * (in2[g,(n,do),h,w,(z,c)] = in[n,g,c,do*stride_d + z*dil_d - pad_d,h,w], zero outside), with one gather pass
+ * before and one permuting pass after the 2-D kernels; backward data sums the Z taps of every input voxel in f32. */
+typedef struct RbConv3dProblem {
+  int32_t n, g, c, k;
+  int32_t d, h, w, z, y, x;
+  int32_t stride_d, stride_h, stride_w, dil_d, dil_h, dil_w;
+  int32_t pad_d, pad_h, pad_w, pad_d_r, pad_h_r, pad_w_r;
+  int32_t dout, ho, wo;
+  int32_t data_type; /* as in RbConvProblem */
+  int32_t direction;
+  int32_t f32_mode;
+  char fil_layout[8], in_layout[8], out_layout[8];
+} RbConv3dProblem;
+
+RB_EXPORT size_t rbConv3dWorkspaceSize(const RbConv3dProblem *p);
+RB_EXPORT RbStatus rbConv3d(const RbConv3dProblem *p, void *filter, void *input, void *output, void *workspace,
+                            size_t workspace_bytes, void *stream);
+
 /* rock.attention (mlir/include/mlir/Dialect/Rock/IR/RockOps.td:208-254): per group g
  *   O = softmax_k( f(Q . K) ) . V      Q [G][Sq][D], K [G][D][Sk] (trans_k: [G][Sk][D]), V [G][Sk][Dv], O [G][Sq][Dv]
  * the buffers of rocmlir-gen's rock_attention kernel (rocmlir-gen.cpp:2149-2200, 2264-2328). The reference has no

@@ -230,6 +230,106 @@ def conv_i8(p: Conv, fil: np.ndarray, inp: np.ndarray, wrap_product: bool = True
     return res
 
 
+# ---- convolution with three image dimensions ----------------------------------------------------------------------
+class _OrcConv3(C.Structure):
+    _fields_ = [(n, C.c_int64) for n in ("n", "g", "c", "k", "d", "h", "w", "z", "y", "x", "dout", "ho", "wo",
+                                         "stride_d", "stride_h", "stride_w", "dil_d", "dil_h", "dil_w",
+                                         "pad_d", "pad_h", "pad_w")] + \
+               [("fs", C.c_int64 * 6), ("is_", C.c_int64 * 6), ("os", C.c_int64 * 6)]
+
+
+@dataclass
+class Conv3d:
+    """Sizes of a convolution over (d, h, w); c and k per group; pad_* are the left paddings, pad_*_r the right ones
+    (default: equal). Layout letters: filter g k c z y x, input n g c d h w, output n g k d h w."""
+    n: int
+    c: int
+    k: int
+    d: int
+    h: int
+    w: int
+    z: int
+    y: int
+    x: int
+    g: int = 1
+    stride_d: int = 1
+    stride_h: int = 1
+    stride_w: int = 1
+    dil_d: int = 1
+    dil_h: int = 1
+    dil_w: int = 1
+    pad_d: int = 0
+    pad_h: int = 0
+    pad_w: int = 0
+    pad_d_r: Optional[int] = None
+    pad_h_r: Optional[int] = None
+    pad_w_r: Optional[int] = None
+    fil_layout: str = "gkczyx"
+    in_layout: str = "ngcdhw"
+    out_layout: str = "ngkdhw"
+    dout: int = field(init=False)
+    ho: int = field(init=False)
+    wo: int = field(init=False)
+
+    def __post_init__(self):
+        for ax in "dhw":
+            if getattr(self, f"pad_{ax}_r") is None:
+                setattr(self, f"pad_{ax}_r", getattr(self, f"pad_{ax}"))
+        self.dout = out_dim(self.d, self.z, self.pad_d, self.pad_d_r, self.stride_d, self.dil_d)
+        self.ho = out_dim(self.h, self.y, self.pad_h, self.pad_h_r, self.stride_h, self.dil_h)
+        self.wo = out_dim(self.w, self.x, self.pad_w, self.pad_w_r, self.stride_w, self.dil_w)
+
+    def sizes(self):
+        return {"fil": {"g": self.g, "k": self.k, "c": self.c, "z": self.z, "y": self.y, "x": self.x},
+                "in": {"n": self.n, "g": self.g, "c": self.c, "d": self.d, "h": self.h, "w": self.w},
+                "out": {"n": self.n, "g": self.g, "k": self.k, "d": self.dout, "h": self.ho, "w": self.wo}}
+
+    def numel(self, which: str) -> int:
+        return int(np.prod(list(self.sizes()[which].values())))
+
+    def shape(self, which: str):
+        """Shape of the tensor as stored, i.e. in its layout's order."""
+        s = self.sizes()[which]
+        lay = {"fil": self.fil_layout, "in": self.in_layout, "out": self.out_layout}[which]
+        return tuple(s[ch] for ch in lay)
+
+    def to_c(self) -> _OrcConv3:
+        s = self.sizes()
+        fs = layout_strides(self.fil_layout, s["fil"])
+        is_ = layout_strides(self.in_layout, s["in"])
+        os_ = layout_strides(self.out_layout, s["out"])
+        p = _OrcConv3(self.n, self.g, self.c, self.k, self.d, self.h, self.w, self.z, self.y, self.x, self.dout,
+                      self.ho, self.wo, self.stride_d, self.stride_h, self.stride_w, self.dil_d, self.dil_h,
+                      self.dil_w, self.pad_d, self.pad_h, self.pad_w)
+        p.fs = (C.c_int64 * 6)(*[fs[ch] for ch in "gkczyx"])
+        p.is_ = (C.c_int64 * 6)(*[is_[ch] for ch in "ngcdhw"])
+        p.os = (C.c_int64 * 6)(*[os_[ch] for ch in "ngkdhw"])
+        return p
+
+
+def conv3d_f32(p: Conv3d, direction: int, fil: Optional[np.ndarray], inp: Optional[np.ndarray],
+               out: Optional[np.ndarray], threads: int = 1, f64: bool = False) -> np.ndarray:
+    """Flat tensors in their storage layouts; returns the flat result tensor of the direction."""
+    which = {FWD: "out", BWD_DATA: "in", BWD_WEIGHT: "fil"}[direction]
+    res = np.zeros(p.numel(which), np.float64 if f64 else np.float32)
+    fil = None if fil is None else np.ascontiguousarray(fil, np.float32)
+    inp = None if inp is None else np.ascontiguousarray(inp, np.float32)
+    out = None if out is None else np.ascontiguousarray(out, np.float32)
+    cp = p.to_c()
+    fn = lib().orc_conv3d_f64 if f64 else lib().orc_conv3d_f32
+    fn(C.byref(cp), C.c_int(direction), _p(fil), _p(inp), _p(out), _p(res), C.c_int(threads))
+    return res
+
+
+def conv3d_i8(p: Conv3d, fil: np.ndarray, inp: np.ndarray, threads: int = 1) -> np.ndarray:
+    res = np.zeros(p.numel("out"), np.int64)
+    fil = np.ascontiguousarray(fil, np.int8)
+    inp = np.ascontiguousarray(inp, np.int8)
+    cp = p.to_c()
+    lib().orc_conv3d_i8(C.byref(cp), _p(fil), _p(inp), _p(res), C.c_int(threads))
+    return res
+
+
 # ---- attention / gemm+gemm ---------------------------------------------------------------------------------------
 def attention(q, k, v, *, elem_type: int, scale=None, bias=None, mask=None, mask_fill: float = 0.0,
               scale_scalar: Optional[float] = None, causal: bool = False, g_range=None, threads: int = 1):

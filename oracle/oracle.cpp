@@ -390,6 +390,117 @@ ORC_API void orc_conv_f64(const OrcConv* p, int dir, const float* fil, const flo
 }
 
 // ------------------------------------------------------------------------------------------------
+// Convolution with three image dimensions: the same generated loop nest with nImageDims = 3
+// (rocmlir-gen.cpp:1745-1830). Image dimensions are numbered 0 = h, 1 = w, 2 = d
+// (parseConvTensorLayout, rocmlir-gen.cpp:1504-1542), and the reduction loops run in that order after the
+// reduction channel, so the depth tap is the innermost loop:
+//   fwd: c, y, x, z      bwd-weight: n, ho, wo, do      bwd-data: k, y, x, z
+// Strides for filter (g,k,c,z,y,x), input (n,g,c,d,h,w), output (n,g,k,do,ho,wo).
+// ------------------------------------------------------------------------------------------------
+struct OrcConv3 {
+  int64_t n, g, c, k, d, h, w, z, y, x, dout, ho, wo;
+  int64_t stride_d, stride_h, stride_w, dil_d, dil_h, dil_w, pad_d, pad_h, pad_w;  // left paddings
+  int64_t fs[6], is[6], os[6];
+};
+
+template <typename TIn, typename TAcc>
+static void conv3_impl(const OrcConv3& p, int dir, const TIn* fil, const TIn* in, const TIn* out, TAcc* res, int threads) {
+  auto F = [&](int64_t g, int64_t k, int64_t c, int64_t z, int64_t y, int64_t x) {
+    return g * p.fs[0] + k * p.fs[1] + c * p.fs[2] + z * p.fs[3] + y * p.fs[4] + x * p.fs[5];
+  };
+  auto I = [&](int64_t n, int64_t g, int64_t c, int64_t d, int64_t h, int64_t w) {
+    return n * p.is[0] + g * p.is[1] + c * p.is[2] + d * p.is[3] + h * p.is[4] + w * p.is[5];
+  };
+  auto O = [&](int64_t n, int64_t g, int64_t k, int64_t d, int64_t h, int64_t w) {
+    return n * p.os[0] + g * p.os[1] + k * p.os[2] + d * p.os[3] + h * p.os[4] + w * p.os[5];
+  };
+  auto mac = [](TAcc acc, TIn a, TIn b) -> TAcc {
+    const TAcc mul = (TAcc)a * (TAcc)b;
+    return acc + mul;
+  };
+  const int nt = threads > 0 ? threads : 1;
+  if (dir == 0) {
+#pragma omp parallel for collapse(3) num_threads(nt) schedule(static)
+    for (int64_t n = 0; n < p.n; ++n)
+      for (int64_t g = 0; g < p.g; ++g)
+        for (int64_t k = 0; k < p.k; ++k)
+          for (int64_t od = 0; od < p.dout; ++od)
+            for (int64_t ho = 0; ho < p.ho; ++ho)
+              for (int64_t wo = 0; wo < p.wo; ++wo) {
+                TAcc acc = 0;
+                for (int64_t c = 0; c < p.c; ++c)
+                  for (int64_t y = 0; y < p.y; ++y)
+                    for (int64_t x = 0; x < p.x; ++x)
+                      for (int64_t z = 0; z < p.z; ++z) {
+                        const int64_t ih = ho * p.stride_h + y * p.dil_h - p.pad_h;
+                        const int64_t iw = wo * p.stride_w + x * p.dil_w - p.pad_w;
+                        const int64_t id = od * p.stride_d + z * p.dil_d - p.pad_d;
+                        if (ih < 0 || ih >= p.h || iw < 0 || iw >= p.w || id < 0 || id >= p.d) continue;
+                        acc = mac(acc, fil[F(g, k, c, z, y, x)], in[I(n, g, c, id, ih, iw)]);
+                      }
+                res[O(n, g, k, od, ho, wo)] = acc;
+              }
+  } else if (dir == 2) {
+#pragma omp parallel for collapse(3) num_threads(nt) schedule(static)
+    for (int64_t g = 0; g < p.g; ++g)
+      for (int64_t k = 0; k < p.k; ++k)
+        for (int64_t c = 0; c < p.c; ++c)
+          for (int64_t z = 0; z < p.z; ++z)
+            for (int64_t y = 0; y < p.y; ++y)
+              for (int64_t x = 0; x < p.x; ++x) {
+                TAcc acc = 0;
+                for (int64_t n = 0; n < p.n; ++n)
+                  for (int64_t ho = 0; ho < p.ho; ++ho)
+                    for (int64_t wo = 0; wo < p.wo; ++wo)
+                      for (int64_t od = 0; od < p.dout; ++od) {
+                        const int64_t ih = ho * p.stride_h + y * p.dil_h - p.pad_h;
+                        const int64_t iw = wo * p.stride_w + x * p.dil_w - p.pad_w;
+                        const int64_t id = od * p.stride_d + z * p.dil_d - p.pad_d;
+                        if (ih < 0 || ih >= p.h || iw < 0 || iw >= p.w || id < 0 || id >= p.d) continue;
+                        acc = mac(acc, out[O(n, g, k, od, ho, wo)], in[I(n, g, c, id, ih, iw)]);
+                      }
+                res[F(g, k, c, z, y, x)] = acc;
+              }
+  } else {
+#pragma omp parallel for collapse(3) num_threads(nt) schedule(static)
+    for (int64_t n = 0; n < p.n; ++n)
+      for (int64_t g = 0; g < p.g; ++g)
+        for (int64_t c = 0; c < p.c; ++c)
+          for (int64_t id = 0; id < p.d; ++id)
+            for (int64_t ih = 0; ih < p.h; ++ih)
+              for (int64_t iw = 0; iw < p.w; ++iw) {
+                TAcc acc = 0;
+                for (int64_t k = 0; k < p.k; ++k)
+                  for (int64_t y = 0; y < p.y; ++y)
+                    for (int64_t x = 0; x < p.x; ++x)
+                      for (int64_t z = 0; z < p.z; ++z) {
+                        const int64_t th = ih + p.pad_h - y * p.dil_h;
+                        const int64_t tw = iw + p.pad_w - x * p.dil_w;
+                        const int64_t td = id + p.pad_d - z * p.dil_d;
+                        if (th < 0 || tw < 0 || td < 0 || th % p.stride_h || tw % p.stride_w || td % p.stride_d) continue;
+                        const int64_t ho = th / p.stride_h, wo = tw / p.stride_w, od = td / p.stride_d;
+                        if (ho >= p.ho || wo >= p.wo || od >= p.dout) continue;
+                        acc = mac(acc, fil[F(g, k, c, z, y, x)], out[O(n, g, k, od, ho, wo)]);
+                      }
+                res[I(n, g, c, id, ih, iw)] = acc;
+              }
+  }
+}
+
+ORC_API void orc_conv3d_f32(const OrcConv3* p, int dir, const float* fil, const float* in, const float* out, float* res,
+                            int threads) {
+  conv3_impl<float, float>(*p, dir, fil, in, out, res, threads);
+}
+ORC_API void orc_conv3d_f64(const OrcConv3* p, int dir, const float* fil, const float* in, const float* out, double* res,
+                            int threads) {
+  conv3_impl<float, double>(*p, dir, fil, in, out, res, threads);
+}
+// i8 forward with the operands widened before the product (exact integer arithmetic)
+ORC_API void orc_conv3d_i8(const OrcConv3* p, const int8_t* fil, const int8_t* in, int64_t* res, int threads) {
+  conv3_impl<int8_t, int64_t>(*p, 0, fil, in, nullptr, res, threads);
+}
+
+// ------------------------------------------------------------------------------------------------
 // Attention (rocmlir-gen.cpp:2507-2638; op order pinned by mlir/test/rocmlir-gen/attention-kernel.mlir).
 // Every TOSA op is typed with the element type T, and tosa.matmul accumulates in its RESULT type
 // (external/llvm-project/mlir/lib/Conversion/TosaToLinalg/TosaToLinalgNamed.cpp:645-657), so with

@@ -43,6 +43,14 @@ class RbConvProblem(C.Structure):
                [("fil_layout", C.c_char * 8), ("in_layout", C.c_char * 8), ("out_layout", C.c_char * 8)]
 
 
+class RbConv3dProblem(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("n", "g", "c", "k", "d", "h", "w", "z", "y", "x", "stride_d", "stride_h",
+                                         "stride_w", "dil_d", "dil_h", "dil_w", "pad_d", "pad_h", "pad_w", "pad_d_r",
+                                         "pad_h_r", "pad_w_r", "dout", "ho", "wo", "data_type", "direction",
+                                         "f32_mode")] + \
+               [("fil_layout", C.c_char * 8), ("in_layout", C.c_char * 8), ("out_layout", C.c_char * 8)]
+
+
 class RbAttentionProblem(C.Structure):
     _fields_ = [("g", C.c_int32), ("seq_q", C.c_int32), ("seq_k", C.c_int32), ("head_qk", C.c_int32),
                 ("head_v", C.c_int32), ("trans_q", C.c_int32), ("trans_k", C.c_int32), ("trans_v", C.c_int32),
@@ -95,6 +103,11 @@ def lib() -> C.CDLL:
         l.rbConv.restype = C.c_int
         l.rbConv.argtypes = [C.POINTER(RbConvProblem), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t,
                              C.c_void_p]
+        l.rbConv3dWorkspaceSize.restype = C.c_size_t
+        l.rbConv3dWorkspaceSize.argtypes = [C.POINTER(RbConv3dProblem)]
+        l.rbConv3d.restype = C.c_int
+        l.rbConv3d.argtypes = [C.POINTER(RbConv3dProblem), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t,
+                               C.c_void_p]
         l.rbAttention.restype = C.c_int
         l.rbAttention.argtypes = [C.POINTER(RbAttentionProblem), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                   C.c_void_p]

@@ -124,3 +124,112 @@ def conv(cfg: ConvConfig, direction: int, filter: torch.Tensor, input: torch.Ten
                     workspace.numel() * workspace.element_size() if workspace is not None else 0, stream)
     L.check(st)
     return {FWD: output, BWD_DATA: input, BWD_WEIGHT: filter}[direction]
+
+
+# ---- three image dimensions ----------------------------------------------------------------------------------------
+def _letters3(layout: str, kind: str) -> str:
+    """Digit aliases 0 1 2 -> h w d (y x z for the filter), as ConvGenerator.cpp:622-627 translates them."""
+    a, b, c = ("y", "x", "z") if kind == "f" else ("h", "w", "d")
+    return layout.replace("0", a).replace("1", b).replace("2", c)
+
+
+def _add_group3(layout: str, channel: str) -> str:
+    if "g" in layout:
+        return layout
+    if channel == "f":
+        return "g" + layout
+    if layout[:2] == "n" + channel:
+        return "ng" + channel + layout[2:]
+    if layout[0] == "n" and layout[-1] == channel:
+        return layout[:-1] + "g" + channel
+    return "g" + layout
+
+
+@dataclass
+class Conv3dConfig:
+    """rocmlir-gen's convolution flags with the depth ones (-in_d -fil_d -conv_stride_d -dilation_d -padding_d_l/_r,
+    rocmlir-gen.cpp:171-260); layouts over g k c z y x / n g c d h w / n g k d h w or their digit spellings."""
+    n: int
+    c: int
+    k: int
+    d: int
+    h: int
+    w: int
+    z: int
+    y: int
+    x: int
+    g: int = 1
+    stride_d: int = 1
+    stride_h: int = 1
+    stride_w: int = 1
+    dil_d: int = 1
+    dil_h: int = 1
+    dil_w: int = 1
+    pad_d: int = 0
+    pad_h: int = 0
+    pad_w: int = 0
+    pad_d_r: Optional[int] = None
+    pad_h_r: Optional[int] = None
+    pad_w_r: Optional[int] = None
+    fil_layout: str = "gkzyxc"
+    in_layout: str = "ndhwgc"
+    out_layout: str = "ndhwgk"
+
+    def __post_init__(self):
+        self.fil_layout = _letters3(self.fil_layout, "f")
+        self.in_layout = _letters3(self.in_layout, "c")
+        self.out_layout = _letters3(self.out_layout, "k")
+        if "k" not in self.out_layout:
+            self.out_layout = self.out_layout.replace("c", "k")
+        if "k" not in self.fil_layout:
+            self.fil_layout = self.fil_layout.replace("n", "k")
+        self.fil_layout = _add_group3(self.fil_layout, "f")
+        self.in_layout = _add_group3(self.in_layout, "c")
+        self.out_layout = _add_group3(self.out_layout, "k")
+        for ax in "dhw":
+            if getattr(self, f"pad_{ax}_r") is None:
+                setattr(self, f"pad_{ax}_r", getattr(self, f"pad_{ax}"))
+        self.dout = out_dim(self.d, self.z, self.pad_d, self.pad_d_r, self.stride_d, self.dil_d)
+        self.ho = out_dim(self.h, self.y, self.pad_h, self.pad_h_r, self.stride_h, self.dil_h)
+        self.wo = out_dim(self.w, self.x, self.pad_w, self.pad_w_r, self.stride_w, self.dil_w)
+
+    def numel(self, which: str) -> int:
+        if which == "fil":
+            return self.g * self.k * self.c * self.z * self.y * self.x
+        if which == "in":
+            return self.n * self.g * self.c * self.d * self.h * self.w
+        return self.n * self.g * self.k * self.dout * self.ho * self.wo
+
+    def flops(self) -> float:
+        return 2.0 * self.n * self.g * self.c * self.k * self.dout * self.ho * self.wo * self.z * self.y * self.x
+
+    def to_c(self, dtype: torch.dtype, direction: int, f32_mode: int = 0) -> L.RbConv3dProblem:
+        p = L.RbConv3dProblem(self.n, self.g, self.c, self.k, self.d, self.h, self.w, self.z, self.y, self.x,
+                              self.stride_d, self.stride_h, self.stride_w, self.dil_d, self.dil_h, self.dil_w,
+                              self.pad_d, self.pad_h, self.pad_w, self.pad_d_r, self.pad_h_r, self.pad_w_r,
+                              self.dout, self.ho, self.wo, rb_dtype(dtype), direction, f32_mode)
+        p.fil_layout = self.fil_layout.encode()
+        p.in_layout = self.in_layout.encode()
+        p.out_layout = self.out_layout.encode()
+        return p
+
+
+def conv3d(cfg: Conv3dConfig, direction: int, filter: torch.Tensor, input: torch.Tensor, output: torch.Tensor, *,
+           workspace: Optional[torch.Tensor] = None, f32_mode: int = 0) -> torch.Tensor:
+    """rbConv3d on flat contiguous CUDA buffers in layout order; returns the tensor the direction produces."""
+    for t_, name in ((filter, "fil"), (input, "in"), (output, "out")):
+        if not t_.is_cuda or not t_.is_contiguous():
+            raise L.RbError(L.INVALID_PARAM, "tensors must be contiguous CUDA buffers (the library has no CPU path)")
+        if t_.numel() != cfg.numel(name):
+            raise L.RbError(L.INVALID_PARAM, f"{name} has {t_.numel()} elements, expected {cfg.numel(name)}")
+    p = cfg.to_c(input.dtype, direction, f32_mode)
+    lib = L.lib()
+    ws_bytes = int(lib.rbConv3dWorkspaceSize(C.byref(p)))
+    if ws_bytes and (workspace is None or workspace.numel() * workspace.element_size() < ws_bytes):
+        workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=input.device)
+    stream = torch.cuda.current_stream(input.device).cuda_stream
+    st = lib.rbConv3d(C.byref(p), filter.data_ptr(), input.data_ptr(), output.data_ptr(),
+                      workspace.data_ptr() if workspace is not None else None,
+                      workspace.numel() * workspace.element_size() if workspace is not None else 0, stream)
+    L.check(st)
+    return {FWD: output, BWD_DATA: input, BWD_WEIGHT: filter}[direction]

@@ -238,7 +238,7 @@ bool is_dense_in_order(const long long* strides, const long long* sizes, const i
   return true;
 }
 
-RbStatus make_plan(const RbConvProblem* p, ConvPlan* pl) {
+RbStatus make_plan(const RbConvProblem* p, ConvPlan* pl, int result_type = -1) {
   if (!p) return fail(RB_INVALID_PARAM, "problem is NULL");
   if (p->n <= 0 || p->g <= 0 || p->c <= 0 || p->k <= 0 || p->h <= 0 || p->w <= 0 || p->y <= 0 || p->x <= 0 ||
       p->stride_h <= 0 || p->stride_w <= 0 || p->dil_h <= 0 || p->dil_w <= 0 || p->pad_h < 0 || p->pad_w < 0 ||
@@ -331,7 +331,9 @@ RbStatus make_plan(const RbConvProblem* p, ConvPlan* pl) {
   } else {
     gp.m = (int)pix_i; gp.n = p->c; gp.k = (int)yxk;
     gp.trans_a = 0; gp.trans_b = 0; gp.trans_c = 0;       // A [M][K] = col2im(out), B [K][N] = filter as (y,x,k) x c
-    gp.c_type = t;
+    gp.c_type = result_type >= 0 ? result_type : t;
+    if (result_type >= 0 && !in_is_mat)
+      return fail(RB_UNSUPPORTED, "a widened input gradient needs the [pixels][channels] input layout");
     pl->a_direct = pointwise && out_is_mat;
     // a 1x1 filter stored (g,k,c) row-major already is the [K][N] matrix
     const int fil_yxkc[5] = {0, 3, 4, 1, 2};
@@ -388,11 +390,13 @@ void launch_es(size_t es, int blocks, cudaStream_t st, K k1, K k2, K k4, Args...
 
 using namespace rb;
 
-extern "C" size_t rbConvWorkspaceSize(const RbConvProblem* p) {
+size_t rb::conv_workspace_bytes(const RbConvProblem* p, int result_type) {
   ConvPlan pl;
-  if (make_plan(p, &pl) != RB_SUCCESS) return 0;
+  if (make_plan(p, &pl, result_type) != RB_SUCCESS) return 0;
   return pl.total;
 }
+
+extern "C" size_t rbConvWorkspaceSize(const RbConvProblem* p) { return rb::conv_workspace_bytes(p, -1); }
 
 extern "C" RbStatus rbConvGetGemmProblem(const RbConvProblem* p, RbGemmProblem* out) {
   ConvPlan pl;
@@ -411,8 +415,13 @@ extern "C" int rbConvKernelCount(const RbConvProblem* p) {
 
 extern "C" RbStatus rbConv(const RbConvProblem* p, void* filter, void* input, void* output, void* workspace,
                            size_t workspace_bytes, void* stream_v) {
+  return rb::conv_run(p, -1, filter, input, output, workspace, workspace_bytes, stream_v);
+}
+
+RbStatus rb::conv_run(const RbConvProblem* p, int result_type, void* filter, void* input, void* output, void* workspace,
+                      size_t workspace_bytes, void* stream_v) {
   ConvPlan pl;
-  RbStatus st = make_plan(p, &pl);
+  RbStatus st = make_plan(p, &pl, result_type);
   if (st != RB_SUCCESS) return st;
   if (!filter || !input || !output) return fail(RB_INVALID_PARAM, "filter, input and output must be device pointers");
   if (pl.total > 0 && (!workspace || workspace_bytes < pl.total))

@@ -61,6 +61,13 @@ size_t gemm_workspace_bytes(const RbGemmProblem* p, int implicit_operand);
 RbStatus f32_planes(const float* src, float* hi, float* lo, int groups, int R, int C, int pitch, bool transpose,
                     bool split, void* stream);
 
+// rbConv / rbConvWorkspaceSize with the result element type overridden (-1: the problem's own). Only backward data
+// into a dense [pixels][channels] input takes an override: the folded 3-D path asks for an f32 gradient so that the
+// sum over its depth taps rounds once.
+size_t conv_workspace_bytes(const RbConvProblem* p, int result_type);
+RbStatus conv_run(const RbConvProblem* p, int result_type, void* filter, void* input, void* output, void* workspace,
+                  size_t workspace_bytes, void* stream);
+
 // cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per (device, kernel, size): the call costs microseconds and
 // small problems are bound by the host's launch path.
 RbStatus ensure_dynamic_smem(const void* kernel, int bytes);

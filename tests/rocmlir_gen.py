@@ -228,8 +228,6 @@ def conv_config(f: Dict[str, str]):
             raise ValueError("channels must be divisible by the group count")
         d = dict(g=g, n=int(f["batchsize"]), c=ci // g, k=co // g, h=int(f["in_h"]), w=int(f["in_w"]),
                  y=int(f["fil_h"]), x=int(f["fil_w"]))
-    if any(k in f for k in ("in_d", "fil_d", "out_d")):
-        raise Unsupported("3-D convolution")
     pad = {}
     for ax in ("h", "w"):
         combined = int(f.get(f"padding_{ax}", 0))
@@ -252,8 +250,22 @@ def conv_config(f: Dict[str, str]):
         pos = [lay.index(c) for c in pair]
         if len(pos) != 2 or abs(pos[0] - pos[1]) != 1:
             raise ValueError(f"unsupported {name} layout: disjointed image dimensions")
-    if len(fl.replace("g", "")) != 4:
-        raise Unsupported("3-D convolution layout")
+    if len(fl.replace("g", "")) == 5:
+        # three image letters: nDims = 3, depth sizes default to 1 (rocmlir-gen.cpp:3545-3581)
+        from rocmlir_b200.conv import Conv3dConfig
+        dd, zz = max(1, int(f.get("in_d", 1))), max(1, int(f.get("fil_d", 1)))
+        combined = int(f.get("padding_d", 0))
+        pd_l, pd_r = int(f.get("padding_d_l", 0)), int(f.get("padding_d_r", 0))
+        if combined > 0 and pd_l == 0 and pd_r == 0:
+            pd_l = pd_r = combined
+        sd, dld = int(f.get("conv_stride_d", 1)), int(f.get("dilation_d", 1))
+        pd_r = fix_right(dd, zz, pd_l, pd_r, sd, dld)
+        cfg3 = Conv3dConfig(d=dd, z=zz, stride_d=sd, stride_h=sh, stride_w=sw, dil_d=dld, dil_h=dh, dil_w=dw,
+                            pad_d=pd_l, pad_h=pad["h"][0], pad_w=pad["w"][0], pad_d_r=pd_r, pad_h_r=pr_h, pad_w_r=pr_w,
+                            fil_layout=fl, in_layout=il, out_layout=ol, **d)
+        if "out_d" in f and int(f["out_d"]) != cfg3.dout:
+            raise ValueError("out_d does not follow from the other sizes")
+        return cfg3
     cfg = ConvConfig(stride_h=sh, stride_w=sw, dil_h=dh, dil_w=dw, pad_h=pad["h"][0], pad_w=pad["w"][0], pad_h_r=pr_h,
                      pad_w_r=pr_w, fil_layout=fl, in_layout=il, out_layout=ol, **d)
     if "out_h" in f and int(f["out_h"]) != cfg.ho or "out_w" in f and int(f["out_w"]) != cfg.wo:
@@ -273,16 +285,28 @@ def run_conv(f: Dict[str, str], direction: int) -> List[int]:
     out_code = oracle.I32 if code == oracle.I8 else code
     if ty.out != out_code:
         raise Unsupported("convolution output type differs from the input type")
-    ocfg = oracle.Conv(n=cfg.n, c=cfg.c, k=cfg.k, h=cfg.h, w=cfg.w, y=cfg.y, x=cfg.x, g=cfg.g, stride_h=cfg.stride_h,
-                       stride_w=cfg.stride_w, dil_h=cfg.dil_h, dil_w=cfg.dil_w, pad_h=cfg.pad_h, pad_w=cfg.pad_w,
-                       pad_h_r=cfg.pad_h_r, pad_w_r=cfg.pad_w_r, fil_layout=cfg.fil_layout, in_layout=cfg.in_layout,
-                       out_layout=cfg.out_layout)
+    three = hasattr(cfg, "dout")
+    if three:
+        from rocmlir_b200.conv import conv3d as conv
+        ocfg = oracle.Conv3d(n=cfg.n, c=cfg.c, k=cfg.k, d=cfg.d, h=cfg.h, w=cfg.w, z=cfg.z, y=cfg.y, x=cfg.x, g=cfg.g,
+                             stride_d=cfg.stride_d, stride_h=cfg.stride_h, stride_w=cfg.stride_w, dil_d=cfg.dil_d,
+                             dil_h=cfg.dil_h, dil_w=cfg.dil_w, pad_d=cfg.pad_d, pad_h=cfg.pad_h, pad_w=cfg.pad_w,
+                             pad_d_r=cfg.pad_d_r, pad_h_r=cfg.pad_h_r, pad_w_r=cfg.pad_w_r, fil_layout=cfg.fil_layout,
+                             in_layout=cfg.in_layout, out_layout=cfg.out_layout)
+    else:
+        ocfg = oracle.Conv(n=cfg.n, c=cfg.c, k=cfg.k, h=cfg.h, w=cfg.w, y=cfg.y, x=cfg.x, g=cfg.g,
+                           stride_h=cfg.stride_h, stride_w=cfg.stride_w, dil_h=cfg.dil_h, dil_w=cfg.dil_w,
+                           pad_h=cfg.pad_h, pad_w=cfg.pad_w, pad_h_r=cfg.pad_h_r, pad_w_r=cfg.pad_w_r,
+                           fil_layout=cfg.fil_layout, in_layout=cfg.in_layout, out_layout=cfg.out_layout)
     fill = Filler(f)
     fil_f, fil_r = fill.tensor(ocfg.numel("fil"), code)
     in_f, in_r = fill.tensor(ocfg.numel("in"), code)
     out_f, out_r = fill.tensor(ocfg.numel("out"), out_code)
     threads = oracle.max_threads()
-    if code == oracle.I8:
+    if three:
+        want = oracle.conv3d_i8(ocfg, fil_r, in_r, threads=threads) if code == oracle.I8 else \
+            oracle.conv3d_f32(ocfg, direction, fil_f, in_f, out_f, threads=threads)
+    elif code == oracle.I8:
         want = oracle.conv_i8(ocfg, fil_r, in_r, threads=threads)
     else:
         want = oracle.conv_f32(ocfg, direction, fil_f, in_f, out_f, threads=threads)
