@@ -148,7 +148,8 @@ RB_EXPORT RbStatus rbGemmHost(const RbGemmProblem *p, const RbEpilogue *epi_host
  * Argument order is (filter, input, output) for all three directions, as in the reference's kernels
  * (ConvGenerator.cpp:825-830); the direction decides which one is written:
  *   0 forward: output; 1 backward data: input; 2 backward weight: filter.
- * i8 (forward only) produces an i32 output, like rocmlir-gen's -t i8. */
+ * i8 (forward only) produces an i32 output and the 8-bit floats RB_F8E4M3 / RB_F8E5M2 (forward only) an f32
+ * output, like rocmlir-gen's -t i8 / fp8 / bf8 (rocmlir-gen.cpp:430-455). */
 typedef struct RbConvProblem {
   int32_t n, g, c, k;
   int32_t h, w, y, x;

@@ -775,8 +775,11 @@ extern "C" RbStatus rbAttention(const RbAttentionProblem* p, const void* q, cons
   if (!(p->data_type == RB_F16 || p->data_type == RB_BF16))
     return fail(RB_UNSUPPORTED, "attention kernels exist for f16 and bf16");
   if (p->trans_q || p->trans_v || p->trans_o) return fail(RB_UNSUPPORTED, "transQ / transV / transO are not supported");
-  if (p->head_qk % 64 || p->head_qk > 128 || p->head_v % 64 || p->head_v > 128)
-    return fail(RB_UNSUPPORTED, "head dimensions must be 64 or 128");
+  // Head dimensions that are not 64 or 128 run as the next multiple of 64: the TMA boxes are 64 elements wide, what
+  // they cover beyond the tensor arrives as zeros (no contribution to Q.K, zero columns of O) and is clipped on the
+  // store of O. A row of Q, K, V or O must still start on a 16-byte boundary.
+  if (p->head_qk % 8 || p->head_qk > 128 || p->head_v % 8 || p->head_v > 128)
+    return fail(RB_UNSUPPORTED, "head dimensions must be multiples of 8, at most 128");
   if (!p->trans_k && p->seq_k % 8) return fail(RB_UNSUPPORTED, "with K stored G x D x Sk, seq_len_k must be a multiple of 8");
   const DeviceInfo* dev = device_info();
   if (!dev) return RB_CUDA_ERROR;
@@ -787,6 +790,7 @@ extern "C" RbStatus rbAttention(const RbAttentionProblem* p, const void* q, cons
   const CUtensorMapDataType dt = p->data_type == RB_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   std::string err;
   const uint64_t G = p->g, Sq = p->seq_q, Sk = p->seq_k, D = p->head_qk, Dv = p->head_v;
+  const uint64_t Dp = (D + 63) / 64 * 64, Dvp = (Dv + 63) / 64 * 64;   // extents the kernels work on
   {
     const uint64_t dims[3] = {D, Sq, G};
     const uint64_t str[2] = {D * 2, Sq * D * 2};
@@ -801,7 +805,7 @@ extern "C" RbStatus rbAttention(const RbAttentionProblem* p, const void* q, cons
   } else {
     const uint64_t dims[3] = {Sk, D, G};
     const uint64_t str[2] = {Sk * 2, D * Sk * 2};
-    const uint32_t box[3] = {64, (uint32_t)D, 1};
+    const uint32_t box[3] = {64, (uint32_t)Dp, 1};
     if (!encode_tiled(&maps.k, dt, 3, k, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B, &err)) return fail(RB_UNSUPPORTED, "K: " + err);
   }
   {
@@ -818,7 +822,7 @@ extern "C" RbStatus rbAttention(const RbAttentionProblem* p, const void* q, cons
   }
   AttParams kp;
   memset(&kp, 0, sizeof(kp));
-  kp.G = p->g; kp.Sq = p->seq_q; kp.Sk = p->seq_k; kp.D = p->head_qk; kp.Dv = p->head_v;
+  kp.G = p->g; kp.Sq = p->seq_q; kp.Sk = p->seq_k; kp.D = (int)Dp; kp.Dv = (int)Dvp;
   kp.trans_k = p->trans_k ? 1 : 0;
   kp.is_bf16 = p->data_type == RB_BF16;
   kp.causal = p->causal ? 1 : 0;
@@ -830,7 +834,7 @@ extern "C" RbStatus rbAttention(const RbAttentionProblem* p, const void* q, cons
   kp.mask_fill = p->mask_fill;
   const uint32_t fmt = kp.is_bf16 ? 1u : 0u;
   kp.idesc_s = make_idesc(1, fmt, fmt, 0, p->trans_k ? 0u : 1u, kQT, kKT);
-  kp.idesc_pv = make_idesc(1, fmt, fmt, 0, 1u, kQT, (uint32_t)p->head_v);
+  kp.idesc_pv = make_idesc(1, fmt, fmt, 0, 1u, kQT, (uint32_t)Dvp);
   kp.status = dev->status_word;
   kp.trace = trace_buffer((size_t)p->g * ((kp.q_tiles + 1) / 2) * 16);
   const long long ctas = (long long)p->g * kp.q_tiles;

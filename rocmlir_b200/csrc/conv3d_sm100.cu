@@ -170,9 +170,10 @@ RbStatus make_plan3d(const RbConv3dProblem* p, Plan3d* pl) {
     return fail(RB_INVALID_PARAM, "dout/ho/wo must equal (in + padL + padR - (fil-1)*dil - 1)/stride + 1 = " +
                                       std::to_string(dout) + " x " + std::to_string(ho) + " x " + std::to_string(wo));
   const int t = p->data_type;
-  if (!(t == RB_F32 || t == RB_F16 || t == RB_BF16 || t == RB_I8)) return fail(RB_INVALID_PARAM, "unsupported element type");
-  if (t == RB_I8 && p->direction != 0)
-    return fail(RB_UNSUPPORTED, "i8 convolution exists in the forward direction only (RockOps.td:101-134)");
+  const bool f8 = t == RB_F8E4M3 || t == RB_F8E5M2;
+  if (!(t == RB_F32 || t == RB_F16 || t == RB_BF16 || t == RB_I8 || f8)) return fail(RB_INVALID_PARAM, "unsupported element type");
+  if ((t == RB_I8 || f8) && p->direction != 0)
+    return fail(RB_UNSUPPORTED, "8-bit convolutions exist in the forward direction only (RockOps.td:101-134, ConvGenerator.cpp:631-638)");
   const long long fsz[6] = {p->g, p->k, p->c, p->z, p->y, p->x};
   const long long isz[6] = {p->n, p->g, p->c, p->d, p->h, p->w};
   const long long osz[6] = {p->n, p->g, p->k, dout, ho, wo};
@@ -209,7 +210,7 @@ RbStatus make_plan3d(const RbConv3dProblem* p, Plan3d* pl) {
     strcpy(q.fil_layout, "gkyxc");
     strcpy(q.in_layout, "gnhwc");     // group outermost: each group's activations are a [pixels][channels] matrix
     strcpy(q.out_layout, "gnhwk");
-    const size_t es = dtype_bytes(t), es_o = dtype_bytes(t == RB_I8 ? RB_I32 : t);
+    const size_t es = dtype_bytes(t), es_o = dtype_bytes(t == RB_I8 ? RB_I32 : f8 ? RB_F32 : t);
     pl->in2_bytes = (size_t)n2 * p->h * p->w * p->g * c2 * (p->direction == 1 ? 4 : es);
     pl->fil2_bytes = (size_t)p->g * p->k * p->y * p->x * c2 * es;
     pl->out2_bytes = (size_t)n2 * ho * wo * p->g * p->k * es_o;
@@ -258,7 +259,7 @@ extern "C" RbStatus rbConv3d(const RbConv3dProblem* p, void* filter, void* input
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   const int blocks = dev->sm_count * 8;
   const int t = p->data_type;
-  const size_t es = dtype_bytes(t), es_o = dtype_bytes(t == RB_I8 ? RB_I32 : t);
+  const size_t es = dtype_bytes(t), es_o = dtype_bytes(t == RB_I8 ? RB_I32 : (t == RB_F8E4M3 || t == RB_F8E5M2) ? RB_F32 : t);
   uint8_t* in2 = ws + pl.in2_off;
   uint8_t* fil2 = ws + pl.fil2_off;
   uint8_t* out2 = ws + pl.out2_off;

@@ -252,9 +252,10 @@ RbStatus make_plan(const RbConvProblem* p, ConvPlan* pl, int result_type = -1) {
     return fail(RB_INVALID_PARAM, "ho/wo must equal (in + padL + padR - (fil-1)*dil - 1)/stride + 1 = " +
                                       std::to_string(ho) + " x " + std::to_string(wo));
   const int t = p->data_type;
-  if (!(t == RB_F32 || t == RB_F16 || t == RB_BF16 || t == RB_I8)) return fail(RB_INVALID_PARAM, "unsupported element type");
-  if (t == RB_I8 && p->direction != 0)
-    return fail(RB_UNSUPPORTED, "i8 convolution exists in the forward direction only (RockOps.td:101-134)");
+  const bool f8 = t == RB_F8E4M3 || t == RB_F8E5M2;
+  if (!(t == RB_F32 || t == RB_F16 || t == RB_BF16 || t == RB_I8 || f8)) return fail(RB_INVALID_PARAM, "unsupported element type");
+  if ((t == RB_I8 || f8) && p->direction != 0)
+    return fail(RB_UNSUPPORTED, "8-bit convolutions exist in the forward direction only (RockOps.td:101-134, ConvGenerator.cpp:631-638)");
   const long long fsz[5] = {p->g, p->k, p->c, p->y, p->x};
   const long long isz[5] = {p->n, p->g, p->c, p->h, p->w};
   const long long osz[5] = {p->n, p->g, p->k, ho, wo};
@@ -263,7 +264,7 @@ RbStatus make_plan(const RbConvProblem* p, ConvPlan* pl, int result_type = -1) {
   if (!layout_strides(p->out_layout, "ngkhw", osz, pl->os, nullptr)) return fail(RB_INVALID_PARAM, "out_layout must be a permutation of ngkhw");
 
   const size_t es = dtype_bytes(t);
-  const int out_t = (t == RB_I8) ? RB_I32 : t;  // rocmlir-gen: -t i8 => i32 output
+  const int out_t = (t == RB_I8) ? RB_I32 : f8 ? RB_F32 : t;  // rocmlir-gen: -t i8 => i32 output, 8-bit floats => f32
   const size_t es_o = dtype_bytes(out_t);
   const long long G = p->g;
   const long long pix_o = (long long)p->n * ho * wo, pix_i = (long long)p->n * p->h * p->w;

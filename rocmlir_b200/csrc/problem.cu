@@ -130,14 +130,17 @@ bool parse_conv(const std::map<std::string, std::string>& m, int direction, Prob
   RbConvProblem& c = h->conv;
   memset(&c, 0, sizeof(c));
   const int in_t = parse_type(m.at("in_type")), fil_t = parse_type(m.at("fil_type")), out_t = parse_type(m.at("out_type"));
-  if (in_t < 0 || fil_t < 0 || out_t < 0 || in_t == RB_I32 || in_t != fil_t || in_t >= RB_F8E4M3) return false;
+  const bool f8 = in_t == RB_F8E4M3 || in_t == RB_F8E5M2;
+  if (in_t < 0 || fil_t < 0 || out_t < 0 || in_t == RB_I32 || in_t != fil_t || in_t > RB_F8E5M2) return false;
   if (in_t == RB_I8) {
     if (out_t != RB_I32) return false;   // i8 x i8 accumulates and stores i32
+  } else if (f8) {
+    if (out_t != RB_F32) return false;   // 8-bit floats accumulate and store f32
   } else if (out_t != in_t) {
     return false;
   }
   // ConvGenerator.cpp:631-638: 8-bit types run forward only
-  if (direction != 0 && (in_t == RB_I8 || in_t == RB_F8E4M3)) return false;
+  if (direction != 0 && (in_t == RB_I8 || f8)) return false;
   c.data_type = in_t;
   c.direction = direction;
   if (!translate_layout(m.at("fil_layout"), 0, c.fil_layout) || !translate_layout(m.at("in_layout"), 1, c.in_layout) ||
@@ -219,7 +222,7 @@ bool parse_attention(const std::map<std::string, std::string>& m, ProblemDesc* h
   }
   if (p.g <= 0 || p.seq_q <= 0 || p.seq_k <= 0) return false;
   if (p.trans_q || p.trans_v || p.trans_o) return false;
-  if (p.head_qk % 64 || p.head_qk > 128 || p.head_qk <= 0 || p.head_v % 64 || p.head_v > 128 || p.head_v <= 0) return false;
+  if (p.head_qk % 8 || p.head_qk > 128 || p.head_qk <= 0 || p.head_v % 8 || p.head_v > 128 || p.head_v <= 0) return false;
   if (!p.trans_k && p.seq_k % 8) return false;
   p.data_type = t;
   h->kind = kAttention;

@@ -278,11 +278,12 @@ def run_conv(f: Dict[str, str], direction: int) -> List[int]:
     ty = resolve_types(f)
     cfg = conv_config(f)
     code = ty.a
-    if code in (oracle.F8E4M3, oracle.F8E5M2) or ty.b != ty.a:
-        raise Unsupported("8-bit float convolution")
-    if code == oracle.I8 and direction != 0:
-        raise ValueError("i8 convolution is forward only")
-    out_code = oracle.I32 if code == oracle.I8 else code
+    f8 = code in (oracle.F8E4M3, oracle.F8E5M2)
+    if ty.b != ty.a:
+        raise Unsupported("convolution with two different 8-bit float formats")
+    if (code == oracle.I8 or f8) and direction != 0:
+        raise ValueError("8-bit convolutions are forward only")
+    out_code = oracle.I32 if code == oracle.I8 else oracle.F32 if f8 else code
     if ty.out != out_code:
         raise Unsupported("convolution output type differs from the input type")
     three = hasattr(cfg, "dout")
@@ -327,8 +328,8 @@ def run_attention(f: Dict[str, str]) -> List[int]:
     else:
         g = int(f.get("g", 1))
         sq, sk, d, dv = int(f["seq_len_q"]), int(f["seq_len_k"]), int(f["head_dim_qk"]), int(f["head_dim_v"])
-    if d not in (64, 128) or dv not in (64, 128):
-        raise Unsupported("head dimensions other than 64 and 128")
+    if d % 8 or dv % 8 or d > 128 or dv > 128:
+        raise Unsupported("head dimensions that are not multiples of 8 up to 128")
     if as_bool(f, "transQ") or as_bool(f, "transV") or as_bool(f, "transO"):
         raise Unsupported("transQ / transV / transO")
     tk = as_bool(f, "transK")

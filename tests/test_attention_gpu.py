@@ -43,7 +43,9 @@ def make_qkv(g, sq, sk, d, dv, code, seed=1):
 # shapes of the reference's PR attention suite (PrAttentionF16.toml:19-66): seq 64..384, head 64 / 128, plus ragged
 # sequence lengths (tails of the 128-row / 128-key tiles)
 SHAPES = [(2, 384, 384, 64, 64), (3, 128, 256, 128, 128), (1, 64, 64, 64, 64), (2, 100, 200, 128, 64),
-          (1, 256, 128, 64, 128), (1, 257, 136, 128, 128)]
+          (1, 256, 128, 64, 128), (1, 257, 136, 128, 128),
+          # head dimensions that are not 64 / 128 (rocmlir-gen's -p default is 32, rocmlir-gen.cpp:1018-1020)
+          (2, 384, 256, 32, 32), (1, 200, 136, 96, 40), (1, 130, 264, 72, 128)]
 
 
 @pytest.mark.parametrize("code", [oracle.F16, oracle.BF16])

@@ -99,6 +99,22 @@ def test_int8_forward_bit_exact(cuda_device, layout):
     assert oracle.verify_int(got, ref)[0] == [1, 1, 1]
 
 
+@pytest.mark.parametrize("layout", ["nhwc", "nchw"])
+@pytest.mark.parametrize("code", [oracle.F8E4M3, oracle.F8E5M2])
+def test_fp8_forward_exact_on_reference_integer_data(cuda_device, code, layout):
+    """-t fp8 / bf8 forward -> f32 (rocmlir-gen.cpp:430-455). -rand 1 values are small integers, exact in both 8-bit
+    formats, so the f32 result must match the oracle bit for bit (NHWC C=128 takes the implicit-GEMM path)."""
+    cfg, ocfg = make_cfgs(n=2, c=128, k=48, h=12, w=12, y=3, x=3, pad_h=1, pad_w=1, **LAYOUTS[layout])
+    (ff, fraw), (inf, iraw) = reference_random([(ocfg.numel("fil"),), (ocfg.numel("in"),)], code, seed=1)
+    ref = oracle.conv_f32(ocfg, 0, ff, inf, None, threads=oracle.max_threads())
+    import torch
+    from rocmlir_b200.conv import conv
+    t = {"fil": to_device(fraw, code), "in": to_device(iraw, code),
+         "out": torch.zeros(ocfg.numel("out"), dtype=torch.float32, device="cuda")}
+    got = conv(cfg, 0, t["fil"], t["in"], t["out"]).cpu().numpy()
+    np.testing.assert_array_equal(got.ravel(), ref.ravel())
+
+
 def test_fp32_nchw_forward_headline_config(cuda_device):
     """BASELINE config 1: fp32 NCHW/KCYX, N=16 C=64 56x56 K=64 3x3 s1 p1, input and filter uniform[-1,1) from a seed;
     judged by the reference verifier with its default RMS threshold 3e-5 (relDiff disabled: summation order)."""

@@ -88,15 +88,17 @@ def test_eight_bit_types_run_forward_only():
     # ConvGenerator.cpp:631-638
     i8 = opts(t="i8").replace("--out_type i8", "--out_type i32")
     miir.Handle(i8).close()
-    with pytest.raises(ValueError):
-        miir.Handle(opts(t="fp8"))            # fp8 exists for GEMMs; the convolution path has no fp8 kernel yet
+    for t in ("fp8", "bf8"):                   # 8-bit floats accumulate and store f32
+        f8 = opts(t=t).replace(f"--out_type {t}", "--out_type fp32")
+        miir.Handle(f8).close()
+        with pytest.raises(ValueError):
+            miir.Handle(opts(t=t))            # ... and nothing else
+        for op in ("conv_bwd_data", "conv_bwd_weight"):
+            with pytest.raises(ValueError):
+                miir.Handle(f8.replace("--operation conv", "--operation " + op))
     for op in ("conv_bwd_data", "conv_bwd_weight"):
         with pytest.raises(ValueError):
             miir.Handle(i8.replace("--operation conv", "--operation " + op))
-        with pytest.raises(ValueError):
-            miir.Handle(opts(op, t="fp8"))
-    with pytest.raises(ValueError):
-        miir.Handle(opts(t="bf8"))            # no kernel for e5m2 here
     with pytest.raises(ValueError):
         miir.Handle(opts(t="i8"))             # i8 x i8 stores i32
 
