@@ -80,6 +80,51 @@ __global__ void permute5_kernel(const uint8_t* __restrict__ src, uint8_t* __rest
   }
 }
 
+// The common permutation - a [pixels][channels] matrix against an NCHW-like tensor - is a batched 2-D transpose:
+// dense side [b0][b1][R][C] (C contiguous), strided side with the R run contiguous (stride 1) and the channel at
+// stride s_c. 32 x 32 tiles through shared memory keep both sides coalesced; permute5_kernel, which walks the dense
+// index and scatters, reaches about a fifth of this kernel's rate on such tensors.
+struct Transpose2 {
+  long long B0, B1, R, C;          // dense extents
+  long long s_b0, s_b1, s_c;       // strided side: strides of b0, b1 and the column; rows have stride 1
+};
+
+template <typename T>
+__global__ void transpose_tiles_kernel(const T* __restrict__ src, T* __restrict__ dst, Transpose2 t, int to_dense) {
+  __shared__ T tile[32][33];
+  const long long tiles_r = (t.R + 31) / 32, tiles_c = (t.C + 31) / 32;
+  const long long total = t.B0 * t.B1 * tiles_r * tiles_c;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;   // 32 x 8 threads
+  for (long long w = blockIdx.x; w < total; w += gridDim.x) {
+    long long rem = w;
+    const long long tc = rem % tiles_c; rem /= tiles_c;
+    const long long tr = rem % tiles_r; rem /= tiles_r;
+    const long long b1 = rem % t.B1, b0 = rem / t.B1;
+    const long long r0 = tr * 32, c0 = tc * 32;
+    const long long dense0 = ((b0 * t.B1 + b1) * t.R) * t.C;
+    const long long strided0 = b0 * t.s_b0 + b1 * t.s_b1;
+    if (to_dense) {
+      // read the strided side along r (contiguous), write the dense side along c
+#pragma unroll
+      for (int j = ty; j < 32; j += 8)
+        if (c0 + j < t.C && r0 + tx < t.R) tile[j][tx] = src[strided0 + (c0 + j) * t.s_c + r0 + tx];
+      __syncthreads();
+#pragma unroll
+      for (int j = ty; j < 32; j += 8)
+        if (r0 + j < t.R && c0 + tx < t.C) dst[dense0 + (r0 + j) * t.C + c0 + tx] = tile[tx][j];
+    } else {
+#pragma unroll
+      for (int j = ty; j < 32; j += 8)
+        if (r0 + j < t.R && c0 + tx < t.C) tile[j][tx] = src[dense0 + (r0 + j) * t.C + c0 + tx];
+      __syncthreads();
+#pragma unroll
+      for (int j = ty; j < 32; j += 8)
+        if (c0 + j < t.C && r0 + tx < t.R) dst[strided0 + (c0 + j) * t.s_c + r0 + tx] = tile[tx][j];
+    }
+    __syncthreads();
+  }
+}
+
 struct GatherParams {
   // matrix: [G][rows = N * P * Q][cols = Y * X * CH], dense, row pitch `pitch` elements
   long long N, G, P, Q, Y, X, CH;
@@ -463,6 +508,24 @@ RbStatus rb::conv_run(const RbConvProblem* p, int result_type, void* filter, voi
                      bool to_dense, size_t esz) {
     Dims5 d;
     for (int i = 0; i < 5; ++i) { d.size[i] = sizes[order[i]]; d.stride[i] = strides[order[i]]; }
+    // dense (b0, b1, r_hi, r_lo, c) against a tensor whose (r_hi, r_lo) run is contiguous: batched 2-D transpose
+    if (d.stride[3] == 1 && d.stride[2] == d.size[3] && d.size[4] >= 8 && d.size[2] * d.size[3] >= 32 &&
+        d.stride[0] >= 0 && d.stride[1] >= 0 && d.stride[4] > 0) {
+      Transpose2 t;
+      t.B0 = d.size[0]; t.B1 = d.size[1]; t.R = d.size[2] * d.size[3]; t.C = d.size[4];
+      t.s_b0 = d.stride[0]; t.s_b1 = d.stride[1]; t.s_c = d.stride[4];
+      const long long tiles = t.B0 * t.B1 * ((t.R + 31) / 32) * ((t.C + 31) / 32);
+      const int tb = (int)std::min<long long>(tiles, (long long)dev->sm_count * 16);
+      const int td = to_dense ? 1 : 0;
+      if (esz == 1)
+        transpose_tiles_kernel<uint8_t><<<tb, 256, 0, stream>>>(static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst), t, td);
+      else if (esz == 2)
+        transpose_tiles_kernel<uint16_t><<<tb, 256, 0, stream>>>(static_cast<const uint16_t*>(src), static_cast<uint16_t*>(dst), t, td);
+      else
+        transpose_tiles_kernel<uint32_t><<<tb, 256, 0, stream>>>(static_cast<const uint32_t*>(src), static_cast<uint32_t*>(dst), t, td);
+      count_launch();
+      return;
+    }
     launch_es(esz, blocks, stream, permute5_kernel<1>, permute5_kernel<2>, permute5_kernel<4>,
               static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst), d, to_dense ? 1 : 0);
     count_launch();
