@@ -84,8 +84,24 @@ int parse_type(const std::string& t) {
 
 // Layout translation of the reference (ConvGenerator.h:124-142) onto this library's letters.
 // which: 0 filter (G N|K C H|Y|0 W|X|1 -> g k c y x), 1 input (n g c h w), 2 output (n g C|K h w -> n g k h w)
-bool translate_layout(const std::string& src, int which, char out[8]) {
-  if (src.size() != 5) return false;   // 3-D convolutions (6 letters) have no kernel here
+bool translate_layout(const std::string& src_in, int which, char out[8], bool unit_depth) {
+  // Six letters name a third image dimension (D / Z / 2, ConvGenerator.cpp:622-627). With every depth equal to 1
+  // that dimension has extent 1 and the tensor is the 2-D tensor on the same bytes, so the letter is dropped; a
+  // real depth goes through rbConv3d, which this option grammar does not reach.
+  std::string src = src_in;
+  if (src.size() == 6 && unit_depth) {
+    size_t hit = std::string::npos;
+    for (size_t i = 0; i < 6; ++i) {
+      const char ch = (char)tolower((unsigned char)src[i]);
+      if (ch == 'd' || ch == 'z' || ch == '2') {
+        if (hit != std::string::npos) return false;
+        hit = i;
+      }
+    }
+    if (hit == std::string::npos) return false;
+    src.erase(hit, 1);
+  }
+  if (src.size() != 5) return false;
   for (size_t i = 0; i < 5; ++i) {
     const char ch = (char)tolower((unsigned char)src[i]);
     char o = 0;
@@ -143,8 +159,20 @@ bool parse_conv(const std::map<std::string, std::string>& m, int direction, Prob
   if (direction != 0 && (in_t == RB_I8 || f8)) return false;
   c.data_type = in_t;
   c.direction = direction;
-  if (!translate_layout(m.at("fil_layout"), 0, c.fil_layout) || !translate_layout(m.at("in_layout"), 1, c.in_layout) ||
-      !translate_layout(m.at("out_layout"), 2, c.out_layout))
+  // depth keys are optional (ConvGenerator.cpp:642-650); anything but 1 has no kernel behind this grammar
+  bool unit_depth = true;
+  for (const char* key : {"in_d", "fil_d", "out_d", "conv_stride_d", "dilation_d"}) {
+    int v = 1;
+    if (!opt_int(m, key, &v) || v <= 0) return false;
+    if (v != 1 && (std::string(key) == "in_d" || std::string(key) == "fil_d" || std::string(key) == "out_d")) unit_depth = false;
+  }
+  int pad_d = 0;
+  if (!opt_int(m, "padding_d", &pad_d) || pad_d < 0) return false;
+  if (pad_d != 0) unit_depth = false;
+  if (!unit_depth) return false;
+  if (!translate_layout(m.at("fil_layout"), 0, c.fil_layout, unit_depth) ||
+      !translate_layout(m.at("in_layout"), 1, c.in_layout, unit_depth) ||
+      !translate_layout(m.at("out_layout"), 2, c.out_layout, unit_depth))
     return false;
   long long n, g, ci, co, ih, iw, oh, ow, fh, fw;
   if (!to_long(m, "batchsize", &n) || !to_long(m, "groupsize", &g) || !to_long(m, "in_channels", &ci) ||

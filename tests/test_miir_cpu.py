@@ -80,8 +80,16 @@ def test_inconsistent_dimensions_give_null():
         miir.Handle(opts().replace("--in_layout NGCHW", "--in_layout NGCH"))
     with pytest.raises(ValueError):
         miir.Handle(opts().replace("--in_layout NGCHW", "--in_layout NGCHH"))
+    # a third image letter: accepted while every depth is 1 (the tensor is the 2-D tensor on the same bytes) ...
+    three = opts().replace("NGCHW", "NGCHWD").replace("GNCHW", "GNCHWD")
+    with miir.Handle(three) as h3, miir.Handle(opts()) as h2:
+        assert h3.workspace_size == h2.workspace_size and h3.kernel_count == h2.kernel_count
+    miir.Handle(three + " --in_d 1 --fil_d 1 --out_d 1").close()
+    # ... a real depth has no kernel behind this option grammar (rbConv3d is the entry point for it)
     with pytest.raises(ValueError):
-        miir.Handle(opts().replace("NGCHW", "NGCHWD").replace("GNCHW", "GNCHWD"))
+        miir.Handle(three + " --in_d 4 --fil_d 3 --out_d 2")
+    with pytest.raises(ValueError):
+        miir.Handle(opts().replace("NGCHW", "NGCHWD"))          # only one of the three layouts names the depth
 
 
 def test_eight_bit_types_run_forward_only():
