@@ -170,6 +170,8 @@ bool parse_conv(const std::map<std::string, std::string>& m, int direction, Prob
   if (!opt_int(m, "padding_d", &pad_d) || pad_d < 0) return false;
   if (pad_d != 0) unit_depth = false;
   if (!unit_depth) return false;
+  if (m.at("fil_layout").size() != m.at("in_layout").size() || m.at("in_layout").size() != m.at("out_layout").size())
+    return false;   // the three tensors have the same number of image dimensions
   if (!translate_layout(m.at("fil_layout"), 0, c.fil_layout, unit_depth) ||
       !translate_layout(m.at("in_layout"), 1, c.in_layout, unit_depth) ||
       !translate_layout(m.at("out_layout"), 2, c.out_layout, unit_depth))
