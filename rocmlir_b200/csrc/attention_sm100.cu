@@ -537,16 +537,15 @@ __global__ void __launch_bounds__(kAtt2Threads, 1) attention_fwd2_kernel(const _
         long long tc = p.trace ? clock64() : 0;
         if (!mbar_wait(&v_full[st], par, p.status, kStatusTimeoutMma + 10 + st)) break;
         if (p.trace) { const long long n = clock64(); w_v += n - tc; tc = n; }
+        // the next K tile is waited for here, while this thread would be idle anyway, not between P.V and S of tile A
+        if (more && !mbar_wait(&k_full[nst], npar, p.status, kStatusTimeoutMma + nst)) break;
+        if (p.trace) { const long long n = clock64(); w_k += n - tc; tc = n; }
         if (j < nbt[0]) {
           if (!mbar_wait(&p_full[0], (uint32_t)j & 1u, p.status, kStatusTimeoutMma + 20)) break;
           if (p.trace) { const long long n = clock64(); w_p[0] += n - tc; tc = n; }
           tc_fence_after();
           issue_pv(0, st, j);
         }
-        if (p.trace) tc = clock64();
-        if (more && !mbar_wait(&k_full[nst], npar, p.status, kStatusTimeoutMma + nst)) break;
-        if (p.trace) { const long long n = clock64(); w_k += n - tc; tc = n; }
-        if (more) tc_fence_after();
         if (j + 1 < nbt[0]) issue_s(0, nst);      // S_A(j+1) overwrites S_A / P_A(j) after PV_A(j): issue order
         if (j < nbt[1]) {
           if (p.trace) tc = clock64();
@@ -555,8 +554,8 @@ __global__ void __launch_bounds__(kAtt2Threads, 1) attention_fwd2_kernel(const _
           tc_fence_after();
           issue_pv(1, st, j);
         }
-        tc_commit<1>(&v_empty[st]);
         if (j + 1 < nbt[1]) issue_s(1, nst);
+        tc_commit<1>(&v_empty[st]);
         if (more) tc_commit<1>(&k_empty[nst]);
         st = nst;
         par = npar;
