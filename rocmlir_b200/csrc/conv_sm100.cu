@@ -17,8 +17,9 @@
 // of 128 bytes: the GEMM producer fetches the im2col tiles itself with TMA im2col descriptors -
 //   forward       A from the input (16-bit and 8-bit types; f32 through TF32 planes of the input, hi and lo, which
 //                 one pass builds and, for an NCHW input, transposes)
-//   backward data A from the output gradient with padding (fil-1)*dil - pad and the filter taps mirrored; with a
-//                 stride the gradient is zero-upsampled into the workspace first
+//   backward data A from the output gradient with padding (fil-1)*dil - pad and the filter taps mirrored. With a
+//                 stride the problem is cut into one unit-stride problem per class of input pixels (see ClassTable);
+//                 only a stride together with a dilation still zero-upsamples the gradient into the workspace
 //   backward wt   B from the input (K index = output pixel), A = the NHWK output gradient in place.
 #include <cuda_runtime.h>
 #include <string.h>
@@ -237,6 +238,56 @@ __global__ void upsample_nhwc_kernel(const uint4* __restrict__ in, uint4* __rest
   }
 }
 
+// Backward data with a stride, by classes of input pixels. An input pixel h only receives taps y with
+// (h + pad - y) divisible by the stride, so the pixels with h mod stride_h = ph and w mod stride_w = pw form a class
+// whose gradient is a UNIT-stride backward-data convolution of the same output gradient with the sub-sampled filter
+// y = y0 + stride_h * j (the reference cuts the same classes into its kernel ids, backwardDataKernelIds,
+// mlir/lib/Dialect/Rock/Transforms/loweringUtils.cpp:107-170). Each class runs through conv_run into a dense
+// [n][h'][w'][g][c] block of the workspace, and this kernel interleaves the blocks into the caller's tensor. No
+// product with a structural zero is computed, unlike the zero-upsampled formulation.
+struct ClassTable {
+  long long N, H, W, G, C;                 // the input gradient
+  long long s_n, s_h, s_w, s_g, s_c;       // its strides in the caller's layout (elements)
+  int sh, sw;
+  long long off[16];                       // element offset of class ph * sw + pw inside the class area, -1: all zero
+  int hs[16], wsz[16];                     // extents of the class block
+};
+
+template <int ES>
+__global__ void interleave_classes_kernel(const uint8_t* __restrict__ cls, uint8_t* __restrict__ dst, ClassTable t) {
+  // One thread per 16-byte vector of channels when the destination is channel-contiguous, else per element. One
+  // block row of threads walks one image row (n, h): the class row, and with it every division by a run-time
+  // extent, is computed once per row; along w the class alternates with w mod stride_w.
+  const bool vec = t.s_c == 1 && (t.C * ES) % 16 == 0 && (t.s_n * ES) % 16 == 0 && (t.s_h * ES) % 16 == 0 &&
+                   (t.s_w * ES) % 16 == 0 && (t.s_g * ES) % 16 == 0;
+  const unsigned per = vec ? 16 / ES : 1;
+  const unsigned cv = (unsigned)(t.C / per);
+  const unsigned G = (unsigned)t.G, W = (unsigned)t.W, H = (unsigned)t.H;
+  const unsigned row_items = W * G * cv;                       // < 2^31 (checked by the plan)
+  const long long rows = t.N * t.H;
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    const unsigned h = (unsigned)(row % H);
+    const long long n = row / H;
+    const unsigned ph = h % (unsigned)t.sh, hq = h / (unsigned)t.sh;
+    const long long drow = n * t.s_n + (long long)h * t.s_h;
+    for (unsigned i = threadIdx.x; i < row_items; i += blockDim.x) {
+      const unsigned c = (i % cv) * per;
+      const unsigned r = i / cv;
+      const unsigned g = r % G, w = r / G;
+      const unsigned k = ph * (unsigned)t.sw + w % (unsigned)t.sw, wq = w / (unsigned)t.sw;
+      const long long d = drow + (long long)w * t.s_w + (long long)g * t.s_g + (long long)c * t.s_c;
+      const long long so = t.off[k] < 0 ? -1
+                                        : t.off[k] + ((((n * t.hs[k] + hq) * t.wsz[k] + wq) * (long long)G + g) * t.C + c);
+      if (vec) {
+        *reinterpret_cast<uint4*>(dst + d * ES) = so < 0 ? make_uint4(0, 0, 0, 0) : *reinterpret_cast<const uint4*>(cls + so * ES);
+      } else {
+        if (ES == 2) reinterpret_cast<uint16_t*>(dst)[d] = so < 0 ? (uint16_t)0 : reinterpret_cast<const uint16_t*>(cls)[so];
+        if (ES == 4) reinterpret_cast<uint32_t*>(dst)[d] = so < 0 ? 0u : reinterpret_cast<const uint32_t*>(cls)[so];
+      }
+    }
+  }
+}
+
 size_t up256(size_t x) { return (x + 255) / 256 * 256; }
 
 // Named-dimension strides of a tensor stored in `layout` order (row-major over the letters).
@@ -271,6 +322,14 @@ struct ConvPlan {
   bool a_nchw;       //   the input is NCHW: the plane pass transposes it to NHWC
   size_t a_bytes, b_bytes, c_bytes, gemm_ws;
   size_t a_off, b_off, c_off, gemm_off, total;
+  // backward data by stride classes (see interleave_classes_kernel): sub-problems and their places in the workspace
+  int n_classes = 0;
+  struct StrideClass {
+    RbConvProblem q;
+    int ph, pw, y0, x0;
+    size_t fil_off, out_off, ws_bytes;   // sub-filter, class block; out_off = SIZE_MAX for a class without taps
+  } cls[16];
+  size_t cls_ws_off = 0;
 };
 
 bool is_dense_in_order(const long long* strides, const long long* sizes, const int* order, int n) {
@@ -414,6 +473,54 @@ RbStatus make_plan(const RbConvProblem* p, ConvPlan* pl, int result_type = -1) {
   if ((long long)gp.m != (p->direction == 0 ? pix_o : p->direction == 2 ? (long long)p->k : pix_i) ||
       pix_o > 0x7fffffffLL || pix_i > 0x7fffffffLL || yxc > 0x7fffffffLL || yxk > 0x7fffffffLL)
     return fail(RB_UNSUPPORTED, "GEMM extent exceeds 2^31");
+  pl->n_classes = 0;
+  if (p->direction == 1 && result_type < 0 && (p->stride_h > 1 || p->stride_w > 1) && p->dil_h == 1 && p->dil_w == 1 &&
+      p->stride_h <= 4 && p->stride_w <= 4) {
+    // stride classes: every class is a unit-stride backward-data problem over the same output gradient
+    bool ok = true;
+    size_t off = 0, sub_ws = 0;
+    int nc = 0;
+    for (int ph = 0; ph < p->stride_h && ok; ++ph)
+      for (int pw = 0; pw < p->stride_w && ok; ++pw) {
+        ConvPlan::StrideClass& c = pl->cls[nc++];
+        memset(&c.q, 0, sizeof(c.q));
+        c.ph = ph; c.pw = pw;
+        const int hs = (p->h - ph + p->stride_h - 1) / p->stride_h, wsz = (p->w - pw + p->stride_w - 1) / p->stride_w;
+        c.y0 = (ph + p->pad_h) % p->stride_h; c.x0 = (pw + p->pad_w) % p->stride_w;
+        const int ty = c.y0 < p->y ? (p->y - c.y0 + p->stride_h - 1) / p->stride_h : 0;
+        const int tx = c.x0 < p->x ? (p->x - c.x0 + p->stride_w - 1) / p->stride_w : 0;
+        const int q0h = (ph + p->pad_h) / p->stride_h, q0w = (pw + p->pad_w) / p->stride_w;
+        c.q.n = p->n; c.q.g = p->g; c.q.c = p->c; c.q.k = p->k;
+        c.q.h = hs; c.q.w = wsz; c.q.y = ty; c.q.x = tx;
+        c.q.stride_h = c.q.stride_w = c.q.dil_h = c.q.dil_w = 1;
+        c.q.pad_h = q0h; c.q.pad_w = q0w;
+        c.q.pad_h_r = (int)ho - hs - q0h + ty - 1; c.q.pad_w_r = (int)wo - wsz - q0w + tx - 1;
+        c.q.ho = (int)ho; c.q.wo = (int)wo;
+        c.q.data_type = t; c.q.direction = 1; c.q.f32_mode = p->f32_mode;
+        strcpy(c.q.fil_layout, "gkyxc");
+        strcpy(c.q.in_layout, "nhwgc");
+        memcpy(c.q.out_layout, p->out_layout, sizeof(c.q.out_layout));
+        c.fil_off = c.out_off = 0; c.ws_bytes = 0;
+        if (hs <= 0 || wsz <= 0) { ok = false; break; }       // fewer input pixels than the stride: not worth a path
+        if (ty == 0 || tx == 0) { c.out_off = SIZE_MAX; continue; }   // no tap reaches this class: zeros
+        if (c.q.pad_h_r < 0 || c.q.pad_w_r < 0) { ok = false; break; }
+        c.fil_off = off; off += up256((size_t)G * p->k * ty * tx * p->c * es);
+        c.out_off = off; off += up256((size_t)p->n * hs * wsz * G * p->c * es);
+        c.ws_bytes = conv_workspace_bytes(&c.q, -1);
+        if (c.ws_bytes == 0) {
+          ConvPlan probe;   // 0 also means "invalid": ask the plan itself
+          if (make_plan(&c.q, &probe, -1) != RB_SUCCESS) { ok = false; break; }
+        }
+        sub_ws = std::max(sub_ws, c.ws_bytes);
+      }
+    if (ok) {
+      pl->n_classes = nc;
+      pl->cls_ws_off = off;
+      pl->total = off + up256(sub_ws);
+      pl->gemm_ws = 0;
+      return RB_SUCCESS;
+    }
+  }
   pl->gemm_ws = gemm_workspace_bytes(&gp, pl->a_implicit ? 0 : pl->b_implicit ? 1 : -1);
   size_t off = 0;
   pl->a_off = off; off += up256(pl->a_bytes);
@@ -456,6 +563,12 @@ extern "C" RbStatus rbConvGetGemmProblem(const RbConvProblem* p, RbGemmProblem* 
 extern "C" int rbConvKernelCount(const RbConvProblem* p) {
   ConvPlan pl;
   if (make_plan(p, &pl) != RB_SUCCESS) return -1;
+  if (pl.n_classes > 0) {
+    int n = 1;   // the interleaving pass
+    for (int i = 0; i < pl.n_classes; ++i)
+      if (pl.cls[i].out_off != SIZE_MAX) n += 1 + rbConvKernelCount(&pl.cls[i].q);
+    return n;
+  }
   return 1 + (pl.a_direct ? 0 : 1) + (pl.b_direct ? 0 : 1) + (pl.c_direct ? 0 : 1);
 }
 
@@ -526,7 +639,9 @@ RbStatus rb::conv_run(const RbConvProblem* p, int result_type, void* filter, voi
       count_launch();
       return;
     }
-    launch_es(esz, blocks, stream, permute5_kernel<1>, permute5_kernel<2>, permute5_kernel<4>,
+    const long long elems = d.size[0] * d.size[1] * d.size[2] * d.size[3] * d.size[4];
+    const int pb = (int)std::max<long long>(1, std::min<long long>(blocks, (elems + 1023) / 1024));   // filters are small
+    launch_es(esz, pb, stream, permute5_kernel<1>, permute5_kernel<2>, permute5_kernel<4>,
               static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst), d, to_dense ? 1 : 0);
     count_launch();
   };
@@ -537,6 +652,36 @@ RbStatus rb::conv_run(const RbConvProblem* p, int result_type, void* filter, voi
   const int fil_kyxc[5] = {0, 1, 3, 4, 2};
   const int fil_yxkc[5] = {0, 3, 4, 1, 2};
   const size_t es_c = dtype_bytes(pl.gemm.c_type);
+
+  if (pl.n_classes > 0) {
+    ClassTable tb;
+    tb.N = p->n; tb.H = p->h; tb.W = p->w; tb.G = p->g; tb.C = p->c;
+    tb.s_n = pl.is[0]; tb.s_g = pl.is[1]; tb.s_c = pl.is[2]; tb.s_h = pl.is[3]; tb.s_w = pl.is[4];
+    tb.sh = p->stride_h; tb.sw = p->stride_w;
+    for (int i = 0; i < 16; ++i) { tb.off[i] = -1; tb.hs[i] = tb.wsz[i] = 1; }
+    for (int i = 0; i < pl.n_classes; ++i) {
+      const ConvPlan::StrideClass& c = pl.cls[i];
+      const int k = c.ph * p->stride_w + c.pw;
+      if (c.out_off == SIZE_MAX) continue;
+      tb.off[k] = (long long)(c.out_off / es);
+      tb.hs[k] = c.q.h; tb.wsz[k] = c.q.w;
+      // sub-filter [g][k][j][i][c] = fil[g][k][c][y0 + stride_h * j][x0 + stride_w * i]
+      const long long ssz[5] = {p->g, p->k, p->c, c.q.y, c.q.x};
+      const long long sst[5] = {pl.fs[0], pl.fs[1], pl.fs[2], pl.fs[3] * p->stride_h, pl.fs[4] * p->stride_w};
+      const uint8_t* first = static_cast<const uint8_t*>(filter) + (c.y0 * pl.fs[3] + c.x0 * pl.fs[4]) * (long long)es;
+      permute(first, ws + c.fil_off, ssz, sst, fil_kyxc, true, es);
+      st = conv_run(&c.q, -1, ws + c.fil_off, ws + c.out_off, output, ws + pl.cls_ws_off, c.ws_bytes, stream_v);
+      if (st != RB_SUCCESS) return st;
+    }
+    const int ib = (int)std::min<long long>((long long)p->n * p->h, (long long)dev->sm_count * 16);
+    if (es == 2)
+      interleave_classes_kernel<2><<<ib, 256, 0, stream>>>(ws, static_cast<uint8_t*>(input), tb);
+    else
+      interleave_classes_kernel<4><<<ib, 256, 0, stream>>>(ws, static_cast<uint8_t*>(input), tb);
+    count_launch();
+    RB_CUDA_TRY(cudaGetLastError());
+    return RB_SUCCESS;
+  }
 
   const void* A;
   const void* B;

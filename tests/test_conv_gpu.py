@@ -87,6 +87,32 @@ def test_conv_exact_on_reference_integer_data(cuda_device, shape, code, layout, 
     np.testing.assert_array_equal(got.ravel(), ref_raw.ravel())
 
 
+# Backward data with a stride runs as one unit-stride problem per class of input pixels (h mod stride, w mod stride):
+# classes without any tap (1x1 filter, stride 2), more classes than taps (stride 3 under a 2x2 filter), different
+# strides per axis, odd extents, groups, a padding larger than the stride.
+STRIDED = [
+    dict(n=2, c=64, k=128, h=14, w=14, y=1, x=1, stride_h=2, stride_w=2),
+    dict(n=2, c=64, k=64, h=15, w=13, y=3, x=3, stride_h=2, stride_w=2, pad_h=1, pad_w=1),
+    dict(n=1, c=64, k=64, h=17, w=16, y=2, x=2, stride_h=3, stride_w=3),
+    dict(n=2, c=8, k=16, h=12, w=11, y=3, x=5, stride_h=2, stride_w=3, pad_h=1, pad_w=2),
+    dict(n=2, c=8, k=8, g=2, h=9, w=9, y=3, x=3, stride_h=2, stride_w=2, pad_h=1, pad_w=1),
+    dict(n=1, c=64, k=64, h=12, w=12, y=7, x=7, stride_h=2, stride_w=2, pad_h=3, pad_w=3),
+    dict(n=1, c=16, k=16, h=10, w=10, y=3, x=3, stride_h=4, stride_w=4, pad_h=1, pad_w=1),
+]
+
+
+@pytest.mark.parametrize("layout", ["nhwc", "nchw"])
+@pytest.mark.parametrize("code", [oracle.F16, oracle.F32, oracle.BF16])
+@pytest.mark.parametrize("shape", STRIDED, ids=lambda s: "x".join(str(v) for v in s.values()))
+def test_strided_backward_data_exact(cuda_device, shape, code, layout):
+    cfg, ocfg = make_cfgs(**shape, **LAYOUTS[layout])
+    (ff, fraw), (inf, iraw), (of, oraw) = reference_random([(ocfg.numel("fil"),), (ocfg.numel("in"),),
+                                                           (ocfg.numel("out"),)], code, seed=1)
+    ref_raw = oracle.from_f32(oracle.conv_f32(ocfg, 1, ff, inf, of, threads=oracle.max_threads()), code)
+    got = run_conv(cfg, 1, code, {"fil": fraw, "in": iraw, "out": oraw})
+    np.testing.assert_array_equal(got.ravel(), ref_raw.ravel())
+
+
 @pytest.mark.parametrize("layout", ["nhwc", "nchw"])
 def test_int8_forward_bit_exact(cuda_device, layout):
     """i8 forward -> i32. The reference's CPU loop multiplies in i8 before widening (rocmlir-gen.cpp:1955-1960);
