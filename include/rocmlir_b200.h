@@ -223,6 +223,13 @@ typedef struct RbAttentionProblem {
   const int8_t *mask;
   const void *scale_tensor; /* optional [G][Sq][Sk] of the element type: s * scale_tensor[g][q][k] before the bias
                                (rocmlir-gen's --with-attn-scale operand, rocmlir-gen.cpp:2338-2391) */
+  /* data_type RB_I8: the first-GEMM-quantised form (rocmlir-gen -t i8, rocmlir-gen.cpp:3497-3515): Q and K are
+   * i8, V, O, scale_tensor and bias f16, and the scores are (i32(Q.K) - quant_bias[0]) cast to f16, times
+   * quant_scale[0] (rocmlir-gen.cpp:2353-2366), before scale, bias and softmax. Both are device pointers to the
+   * single element of the reference's 1x1x1 operands (i8 and f16) and are required for RB_I8, ignored otherwise.
+   * Q and K are widened to f16 (exact) in scratch memory the calling thread owns (grow-only, cudaMalloc on growth). */
+  const void *quant_bias;
+  const void *quant_scale;
 } RbAttentionProblem;
 
 RB_EXPORT RbStatus rbAttention(const RbAttentionProblem *p, const void *q, const void *k, const void *v, void *o,

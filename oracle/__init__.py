@@ -352,6 +352,24 @@ def attention(q, k, v, *, elem_type: int, scale=None, bias=None, mask=None, mask
     return o
 
 
+def attention_i8(q, k, v, quant_bias: int, quant_scale: float, *, scale=None, bias=None, threads: int = 1):
+    """First-GEMM-quantised attention: q [G,Sq,D] and k [G,D,Sk] int8, v [G,Sk,Dv] f32 holding f16 values,
+    quant_bias the i8 zero point, quant_scale an f16 value; optional f16 scale / bias tensors [G,Sq,Sk]."""
+    q = np.ascontiguousarray(q, np.int8)
+    k = np.ascontiguousarray(k, np.int8)
+    v = np.ascontiguousarray(v, np.float32)
+    G, Sq, D = q.shape
+    Sk, Dv = v.shape[1], v.shape[2]
+    assert k.shape == (G, D, Sk)
+    o = np.zeros((G, Sq, Dv), np.float32)
+    scale = None if scale is None else np.ascontiguousarray(scale, np.float32)
+    bias = None if bias is None else np.ascontiguousarray(bias, np.float32)
+    lib().orc_attention_i8(_p(q), _p(k), _p(v), C.c_int(int(quant_bias)), C.c_float(float(quant_scale)), _p(scale),
+                           _p(bias), _p(o), C.c_int64(G), C.c_int64(Sq), C.c_int64(Sk), C.c_int64(D), C.c_int64(Dv),
+                           C.c_int(threads))
+    return o
+
+
 def gemm_gemm(a, b1, b2, mid_type: int, threads: int = 1) -> np.ndarray:
     a = np.ascontiguousarray(a, np.float32)
     b1 = np.ascontiguousarray(b1, np.float32)

@@ -585,6 +585,54 @@ ORC_API void orc_attention(const float* q, const float* k, const float* v, const
     }
 }
 
+// First-GEMM-quantised attention (rocmlir-gen -t i8: Q and K are i8, everything else f16; generator
+// rocmlir-gen.cpp:3497-3515, CPU reference :2562-2581): tosa.matmul i8 x i8 -> i32, minus the i8 quantisation bias
+// widened to i32, cast to f16, times the f16 quantisation scale; from there on the f16 chain of orc_attention.
+// quant_bias and quant_scale are the single elements of their 1x1x1 tensors.
+ORC_API void orc_attention_i8(const int8_t* q, const int8_t* k, const float* v, int quant_bias, float quant_scale,
+                              const float* scale, const float* bias, float* o, int64_t G, int64_t Sq, int64_t Sk,
+                              int64_t D, int64_t Dv, int threads) {
+  const int nt = threads > 0 ? threads : 1;
+  const int T = ORC_F16;
+#pragma omp parallel for collapse(2) num_threads(nt) schedule(static)
+  for (int64_t g = 0; g < G; ++g)
+    for (int64_t i = 0; i < Sq; ++i) {
+      std::vector<float> s(Sk);
+      const int8_t* qg = q + (g * Sq + i) * D;
+      const int8_t* kg = k + g * D * Sk;
+      const float* vg = v + g * Sk * Dv;
+      float* og = o + (g * Sq + i) * Dv;
+      float mx = -INFINITY;
+      for (int64_t j = 0; j < Sk; ++j) {
+        int32_t acc_i = 0;
+        for (int64_t d = 0; d < D; ++d) acc_i += (int32_t)qg[d] * (int32_t)kg[d * Sk + j];
+        acc_i -= (int32_t)quant_bias;
+        float acc = round_to((float)acc_i, T);
+        acc = round_to(acc * quant_scale, T);
+        if (scale) acc = round_to(acc * scale[(g * Sq + i) * Sk + j], T);
+        if (bias) acc = round_to(acc + bias[(g * Sq + i) * Sk + j], T);
+        s[j] = acc;
+        mx = std::max(mx, acc);
+      }
+      float l = 0.0f;
+      for (int64_t j = 0; j < Sk; ++j) {
+        const float e = round_to(std::exp(round_to(s[j] - mx, T)), T);
+        s[j] = e;
+        l = round_to(l + e, T);
+      }
+      const float rl = round_to(1.0f / l, T);
+      for (int64_t j = 0; j < Sk; ++j) s[j] = round_to(s[j] * rl, T);
+      for (int64_t d = 0; d < Dv; ++d) {
+        float acc = 0.0f;
+        for (int64_t j = 0; j < Sk; ++j) {
+          const float mul = round_to(s[j] * vg[j * Dv + d], T);
+          acc = round_to(acc + mul, T);
+        }
+        og[d] = acc;
+      }
+    }
+}
+
 // gemm + gemm: O = (A.B1).B2 with the intermediate rounded to the element type, the behaviour of
 // the attention skeleton with softmax removed
 // (mlir/lib/Dialect/Rock/Transforms/GridwiseGemmToBlockwise.cpp:1790-1813, 2162-2165). f32 accumulation

@@ -56,7 +56,7 @@ class RbAttentionProblem(C.Structure):
                 ("head_v", C.c_int32), ("trans_q", C.c_int32), ("trans_k", C.c_int32), ("trans_v", C.c_int32),
                 ("trans_o", C.c_int32), ("data_type", C.c_int32), ("has_scale", C.c_int32), ("scale", C.c_float),
                 ("causal", C.c_int32), ("mask_fill", C.c_float), ("bias", C.c_void_p), ("mask", C.c_void_p),
-                ("scale_tensor", C.c_void_p)]
+                ("scale_tensor", C.c_void_p), ("quant_bias", C.c_void_p), ("quant_scale", C.c_void_p)]
 
 
 class RbGemmConfigInfo(C.Structure):

@@ -17,7 +17,10 @@ from .gemm import rb_dtype
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, trans_k: bool = False,
               scale: Optional[float] = None, bias: Optional[torch.Tensor] = None,
               mask: Optional[torch.Tensor] = None, mask_fill: float = float("-inf"), causal: bool = False,
-              out: Optional[torch.Tensor] = None, scale_tensor: Optional[torch.Tensor] = None) -> torch.Tensor:
+              out: Optional[torch.Tensor] = None, scale_tensor: Optional[torch.Tensor] = None,
+              quant_bias: Optional[torch.Tensor] = None, quant_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """With int8 `q` and `k` this is the first-GEMM-quantised form (rocmlir-gen -t i8): `v`, the result and the
+    side tensors are f16, and `quant_bias` (one int8) and `quant_scale` (one f16), both CUDA tensors, are required."""
     for t in (q, k, v):
         if not t.is_cuda or not t.is_contiguous():
             raise L.RbError(L.INVALID_PARAM, "q, k, v must be contiguous CUDA tensors (the library has no CPU path)")
@@ -26,16 +29,24 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, trans_k: boo
     kshape = (g, sk, d) if trans_k else (g, d, sk)
     if tuple(k.shape) != kshape or v.shape[0] != g:
         raise L.RbError(L.INVALID_PARAM, f"shape mismatch: Q {tuple(q.shape)} K {tuple(k.shape)} V {tuple(v.shape)}")
+    side_dtype = v.dtype          # the element type of everything but a quantised Q and K
     if out is None:
-        out = torch.empty((g, sq, dv), dtype=q.dtype, device=q.device)
+        out = torch.empty((g, sq, dv), dtype=side_dtype, device=q.device)
     p = L.RbAttentionProblem(g, sq, sk, d, dv, 0, int(trans_k), 0, 0, rb_dtype(q.dtype), int(scale is not None),
-                             float(scale or 0.0), int(causal), float(mask_fill), None, None, None)
+                             float(scale or 0.0), int(causal), float(mask_fill), None, None, None, None, None)
+    if q.dtype == torch.int8:
+        if quant_bias is None or quant_scale is None or quant_bias.dtype != torch.int8 or \
+                quant_scale.dtype != torch.float16 or v.dtype != torch.float16 or k.dtype != torch.int8:
+            raise L.RbError(L.INVALID_PARAM, "the i8 form takes i8 q, k, f16 v, an i8 quant_bias and an f16 quant_scale")
+        assert quant_bias.is_cuda and quant_scale.is_cuda and quant_bias.numel() == 1 and quant_scale.numel() == 1
+        p.quant_bias = quant_bias.data_ptr()
+        p.quant_scale = quant_scale.data_ptr()
     if scale_tensor is not None:
-        assert scale_tensor.is_cuda and scale_tensor.is_contiguous() and scale_tensor.dtype == q.dtype and \
+        assert scale_tensor.is_cuda and scale_tensor.is_contiguous() and scale_tensor.dtype == side_dtype and \
             tuple(scale_tensor.shape) == (g, sq, sk)
         p.scale_tensor = scale_tensor.data_ptr()
     if bias is not None:
-        assert bias.is_cuda and bias.is_contiguous() and bias.dtype == q.dtype and tuple(bias.shape) == (g, sq, sk)
+        assert bias.is_cuda and bias.is_contiguous() and bias.dtype == side_dtype and tuple(bias.shape) == (g, sq, sk)
         p.bias = bias.data_ptr()
     if mask is not None:
         assert mask.is_cuda and mask.is_contiguous() and mask.dtype == torch.int8 and tuple(mask.shape) == (g, sq, sk)

@@ -54,6 +54,8 @@ struct AttParams {
   float mask_fill;
   uint32_t idesc_s, idesc_pv;
   uint32_t* status;
+  const void* quant_bias;      // first-GEMM-quantised form: device pointers to one i8 and one f16 (else null)
+  const void* quant_scale;
   unsigned long long* trace;   // optional [CTAs][16] cycle counters (two-tile kernel), see rbSetTraceBuffer
 };
 
@@ -87,6 +89,8 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+
+__device__ __forceinline__ float f16_round(float x) { return __half2float(__float2half_rn(x)); }
 
 __global__ void __launch_bounds__(kAttThreads, 1) attention_fwd_kernel(const __grid_constant__ AttMaps maps,
                                                                         const AttParams p) {
@@ -222,6 +226,8 @@ __global__ void __launch_bounds__(kAttThreads, 1) attention_fwd_kernel(const __g
     const long long row = (long long)q0 + r;
     const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
     float m_ref = -INFINITY;   // maximum the exponentials are taken against
+    const float qbias = p.quant_bias ? (float)*static_cast<const int8_t*>(p.quant_bias) : 0.0f;
+    const float qscale = p.quant_scale ? __half2float(*static_cast<const __half*>(p.quant_scale)) : 1.0f;
     float l = 0.0f;
     bool ok = true;
     for (int j = 0; j < nb && ok; ++j) {
@@ -230,7 +236,7 @@ __global__ void __launch_bounds__(kAttThreads, 1) attention_fwd_kernel(const __g
       tc_fence_after();
       const uint32_t tmem_s = tmem_base + lane_base + sb * 128;
       const int key0 = j * kKT;
-      const bool side_inputs = p.bias || p.mask || p.scale_t;          // per-element tensors: general path
+      const bool side_inputs = p.bias || p.mask || p.scale_t || p.quant_scale;          // per-element tensors: general path
       const bool edge = (key0 + kKT > p.Sk) || (p.causal && key0 + kKT - 1 > q0);  // key tail or diagonal block
       uint32_t v[128];
 #pragma unroll
@@ -262,9 +268,17 @@ __global__ void __launch_bounds__(kAttThreads, 1) attention_fwd_kernel(const __g
         const long long side_off = ((long long)g * p.Sq + min(row, (long long)p.Sq - 1)) * p.Sk;
 #pragma unroll
         for (int i = 0; i < 128; ++i) {  // fully unrolled: v[] must stay in registers
-          float x = __uint_as_float(v[i]) * p.scale_log2;
+          float x = __uint_as_float(v[i]);
           const int key = key0 + i;
-          if (key < p.Sk) {
+          if (p.quant_scale && key < p.Sk) {
+            // quantised form: every rounding of the reference's f16 chain is reproduced (see the two-tile kernel)
+            x = f16_round(f16_round(x - qbias) * qscale);
+            if (p.scale_t) x = f16_round(x * load_elem(p.scale_t, side_off + key, 0));
+            if (p.bias) x = f16_round(x + load_elem(p.bias, side_off + key, 0));
+            if (p.mask && p.mask[side_off + key] == 0) x = p.mask_fill;
+            x *= p.scale_log2;
+          } else if (key < p.Sk) {
+            x *= p.scale_log2;
             if (p.scale_t) x *= load_elem(p.scale_t, side_off + key, p.is_bf16);
             if (p.bias) x = fmaf(load_elem(p.bias, side_off + key, p.is_bf16), kLog2e, x);
             if (p.mask && p.mask[side_off + key] == 0) x = p.mask_fill * kLog2e;
@@ -583,6 +597,8 @@ __global__ void __launch_bounds__(kAtt2Threads, 1) attention_fwd2_kernel(const _
     const uint32_t tmem_s = tmem_base + lane_base + t * 128;
     const uint32_t tmem_o = tmem_base + lane_base + 256 + t * 128;
     float m_ref = -INFINITY, l = 0.0f;
+    const float qbias = p.quant_bias ? (float)*static_cast<const int8_t*>(p.quant_bias) : 0.0f;
+    const float qscale = p.quant_scale ? __half2float(*static_cast<const __half*>(p.quant_scale)) : 1.0f;
     bool ok = true;
     long long sm_wait = 0, sm_busy = 0;
     for (int j = 0; j < nb && ok; ++j) {
@@ -592,13 +608,26 @@ __global__ void __launch_bounds__(kAtt2Threads, 1) attention_fwd2_kernel(const _
       sm_wait += ts1 - ts0;
       tc_fence_after();
       const int key0 = j * kKT;
-      const bool side_inputs = p.bias || p.mask || p.scale_t;
+      const bool side_inputs = p.bias || p.mask || p.scale_t || p.quant_scale;
       const bool edge = (key0 + kKT > p.Sk) || (p.causal && key0 + kKT - 1 > tq0);
       const int limit = min(p.Sk - key0, p.causal ? (int)min(row - key0 + 1, (long long)kKT) : kKT);
       const long long side_off = ((long long)g * p.Sq + min(row, (long long)p.Sq - 1)) * p.Sk + key0;
       // x(i): score of key key0 + i in the log2 domain after scale, bias and masks
       auto fx = [&](uint32_t raw, int i) -> float {
-        float x = __uint_as_float(raw) * p.scale_log2;
+        float x = __uint_as_float(raw);
+        if (p.quant_scale) {
+          // Quantised form: integer-valued scores of magnitude 10^3..10^4 meet f16 steps of 1..16, so the result
+          // depends on every rounding of the reference's f16 chain (cast, * quant_scale, * scale, + bias); each is
+          // reproduced here before the exponent is taken in f32.
+          x = f16_round(f16_round(x - qbias) * qscale);
+          if (i < p.Sk - key0) {
+            if (p.scale_t) x = f16_round(x * load_elem(p.scale_t, side_off + i, 0));
+            if (p.bias) x = f16_round(x + load_elem(p.bias, side_off + i, 0));
+            if (p.mask && p.mask[side_off + i] == 0) x = p.mask_fill;
+          }
+          return x * p.scale_log2;
+        }
+        x *= p.scale_log2;
         if (side_inputs && i < p.Sk - key0) {
           if (p.scale_t) x *= load_elem(p.scale_t, side_off + i, p.is_bf16);
           if (p.bias) x = fmaf(load_elem(p.bias, side_off + i, p.is_bf16), kLog2e, x);
@@ -612,7 +641,7 @@ __global__ void __launch_bounds__(kAtt2Threads, 1) attention_fwd2_kernel(const _
       // exponent argument x(i) - m; without a bias it is the same single fused multiply-add as on the fast path, so
       // that a mask tensor and the analytic causal mask give bit-identical results
       auto fe = [&](uint32_t raw, int i) -> float {
-        float a = (p.bias || p.scale_t) ? fx(raw, i) - m_use : fmaf(__uint_as_float(raw), p.scale_log2, -m_use);
+        float a = (p.bias || p.scale_t || p.quant_scale) ? fx(raw, i) - m_use : fmaf(__uint_as_float(raw), p.scale_log2, -m_use);
         if (p.mask && i < p.Sk - key0 && p.mask[side_off + i] == 0) a = p.mask_fill * kLog2e - m_use;
         return a;
       };
@@ -760,6 +789,49 @@ __global__ void __launch_bounds__(kAtt2Threads, 1) attention_fwd2_kernel(const _
   }
 }
 
+// i8 -> f16 (exact) for the first-GEMM-quantised form: 16 elements per thread where the count allows
+__global__ void widen_i8_kernel(const int8_t* __restrict__ src, __half* __restrict__ dst, long long n) {
+  const long long nv = (reinterpret_cast<uintptr_t>(src) % 16 == 0) ? n / 16 : 0;   // vector part needs an aligned source
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nv; i += (long long)gridDim.x * blockDim.x) {
+    const int4 raw = reinterpret_cast<const int4*>(src)[i];
+    const int w[4] = {raw.x, raw.y, raw.z, raw.w};
+    __half2 out[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      out[2 * j] = __floats2half2_rn((float)(int8_t)(w[j] & 0xff), (float)(int8_t)((w[j] >> 8) & 0xff));
+      out[2 * j + 1] = __floats2half2_rn((float)(int8_t)((w[j] >> 16) & 0xff), (float)(int8_t)((w[j] >> 24) & 0xff));
+    }
+    reinterpret_cast<int4*>(dst)[2 * i] = *reinterpret_cast<int4*>(&out[0]);
+    reinterpret_cast<int4*>(dst)[2 * i + 1] = *reinterpret_cast<int4*>(&out[4]);
+  }
+  for (long long i = nv * 16 + blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    dst[i] = __float2half_rn((float)src[i]);
+}
+
+// Scratch for the widened Q and K: grow-only, owned by the calling thread (a growth waits for the device first, so
+// no kernel in flight still reads the old block).
+struct QkScratch {
+  void* ptr = nullptr;
+  size_t size = 0;
+  int device = -1;
+};
+thread_local QkScratch t_qk;
+
+RbStatus qk_reserve(size_t bytes) {
+  int dev = 0;
+  RB_CUDA_TRY(cudaGetDevice(&dev));
+  if (t_qk.device == dev && t_qk.size >= bytes) return RB_SUCCESS;
+  if (t_qk.ptr) {
+    RB_CUDA_TRY(cudaDeviceSynchronize());
+    RB_CUDA_TRY(cudaFree(t_qk.ptr));
+    t_qk = QkScratch();
+  }
+  RB_CUDA_TRY(cudaMalloc(&t_qk.ptr, bytes));
+  t_qk.size = bytes;
+  t_qk.device = dev;
+  return RB_SUCCESS;
+}
+
 }  // namespace
 }  // namespace rb
 
@@ -771,8 +843,12 @@ extern "C" RbStatus rbAttention(const RbAttentionProblem* p, const void* q, cons
   if (p->g <= 0 || p->seq_q <= 0 || p->seq_k <= 0 || p->head_qk <= 0 || p->head_v <= 0)
     return fail(RB_INVALID_PARAM, "g, seq_len_q, seq_len_k, head_dim_qk, head_dim_v must be positive");
   if (!q || !k || !v || !o) return fail(RB_INVALID_PARAM, "q, k, v and o must be device pointers");
-  if (!(p->data_type == RB_F16 || p->data_type == RB_BF16))
-    return fail(RB_UNSUPPORTED, "attention kernels exist for f16 and bf16");
+  const bool quantized = p->data_type == RB_I8;
+  if (!(p->data_type == RB_F16 || p->data_type == RB_BF16 || quantized))
+    return fail(RB_UNSUPPORTED, "attention kernels exist for f16, bf16 and the first-GEMM-quantised i8 form");
+  if (quantized && (!p->quant_bias || !p->quant_scale))
+    return fail(RB_INVALID_PARAM, "the i8 form needs quant_bias and quant_scale");
+  if (quantized && p->causal) return fail(RB_UNSUPPORTED, "the i8 form has no analytic causal mask");
   if (p->trans_q || p->trans_v || p->trans_o) return fail(RB_UNSUPPORTED, "transQ / transV / transO are not supported");
   // Head dimensions that are not 64 or 128 run as the next multiple of 64: the TMA boxes are 64 elements wide, what
   // they cover beyond the tensor arrives as zeros (no contribution to Q.K, zero columns of O) and is clipped on the
@@ -784,9 +860,23 @@ extern "C" RbStatus rbAttention(const RbAttentionProblem* p, const void* q, cons
   if (!dev) return RB_CUDA_ERROR;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
 
+  if (quantized) {
+    // Q and K widened to f16: every i8 value and every product is exact, and the f32 accumulation of at most
+    // 128 * 127 * 127 stays below 2^24, so the score equals the i32 of the reference bit for bit
+    const size_t qn = (size_t)p->g * p->seq_q * p->head_qk, kn = (size_t)p->g * p->seq_k * p->head_qk;
+    const size_t q_off = 0, k_off = (qn * 2 + 255) / 256 * 256;
+    RbStatus st = qk_reserve(k_off + kn * 2);
+    if (st != RB_SUCCESS) return st;
+    uint8_t* base = static_cast<uint8_t*>(t_qk.ptr);
+    widen_i8_kernel<<<dev->sm_count * 8, 256, 0, stream>>>(static_cast<const int8_t*>(q), reinterpret_cast<__half*>(base + q_off), (long long)qn);
+    widen_i8_kernel<<<dev->sm_count * 8, 256, 0, stream>>>(static_cast<const int8_t*>(k), reinterpret_cast<__half*>(base + k_off), (long long)kn);
+    count_launch(2);
+    q = base + q_off;
+    k = base + k_off;
+  }
   AttMaps maps;
   memset(&maps, 0, sizeof(maps));
-  const CUtensorMapDataType dt = p->data_type == RB_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  const CUtensorMapDataType dt = p->data_type == RB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   std::string err;
   const uint64_t G = p->g, Sq = p->seq_q, Sk = p->seq_k, D = p->head_qk, Dv = p->head_v;
   const uint64_t Dp = (D + 63) / 64 * 64, Dvp = (Dv + 63) / 64 * 64;   // extents the kernels work on
@@ -829,6 +919,8 @@ extern "C" RbStatus rbAttention(const RbAttentionProblem* p, const void* q, cons
   kp.scale_log2 = (p->has_scale ? p->scale : 1.0f) * kLog2e;
   kp.bias = p->bias;
   kp.scale_t = p->scale_tensor;
+  kp.quant_bias = quantized ? p->quant_bias : nullptr;
+  kp.quant_scale = quantized ? p->quant_scale : nullptr;
   kp.mask = p->mask;
   kp.mask_fill = p->mask_fill;
   const uint32_t fmt = kp.is_bf16 ? 1u : 0u;

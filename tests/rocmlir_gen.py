@@ -321,8 +321,9 @@ def run_attention(f: Dict[str, str]) -> List[int]:
     from rocmlir_b200.attention import attention
     ty = resolve_types(f)
     code = ty.a
-    if code not in (oracle.F16, oracle.BF16):
-        raise Unsupported("attention kernels exist for f16 and bf16")
+    quantized = code == oracle.I8       # first GEMM i8 x i8, everything else f16 (rocmlir-gen.cpp:3497-3515)
+    if code not in (oracle.F16, oracle.BF16, oracle.I8):
+        raise Unsupported("attention kernels exist for f16, bf16 and the first-GEMM-quantised i8 form")
     if as_bool(f, "p"):
         g, sq, sk, d, dv = 1, 1024, 1024, 32, 32
     else:
@@ -338,7 +339,12 @@ def run_attention(f: Dict[str, str]) -> List[int]:
     fill = Filler(f)
     q_f, q_r = fill.tensor(g * sq * d, code)
     k_f, k_r = fill.tensor(g * sk * d, code)
+    if quantized:
+        code = oracle.F16
     v_f, v_r = fill.tensor(g * sk * dv, code)
+    if quantized:
+        qb_f, qb_r = fill.tensor(1, oracle.I8)          # kernel-argument order: q, k, v, quantBias, quantScale, ...
+        qs_f, qs_r = fill.tensor(1, oracle.F16)
     sc = bi = None
     if as_bool(f, "with-attn-scale"):
         sc = fill.tensor(g * sq * sk, code)
@@ -347,6 +353,17 @@ def run_attention(f: Dict[str, str]) -> List[int]:
     fill.tensor(g * sq * dv, code)
     k_shape = (g, sk, d) if tk else (g, d, sk)
     k_log = k_f.reshape(k_shape).transpose(0, 2, 1) if tk else k_f.reshape(k_shape)   # oracle wants [G, D, Sk]
+    if quantized:
+        want = oracle.attention_i8(q_r.reshape(g, sq, d), np.ascontiguousarray(k_log).astype(np.int8),
+                                   v_f.reshape(g, sk, dv), int(qb_f[0]), float(qs_f[0]),
+                                   scale=None if sc is None else sc[0].reshape(g, sq, sk),
+                                   bias=None if bi is None else bi[0].reshape(g, sq, sk), threads=oracle.max_threads())
+        o = attention(to_device(q_r.reshape(g, sq, d), oracle.I8), to_device(k_r.reshape(k_shape), oracle.I8),
+                      to_device(v_r.reshape(g, sk, dv), code), trans_k=tk,
+                      quant_bias=to_device(qb_r, oracle.I8), quant_scale=to_device(qs_r, oracle.F16),
+                      scale_tensor=None if sc is None else to_device(sc[1].reshape(g, sq, sk), code),
+                      bias=None if bi is None else to_device(bi[1].reshape(g, sq, sk), code))
+        return verdict_for(from_device(o, code).ravel(), want.ravel(), code, f)
     want = oracle.attention(q_f.reshape(g, sq, d), np.ascontiguousarray(k_log), v_f.reshape(g, sk, dv), elem_type=code,
                             scale=None if sc is None else sc[0].reshape(g, sq, sk),
                             bias=None if bi is None else bi[0].reshape(g, sq, sk), threads=oracle.max_threads())

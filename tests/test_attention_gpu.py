@@ -124,3 +124,33 @@ def test_headline_size_sampled_groups(cuda_device, causal):
         verdict, info = oracle.verify_float(got[grp], ref[0], 1e-3, 100.0, 1e30)
         assert verdict == [1, 1, 1], (grp, info)
         assert np.abs(got[grp] - ref[0]).max() < 4e-3
+
+
+@pytest.mark.parametrize("trans_k", [False, True])
+@pytest.mark.parametrize("with_side", [False, True])
+def test_first_gemm_quantised_attention(cuda_device, trans_k, with_side):
+    """rocmlir-gen -t i8: Q and K int8, (i32(Q.K) - quant_bias) -> f16, * quant_scale, then the f16 chain. Judged
+    like the reference judges an f16 result by default (RMS 1e-3) against the oracle that rounds every step to f16."""
+    import torch
+    from rocmlir_b200.attention import attention
+    g, sq, sk, d, dv = 2, 200, 136, 64, 64
+    rng = np.random.default_rng(7)
+    q = rng.integers(-5, 5, (g, sq, d)).astype(np.int8)
+    k = rng.integers(-5, 5, (g, d, sk)).astype(np.int8)
+    v = oracle.round_to((rng.standard_normal((g, sk, dv))).astype(np.float32), oracle.F16)
+    qb, qs = 3, oracle.round_to(np.float32([0.0625]), oracle.F16)[0]
+    sc = bi = None
+    if with_side:
+        sc = oracle.round_to(rng.uniform(0.5, 1.5, (g, sq, sk)).astype(np.float32), oracle.F16)
+        bi = oracle.round_to(rng.standard_normal((g, sq, sk)).astype(np.float32), oracle.F16)
+    want = oracle.attention_i8(q, k, v, qb, float(qs), scale=sc, bias=bi, threads=oracle.max_threads())
+    kd = np.ascontiguousarray(k.transpose(0, 2, 1)) if trans_k else k
+    dev = lambda a, t: torch.from_numpy(np.ascontiguousarray(a)).to("cuda").to(t)
+    o = attention(dev(q, torch.int8), dev(kd, torch.int8), dev(v, torch.float16), trans_k=trans_k,
+                  quant_bias=dev(np.int8([qb]), torch.int8), quant_scale=dev(np.float32([qs]), torch.float16),
+                  scale_tensor=None if sc is None else dev(sc, torch.float16),
+                  bias=None if bi is None else dev(bi, torch.float16))
+    torch.cuda.synchronize()
+    got = o.float().cpu().numpy()
+    verdict, info = oracle.verify_float(got, oracle.round_to(want, oracle.F16), 1e-3, 100.0, 100.0)
+    assert verdict == [1, 1, 1], info
