@@ -37,3 +37,27 @@ def test_encode_round_to_nearest_even_and_saturate(code, tdt, maxv):
     big = np.array([maxv, maxv * 1.5, 1e30, np.inf, -maxv * 2], np.float32)
     sat = oracle.to_f32(oracle.from_f32(big, code), code)
     np.testing.assert_array_equal(sat, np.array([maxv, maxv, maxv, maxv, -maxv], np.float32))
+
+
+def test_quantised_attention_oracle_reduces_to_the_f16_one():
+    """With a zero quantisation bias, scale 1 and scores small enough to be exact in f16 (|sum| <= 16 * 25), the
+    first-GEMM-quantised oracle must agree bit for bit with the f16 oracle, which the reference's attention
+    structure test pins (mlir/test/rocmlir-gen/attention-kernel.mlir); and the bias / scale enter as
+    f16((s - b)) * qs."""
+    import oracle
+    rng = np.random.default_rng(11)
+    g, sq, sk, d, dv = 2, 9, 13, 16, 8
+    q = rng.integers(-5, 5, (g, sq, d)).astype(np.int8)
+    k = rng.integers(-5, 5, (g, d, sk)).astype(np.int8)
+    v = oracle.round_to(rng.standard_normal((g, sk, dv)).astype(np.float32), oracle.F16)
+    a = oracle.attention_i8(q, k, v, 0, 1.0)
+    b = oracle.attention(q.astype(np.float32), k.astype(np.float32), v, elem_type=oracle.F16)
+    np.testing.assert_array_equal(a, b)
+    # (s - 3) * 0.5 == the f16 oracle on pre-shifted scores expressed through a bias tensor and a scalar scale
+    s = np.einsum("gid,gdj->gij", q.astype(np.int32), k.astype(np.int32))
+    shifted = oracle.round_to(oracle.round_to((s - 3).astype(np.float32), oracle.F16) * np.float32(0.5), oracle.F16)
+    c = oracle.attention_i8(q, k, v, 3, 0.5)
+    # same softmax input => same result as feeding `shifted` as a bias over zero scores
+    zq = np.zeros((g, sq, d), np.float32)
+    e = oracle.attention(zq, k.astype(np.float32), v, elem_type=oracle.F16, bias=shifted)
+    np.testing.assert_array_equal(c, e)
