@@ -14,7 +14,8 @@ from . import _lib as L
 from .gemm import rb_dtype
 
 
-def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, trans_k: bool = False,
+def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, trans_k: bool = False, trans_q: bool = False,
+              trans_v: bool = False, trans_o: bool = False,
               scale: Optional[float] = None, bias: Optional[torch.Tensor] = None,
               mask: Optional[torch.Tensor] = None, mask_fill: float = float("-inf"), causal: bool = False,
               out: Optional[torch.Tensor] = None, scale_tensor: Optional[torch.Tensor] = None,
@@ -24,15 +25,18 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, trans_k: boo
     for t in (q, k, v):
         if not t.is_cuda or not t.is_contiguous():
             raise L.RbError(L.INVALID_PARAM, "q, k, v must be contiguous CUDA tensors (the library has no CPU path)")
-    g, sq, d = q.shape
-    sk, dv = v.shape[1], v.shape[2]
+    # stored shapes: Q [G,Sq,D] (trans_q: [G,D,Sq]), V [G,Sk,Dv] (trans_v: [G,Dv,Sk]), O [G,Sq,Dv] (trans_o: [G,Dv,Sq])
+    g = q.shape[0]
+    d, sq = (q.shape[1], q.shape[2]) if trans_q else (q.shape[2], q.shape[1])
+    dv, sk = (v.shape[1], v.shape[2]) if trans_v else (v.shape[2], v.shape[1])
     kshape = (g, sk, d) if trans_k else (g, d, sk)
     if tuple(k.shape) != kshape or v.shape[0] != g:
         raise L.RbError(L.INVALID_PARAM, f"shape mismatch: Q {tuple(q.shape)} K {tuple(k.shape)} V {tuple(v.shape)}")
     side_dtype = v.dtype          # the element type of everything but a quantised Q and K
     if out is None:
-        out = torch.empty((g, sq, dv), dtype=side_dtype, device=q.device)
-    p = L.RbAttentionProblem(g, sq, sk, d, dv, 0, int(trans_k), 0, 0, rb_dtype(q.dtype), int(scale is not None),
+        out = torch.empty((g, dv, sq) if trans_o else (g, sq, dv), dtype=side_dtype, device=q.device)
+    p = L.RbAttentionProblem(g, sq, sk, d, dv, int(trans_q), int(trans_k), int(trans_v), int(trans_o), rb_dtype(q.dtype),
+                             int(scale is not None),
                              float(scale or 0.0), int(causal), float(mask_fill), None, None, None, None, None)
     if q.dtype == torch.int8:
         if quant_bias is None or quant_scale is None or quant_bias.dtype != torch.int8 or \

@@ -808,6 +808,19 @@ __global__ void widen_i8_kernel(const int8_t* __restrict__ src, __half* __restri
     dst[i] = __float2half_rn((float)src[i]);
 }
 
+// dst[g][r][c] (row pitch dst_pitch) = src[g * s_g + r * s_r + c * s_c] for 2-byte elements: the transposed operand
+// forms (transQ / transV / transO of rocmlir-gen) and K rows that do not start on 16-byte boundaries are brought to
+// the layout the kernels load, in scratch memory. Consecutive threads walk c, so the destination is written in rows.
+__global__ void restride16_kernel(const uint16_t* __restrict__ src, uint16_t* __restrict__ dst, long long G, long long R,
+                                  long long C, long long dst_pitch, long long s_g, long long s_r, long long s_c) {
+  const long long total = G * R * C;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long c = i % C, t = i / C;
+    const long long r = t % R, g = t / R;
+    dst[(g * R + r) * dst_pitch + c] = src[g * s_g + r * s_r + c * s_c];
+  }
+}
+
 // Scratch for the widened Q and K: grow-only, owned by the calling thread (a growth waits for the device first, so
 // no kernel in flight still reads the old block).
 struct QkScratch {
@@ -849,31 +862,65 @@ extern "C" RbStatus rbAttention(const RbAttentionProblem* p, const void* q, cons
   if (quantized && (!p->quant_bias || !p->quant_scale))
     return fail(RB_INVALID_PARAM, "the i8 form needs quant_bias and quant_scale");
   if (quantized && p->causal) return fail(RB_UNSUPPORTED, "the i8 form has no analytic causal mask");
-  if (p->trans_q || p->trans_v || p->trans_o) return fail(RB_UNSUPPORTED, "transQ / transV / transO are not supported");
   // Head dimensions that are not 64 or 128 run as the next multiple of 64: the TMA boxes are 64 elements wide, what
   // they cover beyond the tensor arrives as zeros (no contribution to Q.K, zero columns of O) and is clipped on the
   // store of O. A row of Q, K, V or O must still start on a 16-byte boundary.
   if (p->head_qk % 8 || p->head_qk > 128 || p->head_v % 8 || p->head_v > 128)
     return fail(RB_UNSUPPORTED, "head dimensions must be multiples of 8, at most 128");
-  if (!p->trans_k && p->seq_k % 8) return fail(RB_UNSUPPORTED, "with K stored G x D x Sk, seq_len_k must be a multiple of 8");
   const DeviceInfo* dev = device_info();
   if (!dev) return RB_CUDA_ERROR;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
 
-  if (quantized) {
-    // Q and K widened to f16: every i8 value and every product is exact, and the f32 accumulation of at most
-    // 128 * 127 * 127 stays below 2^24, so the score equals the i32 of the reference bit for bit
-    const size_t qn = (size_t)p->g * p->seq_q * p->head_qk, kn = (size_t)p->g * p->seq_k * p->head_qk;
-    const size_t q_off = 0, k_off = (qn * 2 + 255) / 256 * 256;
-    RbStatus st = qk_reserve(k_off + kn * 2);
+  // Operands the kernels cannot load as they lie are staged in scratch the calling thread owns: i8 Q and K widened
+  // to f16 (every value and product exact; the f32 accumulation of at most 128 * 127 * 127 stays below 2^24, so the
+  // score equals the reference's i32), Q / V stored transposed, K stored G x D x Sk with rows off 16-byte boundaries;
+  // a transposed O is written to scratch and turned afterwards.
+  const size_t qn = (size_t)p->g * p->seq_q * p->head_qk, kn = (size_t)p->g * p->seq_k * p->head_qk;
+  const size_t vn = (size_t)p->g * p->seq_k * p->head_v, on = (size_t)p->g * p->seq_q * p->head_v;
+  const long long sk_pitch = (p->seq_k + 7) / 8 * 8;
+  const bool k_repitch = !p->trans_k && p->seq_k % 8 != 0;
+  auto up = [](size_t x) { return (x + 255) / 256 * 256; };
+  size_t off = 0;
+  const size_t qw_off = off; off += quantized ? up(qn * 2) : 0;
+  const size_t kw_off = off; off += quantized ? up(kn * 2) : 0;
+  const size_t qt_off = off; off += p->trans_q ? up(qn * 2) : 0;
+  const size_t kp_off = off; off += k_repitch ? up((size_t)p->g * p->head_qk * sk_pitch * 2) : 0;
+  const size_t vt_off = off; off += p->trans_v ? up(vn * 2) : 0;
+  const size_t ot_off = off; off += p->trans_o ? up(on * 2) : 0;
+  uint8_t* base = nullptr;
+  if (off) {
+    RbStatus st = qk_reserve(off);
     if (st != RB_SUCCESS) return st;
-    uint8_t* base = static_cast<uint8_t*>(t_qk.ptr);
-    widen_i8_kernel<<<dev->sm_count * 8, 256, 0, stream>>>(static_cast<const int8_t*>(q), reinterpret_cast<__half*>(base + q_off), (long long)qn);
-    widen_i8_kernel<<<dev->sm_count * 8, 256, 0, stream>>>(static_cast<const int8_t*>(k), reinterpret_cast<__half*>(base + k_off), (long long)kn);
-    count_launch(2);
-    q = base + q_off;
-    k = base + k_off;
+    base = static_cast<uint8_t*>(t_qk.ptr);
   }
+  const int sblocks = dev->sm_count * 8;
+  if (quantized) {
+    widen_i8_kernel<<<sblocks, 256, 0, stream>>>(static_cast<const int8_t*>(q), reinterpret_cast<__half*>(base + qw_off), (long long)qn);
+    widen_i8_kernel<<<sblocks, 256, 0, stream>>>(static_cast<const int8_t*>(k), reinterpret_cast<__half*>(base + kw_off), (long long)kn);
+    count_launch(2);
+    q = base + qw_off;
+    k = base + kw_off;
+  }
+  if (p->trans_q) {   // stored [G][D][Sq]
+    restride16_kernel<<<sblocks, 256, 0, stream>>>(static_cast<const uint16_t*>(q), reinterpret_cast<uint16_t*>(base + qt_off), p->g,
+                                                   p->seq_q, p->head_qk, p->head_qk, (long long)p->head_qk * p->seq_q, 1, p->seq_q);
+    count_launch();
+    q = base + qt_off;
+  }
+  if (k_repitch) {    // stored [G][D][Sk]: the same with a row pitch of a multiple of 8 elements
+    restride16_kernel<<<sblocks, 256, 0, stream>>>(static_cast<const uint16_t*>(k), reinterpret_cast<uint16_t*>(base + kp_off), p->g,
+                                                   p->head_qk, p->seq_k, sk_pitch, (long long)p->head_qk * p->seq_k, p->seq_k, 1);
+    count_launch();
+    k = base + kp_off;
+  }
+  if (p->trans_v) {   // stored [G][Dv][Sk]
+    restride16_kernel<<<sblocks, 256, 0, stream>>>(static_cast<const uint16_t*>(v), reinterpret_cast<uint16_t*>(base + vt_off), p->g,
+                                                   p->seq_k, p->head_v, p->head_v, (long long)p->head_v * p->seq_k, 1, p->seq_k);
+    count_launch();
+    v = base + vt_off;
+  }
+  void* o_user = o;
+  if (p->trans_o) o = base + ot_off;
   AttMaps maps;
   memset(&maps, 0, sizeof(maps));
   const CUtensorMapDataType dt = p->data_type == RB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
@@ -893,7 +940,8 @@ extern "C" RbStatus rbAttention(const RbAttentionProblem* p, const void* q, cons
     if (!encode_tiled(&maps.k, dt, 3, k, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B, &err)) return fail(RB_UNSUPPORTED, "K: " + err);
   } else {
     const uint64_t dims[3] = {Sk, D, G};
-    const uint64_t str[2] = {Sk * 2, D * Sk * 2};
+    const uint64_t pitch = k_repitch ? (uint64_t)sk_pitch : Sk;
+    const uint64_t str[2] = {pitch * 2, D * pitch * 2};
     const uint32_t box[3] = {64, (uint32_t)Dp, 1};
     if (!encode_tiled(&maps.k, dt, 3, k, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B, &err)) return fail(RB_UNSUPPORTED, "K: " + err);
   }
@@ -941,5 +989,11 @@ extern "C" RbStatus rbAttention(const RbAttentionProblem* p, const void* q, cons
   }
   RB_CUDA_TRY(cudaGetLastError());
   count_launch();
+  if (p->trans_o) {   // caller's O is [G][Dv][Sq]
+    restride16_kernel<<<sblocks, 256, 0, stream>>>(static_cast<const uint16_t*>(o), static_cast<uint16_t*>(o_user), p->g, p->head_v,
+                                                   p->seq_q, p->seq_q, (long long)p->seq_q * p->head_v, 1, p->head_v);
+    RB_CUDA_TRY(cudaGetLastError());
+    count_launch();
+  }
   return RB_SUCCESS;
 }

@@ -251,9 +251,7 @@ bool parse_attention(const std::map<std::string, std::string>& m, ProblemDesc* h
     }
   }
   if (p.g <= 0 || p.seq_q <= 0 || p.seq_k <= 0) return false;
-  if (p.trans_q || p.trans_v || p.trans_o) return false;
   if (p.head_qk % 8 || p.head_qk > 128 || p.head_qk <= 0 || p.head_v % 8 || p.head_v > 128 || p.head_v <= 0) return false;
-  if (!p.trans_k && p.seq_k % 8) return false;
   p.data_type = t;
   h->kind = kAttention;
   return true;

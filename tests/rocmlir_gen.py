@@ -331,11 +331,8 @@ def run_attention(f: Dict[str, str]) -> List[int]:
         sq, sk, d, dv = int(f["seq_len_q"]), int(f["seq_len_k"]), int(f["head_dim_qk"]), int(f["head_dim_v"])
     if d % 8 or dv % 8 or d > 128 or dv > 128:
         raise Unsupported("head dimensions that are not multiples of 8 up to 128")
-    if as_bool(f, "transQ") or as_bool(f, "transV") or as_bool(f, "transO"):
-        raise Unsupported("transQ / transV / transO")
+    tq, tv, to = as_bool(f, "transQ"), as_bool(f, "transV"), as_bool(f, "transO")
     tk = as_bool(f, "transK")
-    if not tk and sk % 8:
-        raise Unsupported("K stored G x D x Sk needs seq_len_k % 8 == 0")
     fill = Filler(f)
     q_f, q_r = fill.tensor(g * sq * d, code)
     k_f, k_r = fill.tensor(g * sk * d, code)
@@ -351,26 +348,30 @@ def run_attention(f: Dict[str, str]) -> List[int]:
     if as_bool(f, "with-attn-bias"):
         bi = fill.tensor(g * sq * sk, code)
     fill.tensor(g * sq * dv, code)
+    # stored shapes follow the trans flags (rocmlir-gen.cpp:2149-2200); the oracle takes Q [G,Sq,D], K [G,D,Sk],
+    # V [G,Sk,Dv] and returns O [G,Sq,Dv]
+    q_shape = (g, d, sq) if tq else (g, sq, d)
     k_shape = (g, sk, d) if tk else (g, d, sk)
-    k_log = k_f.reshape(k_shape).transpose(0, 2, 1) if tk else k_f.reshape(k_shape)   # oracle wants [G, D, Sk]
+    v_shape = (g, dv, sk) if tv else (g, sk, dv)
+    logical = lambda a, shape, t: np.ascontiguousarray(a.reshape(shape).transpose(0, 2, 1) if t else a.reshape(shape))
+    sc_f = None if sc is None else sc[0].reshape(g, sq, sk)
+    bi_f = None if bi is None else bi[0].reshape(g, sq, sk)
+    kw = dict(trans_q=tq, trans_k=tk, trans_v=tv, trans_o=to,
+              scale_tensor=None if sc is None else to_device(sc[1].reshape(g, sq, sk), code),
+              bias=None if bi is None else to_device(bi[1].reshape(g, sq, sk), code))
     if quantized:
-        want = oracle.attention_i8(q_r.reshape(g, sq, d), np.ascontiguousarray(k_log).astype(np.int8),
-                                   v_f.reshape(g, sk, dv), int(qb_f[0]), float(qs_f[0]),
-                                   scale=None if sc is None else sc[0].reshape(g, sq, sk),
-                                   bias=None if bi is None else bi[0].reshape(g, sq, sk), threads=oracle.max_threads())
-        o = attention(to_device(q_r.reshape(g, sq, d), oracle.I8), to_device(k_r.reshape(k_shape), oracle.I8),
-                      to_device(v_r.reshape(g, sk, dv), code), trans_k=tk,
-                      quant_bias=to_device(qb_r, oracle.I8), quant_scale=to_device(qs_r, oracle.F16),
-                      scale_tensor=None if sc is None else to_device(sc[1].reshape(g, sq, sk), code),
-                      bias=None if bi is None else to_device(bi[1].reshape(g, sq, sk), code))
-        return verdict_for(from_device(o, code).ravel(), want.ravel(), code, f)
-    want = oracle.attention(q_f.reshape(g, sq, d), np.ascontiguousarray(k_log), v_f.reshape(g, sk, dv), elem_type=code,
-                            scale=None if sc is None else sc[0].reshape(g, sq, sk),
-                            bias=None if bi is None else bi[0].reshape(g, sq, sk), threads=oracle.max_threads())
-    o = attention(to_device(q_r.reshape(g, sq, d), code), to_device(k_r.reshape(k_shape), code),
-                  to_device(v_r.reshape(g, sk, dv), code), trans_k=tk,
-                  scale_tensor=None if sc is None else to_device(sc[1].reshape(g, sq, sk), code),
-                  bias=None if bi is None else to_device(bi[1].reshape(g, sq, sk), code))
+        want = oracle.attention_i8(logical(q_r, q_shape, tq), logical(k_r, k_shape, tk), logical(v_f, v_shape, tv),
+                                   int(qb_f[0]), float(qs_f[0]), scale=sc_f, bias=bi_f, threads=oracle.max_threads())
+        o = attention(to_device(q_r.reshape(q_shape), oracle.I8), to_device(k_r.reshape(k_shape), oracle.I8),
+                      to_device(v_r.reshape(v_shape), code), quant_bias=to_device(qb_r, oracle.I8),
+                      quant_scale=to_device(qs_r, oracle.F16), **kw)
+    else:
+        want = oracle.attention(logical(q_f, q_shape, tq), logical(k_f, k_shape, tk), logical(v_f, v_shape, tv),
+                                elem_type=code, scale=sc_f, bias=bi_f, threads=oracle.max_threads())
+        o = attention(to_device(q_r.reshape(q_shape), code), to_device(k_r.reshape(k_shape), code),
+                      to_device(v_r.reshape(v_shape), code), **kw)
+    if to:
+        want = np.ascontiguousarray(want.transpose(0, 2, 1))
     return verdict_for(from_device(o, code).ravel(), want.ravel(), code, f)
 
 

@@ -154,3 +154,29 @@ def test_first_gemm_quantised_attention(cuda_device, trans_k, with_side):
     got = o.float().cpu().numpy()
     verdict, info = oracle.verify_float(got, oracle.round_to(want, oracle.F16), 1e-3, 100.0, 100.0)
     assert verdict == [1, 1, 1], info
+
+
+@pytest.mark.parametrize("tq,tk,tv,to", [(True, False, False, False), (False, True, True, False),
+                                         (False, False, False, True), (True, True, True, True)])
+def test_transposed_operand_forms(cuda_device, tq, tk, tv, to):
+    """rocmlir-gen's -transQ / -transK / -transV / -transO (rocmlir-gen.cpp:2149-2200): the same operation on operands
+    stored transposed must give the same bits as on the plain ones, and so must K stored G x D x Sk with Sk = 27,
+    whose rows do not start on 16-byte boundaries."""
+    import torch
+    from rocmlir_b200.attention import attention
+    g, sq, sk, d, dv = 2, 150, 27, 64, 32
+    (q, qraw), (k, kraw), (v, vraw) = make_qkv(g, sq, sk, d, dv, oracle.F16)
+    from helpers import to_device
+    dev = lambda a: to_device(np.ascontiguousarray(a), oracle.F16)
+    scale = 1.0 / math.sqrt(d)
+    base = attention(dev(qraw), dev(kraw.transpose(0, 2, 1)), dev(vraw), trans_k=True, scale=scale)   # K [G,Sk,D]
+    got = attention(dev(qraw.transpose(0, 2, 1)) if tq else dev(qraw),
+                    dev(kraw.transpose(0, 2, 1)) if tk else dev(kraw),
+                    dev(vraw.transpose(0, 2, 1)) if tv else dev(vraw),
+                    trans_q=tq, trans_k=tk, trans_v=tv, trans_o=to, scale=scale)
+    torch.cuda.synchronize()
+    if to:
+        got = got.transpose(1, 2)
+    assert torch.equal(got.contiguous(), base)
+    ref64 = oracle.attention(q, k, v, elem_type=oracle.F64, scale_scalar=scale, threads=oracle.max_threads())
+    assert np.abs(base.float().cpu().numpy() - ref64).max() <= 2.0 ** -9 * max(1.0, np.abs(ref64).max())
