@@ -210,8 +210,9 @@ RB_EXPORT RbStatus rbConv3d(const RbConv3dProblem *p, void *filter, void *input,
  * (optional)  + bias[g][q][k]
  * (optional, element type)  then  where(mask[g][q][k] != 0, s, mask_fill) (optional, i8: the mixr-attn-where form)
  * then, with `causal`, keys k > q are dropped analytically (equal to a lower-triangular mask with fill -inf, without
- * reading a [G][Sq][Sk] tensor). Row statistics are f32. f16 and bf16 (and the i8 form below); head dimensions
- * multiples of 8 up to 128. trans_q / trans_v / trans_o mean Q [G][D][Sq], V [G][Dv][Sk], O [G][Dv][Sq]
+ * reading a [G][Sq][Sk] tensor). Row statistics are f32. f16 and bf16 (and the i8 form below) with head dimensions
+ * multiples of 8 up to 128; f32 (any head dimension) runs as three kernels in true f32 - both products on the FMA
+ * pipe in the reference's operation order around a row softmax - with the score matrix in scratch. trans_q / trans_v / trans_o mean Q [G][D][Sq], V [G][Dv][Sk], O [G][Dv][Sq]
  * (rocmlir-gen's -transQ / -transV / -transO); those, and a K [G][D][Sk] whose rows do not start on 16-byte
  * boundaries, cost one re-striding pass each in scratch memory the calling thread owns. */
 typedef struct RbAttentionProblem {

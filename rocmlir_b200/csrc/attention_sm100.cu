@@ -23,6 +23,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <algorithm>
 #include <string>
 
 #include "epilogue.cuh"
@@ -821,6 +822,125 @@ __global__ void restride16_kernel(const uint16_t* __restrict__ src, uint16_t* __
   }
 }
 
+// f32 attention is a precision-first path. The reference's f32 suite accepts a relative difference of 5e-6 on EVERY
+// nonzero element (PrAttentionF32.toml:3), including results that are small by cancellation; a TF32 split (hi + lo,
+// 22 bits) leaves 5e-7 of the largest term there, which fails it, so both products run in true f32 on the FMA pipe
+// (sgemm_strided_kernel) around this row softmax over the score matrix in scratch. Operation order is the
+// reference's (rocmlir-gen.cpp:2582-2630): f(s), row maximum, exp(s - max), row sum, times the reciprocal of the sum.
+struct SgemmParams {
+  int M, N, K;
+  long long a_g, a_m, a_k;   // element strides of A[g][m][k], B[g][k][n], C[g][m][n]
+  long long b_g, b_k, b_n;
+  long long c_g, c_m, c_n;
+};
+
+// C = A . B in f32, k ascending, product and sum rounded separately like the reference's generated host loops (no
+// contraction flags are set there): 64 x 64 tile per 256-thread block, 4 x 4 per thread
+__global__ void __launch_bounds__(256) sgemm_strided_kernel(const float* __restrict__ A, const float* __restrict__ B,
+                                                            float* __restrict__ C, SgemmParams p) {
+  __shared__ float As[16][64 + 4];
+  __shared__ float Bs[16][64 + 4];
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+  const float* Ag = A + (long long)blockIdx.z * p.a_g;
+  const float* Bg = B + (long long)blockIdx.z * p.b_g;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+  for (int k0 = 0; k0 < p.K; k0 += 16) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int idx = threadIdx.x + i * 256;
+      // A tile: walk the dimension that is contiguous in memory fastest
+      const int am = p.a_k == 1 ? idx / 16 : idx % 64, ak = p.a_k == 1 ? idx % 16 : idx / 64;
+      As[ak][am] = (m0 + am < p.M && k0 + ak < p.K) ? Ag[(long long)(m0 + am) * p.a_m + (long long)(k0 + ak) * p.a_k] : 0.0f;
+      const int bn = p.b_n == 1 ? idx % 64 : idx / 16, bk = p.b_n == 1 ? idx / 64 : idx % 16;
+      Bs[bk][bn] = (n0 + bn < p.N && k0 + bk < p.K) ? Bg[(long long)(k0 + bk) * p.b_k + (long long)(n0 + bn) * p.b_n] : 0.0f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < 16; ++kk) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { a[i] = As[kk][ty * 4 + i]; b[i] = Bs[kk][tx * 4 + i]; }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = __fadd_rn(acc[i][j], __fmul_rn(a[i], b[j]));   // no contraction
+    }
+    __syncthreads();
+  }
+  float* Cg = C + (long long)blockIdx.z * p.c_g;
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
+      if (m < p.M && n < p.N) Cg[(long long)m * p.c_m + (long long)n * p.c_n] = acc[i][j];
+    }
+}
+
+struct SoftmaxF32Params {
+  long long G, Sq, Sk;
+  int has_scale, causal;
+  float scale, mask_fill;
+  const float* scale_t;
+  const float* bias;
+  const int8_t* mask;
+};
+
+__global__ void softmax_rows_f32_kernel(float* __restrict__ s, SoftmaxF32Params p) {
+  __shared__ float red[32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  auto block_reduce = [&](float v, bool is_max) -> float {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float w = __shfl_xor_sync(0xffffffffu, v, o);
+      v = is_max ? fmaxf(v, w) : v + w;
+    }
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float r = red[0];
+    for (int i = 1; i < nwarps; ++i) r = is_max ? fmaxf(r, red[i]) : r + red[i];
+    return r;
+  };
+  for (long long row = blockIdx.x; row < p.G * p.Sq; row += gridDim.x) {
+    float* sr = s + row * p.Sk;
+    const long long q = row % p.Sq;
+    const long long side = row * p.Sk;
+    float mx = -INFINITY;
+    for (long long j = threadIdx.x; j < p.Sk; j += blockDim.x) {
+      float x = sr[j];
+      if (p.has_scale) x *= p.scale;
+      if (p.scale_t) x *= p.scale_t[side + j];
+      if (p.bias) x += p.bias[side + j];
+      if (p.mask && p.mask[side + j] == 0) x = p.mask_fill;
+      if (p.causal && j > q) x = -INFINITY;
+      sr[j] = x;
+      mx = fmaxf(mx, x);
+    }
+    mx = block_reduce(mx, true);
+    // exp through double and rounded once (what the host's expf returns), and the row sum taken by one thread in key
+    // order like the reference's loop: results that are small by cancellation inherit every ulp of P, and the f32
+    // suite judges each element at 5e-6 relative
+    for (long long j = threadIdx.x; j < p.Sk; j += blockDim.x)
+      sr[j] = (mx == -INFINITY) ? 0.0f : (float)exp((double)(sr[j] - mx));
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float acc = 0.0f;
+      for (long long j = 0; j < p.Sk; ++j) acc = __fadd_rn(acc, sr[j]);
+      red[0] = acc;
+    }
+    __syncthreads();
+    const float l = red[0];
+    const float rl = l > 0.0f ? 1.0f / l : 0.0f;
+    for (long long j = threadIdx.x; j < p.Sk; j += blockDim.x) sr[j] *= rl;
+  }
+}
+
 // Scratch for the widened Q and K: grow-only, owned by the calling thread (a growth waits for the device first, so
 // no kernel in flight still reads the old block).
 struct QkScratch {
@@ -845,6 +965,41 @@ RbStatus qk_reserve(size_t bytes) {
   return RB_SUCCESS;
 }
 
+RbStatus attention_f32(const RbAttentionProblem* p, const void* q, const void* k, const void* v, void* o, void* stream_v) {
+  const DeviceInfo* dev = device_info();
+  if (!dev) return RB_CUDA_ERROR;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  const long long G = p->g, Sq = p->seq_q, Sk = p->seq_k, D = p->head_qk, Dv = p->head_v;
+  if (G > 65535) return fail(RB_UNSUPPORTED, "f32 attention: more than 65535 groups");
+  RbStatus st = qk_reserve((size_t)G * Sq * Sk * 4);
+  if (st != RB_SUCCESS) return st;
+  float* s = static_cast<float*>(t_qk.ptr);
+  SgemmParams g1;   // S[g] = Q[g] . K[g]:  M = Sq, N = Sk, K = D
+  g1.M = (int)Sq; g1.N = (int)Sk; g1.K = (int)D;
+  g1.a_g = Sq * D; g1.a_m = p->trans_q ? 1 : D; g1.a_k = p->trans_q ? Sq : 1;     // Q [Sq][D] or [D][Sq]
+  g1.b_g = Sk * D; g1.b_k = p->trans_k ? 1 : Sk; g1.b_n = p->trans_k ? D : 1;     // K [D][Sk] or [Sk][D]
+  g1.c_g = Sq * Sk; g1.c_m = Sk; g1.c_n = 1;
+  sgemm_strided_kernel<<<dim3((unsigned)((Sk + 63) / 64), (unsigned)((Sq + 63) / 64), (unsigned)G), 256, 0, stream>>>(
+      static_cast<const float*>(q), static_cast<const float*>(k), s, g1);
+  SoftmaxF32Params sp;
+  sp.G = G; sp.Sq = Sq; sp.Sk = Sk;
+  sp.has_scale = p->has_scale; sp.causal = p->causal; sp.scale = p->scale; sp.mask_fill = p->mask_fill;
+  sp.scale_t = static_cast<const float*>(p->scale_tensor);
+  sp.bias = static_cast<const float*>(p->bias);
+  sp.mask = p->mask;
+  softmax_rows_f32_kernel<<<(unsigned)std::min<long long>(G * Sq, (long long)dev->sm_count * 16), 256, 0, stream>>>(s, sp);
+  SgemmParams g2;   // O[g] = P[g] . V[g]:  M = Sq, N = Dv, K = Sk
+  g2.M = (int)Sq; g2.N = (int)Dv; g2.K = (int)Sk;
+  g2.a_g = Sq * Sk; g2.a_m = Sk; g2.a_k = 1;
+  g2.b_g = Sk * Dv; g2.b_k = p->trans_v ? 1 : Dv; g2.b_n = p->trans_v ? Sk : 1;   // V [Sk][Dv] or [Dv][Sk]
+  g2.c_g = Sq * Dv; g2.c_m = p->trans_o ? 1 : Dv; g2.c_n = p->trans_o ? Sq : 1;   // O [Sq][Dv] or [Dv][Sq]
+  sgemm_strided_kernel<<<dim3((unsigned)((Dv + 63) / 64), (unsigned)((Sq + 63) / 64), (unsigned)G), 256, 0, stream>>>(
+      s, static_cast<const float*>(v), static_cast<float*>(o), g2);
+  RB_CUDA_TRY(cudaGetLastError());
+  count_launch(3);
+  return RB_SUCCESS;
+}
+
 }  // namespace
 }  // namespace rb
 
@@ -857,8 +1012,9 @@ extern "C" RbStatus rbAttention(const RbAttentionProblem* p, const void* q, cons
     return fail(RB_INVALID_PARAM, "g, seq_len_q, seq_len_k, head_dim_qk, head_dim_v must be positive");
   if (!q || !k || !v || !o) return fail(RB_INVALID_PARAM, "q, k, v and o must be device pointers");
   const bool quantized = p->data_type == RB_I8;
+  if (p->data_type == RB_F32) return attention_f32(p, q, k, v, o, stream_v);
   if (!(p->data_type == RB_F16 || p->data_type == RB_BF16 || quantized))
-    return fail(RB_UNSUPPORTED, "attention kernels exist for f16, bf16 and the first-GEMM-quantised i8 form");
+    return fail(RB_UNSUPPORTED, "attention exists for f32, f16, bf16 and the first-GEMM-quantised i8 form");
   if (quantized && (!p->quant_bias || !p->quant_scale))
     return fail(RB_INVALID_PARAM, "the i8 form needs quant_bias and quant_scale");
   if (quantized && p->causal) return fail(RB_UNSUPPORTED, "the i8 form has no analytic causal mask");

@@ -12,7 +12,7 @@ import tomllib
 
 # matrices that exercise the path of this library (PR suites + regression lists); the nightly model sweeps
 # (Resnet50Config, Resnet101Config, Resnext101Config) repeat the same kernels on ~100 more shapes each
-FILES = ["PrGemm.toml", "PrGemmSplitK.toml", "PrResnet50.toml", "PrAttentionF16.toml", "PrAttentionI8.toml",
+FILES = ["PrGemm.toml", "PrGemmSplitK.toml", "PrResnet50.toml", "PrAttentionF16.toml", "PrAttentionI8.toml", "PrAttentionF32.toml",
          "PaddedGemmConfig.toml",
          "GemmVariants.toml", "MixedConvLayouts.toml", "conv_regression_fwd.toml", "conv_regression_bwd.toml",
          "gemm_split_k_f16.toml", "gemm_split_k_f32.toml", "conv_wrw_perf_config.toml"]

@@ -322,14 +322,14 @@ def run_attention(f: Dict[str, str]) -> List[int]:
     ty = resolve_types(f)
     code = ty.a
     quantized = code == oracle.I8       # first GEMM i8 x i8, everything else f16 (rocmlir-gen.cpp:3497-3515)
-    if code not in (oracle.F16, oracle.BF16, oracle.I8):
-        raise Unsupported("attention kernels exist for f16, bf16 and the first-GEMM-quantised i8 form")
+    if code not in (oracle.F32, oracle.F16, oracle.BF16, oracle.I8):
+        raise Unsupported("attention exists for f32, f16, bf16 and the first-GEMM-quantised i8 form")
     if as_bool(f, "p"):
         g, sq, sk, d, dv = 1, 1024, 1024, 32, 32
     else:
         g = int(f.get("g", 1))
         sq, sk, d, dv = int(f["seq_len_q"]), int(f["seq_len_k"]), int(f["head_dim_qk"]), int(f["head_dim_v"])
-    if d % 8 or dv % 8 or d > 128 or dv > 128:
+    if code != oracle.F32 and (d % 8 or dv % 8 or d > 128 or dv > 128):
         raise Unsupported("head dimensions that are not multiples of 8 up to 128")
     tq, tv, to = as_bool(f, "transQ"), as_bool(f, "transV"), as_bool(f, "transO")
     tk = as_bool(f, "transK")

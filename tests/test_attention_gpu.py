@@ -180,3 +180,28 @@ def test_transposed_operand_forms(cuda_device, tq, tk, tv, to):
     assert torch.equal(got.contiguous(), base)
     ref64 = oracle.attention(q, k, v, elem_type=oracle.F64, scale_scalar=scale, threads=oracle.max_threads())
     assert np.abs(base.float().cpu().numpy() - ref64).max() <= 2.0 ** -9 * max(1.0, np.abs(ref64).max())
+
+
+@pytest.mark.parametrize("g,sq,sk,d,dv", [(2, 384, 384, 64, 64), (1, 128, 27, 64, 32), (2, 77, 200, 40, 24)])
+def test_f32_attention_unfused(cuda_device, g, sq, sk, d, dv):
+    """-t f32: two 3xTF32 GEMMs around a row softmax. On the reference's -rand 1 integer data the scores are exact, and
+    the result must pass the reference verifier at the thresholds of its f32 PR suite (RMS 3e-5 default, relDiff 5e-6:
+    PrAttentionF32.toml:3); with scale and bias tensors as well."""
+    import torch
+    from rocmlir_b200.attention import attention
+    from helpers import reference_random
+    (q, _), (k, _), (v, _), (sc, _), (bi, _) = reference_random([(g, sq, d), (g, d, sk), (g, sk, dv), (g, sq, sk),
+                                                                  (g, sq, sk)], oracle.F32, seed=1)
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to("cuda")
+    for side in (False, True):
+        want = oracle.attention(q, k, v, elem_type=oracle.F32, scale=sc if side else None, bias=bi if side else None,
+                                threads=oracle.max_threads())
+        got = attention(dev(q), dev(k), dev(v), scale_tensor=dev(sc) if side else None, bias=dev(bi) if side else None)
+        torch.cuda.synchronize()
+        verdict, info = oracle.verify_float(got.cpu().numpy(), want, 3e-5, 100.0, 5e-6)
+        assert verdict == [1, 1, 1], info
+    # a scalar scale and the analytic causal mask against the float64 oracle
+    qn, kn, vn = (np.random.default_rng(s).standard_normal(x.shape).astype(np.float32) for s, x in ((1, q), (2, k), (3, v)))
+    ref64 = oracle.attention(qn, kn, vn, elem_type=oracle.F64, scale_scalar=0.125, causal=True, threads=oracle.max_threads())
+    got = attention(dev(qn), dev(kn), dev(vn), scale=0.125, causal=True).cpu().numpy()
+    assert np.abs(got - ref64).max() <= 2e-5 * max(1.0, np.abs(ref64).max())
