@@ -9,6 +9,11 @@
 // (:2338-2356). Differences by design: the row statistics are f32 (the reference keeps them in the element
 // type), and a causal mask can be given analytically instead of as a [G,Sq,Sk] tensor.
 //
+// Element types: f16 and bf16 on the kernels below; the first-GEMM-quantised form of rocmlir-gen -t i8 on the same
+// kernels after widening Q and K to f16 (exact), with the reference's f16 rounding chain reproduced in f; f32 on a
+// separate unfused true-f32 path (attention_f32). Operands stored transposed (transQ / transV / transO) and K rows
+// off 16-byte boundaries are re-strided in scratch first.
+//
 // CTA = one 128-row query tile, 256 threads:
 //   warp 0   producer: TMA loads of Q (once) and of the K and V tiles of each key block (2-deep rings)
 //   warp 1   MMA issuer: S_j = Q.K_j^T into one of two TMEM score buffers, O += P_j.V_j
