@@ -288,6 +288,36 @@ __global__ void interleave_classes_kernel(const uint8_t* __restrict__ cls, uint8
   }
 }
 
+// The filter matrices of all stride classes in one pass. Class i gets B_i[c][(y', x', k)] =
+// fil[k][c][y0 + stride_h * (ty - 1 - y')][x0 + stride_w * (tx - 1 - x')]: its sub-sampled taps, mirrored, in the
+// c x (taps, k) form the unit-stride implicit GEMM reads (one group).
+struct ClassFilters {
+  long long s_k, s_c, s_y, s_x;     // filter strides in elements
+  int K, C, sh, sw, n;
+  int y0[16], x0[16], ty[16], tx[16];
+  long long dst[16];                // element offset of B_i in the workspace
+  long long first[17];              // prefix sums of the element counts
+};
+
+template <int ES>
+__global__ void class_filters_kernel(const uint8_t* __restrict__ fil, uint8_t* __restrict__ ws, ClassFilters f) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < f.first[f.n]; i += (long long)gridDim.x * blockDim.x) {
+    int c = 0;
+    while (i >= f.first[c + 1]) ++c;
+    long long r = i - f.first[c];
+    const int k = (int)(r % f.K); r /= f.K;
+    const int xp = (int)(r % f.tx[c]); r /= f.tx[c];
+    const int yp = (int)(r % f.ty[c]);
+    const int ch = (int)(r / f.ty[c]);
+    const long long src = (long long)k * f.s_k + (long long)ch * f.s_c +
+                          (long long)(f.y0[c] + f.sh * (f.ty[c] - 1 - yp)) * f.s_y +
+                          (long long)(f.x0[c] + f.sw * (f.tx[c] - 1 - xp)) * f.s_x;
+    const long long d = f.dst[c] + (i - f.first[c]);
+    if (ES == 2) reinterpret_cast<uint16_t*>(ws)[d] = reinterpret_cast<const uint16_t*>(fil)[src];
+    if (ES == 4) reinterpret_cast<uint32_t*>(ws)[d] = reinterpret_cast<const uint32_t*>(fil)[src];
+  }
+}
+
 size_t up256(size_t x) { return (x + 255) / 256 * 256; }
 
 // Named-dimension strides of a tensor stored in `layout` order (row-major over the letters).
@@ -328,8 +358,12 @@ struct ConvPlan {
     RbConvProblem q;
     int ph, pw, y0, x0;
     size_t fil_off, out_off, ws_bytes;   // sub-filter, class block; out_off = SIZE_MAX for a class without taps
+    RbGemmProblem gemm;                  // the class's GEMM when the whole set runs fused
+    size_t gemm_ws;
+    bool pointwise;                      //   a single tap without padding: A is the output gradient in place
   } cls[16];
   size_t cls_ws_off = 0;
+  bool cls_fused = false;   // every class takes the implicit unit-stride path: one filter pass, one GEMM per class
 };
 
 bool is_dense_in_order(const long long* strides, const long long* sizes, const int* order, int n) {
@@ -477,7 +511,7 @@ RbStatus make_plan(const RbConvProblem* p, ConvPlan* pl, int result_type = -1) {
   if (p->direction == 1 && result_type < 0 && (p->stride_h > 1 || p->stride_w > 1) && p->dil_h == 1 && p->dil_w == 1 &&
       p->stride_h <= 4 && p->stride_w <= 4) {
     // stride classes: every class is a unit-stride backward-data problem over the same output gradient
-    bool ok = true;
+    bool ok = true, fused = true;
     size_t off = 0, sub_ws = 0;
     int nc = 0;
     for (int ph = 0; ph < p->stride_h && ok; ++ph)
@@ -506,14 +540,23 @@ RbStatus make_plan(const RbConvProblem* p, ConvPlan* pl, int result_type = -1) {
         if (c.q.pad_h_r < 0 || c.q.pad_w_r < 0) { ok = false; break; }
         c.fil_off = off; off += up256((size_t)G * p->k * ty * tx * p->c * es);
         c.out_off = off; off += up256((size_t)p->n * hs * wsz * G * p->c * es);
-        c.ws_bytes = conv_workspace_bytes(&c.q, -1);
-        if (c.ws_bytes == 0) {
-          ConvPlan probe;   // 0 also means "invalid": ask the plan itself
-          if (make_plan(&c.q, &probe, -1) != RB_SUCCESS) { ok = false; break; }
+        {
+          ConvPlan sub;
+          if (make_plan(&c.q, &sub, -1) != RB_SUCCESS) { ok = false; break; }
+          c.ws_bytes = sub.total;
+          c.gemm = sub.gemm;
+          c.gemm_ws = sub.gemm_ws;
+          c.pointwise = !sub.a_implicit && sub.a_direct;   // one tap, no padding: the output gradient is the A matrix
+          if (c.pointwise) {
+            c.gemm.trans_b = 1;                            // the filter pass writes c x k for every class
+            c.gemm_ws = gemm_workspace_bytes(&c.gemm, -1);
+          }
+          if (!((sub.a_implicit || c.pointwise) && sub.c_direct && !sub.a_up && G == 1)) fused = false;
         }
         sub_ws = std::max(sub_ws, c.ws_bytes);
       }
     if (ok) {
+      pl->cls_fused = fused;
       pl->n_classes = nc;
       pl->cls_ws_off = off;
       pl->total = off + up256(sub_ws);
@@ -564,9 +607,9 @@ extern "C" int rbConvKernelCount(const RbConvProblem* p) {
   ConvPlan pl;
   if (make_plan(p, &pl) != RB_SUCCESS) return -1;
   if (pl.n_classes > 0) {
-    int n = 1;   // the interleaving pass
+    int n = 1 + (pl.cls_fused ? 1 : 0);   // the interleaving pass (and the one filter pass of the fused form)
     for (int i = 0; i < pl.n_classes; ++i)
-      if (pl.cls[i].out_off != SIZE_MAX) n += 1 + rbConvKernelCount(&pl.cls[i].q);
+      if (pl.cls[i].out_off != SIZE_MAX) n += pl.cls_fused ? 1 : 1 + rbConvKernelCount(&pl.cls[i].q);
     return n;
   }
   return 1 + (pl.a_direct ? 0 : 1) + (pl.b_direct ? 0 : 1) + (pl.c_direct ? 0 : 1);
@@ -659,12 +702,52 @@ RbStatus rb::conv_run(const RbConvProblem* p, int result_type, void* filter, voi
     tb.s_n = pl.is[0]; tb.s_g = pl.is[1]; tb.s_c = pl.is[2]; tb.s_h = pl.is[3]; tb.s_w = pl.is[4];
     tb.sh = p->stride_h; tb.sw = p->stride_w;
     for (int i = 0; i < 16; ++i) { tb.off[i] = -1; tb.hs[i] = tb.wsz[i] = 1; }
+    if (pl.cls_fused) {
+      ClassFilters ft;
+      ft.s_k = pl.fs[1]; ft.s_c = pl.fs[2]; ft.s_y = pl.fs[3]; ft.s_x = pl.fs[4];
+      ft.K = p->k; ft.C = p->c; ft.sh = p->stride_h; ft.sw = p->stride_w;
+      ft.n = 0;
+      ft.first[0] = 0;
+      for (int i = 0; i < pl.n_classes; ++i) {
+        const ConvPlan::StrideClass& c = pl.cls[i];
+        if (c.out_off == SIZE_MAX) continue;
+        const int j = ft.n++;
+        ft.y0[j] = c.y0; ft.x0[j] = c.x0; ft.ty[j] = c.q.y; ft.tx[j] = c.q.x;
+        ft.dst[j] = (long long)(c.fil_off / es);
+        ft.first[j + 1] = ft.first[j] + (long long)p->c * c.q.y * c.q.x * p->k;
+      }
+      const int fb = (int)std::max<long long>(1, std::min<long long>(blocks, (ft.first[ft.n] + 1023) / 1024));
+      if (es == 2) class_filters_kernel<2><<<fb, 256, 0, stream>>>(static_cast<const uint8_t*>(filter), ws, ft);
+      else class_filters_kernel<4><<<fb, 256, 0, stream>>>(static_cast<const uint8_t*>(filter), ws, ft);
+      count_launch();
+    }
     for (int i = 0; i < pl.n_classes; ++i) {
       const ConvPlan::StrideClass& c = pl.cls[i];
       const int k = c.ph * p->stride_w + c.pw;
       if (c.out_off == SIZE_MAX) continue;
       tb.off[k] = (long long)(c.out_off / es);
       tb.hs[k] = c.q.h; tb.wsz[k] = c.q.w;
+      if (pl.cls_fused && c.pointwise) {
+        st = rbGemm(&c.gemm, nullptr, output, ws + c.fil_off, ws + c.out_off, c.gemm_ws ? ws + pl.cls_ws_off : nullptr,
+                    c.gemm_ws, stream_v);
+        if (st != RB_SUCCESS) return st;
+        continue;
+      }
+      if (pl.cls_fused) {
+        // the unit-stride implicit GEMM of the class: "image" = output gradient, "output pixels" = the class's pixels
+        ConvAOperand cv;
+        cv.tensor = output;
+        cv.N = p->n; cv.H = (int)ho; cv.W = (int)wo; cv.C = p->k;
+        cv.P = c.q.h; cv.Q = c.q.w; cv.Y = c.q.y; cv.X = c.q.x;
+        cv.stride_h = cv.stride_w = cv.dil_h = cv.dil_w = 1;
+        cv.pad_h = (c.q.y - 1) - c.q.pad_h; cv.pad_w = (c.q.x - 1) - c.q.pad_w;
+        cv.pad_h_hi = c.q.h - (int)ho - cv.pad_h + (c.q.y - 1);
+        cv.pad_w_hi = c.q.w - (int)wo - cv.pad_w + (c.q.x - 1);
+        st = gemm_run(&c.gemm, nullptr, nullptr, ws + c.fil_off, ws + c.out_off, c.gemm_ws ? ws + pl.cls_ws_off : nullptr,
+                      c.gemm_ws, stream_v, &cv);
+        if (st != RB_SUCCESS) return st;
+        continue;
+      }
       // sub-filter [g][k][j][i][c] = fil[g][k][c][y0 + stride_h * j][x0 + stride_w * i]
       const long long ssz[5] = {p->g, p->k, p->c, c.q.y, c.q.x};
       const long long sst[5] = {pl.fs[0], pl.fs[1], pl.fs[2], pl.fs[3] * p->stride_h, pl.fs[4] * p->stride_w};
