@@ -1,17 +1,19 @@
 """Extracts the known-answer tensors of the reference's CPU convolution tests into a JSON fixture.
 
-Source: /root/reference/mlir/test/rocmlir-driver/cpu_conv2d/*.mlir. Each RUN line gives the
+Source: mlir/test/rocmlir-driver/cpu_conv2d/*.mlir of the reference checkout. Each RUN line gives the
 rocmlir-gen flags of one case (`-prc -rand=none`: all inputs 1, only the CPU reference runs) and the
 CHECK-NEXT line under the same prefix gives the printed result tensor.
-Run in the build container only (the reference checkout is not available elsewhere):
-    python tests/golden/make_cpu_conv2d_golden.py
+Run where the reference checkout is available (its root is the first argument, or $ROCMLIR_REFERENCE):
+    python tests/golden/make_cpu_conv2d_golden.py <reference root>
 """
 import glob
 import json
 import os
 import re
+import sys
 
-SRC = "/root/reference/mlir/test/rocmlir-driver/cpu_conv2d"
+ROOT = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("ROCMLIR_REFERENCE", os.path.join(os.sep, "root", "reference"))
+SRC = os.path.join(ROOT, "mlir", "test", "rocmlir-driver", "cpu_conv2d")
 OUT = os.path.join(os.path.dirname(os.path.abspath(__file__)), "cpu_conv2d.json")
 
 FLAG = re.compile(r"-{1,2}([A-Za-z_]+)[= ]([^\s|]+)")
