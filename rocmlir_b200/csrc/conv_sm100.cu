@@ -265,6 +265,32 @@ __global__ void interleave_classes_kernel(const uint8_t* __restrict__ cls, uint8
   const unsigned G = (unsigned)t.G, W = (unsigned)t.W, H = (unsigned)t.H;
   const unsigned row_items = W * G * cv;                       // < 2^31 (checked by the plan)
   const long long rows = t.N * t.H;
+  if (row_items <= blockDim.x) {
+    // the launch gave every item of a row its own thread: the position inside the row, and with it every division
+    // but the two of the row index, is computed once
+    if (threadIdx.x >= row_items) return;
+    const unsigned i = threadIdx.x;
+    const unsigned c = (i % cv) * per;
+    const unsigned r = i / cv;
+    const unsigned g = r % G, w = r / G;
+    const unsigned kw = w % (unsigned)t.sw, wq = w / (unsigned)t.sw;
+    const long long dcol = (long long)w * t.s_w + (long long)g * t.s_g + (long long)c * t.s_c;
+    for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+      const unsigned h = (unsigned)(row % H);
+      const long long n = row / H;
+      const unsigned k = (h % (unsigned)t.sh) * (unsigned)t.sw + kw, hq = h / (unsigned)t.sh;
+      const long long d = n * t.s_n + (long long)h * t.s_h + dcol;
+      const long long so = t.off[k] < 0 ? -1
+                                        : t.off[k] + ((((n * t.hs[k] + hq) * t.wsz[k] + wq) * (long long)G + g) * t.C + c);
+      if (vec) {
+        *reinterpret_cast<uint4*>(dst + d * ES) = so < 0 ? make_uint4(0, 0, 0, 0) : *reinterpret_cast<const uint4*>(cls + so * ES);
+      } else {
+        if (ES == 2) reinterpret_cast<uint16_t*>(dst)[d] = so < 0 ? (uint16_t)0 : reinterpret_cast<const uint16_t*>(cls)[so];
+        if (ES == 4) reinterpret_cast<uint32_t*>(dst)[d] = so < 0 ? 0u : reinterpret_cast<const uint32_t*>(cls)[so];
+      }
+    }
+    return;
+  }
   for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
     const unsigned h = (unsigned)(row % H);
     const long long n = row / H;
@@ -304,11 +330,11 @@ __global__ void class_filters_kernel(const uint8_t* __restrict__ fil, uint8_t* _
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < f.first[f.n]; i += (long long)gridDim.x * blockDim.x) {
     int c = 0;
     while (i >= f.first[c + 1]) ++c;
-    long long r = i - f.first[c];
-    const int k = (int)(r % f.K); r /= f.K;
-    const int xp = (int)(r % f.tx[c]); r /= f.tx[c];
-    const int yp = (int)(r % f.ty[c]);
-    const int ch = (int)(r / f.ty[c]);
+    unsigned r = (unsigned)(i - f.first[c]);            // a filter has far fewer than 2^32 elements
+    const int k = (int)(r % (unsigned)f.K); r /= (unsigned)f.K;
+    const int xp = (int)(r % (unsigned)f.tx[c]); r /= (unsigned)f.tx[c];
+    const int yp = (int)(r % (unsigned)f.ty[c]);
+    const int ch = (int)(r / (unsigned)f.ty[c]);
     const long long src = (long long)k * f.s_k + (long long)ch * f.s_c +
                           (long long)(f.y0[c] + f.sh * (f.ty[c] - 1 - yp)) * f.s_y +
                           (long long)(f.x0[c] + f.sw * (f.tx[c] - 1 - xp)) * f.s_x;
@@ -756,11 +782,17 @@ RbStatus rb::conv_run(const RbConvProblem* p, int result_type, void* filter, voi
       st = conv_run(&c.q, -1, ws + c.fil_off, ws + c.out_off, output, ws + pl.cls_ws_off, c.ws_bytes, stream_v);
       if (st != RB_SUCCESS) return st;
     }
-    const int ib = (int)std::min<long long>((long long)p->n * p->h, (long long)dev->sm_count * 16);
+    // one thread per item of an image row when a row has at most 1024 items (vectors of 16 bytes where the kernel
+    // can use them: the same test as inside it)
+    const bool ivec = tb.s_c == 1 && (tb.C * (long long)es) % 16 == 0 && (tb.s_n * (long long)es) % 16 == 0 &&
+                      (tb.s_h * (long long)es) % 16 == 0 && (tb.s_w * (long long)es) % 16 == 0 && (tb.s_g * (long long)es) % 16 == 0;
+    const long long row_items = (long long)p->w * p->g * (p->c / (ivec ? (int)(16 / es) : 1));
+    const int ithreads = row_items <= 1024 ? (int)((row_items + 31) / 32 * 32) : 256;
+    const int ib = (int)std::min<long long>((long long)p->n * p->h, (long long)dev->sm_count * (2048 / ithreads) * 2);
     if (es == 2)
-      interleave_classes_kernel<2><<<ib, 256, 0, stream>>>(ws, static_cast<uint8_t*>(input), tb);
+      interleave_classes_kernel<2><<<ib, ithreads, 0, stream>>>(ws, static_cast<uint8_t*>(input), tb);
     else
-      interleave_classes_kernel<4><<<ib, 256, 0, stream>>>(ws, static_cast<uint8_t*>(input), tb);
+      interleave_classes_kernel<4><<<ib, ithreads, 0, stream>>>(ws, static_cast<uint8_t*>(input), tb);
     count_launch();
     RB_CUDA_TRY(cudaGetLastError());
     return RB_SUCCESS;
