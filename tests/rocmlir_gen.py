@@ -99,11 +99,20 @@ def resolve_types(f: Dict[str, str]) -> Types:
     return Types(TYPE_CODES[fil], TYPE_CODES[inp], TYPE_CODES[out])
 
 
+class Planned(Exception):
+    """Raised by plan() once a command line has been parsed, typed and sized, before any tensor is filled."""
+
+
+_PLAN_ONLY = False
+
+
 class Filler:
     """Tensors filled in kernel-argument order (rocmlir-gen.cpp:3157-3218): one libc rand() per element with
     `-rand N`, the fixed pattern or all-ones otherwise."""
 
     def __init__(self, f: Dict[str, str]):
+        if _PLAN_ONLY:
+            raise Planned()
         self.mode = f.get("rand", "fixed")
         self.rand_float = f.get("rand_type", "int") == "float"
         self.mn = int(f.get("rand_min", 0))
@@ -398,6 +407,33 @@ def run(flags: str) -> List[int]:
     if L.kernel_status() != 0:
         raise RuntimeError("a kernel reported a bounded-wait timeout")
     return v
+
+
+def plan(flags: str) -> None:
+    """Parses, types and sizes one command line exactly as run() does and stops before touching data or the GPU:
+    raises Unsupported / ValueError like run(), returns None for a line run() would execute."""
+    global _PLAN_ONLY
+    f = parse_flags(flags.replace("%arch", "sm_100a"))
+    if f.get("arch", "sm_100a") not in ("sm_100a", "sm_100"):
+        raise ValueError("architecture is not this hardware")
+    if "pv_with_gpu" in f or "pv_with_mlir" in f:
+        raise Unsupported("validation against a second GPU kernel: the CPU validator is the oracle here")
+    op = f.get("operation", "conv")
+    _PLAN_ONLY = True
+    try:
+        if op == "gemm":
+            run_gemm(f)
+        elif op in ("conv", "conv_bwd_data", "conv_bwd_weight"):
+            run_conv(f, {"conv": 0, "conv_bwd_data": 1, "conv_bwd_weight": 2}[op])
+        elif op == "attention":
+            run_attention(f)
+        else:
+            raise ValueError(f"unknown operation {op}")
+    except Planned:
+        return None
+    finally:
+        _PLAN_ONLY = False
+    raise AssertionError("the operation ran without building a Filler")
 
 
 def main(argv: List[str]) -> int:
