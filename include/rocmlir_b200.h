@@ -19,7 +19,7 @@
 extern "C" {
 #endif
 
-#define RB_API_VERSION 1
+#define RB_API_VERSION 2
 
 #if defined(__GNUC__)
 #define RB_EXPORT __attribute__((visibility("default")))
@@ -50,7 +50,8 @@ typedef enum RbStatus {
                              mlirMIGraphXAddApplicabilityPipeline (mlir-c/Dialect/MIGraphX.h:66-73) */
   RB_WORKSPACE_TOO_SMALL = 3,
   RB_CUDA_ERROR = 4,
-  RB_KERNEL_TIMEOUT = 5   /* a bounded device-side wait ran out; see rbReadKernelStatus */
+  RB_KERNEL_TIMEOUT = 5   /* a bounded device-side wait ran out. Returned by the synchronous entry points (rbGemmHost);
+                             the asynchronous ones return before the kernel ends: poll rbReadKernelStatus */
 } RbStatus;
 
 /* Fused elementwise epilogue applied to the accumulator tile before the single global store.
@@ -257,7 +258,8 @@ RB_EXPORT int rbGetGemmVariant(void);
 /* The tile configuration the library would launch for `p` under the calling thread's variant word (on a
  * 148-SM B200): the information rocMLIR attaches to a lowered kernel as block_size / grid_size attributes
  * (mlir/lib/Dialect/Rock/Transforms/AffixTuningParameters.cpp:69-87) plus what a 1-D launch cannot carry on
- * this hardware (dynamic shared memory, CTAs per cluster). `variant` is the explicit variant word that
+ * this hardware (dynamic shared memory, CTAs per cluster). Planned for the SM count of the current device (148
+ * without one). `variant` is the explicit variant word that
  * reproduces the configuration. */
 typedef struct RbGemmConfigInfo {
   int32_t tile_m, tile_n, tile_k; /* output tile of one CTA group; K elements per pipeline stage */
@@ -266,8 +268,11 @@ typedef struct RbGemmConfigInfo {
   int32_t splits;                 /* K ranges (1 = no split) */
   int32_t stream_k;               /* 1 when the stream-K tail is active */
   uint32_t grid, block;           /* 1-D launch: CTAs and threads per CTA */
-  uint32_t dynamic_smem;          /* bytes */
-  uint32_t variant;
+  uint32_t dynamic_smem;          /* bytes, for a call without per-column epilogue vectors */
+  uint32_t variant;               /* reproduces tile, CTAs, ring depth, K split, stream-K and kpr when set explicitly */
+  int32_t kpr;                    /* K blocks per barrier round of the ring (1, 2 or 4) */
+  int32_t stages_epi_vec;         /* ring depth and dynamic shared memory of the same problem when the epilogue */
+  uint32_t dynamic_smem_epi_vec;  /* carries bias[] or col_scale[] (their staging takes room from the ring) */
 } RbGemmConfigInfo;
 RB_EXPORT RbStatus rbGemmGetConfig(const RbGemmProblem *p, RbGemmConfigInfo *out);
 
@@ -281,6 +286,17 @@ RB_EXPORT void rbSetTraceBuffer(unsigned long long *device_buf, size_t n_u64);
 
 /* Device status word: 0 when every bounded wait completed. Synchronises the device. */
 RB_EXPORT RbStatus rbReadKernelStatus(uint32_t *status_out, int clear);
+
+/* Budget of every bounded device-side wait of the GEMM kernel (mbarrier and flag waits of all roles) for launches
+ * made by the calling thread, in SM clock cycles; 0 restores the default of about two seconds. When a wait runs
+ * out the role records a code in the status word, the CTA frees its tensor memory and returns: the context stays
+ * usable and the next launch works. The reference has no counterpart (a hung kernel there is the runtime's). */
+RB_EXPORT void rbSetWaitLimit(uint64_t sm_cycles);
+
+/* Failure-detection test hook: the next `launches` GEMM kernels launched by the calling thread issue no operand
+ * loads, so that every wait of every role runs out after the wait limit and the kernel returns with a nonzero
+ * status word and an undefined result. Injected on the host; nothing faults or hangs. */
+RB_EXPORT void rbInjectStall(int launches);
 
 /* Number of kernel launches this library issued since load (a monotone counter). */
 RB_EXPORT uint64_t rbLaunchCount(void);

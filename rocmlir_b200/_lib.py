@@ -61,7 +61,8 @@ class RbAttentionProblem(C.Structure):
 
 class RbGemmConfigInfo(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("tile_m", "tile_n", "tile_k", "ctas", "stages", "splits", "stream_k")] + \
-               [(n, C.c_uint32) for n in ("grid", "block", "dynamic_smem", "variant")]
+               [(n, C.c_uint32) for n in ("grid", "block", "dynamic_smem", "variant")] + \
+               [("kpr", C.c_int32), ("stages_epi_vec", C.c_int32), ("dynamic_smem_epi_vec", C.c_uint32)]
 
 
 class _Handle(C.Structure):
@@ -195,6 +196,10 @@ def lib() -> C.CDLL:
         l.rbSetTraceBuffer.argtypes = [C.c_void_p, C.c_size_t]
         l.rbReadKernelStatus.restype = C.c_int
         l.rbReadKernelStatus.argtypes = [C.POINTER(C.c_uint32), C.c_int]
+        l.rbSetWaitLimit.restype = None
+        l.rbSetWaitLimit.argtypes = [C.c_uint64]
+        l.rbInjectStall.restype = None
+        l.rbInjectStall.argtypes = [C.c_int]
         l.rbLaunchCount.restype = C.c_uint64
         l.rbGetLastError.restype = C.c_char_p
         _lib = l

@@ -12,6 +12,8 @@ namespace rb {
 namespace {
 
 thread_local int t_variant = 0;
+thread_local long long t_wait_cycles = kWaitCycles;   // rbSetWaitLimit
+thread_local int t_stall_launches = 0;                // rbInjectStall: GEMM launches left to stall
 
 // ---- auxiliary kernels ---------------------------------------------------------------------------
 // Copies `rows` rows of `row_bytes` bytes into rows of `pitch_bytes` bytes, zero-filling the pad.
@@ -113,7 +115,9 @@ GemmKernel pick_kernel(int kind, bool a_mn, bool b_mn) {
 // the operand layout allows them, the deepest ring that fits, and a K split when the output has too few
 // tiles to fill the GPU (the role of split-K in mlir/lib/Dialect/Rock/Transforms/GemmToGridwise.cpp:268-394,
 // here with f32 partial planes and a fixed-order reduction instead of atomics).
-constexpr int kAssumedSMs = 148;  // B200
+// Planning uses the SM count of the current device when one is present (148 on a B200) and 148 otherwise, so that
+// the configuration queries answer the same on a build machine without a GPU.
+int planned_sms() { return planning_sm_count(); }
 
 struct GemmConfig {
   int ctas, bn, stages, splits;
@@ -155,7 +159,7 @@ GemmConfig choose_config(const RbGemmProblem* p, int variant, bool epi_vec = fal
   const int bke = kRowBytes / es;
   const long long kblocks = (p->k + bke - 1) / bke;
   const long long tiles = (long long)p->g * ((p->m + kBM * c.ctas - 1) / (kBM * c.ctas)) * ((p->n + c.bn - 1) / c.bn);
-  const long long units = kAssumedSMs / c.ctas;
+  const long long units = planned_sms() / c.ctas;
   c.splits = (variant >> 16) & 0xFF;
   if (c.splits == 0) {
     c.splits = 1;
@@ -286,7 +290,7 @@ Workspace plan_workspace(const RbGemmProblem* p, const OperandPlan& oa, const Op
     off += align_up((size_t)cfg.splits * p->g * p->m * p->n * 4, 256);
   }
   if (cfg.sk_tiles > 0) {
-    const size_t units = kAssumedSMs / cfg.ctas;
+    const size_t units = planned_sms() / cfg.ctas;
     w.sk_off = off;
     off += align_up(units * (size_t)(kBM * cfg.ctas) * cfg.bn * 4, 256);
     w.sk_flags_off = off;
@@ -304,6 +308,10 @@ using namespace rb;
 
 extern "C" void rbSetGemmVariant(int variant) { t_variant = variant; }
 extern "C" int rbGetGemmVariant(void) { return t_variant; }
+extern "C" void rbSetWaitLimit(uint64_t sm_cycles) {
+  t_wait_cycles = sm_cycles == 0 ? kWaitCycles : (long long)std::min<uint64_t>(sm_cycles, (uint64_t)1 << 40);
+}
+extern "C" void rbInjectStall(int launches) { t_stall_launches = launches > 0 ? launches : 0; }
 
 size_t rb::gemm_workspace_bytes(const RbGemmProblem* p, int implicit_operand) {
   if (check_problem(p) != RB_SUCCESS) return 0;
@@ -348,7 +356,7 @@ extern "C" RbStatus rbGemmGetConfig(const RbGemmProblem* p, RbGemmConfigInfo* ou
   const int es = (int)dtype_bytes(p->ab_type);
   const long long tiles = (long long)p->g * ((p->m + kBM * c.ctas - 1) / (kBM * c.ctas)) * ((p->n + c.bn - 1) / c.bn);
   const long long items = tiles * c.splits;
-  const long long units = kAssumedSMs / c.ctas;
+  const long long units = planned_sms() / c.ctas;
   memset(out, 0, sizeof(*out));
   out->tile_m = kBM * c.ctas;
   out->tile_n = c.bn;
@@ -361,9 +369,19 @@ extern "C" RbStatus rbGemmGetConfig(const RbGemmProblem* p, RbGemmConfigInfo* ou
   out->block = kGemmThreads;
   out->dynamic_smem = (uint32_t)(c.ctas == 2 ? GemmSmemLayout<2>::total(c.stages, c.bn, false)
                                               : GemmSmemLayout<1>::total(c.stages, c.bn, false));
+  // with per-column epilogue vectors (bias / column scales) the ring may be one stage shorter and the staging single
+  {
+    const GemmConfig ce = choose_config(p, t_variant, true);
+    out->stages_epi_vec = ce.stages;
+    out->dynamic_smem_epi_vec = (uint32_t)(ce.ctas == 2 ? GemmSmemLayout<2>::total(ce.stages, ce.bn, true)
+                                                        : GemmSmemLayout<1>::total(ce.stages, ce.bn, true));
+  }
+  out->kpr = c.kpr;
   const int bn_code = c.bn == 64 ? 1 : c.bn == 128 ? 2 : 3;
+  const int kpr_code = c.kpr == 1 ? 1 : c.kpr == 2 ? 2 : 3;
   out->variant = (uint32_t)c.ctas | ((uint32_t)c.stages << 4) | (c.plain_stores ? 1u << 8 : 0u) |
-                 (c.sk_tiles > 0 ? 1u << 9 : 0u) | ((uint32_t)bn_code << 12) | ((uint32_t)c.splits << 16);
+                 (c.sk_tiles > 0 ? 1u << 9 : 0u) | ((uint32_t)bn_code << 12) | ((uint32_t)c.splits << 16) |
+                 ((uint32_t)kpr_code << 28);
   return RB_SUCCESS;
 }
 
@@ -615,7 +633,9 @@ RbStatus rb::gemm_run(const RbGemmProblem* p, const RbEpilogue* epi, const void*
   kp.status = dev->status_word;
   kp.stages = stages;
   kp.kpr = cfg.kpr;
-  kp.probe = (t_variant >> 24) & 7;
+  kp.probe = kProbeBuild ? (t_variant >> 24) & 7 : 0;
+  kp.wait_cycles = t_wait_cycles;
+  if (t_stall_launches > 0) { kp.stall = 1; --t_stall_launches; }
   if (conva) {
     kp.conva.enabled = conv_a ? 1 : 2; kp.conva.P = conva->P; kp.conva.Q = conva->Q; kp.conva.X = conva->X;
     kp.conva.cchunks = conva->C / bke;
@@ -629,7 +649,7 @@ RbStatus rb::gemm_run(const RbGemmProblem* p, const RbEpilogue* epi, const void*
   const long long num_items = num_tiles * splits;
   if (num_items > 0x7fffffffLL) return fail(RB_UNSUPPORTED, "too many tiles");
   // the stream-K split was planned for a B200's SM count; on anything else every tile is computed whole
-  const bool use_sk = cfg.sk_tiles > 0 && dev->sm_count == kAssumedSMs;
+  const bool use_sk = cfg.sk_tiles > 0 && dev->sm_count == planned_sms();
   kp.dp_tiles = use_sk ? cfg.dp_tiles : (int)num_tiles;
   kp.sk_tiles = use_sk ? cfg.sk_tiles : 0;
   if (use_sk) {
@@ -684,9 +704,8 @@ constexpr size_t kNoAllocScratchBytes = RB_NO_ALLOC_SCRATCH_BYTES;
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
 
 constexpr int kNoAllocMaxDevices = 16;
-void* g_noalloc_ptr[kNoAllocMaxDevices];
-cudaError_t g_noalloc_err[kNoAllocMaxDevices];
-std::once_flag g_noalloc_once[kNoAllocMaxDevices];
+std::mutex g_noalloc_mu;
+void* g_noalloc_ptr[kNoAllocMaxDevices];   // nullptr until a lookup on that device has succeeded
 }  // namespace
 
 extern "C" RbStatus rbGemmNoAlloc(const RbGemmProblem* p, const RbEpilogue* epi, const void* a, const void* b, void* c,
@@ -702,15 +721,21 @@ extern "C" RbStatus rbGemmNoAlloc(const RbGemmProblem* p, const RbEpilogue* epi,
   RB_CUDA_TRY(cudaGetDevice(&dev));
   if (dev < 0 || dev >= kNoAllocMaxDevices) return rb::fail(RB_CUDA_ERROR, "device index out of range");
   // In host code the array's name is only a handle for the runtime, not a device address: the address the kernels
-  // get is looked up once per device, with that device current.
-  std::call_once(g_noalloc_once[dev], [dev] {
-    void* ptr = nullptr;
-    g_noalloc_err[dev] = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
-    g_noalloc_ptr[dev] = g_noalloc_err[dev] == cudaSuccess ? ptr : nullptr;
-  });
-  if (g_noalloc_err[dev] != cudaSuccess || !g_noalloc_ptr[dev])
-    return rb::fail(RB_CUDA_ERROR, std::string("cudaGetSymbolAddress(scratch): ") + cudaGetErrorString(g_noalloc_err[dev]));
-  return rbGemm(p, epi, a, b, c, need ? g_noalloc_ptr[dev] : nullptr, need ? kNoAllocScratchBytes : 0, stream);
+  // get is looked up per device, with that device current. Only a successful lookup is remembered; a failed one
+  // (for instance a first call made while a stream capture was open) is reported and tried again by the next call.
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_noalloc_mu);
+    if (!g_noalloc_ptr[dev]) {
+      void* ptr = nullptr;
+      const cudaError_t e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+      if (e != cudaSuccess || !ptr)
+        return rb::fail(RB_CUDA_ERROR, std::string("cudaGetSymbolAddress(scratch): ") + cudaGetErrorString(e));
+      g_noalloc_ptr[dev] = ptr;
+    }
+    scratch = g_noalloc_ptr[dev];
+  }
+  return rbGemm(p, epi, a, b, c, need ? scratch : nullptr, need ? kNoAllocScratchBytes : 0, stream);
 }
 
 // ---- rbGemmGemm -------------------------------------------------------------------------------------------

@@ -34,6 +34,11 @@ constexpr int kRowBytes = 128;    // bytes of the contiguous dimension per share
 constexpr int kGemmThreads = 256;
 constexpr int kTmemCols = 512;
 constexpr int kGroupM = 8;        // M blocks per rasterisation group
+#ifdef RB_ENABLE_PROBE
+constexpr bool kProbeBuild = true;
+#else
+constexpr bool kProbeBuild = false;
+#endif
 
 template <int KIND>
 struct KindTraits;
@@ -99,8 +104,12 @@ struct GemmParams {
   unsigned int sk_token;       // unique per launch, so stale words of earlier launches never match
   ConvAParams conva;
   int a_fused, b_fused;       // MN-major operand loaded with one 4-D box per stage (extent a multiple of the chunk)
-  int probe;                  // instrumentation (results become meaningless): bit0 = no loads, bit1 = no epilogue work,
-                              // bit2 = epilogue without its global stores
+  int probe;                  // instrumentation, only in builds with -DRB_ENABLE_PROBE (results become meaningless):
+                              // bit0 = no loads, bit1 = no epilogue work, bit2 = epilogue without its global stores
+  int stall;                  // failure-detection test hook (rbInjectStall): the producer issues no loads and never
+                              // completes a stage, so every role's bounded wait runs out and the kernel returns with a
+                              // status code instead of a result
+  long long wait_cycles;      // budget of every bounded wait in SM cycles (rbSetWaitLimit; default kWaitCycles)
   int stages;                 // shared-memory ring depth (<= GemmSmemLayout::kMaxStages), a multiple of kpr
   int kpr;                    // K blocks per barrier round (1, 2 or 4): one full/empty barrier pair serves kpr ring slots
 };
@@ -222,6 +231,8 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
   constexpr int CHUNK_BYTES = BKE * kRowBytes; // one MN-major chunk: BKE k-rows of 128 B
   const int bn_cta = p.bn / CTAS;              // columns of B this CTA loads
   const int stage_bytes = L::stage_bytes(p.bn);
+  const int probe = kProbeBuild ? p.probe : 0;  // folds to 0 (and every probe branch away) in the shipped build
+  const long long wait_limit = p.wait_cycles;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -302,9 +313,11 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
         for (int kk0 = 0; kk0 < ktotal; kk0 += kpr) {
           const int nblk = min(kpr, ktotal - kk0);
           const long long tw = p.trace ? clock64() : 0;
-          if (!mbar_wait(&empty_bar[s], ph ^ 1u, p.status, kStatusTimeoutProducer + s)) { ok = false; break; }
+          if (!mbar_wait(&empty_bar[s], ph ^ 1u, p.status, kStatusTimeoutProducer + s, wait_limit)) { ok = false; break; }
           if (p.trace) w_empty += clock64() - tw;
-          if (p.probe & 1) {
+          if (p.stall) {
+            // injected stall: the stage is never filled
+          } else if (probe & 1) {
             if (CTAS == 1 || rank == 0) mbar_arrive(&full_bar[s]);
           } else if constexpr (CTAS == 1) {
             mbar_expect_tx(&full_bar[s], nblk * stage_bytes);
@@ -315,8 +328,8 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
             uint8_t* sa = smem + (s * kpr + j) * stage_bytes;
             uint8_t* sb = sa + L::kABytes;
             const int k0 = kb * BKE;
-            if (p.probe & 1) {
-              // loads switched off: the round's barrier was completed above
+            if ((probe & 1) || p.stall) {
+              // loads switched off: the round's barrier was completed above (probe) or is left incomplete (stall)
             } else if constexpr (CTAS == 1) {
               if (!A_MN && p.conva.enabled == 1) {
                 const int tap = kb / p.conva.cchunks, cc = kb - tap * p.conva.cchunks;
@@ -419,7 +432,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
         const uint32_t buf = t & 1u;
         const uint32_t bph = (t >> 1) & 1u;
         const long long tw0 = p.trace ? clock64() : 0;
-        if (!mbar_wait(&tempty_bar[buf], bph ^ 1u, p.status, kStatusTimeoutMma + 0x10 + buf)) { ok = false; break; }
+        if (!mbar_wait(&tempty_bar[buf], bph ^ 1u, p.status, kStatusTimeoutMma + 0x10 + buf, wait_limit)) { ok = false; break; }
         if (p.trace) w_tempty += clock64() - tw0;
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + buf * kMaxBN;
@@ -432,7 +445,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
           for (int kk = 0; kk < ktotal; ++kk) {
             if (!ready) {
               const long long tw = p.trace ? clock64() : 0;
-              if (!mbar_wait(&full_bar[s], ph, p.status, kStatusTimeoutMma + s)) { ok = false; break; }
+              if (!mbar_wait(&full_bar[s], ph, p.status, kStatusTimeoutMma + s, wait_limit)) { ok = false; break; }
               if (p.trace) w_full += clock64() - tw;
             }
             uint32_t ns = s + 1, nph = ph;
@@ -460,7 +473,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
             const int nblk = min(kpr, ktotal - kk0);
             if (!ready) {
               const long long tw = p.trace ? clock64() : 0;
-              if (!mbar_wait(&full_bar[s], ph, p.status, kStatusTimeoutMma + s)) { ok = false; break; }
+              if (!mbar_wait(&full_bar[s], ph, p.status, kStatusTimeoutMma + s, wait_limit)) { ok = false; break; }
               if (p.trace) w_full += clock64() - tw;
             }
             // no tcgen05 fence here: the operands arrive through the async proxy (TMA) and are ordered by the
@@ -530,7 +543,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
       const uint32_t buf = t & 1u;
       const uint32_t bph = (t >> 1) & 1u;
       const long long tw = p.trace ? clock64() : 0;
-      if (!mbar_wait(&tfull_bar[buf], bph, p.status, kStatusTimeoutEpilogue + buf)) break;
+      if (!mbar_wait(&tfull_bar[buf], bph, p.status, kStatusTimeoutEpilogue + buf, wait_limit)) break;
       const long long te = p.trace ? clock64() : 0;
       w_tfull += te - tw;
       tc_fence_after();
@@ -567,7 +580,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
           const volatile unsigned int* flag = p.sk_flags + u * 8 + (int)rank * 4 + q;
           const long long t0 = clock64();
           while (*flag != p.sk_token) {
-            if (clock64() - t0 > kWaitCycles) { atomicCAS(p.status, 0u, kStatusTimeoutAux + 1); got = false; break; }
+            if (clock64() - t0 > wait_limit) { atomicCAS(p.status, 0u, kStatusTimeoutAux + 1); got = false; break; }
           }
         }
         __threadfence();
@@ -577,10 +590,10 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
       // compact loop - 64 columns = one 128-byte staging row per step. The general loop below handles every other
       // case; keeping this one small matters because the general loop's code is far larger than the instruction
       // cache and ran at about 1400 cycles per 32 columns where this one needs about 150.
-      const bool fast16 = w.kind == 0 && p.c_tma && p.epi.flags == 0 && !p.acc_is_int && !p.probe &&
+      const bool fast16 = w.kind == 0 && p.c_tma && p.epi.flags == 0 && !p.acc_is_int && !probe &&
                           (p.c_type == RB_F16 || p.c_type == RB_BF16);
       // 4-byte C (f32 results, raw i32 results, the raw planes of a K split): 32 columns = one staging row per step
-      const bool fast32 = w.kind == 0 && p.c_tma && !p.probe &&
+      const bool fast32 = w.kind == 0 && p.c_tma && !probe &&
                           ((p.epi.flags == 0 && !p.acc_is_int && p.c_type == RB_F32) || raw_i32);
       if (fast16) {
         const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + buf * kMaxBN;
@@ -655,7 +668,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
       }
       // Fused elementwise work (or 1-byte / converted outputs) on whole tiles through TMA stores: the general loop's
       // body without its stream-K and plain-store branches.
-      const bool fast_epi = !fast16 && !fast32 && w.kind == 0 && p.c_tma && !p.probe && !raw_i32;
+      const bool fast_epi = !fast16 && !fast32 && w.kind == 0 && p.c_tma && !probe && !raw_i32;
       if (fast_epi) {
         const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + buf * kMaxBN;
 #pragma unroll 1
@@ -700,7 +713,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
       for (int c = 0; c < ngroups && !fast16 && !fast32 && !fast_epi; ++c) {
         const int n0 = nb * p.bn + c * 32;
         if (n0 >= p.N) break;  // warp-uniform
-        if (p.probe & 2) break;
+        if (probe & 2) break;
         uint32_t v[32];
         const long long tl0 = p.trace ? clock64() : 0;
         tmem_ld32(tmem_base + (uint32_t(q * 32) << 16) + buf * kMaxBN + c * 32, v);
@@ -777,13 +790,13 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
           if (last_group) {
             fence_proxy_async();
             __syncwarp();
-            if (lane == 0 && row0 < p.M && !(p.probe & 4)) {
+            if (lane == 0 && row0 < p.M && !(probe & 4)) {
               tma_store_3d(&maps.c, stg, n0 - sub * 32, (int)row0, gz);
               bulk_commit();
             }
             ++nstores;
           }
-        } else if (nw > 0 && row_ok && !(p.probe & 4)) {
+        } else if (nw > 0 && row_ok && !(probe & 4)) {
           if (p.vec_ok && n0 + 32 <= p.N) {
             uint4* d = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.c) + (c_row_off + n0) * es_c);
 #pragma unroll

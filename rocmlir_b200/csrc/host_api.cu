@@ -80,5 +80,11 @@ extern "C" RbStatus rbGemmHost(const RbGemmProblem* p, const RbEpilogue* epi_hos
   if (st != RB_SUCCESS) return st;
   RB_CUDA_TRY(cudaMemcpyAsync(c_host, dc, c_bytes, cudaMemcpyDeviceToHost, stream));
   RB_CUDA_TRY(cudaStreamSynchronize(stream));
+  // This entry point is synchronous, so it can report what the asynchronous ones leave to rbReadKernelStatus: a
+  // bounded device-side wait that ran out (the result in c_host is then not valid).
+  uint32_t word = 0;
+  st = read_status_word(&word, true);
+  if (st != RB_SUCCESS) return st;
+  if (word) return fail(RB_KERNEL_TIMEOUT, "a bounded device-side wait ran out (status code " + std::to_string(word) + ")");
   return RB_SUCCESS;
 }

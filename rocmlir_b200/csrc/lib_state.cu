@@ -80,6 +80,27 @@ const DeviceInfo* device_info() {
   return &g_devices[dev];
 }
 
+int planning_sm_count() {
+  static const int cached = [] {
+    int dev = 0, n = 0, major = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess &&
+        cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) == cudaSuccess && major == 10 &&
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
+      return n;
+    (void)cudaGetLastError();   // no device: not an error for a planning query
+    return 148;
+  }();
+  return cached;
+}
+
+RbStatus read_status_word(uint32_t* out, bool clear) {
+  const DeviceInfo* d = device_info();
+  if (!d) return RB_CUDA_ERROR;
+  RB_CUDA_TRY(cudaMemcpy(out, d->status_word, sizeof(uint32_t), cudaMemcpyDeviceToHost));
+  if (clear && *out) RB_CUDA_TRY(cudaMemset(d->status_word, 0, sizeof(uint32_t)));
+  return RB_SUCCESS;
+}
+
 bool encode_tiled(CUtensorMap* out, CUtensorMapDataType dt, int rank, const void* base, const uint64_t* dims,
                   const uint64_t* strides_bytes, const uint32_t* box, CUtensorMapSwizzle swizzle, std::string* err) {
   std::call_once(g_encode_once, [] {

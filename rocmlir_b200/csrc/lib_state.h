@@ -24,6 +24,12 @@ struct DeviceInfo {
 // Per-device lazy initialisation (current device). Returns nullptr and sets the error on failure.
 const DeviceInfo* device_info();
 
+// SM count used when planning a launch: that of the current device if it is an sm_100 GPU, else 148 (a B200).
+int planning_sm_count();
+// Reads the current device's status word after the caller has synchronised; nonzero = a bounded wait ran out.
+// With `clear` the word is reset.
+RbStatus read_status_word(uint32_t* out, bool clear);
+
 // Encodes a rank-`rank` tiled tensor map (128-byte swizzle unless `swizzle` says otherwise).
 // dims/box are innermost-first; strides_bytes has rank-1 entries (dimension 1 upward).
 bool encode_tiled(CUtensorMap* out, CUtensorMapDataType dt, int rank, const void* base, const uint64_t* dims,

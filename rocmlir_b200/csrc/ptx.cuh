@@ -18,7 +18,8 @@ enum : uint32_t {
   kStatusTimeoutAux = 0x400,
 };
 
-// Wait budget in SM clock cycles (about two seconds at 1.9 GHz).
+// Default wait budget in SM clock cycles (about two seconds at 1.9 GHz). Kernels that take a run-time limit
+// (GemmParams::wait_cycles, set with rbSetWaitLimit) pass it to mbar_wait instead.
 constexpr long long kWaitCycles = 4000000000LL;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -97,11 +98,11 @@ __device__ __forceinline__ bool mbar_test_wait_addr(uint32_t bar_addr, uint32_t 
 }
 // Bounded wait. On expiry writes `code` to *status (first writer wins) and returns false.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t* status,
-                                          uint32_t code) {
+                                          uint32_t code, long long limit = kWaitCycles) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (!mbar_try_wait(bar, parity)) {
-    if (clock64() - t0 > kWaitCycles) {
+    if (clock64() - t0 > limit) {
       atomicCAS(status, 0u, code);
       return false;
     }

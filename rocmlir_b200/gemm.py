@@ -119,16 +119,22 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bo
     else:
         assert out.is_contiguous() and out.dtype == out_dtype and out.numel() == p.g * p.m * p.n
     lib = L.lib()
-    if variant is not None:   # before the workspace query: a K split or a stream-K tail changes what is needed
-        lib.rbSetGemmVariant(int(variant))
-    ws_bytes = workspace_size(p)
-    if ws_bytes and (workspace is None or workspace.numel() * workspace.element_size() < ws_bytes):
-        workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=a.device)
-    e = epilogue.to_c() if epilogue is not None else None
-    stream = torch.cuda.current_stream(a.device).cuda_stream
-    st = lib.rbGemm(C.byref(p), C.byref(e) if e is not None else None, a.data_ptr(), b.data_ptr(), out.data_ptr(),
-                    workspace.data_ptr() if workspace is not None else None,
-                    workspace.numel() * workspace.element_size() if workspace is not None else 0, stream)
+    # The variant word is state of the calling thread inside the library: set it for this call only and put the
+    # caller's value back, so that a tuned call does not change what later calls (of any operator) run.
+    saved = lib.rbGetGemmVariant()
+    try:
+        if variant is not None:   # before the workspace query: a K split or a stream-K tail changes what is needed
+            lib.rbSetGemmVariant(int(variant))
+        ws_bytes = workspace_size(p)
+        if ws_bytes and (workspace is None or workspace.numel() * workspace.element_size() < ws_bytes):
+            workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=a.device)
+        e = epilogue.to_c() if epilogue is not None else None
+        stream = torch.cuda.current_stream(a.device).cuda_stream
+        st = lib.rbGemm(C.byref(p), C.byref(e) if e is not None else None, a.data_ptr(), b.data_ptr(), out.data_ptr(),
+                        workspace.data_ptr() if workspace is not None else None,
+                        workspace.numel() * workspace.element_size() if workspace is not None else 0, stream)
+    finally:
+        lib.rbSetGemmVariant(saved)
     L.check(st)
     if a.dim() == 2 and b.dim() == 2:
         out = out.view(shape[1], shape[2])
@@ -162,13 +168,17 @@ def gemm_host(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, trans_a: b
             e.bias = bs.data_ptr()
             e.bias_type = rb_dtype(bs.dtype)
     lib = L.lib()
-    if variant is not None:
-        lib.rbSetGemmVariant(int(variant))
-    dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
-    with torch.cuda.device(dev):
-        stream = torch.cuda.current_stream(dev).cuda_stream
-        st = lib.rbGemmHost(C.byref(p), C.byref(e) if e is not None else None, a.data_ptr(), b.data_ptr(),
-                            out.data_ptr(), stream)
+    saved = lib.rbGetGemmVariant()
+    try:
+        if variant is not None:
+            lib.rbSetGemmVariant(int(variant))
+        dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        with torch.cuda.device(dev):
+            stream = torch.cuda.current_stream(dev).cuda_stream
+            st = lib.rbGemmHost(C.byref(p), C.byref(e) if e is not None else None, a.data_ptr(), b.data_ptr(),
+                                out.data_ptr(), stream)
+    finally:
+        lib.rbSetGemmVariant(saved)
     L.check(st)
     return out
 

@@ -150,23 +150,27 @@ def tune(problem: Problem, run: Callable[[int], None], kind: int = FULL, iters: 
     records the winner in `table`."""
     import torch
     results = []
-    for perf in problem.space(kind):
-        if not problem.set_from_str(perf):
-            continue
-        v = problem.variant
-        for _ in range(2):
-            run(v)
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize()
-        e0.record()
-        for _ in range(iters):
-            run(v)
-        e1.record()
-        torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1) / iters
-        results.append((perf, ms))
-        if table is not None and problem.key is not None:
-            table.update(problem.key, perf, ms)
+    saved = L.lib().rbGetGemmVariant()   # `run` may set the thread's variant word: the caller's value is put back
+    try:
+        for perf in problem.space(kind):
+            if not problem.set_from_str(perf):
+                continue
+            v = problem.variant
+            for _ in range(2):
+                run(v)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(iters):
+                run(v)
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / iters
+            results.append((perf, ms))
+            if table is not None and problem.key is not None:
+                table.update(problem.key, perf, ms)
+    finally:
+        L.lib().rbSetGemmVariant(saved)
     results.sort(key=lambda r: r[1])
     return results
 

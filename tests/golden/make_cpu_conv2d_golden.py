@@ -3,7 +3,7 @@
 Source: mlir/test/rocmlir-driver/cpu_conv2d/*.mlir of the reference checkout. Each RUN line gives the
 rocmlir-gen flags of one case (`-prc -rand=none`: all inputs 1, only the CPU reference runs) and the
 CHECK-NEXT line under the same prefix gives the printed result tensor.
-Run where the reference checkout is available (its root is the first argument, or $ROCMLIR_REFERENCE):
+Run where the reference checkout is available (its root is the first argument, or $ROCMLIR_REFERENCE_DIR):
     python tests/golden/make_cpu_conv2d_golden.py <reference root>
 """
 import glob
@@ -12,7 +12,7 @@ import os
 import re
 import sys
 
-ROOT = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("ROCMLIR_REFERENCE", os.path.join(os.sep, "root", "reference"))
+ROOT = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("ROCMLIR_REFERENCE_DIR") or sys.exit("usage: pass the root of the reference checkout as the first argument (or set ROCMLIR_REFERENCE_DIR)")
 SRC = os.path.join(ROOT, "mlir", "test", "rocmlir-driver", "cpu_conv2d")
 OUT = os.path.join(os.path.dirname(os.path.abspath(__file__)), "cpu_conv2d.json")
 

@@ -52,7 +52,7 @@ def expand(path):
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("ROCMLIR_REFERENCE", os.path.join(os.sep, "root", "reference"))
+    root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("ROCMLIR_REFERENCE_DIR") or sys.exit("usage: pass the root of the reference checkout as the first argument (or set ROCMLIR_REFERENCE_DIR)")
     cases = []
     for f in FILES:
         cases += expand(os.path.join(root, "mlir", "test", "e2e", f))

@@ -1,6 +1,6 @@
 """Known answers the reference's fusion end-to-end tests print for all-ones inputs (`-rand none`), as a JSON fixture.
 
-Source: mlir/test/fusion/pr-e2e/**.mlir of the reference checkout (root = first argument or $ROCMLIR_REFERENCE).
+Source: mlir/test/fusion/pr-e2e/**.mlir of the reference checkout (root = first argument or $ROCMLIR_REFERENCE_DIR).
 Each listed file holds one function and one CHECK line with the printed result; the operation and its sizes are
 read from the function signature by the patterns below. Only files whose function is a plain dot / quant_dot
 (optionally followed by an add of a same-shape tensor or a transpose / reshape, which do not change the values)
@@ -12,7 +12,7 @@ import os
 import re
 import sys
 
-ROOT = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("ROCMLIR_REFERENCE", os.path.join(os.sep, "root", "reference"))
+ROOT = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("ROCMLIR_REFERENCE_DIR") or sys.exit("usage: pass the root of the reference checkout as the first argument (or set ROCMLIR_REFERENCE_DIR)")
 DIR = os.path.join(ROOT, "mlir", "test", "fusion", "pr-e2e")
 FILES = ["mixr-gemm/mixr-gemm-add.e2e.mlir", "mixr-gemm/mixr-gemm-bcast-add.e2e.mlir",
          "mixr-gemm/mixr-gemm-reshape-case1.e2e.mlir", "mixr-gemm/mixr-gemm-reshape-case1-quant.e2e.mlir",

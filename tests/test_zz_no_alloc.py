@@ -17,15 +17,16 @@ pytestmark = pytest.mark.gpu
 CASES = [(1, 64, 576, 8192, oracle.F16), (1, 1024, 512, 769, oracle.F16), (1, 200, 300, 256, oracle.F32)]
 
 
-def _run(entry, prob, a, b, out, ws=None):
+def _run(entry, prob, a, b, out, ws=None, epi=None):
     import torch
     from rocmlir_b200 import _lib as L
     lib = L.lib()
     stream = torch.cuda.current_stream().cuda_stream
+    e = C.byref(epi) if epi is not None else None
     if entry == "noalloc":
-        st = lib.rbGemmNoAlloc(C.byref(prob), None, a.data_ptr(), b.data_ptr(), out.data_ptr(), stream)
+        st = lib.rbGemmNoAlloc(C.byref(prob), e, a.data_ptr(), b.data_ptr(), out.data_ptr(), stream)
     else:
-        st = lib.rbGemm(C.byref(prob), None, a.data_ptr(), b.data_ptr(), out.data_ptr(), ws.data_ptr(), ws.numel(),
+        st = lib.rbGemm(C.byref(prob), e, a.data_ptr(), b.data_ptr(), out.data_ptr(), ws.data_ptr(), ws.numel(),
                         stream)
     L.check(st)
     torch.cuda.synchronize()
@@ -53,6 +54,34 @@ def test_no_alloc_matches_workspace_entry_point_twice(cuda_device, g, m, n, k, c
     ref = oracle.from_f32(oracle.gemm_f32(af, bf, g, m, n, k, threads=oracle.max_threads()), code)
     from helpers import from_device
     np.testing.assert_array_equal(from_device(want, code).reshape(ref.shape), ref)
+
+
+def test_no_alloc_carries_the_fused_epilogue(cuda_device):
+    """The same entry point with a fused tail, relu(C + bias[N]) rounded through f16, on a problem whose K split puts
+    the epilogue into the reduction pass over the built-in scratch: equal to rbGemm with a caller workspace, twice, and
+    equal to the oracle's op-by-op restatement on integer-valued data."""
+    import torch
+    from rocmlir_b200 import _lib as L
+    from rocmlir_b200.gemm import Epilogue
+    from helpers import from_device
+    g, m, n, k = 1, 64, 576, 8192
+    prob = L.RbGemmProblem(g, m, n, k, 0, 0, 0, L.F16, L.F16, 0)
+    need = L.lib().rbGemmWorkspaceSize(C.byref(prob))
+    assert 0 < need <= (16 << 20)
+    (af, araw), (bf, braw) = reference_random([(g, m, k), (g, k, n)], oracle.F16, seed=1)
+    bias = (np.arange(n, dtype=np.float32) % 9) - 4
+    a, b = to_device(araw, oracle.F16), to_device(braw, oracle.F16)
+    epi = Epilogue(bias=to_device(oracle.from_f32(bias, oracle.F16), oracle.F16), relu=True, mid_type=oracle.F16).to_c()
+    ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+    want = torch.empty((g, m, n), dtype=torch.float16, device="cuda")
+    _run("workspace", prob, a, b, want, ws, epi)
+    for call in range(2):
+        got = torch.full((g, m, n), 7.0, dtype=torch.float16, device="cuda")
+        _run("noalloc", prob, a, b, got, epi=epi)
+        assert torch.equal(got, want), f"call {call}: rbGemmNoAlloc with an epilogue differs from rbGemm"
+    acc = oracle.gemm_f32(af, bf, g, m, n, k, threads=oracle.max_threads())
+    ref = oracle.from_f32(oracle.epilogue(acc, n, bias=bias, relu=True, mid_type=oracle.F16), oracle.F16)
+    np.testing.assert_array_equal(from_device(want, oracle.F16).reshape(ref.shape), ref)
 
 
 def test_no_alloc_rejects_oversized_scratch_need(cuda_device):
