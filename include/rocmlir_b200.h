@@ -62,20 +62,34 @@ typedef enum RbStatus {
  *
  * Order of evaluation, each step an individually rounded f32 (or `mid_type`) operation:
  *   x = acc                       (f32, or i32 -> f32 round-to-nearest-even when any float step is on)
+ *   x = x - in_zero               if RB_EPI_ZP_IN      (dequantizelinear zero point, cast to f32 by the caller:
+ *                                                       (cast(x) - cast(zp)) * scale, MIGraphXToTosa.cpp:879-902)
  *   x = round_to(mid_type, x)     if RB_EPI_ROUND_MID  (the GEMM's declared result type)
  *   x = x * alpha                 if RB_EPI_ALPHA      (per-tensor scale product, fp8)
  *   x = x * col_scale[n]          if RB_EPI_COL_SCALE  (per-column dequantisation scale, f32)
- *   x = x + bias[n]               if RB_EPI_BIAS       (then round_to(mid_type) if ROUND_MID)
+ *   x = x + bias[n]               if RB_EPI_BIAS       (then round_to(mid_type) if ROUND_MID); with RB_EPI_BIAS_ROW the
+ *                                                       vector is indexed by the row m (a bias broadcast along N), with
+ *                                                       RB_EPI_BIAS_SCALAR it is the single element bias[0]
+ *   x = x + residual[g][m][n]     if RB_EPI_RESIDUAL   (a tensor of C's shape and layout: the same-shape add of
+ *                                                       mixr-gemm-add; then round_to(mid_type) if ROUND_MID)
  *   x = max(x, 0)                 if RB_EPI_RELU
+ *   x = min(max(x, lo), hi)       if RB_EPI_CLIP       (migraphx.clip, MIGraphXToTosa.cpp:1089-1101)
  *   x = x * out_recip             if RB_EPI_REQUANT    (out_recip = 1/scale computed by the caller in f32)
- *   store: convert x to the C type (floats: RNE, fp8 saturating; integers: RNE then saturate). */
+ *   store: convert x to the C type (floats: RNE, fp8 saturating; integers: RNE then saturate; i8 with
+ *          RB_EPI_ZP_OUT: cast to i32, + out_zero, clamp to [-128, 127], MIGraphXToTosa.cpp:908-982). */
 enum {
   RB_EPI_ALPHA = 1,
   RB_EPI_COL_SCALE = 2,
   RB_EPI_BIAS = 4,
   RB_EPI_RELU = 8,
   RB_EPI_REQUANT = 16,
-  RB_EPI_ROUND_MID = 32
+  RB_EPI_ROUND_MID = 32,
+  RB_EPI_CLIP = 64,
+  RB_EPI_RESIDUAL = 128,
+  RB_EPI_BIAS_ROW = 256,
+  RB_EPI_BIAS_SCALAR = 512,
+  RB_EPI_ZP_IN = 1024,
+  RB_EPI_ZP_OUT = 2048
 };
 
 typedef struct RbEpilogue {
@@ -85,7 +99,12 @@ typedef struct RbEpilogue {
   int32_t mid_type;        /* RbDType used by RB_EPI_ROUND_MID */
   int32_t bias_type;       /* RbDType of bias[]: RB_F32, RB_F16 or RB_BF16 */
   const float *col_scale;  /* device, [n] */
-  const void *bias;        /* device, [n] */
+  const void *bias;        /* device, [n] ([m] with RB_EPI_BIAS_ROW, one element with RB_EPI_BIAS_SCALAR) */
+  float clip_lo, clip_hi;  /* RB_EPI_CLIP */
+  float in_zero;           /* RB_EPI_ZP_IN */
+  int32_t out_zero;        /* RB_EPI_ZP_OUT */
+  const void *residual;    /* device, C's shape and layout (also under trans_c) */
+  int32_t res_type;        /* RbDType of residual[]: RB_F32, RB_F16 or RB_BF16 */
 } RbEpilogue;
 
 /* rock.gemm (mlir/include/mlir/Dialect/Rock/IR/RockOps.td:136-181):
@@ -100,6 +119,9 @@ typedef struct RbGemmProblem {
   int32_t ab_type; /* RbDType of A and B */
   int32_t c_type;  /* RbDType of C */
   int32_t f32_mode; /* for ab_type RB_F32: 0 = 3xTF32 split (fp32-class accuracy), 1 = single TF32 pass */
+  int32_t store_method; /* 0 = set: C = A.B; 1 = add: C = C + A.B on a C the caller has filled (rock.gemm's
+                           store_method = atomic_add, rocmlir-gen --store-method, rocmlir-gen.cpp:325-331). The product is
+                           rounded to C's type and added in it; f32 / f16 / bf16 results. Deterministic: no atomics. */
 } RbGemmProblem;
 
 /* Bytes of caller-provided device workspace rbGemm needs for this problem (0 for most). */
@@ -178,6 +200,17 @@ RB_EXPORT RbStatus rbConvGetGemmProblem(const RbConvProblem *p, RbGemmProblem *o
 
 RB_EXPORT RbStatus rbConv(const RbConvProblem *p, void *filter, void *input, void *output, void *workspace,
                           size_t workspace_bytes, void *stream);
+
+/* Forward convolution with the fused elementwise tail MIGraphX attaches to it (convolution + broadcast add +
+ * relu / clip: mlir/test/CAPI/mixr_full.c:88-159, mlir/test/fusion/pr-e2e/mixr-conv-bias-clipped-relu.mlir:5-13;
+ * quant_convolution -> dequantizelinear -> ... -> quantizelinear: mlir/test/fusion/pr-e2e/tosa-to-rock-quantization.e2e.mlir).
+ * The epilogue is RbEpilogue as for rbGemm, with the output channel k in the place of the column n (bias[k],
+ * col_scale[k]); a residual operand has the output tensor's shape and needs the "nhwgk" output layout. `out_type` is
+ * the element type of the output tensor after the epilogue (an RbDType, e.g. RB_I8 for a requantised i8 convolution),
+ * -1 for the type rbConv would write. Forward direction only (the reference fuses nothing into the backward ops). */
+RB_EXPORT size_t rbConvEpiWorkspaceSize(const RbConvProblem *p, int32_t out_type);
+RB_EXPORT RbStatus rbConvEpi(const RbConvProblem *p, const RbEpilogue *epi /* may be NULL */, int32_t out_type, void *filter,
+                             void *input, void *output, void *workspace, size_t workspace_bytes, void *stream);
 
 /* The same three operations with a third image dimension (depth), as rocmlir-gen builds them for layouts with
  * three image letters (mlir/tools/rocmlir-gen/rocmlir-gen.cpp:3545-3581; letters and their digit aliases in

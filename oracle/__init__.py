@@ -384,29 +384,46 @@ def gemm_gemm(a, b1, b2, mid_type: int, threads: int = 1) -> np.ndarray:
 
 # ---- epilogue -------------------------------------------------------------------------------------------------------
 EPI_ALPHA, EPI_COL_SCALE, EPI_BIAS, EPI_RELU, EPI_REQUANT, EPI_ROUND_MID = 1, 2, 4, 8, 16, 32
+EPI_CLIP, EPI_RESIDUAL, EPI_BIAS_ROW, EPI_BIAS_SCALAR, EPI_ZP_IN = 64, 128, 256, 512, 1024
 
 
 def epilogue(acc: np.ndarray, N: int, *, alpha=None, col_scale=None, bias=None, relu=False, requant_scale=None,
-             mid_type=None) -> np.ndarray:
-    """acc: f32 or i64 accumulators, last dimension N. Returns f32 (convert with from_f32(..., sat_int=True))."""
+             mid_type=None, bias_mode: str = "col", residual=None, clip=None, in_zero=None) -> np.ndarray:
+    """acc: f32 or i64 accumulators, last dimension N; `bias_mode` "col" (bias[n]), "row" (bias[row], rows counted
+    over all leading dimensions) or "scalar"; `residual` an f32 array of acc's shape; `clip` = (lo, hi); `in_zero` the
+    dequantisation zero point. Returns f32 (convert with from_f32(..., sat_int=True) or quantize_i8)."""
     flags = 0
     if alpha is not None: flags |= EPI_ALPHA
     if col_scale is not None: flags |= EPI_COL_SCALE
-    if bias is not None: flags |= EPI_BIAS
+    if bias is not None: flags |= EPI_BIAS | {"col": 0, "row": EPI_BIAS_ROW, "scalar": EPI_BIAS_SCALAR}[bias_mode]
     if relu: flags |= EPI_RELU
     if requant_scale is not None: flags |= EPI_REQUANT
     if mid_type is not None: flags |= EPI_ROUND_MID
+    if residual is not None: flags |= EPI_RESIDUAL
+    if clip is not None: flags |= EPI_CLIP
+    if in_zero is not None: flags |= EPI_ZP_IN
     rows = acc.size // N
     out = np.empty(acc.shape, np.float32)
     is_int = acc.dtype == np.int64
     accc = np.ascontiguousarray(acc)
     cs = None if col_scale is None else np.ascontiguousarray(col_scale, np.float32)
-    bs = None if bias is None else np.ascontiguousarray(bias, np.float32)
+    bs = None if bias is None else np.ascontiguousarray(bias, np.float32).ravel()
+    rs = None if residual is None else np.ascontiguousarray(residual, np.float32)
+    assert rs is None or rs.size == acc.size
     recip = np.float32(1.0) / np.float32(requant_scale) if requant_scale is not None else np.float32(0)
+    lo, hi = clip if clip is not None else (0.0, 0.0)
     lib().orc_epilogue(None if is_int else _p(accc), _p(accc) if is_int else None, _p(out), C.c_int64(rows),
                        C.c_int64(N), C.c_uint32(flags), C.c_float(np.float32(alpha or 0.0)), _p(cs), _p(bs),
-                       C.c_float(recip), C.c_int(mid_type if mid_type is not None else F32))
+                       C.c_float(recip), C.c_int(mid_type if mid_type is not None else F32), C.c_float(np.float32(lo)),
+                       C.c_float(np.float32(hi)), C.c_float(np.float32(in_zero or 0.0)), _p(rs))
     return out
+
+
+def quantize_i8(x: np.ndarray, zero_point: int = 0) -> np.ndarray:
+    """The store of quantizelinear (MIGraphXToTosa.cpp:908-982): cast to i32 with round-half-even and saturation, add
+    the zero point, clamp to [-128, 127]."""
+    q = np.clip(np.rint(np.asarray(x, np.float64)), -2.0 ** 31, 2.0 ** 31 - 1).astype(np.int64) + int(zero_point)
+    return np.clip(q, -128, 127).astype(np.int8)
 
 
 # ---- verification ------------------------------------------------------------------------------------------------------

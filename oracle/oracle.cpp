@@ -666,15 +666,24 @@ ORC_API void orc_gemm_gemm(const float* a, const float* b1, const float* b2, flo
 // ------------------------------------------------------------------------------------------------
 ORC_API void orc_epilogue(const float* acc_f32, const int64_t* acc_i64, float* out, int64_t rows, int64_t N,
                           uint32_t flags, float alpha, const float* col_scale, const float* bias, float out_recip,
-                          int mid_type) {
+                          int mid_type, float clip_lo, float clip_hi, float in_zero, const float* residual) {
+  // flags: 1 alpha, 2 col_scale, 4 bias (256: indexed by the row, 512: a scalar), 8 relu, 16 requant, 32 round to
+  // mid_type, 64 clip (tosa.maximum then tosa.minimum, MIGraphXToTosa.cpp:1089-1101), 128 same-shape add,
+  // 1024 dequantisation zero point: (cast(x) - cast(zp)) * scale (MIGraphXToTosa.cpp:879-902)
   for (int64_t r = 0; r < rows; ++r)
     for (int64_t n = 0; n < N; ++n) {
       float x = acc_i64 ? (float)(int32_t)acc_i64[r * N + n] : acc_f32[r * N + n];
+      if (flags & 1024) x = x - in_zero;
       if (flags & 32) x = round_to(x, mid_type);
       if (flags & 1) x = x * alpha;
       if (flags & 2) x = x * col_scale[n];
-      if (flags & 4) { x = x + bias[n]; if (flags & 32) x = round_to(x, mid_type); }
+      if (flags & 4) {
+        x = x + bias[(flags & 512) ? 0 : (flags & 256) ? r : n];
+        if (flags & 32) x = round_to(x, mid_type);
+      }
+      if (flags & 128) { x = x + residual[r * N + n]; if (flags & 32) x = round_to(x, mid_type); }
       if (flags & 8) x = x > 0.0f ? x : 0.0f;
+      if (flags & 64) { x = x > clip_lo ? x : clip_lo; x = x < clip_hi ? x : clip_hi; }
       if (flags & 16) x = x * out_recip;
       out[r * N + n] = x;
     }

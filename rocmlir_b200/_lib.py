@@ -23,17 +23,20 @@ STATUS_NAMES = ["RB_SUCCESS", "RB_INVALID_PARAM", "RB_UNSUPPORTED", "RB_WORKSPAC
                 "RB_KERNEL_TIMEOUT"]
 
 EPI_ALPHA, EPI_COL_SCALE, EPI_BIAS, EPI_RELU, EPI_REQUANT, EPI_ROUND_MID = 1, 2, 4, 8, 16, 32
+EPI_CLIP, EPI_RESIDUAL, EPI_BIAS_ROW, EPI_BIAS_SCALAR, EPI_ZP_IN, EPI_ZP_OUT = 64, 128, 256, 512, 1024, 2048
 
 
 class RbEpilogue(C.Structure):
     _fields_ = [("flags", C.c_uint32), ("alpha", C.c_float), ("out_recip", C.c_float), ("mid_type", C.c_int32),
-                ("bias_type", C.c_int32), ("col_scale", C.c_void_p), ("bias", C.c_void_p)]
+                ("bias_type", C.c_int32), ("col_scale", C.c_void_p), ("bias", C.c_void_p), ("clip_lo", C.c_float),
+                ("clip_hi", C.c_float), ("in_zero", C.c_float), ("out_zero", C.c_int32), ("residual", C.c_void_p),
+                ("res_type", C.c_int32)]
 
 
 class RbGemmProblem(C.Structure):
     _fields_ = [("g", C.c_int32), ("m", C.c_int32), ("n", C.c_int32), ("k", C.c_int32), ("trans_a", C.c_int32),
                 ("trans_b", C.c_int32), ("trans_c", C.c_int32), ("ab_type", C.c_int32), ("c_type", C.c_int32),
-                ("f32_mode", C.c_int32)]
+                ("f32_mode", C.c_int32), ("store_method", C.c_int32)]
 
 
 class RbConvProblem(C.Structure):
@@ -104,6 +107,11 @@ def lib() -> C.CDLL:
         l.rbConv.restype = C.c_int
         l.rbConv.argtypes = [C.POINTER(RbConvProblem), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t,
                              C.c_void_p]
+        l.rbConvEpiWorkspaceSize.restype = C.c_size_t
+        l.rbConvEpiWorkspaceSize.argtypes = [C.POINTER(RbConvProblem), C.c_int32]
+        l.rbConvEpi.restype = C.c_int
+        l.rbConvEpi.argtypes = [C.POINTER(RbConvProblem), C.POINTER(RbEpilogue), C.c_int32, C.c_void_p, C.c_void_p,
+                                C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
         l.rbConv3dWorkspaceSize.restype = C.c_size_t
         l.rbConv3dWorkspaceSize.argtypes = [C.POINTER(RbConv3dProblem)]
         l.rbConv3d.restype = C.c_int

@@ -126,6 +126,31 @@ def conv(cfg: ConvConfig, direction: int, filter: torch.Tensor, input: torch.Ten
     return {FWD: output, BWD_DATA: input, BWD_WEIGHT: filter}[direction]
 
 
+def conv_fused(cfg: ConvConfig, filter: torch.Tensor, input: torch.Tensor, output: torch.Tensor, epilogue,
+               *, workspace: Optional[torch.Tensor] = None, f32_mode: int = 0) -> torch.Tensor:
+    """Forward convolution with a fused elementwise tail (rbConvEpi): `epilogue` is a rocmlir_b200.gemm.Epilogue whose
+    vectors are indexed by the output channel; the element type of `output` is the result type after the epilogue
+    (e.g. int8 for a requantised i8 convolution)."""
+    for t_, name in ((filter, "fil"), (input, "in"), (output, "out")):
+        if not t_.is_cuda or not t_.is_contiguous():
+            raise L.RbError(L.INVALID_PARAM, "tensors must be contiguous CUDA buffers (the library has no CPU path)")
+        if t_.numel() != cfg.numel(name):
+            raise L.RbError(L.INVALID_PARAM, f"{name} has {t_.numel()} elements, expected {cfg.numel(name)}")
+    p = cfg.to_c(input.dtype, FWD, f32_mode)
+    out_type = rb_dtype(output.dtype)
+    lib = L.lib()
+    ws_bytes = int(lib.rbConvEpiWorkspaceSize(C.byref(p), out_type))
+    if ws_bytes and (workspace is None or workspace.numel() * workspace.element_size() < ws_bytes):
+        workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=input.device)
+    e = epilogue.to_c() if epilogue is not None else None
+    stream = torch.cuda.current_stream(input.device).cuda_stream
+    L.check(lib.rbConvEpi(C.byref(p), C.byref(e) if e is not None else None, out_type, filter.data_ptr(),
+                          input.data_ptr(), output.data_ptr(),
+                          workspace.data_ptr() if workspace is not None else None,
+                          workspace.numel() * workspace.element_size() if workspace is not None else 0, stream))
+    return output
+
+
 # ---- three image dimensions ----------------------------------------------------------------------------------------
 def _letters3(layout: str, kind: str) -> str:
     """Digit aliases 0 1 2 -> h w d (y x z for the filter), as ConvGenerator.cpp:622-627 translates them."""

@@ -428,7 +428,9 @@ RbStatus make_plan(const RbConvProblem* p, ConvPlan* pl, int result_type = -1) {
   if (!layout_strides(p->out_layout, "ngkhw", osz, pl->os, nullptr)) return fail(RB_INVALID_PARAM, "out_layout must be a permutation of ngkhw");
 
   const size_t es = dtype_bytes(t);
-  const int out_t = (t == RB_I8) ? RB_I32 : f8 ? RB_F32 : t;  // rocmlir-gen: -t i8 => i32 output, 8-bit floats => f32
+  // rocmlir-gen: -t i8 => i32 output, 8-bit floats => f32; a fused epilogue of the forward direction may declare
+  // another result type (quant_convolution -> dequantize -> quantize ends in i8)
+  const int out_t = (p->direction == 0 && result_type >= 0) ? result_type : (t == RB_I8) ? RB_I32 : f8 ? RB_F32 : t;
   const size_t es_o = dtype_bytes(out_t);
   const long long G = p->g;
   const long long pix_o = (long long)p->n * ho * wo, pix_i = (long long)p->n * p->h * p->w;
@@ -646,11 +648,26 @@ extern "C" RbStatus rbConv(const RbConvProblem* p, void* filter, void* input, vo
   return rb::conv_run(p, -1, filter, input, output, workspace, workspace_bytes, stream_v);
 }
 
+extern "C" size_t rbConvEpiWorkspaceSize(const RbConvProblem* p, int32_t out_type) {
+  return rb::conv_workspace_bytes(p, out_type);
+}
+
+extern "C" RbStatus rbConvEpi(const RbConvProblem* p, const RbEpilogue* epi, int32_t out_type, void* filter, void* input,
+                              void* output, void* workspace, size_t workspace_bytes, void* stream_v) {
+  if (p && p->direction != 0) return fail(RB_UNSUPPORTED, "a fused epilogue exists for the forward convolution only");
+  if (out_type >= 0 && !dtype_bytes(out_type)) return fail(RB_INVALID_PARAM, "unknown out_type");
+  return rb::conv_run(p, out_type, filter, input, output, workspace, workspace_bytes, stream_v, epi);
+}
+
 RbStatus rb::conv_run(const RbConvProblem* p, int result_type, void* filter, void* input, void* output, void* workspace,
-                      size_t workspace_bytes, void* stream_v) {
+                      size_t workspace_bytes, void* stream_v, const RbEpilogue* epi) {
   ConvPlan pl;
   RbStatus st = make_plan(p, &pl, result_type);
   if (st != RB_SUCCESS) return st;
+  if (epi && p->direction != 0) return fail(RB_UNSUPPORTED, "a fused epilogue exists for the forward convolution only");
+  if (epi && (epi->flags & RB_EPI_RESIDUAL) && !pl.c_direct)
+    return fail(RB_UNSUPPORTED, "a residual operand needs the [pixels][channels] output layout (nhwgk)");
+  if (epi && (epi->flags & RB_EPI_BIAS_ROW)) return fail(RB_UNSUPPORTED, "the bias of a convolution is per output channel or scalar");
   if (!filter || !input || !output) return fail(RB_INVALID_PARAM, "filter, input and output must be device pointers");
   if (pl.total > 0 && (!workspace || workspace_bytes < pl.total))
     return fail(RB_WORKSPACE_TOO_SMALL, "workspace of " + std::to_string(pl.total) + " bytes required");
@@ -876,9 +893,9 @@ RbStatus rb::conv_run(const RbConvProblem* p, int result_type, void* filter, voi
       cv.pad_h_hi = p->h - uh - cv.pad_h + (p->y - 1) * p->dil_h;
       cv.pad_w_hi = p->w - uw - cv.pad_w + (p->x - 1) * p->dil_w;
     }
-    st = gemm_run(&pl.gemm, nullptr, nullptr, B, C, pl.gemm_ws ? ws + pl.gemm_off : nullptr, pl.gemm_ws, stream_v, &cv);
+    st = gemm_run(&pl.gemm, epi, nullptr, B, C, pl.gemm_ws ? ws + pl.gemm_off : nullptr, pl.gemm_ws, stream_v, &cv);
   } else {
-    st = rbGemm(&pl.gemm, nullptr, A, B, C, pl.gemm_ws ? ws + pl.gemm_off : nullptr, pl.gemm_ws, stream_v);
+    st = rbGemm(&pl.gemm, epi, A, B, C, pl.gemm_ws ? ws + pl.gemm_off : nullptr, pl.gemm_ws, stream_v);
   }
   if (st != RB_SUCCESS) return st;
   if (!pl.c_direct) {

@@ -217,14 +217,14 @@ __global__ void splitk_reduce_kernel(const void* __restrict__ partial, int split
         reinterpret_cast<int*>(c)[o] = acc;
       } else {
         float x = __int2float_rn(acc);
-        if (epi.flags) x = epi_apply(x, epi, n);
-        store_elem(c, o, x, c_type);
+        if (epi.flags) x = epi_apply(x, epi, n, m, o);
+        store_elem(c, o, x, c_type, epi.out_zero);
       }
     } else {
       float acc = 0.0f;
       for (int s = 0; s < splits; ++s) acc = __fadd_rn(acc, reinterpret_cast<const float*>(partial)[s * plane + i]);
-      if (epi.flags) acc = epi_apply(acc, epi, n);
-      store_elem(c, o, acc, c_type);
+      if (epi.flags) acc = epi_apply(acc, epi, n, m, o);
+      store_elem(c, o, acc, c_type, epi.out_zero);
     }
   }
 }
@@ -410,15 +410,28 @@ RbStatus rb::gemm_run(const RbGemmProblem* p, const RbEpilogue* epi, const void*
   const int abt = p->ab_type;
   const size_t es = dtype_bytes(abt);
   const bool is_int = abt == RB_I8;
-  const uint32_t flags = epi ? epi->flags : 0u;
+  const uint32_t flags = (epi ? epi->flags : 0u) | (p->store_method == 1 ? (uint32_t)RB_EPI_RESIDUAL : 0u);
   if (is_int && flags == 0 && p->c_type != RB_I32)
     return fail(RB_UNSUPPORTED, "i8 x i8 without an epilogue produces i32 (rocmlir-gen: -t i8 implies an i32 result)");
   if (!is_int && p->c_type == RB_I32) return fail(RB_UNSUPPORTED, "float inputs cannot produce an i32 result");
+  if (p->store_method != 0 && p->store_method != 1) return fail(RB_INVALID_PARAM, "store_method must be 0 (set) or 1 (add)");
+  if (p->store_method == 1) {
+    // C += A.B (rock.gemm with store_method = atomic_add, RockOps.td:136-181): the fused residual step reading C itself
+    if (!(p->c_type == RB_F32 || p->c_type == RB_F16 || p->c_type == RB_BF16))
+      return fail(RB_UNSUPPORTED, "store_method add exists for f32, f16 and bf16 results");
+    if (epi && (epi->flags & RB_EPI_RESIDUAL)) return fail(RB_UNSUPPORTED, "store_method add cannot be combined with a residual operand");
+  }
   if (epi) {
     if ((flags & RB_EPI_COL_SCALE) && !epi->col_scale) return fail(RB_INVALID_PARAM, "col_scale is NULL");
     if ((flags & RB_EPI_BIAS) && !epi->bias) return fail(RB_INVALID_PARAM, "bias is NULL");
     if ((flags & RB_EPI_BIAS) && !(epi->bias_type == RB_F32 || epi->bias_type == RB_F16 || epi->bias_type == RB_BF16))
       return fail(RB_INVALID_PARAM, "bias_type must be f32, f16 or bf16");
+    if ((flags & RB_EPI_BIAS_ROW) && (flags & RB_EPI_BIAS_SCALAR)) return fail(RB_INVALID_PARAM, "bias is per row or scalar, not both");
+    if ((epi->flags & RB_EPI_RESIDUAL) && !epi->residual) return fail(RB_INVALID_PARAM, "residual is NULL");
+    if ((epi->flags & RB_EPI_RESIDUAL) && !(epi->res_type == RB_F32 || epi->res_type == RB_F16 || epi->res_type == RB_BF16))
+      return fail(RB_INVALID_PARAM, "res_type must be f32, f16 or bf16");
+    if ((flags & RB_EPI_CLIP) && !(epi->clip_lo <= epi->clip_hi)) return fail(RB_INVALID_PARAM, "clip needs lo <= hi");
+    if ((flags & RB_EPI_ZP_OUT) && p->c_type != RB_I8) return fail(RB_INVALID_PARAM, "an output zero point needs an i8 result");
   }
 
   int kind;
@@ -447,7 +460,7 @@ RbStatus rb::gemm_run(const RbGemmProblem* p, const RbEpilogue* epi, const void*
     ob.pitch = ob.cols;
   }
   const bool a_mn = oa.mn_major, b_mn = ob.mn_major;
-  const bool epi_vec = (flags & (RB_EPI_COL_SCALE | RB_EPI_BIAS)) != 0;
+  const bool epi_vec = epi_needs_col_vectors(flags);
   GemmConfig cfg = choose_config(p, t_variant, epi_vec);
   Workspace ws = plan_workspace(p, oa, ob, cfg);
   if (cfg.sk_tiles > 0 && (!workspace || workspace_bytes < ws.total)) {
@@ -595,6 +608,15 @@ RbStatus rb::gemm_run(const RbGemmProblem* p, const RbEpilogue* epi, const void*
     ep.flags = epi->flags; ep.alpha = epi->alpha; ep.out_recip = epi->out_recip;
     ep.mid_type = epi->mid_type; ep.bias_type = epi->bias_type;
     ep.col_scale = epi->col_scale; ep.bias = epi->bias;
+    ep.clip_lo = epi->clip_lo; ep.clip_hi = epi->clip_hi;
+    ep.in_zero = epi->in_zero; ep.out_zero = (epi->flags & RB_EPI_ZP_OUT) ? epi->out_zero : 0;
+    ep.residual = epi->residual; ep.res_type = epi->res_type;
+  }
+  if (p->store_method == 1) {
+    // the kernel's result is rounded to C's type and added to what C holds, like an atomic add of the stored value
+    ep.flags |= RB_EPI_RESIDUAL;
+    ep.residual = c; ep.res_type = p->c_type;
+    if (!(ep.flags & RB_EPI_ROUND_MID)) { ep.flags |= RB_EPI_ROUND_MID; ep.mid_type = p->c_type; }
   }
   const size_t es_c = dtype_bytes(p->c_type);
   void* partial = splits > 1 ? static_cast<void*>(wsb + ws.partial_off) : nullptr;

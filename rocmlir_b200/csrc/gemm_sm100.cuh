@@ -240,7 +240,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
   const int kpr = p.kpr;               // K blocks per barrier round
   const int rounds = stages / kpr;     // barrier pairs in use
   uint8_t* staging = smem + stages * stage_bytes;  // 1024-byte aligned (stage sizes are multiples of 1024)
-  const bool epi_vec = (p.epi.flags & (RB_EPI_COL_SCALE | RB_EPI_BIAS)) != 0;
+  const bool epi_vec = epi_needs_col_vectors(p.epi.flags);
   float* epi_vecs = reinterpret_cast<float*>(staging + L::staging_bytes(epi_vec));   // present only when epi_vec
   uint64_t* bars = reinterpret_cast<uint64_t*>(staging + L::staging_bytes(epi_vec) + (epi_vec ? L::kEpiVecBytes : 0));
   uint64_t* full_bar = bars;                       // [stages]
@@ -560,12 +560,25 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
         for (int j = lane; j < p.bn; j += 32) {
           const int n = min(nb * p.bn + j, p.N - 1);
           if (p.epi.flags & RB_EPI_COL_SCALE) vec_scale[j] = __ldg(p.epi.col_scale + n);
-          if (p.epi.flags & RB_EPI_BIAS) vec_bias[j] = load_bias(p.epi.bias, p.epi.bias_type, n);
+          if (epi_col_bias(p.epi.flags)) vec_bias[j] = load_bias(p.epi.bias, p.epi.bias_type, n);
         }
         __syncwarp();
       }
       const long long c_row_off =
           (long long)w.split * p.split_stride + (long long)g * p.c_stride_g + row * p.c_stride_m;
+      // what this thread's row contributes to the fused elementwise steps (row / scalar bias, residual address)
+      EpiRow erow;
+      if ((p.epi.flags & RB_EPI_BIAS) && (p.epi.flags & (RB_EPI_BIAS_ROW | RB_EPI_BIAS_SCALAR)))
+        erow.row_bias = load_bias(p.epi.bias, p.epi.bias_type,
+                                  (p.epi.flags & RB_EPI_BIAS_SCALAR) ? 0 : min(row, (long long)p.M - 1));
+      erow.res_stride = p.c_stride_n;
+      const int res_es = p.epi.res_type == RB_F32 ? 4 : 2;
+      auto set_res = [&](int n0) {
+        erow.ncols = min(32, p.N - n0);
+        erow.res = (row_ok && (p.epi.flags & RB_EPI_RESIDUAL))
+                       ? static_cast<const uint8_t*>(p.epi.residual) + (c_row_off + (long long)n0 * p.c_stride_n) * res_es
+                       : nullptr;
+      };
       // stream-K: 16-byte word i of column group c of this thread's row in the partial tile of unit u
       const int tile_row = (int)rank * kBM + q * 32 + lane;
       auto sk_word = [&](int u, int c, int i) -> uint4* {
@@ -687,9 +700,12 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
           float x[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) x[j] = p.acc_is_int ? __int2float_rn((int)v[j]) : __uint_as_float(v[j]);
-          if (p.epi.flags) epi_apply32(x, p.epi, vec_scale + c * 32, vec_bias + c * 32);
+          if (p.epi.flags) {
+            set_res(n0);
+            epi_apply32(x, p.epi, vec_scale + c * 32, vec_bias + c * 32, erow);
+          }
           uint4 w4[8];
-          const int nw = pack_row32(x, p.c_type, w4);
+          const int nw = pack_row32(x, p.c_type, w4, p.epi.out_zero);
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             if (i < nw) {
@@ -755,16 +771,17 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
           } else {
 #pragma unroll
             for (int j = 0; j < 32; ++j) x[j] = p.acc_is_int ? __int2float_rn((int)v[j]) : __uint_as_float(v[j]);
-            epi_apply32(x, p.epi, vec_scale + c * 32, vec_bias + c * 32);
+            set_res(n0);
+            epi_apply32(x, p.epi, vec_scale + c * 32, vec_bias + c * 32, erow);
           }
           if (p.c_tma || (p.vec_ok && n0 + 32 <= p.N)) {
-            nw = pack_row32(x, p.c_type, w4);
+            nw = pack_row32(x, p.c_type, w4, p.epi.out_zero);
           } else {
             nw = 0;
             if (row_ok) {
 #pragma unroll
               for (int j = 0; j < 32; ++j)
-                if (n0 + j < p.N) store_elem(p.c, c_row_off + (long long)(n0 + j) * p.c_stride_n, x[j], p.c_type);
+                if (n0 + j < p.N) store_elem(p.c, c_row_off + (long long)(n0 + j) * p.c_stride_n, x[j], p.c_type, p.epi.out_zero);
             }
           }
         }

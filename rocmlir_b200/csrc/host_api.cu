@@ -47,6 +47,9 @@ extern "C" RbStatus rbGemmHost(const RbGemmProblem* p, const RbEpilogue* epi_hos
   const size_t c_bytes = (size_t)p->g * p->m * p->n * es_c;
   const size_t ws_bytes = rbGemmWorkspaceSize(p);
   const uint32_t flags = epi_host ? epi_host->flags : 0u;
+  if (flags & (RB_EPI_RESIDUAL | RB_EPI_BIAS_ROW | RB_EPI_BIAS_SCALAR))
+    return fail(RB_UNSUPPORTED, "the host-buffer entry point carries per-column epilogue vectors only");
+  if (p->store_method != 0) return fail(RB_UNSUPPORTED, "the host-buffer entry point computes C = A.B only");
   const size_t scale_bytes = (flags & RB_EPI_COL_SCALE) ? (size_t)p->n * 4 : 0;
   const size_t bias_bytes = (flags & RB_EPI_BIAS) ? (size_t)p->n * dtype_bytes(epi_host->bias_type) : 0;
   const size_t total = up256(a_bytes) + up256(b_bytes) + up256(c_bytes) + up256(ws_bytes) + up256(scale_bytes) +

@@ -67,12 +67,13 @@ size_t gemm_workspace_bytes(const RbGemmProblem* p, int implicit_operand);
 RbStatus f32_planes(const float* src, float* hi, float* lo, int groups, int R, int C, int pitch, bool transpose,
                     bool split, void* stream);
 
-// rbConv / rbConvWorkspaceSize with the result element type overridden (-1: the problem's own). Only backward data
-// into a dense [pixels][channels] input takes an override: the folded 3-D path asks for an f32 gradient so that the
-// sum over its depth taps rounds once.
+// rbConv / rbConvWorkspaceSize with the result element type overridden (-1: the problem's own). Backward data into a
+// dense [pixels][channels] input takes an override (the folded 3-D path asks for an f32 gradient so that the sum over
+// its depth taps rounds once), and so does the forward direction with a fused epilogue (`epi`, applied per output
+// channel by the GEMM that ends the convolution).
 size_t conv_workspace_bytes(const RbConvProblem* p, int result_type);
 RbStatus conv_run(const RbConvProblem* p, int result_type, void* filter, void* input, void* output, void* workspace,
-                  size_t workspace_bytes, void* stream);
+                  size_t workspace_bytes, void* stream, const RbEpilogue* epi = nullptr);
 
 // cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per (device, kernel, size): the call costs microseconds and
 // small problems are bound by the host's launch path.

@@ -39,6 +39,11 @@ class Epilogue:
     relu: bool = False
     requant_scale: Optional[float] = None       # quantizelinear scale; the kernel multiplies by fl32(1/scale)
     mid_type: Optional[int] = None              # declared GEMM result type: round to it before/after the bias add
+    bias_mode: str = "col"                      # "col": bias[n]; "row": bias[m] (broadcast along N); "scalar": bias[0]
+    residual: Optional[torch.Tensor] = None     # same shape and layout as C: the same-shape add of dot + add
+    clip: Optional[tuple] = None                # (lo, hi): migraphx.clip after the rectifier
+    in_zero: Optional[float] = None             # dequantizelinear zero point (subtracted from the accumulator)
+    out_zero: Optional[int] = None              # quantizelinear zero point (added after the rounding cast, i8 results)
 
     def to_c(self) -> L.RbEpilogue:
         e = L.RbEpilogue()
@@ -55,6 +60,21 @@ class Epilogue:
             flags |= L.EPI_BIAS
             e.bias = self.bias.data_ptr()
             e.bias_type = rb_dtype(self.bias.dtype)
+            flags |= {"col": 0, "row": L.EPI_BIAS_ROW, "scalar": L.EPI_BIAS_SCALAR}[self.bias_mode]
+        if self.residual is not None:
+            assert self.residual.is_cuda and self.residual.is_contiguous()
+            flags |= L.EPI_RESIDUAL
+            e.residual = self.residual.data_ptr()
+            e.res_type = rb_dtype(self.residual.dtype)
+        if self.clip is not None:
+            flags |= L.EPI_CLIP
+            e.clip_lo, e.clip_hi = float(np.float32(self.clip[0])), float(np.float32(self.clip[1]))
+        if self.in_zero is not None:
+            flags |= L.EPI_ZP_IN
+            e.in_zero = float(np.float32(self.in_zero))
+        if self.out_zero is not None:
+            flags |= L.EPI_ZP_OUT
+            e.out_zero = int(self.out_zero)
         if self.relu:
             flags |= L.EPI_RELU
         if self.requant_scale is not None:
@@ -72,7 +92,7 @@ def _as3d(t: torch.Tensor) -> torch.Tensor:
 
 
 def problem(a: torch.Tensor, b: torch.Tensor, trans_a: bool, trans_b: bool, trans_c: bool, out_dtype: torch.dtype,
-            f32_mode: int = 0) -> L.RbGemmProblem:
+            f32_mode: int = 0, accumulate: bool = False) -> L.RbGemmProblem:
     a3, b3 = _as3d(a), _as3d(b)
     g = a3.shape[0]
     m, k = (a3.shape[2], a3.shape[1]) if trans_a else (a3.shape[1], a3.shape[2])
@@ -87,7 +107,8 @@ def problem(a: torch.Tensor, b: torch.Tensor, trans_a: bool, trans_b: bool, tran
         ab = L.F8E5M2_E4M3      # -t bf8_fp8
     else:
         raise L.RbError(L.UNSUPPORTED, "mixed A/B element types exist for the two 8-bit float formats only")
-    return L.RbGemmProblem(g, m, n, k, int(trans_a), int(trans_b), int(trans_c), ab, rb_dtype(out_dtype), int(f32_mode))
+    return L.RbGemmProblem(g, m, n, k, int(trans_a), int(trans_b), int(trans_c), ab, rb_dtype(out_dtype), int(f32_mode),
+                           int(accumulate))
 
 
 def default_out_dtype(ab: torch.dtype) -> torch.dtype:
@@ -106,13 +127,16 @@ def workspace_size(p: L.RbGemmProblem) -> int:
 def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bool = False, trans_c: bool = False,
          out_dtype: Optional[torch.dtype] = None, epilogue: Optional[Epilogue] = None,
          out: Optional[torch.Tensor] = None, workspace: Optional[torch.Tensor] = None, f32_mode: int = 0,
-         variant: Optional[int] = None) -> torch.Tensor:
+         variant: Optional[int] = None, accumulate: bool = False) -> torch.Tensor:
+    """`accumulate`: C = C + A.B on the given `out` (rocmlir-gen's --store-method=atomic_add)."""
+    if accumulate and out is None:
+        raise L.RbError(L.INVALID_PARAM, "accumulate adds to `out`, which must be given")
     if not (a.is_cuda and b.is_cuda):
         raise L.RbError(L.CUDA_ERROR, "operands must be CUDA tensors (the library has no CPU path)")
     if not (a.is_contiguous() and b.is_contiguous()):
         raise L.RbError(L.INVALID_PARAM, "operands must be contiguous")
     out_dtype = out_dtype or default_out_dtype(a.dtype)
-    p = problem(a, b, trans_a, trans_b, trans_c, out_dtype, f32_mode)
+    p = problem(a, b, trans_a, trans_b, trans_c, out_dtype, f32_mode, accumulate)
     shape = (p.g, p.n, p.m) if trans_c else (p.g, p.m, p.n)
     if out is None:
         out = torch.empty(shape, dtype=out_dtype, device=a.device)
