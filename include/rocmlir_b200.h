@@ -270,6 +270,19 @@ typedef struct RbAttentionProblem {
   const void *quant_scale;
 } RbAttentionProblem;
 
+/* Scratch: operands the kernels cannot load as they lie (i8 Q / K, transposed Q / V / O, a K whose rows are off
+ * 16-byte boundaries) are staged, and the f32 form keeps its G x Sq x Sk score matrix, in scratch memory.
+ * rbAttentionWs takes that memory from the caller like rbGemm and rbConv do: rbAttentionWorkspaceSize bytes (0 for
+ * the plain f16 / bf16 form), 16-byte aligned; it allocates nothing, so it may be captured into a CUDA graph and
+ * calls on different streams may overlap when each has its own workspace.
+ * rbAttention is the same call with scratch owned by the calling thread: one grow-only block per host thread, grown
+ * with cudaDeviceSynchronize + cudaFree + cudaMalloc inside the call and kept until the thread exits (1 GiB for an f32
+ * problem with G = 64, S = 2048). Because of that block, rbAttention calls that need scratch must not overlap on the
+ * GPU when issued by one host thread (two streams would race on it) and must not be made during stream capture when
+ * the block may grow; forms that need no scratch have neither restriction. */
+RB_EXPORT size_t rbAttentionWorkspaceSize(const RbAttentionProblem *p);
+RB_EXPORT RbStatus rbAttentionWs(const RbAttentionProblem *p, const void *q, const void *k, const void *v, void *o,
+                                 void *workspace, size_t workspace_bytes, void *stream);
 RB_EXPORT RbStatus rbAttention(const RbAttentionProblem *p, const void *q, const void *k, const void *v, void *o,
                                void *stream);
 

@@ -120,6 +120,11 @@ def lib() -> C.CDLL:
         l.rbAttention.restype = C.c_int
         l.rbAttention.argtypes = [C.POINTER(RbAttentionProblem), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                   C.c_void_p]
+        l.rbAttentionWorkspaceSize.restype = C.c_size_t
+        l.rbAttentionWorkspaceSize.argtypes = [C.POINTER(RbAttentionProblem)]
+        l.rbAttentionWs.restype = C.c_int
+        l.rbAttentionWs.argtypes = [C.POINTER(RbAttentionProblem), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                    C.c_void_p, C.c_size_t, C.c_void_p]
         l.rbGemmGemmWorkspaceSize.restype = C.c_size_t
         l.rbGemmGemmWorkspaceSize.argtypes = [C.c_int32] * 6
         l.rbGemmGemm.restype = C.c_int

@@ -19,7 +19,8 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, trans_k: boo
               scale: Optional[float] = None, bias: Optional[torch.Tensor] = None,
               mask: Optional[torch.Tensor] = None, mask_fill: float = float("-inf"), causal: bool = False,
               out: Optional[torch.Tensor] = None, scale_tensor: Optional[torch.Tensor] = None,
-              quant_bias: Optional[torch.Tensor] = None, quant_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+              quant_bias: Optional[torch.Tensor] = None, quant_scale: Optional[torch.Tensor] = None,
+              workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
     """With int8 `q` and `k` this is the first-GEMM-quantised form (rocmlir-gen -t i8): `v`, the result and the
     side tensors are f16, and `quant_bias` (one int8) and `quant_scale` (one f16), both CUDA tensors, are required."""
     for t in (q, k, v):
@@ -56,7 +57,13 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, trans_k: boo
         assert mask.is_cuda and mask.is_contiguous() and mask.dtype == torch.int8 and tuple(mask.shape) == (g, sq, sk)
         p.mask = mask.data_ptr()
     stream = torch.cuda.current_stream(q.device).cuda_stream
-    L.check(L.lib().rbAttention(C.byref(p), q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), stream))
+    # scratch for staged operands comes from the caller's side (rbAttentionWs): the library allocates nothing
+    need = int(L.lib().rbAttentionWorkspaceSize(C.byref(p)))
+    if need and (workspace is None or workspace.numel() * workspace.element_size() < need):
+        workspace = torch.empty(need, dtype=torch.uint8, device=q.device)
+    L.check(L.lib().rbAttentionWs(C.byref(p), q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                                  workspace.data_ptr() if need else None,
+                                  workspace.numel() * workspace.element_size() if need else 0, stream))
     return out
 
 

@@ -970,15 +970,14 @@ RbStatus qk_reserve(size_t bytes) {
   return RB_SUCCESS;
 }
 
-RbStatus attention_f32(const RbAttentionProblem* p, const void* q, const void* k, const void* v, void* o, void* stream_v) {
+RbStatus attention_f32(const RbAttentionProblem* p, const void* q, const void* k, const void* v, void* o, void* scratch,
+                       void* stream_v) {
   const DeviceInfo* dev = device_info();
   if (!dev) return RB_CUDA_ERROR;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   const long long G = p->g, Sq = p->seq_q, Sk = p->seq_k, D = p->head_qk, Dv = p->head_v;
   if (G > 65535) return fail(RB_UNSUPPORTED, "f32 attention: more than 65535 groups");
-  RbStatus st = qk_reserve((size_t)G * Sq * Sk * 4);
-  if (st != RB_SUCCESS) return st;
-  float* s = static_cast<float*>(t_qk.ptr);
+  float* s = static_cast<float*>(scratch);
   SgemmParams g1;   // S[g] = Q[g] . K[g]:  M = Sq, N = Sk, K = D
   g1.M = (int)Sq; g1.N = (int)Sk; g1.K = (int)D;
   g1.a_g = Sq * D; g1.a_m = p->trans_q ? 1 : D; g1.a_k = p->trans_q ? Sq : 1;     // Q [Sq][D] or [D][Sq]
@@ -1005,19 +1004,80 @@ RbStatus attention_f32(const RbAttentionProblem* p, const void* q, const void* k
   return RB_SUCCESS;
 }
 
+// Scratch an attention call stages operands in (0 for the plain f16 / bf16 form with loadable layouts).
+struct AttScratch {
+  size_t qw_off, kw_off, qt_off, kp_off, vt_off, ot_off, total;
+  long long sk_pitch;
+  bool k_repitch;
+};
+AttScratch plan_scratch(const RbAttentionProblem* p) {
+  AttScratch a{};
+  auto up = [](size_t x) { return (x + 255) / 256 * 256; };
+  if (p->data_type == RB_F32) {   // the whole score matrix
+    a.total = up((size_t)p->g * p->seq_q * p->seq_k * 4);
+    return a;
+  }
+  const bool quantized = p->data_type == RB_I8;
+  const size_t qn = (size_t)p->g * p->seq_q * p->head_qk, kn = (size_t)p->g * p->seq_k * p->head_qk;
+  const size_t vn = (size_t)p->g * p->seq_k * p->head_v, on = (size_t)p->g * p->seq_q * p->head_v;
+  a.sk_pitch = (p->seq_k + 7) / 8 * 8;
+  a.k_repitch = !p->trans_k && p->seq_k % 8 != 0;
+  size_t off = 0;
+  a.qw_off = off; off += quantized ? up(qn * 2) : 0;
+  a.kw_off = off; off += quantized ? up(kn * 2) : 0;
+  a.qt_off = off; off += p->trans_q ? up(qn * 2) : 0;
+  a.kp_off = off; off += a.k_repitch ? up((size_t)p->g * p->head_qk * a.sk_pitch * 2) : 0;
+  a.vt_off = off; off += p->trans_v ? up(vn * 2) : 0;
+  a.ot_off = off; off += p->trans_o ? up(on * 2) : 0;
+  a.total = off;
+  return a;
+}
+bool valid_sizes(const RbAttentionProblem* p) {
+  return p && p->g > 0 && p->seq_q > 0 && p->seq_k > 0 && p->head_qk > 0 && p->head_v > 0;
+}
 }  // namespace
+static RbStatus attention_run(const RbAttentionProblem* p, const void* q, const void* k, const void* v, void* o,
+                              void* workspace, size_t workspace_bytes, bool own_scratch, void* stream_v);
 }  // namespace rb
 
 using namespace rb;
 
+extern "C" size_t rbAttentionWorkspaceSize(const RbAttentionProblem* p) {
+  return valid_sizes(p) ? plan_scratch(p).total : 0;
+}
+
+extern "C" RbStatus rbAttentionWs(const RbAttentionProblem* p, const void* q, const void* k, const void* v, void* o,
+                                  void* workspace, size_t workspace_bytes, void* stream_v) {
+  return attention_run(p, q, k, v, o, workspace, workspace_bytes, false, stream_v);
+}
+
 extern "C" RbStatus rbAttention(const RbAttentionProblem* p, const void* q, const void* k, const void* v, void* o,
                                 void* stream_v) {
+  return attention_run(p, q, k, v, o, nullptr, 0, true, stream_v);
+}
+
+static RbStatus rb::attention_run(const RbAttentionProblem* p, const void* q, const void* k, const void* v, void* o,
+                                  void* workspace, size_t workspace_bytes, bool own_scratch, void* stream_v) {
   if (!p) return fail(RB_INVALID_PARAM, "problem is NULL");
   if (p->g <= 0 || p->seq_q <= 0 || p->seq_k <= 0 || p->head_qk <= 0 || p->head_v <= 0)
     return fail(RB_INVALID_PARAM, "g, seq_len_q, seq_len_k, head_dim_qk, head_dim_v must be positive");
   if (!q || !k || !v || !o) return fail(RB_INVALID_PARAM, "q, k, v and o must be device pointers");
   const bool quantized = p->data_type == RB_I8;
-  if (p->data_type == RB_F32) return attention_f32(p, q, k, v, o, stream_v);
+  const AttScratch sc = plan_scratch(p);
+  uint8_t* base = nullptr;
+  if (sc.total) {
+    if (own_scratch) {       // rbAttention: the calling thread's grow-only block (allocates on growth)
+      RbStatus st = qk_reserve(sc.total);
+      if (st != RB_SUCCESS) return st;
+      base = static_cast<uint8_t*>(t_qk.ptr);
+    } else {
+      if (!workspace || workspace_bytes < sc.total)
+        return fail(RB_WORKSPACE_TOO_SMALL, "workspace of " + std::to_string(sc.total) + " bytes required");
+      if (reinterpret_cast<uintptr_t>(workspace) % 16) return fail(RB_INVALID_PARAM, "workspace must be 16-byte aligned");
+      base = static_cast<uint8_t*>(workspace);
+    }
+  }
+  if (p->data_type == RB_F32) return attention_f32(p, q, k, v, o, base, stream_v);
   if (!(p->data_type == RB_F16 || p->data_type == RB_BF16 || quantized))
     return fail(RB_UNSUPPORTED, "attention exists for f32, f16, bf16 and the first-GEMM-quantised i8 form");
   if (quantized && (!p->quant_bias || !p->quant_scale))
@@ -1037,23 +1097,10 @@ extern "C" RbStatus rbAttention(const RbAttentionProblem* p, const void* q, cons
   // score equals the reference's i32), Q / V stored transposed, K stored G x D x Sk with rows off 16-byte boundaries;
   // a transposed O is written to scratch and turned afterwards.
   const size_t qn = (size_t)p->g * p->seq_q * p->head_qk, kn = (size_t)p->g * p->seq_k * p->head_qk;
-  const size_t vn = (size_t)p->g * p->seq_k * p->head_v, on = (size_t)p->g * p->seq_q * p->head_v;
-  const long long sk_pitch = (p->seq_k + 7) / 8 * 8;
-  const bool k_repitch = !p->trans_k && p->seq_k % 8 != 0;
-  auto up = [](size_t x) { return (x + 255) / 256 * 256; };
-  size_t off = 0;
-  const size_t qw_off = off; off += quantized ? up(qn * 2) : 0;
-  const size_t kw_off = off; off += quantized ? up(kn * 2) : 0;
-  const size_t qt_off = off; off += p->trans_q ? up(qn * 2) : 0;
-  const size_t kp_off = off; off += k_repitch ? up((size_t)p->g * p->head_qk * sk_pitch * 2) : 0;
-  const size_t vt_off = off; off += p->trans_v ? up(vn * 2) : 0;
-  const size_t ot_off = off; off += p->trans_o ? up(on * 2) : 0;
-  uint8_t* base = nullptr;
-  if (off) {
-    RbStatus st = qk_reserve(off);
-    if (st != RB_SUCCESS) return st;
-    base = static_cast<uint8_t*>(t_qk.ptr);
-  }
+  const long long sk_pitch = sc.sk_pitch;
+  const bool k_repitch = sc.k_repitch;
+  const size_t qw_off = sc.qw_off, kw_off = sc.kw_off, qt_off = sc.qt_off, kp_off = sc.kp_off, vt_off = sc.vt_off,
+               ot_off = sc.ot_off;
   const int sblocks = dev->sm_count * 8;
   if (quantized) {
     widen_i8_kernel<<<sblocks, 256, 0, stream>>>(static_cast<const int8_t*>(q), reinterpret_cast<__half*>(base + qw_off), (long long)qn);
@@ -1139,7 +1186,8 @@ extern "C" RbStatus rbAttention(const RbAttentionProblem* p, const void* q, cons
   kp.trace = trace_buffer((size_t)p->g * ((kp.q_tiles + 1) / 2) * 16);
   const long long ctas = (long long)p->g * kp.q_tiles;
   if (ctas > 0x7fffffffLL) return fail(RB_UNSUPPORTED, "too many query tiles");
-  if (p->seq_q > kQT && p->scale >= 0.0f) {
+  const float eff_scale = p->has_scale ? p->scale : 1.0f;   // an unset scale field must not pick the kernel
+  if (p->seq_q > kQT && eff_scale >= 0.0f) {
     // two query tiles per CTA (the fast path folds the scale into the row maximum, which needs scale >= 0)
     const long long ctas2 = (long long)p->g * ((kp.q_tiles + 1) / 2);
     if (ensure_dynamic_smem(reinterpret_cast<const void*>(attention_fwd2_kernel), Att2Smem::kTotal) != RB_SUCCESS) return RB_CUDA_ERROR;

@@ -4,6 +4,8 @@
 // by the calling thread, so repeated calls of the same size allocate nothing.
 #include <cuda_runtime.h>
 
+#include <algorithm>
+
 #include "lib_state.h"
 
 namespace rb {
@@ -30,6 +32,33 @@ RbStatus arena_reserve(size_t bytes) {
   return RB_SUCCESS;
 }
 size_t up256(size_t x) { return (x + 255) / 256 * 256; }
+
+// Copy streams and events of the pipelined host path, one set per calling thread and device, created on first use
+// and kept for the life of the thread.
+struct HostPipe {
+  static constexpr int kEvents = 16;
+  int device = -1;
+  cudaStream_t in = nullptr, out = nullptr;
+  cudaEvent_t start = nullptr, ev[kEvents] = {}, evg[kEvents] = {};
+};
+thread_local HostPipe t_pipe;
+
+HostPipe* host_pipe() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) { fail(RB_CUDA_ERROR, "cudaGetDevice failed"); return nullptr; }
+  if (t_pipe.device == dev) return &t_pipe;
+  HostPipe hp;
+  bool ok = cudaStreamCreateWithFlags(&hp.in, cudaStreamNonBlocking) == cudaSuccess &&
+            cudaStreamCreateWithFlags(&hp.out, cudaStreamNonBlocking) == cudaSuccess &&
+            cudaEventCreateWithFlags(&hp.start, cudaEventDisableTiming) == cudaSuccess;
+  for (int i = 0; ok && i < HostPipe::kEvents; ++i)
+    ok = cudaEventCreateWithFlags(&hp.ev[i], cudaEventDisableTiming) == cudaSuccess &&
+         cudaEventCreateWithFlags(&hp.evg[i], cudaEventDisableTiming) == cudaSuccess;
+  if (!ok) { fail(RB_CUDA_ERROR, "could not create the copy streams of the host path"); return nullptr; }
+  hp.device = dev;
+  t_pipe = hp;
+  return &t_pipe;
+}
 }  // namespace
 }  // namespace rb
 
@@ -63,8 +92,6 @@ extern "C" RbStatus rbGemmHost(const RbGemmProblem* p, const RbEpilogue* epi_hos
   uint8_t* dws = dc + up256(c_bytes);
   uint8_t* dscale = dws + up256(ws_bytes);
   uint8_t* dbias = dscale + up256(scale_bytes);
-  RB_CUDA_TRY(cudaMemcpyAsync(da, a_host, a_bytes, cudaMemcpyHostToDevice, stream));
-  RB_CUDA_TRY(cudaMemcpyAsync(db, b_host, b_bytes, cudaMemcpyHostToDevice, stream));
   RbEpilogue e;
   if (epi_host) {
     e = *epi_host;
@@ -79,10 +106,62 @@ extern "C" RbStatus rbGemmHost(const RbGemmProblem* p, const RbEpilogue* epi_hos
       e.bias = dbias;
     }
   }
-  st = rbGemm(p, epi_host ? &e : nullptr, da, db, dc, ws_bytes ? dws : nullptr, ws_bytes, stream_v);
-  if (st != RB_SUCCESS) return st;
-  RB_CUDA_TRY(cudaMemcpyAsync(c_host, dc, c_bytes, cudaMemcpyDeviceToHost, stream));
-  RB_CUDA_TRY(cudaStreamSynchronize(stream));
+  // Pipelined form: B first, then A in blocks of rows; the GEMM of a block runs as soon as its rows have arrived and
+  // its rows of C travel back while later blocks are still uploading, so both directions of the host link are busy at
+  // once. Rows of C depend on their own rows of A only and every element keeps its K order, so the result is bit for
+  // bit that of one rbGemm over the whole problem. Applies to one group with A and C stored row by row.
+  const int kBlockRows = 512;
+  const bool pipelined = p->g == 1 && !p->trans_a && !p->trans_c && p->m >= 4 * kBlockRows && ws_bytes == 0 &&
+                         a_bytes + b_bytes + c_bytes >= ((size_t)8 << 20);
+  if (pipelined) {
+    HostPipe* hp = host_pipe();
+    if (!hp) return RB_CUDA_ERROR;
+    const int nblk = (p->m + kBlockRows - 1) / kBlockRows;
+    RB_CUDA_TRY(cudaEventRecord(hp->start, stream));               // epilogue vectors, and whatever `stream` held before
+    RB_CUDA_TRY(cudaStreamWaitEvent(hp->in, hp->start, 0));
+    RB_CUDA_TRY(cudaStreamWaitEvent(hp->out, hp->start, 0));
+    RB_CUDA_TRY(cudaMemcpyAsync(db, b_host, b_bytes, cudaMemcpyHostToDevice, hp->in));
+    const int saved_variant = rbGetGemmVariant();
+    // whole tiles per block: a K split would only add a reduction pass to a GEMM that hides behind the copies anyway
+    rbSetGemmVariant((saved_variant & ~0xFF0000) | (1 << 16));
+    RbStatus bst = RB_SUCCESS;
+    for (int i = 0; i < nblk && bst == RB_SUCCESS; ++i) {
+      const int r0 = i * kBlockRows, rows = std::min(kBlockRows, p->m - r0);
+      const size_t a_off = (size_t)r0 * p->k * es, c_off = (size_t)r0 * p->n * es_c;
+      cudaEvent_t ev = hp->ev[i % HostPipe::kEvents];
+      cudaError_t ce = cudaMemcpyAsync(da + a_off, static_cast<const uint8_t*>(a_host) + a_off, (size_t)rows * p->k * es,
+                                       cudaMemcpyHostToDevice, hp->in);
+      if (ce == cudaSuccess) ce = cudaEventRecord(ev, hp->in);
+      if (ce == cudaSuccess) ce = cudaStreamWaitEvent(stream, ev, 0);
+      if (ce != cudaSuccess) { bst = fail(RB_CUDA_ERROR, cudaGetErrorString(ce)); break; }
+      RbGemmProblem bp = *p;
+      bp.m = rows;
+      bst = rbGemm(&bp, epi_host ? &e : nullptr, da + a_off, db, dc + c_off, nullptr, 0, stream_v);
+      if (bst != RB_SUCCESS) break;
+      cudaEvent_t evg = hp->evg[i % HostPipe::kEvents];
+      ce = cudaEventRecord(evg, stream);
+      if (ce == cudaSuccess) ce = cudaStreamWaitEvent(hp->out, evg, 0);
+      if (ce == cudaSuccess)
+        ce = cudaMemcpyAsync(static_cast<uint8_t*>(c_host) + c_off, dc + c_off, (size_t)rows * p->n * es_c,
+                             cudaMemcpyDeviceToHost, hp->out);
+      if (ce != cudaSuccess) bst = fail(RB_CUDA_ERROR, cudaGetErrorString(ce));
+    }
+    rbSetGemmVariant(saved_variant);
+    // the copy streams are the library's own: always drain them, also after an error
+    const cudaError_t s1 = cudaStreamSynchronize(hp->in), s2 = cudaStreamSynchronize(hp->out),
+                      s3 = cudaStreamSynchronize(stream);
+    if (bst != RB_SUCCESS) return bst;
+    RB_CUDA_TRY(s1);
+    RB_CUDA_TRY(s2);
+    RB_CUDA_TRY(s3);
+  } else {
+    RB_CUDA_TRY(cudaMemcpyAsync(da, a_host, a_bytes, cudaMemcpyHostToDevice, stream));
+    RB_CUDA_TRY(cudaMemcpyAsync(db, b_host, b_bytes, cudaMemcpyHostToDevice, stream));
+    st = rbGemm(p, epi_host ? &e : nullptr, da, db, dc, ws_bytes ? dws : nullptr, ws_bytes, stream_v);
+    if (st != RB_SUCCESS) return st;
+    RB_CUDA_TRY(cudaMemcpyAsync(c_host, dc, c_bytes, cudaMemcpyDeviceToHost, stream));
+    RB_CUDA_TRY(cudaStreamSynchronize(stream));
+  }
   // This entry point is synchronous, so it can report what the asynchronous ones leave to rbReadKernelStatus: a
   // bounded device-side wait that ran out (the result in c_host is then not valid).
   uint32_t word = 0;

@@ -63,7 +63,7 @@ MiirStatus lower(Handle* h, bool binary) {
     // attention: one CTA per pair of 128-row query tiles (single tiles for short sequences), 10 or 8 warps
     const RbAttentionProblem& a = h->d.att;
     const long long tiles = (a.seq_q + 127) / 128;
-    const bool two = a.seq_q > 128;
+    const bool two = a.seq_q > 128 && (a.has_scale ? a.scale : 1.0f) >= 0.0f;   // the same rule as the launch
     h->grid = (size_t)((long long)a.g * (two ? (tiles + 1) / 2 : tiles));
     h->block = two ? 384 : 256;
   }

@@ -205,3 +205,59 @@ def test_f32_attention_unfused(cuda_device, g, sq, sk, d, dv):
     ref64 = oracle.attention(qn, kn, vn, elem_type=oracle.F64, scale_scalar=0.125, causal=True, threads=oracle.max_threads())
     got = attention(dev(qn), dev(kn), dev(vn), scale=0.125, causal=True).cpu().numpy()
     assert np.abs(got - ref64).max() <= 2e-5 * max(1.0, np.abs(ref64).max())
+
+
+def test_negative_scale_takes_the_general_kernel_and_matches_the_oracle(cuda_device):
+    """A negative scale cannot be folded into the row maximum: the call must still be right (it runs the one-tile
+    kernel), and a problem without a scale must not be dispatched on whatever its unused `scale` field holds."""
+    import ctypes as C
+    import torch
+    from rocmlir_b200 import _lib as L
+    g, sq, sk, d, dv = 2, 300, 264, 64, 64
+    (q, qraw), (k, kraw), (v, vraw) = make_qkv(g, sq, sk, d, dv, oracle.F16)
+    got = run_attention(qraw, kraw, vraw, oracle.F16, scale=-0.125)
+    ref64 = oracle.attention(q, k, v, elem_type=oracle.F64, scale_scalar=-0.125, threads=oracle.max_threads())
+    verdict, info = oracle.verify_float(got, ref64, 1e-3, 100.0, 1e30)
+    assert verdict == [1, 1, 1], info
+    # has_scale = 0 with a garbage negative `scale` field: same result as the clean call
+    tq, tk, tv = to_device(qraw, oracle.F16), to_device(kraw, oracle.F16), to_device(vraw, oracle.F16)
+    outs = []
+    for junk in (0.0, -7.0):
+        o = torch.empty((g, sq, dv), dtype=torch.float16, device="cuda")
+        p = L.RbAttentionProblem(g, sq, sk, d, dv, 0, 0, 0, 0, L.F16, 0, junk, 0, 0.0, None, None, None, None, None)
+        L.check(L.lib().rbAttention(C.byref(p), tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), o.data_ptr(),
+                                    torch.cuda.current_stream().cuda_stream))
+        torch.cuda.synchronize()
+        outs.append(o)
+    assert torch.equal(outs[0], outs[1])
+
+
+def test_caller_workspace_entry_point_equals_thread_scratch_entry_point(cuda_device):
+    """rbAttentionWs (scratch from the caller, nothing allocated) and rbAttention (scratch owned by the calling
+    thread) run the same kernels: identical results on a form that stages three operands (transposed Q, V and O)."""
+    import ctypes as C
+    import torch
+    from rocmlir_b200 import _lib as L
+    g, sq, sk, d, dv = 2, 200, 136, 64, 64
+    (q, qraw), (k, kraw), (v, vraw) = make_qkv(g, sq, sk, d, dv, oracle.F16)
+    tq = to_device(np.ascontiguousarray(np.swapaxes(qraw, 1, 2)), oracle.F16)
+    tv = to_device(np.ascontiguousarray(np.swapaxes(vraw, 1, 2)), oracle.F16)
+    tk = to_device(kraw, oracle.F16)
+    p = L.RbAttentionProblem(g, sq, sk, d, dv, 1, 0, 1, 1, L.F16, 1, 0.125, 0, 0.0, None, None, None, None, None)
+    need = L.lib().rbAttentionWorkspaceSize(C.byref(p))
+    assert need >= 2 * (g * sq * d + g * sk * dv + g * sq * dv)
+    stream = torch.cuda.current_stream().cuda_stream
+    o1 = torch.zeros((g, dv, sq), dtype=torch.float16, device="cuda")
+    o2 = torch.zeros((g, dv, sq), dtype=torch.float16, device="cuda")
+    st = L.lib().rbAttentionWs(C.byref(p), tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), o1.data_ptr(), None, 0, stream)
+    assert st == L.WORKSPACE_TOO_SMALL and str(need) in L.lib().rbGetLastError().decode()
+    ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+    L.check(L.lib().rbAttentionWs(C.byref(p), tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), o1.data_ptr(), ws.data_ptr(), need, stream))
+    L.check(L.lib().rbAttention(C.byref(p), tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), o2.data_ptr(), stream))
+    torch.cuda.synchronize()
+    assert L.kernel_status() == 0
+    assert torch.equal(o1, o2)
+    ref64 = oracle.attention(q, k, v, elem_type=oracle.F64, scale_scalar=0.125, threads=oracle.max_threads())
+    got = oracle.to_f32(from_device(o1, oracle.F16), oracle.F16).reshape(g, dv, sq).swapaxes(1, 2)
+    verdict, info = oracle.verify_float(got, ref64, 1e-3, 100.0, 1e30)
+    assert verdict == [1, 1, 1], info
