@@ -20,15 +20,21 @@
  *  - a handle describes the whole operation: miirGetKernelCount() is 1 and `--kernel_id` may only be 0 (the
  *    reference needs up to 3 kernels and one handle per kernel id; the gather / reduction passes of this library
  *    are launched inside miirLaunch);
- *  - the "binary" of miirBufferGet is not device code but a relocatable launch descriptor (problem, tile
- *    configuration), which miirLaunchFromBuffer turns into launches; kernels live in the library itself;
- *  - miirLaunch / miirLaunchFromBuffer replace the client's own hipModuleLaunchKernel.
+ *  - the binary of miirBufferGet is an sm_100a cubin (an ELF image for cuModuleLoadData) where the reference's is an
+ *    hsaco; it holds every instantiation of the GEMM / implicit-GEMM kernel, the one a given handle launches is named
+ *    by miirGetKernelLaunch, which also carries what the reference's two execution dimensions cannot: cluster size,
+ *    dynamic shared memory and the parameter block with the TMA tensor maps of the caller's buffers;
+ *  - operations that run as several kernels (layout, filter or reduction passes beside the GEMM kernel; attention)
+ *    are launched through miirLaunch, or later through miirLaunchFromBuffer from the small relocatable descriptor of
+ *    miirDescriptorGet (problem + tile configuration), in place of the client's own hipModuleLaunchKernel.
  */
 #ifndef MIIR_B200_H
 #define MIIR_B200_H
 
 #include <stddef.h>
 #include <stdint.h>
+
+#include "rocmlir_b200.h" /* RbKernelLaunch */
 
 #ifdef __cplusplus
 extern "C" {
@@ -63,13 +69,26 @@ MIIR_EXPORT int miirGetWorkspaceSize(MiirHandle handle);
 /* Miir.h:70: selects the tile configuration (the applicability + tuning-parameter part of lowering). */
 MIIR_EXPORT MiirStatus miirLowerTuningParams(MiirHandle handle);
 
-/* Miir.h:75: the same selection plus the launch descriptor miirBufferGet hands out. */
+/* Miir.h:75: the same selection; afterwards miirBufferGet / miirGetKernelLaunch / miirDescriptorGet answer. */
 MIIR_EXPORT MiirStatus miirLowerBin(MiirHandle handle);
 
-/* Miir.h:89: two-call protocol. buffer == NULL: *size receives the descriptor's size; otherwise the descriptor is
- * copied into buffer. MIIR_INVALID_PARAM when both are NULL or the handle is NULL; MIIR_INVALID_MODULE before
- * miirLowerBin. */
+/* Miir.h:89: two-call protocol. buffer == NULL: *size receives the size of the code object; otherwise the code
+ * object - the library's sm_100a cubin - is copied into buffer. MIIR_INVALID_PARAM when both are NULL or the handle is
+ * NULL; MIIR_INVALID_MODULE before miirLowerBin; MIIR_BUILD_FAILURE for an attention handle (its kernels are launched
+ * through miirLaunch only). */
 MIIR_EXPORT MiirStatus miirBufferGet(MiirHandle handle, char *buffer, size_t *size);
+
+/* What the reference's {code object, global size, local size} cannot say on this hardware (no counterpart in Miir.h):
+ * for the buffers arg0..arg2 (kernel-argument order: filter, input, output / a, b, c) the name of the handle's
+ * kernel inside the cubin, its cluster size, dynamic shared memory and parameter block. See RbKernelLaunch in
+ * rocmlir_b200.h for how to launch it with cuLaunchKernelEx. MIIR_BUILD_FAILURE when the operation does not run as
+ * one kernel (then use miirLaunch); MIIR_INVALID_MODULE before miirLowerBin. Needs the GPU (tensor maps are
+ * encoded by the driver). */
+MIIR_EXPORT MiirStatus miirGetKernelLaunch(MiirHandle handle, void *arg0, void *arg1, void *arg2, RbKernelLaunch *out);
+
+/* The relocatable launch descriptor of the whole operation (problem + tile configuration, a few hundred bytes), same
+ * two-call protocol: what a client's kernel cache keeps for miirLaunchFromBuffer. No counterpart in Miir.h. */
+MIIR_EXPORT MiirStatus miirDescriptorGet(MiirHandle handle, char *buffer, size_t *size);
 
 /* Miir.h:97: global_size = grid * block and local_size = block of the operation's GEMM kernel (1-D).
  * MIIR_INVALID_MODULE before one of the miirLower* calls. */
@@ -86,7 +105,7 @@ MIIR_EXPORT MiirStatus miirDestroyHandle(MiirHandle handle);
 MIIR_EXPORT MiirStatus miirLaunch(MiirHandle handle, void *arg0, void *arg1, void *arg2, void *extra, void *workspace,
                                   size_t workspace_bytes, void *stream);
 
-/* The same from a descriptor obtained with miirBufferGet (e.g. out of a client's kernel cache). */
+/* The same from a descriptor obtained with miirDescriptorGet (e.g. out of a client's kernel cache). */
 MIIR_EXPORT MiirStatus miirLaunchFromBuffer(const char *buffer, size_t size, void *arg0, void *arg1, void *arg2,
                                             void *extra, void *workspace, size_t workspace_bytes, void *stream);
 

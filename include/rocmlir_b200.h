@@ -295,6 +295,35 @@ RB_EXPORT RbStatus rbGemmGemm(int32_t g, int32_t m, int32_t k1, int32_t n1, int3
                               const void *b1, const void *b2, void *o, void *workspace, size_t workspace_bytes,
                               void *stream);
 
+/* ---- The kernels as a loadable binary ------------------------------------------------------------------------------
+ * Where the reference hands its client a code object plus {block size, grid size} (mlirGetBinary / mlirGetKernelAttrs,
+ * mlir/include/mlir-c/Dialect/MIGraphX.h:48-56; miirBufferGet, mlir/tools/rocmlir-lib/Miir.h:89) and the client
+ * launches it itself, this library hands out an sm_100a cubin (an ELF image for cuModuleLoadData) that holds every
+ * instantiation of its GEMM / implicit-GEMM-convolution kernel, and describes the launch of one problem in
+ * RbKernelLaunch: what the two integers of the reference cannot carry on this hardware - the kernel's name inside the
+ * image, the cluster size (cuLaunchKernelEx, CU_LAUNCH_ATTRIBUTE_CLUSTER_DIMENSION), the dynamic shared memory
+ * (CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES and the launch) and the kernel's parameter block, which contains
+ * the TMA tensor maps with the device addresses of the operands encoded (so it is made per set of buffers).
+ * Launch: kernelParams[i] = params + param_offset[i] for i < param_count; grid (grid,1,1), block (block,1,1).
+ * Only problems that run as ONE kernel have such a description (no operand copy, TF32 planes, K split, layout or
+ * filter pass): the others return RB_UNSUPPORTED here and are launched through rbGemm / rbConv. */
+typedef struct RbKernelLaunch {
+  char symbol[160];
+  uint32_t grid, block;
+  uint32_t cluster;            /* CTAs per cluster along x: 1 or 2 */
+  uint32_t dynamic_smem;       /* bytes */
+  uint32_t param_count;        /* 2 */
+  uint32_t param_offset[4], param_size[4];
+  uint32_t reserved[3];
+  unsigned char params[2048] __attribute__((aligned(64)));
+} RbKernelLaunch;
+
+RB_EXPORT RbStatus rbGetKernelBinary(const void **image, size_t *size);
+RB_EXPORT RbStatus rbGemmEncodeLaunch(const RbGemmProblem *p, const RbEpilogue *epi /* may be NULL */, const void *a,
+                                      const void *b, void *c, RbKernelLaunch *out);
+RB_EXPORT RbStatus rbConvEncodeLaunch(const RbConvProblem *p, const RbEpilogue *epi /* may be NULL */, int32_t out_type,
+                                      void *filter, void *input, void *output, RbKernelLaunch *out);
+
 /* Kernel-selection knob for tuning/experiments: tile variant used by subsequent rbGemm calls on this
  * thread's library state. 0 = automatic (measured table). Mirrors the role of rocMLIR's perf_config
  * (mlir/include/mlir/Dialect/Rock/Tuning/GridwiseGemmParams.h:138-194). */

@@ -68,6 +68,12 @@ class RbGemmConfigInfo(C.Structure):
                [("kpr", C.c_int32), ("stages_epi_vec", C.c_int32), ("dynamic_smem_epi_vec", C.c_uint32)]
 
 
+class RbKernelLaunch(C.Structure):
+    _fields_ = [("symbol", C.c_char * 160), ("grid", C.c_uint32), ("block", C.c_uint32), ("cluster", C.c_uint32),
+                ("dynamic_smem", C.c_uint32), ("param_count", C.c_uint32), ("param_offset", C.c_uint32 * 4),
+                ("param_size", C.c_uint32 * 4), ("reserved", C.c_uint32 * 3), ("params", C.c_ubyte * 2048)]
+
+
 class _Handle(C.Structure):
     """The one-pointer opaque structs of the tuning API (RbProblem, RbTuningSpace, RbTuningParam, RbTuningTable)."""
     _fields_ = [("ptr", C.c_void_p)]
@@ -148,6 +154,18 @@ def lib() -> C.CDLL:
         l.miirBufferGet.argtypes = [C.c_void_p, C.c_char_p, C.POINTER(C.c_size_t)]
         l.miirGetExecutionDims.restype = C.c_int
         l.miirGetExecutionDims.argtypes = [C.c_void_p, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]
+        l.miirDescriptorGet.restype = C.c_int
+        l.miirDescriptorGet.argtypes = [C.c_void_p, C.c_char_p, C.POINTER(C.c_size_t)]
+        l.miirGetKernelLaunch.restype = C.c_int
+        l.miirGetKernelLaunch.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(RbKernelLaunch)]
+        l.rbGetKernelBinary.restype = C.c_int
+        l.rbGetKernelBinary.argtypes = [C.POINTER(C.c_void_p), C.POINTER(C.c_size_t)]
+        l.rbGemmEncodeLaunch.restype = C.c_int
+        l.rbGemmEncodeLaunch.argtypes = [C.POINTER(RbGemmProblem), C.POINTER(RbEpilogue), C.c_void_p, C.c_void_p, C.c_void_p,
+                                         C.POINTER(RbKernelLaunch)]
+        l.rbConvEncodeLaunch.restype = C.c_int
+        l.rbConvEncodeLaunch.argtypes = [C.POINTER(RbConvProblem), C.POINTER(RbEpilogue), C.c_int32, C.c_void_p, C.c_void_p,
+                                         C.c_void_p, C.POINTER(RbKernelLaunch)]
         l.miirLaunch.restype = C.c_int
         l.miirLaunch.argtypes = [C.c_void_p] * 6 + [C.c_size_t, C.c_void_p]
         l.miirLaunchFromBuffer.restype = C.c_int

@@ -36,9 +36,12 @@ def sources() -> list[str]:
     return sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".cu"))
 
 
+CUBIN_SRC = os.path.join(CSRC, "cubin", "gemm_kernels.cu")
+
+
 def _deps_digest() -> str:
     h = hashlib.sha256()
-    for root in (CSRC, INCLUDE):
+    for root in (CSRC, INCLUDE, os.path.join(CSRC, "cubin")):
         for f in sorted(os.listdir(root)):
             if f.endswith((".cu", ".cuh", ".h")):
                 with open(os.path.join(root, f), "rb") as fh:
@@ -67,8 +70,32 @@ def build(force: bool = False, verbose: bool = False) -> str:
             raise RuntimeError(f"nvcc failed on {src}")
         return obj
 
-    with cf.ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
+    def cubin_object(_=None) -> str:
+        """The kernels once more as a cubin (an ELF image for cuModuleLoadData), wrapped into an object file as
+        read-only data between the symbols rb_gemm_cubin_start / rb_gemm_cubin_end."""
+        cubin = os.path.join(OBJ, "gemm_kernels.cubin")
+        cmd = [nvcc, "-cubin", CUBIN_SRC, "-o", cubin] + ARCH_FLAGS + ["-O3", "-std=c++17", "-lineinfo",
+                                                                      "--expt-relaxed-constexpr", "-I", INCLUDE, "-I", CSRC]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            sys.stderr.write(r.stdout + r.stderr)
+            raise RuntimeError("nvcc -cubin failed")
+        asm = os.path.join(OBJ, "gemm_cubin_blob.S")
+        with open(asm, "w") as fh:
+            fh.write('.section .rodata\n.balign 64\n.global rb_gemm_cubin_start\nrb_gemm_cubin_start:\n'
+                     '.incbin "gemm_kernels.cubin"\n.global rb_gemm_cubin_end\nrb_gemm_cubin_end:\n'
+                     '.section .note.GNU-stack,"",@progbits\n')
+        obj = os.path.join(OBJ, "gemm_cubin_blob.o")
+        r = subprocess.run(["gcc", "-c", "gemm_cubin_blob.S", "-o", obj], cwd=OBJ, capture_output=True, text=True)
+        if r.returncode != 0:
+            sys.stderr.write(r.stdout + r.stderr)
+            raise RuntimeError("assembling the cubin blob failed")
+        return obj
+
+    with cf.ThreadPoolExecutor(max_workers=min(8, len(srcs) + 1)) as ex:
+        blob = ex.submit(cubin_object)
         objs = list(ex.map(compile_one, srcs))
+        objs.append(blob.result())
     cmd = [nvcc, "-shared", "-o", LIB] + objs + ARCH_FLAGS + ["-cudart", "static", "-Xcompiler", "-fPIC"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:

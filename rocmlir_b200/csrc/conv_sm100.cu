@@ -659,17 +659,27 @@ extern "C" RbStatus rbConvEpi(const RbConvProblem* p, const RbEpilogue* epi, int
   return rb::conv_run(p, out_type, filter, input, output, workspace, workspace_bytes, stream_v, epi);
 }
 
+extern "C" RbStatus rbConvEncodeLaunch(const RbConvProblem* p, const RbEpilogue* epi, int32_t out_type, void* filter,
+                                       void* input, void* output, RbKernelLaunch* out) {
+  if (!out) return fail(RB_INVALID_PARAM, "out is NULL");
+  return rb::conv_run(p, out_type, filter, input, output, nullptr, 0, nullptr, epi, out);
+}
+
 RbStatus rb::conv_run(const RbConvProblem* p, int result_type, void* filter, void* input, void* output, void* workspace,
-                      size_t workspace_bytes, void* stream_v, const RbEpilogue* epi) {
+                      size_t workspace_bytes, void* stream_v, const RbEpilogue* epi, RbKernelLaunch* capture) {
   ConvPlan pl;
   RbStatus st = make_plan(p, &pl, result_type);
   if (st != RB_SUCCESS) return st;
+  if (capture && (pl.n_classes > 0 || !pl.a_direct || !pl.b_direct || !pl.c_direct || pl.a_up || pl.a_planes > 0 ||
+                  (p->direction == 1 && pl.a_implicit)))
+    return fail(RB_UNSUPPORTED, "this convolution runs as several kernels (layout, filter or reduction passes): it has no "
+                                "single-kernel binary; launch it through the library");
   if (epi && p->direction != 0) return fail(RB_UNSUPPORTED, "a fused epilogue exists for the forward convolution only");
   if (epi && (epi->flags & RB_EPI_RESIDUAL) && !pl.c_direct)
     return fail(RB_UNSUPPORTED, "a residual operand needs the [pixels][channels] output layout (nhwgk)");
   if (epi && (epi->flags & RB_EPI_BIAS_ROW)) return fail(RB_UNSUPPORTED, "the bias of a convolution is per output channel or scalar");
   if (!filter || !input || !output) return fail(RB_INVALID_PARAM, "filter, input and output must be device pointers");
-  if (pl.total > 0 && (!workspace || workspace_bytes < pl.total))
+  if (!capture && pl.total > 0 && (!workspace || workspace_bytes < pl.total))
     return fail(RB_WORKSPACE_TOO_SMALL, "workspace of " + std::to_string(pl.total) + " bytes required");
   const DeviceInfo* dev = device_info();
   if (!dev) return RB_CUDA_ERROR;
@@ -848,7 +858,7 @@ RbStatus rb::conv_run(const RbConvProblem* p, int result_type, void* filter, voi
       cv.P = (int)ho; cv.Q = (int)wo; cv.Y = p->y; cv.X = p->x;
       cv.stride_h = p->stride_h; cv.stride_w = p->stride_w; cv.dil_h = p->dil_h; cv.dil_w = p->dil_w;
       cv.pad_h = p->pad_h; cv.pad_w = p->pad_w; cv.pad_h_hi = p->pad_h_r; cv.pad_w_hi = p->pad_w_r;
-      st = gemm_run(&pl.gemm, nullptr, A, nullptr, C, pl.gemm_ws ? ws + pl.gemm_off : nullptr, pl.gemm_ws, stream_v, &cv);
+      st = gemm_run(&pl.gemm, nullptr, A, nullptr, C, pl.gemm_ws ? ws + pl.gemm_off : nullptr, pl.gemm_ws, stream_v, &cv, capture);
       if (st != RB_SUCCESS) return st;
       if (!pl.c_direct) permute(C, filter, fsz, pl.fs, fil_kyxc, false, es_c);
       return RB_SUCCESS;
@@ -893,9 +903,9 @@ RbStatus rb::conv_run(const RbConvProblem* p, int result_type, void* filter, voi
       cv.pad_h_hi = p->h - uh - cv.pad_h + (p->y - 1) * p->dil_h;
       cv.pad_w_hi = p->w - uw - cv.pad_w + (p->x - 1) * p->dil_w;
     }
-    st = gemm_run(&pl.gemm, epi, nullptr, B, C, pl.gemm_ws ? ws + pl.gemm_off : nullptr, pl.gemm_ws, stream_v, &cv);
+    st = gemm_run(&pl.gemm, epi, nullptr, B, C, pl.gemm_ws ? ws + pl.gemm_off : nullptr, pl.gemm_ws, stream_v, &cv, capture);
   } else {
-    st = rbGemm(&pl.gemm, epi, A, B, C, pl.gemm_ws ? ws + pl.gemm_off : nullptr, pl.gemm_ws, stream_v);
+    st = gemm_run(&pl.gemm, epi, A, B, C, pl.gemm_ws ? ws + pl.gemm_off : nullptr, pl.gemm_ws, stream_v, nullptr, capture);
   }
   if (st != RB_SUCCESS) return st;
   if (!pl.c_direct) {

@@ -4,6 +4,7 @@
 #include "gemm_sm100.cuh"
 
 #include <atomic>
+#include <cstdio>
 #include <mutex>
 
 #include "lib_state.h"
@@ -390,8 +391,16 @@ extern "C" RbStatus rbGemm(const RbGemmProblem* p, const RbEpilogue* epi, const 
   return rb::gemm_run(p, epi, a, b, c, workspace, workspace_bytes, stream_v, nullptr);
 }
 
+// Name of an instantiation of gemm_tcgen05_kernel inside the cubin image (Itanium mangling of
+// rb::gemm_tcgen05_kernel<KIND, A_MN, B_MN, CTAS>(GemmTensorMaps, GemmParams)).
+static std::string kernel_symbol(int kind, bool a_mn, bool b_mn, int ctas) {
+  return "_ZN2rb19gemm_tcgen05_kernelILi" + std::to_string(kind) + "ELb" + (a_mn ? "1" : "0") + "ELb" + (b_mn ? "1" : "0") +
+         "ELi" + std::to_string(ctas) + "EEEvNS_14GemmTensorMapsENS_10GemmParamsE";
+}
+
 RbStatus rb::gemm_run(const RbGemmProblem* p, const RbEpilogue* epi, const void* a, const void* b, void* c,
-                      void* workspace, size_t workspace_bytes, void* stream_v, const ConvAOperand* conva) {
+                      void* workspace, size_t workspace_bytes, void* stream_v, const ConvAOperand* conva,
+                      RbKernelLaunch* capture) {
   RbStatus st = check_problem(p);
   if (st != RB_SUCCESS) return st;
   const bool conv_a = conva && conva->operand == 0, conv_b = conva && conva->operand == 1;
@@ -476,6 +485,9 @@ RbStatus rb::gemm_run(const RbGemmProblem* p, const RbEpilogue* epi, const void*
   if ((reinterpret_cast<uintptr_t>(a) % 16 && !oa.needs_copy) || (reinterpret_cast<uintptr_t>(b) % 16 && !ob.needs_copy))
     return fail(RB_UNSUPPORTED, "operand base addresses must be 16-byte aligned");
 
+  if (capture && (oa.needs_copy || ob.needs_copy || cfg.splits > 1))
+    return fail(RB_UNSUPPORTED, "this problem runs as several kernels (operand copy, TF32 planes or a K split): it has no "
+                                "single-kernel binary; launch it through the library");
   uint8_t* wsb = static_cast<uint8_t*>(workspace);
   const void* a_src[2] = {a, nullptr};
   const void* b_src[2] = {b, nullptr};
@@ -705,6 +717,25 @@ RbStatus rb::gemm_run(const RbGemmProblem* p, const RbEpilogue* epi, const void*
   } else {
     lc.gridDim = dim3((unsigned)std::min<long long>(num_items, dev->sm_count), 1, 1);
   }
+  if (capture) {
+    static_assert(sizeof(GemmTensorMaps) + sizeof(GemmParams) + 64 <= sizeof(capture->params), "parameter block too small");
+    memset(capture, 0, sizeof(*capture));
+    const std::string sym = kernel_symbol(kind, kind == kKindTF32 ? false : a_mn, kind == kKindTF32 ? false : b_mn, ctas);
+    snprintf(capture->symbol, sizeof(capture->symbol), "%s", sym.c_str());
+    capture->grid = lc.gridDim.x;
+    capture->block = kGemmThreads;
+    capture->cluster = (uint32_t)ctas;
+    capture->dynamic_smem = (uint32_t)smem;
+    capture->param_count = 2;
+    capture->param_offset[0] = 0;
+    capture->param_size[0] = (uint32_t)sizeof(GemmTensorMaps);
+    capture->param_offset[1] = (uint32_t)((sizeof(GemmTensorMaps) + 63) / 64 * 64);
+    capture->param_size[1] = (uint32_t)sizeof(GemmParams);
+    kp.trace = nullptr;
+    memcpy(capture->params + capture->param_offset[0], &maps, sizeof(maps));
+    memcpy(capture->params + capture->param_offset[1], &kp, sizeof(kp));
+    return RB_SUCCESS;
+  }
   kp.trace = trace_buffer((size_t)lc.gridDim.x * 16);
   RB_CUDA_TRY(cudaLaunchKernelEx(&lc, kern, maps, kp));
   count_launch();
@@ -716,6 +747,25 @@ RbStatus rb::gemm_run(const RbGemmProblem* p, const RbEpilogue* epi, const void*
     count_launch();
   }
   return RB_SUCCESS;
+}
+
+// ---- the kernels as a loadable binary --------------------------------------------------------------------------------
+// The image is the cubin that nvcc makes of csrc/cubin/gemm_kernels.cu (every instantiation of gemm_tcgen05_kernel
+// for sm_100a), linked into the library as data.
+extern "C" const unsigned char rb_gemm_cubin_start[];
+extern "C" const unsigned char rb_gemm_cubin_end[];
+
+extern "C" RbStatus rbGetKernelBinary(const void** image, size_t* size) {
+  if (!image && !size) return rb::fail(RB_INVALID_PARAM, "image and size are both NULL");
+  if (image) *image = rb_gemm_cubin_start;
+  if (size) *size = (size_t)(rb_gemm_cubin_end - rb_gemm_cubin_start);
+  return RB_SUCCESS;
+}
+
+extern "C" RbStatus rbGemmEncodeLaunch(const RbGemmProblem* p, const RbEpilogue* epi, const void* a, const void* b, void* c,
+                                       RbKernelLaunch* out) {
+  if (!out) return rb::fail(RB_INVALID_PARAM, "out is NULL");
+  return rb::gemm_run(p, epi, a, b, c, nullptr, 0, nullptr, nullptr, out);
 }
 
 // ---- rbGemmNoAlloc ------------------------------------------------------------------------------------

@@ -56,8 +56,11 @@ struct ConvAOperand {
   int pad_h_hi, pad_w_hi;    // upper paddings (bounding box of the base pixel)
 };
 // rbGemm with an optional implicit operand (then `a` (or `b`) is ignored, trans_a (trans_b) must be 0, g must be 1).
+// With `capture` nothing is launched: the call prepares everything as usual and writes the one kernel launch it
+// would make (symbol in the library's cubin, grid, block, cluster, shared memory, parameter block) into `capture`;
+// it fails with RB_UNSUPPORTED when the operation needs more than that one kernel (operand copies, a K split).
 RbStatus gemm_run(const RbGemmProblem* p, const RbEpilogue* epi, const void* a, const void* b, void* c, void* workspace,
-                  size_t workspace_bytes, void* stream, const ConvAOperand* conva);
+                  size_t workspace_bytes, void* stream, const ConvAOperand* conva, RbKernelLaunch* capture = nullptr);
 
 // rbGemmWorkspaceSize when operand `implicit_operand` (0 = A, 1 = B, -1 = none) is fetched in place by im2col loads
 // and therefore needs neither a pitched copy nor TF32 planes inside the GEMM's own workspace.
@@ -73,7 +76,7 @@ RbStatus f32_planes(const float* src, float* hi, float* lo, int groups, int R, i
 // channel by the GEMM that ends the convolution).
 size_t conv_workspace_bytes(const RbConvProblem* p, int result_type);
 RbStatus conv_run(const RbConvProblem* p, int result_type, void* filter, void* input, void* output, void* workspace,
-                  size_t workspace_bytes, void* stream, const RbEpilogue* epi = nullptr);
+                  size_t workspace_bytes, void* stream, const RbEpilogue* epi = nullptr, RbKernelLaunch* capture = nullptr);
 
 // cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per (device, kernel, size): the call costs microseconds and
 // small problems are bound by the host's launch path.

@@ -139,6 +139,21 @@ extern "C" MiirStatus miirBufferGet(MiirHandle handle, char* buffer, size_t* siz
   Handle* h = static_cast<Handle*>(handle);
   if (!h) return MIIR_INVALID_PARAM;
   if (!h->binary) return MIIR_INVALID_MODULE;
+  if (h->d.kind == kAttention) return MIIR_BUILD_FAILURE;   // the attention kernels are not part of the cubin image
+  const void* image = nullptr;
+  size_t bytes = 0;
+  if (rbGetKernelBinary(&image, &bytes) != RB_SUCCESS) return MIIR_BUILD_FAILURE;
+  if (buffer) memcpy(buffer, image, bytes);
+  if (size) *size = bytes;
+  return MIIR_SUCCESS;
+}
+
+extern "C" MiirStatus miirDescriptorGet(MiirHandle handle, char* buffer, size_t* size) {
+  const std::lock_guard<std::mutex> lock(g_miir_mutex);
+  if (!buffer && !size) return MIIR_INVALID_PARAM;
+  Handle* h = static_cast<Handle*>(handle);
+  if (!h) return MIIR_INVALID_PARAM;
+  if (!h->binary) return MIIR_INVALID_MODULE;
   if (!buffer) {
     *size = sizeof(LaunchDescriptor);
   } else {
@@ -146,6 +161,25 @@ extern "C" MiirStatus miirBufferGet(MiirHandle handle, char* buffer, size_t* siz
     if (size) *size = sizeof(LaunchDescriptor);
   }
   return MIIR_SUCCESS;
+}
+
+extern "C" MiirStatus miirGetKernelLaunch(MiirHandle handle, void* arg0, void* arg1, void* arg2, RbKernelLaunch* out) {
+  Handle* h = static_cast<Handle*>(handle);
+  if (!h || !out) return MIIR_INVALID_PARAM;
+  LaunchDescriptor d;
+  {
+    const std::lock_guard<std::mutex> lock(g_miir_mutex);
+    if (!h->binary) return MIIR_INVALID_MODULE;
+    d = h->d;
+  }
+  RbStatus st = RB_UNSUPPORTED;
+  const int saved_variant = rbGetGemmVariant();
+  rbSetGemmVariant((int)d.variant);
+  if (d.kind == kConv) st = rbConvEncodeLaunch(&d.conv, nullptr, -1, arg0, arg1, arg2, out);
+  else if (d.kind == kGemm) st = rbGemmEncodeLaunch(&d.gemm, nullptr, arg0, arg1, arg2, out);
+  rbSetGemmVariant(saved_variant);
+  if (st == RB_SUCCESS) return MIIR_SUCCESS;
+  return st == RB_INVALID_PARAM ? MIIR_INVALID_PARAM : MIIR_BUILD_FAILURE;
 }
 
 extern "C" MiirStatus miirGetExecutionDims(MiirHandle handle, size_t* global_size, size_t* local_size) {

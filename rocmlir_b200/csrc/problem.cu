@@ -259,16 +259,58 @@ bool parse_attention(const std::map<std::string, std::string>& m, ProblemDesc* h
 
 }  // namespace
 
+// Strings of the reference's accelerated GEMM / convolution parameters (Serializable.h:64-131, RockAttrDefs.td:300-434):
+//   v2:MPerBlock,NPerBlock,KpackPerBlock,MPerWave,NPerWaveOrMnPerXdl,KPack,SplitKFactor,ForceUnroll,ThreadCopyMore
+// and the un-prefixed version 1 with the same fields minus SplitKFactor. They describe an MFMA tiling; what carries
+// over to this hardware is the block tile and the K split: MPerBlock picks one CTA (<= 128 rows) or a CTA pair,
+// NPerBlock the nearest tile width not below it (64 / 128 / 256), SplitKFactor is honoured as given; the wave-level
+// fields have no counterpart and are only checked for sanity. Anything else fails applicability.
+static bool reference_perf_config_to_variant(const char* str, uint32_t* variant) {
+  const bool v2 = strncmp(str, "v2:", 3) == 0;
+  const char* body = v2 ? str + 3 : str;
+  int f[9] = {0, 0, 0, 0, 0, 0, 1, 0, 0}, n = 0;
+  const char* q = body;
+  while (n < 9) {
+    char* end = nullptr;
+    const long v = strtol(q, &end, 10);
+    if (end == q || v < 0 || v > (1 << 20)) return false;
+    f[n++] = (int)v;
+    if (*end == '\0') break;
+    if (*end != ',') return false;
+    q = end + 1;
+    if (n == 9) return false;   // a tenth field
+  }
+  if (v2 ? (n < 7 || n > 9) : n != 8) return false;   // Serializable.h:72-80: six to eight commas for v2
+  if (!v2) { f[8] = f[7]; f[7] = f[6]; f[6] = 1; }     // version 1 has no SplitKFactor
+  const int m_per_block = f[0], n_per_block = f[1], kpack_per_block = f[2], kpack = f[5], split_k = f[6];
+  if (m_per_block <= 0 || n_per_block <= 0 || kpack_per_block <= 0 || kpack <= 0 || split_k <= 0 || split_k > 255) return false;
+  if (m_per_block > 256 || n_per_block > 256) return false;
+  const uint32_t ctas = m_per_block <= 128 ? 1u : 2u;
+  const uint32_t bn_code = n_per_block <= 64 ? 1u : n_per_block <= 128 ? 2u : 3u;
+  *variant = ctas | (bn_code << 12) | ((uint32_t)split_k << 16);
+  return true;
+}
+
 bool perf_config_to_variant(const char* str, uint32_t* variant) {
   if (!str || !variant) return false;
-  int tm = 0, tn = 0, stages = 0, splits = 0, sk = 0;
+  if (strncmp(str, "b200:", 5) != 0) return reference_perf_config_to_variant(str, variant);
+  int tm = 0, tn = 0, stages = 0, splits = 0, sk = 0, kpr = 0;
   char tail = 0;
-  if (sscanf(str, "v1:%d,%d,%d,%d,%d%c", &tm, &tn, &stages, &splits, &sk, &tail) != 5) return false;
+  const int got = sscanf(str, "b200:%d,%d,%d,%d,%d,%d%c", &tm, &tn, &stages, &splits, &sk, &kpr, &tail);
+  if (got != 5 && got != 6) return false;
+  if (got == 5) {   // a sixth field must not be half there ("...,0," or trailing junk)
+    int commas = 0;
+    for (const char* c = str; *c; ++c) commas += *c == ',';
+    const char last = str[strlen(str) - 1];
+    if (commas != 4 || last < '0' || last > '9') return false;
+  }
   if (!(tm == 128 || tm == 256) || !(tn == 64 || tn == 128 || tn == 256)) return false;
   if (stages < 0 || stages > 15 || splits < 0 || splits > 255 || !(sk == 0 || sk == 1)) return false;
+  if (!(kpr == 0 || kpr == 1 || kpr == 2 || kpr == 4)) return false;
   const uint32_t bn_code = tn == 64 ? 1u : tn == 128 ? 2u : 3u;
+  const uint32_t kpr_code = kpr == 0 ? 0u : kpr == 1 ? 1u : kpr == 2 ? 2u : 3u;
   *variant = (tm == 256 ? 2u : 1u) | ((uint32_t)stages << 4) | ((uint32_t)sk << 9) | (bn_code << 12) |
-             ((uint32_t)splits << 16);
+             ((uint32_t)splits << 16) | (kpr_code << 28);
   return true;
 }
 
@@ -276,9 +318,11 @@ std::string variant_to_perf_config(uint32_t v) {
   const int ctas = (v & 0xF) == 1 ? 1 : 2;
   const int bn_code = (v >> 12) & 0xF;
   const int tn = bn_code == 1 ? 64 : bn_code == 2 ? 128 : 256;
+  const int kpr_code = (v >> 28) & 3;
   char buf[64];
-  snprintf(buf, sizeof(buf), "v1:%d,%d,%d,%d,%d", ctas == 2 ? 256 : 128, tn, (int)((v >> 4) & 0xF), (int)((v >> 16) & 0xFF),
-           (int)((v >> 9) & 1));
+  int len = snprintf(buf, sizeof(buf), "b200:%d,%d,%d,%d,%d", ctas == 2 ? 256 : 128, tn, (int)((v >> 4) & 0xF),
+                     (int)((v >> 16) & 0xFF), (int)((v >> 9) & 1));
+  if (kpr_code) snprintf(buf + len, sizeof(buf) - len, ",%d", kpr_code == 1 ? 1 : kpr_code == 2 ? 2 : 4);
   return buf;
 }
 

@@ -32,10 +32,12 @@ bool parse_problem(const char* options, ProblemDesc* out);
 // Recomputes `workspace` after `variant` changed. False if the variant is not usable for the problem.
 bool refresh_problem(ProblemDesc* d);
 
-// perf_config strings of this library: "v1:<tile_m>,<tile_n>,<stages>,<splitK>,<streamK>" with tile_m 128 (one
-// CTA) or 256 (CTA pair), tile_n 64 / 128 / 256, stages 0 = deepest ring that fits, splitK >= 1 (0 = the
-// library's rule), streamK 0 / 1 - the role of the reference's "v2:..." strings
-// (mlir/include/mlir/Dialect/Rock/Tuning/GridwiseGemmParams.h:138-194, Serializable.h:37-131).
+// perf_config strings of this library: "b200:<tile_m>,<tile_n>,<stages>,<splitK>,<streamK>[,<kpr>]" with tile_m 128
+// (one CTA) or 256 (CTA pair), tile_n 64 / 128 / 256, stages 0 = deepest ring that fits, splitK >= 1 (0 = the
+// library's rule), streamK 0 / 1, kpr = K blocks per barrier round (1 / 2 / 4; absent or 0 = the library's rule).
+// The reference's own strings - "v2:M,N,KpackPerBlock,MPerWave,NPerWave,KPack,SplitK,ForceUnroll,ThreadCopyMore" and
+// the un-prefixed version 1 (mlir/include/mlir/Dialect/Rock/Tuning/GridwiseGemmParams.h:138-194,
+// Serializable.h:37-131) - are accepted too and mapped onto the nearest tile with the K split honoured.
 bool perf_config_to_variant(const char* str, uint32_t* variant);
 std::string variant_to_perf_config(uint32_t variant);
 

@@ -90,7 +90,7 @@ void build_space(const ProblemDesc& d, RbTuningParamSetKind kind, Space* sp) {
     // attention has one kernel configuration
     Param p;
     p.variant = 0;
-    p.text = "v1:attention";
+    p.text = "b200:attention";
     sp->params.push_back(p);
     sp->quick.push_back(p);
     return;
@@ -217,7 +217,7 @@ double work_imbalance(int64_t g, int64_t m, int64_t n, int64_t tile_m, int64_t t
 
 bool set_variant(ProblemDesc* d, uint32_t variant, const std::string& text) {
   if (d->kind == kAttention) {
-    if (text != "v1:attention") return false;
+    if (text != "b200:attention") return false;
     d->perf_config = text;
     return true;
   }
@@ -441,7 +441,7 @@ bool rbIsProblemFusible(RbProblem problem, const char* perfStr, size_t perfLen) 
   if (!problem.ptr || !perfStr) return false;
   const ProblemDesc* d = static_cast<ProblemDesc*>(problem.ptr);
   const std::string text(perfStr, perfLen);
-  if (d->kind == kAttention) return text == "v1:attention";
+  if (d->kind == kAttention) return text == "b200:attention";
   uint32_t v = 0;
   return perf_config_to_variant(text.c_str(), &v);
 }

@@ -62,17 +62,33 @@ class Handle:
         if st != SUCCESS:
             raise MiirError(st, "miirLowerBin")
 
-    def buffer(self) -> bytes:
-        """Two-call protocol: size first, then the bytes."""
+    def _two_call(self, fn, what: str) -> bytes:
         size = C.c_size_t(0)
-        st = L.lib().miirBufferGet(self._h, None, C.byref(size))
+        st = fn(self._h, None, C.byref(size))
         if st != SUCCESS:
-            raise MiirError(st, "miirBufferGet(size)")
+            raise MiirError(st, what + "(size)")
         buf = C.create_string_buffer(size.value)
-        st = L.lib().miirBufferGet(self._h, buf, C.byref(size))
+        st = fn(self._h, buf, C.byref(size))
         if st != SUCCESS:
-            raise MiirError(st, "miirBufferGet(copy)")
+            raise MiirError(st, what + "(copy)")
         return buf.raw[: size.value]
+
+    def buffer(self) -> bytes:
+        """The code object (an sm_100a cubin). Two-call protocol: size first, then the bytes."""
+        return self._two_call(L.lib().miirBufferGet, "miirBufferGet")
+
+    def descriptor(self) -> bytes:
+        """The relocatable launch descriptor for launch_from_buffer."""
+        return self._two_call(L.lib().miirDescriptorGet, "miirDescriptorGet")
+
+    def kernel_launch(self, arg0, arg1, arg2) -> "L.RbKernelLaunch":
+        """Name, cluster size, shared memory and parameter block of the handle's kernel for these device buffers."""
+        out = L.RbKernelLaunch()
+        ptr = lambda t: None if t is None else t.data_ptr()
+        st = L.lib().miirGetKernelLaunch(self._h, ptr(arg0), ptr(arg1), ptr(arg2), C.byref(out))
+        if st != SUCCESS:
+            raise MiirError(st, "miirGetKernelLaunch (" + L.lib().rbGetLastError().decode() + ")")
+        return out
 
     def execution_dims(self) -> Tuple[int, int]:
         g, l = C.c_size_t(0), C.c_size_t(0)

@@ -146,7 +146,11 @@ def test_lowering_state_machine_and_buffer_protocol():
         h.lower_tuning_params()
         assert lib.miirBufferGet(h._h, None, C.byref(size)) == miir.INVALID_MODULE             # tuned, but no binary
         h.lower_bin()
-        blob = h.buffer()
+        # the code object is an ELF image (the sm_100a cubin), as the reference's is an ELF hsaco
+        assert lib.miirBufferGet(h._h, None, C.byref(size)) == miir.SUCCESS and size.value > 1 << 20
+        image = h.buffer()
+        assert image[:4] == b"\x7fELF" and len(image) == size.value
+        blob = h.descriptor()
         assert blob[:7] == b"RB2KDSC" and len(blob) > 64
         assert lib.miirGetExecutionDims(h._h, None, C.byref(l)) == miir.INVALID_PARAM
         # a descriptor with a damaged header is refused before anything is launched
@@ -156,13 +160,21 @@ def test_lowering_state_machine_and_buffer_protocol():
 
 
 def test_perf_config_selects_the_tile():
-    with miir.Handle(opts(extra="--perf_config v1:128,128,0,1,0")) as h:
+    with miir.Handle(opts(extra="--perf_config b200:128,128,0,1,0")) as h:
         h.lower_tuning_params()
         g_small, _ = h.execution_dims()
-    with pytest.raises(ValueError):
-        miir.Handle(opts(extra="--perf_config v2:64,64,8,32,32,8,1,1,1"))     # the reference's own grammar is foreign here
-    with pytest.raises(ValueError):
-        miir.Handle(opts(extra="--perf_config v1:100,128,0,1,0"))
+    # the reference's own strings are accepted and mapped onto the nearest tile (MPerBlock <= 128: one CTA per tile;
+    # NPerBlock 64 -> 64-column tiles), here the one of mlir/test/CAPI/mixr_split_k.cpp:351
+    with miir.Handle(opts(extra="--perf_config v2:64,64,16,32,32,4,1,1,1")) as h:
+        h.lower_tuning_params()
+        g_ref, l_ref = h.execution_dims()
+        assert l_ref == 256 and g_ref > 0
+    with miir.Handle(opts(extra="--perf_config 128,128,8,64,64,8,1,1")) as h:      # version 1: un-prefixed, no split field
+        h.lower_tuning_params()
+    for bad in ("b200:100,128,0,1,0", "v2:64,64,16", "v2:64,64,16,32,32,4,0,1,1", "v2:64,x,16,32,32,4,1,1,1",
+                "v2:512,64,16,32,32,4,1,1,1", "v1:128,128,0,1,0", "64,64,16,32,32,4,1,1,1,1"):
+        with pytest.raises(ValueError):     # unmappable strings fail applicability (a NULL handle), they do not crash
+            miir.Handle(opts(extra="--perf_config " + bad))
     assert g_small > 0
 
 

@@ -36,7 +36,7 @@ def test_conv_through_the_handle_api(cuda_device, op, direction, layout, via):
         if via == "handle":
             h.launch(t["fil"], t["in"], t["out"], workspace=ws)
         else:
-            blob = h.buffer()
+            blob = h.descriptor()
     if via == "buffer":   # the handle is gone: the descriptor alone is enough
         miir.launch_from_buffer(blob, t["fil"], t["in"], t["out"], workspace=ws)
     torch.cuda.synchronize()

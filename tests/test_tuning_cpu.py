@@ -64,7 +64,7 @@ def test_split_k_likelihood_examples_of_the_reference():
 def test_spaces_and_param_strings():
     p = tuning.Problem("--operation gemm --arch sm_100a -t f16 -m 4096 -n 4096 -k 4096")
     quick, full, exhaustive = p.space(tuning.QUICK), p.space(tuning.FULL), p.space(tuning.EXHAUSTIVE)
-    assert quick[0] == "v1:256,256,0,1,0"                 # the library's own choice comes first
+    assert quick[0] == "b200:256,256,0,1,0"                 # the library's own choice comes first
     assert 1 < len(quick) < len(full) < len(exhaustive)
     assert set(quick) <= set(full)
     assert p.quick_space() == quick                        # GetQuick on a full space
@@ -74,12 +74,12 @@ def test_spaces_and_param_strings():
         assert p.perf_config == s
     # a skinny problem: tiles that would be at least half empty are not offered, K splits are
     skinny = tuning.Problem("--operation gemm --arch sm_100a -t f16 -m 64 -n 64 -k 8192")
-    assert all(s.startswith("v1:128,64,") for s in skinny.space(tuning.FULL))
+    assert all(s.startswith("b200:128,64,") for s in skinny.space(tuning.FULL))
     assert any(int(s.split(",")[3]) > 1 for s in skinny.space(tuning.FULL))
-    assert not skinny.set_from_str("v1:128,64,0,200,0")     # more K ranges than the library will make
-    assert not p.set_from_str("v1:256,256,0,1")           # malformed
+    assert not skinny.set_from_str("b200:128,64,0,200,0")     # more K ranges than the library will make
+    assert not p.set_from_str("b200:256,256,0,1")           # malformed
     assert not p.set_from_str("garbage")
-    assert p.is_fusible("v1:256,256,0,4,0") and not p.is_fusible("nonsense")
+    assert p.is_fusible("b200:256,256,0,4,0") and not p.is_fusible("nonsense")
     assert p.num_prefill_args == 0 and p.num_aux_buffers == 0
 
 
@@ -87,20 +87,20 @@ def test_table_keeps_the_fastest_entry_and_is_shareable():
     p = tuning.Problem("--operation gemm --arch sm_100a -t f16 -m 4096 -n 4096 -k 4096")
     t = tuning.Table()
     assert not p.set_from_table(t)                          # empty table
-    assert t.update(p.key, "v1:256,128,0,1,0", 2.0)
-    assert not t.update(p.key, "v1:128,128,0,1,0", 3.0)     # slower: rejected
-    assert t.update(p.key, "v1:256,256,0,1,0", 1.0)         # faster: replaces
-    assert p.set_from_table(t) and p.perf_config == "v1:256,256,0,1,0"
+    assert t.update(p.key, "b200:256,128,0,1,0", 2.0)
+    assert not t.update(p.key, "b200:128,128,0,1,0", 3.0)     # slower: rejected
+    assert t.update(p.key, "b200:256,256,0,1,0", 1.0)         # faster: replaces
+    assert p.set_from_table(t) and p.perf_config == "b200:256,256,0,1,0"
     other = tuning.Problem("--operation gemm --arch sm_100a -t f16 -m 512 -n 512 -k 512")
     assert not other.set_from_table(t)
 
     def writer(i):
         for j in range(200):
-            t.update(f"key{j % 7}", "v1:256,256,0,1,0", float(1000 - i - j))
+            t.update(f"key{j % 7}", "b200:256,256,0,1,0", float(1000 - i - j))
     threads = [threading.Thread(target=writer, args=(i,)) for i in range(4)]
     [th.start() for th in threads]
     [th.join() for th in threads]
-    assert not t.update("key0", "v1:256,256,0,1,0", 5000.0)
+    assert not t.update("key0", "b200:256,256,0,1,0", 5000.0)
 
 
 def test_get_config_reports_the_launch():

@@ -71,7 +71,8 @@ def test_no_alloc_carries_the_fused_epilogue(cuda_device):
     (af, araw), (bf, braw) = reference_random([(g, m, k), (g, k, n)], oracle.F16, seed=1)
     bias = (np.arange(n, dtype=np.float32) % 9) - 4
     a, b = to_device(araw, oracle.F16), to_device(braw, oracle.F16)
-    epi = Epilogue(bias=to_device(oracle.from_f32(bias, oracle.F16), oracle.F16), relu=True, mid_type=oracle.F16).to_c()
+    bias_dev = to_device(oracle.from_f32(bias, oracle.F16), oracle.F16)     # kept alive: the C struct only holds its address
+    epi = Epilogue(bias=bias_dev, relu=True, mid_type=oracle.F16).to_c()
     ws = torch.empty(need, dtype=torch.uint8, device="cuda")
     want = torch.empty((g, m, n), dtype=torch.float16, device="cuda")
     _run("workspace", prob, a, b, want, ws, epi)
