@@ -1,13 +1,15 @@
-"""A test driver with rocmlir-gen's command line: generate the inputs the way `rocmlir-gen -ph -pv -rand N` does,
-run the operation on the GPU through the library, run the CPU restatement of the reference's validator, compare
-with the reference's verifier and thresholds, and print the verdict line `[1 1 1]`
+"""The validation harness behind the `rocmlir-gen` / `rocmlir-driver` tools of this repository (oracle/bin/): takes
+rocmlir-gen's command line, generates the inputs the way `rocmlir-gen -ph -pv -rand N` does, runs the operation on
+the GPU through the library, runs the CPU restatement of the reference's validator, compares with the reference's
+verifier and thresholds, and gives the verdict line `[1 1 1]`
 (mlir/tools/rocmlir-gen/rocmlir-gen.cpp:73-785 flags, :996-1092 defaults, :837-972 layout and padding fix-ups,
-:1325-1486 data fill, :2696-2886 verification). It replaces the reference's pipeline
-`rocmlir-gen ... -pv | rocmlir-driver -c | mlir-cpu-runner` for the tests of this repository.
+:1325-1486 data fill, :2696-2886 verification). It stands in for the reference's pipeline
+`rocmlir-gen ... -pv | rocmlir-driver -c | mlir-cpu-runner`:
 
-    python tests/rocmlir_gen.py --operation gemm -t f16 -g 3 -m 1024 -k 769 -n 1024 --arch sm_100a -pv -rand 1
+    oracle/bin/rocmlir-gen --operation gemm -t f16 -g 3 -m 1024 -k 769 -n 1024 --arch sm_100a -pv -rand 1 | oracle/bin/rocmlir-driver -c
 
-This file is test infrastructure: it is the only place where the library and the oracle meet.
+CHECKER-SIDE infrastructure like the rest of oracle/: the one place where the library and the oracle meet. The product
+package never imports it.
 """
 from __future__ import annotations
 
@@ -19,10 +21,31 @@ from typing import Dict, List, Optional
 import numpy as np
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
-sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 import oracle  # noqa: E402
-from helpers import from_device, to_device  # noqa: E402
+
+
+def _torch_dtype(code):
+    import torch
+    return {oracle.F32: torch.float32, oracle.F16: torch.float16, oracle.BF16: torch.bfloat16, oracle.I8: torch.int8,
+            oracle.I32: torch.int32, oracle.F8E4M3: torch.float8_e4m3fn, oracle.F8E5M2: torch.float8_e5m2}[code]
+
+
+def to_device(raw: np.ndarray, code: int, device="cuda"):
+    """Raw storage bits (as produced by oracle.from_f32) -> torch tensor of the matching dtype."""
+    import torch
+    t = torch.from_numpy(np.ascontiguousarray(raw).view(np.int16) if raw.dtype == np.uint16 else np.ascontiguousarray(raw))
+    return t.to(device).view(_torch_dtype(code))
+
+
+def from_device(t, code: int) -> np.ndarray:
+    """Torch tensor -> raw storage bits as numpy."""
+    import torch
+    if code in (oracle.F16, oracle.BF16):
+        return t.contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+    if code in (oracle.F8E4M3, oracle.F8E5M2):
+        return t.contiguous().view(torch.uint8).cpu().numpy()
+    return t.contiguous().cpu().numpy()
 
 
 class Unsupported(Exception):

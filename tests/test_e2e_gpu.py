@@ -1,5 +1,5 @@
 """The reference's end-to-end matrices (mlir/test/e2e/*.toml, expanded by tests/golden/make_e2e_configs.py into
-tests/golden/e2e_configs.json) run through tests/rocmlir_gen.py: every command line must end in the verdict
+tests/golden/e2e_configs.json) run through oracle/harness.py: every command line must end in the verdict
 `[1 1 1]`, exactly what the reference's generated lit tests CHECK for.
 
 By default the PR suites run in full and every 4th line of the large regression matrices; set RB_E2E_ALL=1 to run
@@ -9,7 +9,7 @@ import os
 
 import pytest
 
-import rocmlir_gen
+from oracle import harness as rocmlir_gen
 
 pytestmark = pytest.mark.gpu
 
@@ -34,3 +34,22 @@ def test_reference_e2e_line_gives_111(cuda_device, case):
     except rocmlir_gen.Unsupported as e:
         pytest.skip(f"no kernel: {e}")
     assert verdict == [1, 1, 1], case["flags"]
+
+
+@pytest.mark.parametrize("line", [
+    "--operation gemm -t f16 -g 3 -m 1024 -k 769 -n 1024 --arch sm_100a -ph -pv -rand 1",
+    "--operation conv -t f16 --fil_layout gkyxc --in_layout nhwgc --out_layout nhwgk --batchsize 4 --in_channels 64 "
+    "--out_channels 64 --in_h 14 --in_w 14 --fil_h 3 --fil_w 3 --padding_h 1 --padding_w 1 --arch sm_100a -ph -pv -rand 1",
+    "--operation attention -t f16 -seq_len_q 256 -seq_len_k 256 -head_dim_qk 64 -head_dim_v 64 --arch sm_100a -ph -pv -rand 1 "
+    "-rand_type float -RMS_threshold 0.015 -absDiff_threshold 0.02",
+])
+def test_tools_pipeline_prints_the_verdict(cuda_device, line):
+    """`rocmlir-gen <flags> -ph -pv | rocmlir-driver -c` with this repository's tools of those names."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    gen = subprocess.run([sys.executable, os.path.join(root, "oracle", "bin", "rocmlir-gen")] + line.split(),
+                         capture_output=True, text=True, check=True)
+    drv = subprocess.run([sys.executable, os.path.join(root, "oracle", "bin", "rocmlir-driver"), "-c"], input=gen.stdout,
+                         capture_output=True, text=True, timeout=600)
+    assert drv.returncode == 0 and drv.stdout.strip().endswith("[1 1 1]"), drv.stdout + drv.stderr
