@@ -15,7 +15,7 @@ import tomllib
 FILES = ["PrGemm.toml", "PrGemmSplitK.toml", "PrResnet50.toml", "PrAttentionF16.toml", "PrAttentionI8.toml", "PrAttentionF32.toml",
          "PaddedGemmConfig.toml",
          "GemmVariants.toml", "MixedConvLayouts.toml", "conv_regression_fwd.toml", "conv_regression_bwd.toml",
-         "gemm_split_k_f16.toml", "gemm_split_k_f32.toml", "conv_wrw_perf_config.toml"]
+         "gemm_split_k_f16.toml", "gemm_split_k_f32.toml", "conv_wrw_perf_config.toml", "gemm_with_atomic_add.toml"]
 
 # lit substitutions of the reference's default configuration (mlir/test/e2e/lit.site.cfg.py.in:22-23,
 # mlir/test/lit.cfg.py:35-38): validation on the CPU, random data seed 1

@@ -15,7 +15,7 @@ pytestmark = pytest.mark.gpu
 
 CASES = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "e2e_configs.json")))["cases"]
 FULL_FILES = {"PrGemm.toml", "PrGemmSplitK.toml", "PrResnet50.toml", "PrAttentionF16.toml", "PrAttentionI8.toml", "PrAttentionF32.toml", "gemm_split_k_f16.toml",
-              "gemm_split_k_f32.toml", "conv_wrw_perf_config.toml"}
+              "gemm_split_k_f32.toml", "conv_wrw_perf_config.toml", "gemm_with_atomic_add.toml"}
 
 
 def selected():

@@ -26,7 +26,7 @@ def test_every_line_plans():
 
 def test_fixture_covers_the_suites():
     files = collections.Counter(c["file"] for c in CASES)
-    assert len(CASES) == 1371
+    assert len(CASES) == 1375 and files["gemm_with_atomic_add.toml"] == 4
     for name in ("PrGemm.toml", "PrResnet50.toml", "PrAttentionF16.toml", "PrAttentionI8.toml", "PrAttentionF32.toml",
                  "conv_regression_fwd.toml", "conv_regression_bwd.toml", "MixedConvLayouts.toml"):
         assert files[name] > 0, name
