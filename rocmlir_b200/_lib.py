@@ -71,7 +71,9 @@ class RbGemmConfigInfo(C.Structure):
 class RbKernelLaunch(C.Structure):
     _fields_ = [("symbol", C.c_char * 160), ("grid", C.c_uint32), ("block", C.c_uint32), ("cluster", C.c_uint32),
                 ("dynamic_smem", C.c_uint32), ("param_count", C.c_uint32), ("param_offset", C.c_uint32 * 4),
-                ("param_size", C.c_uint32 * 4), ("reserved", C.c_uint32 * 3), ("params", C.c_ubyte * 2048)]
+                ("param_size", C.c_uint32 * 4), ("reserved", C.c_uint32 * 3),
+                ("_pad", C.c_ubyte * 32),      # the C struct aligns `params` to 64 bytes: offset 256
+                ("params", C.c_ubyte * 2048)]
 
 
 class _Handle(C.Structure):

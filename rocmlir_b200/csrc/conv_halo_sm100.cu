@@ -1,0 +1,269 @@
+// Unit-stride NHWC convolution (forward, and backward data as a forward convolution of the output gradient with
+// mirrored taps) as an implicit GEMM that reads every input pixel from L2 ONCE per output tile.
+//
+// rocMLIR's implicit GEMM (ConvRewritePattern, mlir/lib/Dialect/Rock/Transforms/ConvToGemm.cpp:1133-1400) views the
+// input through a pad -> embed -> merge coordinate map, so every filter tap re-reads its shifted window; the im2col-TMA
+// form of this library (gemm_sm100.cuh) does the same and is bound by the L2 -> SM fabric for 3x3 filters (nine 16 KB
+// tiles per 128 x 64 output tile). This kernel loads the tile's input window WITH ITS HALO once per 64-channel block:
+//
+//   * an output tile is R whole output rows of one image, indexed on the padded raster m = r * Wp + q with
+//     Wp = Q + (X - 1) * dil_w (the columns q >= Q of a row are computed and thrown away); R * Wp <= 128;
+//   * one TMA tiled load of the box {64 channels, Wp, R + (Y - 1) * dil_h, 1} starting at (w, h) = (-pad_w, p0 - pad_h)
+//     puts the window into shared memory as [rows][Wp] pixels of 128 bytes, zero outside the image (the padding);
+//   * on that raster the A operand of tap (y, x) is the SAME buffer shifted by y * dil_h * Wp + x * dil_w pixel rows:
+//     a K-major 128-byte-swizzled tile whose start address is not on a 1024-byte boundary. The tensor core applies the
+//     swizzle to absolute shared-memory address bits, exactly as the TMA engine did when it wrote the window, so the
+//     shifted start address alone is enough: the descriptor's base-offset field stays 0 (measured on B200: results
+//     are exact that way, and wrong when the field is set to the start's row phase);
+//   * the filter matrix B[k][(y, x, c)] stays resident in shared memory for all tiles of the persistent CTA.
+// Per tile the tensor pipe sees the same Y * X * C / 16 MMAs as before, but L2 -> SM traffic drops from
+// Y * X * (16 + N / 8) KB to about (R + Y - 1) * Wp / 8 KB per channel block.
+//
+// Roles, barriers, TMEM double buffering and bounded waits are those of gemm_tcgen05_kernel.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <string>
+
+#include "epilogue.cuh"
+#include "lib_state.h"
+#include "ptx.cuh"
+
+namespace rb {
+namespace {
+
+constexpr int kHaloThreads = 256;
+constexpr int kHaloMaxStages = 6;
+
+struct HaloMaps {
+  CUtensorMap in;    // {C, W, H, N} of the NHWC image tensor, box {64, Wp, rows_box, 1}
+  CUtensorMap fil;   // {Y * X * C, Kout, 1} of the K-major filter matrix, box {64, Kout, 1}
+};
+
+struct HaloParams {
+  int N, P, Q, Kout, cchunks;       // output image P x Q with Kout channels; input channels = cchunks * 64
+  int Y, X, dil_h, dil_w, pad_h, pad_w;
+  int Wp, R, rows_box;              // padded raster width, output rows per tile, input rows per box
+  int tiles_per_img, num_tiles;
+  int stage_bytes, stages;
+  int b_tile_bytes, b_tiles;        // one (tap, channel block) slab of the filter: Kout rows of 128 bytes
+  uint32_t idesc;
+  int is_bf16;
+  void* out;                        // [N][P][Q][Kout], 16-bit elements
+  long long o_n, o_p, o_q;          // element strides of the output pixel (n, p, q)
+  uint32_t* status;
+  long long wait_cycles;
+};
+
+__global__ void __launch_bounds__(kHaloThreads, 1)
+conv_halo_kernel(const __grid_constant__ HaloMaps maps, const HaloParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // [A ring: stages * stage_bytes][slack: rows that shifted descriptors may touch past the last stage][B][barriers]
+  const int slack = 160 * 128;
+  uint8_t* b_smem = smem + p.stages * p.stage_bytes + slack;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(b_smem + p.b_tiles * p.b_tile_bytes);
+  uint64_t* full_bar = bars;                      // [stages]
+  uint64_t* empty_bar = bars + kHaloMaxStages;    // [stages]
+  uint64_t* tfull_bar = bars + 2 * kHaloMaxStages;       // [2]
+  uint64_t* tempty_bar = bars + 2 * kHaloMaxStages + 2;  // [2]
+  uint64_t* bfull_bar = bars + 2 * kHaloMaxStages + 4;   // [1]
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * kHaloMaxStages + 5);
+  const int warp = threadIdx.x >> 5;
+  const long long wait_limit = p.wait_cycles;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&tfull_bar[b], 1); mbar_init(&tempty_bar[b], 4); }
+    mbar_init(bfull_bar, 1);
+    fence_mbar_init();
+  }
+  if (warp == 2) {
+    tmem_alloc<1>(tmem_holder, 512);
+    tmem_relinquish<1>();
+  }
+  if (warp == 0 && lane_id() == 0) { prefetch_tmap(&maps.in); prefetch_tmap(&maps.fil); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ------------------------------ producer ------------------------------
+    if (lane_id() == 0) {
+      // the filter, once: slab (tap, cc) = Kout rows x 64 channels
+      mbar_expect_tx(bfull_bar, (uint32_t)(p.b_tiles * p.b_tile_bytes));
+      for (int j = 0; j < p.b_tiles; ++j) tma_load_3d(b_smem + (size_t)j * p.b_tile_bytes, &maps.fil, bfull_bar, j * 64, 0, 0);
+      uint32_t s = 0, ph = 0;
+      bool ok = true;
+      const uint32_t box_bytes = (uint32_t)(p.Wp * p.rows_box * 128);
+      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+        const int n = tile / p.tiles_per_img;
+        const int p0 = (tile - n * p.tiles_per_img) * p.R;
+        for (int cc = 0; cc < p.cchunks; ++cc) {
+          if (!mbar_wait(&empty_bar[s], ph ^ 1u, p.status, kStatusTimeoutProducer + s, wait_limit)) { ok = false; break; }
+          mbar_expect_tx(&full_bar[s], box_bytes);
+          tma_load_4d(smem + (size_t)s * p.stage_bytes, &maps.in, &full_bar[s], cc * 64, -p.pad_w, p0 - p.pad_h, n);
+          if (++s == (uint32_t)p.stages) { s = 0; ph ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane_id() == 0) {
+      bool ok = mbar_wait(bfull_bar, 0, p.status, kStatusTimeoutMma + 0x20, wait_limit);
+      uint32_t s = 0, ph = 0, t = 0;
+      const uint32_t desc_hi0 = smem_desc_hi(1024);
+      const uint32_t b_lo0 = smem_desc_lo(smem_u32(b_smem), 16);
+      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++t) {
+        const uint32_t buf = t & 1u, bph = (t >> 1) & 1u;
+        if (!mbar_wait(&tempty_bar[buf], bph ^ 1u, p.status, kStatusTimeoutMma + 0x10 + buf, wait_limit)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + buf * 256;
+        uint32_t accum = 0;
+        for (int cc = 0; cc < p.cchunks && ok; ++cc) {
+          if (!mbar_wait(&full_bar[s], ph, p.status, kStatusTimeoutMma + s, wait_limit)) { ok = false; break; }
+          const uint32_t a_base = smem_u32(smem) + s * (uint32_t)p.stage_bytes;
+          int tap = 0;
+          for (int y = 0; y < p.Y; ++y)
+            for (int x = 0; x < p.X; ++x, ++tap) {
+              const uint32_t shift = (uint32_t)(y * p.dil_h * p.Wp + x * p.dil_w);   // pixel rows of 128 bytes
+              const uint32_t a_addr = a_base + shift * 128u;
+              // the tile starts `shift` rows into the 8-row swizzle pattern of the stage buffer; the pattern follows the
+              // absolute address, so no base offset is set
+              const uint32_t a_lo = smem_desc_lo(a_addr, 16);
+              const uint32_t b_lo = b_lo0 + (((uint32_t)(tap * p.cchunks + cc) * (uint32_t)p.b_tile_bytes) >> 4);
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {   // 64 channels = four K steps of 16
+                umma_ss<kKindF16, 1>(tmem_d, desc64(a_lo + k * 2, desc_hi0), desc64(b_lo + k * 2, desc_hi0), p.idesc, accum);
+                accum = 1;
+              }
+            }
+          tc_commit_addr1(smem_u32(&empty_bar[s]));
+          if (++s == (uint32_t)p.stages) { s = 0; ph ^= 1u; }
+        }
+        if (!ok) break;
+        tc_commit<1>(&tfull_bar[buf]);
+      }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------ epilogue ------------------------------
+    const int q4 = warp & 3, lane = lane_id();
+    const int m = q4 * 32 + lane;              // position on the tile's padded raster
+    const int rr = m / p.Wp, qq = m - rr * p.Wp;
+    uint32_t t = 0;
+    for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++t) {
+      const uint32_t buf = t & 1u, bph = (t >> 1) & 1u;
+      if (!mbar_wait(&tfull_bar[buf], bph, p.status, kStatusTimeoutEpilogue + buf, wait_limit)) break;
+      tc_fence_after();
+      const int n = tile / p.tiles_per_img;
+      const int p0 = (tile - n * p.tiles_per_img) * p.R;
+      const bool valid = rr < p.R && qq < p.Q && p0 + rr < p.P;
+      uint8_t* dst = static_cast<uint8_t*>(p.out) + 2 * ((long long)n * p.o_n + (long long)(p0 + rr) * p.o_p + (long long)qq * p.o_q);
+      const uint32_t taddr = tmem_base + (uint32_t(q4 * 32) << 16) + buf * 256;
+#pragma unroll 1
+      for (int c = 0; c < p.Kout; c += 32) {
+        uint32_t v[32];
+        tmem_ld32(taddr + c, v);
+        tmem_ld_wait();
+        if (valid) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint32_t h[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float lo = __uint_as_float(v[8 * i + 2 * j]), hi = __uint_as_float(v[8 * i + 2 * j + 1]);
+              if (p.is_bf16) { __nv_bfloat162 t2 = __floats2bfloat162_rn(lo, hi); h[j] = *reinterpret_cast<uint32_t*>(&t2); }
+              else { __half2 t2 = __floats2half2_rn(lo, hi); h[j] = *reinterpret_cast<uint32_t*>(&t2); }
+            }
+            *reinterpret_cast<uint4*>(dst + c * 2 + i * 16) = make_uint4(h[0], h[1], h[2], h[3]);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[buf]);
+    }
+  }
+  // ------------------------------ teardown ------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc<1>(tmem_base, 512);
+  }
+}
+
+}  // namespace
+
+bool conv_halo_applicable(const HaloConv& c) {
+  if (c.C % 64 || c.Kout % 32 || c.Kout > 256 || c.Kout < 32) return false;
+  if (c.dil_h < 1 || c.dil_w < 1 || c.pad_h < 0 || c.pad_w < 0) return false;
+  const int Wp = c.Q + (c.X - 1) * c.dil_w;
+  if (Wp > 128 || Wp != c.W + c.pad_w + c.pad_w_r) return false;
+  if (c.P + (c.Y - 1) * c.dil_h != c.H + c.pad_h + c.pad_h_r) return false;
+  const int R = std::min(128 / Wp, c.P);
+  const int rows_box = R + (c.Y - 1) * c.dil_h;
+  if (R < 1 || rows_box > 256 || Wp > 256) return false;
+  const long long b_bytes = (long long)c.Y * c.X * (c.C / 64) * c.Kout * 128;
+  const int stage_bytes = (Wp * rows_box + 7) / 8 * 8 * 128;
+  // the filter stays resident beside at least two stages of the window ring
+  return b_bytes + 2LL * stage_bytes + 160 * 128 + 2048 <= 232448 - 1024;
+}
+
+RbStatus conv_halo_run(const HaloConv& c, const void* image, const void* filter_matrix, void* out, void* stream_v) {
+  const DeviceInfo* dev = device_info();
+  if (!dev) return RB_CUDA_ERROR;
+  if (!conv_halo_applicable(c)) return fail(RB_UNSUPPORTED, "convolution outside the reach of the halo kernel");
+  HaloParams p;
+  memset(&p, 0, sizeof(p));
+  p.N = c.N; p.P = c.P; p.Q = c.Q; p.Kout = c.Kout; p.cchunks = c.C / 64;
+  p.Y = c.Y; p.X = c.X; p.dil_h = c.dil_h; p.dil_w = c.dil_w; p.pad_h = c.pad_h; p.pad_w = c.pad_w;
+  p.Wp = c.Q + (c.X - 1) * c.dil_w;
+  p.R = std::min(128 / p.Wp, c.P);
+  p.rows_box = p.R + (c.Y - 1) * c.dil_h;
+  p.tiles_per_img = (c.P + p.R - 1) / p.R;
+  p.num_tiles = c.N * p.tiles_per_img;
+  p.stage_bytes = (p.Wp * p.rows_box + 7) / 8 * 8 * 128;
+  p.b_tile_bytes = c.Kout * 128;
+  p.b_tiles = c.Y * c.X * p.cchunks;
+  const int fixed = 160 * 128 + p.b_tiles * p.b_tile_bytes + 2048;
+  p.stages = std::min(kHaloMaxStages, (232448 - 1024 - fixed) / p.stage_bytes);
+  const uint32_t fmt = c.is_bf16 ? 1u : 0u;
+  p.idesc = make_idesc(1, fmt, fmt, 0, 0, 128, (uint32_t)c.Kout);
+  p.is_bf16 = c.is_bf16;
+  p.out = out;
+  p.o_n = c.o_n; p.o_p = c.o_p; p.o_q = c.o_q;
+  p.status = dev->status_word;
+  p.wait_cycles = kWaitCycles;
+
+  HaloMaps maps;
+  memset(&maps, 0, sizeof(maps));
+  std::string err;
+  const CUtensorMapDataType dt = c.is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  {
+    const uint64_t dims[4] = {(uint64_t)c.C, (uint64_t)c.W, (uint64_t)c.H, (uint64_t)c.N};
+    const uint64_t strides[3] = {(uint64_t)c.C * 2, (uint64_t)c.W * c.C * 2, (uint64_t)c.H * c.W * c.C * 2};
+    const uint32_t box[4] = {64u, (uint32_t)p.Wp, (uint32_t)p.rows_box, 1u};
+    if (!encode_tiled(&maps.in, dt, 4, image, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, &err))
+      return fail(RB_UNSUPPORTED, "halo kernel, image: " + err);
+  }
+  {
+    const uint64_t ktot = (uint64_t)c.Y * c.X * c.C;
+    const uint64_t dims[3] = {ktot, (uint64_t)c.Kout, 1};
+    const uint64_t strides[2] = {ktot * 2, ktot * c.Kout * 2};
+    const uint32_t box[3] = {64u, (uint32_t)c.Kout, 1u};
+    if (!encode_tiled(&maps.fil, dt, 3, filter_matrix, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, &err))
+      return fail(RB_UNSUPPORTED, "halo kernel, filter: " + err);
+  }
+  const int smem = p.stages * p.stage_bytes + fixed + 1024;
+  RbStatus st = ensure_dynamic_smem(reinterpret_cast<const void*>(conv_halo_kernel), smem);
+  if (st != RB_SUCCESS) return st;
+  const int grid = std::min(p.num_tiles, dev->sm_count);
+  conv_halo_kernel<<<grid, kHaloThreads, smem, static_cast<cudaStream_t>(stream_v)>>>(maps, p);
+  RB_CUDA_TRY(cudaGetLastError());
+  count_launch();
+  return RB_SUCCESS;
+}
+
+}  // namespace rb

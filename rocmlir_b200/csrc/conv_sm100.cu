@@ -442,6 +442,8 @@ RbStatus make_plan(const RbConvProblem* p, ConvPlan* pl, int result_type = -1) {
   pl->a_implicit = false;
   pl->b_implicit = false;
   pl->a_up = false;
+  pl->a_planes = 0;
+  pl->a_nchw = false;
   gp.g = (int)G;
   gp.ab_type = t;
   gp.f32_mode = p->f32_mode;
@@ -874,6 +876,28 @@ RbStatus rb::conv_run(const RbConvProblem* p, int result_type, void* filter, voi
       B = ws + pl.b_off;
     } else if (pl.b_direct) B = filter; else { permute(filter, ws + pl.b_off, fsz, pl.fs, fil_yxkc, true, es); B = ws + pl.b_off; }
     C = pl.c_direct ? input : static_cast<void*>(ws + pl.c_off);
+  }
+  // Unit-stride 16-bit NHWC convolutions whose filter fits into shared memory run on the halo kernel: the window of an
+  // output tile is loaded once instead of once per tap (csrc/conv_halo_sm100.cu). Variant bit 26 keeps the im2col form.
+  if (pl.a_implicit && !capture && !epi && pl.a_planes == 0 && !pl.a_up && pl.c_direct && p->stride_h == 1 && p->stride_w == 1 &&
+      (p->data_type == RB_F16 || p->data_type == RB_BF16) && pl.gemm.c_type == p->data_type && !((rbGetGemmVariant() >> 26) & 1)) {
+    HaloConv hc;
+    hc.is_bf16 = p->data_type == RB_BF16;
+    hc.Y = p->y; hc.X = p->x; hc.dil_h = p->dil_h; hc.dil_w = p->dil_w;
+    const void* image;
+    void* result;
+    if (p->direction == 0) {
+      image = input; result = output;
+      hc.N = p->n; hc.H = p->h; hc.W = p->w; hc.C = p->c; hc.P = (int)ho; hc.Q = (int)wo; hc.Kout = p->k;
+      hc.pad_h = p->pad_h; hc.pad_w = p->pad_w; hc.pad_h_r = p->pad_h_r; hc.pad_w_r = p->pad_w_r;
+    } else {   // backward data: a forward convolution of the output gradient with the mirrored filter matrix B
+      image = output; result = input;
+      hc.N = p->n; hc.H = (int)ho; hc.W = (int)wo; hc.C = p->k; hc.P = p->h; hc.Q = p->w; hc.Kout = p->c;
+      hc.pad_h = (p->y - 1) * p->dil_h - p->pad_h; hc.pad_w = (p->x - 1) * p->dil_w - p->pad_w;
+      hc.pad_h_r = p->h - (int)ho - hc.pad_h + (p->y - 1) * p->dil_h; hc.pad_w_r = p->w - (int)wo - hc.pad_w + (p->x - 1) * p->dil_w;
+    }
+    hc.o_q = hc.Kout; hc.o_p = (long long)hc.Q * hc.Kout; hc.o_n = (long long)hc.P * hc.Q * hc.Kout;
+    if (conv_halo_applicable(hc)) return conv_halo_run(hc, image, B, result, stream_v);
   }
   if (pl.a_implicit) {
     ConvAOperand cv;

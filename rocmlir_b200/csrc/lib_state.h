@@ -78,6 +78,19 @@ size_t conv_workspace_bytes(const RbConvProblem* p, int result_type);
 RbStatus conv_run(const RbConvProblem* p, int result_type, void* filter, void* input, void* output, void* workspace,
                   size_t workspace_bytes, void* stream, const RbEpilogue* epi = nullptr, RbKernelLaunch* capture = nullptr);
 
+// A unit-stride NHWC convolution for conv_halo_run (csrc/conv_halo_sm100.cu): image [N][H][W][C] -> out pixels (n, p, q)
+// at element offsets n * o_n + p * o_p + q * o_q with Kout contiguous channels, filter matrix [Kout][(y, x, c)] K-major.
+struct HaloConv {
+  int N, H, W, C;        // the image tensor that is convolved (input, or the output gradient for backward data)
+  int P, Q, Kout;        // output image and channels
+  int Y, X, dil_h, dil_w;
+  int pad_h, pad_w, pad_h_r, pad_w_r;
+  int is_bf16;
+  long long o_n, o_p, o_q;
+};
+bool conv_halo_applicable(const HaloConv& c);
+RbStatus conv_halo_run(const HaloConv& c, const void* image, const void* filter_matrix, void* out, void* stream);
+
 // cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per (device, kernel, size): the call costs microseconds and
 // small problems are bound by the host's launch path.
 RbStatus ensure_dynamic_smem(const void* kernel, int bytes);

@@ -63,9 +63,9 @@ int main(int argc, char **argv) {
   CUdevice dev; CUcontext ctx;
   CHECK(cuInit(0)); CHECK(cuDeviceGet(&dev, 0)); CHECK(cuDevicePrimaryCtxRetain(&ctx, dev)); CHECK(cuCtxSetCurrent(ctx));
 
-  /* one batch, M = 384 (a CTA pair and a half), N = 520 (ragged last tile), K = 1024; integer-valued data: exact */
+  /* one batch, M = 384 (a CTA pair and a half), N = 520 (ragged last tile), K = 512; integer-valued data: exact */
   RbGemmProblem p; memset(&p, 0, sizeof(p));
-  p.g = 1; p.m = 384; p.n = 520; p.k = 1024; p.ab_type = RB_F16; p.c_type = RB_F16;
+  p.g = 1; p.m = 384; p.n = 520; p.k = 512;   /* eight K blocks: short enough that the library does not cut K into ranges */ p.ab_type = RB_F16; p.c_type = RB_F16;
   size_t na = (size_t)p.m * p.k, nb = (size_t)p.k * p.n, nc = (size_t)p.m * p.n;
   uint16_t *ha = malloc(na * 2), *hb = malloc(nb * 2), *c1 = malloc(nc * 2), *c2 = malloc(nc * 2);
   unsigned s = 12345;

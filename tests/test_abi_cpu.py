@@ -69,3 +69,18 @@ def test_product_does_not_import_oracle():
         if path.endswith((".py", ".cu", ".cuh", ".h", ".cpp")):
             txt = open(path, errors="ignore").read()
             assert "import oracle" not in txt and "from oracle" not in txt and "liboracle" not in txt, path
+
+
+def test_ctypes_mirror_of_the_launch_description_matches_the_c_layout(tmp_path):
+    """RbKernelLaunch is filled by the library: the Python mirror must have the C struct's size and field offsets."""
+    import subprocess
+    from rocmlir_b200 import _lib as L
+    src = tmp_path / "layout.c"
+    src.write_text('#include <stdio.h>\n#include <stddef.h>\n#include "rocmlir_b200.h"\n'
+                   'int main(void) { printf("%zu %zu %zu %zu\\n", sizeof(RbKernelLaunch), offsetof(RbKernelLaunch, params), '
+                   'offsetof(RbKernelLaunch, grid), sizeof(RbEpilogue)); return 0; }\n')
+    exe = str(tmp_path / "layout")
+    subprocess.run(["gcc", "-I", os.path.join(ROOT, "include"), "-o", exe, str(src)], check=True)
+    size, params_off, grid_off, epi = map(int, subprocess.run([exe], capture_output=True, text=True, check=True).stdout.split())
+    assert (C.sizeof(L.RbKernelLaunch), L.RbKernelLaunch.params.offset, L.RbKernelLaunch.grid.offset) == (size, params_off, grid_off)
+    assert C.sizeof(L.RbEpilogue) == epi
