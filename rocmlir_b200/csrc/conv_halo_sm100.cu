@@ -34,6 +34,7 @@ namespace {
 
 constexpr int kHaloThreads = 256;
 constexpr int kHaloMaxStages = 6;
+constexpr int kHaloMaxTaps = 49;   // up to 7 x 7 filters
 
 struct HaloMaps {
   CUtensorMap in;    // {C, W, H, N} of the NHWC image tensor, box {64, Wp, rows_box, 1}
@@ -49,12 +50,20 @@ struct HaloParams {
   int b_tile_bytes, b_tiles;        // one (tap, channel block) slab of the filter: Kout rows of 128 bytes
   uint32_t idesc;
   int is_bf16;
-  void* out;                        // [N][P][Q][Kout], 16-bit elements
+  void* out;                        // output pixels of Kout contiguous channels
   long long o_n, o_p, o_q;          // element strides of the output pixel (n, p, q)
+  EpiParams epi;                    // fused elementwise tail over the output channel (flags == 0: none)
+  int out_type;                     // RbDType of `out` when the epilogue converts (else the 16-bit element type)
   uint32_t* status;
   long long wait_cycles;
+  unsigned long long* trace;        // optional [gridDim.x][16] cycle counters (rbSetTraceBuffer): [2] MMA thread waited for
+                                    // a window, [3] for an accumulator, [4] its loop in total, [5] tiles, [6] epilogue
+                                    // waited for a tile, [7] epilogue busy
 };
 
+// EPI = false is the plain store of the 16-bit result; the fused elementwise tail lives in its own instantiation so that
+// its (large) code does not share the instruction cache with the plain kernel's loops.
+template <bool EPI>
 __global__ void __launch_bounds__(kHaloThreads, 1)
 conv_halo_kernel(const __grid_constant__ HaloMaps maps, const HaloParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -113,37 +122,60 @@ conv_halo_kernel(const __grid_constant__ HaloMaps maps, const HaloParams p) {
     if (lane_id() == 0) {
       bool ok = mbar_wait(bfull_bar, 0, p.status, kStatusTimeoutMma + 0x20, wait_limit);
       uint32_t s = 0, ph = 0, t = 0;
+      bool ready = false;
       const uint32_t desc_hi0 = smem_desc_hi(1024);
+      // descriptor-address steps in 16-byte units: one tap to the right, one tap row down, one filter slab on
+      const uint32_t a_xstep = (uint32_t)p.dil_w * 8u, a_ystep = (uint32_t)(p.dil_h * p.Wp) * 8u;
+      const uint32_t b_slab = (uint32_t)p.b_tile_bytes >> 4, b_tapstep = b_slab * (uint32_t)p.cchunks;
+      long long w_full = 0, w_tempty = 0;
+      const long long t_begin = p.trace ? clock64() : 0;
       const uint32_t b_lo0 = smem_desc_lo(smem_u32(b_smem), 16);
       for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++t) {
         const uint32_t buf = t & 1u, bph = (t >> 1) & 1u;
+        const long long tw0 = p.trace ? clock64() : 0;
         if (!mbar_wait(&tempty_bar[buf], bph ^ 1u, p.status, kStatusTimeoutMma + 0x10 + buf, wait_limit)) { ok = false; break; }
+        if (p.trace) w_tempty += clock64() - tw0;
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + buf * 256;
         uint32_t accum = 0;
         for (int cc = 0; cc < p.cchunks && ok; ++cc) {
-          if (!mbar_wait(&full_bar[s], ph, p.status, kStatusTimeoutMma + s, wait_limit)) { ok = false; break; }
-          const uint32_t a_base = smem_u32(smem) + s * (uint32_t)p.stage_bytes;
-          int tap = 0;
-          for (int y = 0; y < p.Y; ++y)
-            for (int x = 0; x < p.X; ++x, ++tap) {
-              const uint32_t shift = (uint32_t)(y * p.dil_h * p.Wp + x * p.dil_w);   // pixel rows of 128 bytes
-              const uint32_t a_addr = a_base + shift * 128u;
-              // the tile starts `shift` rows into the 8-row swizzle pattern of the stage buffer; the pattern follows the
-              // absolute address, so no base offset is set
-              const uint32_t a_lo = smem_desc_lo(a_addr, 16);
-              const uint32_t b_lo = b_lo0 + (((uint32_t)(tap * p.cchunks + cc) * (uint32_t)p.b_tile_bytes) >> 4);
+          if (!ready) {
+            const long long tw = p.trace ? clock64() : 0;
+            if (!mbar_wait(&full_bar[s], ph, p.status, kStatusTimeoutMma + s, wait_limit)) { ok = false; break; }
+            if (p.trace) w_full += clock64() - tw;
+          }
+          // the test of the NEXT stage's barrier is issued before this stage's MMAs and consumed after them
+          uint32_t ns = s + 1, nph = ph;
+          if (ns == (uint32_t)p.stages) { ns = 0; nph ^= 1u; }
+          const bool next_ready = mbar_test_wait(&full_bar[ns], nph);
+          // every tap is the same window, shifted: the swizzle pattern follows the absolute address, so the shifted
+          // start address is all the descriptor needs
+          uint32_t a_row = smem_desc_lo(smem_u32(smem) + s * (uint32_t)p.stage_bytes, 16);
+          uint32_t b_lo = b_lo0 + (uint32_t)cc * b_slab;
+          for (int y = 0; y < p.Y; ++y) {
+            uint32_t a_lo = a_row;
+            for (int x = 0; x < p.X; ++x) {
 #pragma unroll
               for (int k = 0; k < 4; ++k) {   // 64 channels = four K steps of 16
                 umma_ss<kKindF16, 1>(tmem_d, desc64(a_lo + k * 2, desc_hi0), desc64(b_lo + k * 2, desc_hi0), p.idesc, accum);
                 accum = 1;
               }
+              a_lo += a_xstep;
+              b_lo += b_tapstep;
             }
+            a_row += a_ystep;
+          }
           tc_commit_addr1(smem_u32(&empty_bar[s]));
-          if (++s == (uint32_t)p.stages) { s = 0; ph ^= 1u; }
+          s = ns; ph = nph; ready = next_ready;
         }
         if (!ok) break;
         tc_commit<1>(&tfull_bar[buf]);
+      }
+      if (p.trace) {
+        p.trace[blockIdx.x * 16 + 2] = (unsigned long long)w_full;
+        p.trace[blockIdx.x * 16 + 3] = (unsigned long long)w_tempty;
+        p.trace[blockIdx.x * 16 + 4] = (unsigned long long)(clock64() - t_begin);
+        p.trace[blockIdx.x * 16 + 5] = t;
       }
     }
   } else if (warp >= 4) {
@@ -152,37 +184,82 @@ conv_halo_kernel(const __grid_constant__ HaloMaps maps, const HaloParams p) {
     const int m = q4 * 32 + lane;              // position on the tile's padded raster
     const int rr = m / p.Wp, qq = m - rr * p.Wp;
     uint32_t t = 0;
+    long long w_tfull = 0, e_work = 0;
     for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++t) {
       const uint32_t buf = t & 1u, bph = (t >> 1) & 1u;
-      if (!mbar_wait(&tfull_bar[buf], bph, p.status, kStatusTimeoutEpilogue + buf, wait_limit)) break;
+      const long long tw = p.trace ? clock64() : 0;
+      if (!mbar_wait_warp(&tfull_bar[buf], bph, p.status, kStatusTimeoutEpilogue + buf, wait_limit)) break;
+      const long long te = p.trace ? clock64() : 0;
+      w_tfull += te - tw;
       tc_fence_after();
       const int n = tile / p.tiles_per_img;
       const int p0 = (tile - n * p.tiles_per_img) * p.R;
       const bool valid = rr < p.R && qq < p.Q && p0 + rr < p.P;
-      uint8_t* dst = static_cast<uint8_t*>(p.out) + 2 * ((long long)n * p.o_n + (long long)(p0 + rr) * p.o_p + (long long)qq * p.o_q);
+      const long long pix = (long long)n * p.o_n + (long long)(p0 + rr) * p.o_p + (long long)qq * p.o_q;   // elements
       const uint32_t taddr = tmem_base + (uint32_t(q4 * 32) << 16) + buf * 256;
+      if constexpr (!EPI) {
+        uint8_t* dst = static_cast<uint8_t*>(p.out) + 2 * pix;
 #pragma unroll 1
-      for (int c = 0; c < p.Kout; c += 32) {
-        uint32_t v[32];
-        tmem_ld32(taddr + c, v);
-        tmem_ld_wait();
-        if (valid) {
+        for (int c = 0; c < p.Kout; c += 32) {
+          uint32_t v[32];
+          tmem_ld32(taddr + c, v);
+          tmem_ld_wait();
+          if (valid) {
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            uint32_t h[4];
+            for (int i = 0; i < 4; ++i) {
+              uint32_t h[4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float lo = __uint_as_float(v[8 * i + 2 * j]), hi = __uint_as_float(v[8 * i + 2 * j + 1]);
-              if (p.is_bf16) { __nv_bfloat162 t2 = __floats2bfloat162_rn(lo, hi); h[j] = *reinterpret_cast<uint32_t*>(&t2); }
-              else { __half2 t2 = __floats2half2_rn(lo, hi); h[j] = *reinterpret_cast<uint32_t*>(&t2); }
+              for (int j = 0; j < 4; ++j) {
+                const float lo = __uint_as_float(v[8 * i + 2 * j]), hi = __uint_as_float(v[8 * i + 2 * j + 1]);
+                if (p.is_bf16) { __nv_bfloat162 t2 = __floats2bfloat162_rn(lo, hi); h[j] = *reinterpret_cast<uint32_t*>(&t2); }
+                else { __half2 t2 = __floats2half2_rn(lo, hi); h[j] = *reinterpret_cast<uint32_t*>(&t2); }
+              }
+              *reinterpret_cast<uint4*>(dst + c * 2 + i * 16) = make_uint4(h[0], h[1], h[2], h[3]);
             }
-            *reinterpret_cast<uint4*>(dst + c * 2 + i * 16) = make_uint4(h[0], h[1], h[2], h[3]);
+          }
+        }
+      } else {
+        // fused tail (bias / scale per output channel, residual, relu, clip, requantisation): the same steps in the
+        // same order as the GEMM kernel's epilogue; the per-channel vectors are read through the read-only cache
+        const int es_o = dtype_size(p.out_type);
+        uint8_t* dst = static_cast<uint8_t*>(p.out) + (long long)es_o * pix;
+        EpiRow erow;
+        if ((p.epi.flags & RB_EPI_BIAS) && (p.epi.flags & RB_EPI_BIAS_SCALAR)) erow.row_bias = load_bias(p.epi.bias, p.epi.bias_type, 0);
+        erow.res_stride = 1;
+        erow.ncols = 32;
+#pragma unroll 1
+        for (int c = 0; c < p.Kout; c += 32) {
+          uint32_t v[32];
+          tmem_ld32(taddr + c, v);
+          tmem_ld_wait();
+          float xv[32], cs[32], bs[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            xv[j] = __uint_as_float(v[j]);
+            cs[j] = (p.epi.flags & RB_EPI_COL_SCALE) ? __ldg(p.epi.col_scale + c + j) : 1.0f;
+            bs[j] = epi_col_bias(p.epi.flags) ? load_bias(p.epi.bias, p.epi.bias_type, c + j) : 0.0f;
+          }
+          erow.res = (valid && (p.epi.flags & RB_EPI_RESIDUAL))
+                         ? static_cast<const uint8_t*>(p.epi.residual) + (p.epi.res_type == RB_F32 ? 4 : 2) * (pix + c)
+                         : nullptr;
+          epi_apply32(xv, p.epi, cs, bs, erow);
+          uint4 w4[8];
+          const int nw = pack_row32(xv, p.out_type, w4, p.epi.out_zero);
+          if (valid) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              if (i < nw) *reinterpret_cast<uint4*>(dst + c * es_o + i * 16) = w4[i];
           }
         }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[buf]);
+      if (p.trace) e_work += clock64() - te;
+    }
+    if (p.trace && warp == 4 && lane == 0) {
+      p.trace[blockIdx.x * 16 + 6] = (unsigned long long)w_tfull;
+      p.trace[blockIdx.x * 16 + 7] = (unsigned long long)e_work;
     }
   }
   // ------------------------------ teardown ------------------------------
@@ -198,7 +275,7 @@ conv_halo_kernel(const __grid_constant__ HaloMaps maps, const HaloParams p) {
 
 bool conv_halo_applicable(const HaloConv& c) {
   if (c.C % 64 || c.Kout % 32 || c.Kout > 256 || c.Kout < 32) return false;
-  if (c.dil_h < 1 || c.dil_w < 1 || c.pad_h < 0 || c.pad_w < 0) return false;
+  if (c.dil_h < 1 || c.dil_w < 1 || c.pad_h < 0 || c.pad_w < 0 || c.Y * c.X > 49) return false;
   const int Wp = c.Q + (c.X - 1) * c.dil_w;
   if (Wp > 128 || Wp != c.W + c.pad_w + c.pad_w_r) return false;
   if (c.P + (c.Y - 1) * c.dil_h != c.H + c.pad_h + c.pad_h_r) return false;
@@ -211,7 +288,8 @@ bool conv_halo_applicable(const HaloConv& c) {
   return b_bytes + 2LL * stage_bytes + 160 * 128 + 2048 <= 232448 - 1024;
 }
 
-RbStatus conv_halo_run(const HaloConv& c, const void* image, const void* filter_matrix, void* out, void* stream_v) {
+RbStatus conv_halo_run(const HaloConv& c, const void* image, const void* filter_matrix, void* out, void* stream_v,
+                       const RbEpilogue* epi, int out_type) {
   const DeviceInfo* dev = device_info();
   if (!dev) return RB_CUDA_ERROR;
   if (!conv_halo_applicable(c)) return fail(RB_UNSUPPORTED, "convolution outside the reach of the halo kernel");
@@ -227,6 +305,7 @@ RbStatus conv_halo_run(const HaloConv& c, const void* image, const void* filter_
   p.stage_bytes = (p.Wp * p.rows_box + 7) / 8 * 8 * 128;
   p.b_tile_bytes = c.Kout * 128;
   p.b_tiles = c.Y * c.X * p.cchunks;
+  if (c.Y * c.X > kHaloMaxTaps) return fail(RB_UNSUPPORTED, "halo kernel: filter larger than 7 x 7");
   const int fixed = 160 * 128 + p.b_tiles * p.b_tile_bytes + 2048;
   p.stages = std::min(kHaloMaxStages, (232448 - 1024 - fixed) / p.stage_bytes);
   const uint32_t fmt = c.is_bf16 ? 1u : 0u;
@@ -234,6 +313,16 @@ RbStatus conv_halo_run(const HaloConv& c, const void* image, const void* filter_
   p.is_bf16 = c.is_bf16;
   p.out = out;
   p.o_n = c.o_n; p.o_p = c.o_p; p.o_q = c.o_q;
+  p.out_type = out_type >= 0 ? out_type : (c.is_bf16 ? RB_BF16 : RB_F16);
+  if (epi && epi->flags) {
+    p.epi.flags = epi->flags; p.epi.alpha = epi->alpha; p.epi.out_recip = epi->out_recip; p.epi.mid_type = epi->mid_type;
+    p.epi.bias_type = epi->bias_type; p.epi.col_scale = epi->col_scale; p.epi.bias = epi->bias;
+    p.epi.clip_lo = epi->clip_lo; p.epi.clip_hi = epi->clip_hi; p.epi.in_zero = epi->in_zero;
+    p.epi.out_zero = (epi->flags & RB_EPI_ZP_OUT) ? epi->out_zero : 0;
+    p.epi.residual = epi->residual; p.epi.res_type = epi->res_type;
+  } else if (p.out_type != (c.is_bf16 ? RB_BF16 : RB_F16)) {
+    return fail(RB_UNSUPPORTED, "halo kernel: a converted result needs an epilogue");
+  }
   p.status = dev->status_word;
   p.wait_cycles = kWaitCycles;
 
@@ -257,10 +346,14 @@ RbStatus conv_halo_run(const HaloConv& c, const void* image, const void* filter_
       return fail(RB_UNSUPPORTED, "halo kernel, filter: " + err);
   }
   const int smem = p.stages * p.stage_bytes + fixed + 1024;
-  RbStatus st = ensure_dynamic_smem(reinterpret_cast<const void*>(conv_halo_kernel), smem);
+  const bool with_epi = p.epi.flags != 0;
+  const void* kern = with_epi ? reinterpret_cast<const void*>(conv_halo_kernel<true>) : reinterpret_cast<const void*>(conv_halo_kernel<false>);
+  RbStatus st = ensure_dynamic_smem(kern, smem);
   if (st != RB_SUCCESS) return st;
   const int grid = std::min(p.num_tiles, dev->sm_count);
-  conv_halo_kernel<<<grid, kHaloThreads, smem, static_cast<cudaStream_t>(stream_v)>>>(maps, p);
+  p.trace = trace_buffer((size_t)grid * 16);
+  if (with_epi) conv_halo_kernel<true><<<grid, kHaloThreads, smem, static_cast<cudaStream_t>(stream_v)>>>(maps, p);
+  else conv_halo_kernel<false><<<grid, kHaloThreads, smem, static_cast<cudaStream_t>(stream_v)>>>(maps, p);
   RB_CUDA_TRY(cudaGetLastError());
   count_launch();
   return RB_SUCCESS;

@@ -776,6 +776,38 @@ RbStatus rb::conv_run(const RbConvProblem* p, int result_type, void* filter, voi
       else class_filters_kernel<4><<<fb, 256, 0, stream>>>(static_cast<const uint8_t*>(filter), ws, ft);
       count_launch();
     }
+    // Every class is a unit-stride convolution of the output gradient: on the halo kernel each one writes its pixels
+    // straight into the caller's tensor (pixel strides = the convolution's strides), so the class blocks in the
+    // workspace and the interleaving pass fall away.
+    if (pl.cls_fused && pl.c_direct && es == 2 && !((rbGetGemmVariant() >> 26) & 1)) {
+      HaloConv hc[16];
+      bool all = true, any_empty = false;
+      for (int i = 0; i < pl.n_classes && all; ++i) {
+        const ConvPlan::StrideClass& c = pl.cls[i];
+        if (c.out_off == SIZE_MAX) { any_empty = true; continue; }
+        HaloConv& h = hc[i];
+        h.is_bf16 = p->data_type == RB_BF16;
+        h.N = p->n; h.H = (int)ho; h.W = (int)wo; h.C = p->k; h.P = c.q.h; h.Q = c.q.w; h.Kout = p->c;
+        h.Y = c.q.y; h.X = c.q.x; h.dil_h = h.dil_w = 1;
+        h.pad_h = (c.q.y - 1) - c.q.pad_h; h.pad_w = (c.q.x - 1) - c.q.pad_w;
+        h.pad_h_r = c.q.h - (int)ho - h.pad_h + (c.q.y - 1); h.pad_w_r = c.q.w - (int)wo - h.pad_w + (c.q.x - 1);
+        h.o_q = (long long)p->stride_w * p->c; h.o_p = (long long)p->stride_h * p->w * p->c; h.o_n = (long long)p->h * p->w * p->c;
+        all = conv_halo_applicable(h);
+      }
+      if (all) {
+        if (any_empty) {   // pixels no tap reaches
+          RB_CUDA_TRY(cudaMemsetAsync(input, 0, (size_t)p->n * p->h * p->w * p->c * es, stream));
+        }
+        for (int i = 0; i < pl.n_classes; ++i) {
+          const ConvPlan::StrideClass& c = pl.cls[i];
+          if (c.out_off == SIZE_MAX) continue;
+          uint8_t* first = static_cast<uint8_t*>(input) + ((size_t)c.ph * p->w + c.pw) * p->c * es;
+          st = conv_halo_run(hc[i], output, ws + c.fil_off, first, stream_v);
+          if (st != RB_SUCCESS) return st;
+        }
+        return RB_SUCCESS;
+      }
+    }
     for (int i = 0; i < pl.n_classes; ++i) {
       const ConvPlan::StrideClass& c = pl.cls[i];
       const int k = c.ph * p->stride_w + c.pw;
@@ -879,8 +911,9 @@ RbStatus rb::conv_run(const RbConvProblem* p, int result_type, void* filter, voi
   }
   // Unit-stride 16-bit NHWC convolutions whose filter fits into shared memory run on the halo kernel: the window of an
   // output tile is loaded once instead of once per tap (csrc/conv_halo_sm100.cu). Variant bit 26 keeps the im2col form.
-  if (pl.a_implicit && !capture && !epi && pl.a_planes == 0 && !pl.a_up && pl.c_direct && p->stride_h == 1 && p->stride_w == 1 &&
-      (p->data_type == RB_F16 || p->data_type == RB_BF16) && pl.gemm.c_type == p->data_type && !((rbGetGemmVariant() >> 26) & 1)) {
+  if (pl.a_implicit && !capture && pl.a_planes == 0 && !pl.a_up && pl.c_direct && p->stride_h == 1 && p->stride_w == 1 &&
+      (p->data_type == RB_F16 || p->data_type == RB_BF16) && (epi || pl.gemm.c_type == p->data_type) &&
+      !((rbGetGemmVariant() >> 26) & 1)) {
     HaloConv hc;
     hc.is_bf16 = p->data_type == RB_BF16;
     hc.Y = p->y; hc.X = p->x; hc.dil_h = p->dil_h; hc.dil_w = p->dil_w;
@@ -897,7 +930,7 @@ RbStatus rb::conv_run(const RbConvProblem* p, int result_type, void* filter, voi
       hc.pad_h_r = p->h - (int)ho - hc.pad_h + (p->y - 1) * p->dil_h; hc.pad_w_r = p->w - (int)wo - hc.pad_w + (p->x - 1) * p->dil_w;
     }
     hc.o_q = hc.Kout; hc.o_p = (long long)hc.Q * hc.Kout; hc.o_n = (long long)hc.P * hc.Q * hc.Kout;
-    if (conv_halo_applicable(hc)) return conv_halo_run(hc, image, B, result, stream_v);
+    if (conv_halo_applicable(hc)) return conv_halo_run(hc, image, B, result, stream_v, epi, pl.gemm.c_type);
   }
   if (pl.a_implicit) {
     ConvAOperand cv;

@@ -477,6 +477,9 @@ RbStatus rb::gemm_run(const RbGemmProblem* p, const RbEpilogue* epi, const void*
     cfg.sk_tiles = 0;
     ws = plan_workspace(p, oa, ob, cfg);
   }
+  if (capture && (oa.needs_copy || ob.needs_copy || cfg.splits > 1))
+    return fail(RB_UNSUPPORTED, "this problem runs as several kernels (operand copy, TF32 planes or a K split): it has no "
+                                "single-kernel binary; launch it through the library");
   if (ws.total > 0) {
     if (!workspace || workspace_bytes < ws.total)
       return fail(RB_WORKSPACE_TOO_SMALL, "workspace of " + std::to_string(ws.total) + " bytes required");
@@ -485,9 +488,6 @@ RbStatus rb::gemm_run(const RbGemmProblem* p, const RbEpilogue* epi, const void*
   if ((reinterpret_cast<uintptr_t>(a) % 16 && !oa.needs_copy) || (reinterpret_cast<uintptr_t>(b) % 16 && !ob.needs_copy))
     return fail(RB_UNSUPPORTED, "operand base addresses must be 16-byte aligned");
 
-  if (capture && (oa.needs_copy || ob.needs_copy || cfg.splits > 1))
-    return fail(RB_UNSUPPORTED, "this problem runs as several kernels (operand copy, TF32 planes or a K split): it has no "
-                                "single-kernel binary; launch it through the library");
   uint8_t* wsb = static_cast<uint8_t*>(workspace);
   const void* a_src[2] = {a, nullptr};
   const void* b_src[2] = {b, nullptr};

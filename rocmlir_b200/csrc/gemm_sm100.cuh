@@ -543,7 +543,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
       const uint32_t buf = t & 1u;
       const uint32_t bph = (t >> 1) & 1u;
       const long long tw = p.trace ? clock64() : 0;
-      if (!mbar_wait(&tfull_bar[buf], bph, p.status, kStatusTimeoutEpilogue + buf, wait_limit)) break;
+      if (!mbar_wait_warp(&tfull_bar[buf], bph, p.status, kStatusTimeoutEpilogue + buf, wait_limit)) break;
       const long long te = p.trace ? clock64() : 0;
       w_tfull += te - tw;
       tc_fence_after();

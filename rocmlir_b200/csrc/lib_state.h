@@ -89,7 +89,8 @@ struct HaloConv {
   long long o_n, o_p, o_q;
 };
 bool conv_halo_applicable(const HaloConv& c);
-RbStatus conv_halo_run(const HaloConv& c, const void* image, const void* filter_matrix, void* out, void* stream);
+RbStatus conv_halo_run(const HaloConv& c, const void* image, const void* filter_matrix, void* out, void* stream,
+                       const RbEpilogue* epi = nullptr, int out_type = -1);
 
 // cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per (device, kernel, size): the call costs microseconds and
 // small problems are bound by the host's launch path.

@@ -110,6 +110,17 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32
   return true;
 }
 
+// The same wait for a whole warp: one lane polls the barrier and the result is broadcast, so that a waiting warp costs
+// one polling thread's worth of shared-memory traffic instead of thirty-two (the tensor core reads its operands from
+// the same shared memory). All 32 lanes must call it.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, uint32_t* status, uint32_t code,
+                                               long long limit = kWaitCycles) {
+  uint32_t ok = 1;
+  if (lane_id() == 0) ok = mbar_wait(bar, parity, status, code, limit) ? 1u : 0u;
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  return ok != 0;
+}
+
 // ---- TMA -------------------------------------------------------------------------------------
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
