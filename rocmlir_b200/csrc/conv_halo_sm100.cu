@@ -54,6 +54,7 @@ struct HaloParams {
   long long o_n, o_p, o_q;          // element strides of the output pixel (n, p, q)
   EpiParams epi;                    // fused elementwise tail over the output channel (flags == 0: none)
   int out_type;                     // RbDType of `out` when the epilogue converts (else the 16-bit element type)
+  int wide_store;                   // `out` is 32-byte aligned: the plain epilogue stores 32 bytes at a time
   uint32_t* status;
   long long wait_cycles;
   unsigned long long* trace;        // optional [gridDim.x][16] cycle counters (rbSetTraceBuffer): [2] MMA thread waited for
@@ -61,11 +62,28 @@ struct HaloParams {
                                     // waited for a tile, [7] epilogue busy
 };
 
+// Up to four convolutions of one launch (the stride classes of a strided backward-data convolution): CTAs
+// [first_cta[i], first_cta[i + 1]) work on convolution i with its own tensor maps, tile raster and resident filter.
+constexpr int kHaloMaxGroup = 4;
+struct HaloGroup {
+  HaloMaps maps[kHaloMaxGroup];
+  HaloParams prm[kHaloMaxGroup];
+  int first_cta[kHaloMaxGroup + 1];
+  int n;
+};
+
 // EPI = false is the plain store of the 16-bit result; the fused elementwise tail lives in its own instantiation so that
 // its (large) code does not share the instruction cache with the plain kernel's loops.
 template <bool EPI>
 __global__ void __launch_bounds__(kHaloThreads, 1)
-conv_halo_kernel(const __grid_constant__ HaloMaps maps, const HaloParams p) {
+conv_halo_kernel(const __grid_constant__ HaloGroup g) {
+  int member = 0;
+#pragma unroll
+  for (int i = 1; i < kHaloMaxGroup; ++i)
+    if (i < g.n && (int)blockIdx.x >= g.first_cta[i]) member = i;
+  const HaloParams& p = g.prm[member];
+  const HaloMaps& maps = g.maps[member];
+  const int cta = (int)blockIdx.x - g.first_cta[member], ctas = g.first_cta[member + 1] - g.first_cta[member];
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   // [A ring: stages * stage_bytes][slack: rows that shifted descriptors may touch past the last stage][B][barriers]
@@ -78,7 +96,7 @@ conv_halo_kernel(const __grid_constant__ HaloMaps maps, const HaloParams p) {
   uint64_t* tempty_bar = bars + 2 * kHaloMaxStages + 2;  // [2]
   uint64_t* bfull_bar = bars + 2 * kHaloMaxStages + 4;   // [1]
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * kHaloMaxStages + 5);
-  const int warp = threadIdx.x >> 5;
+  const int warp = warp_id_uniform();
   const long long wait_limit = p.wait_cycles;
 
   if (threadIdx.x == 0) {
@@ -106,7 +124,7 @@ conv_halo_kernel(const __grid_constant__ HaloMaps maps, const HaloParams p) {
       uint32_t s = 0, ph = 0;
       bool ok = true;
       const uint32_t box_bytes = (uint32_t)(p.Wp * p.rows_box * 128);
-      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+      for (int tile = cta; ok && tile < p.num_tiles; tile += ctas) {
         const int n = tile / p.tiles_per_img;
         const int p0 = (tile - n * p.tiles_per_img) * p.R;
         for (int cc = 0; cc < p.cchunks; ++cc) {
@@ -119,102 +137,131 @@ conv_halo_kernel(const __grid_constant__ HaloMaps maps, const HaloParams p) {
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
-    if (lane_id() == 0) {
-      bool ok = mbar_wait(bfull_bar, 0, p.status, kStatusTimeoutMma + 0x20, wait_limit);
-      uint32_t s = 0, ph = 0, t = 0;
-      bool ready = false;
-      const uint32_t desc_hi0 = smem_desc_hi(1024);
-      // descriptor-address steps in 16-byte units: one tap to the right, one tap row down, one filter slab on
-      const uint32_t a_xstep = (uint32_t)p.dil_w * 8u, a_ystep = (uint32_t)(p.dil_h * p.Wp) * 8u;
-      const uint32_t b_slab = (uint32_t)p.b_tile_bytes >> 4, b_tapstep = b_slab * (uint32_t)p.cchunks;
-      long long w_full = 0, w_tempty = 0;
-      const long long t_begin = p.trace ? clock64() : 0;
-      const uint32_t b_lo0 = smem_desc_lo(smem_u32(b_smem), 16);
-      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++t) {
-        const uint32_t buf = t & 1u, bph = (t >> 1) & 1u;
-        const long long tw0 = p.trace ? clock64() : 0;
-        if (!mbar_wait(&tempty_bar[buf], bph ^ 1u, p.status, kStatusTimeoutMma + 0x10 + buf, wait_limit)) { ok = false; break; }
-        if (p.trace) w_tempty += clock64() - tw0;
-        tc_fence_after();
-        const uint32_t tmem_d = tmem_base + buf * 256;
-        uint32_t accum = 0;
-        for (int cc = 0; cc < p.cchunks && ok; ++cc) {
-          if (!ready) {
-            const long long tw = p.trace ? clock64() : 0;
-            if (!mbar_wait(&full_bar[s], ph, p.status, kStatusTimeoutMma + s, wait_limit)) { ok = false; break; }
-            if (p.trace) w_full += clock64() - tw;
-          }
-          // the test of the NEXT stage's barrier is issued before this stage's MMAs and consumed after them
-          uint32_t ns = s + 1, nph = ph;
-          if (ns == (uint32_t)p.stages) { ns = 0; nph ^= 1u; }
-          const bool next_ready = mbar_test_wait(&full_bar[ns], nph);
-          // every tap is the same window, shifted: the swizzle pattern follows the absolute address, so the shifted
-          // start address is all the descriptor needs
-          uint32_t a_row = smem_desc_lo(smem_u32(smem) + s * (uint32_t)p.stage_bytes, 16);
-          uint32_t b_lo = b_lo0 + (uint32_t)cc * b_slab;
-          for (int y = 0; y < p.Y; ++y) {
-            uint32_t a_lo = a_row;
-            for (int x = 0; x < p.X; ++x) {
-#pragma unroll
-              for (int k = 0; k < 4; ++k) {   // 64 channels = four K steps of 16
-                umma_ss<kKindF16, 1>(tmem_d, desc64(a_lo + k * 2, desc_hi0), desc64(b_lo + k * 2, desc_hi0), p.idesc, accum);
-                accum = 1;
-              }
-              a_lo += a_xstep;
-              b_lo += b_tapstep;
-            }
-            a_row += a_ystep;
-          }
-          tc_commit_addr1(smem_u32(&empty_bar[s]));
-          s = ns; ph = nph; ready = next_ready;
+    // All 32 lanes run the loop (so that its counters and descriptor addresses are warp-uniform values) and one elected
+    // lane issues the tensor-core instructions and their commits.
+    // the loop's invariants, read once (the parameter block is indexed by the group member)
+    const int Y = p.Y, X = p.X, cchunks = p.cchunks, num_tiles = p.num_tiles;
+    const uint32_t stages = (uint32_t)p.stages, idesc = p.idesc;
+    const bool tracing = p.trace != nullptr;
+    uint32_t* const status = p.status;
+    bool ok = mbar_wait_warp(bfull_bar, 0, status, kStatusTimeoutMma + 0x20, wait_limit);
+    uint32_t s = 0, ph = 0, t = 0;
+    bool ready = false, tready = false;
+    const uint32_t desc_hi0 = smem_desc_hi(1024);
+    // descriptor-address steps in 16-byte units: one tap to the right, one tap row down, one filter slab on
+    const uint32_t a_xstep = (uint32_t)p.dil_w * 8u, a_ystep = (uint32_t)(p.dil_h * p.Wp) * 8u;
+    const uint32_t b_slab = (uint32_t)p.b_tile_bytes >> 4, b_tapstep = b_slab * (uint32_t)cchunks;
+    long long w_full = 0, w_tempty = 0;
+    const long long t_begin = tracing ? clock64() : 0;
+    const uint32_t b_lo0 = smem_desc_lo(smem_u32(b_smem), 16);
+    const uint32_t a_lo0 = smem_desc_lo(smem_u32(smem), 16);
+    const uint32_t a_stage = (uint32_t)p.stage_bytes >> 4;
+    for (int tile = cta; ok && tile < num_tiles; tile += ctas, ++t) {
+      const uint32_t buf = t & 1u, bph = (t >> 1) & 1u;
+      if (!tready) {
+        const long long tw0 = tracing ? clock64() : 0;
+        if (!mbar_wait_warp(&tempty_bar[buf], bph ^ 1u, status, kStatusTimeoutMma + 0x10 + buf, wait_limit)) { ok = false; break; }
+        if (tracing) w_tempty += clock64() - tw0;
+      }
+      tc_fence_after();
+      const uint32_t tmem_d = tmem_base + buf * 256;
+      uint32_t accum = 0;
+      for (int cc = 0; cc < cchunks && ok; ++cc) {
+        if (!ready) {
+          const long long tw = tracing ? clock64() : 0;
+          if (!mbar_wait_warp(&full_bar[s], ph, status, kStatusTimeoutMma + s, wait_limit)) { ok = false; break; }
+          if (tracing) w_full += clock64() - tw;
+          tc_fence_after();
         }
-        if (!ok) break;
-        tc_commit<1>(&tfull_bar[buf]);
+        // the NEXT stage's barrier, and after the last channel chunk the next tile's accumulator, are tested just
+        // before this stage's last tap is issued, so that the answers arrive while those MMAs queue up
+        uint32_t ns = s + 1, nph = ph;
+        if (ns == stages) { ns = 0; nph ^= 1u; }
+        bool next_ready = false, next_tready = false;
+        const bool last_cc = cc + 1 == cchunks;
+        // every tap is the same window, shifted: the swizzle pattern follows the absolute address, so the shifted
+        // start address is all the descriptor needs
+        uint32_t a_row = a_lo0 + s * a_stage;
+        uint32_t b_lo = b_lo0 + (uint32_t)cc * b_slab;
+        for (int y = 0; y < Y; ++y) {
+          uint32_t a_lo = a_row;
+          for (int x = 0; x < X; ++x) {
+            if (y + 1 == Y && x + 1 == X) {
+              uint32_t f = mbar_test_wait(&full_bar[ns], nph) ? 1u : 0u;
+              if (last_cc && mbar_test_wait(&tempty_bar[buf ^ 1u], (((t + 1) >> 1) & 1u) ^ 1u)) f |= 2u;
+              f = __shfl_sync(0xffffffffu, f, 0);
+              next_ready = f & 1u;
+              next_tready = f & 2u;
+            }
+            if (elect_one()) {
+#pragma unroll
+              for (int k = 0; k < 4; ++k)   // 64 channels = four K steps of 16
+                umma_ss<kKindF16, 1>(tmem_d, desc64(a_lo + k * 2, desc_hi0), desc64(b_lo + k * 2, desc_hi0), idesc, k ? 1u : accum);
+            }
+            accum = 1;
+            a_lo += a_xstep;
+            b_lo += b_tapstep;
+          }
+          a_row += a_ystep;
+        }
+        if (elect_one()) tc_commit_addr1(smem_u32(&empty_bar[s]));
+        s = ns; ph = nph; ready = next_ready;
+        if (last_cc) tready = next_tready;
       }
-      if (p.trace) {
-        p.trace[blockIdx.x * 16 + 2] = (unsigned long long)w_full;
-        p.trace[blockIdx.x * 16 + 3] = (unsigned long long)w_tempty;
-        p.trace[blockIdx.x * 16 + 4] = (unsigned long long)(clock64() - t_begin);
-        p.trace[blockIdx.x * 16 + 5] = t;
-      }
+      if (!ok) break;
+      if (elect_one()) tc_commit<1>(&tfull_bar[buf]);
+    }
+    if (tracing && lane_id() == 0) {
+      p.trace[blockIdx.x * 16 + 2] = (unsigned long long)w_full;
+      p.trace[blockIdx.x * 16 + 3] = (unsigned long long)w_tempty;
+      p.trace[blockIdx.x * 16 + 4] = (unsigned long long)(clock64() - t_begin);
+      p.trace[blockIdx.x * 16 + 5] = t;
     }
   } else if (warp >= 4) {
     // ------------------------------ epilogue ------------------------------
     const int q4 = warp & 3, lane = lane_id();
     const int m = q4 * 32 + lane;              // position on the tile's padded raster
-    const int rr = m / p.Wp, qq = m - rr * p.Wp;
+    const int Wp = p.Wp, R = p.R, P = p.P, Q = p.Q, Kout = p.Kout, tiles_per_img = p.tiles_per_img, num_tiles = p.num_tiles;
+    const long long o_n = p.o_n, o_p = p.o_p, o_q = p.o_q;
+    const bool is_bf16 = p.is_bf16 != 0, wide = p.wide_store != 0, tracing = p.trace != nullptr;
+    uint8_t* const out = static_cast<uint8_t*>(p.out);
+    const int rr = m / Wp, qq = m - rr * Wp;
     uint32_t t = 0;
     long long w_tfull = 0, e_work = 0;
-    for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++t) {
+    for (int tile = cta; tile < num_tiles; tile += ctas, ++t) {
       const uint32_t buf = t & 1u, bph = (t >> 1) & 1u;
-      const long long tw = p.trace ? clock64() : 0;
+      const long long tw = tracing ? clock64() : 0;
       if (!mbar_wait_warp(&tfull_bar[buf], bph, p.status, kStatusTimeoutEpilogue + buf, wait_limit)) break;
-      const long long te = p.trace ? clock64() : 0;
+      const long long te = tracing ? clock64() : 0;
       w_tfull += te - tw;
       tc_fence_after();
-      const int n = tile / p.tiles_per_img;
-      const int p0 = (tile - n * p.tiles_per_img) * p.R;
-      const bool valid = rr < p.R && qq < p.Q && p0 + rr < p.P;
-      const long long pix = (long long)n * p.o_n + (long long)(p0 + rr) * p.o_p + (long long)qq * p.o_q;   // elements
+      const int n = tile / tiles_per_img;
+      const int p0 = (tile - n * tiles_per_img) * R;
+      const bool valid = rr < R && qq < Q && p0 + rr < P;
+      const long long pix = (long long)n * o_n + (long long)(p0 + rr) * o_p + (long long)qq * o_q;   // elements
       const uint32_t taddr = tmem_base + (uint32_t(q4 * 32) << 16) + buf * 256;
       if constexpr (!EPI) {
-        uint8_t* dst = static_cast<uint8_t*>(p.out) + 2 * pix;
+        uint8_t* dst = out + 2 * pix;
 #pragma unroll 1
-        for (int c = 0; c < p.Kout; c += 32) {
+        for (int c = 0; c < Kout; c += 32) {
           uint32_t v[32];
           tmem_ld32(taddr + c, v);
           tmem_ld_wait();
+          uint32_t h[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float lo = __uint_as_float(v[2 * j]), hi = __uint_as_float(v[2 * j + 1]);
+            if (is_bf16) { __nv_bfloat162 t2 = __floats2bfloat162_rn(lo, hi); h[j] = *reinterpret_cast<uint32_t*>(&t2); }
+            else { __half2 t2 = __floats2half2_rn(lo, hi); h[j] = *reinterpret_cast<uint32_t*>(&t2); }
+          }
           if (valid) {
+            if (wide) {   // 32 bytes per store: half as many trips through the load/store unit
+              st_global_v8(dst + c * 2, h);
+              st_global_v8(dst + c * 2 + 32, h + 8);
+            } else {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              uint32_t h[4];
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const float lo = __uint_as_float(v[8 * i + 2 * j]), hi = __uint_as_float(v[8 * i + 2 * j + 1]);
-                if (p.is_bf16) { __nv_bfloat162 t2 = __floats2bfloat162_rn(lo, hi); h[j] = *reinterpret_cast<uint32_t*>(&t2); }
-                else { __half2 t2 = __floats2half2_rn(lo, hi); h[j] = *reinterpret_cast<uint32_t*>(&t2); }
-              }
-              *reinterpret_cast<uint4*>(dst + c * 2 + i * 16) = make_uint4(h[0], h[1], h[2], h[3]);
+              for (int i = 0; i < 4; ++i)
+                *reinterpret_cast<uint4*>(dst + c * 2 + i * 16) = make_uint4(h[4 * i], h[4 * i + 1], h[4 * i + 2], h[4 * i + 3]);
             }
           }
         }
@@ -222,13 +269,13 @@ conv_halo_kernel(const __grid_constant__ HaloMaps maps, const HaloParams p) {
         // fused tail (bias / scale per output channel, residual, relu, clip, requantisation): the same steps in the
         // same order as the GEMM kernel's epilogue; the per-channel vectors are read through the read-only cache
         const int es_o = dtype_size(p.out_type);
-        uint8_t* dst = static_cast<uint8_t*>(p.out) + (long long)es_o * pix;
+        uint8_t* dst = out + (long long)es_o * pix;
         EpiRow erow;
         if ((p.epi.flags & RB_EPI_BIAS) && (p.epi.flags & RB_EPI_BIAS_SCALAR)) erow.row_bias = load_bias(p.epi.bias, p.epi.bias_type, 0);
         erow.res_stride = 1;
         erow.ncols = 32;
 #pragma unroll 1
-        for (int c = 0; c < p.Kout; c += 32) {
+        for (int c = 0; c < Kout; c += 32) {
           uint32_t v[32];
           tmem_ld32(taddr + c, v);
           tmem_ld_wait();
@@ -255,9 +302,9 @@ conv_halo_kernel(const __grid_constant__ HaloMaps maps, const HaloParams p) {
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[buf]);
-      if (p.trace) e_work += clock64() - te;
+      if (tracing) e_work += clock64() - te;
     }
-    if (p.trace && warp == 4 && lane == 0) {
+    if (tracing && warp == 4 && lane == 0) {
       p.trace[blockIdx.x * 16 + 6] = (unsigned long long)w_tfull;
       p.trace[blockIdx.x * 16 + 7] = (unsigned long long)e_work;
     }
@@ -288,12 +335,12 @@ bool conv_halo_applicable(const HaloConv& c) {
   return b_bytes + 2LL * stage_bytes + 160 * 128 + 2048 <= 232448 - 1024;
 }
 
-RbStatus conv_halo_run(const HaloConv& c, const void* image, const void* filter_matrix, void* out, void* stream_v,
-                       const RbEpilogue* epi, int out_type) {
-  const DeviceInfo* dev = device_info();
-  if (!dev) return RB_CUDA_ERROR;
+namespace {
+
+// Fills the kernel's description of one convolution; `smem` returns the dynamic shared memory it wants.
+RbStatus halo_setup(const HaloConv& c, const void* image, const void* filter_matrix, void* out, const RbEpilogue* epi,
+                    int out_type, const DeviceInfo* dev, HaloParams& p, HaloMaps& maps, int* smem) {
   if (!conv_halo_applicable(c)) return fail(RB_UNSUPPORTED, "convolution outside the reach of the halo kernel");
-  HaloParams p;
   memset(&p, 0, sizeof(p));
   p.N = c.N; p.P = c.P; p.Q = c.Q; p.Kout = c.Kout; p.cchunks = c.C / 64;
   p.Y = c.Y; p.X = c.X; p.dil_h = c.dil_h; p.dil_w = c.dil_w; p.pad_h = c.pad_h; p.pad_w = c.pad_w;
@@ -325,8 +372,8 @@ RbStatus conv_halo_run(const HaloConv& c, const void* image, const void* filter_
   }
   p.status = dev->status_word;
   p.wait_cycles = kWaitCycles;
+  p.wide_store = reinterpret_cast<uintptr_t>(out) % 32 == 0 && (c.o_n * 2) % 32 == 0 && (c.o_p * 2) % 32 == 0 && (c.o_q * 2) % 32 == 0;
 
-  HaloMaps maps;
   memset(&maps, 0, sizeof(maps));
   std::string err;
   const CUtensorMapDataType dt = c.is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
@@ -345,15 +392,72 @@ RbStatus conv_halo_run(const HaloConv& c, const void* image, const void* filter_
     if (!encode_tiled(&maps.fil, dt, 3, filter_matrix, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, &err))
       return fail(RB_UNSUPPORTED, "halo kernel, filter: " + err);
   }
-  const int smem = p.stages * p.stage_bytes + fixed + 1024;
-  const bool with_epi = p.epi.flags != 0;
+  *smem = p.stages * p.stage_bytes + fixed + 1024;
+  return RB_SUCCESS;
+}
+
+// Rough cycles of one tile: its MMAs (shared-memory bound: 128 rows of A and Kout rows of B, 32 bytes each, per MMA at
+// about 100 bytes per clock) or its epilogue, whichever is longer. Only the RATIO between the members of a group matters.
+long long halo_tile_cost(const HaloParams& p) {
+  const long long mma = (long long)p.Y * p.X * p.cchunks * 4 * ((4096 + p.Kout * 32) / 100) + 450;
+  const long long epilogue = (long long)(p.Kout / 32) * 480 + 100;
+  return std::max(mma, epilogue);
+}
+
+}  // namespace
+
+RbStatus conv_halo_run(const HaloConv& c, const void* image, const void* filter_matrix, void* out, void* stream_v,
+                       const RbEpilogue* epi, int out_type) {
+  const void* filters[1] = {filter_matrix};
+  void* outs[1] = {out};
+  return conv_halo_run_group(&c, 1, image, filters, outs, stream_v, epi, out_type);
+}
+
+RbStatus conv_halo_run_group(const HaloConv* cs, int count, const void* image, const void* const* filter_matrices,
+                             void* const* outs, void* stream_v, const RbEpilogue* epi, int out_type) {
+  const DeviceInfo* dev = device_info();
+  if (!dev) return RB_CUDA_ERROR;
+  if (count < 1 || count > kHaloMaxGroup) return fail(RB_UNSUPPORTED, "halo kernel: one to four convolutions per launch");
+  HaloGroup g;
+  memset(&g, 0, sizeof(g));
+  g.n = count;
+  int smem = 0;
+  long long total_tiles = 0;
+  for (int i = 0; i < count; ++i) {
+    int sm = 0;
+    RbStatus st = halo_setup(cs[i], image, filter_matrices[i], outs[i], epi, out_type, dev, g.prm[i], g.maps[i], &sm);
+    if (st != RB_SUCCESS) return st;
+    smem = std::max(smem, sm);
+    total_tiles += g.prm[i].num_tiles;
+  }
+  // CTAs per member: one each, then one at a time to the member that would finish last
+  int ctas[kHaloMaxGroup] = {0, 0, 0, 0};
+  int grid = (int)std::min<long long>(total_tiles, dev->sm_count);
+  if (grid < count) grid = count;
+  for (int i = 0; i < count; ++i) ctas[i] = 1;
+  for (int used = count; used < grid; ++used) {
+    int worst = -1;
+    long long worst_t = -1;
+    for (int i = 0; i < count; ++i) {
+      if (ctas[i] >= g.prm[i].num_tiles) continue;
+      const long long t = (g.prm[i].num_tiles + ctas[i] - 1) / ctas[i] * halo_tile_cost(g.prm[i]);
+      if (t > worst_t) { worst_t = t; worst = i; }
+    }
+    if (worst < 0) { grid = used; break; }
+    ++ctas[worst];
+  }
+  for (int i = 0; i < count; ++i) g.first_cta[i + 1] = g.first_cta[i] + ctas[i];
+  for (int i = count; i < kHaloMaxGroup; ++i) g.first_cta[i + 1] = g.first_cta[count];
+  grid = g.first_cta[count];
+
+  const bool with_epi = g.prm[0].epi.flags != 0;
   const void* kern = with_epi ? reinterpret_cast<const void*>(conv_halo_kernel<true>) : reinterpret_cast<const void*>(conv_halo_kernel<false>);
   RbStatus st = ensure_dynamic_smem(kern, smem);
   if (st != RB_SUCCESS) return st;
-  const int grid = std::min(p.num_tiles, dev->sm_count);
-  p.trace = trace_buffer((size_t)grid * 16);
-  if (with_epi) conv_halo_kernel<true><<<grid, kHaloThreads, smem, static_cast<cudaStream_t>(stream_v)>>>(maps, p);
-  else conv_halo_kernel<false><<<grid, kHaloThreads, smem, static_cast<cudaStream_t>(stream_v)>>>(maps, p);
+  unsigned long long* trace = trace_buffer((size_t)grid * 16);
+  for (int i = 0; i < count; ++i) g.prm[i].trace = trace;
+  if (with_epi) conv_halo_kernel<true><<<grid, kHaloThreads, smem, static_cast<cudaStream_t>(stream_v)>>>(g);
+  else conv_halo_kernel<false><<<grid, kHaloThreads, smem, static_cast<cudaStream_t>(stream_v)>>>(g);
   RB_CUDA_TRY(cudaGetLastError());
   count_launch();
   return RB_SUCCESS;

@@ -798,12 +798,24 @@ RbStatus rb::conv_run(const RbConvProblem* p, int result_type, void* filter, voi
         if (any_empty) {   // pixels no tap reaches
           RB_CUDA_TRY(cudaMemsetAsync(input, 0, (size_t)p->n * p->h * p->w * p->c * es, stream));
         }
-        for (int i = 0; i < pl.n_classes; ++i) {
-          const ConvPlan::StrideClass& c = pl.cls[i];
-          if (c.out_off == SIZE_MAX) continue;
-          uint8_t* first = static_cast<uint8_t*>(input) + ((size_t)c.ph * p->w + c.pw) * p->c * es;
-          st = conv_halo_run(hc[i], output, ws + c.fil_off, first, stream_v);
-          if (st != RB_SUCCESS) return st;
+        // four classes per launch (a 2 x 2 stride has exactly four)
+        HaloConv group[4];
+        const void* fils[4];
+        void* firsts[4];
+        int n = 0;
+        for (int i = 0; i <= pl.n_classes; ++i) {
+          if (i < pl.n_classes && pl.cls[i].out_off != SIZE_MAX) {
+            const ConvPlan::StrideClass& c = pl.cls[i];
+            group[n] = hc[i];
+            fils[n] = ws + c.fil_off;
+            firsts[n] = static_cast<uint8_t*>(input) + ((size_t)c.ph * p->w + c.pw) * p->c * es;
+            ++n;
+          }
+          if (n == 4 || (i == pl.n_classes && n > 0)) {
+            st = conv_halo_run_group(group, n, output, fils, firsts, stream_v);
+            if (st != RB_SUCCESS) return st;
+            n = 0;
+          }
         }
         return RB_SUCCESS;
       }

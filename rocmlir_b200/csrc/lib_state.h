@@ -91,6 +91,10 @@ struct HaloConv {
 bool conv_halo_applicable(const HaloConv& c);
 RbStatus conv_halo_run(const HaloConv& c, const void* image, const void* filter_matrix, void* out, void* stream,
                        const RbEpilogue* epi = nullptr, int out_type = -1);
+// Up to four such convolutions of the SAME image in one launch (each with its own filter matrix, output pointer and
+// pixel strides): the CTAs are divided among them in proportion to their work.
+RbStatus conv_halo_run_group(const HaloConv* cs, int count, const void* image, const void* const* filter_matrices,
+                             void* const* outs, void* stream, const RbEpilogue* epi = nullptr, int out_type = -1);
 
 // cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per (device, kernel, size): the call costs microseconds and
 // small problems are bound by the host's launch path.

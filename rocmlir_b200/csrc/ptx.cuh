@@ -28,6 +28,10 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
 
 __device__ __forceinline__ uint32_t lane_id() { return threadIdx.x & 31u; }
 
+// The warp's index as a value the compiler knows to be the same in all 32 lanes (a broadcast), so that branches and
+// loops on it, and the address arithmetic inside them, can be compiled for the uniform datapath.
+__device__ __forceinline__ int warp_id_uniform() { return __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0); }
+
 __device__ __forceinline__ bool elect_one() {
   uint32_t pred = 0;
   asm volatile(
@@ -118,7 +122,15 @@ __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, u
   uint32_t ok = 1;
   if (lane_id() == 0) ok = mbar_wait(bar, parity, status, code, limit) ? 1u : 0u;
   ok = __shfl_sync(0xffffffffu, ok, 0);
+  __syncwarp();   // orders the other lanes' accesses after the polling lane's observation
   return ok != 0;
+}
+
+// One 32-byte store to global memory (sm_100 and later); the address is 32-byte aligned.
+__device__ __forceinline__ void st_global_v8(void* ptr, const uint32_t* w) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(ptr), "r"(w[0]), "r"(w[1]), "r"(w[2]),
+               "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+               : "memory");
 }
 
 // ---- TMA -------------------------------------------------------------------------------------
@@ -278,22 +290,22 @@ enum : int { kKindF16 = 0, kKindTF32 = 1, kKindI8 = 2, kKindF8 = 3 };
 template <int KIND, int CTAS>
 __device__ __forceinline__ void umma_ss(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
                                         uint32_t accumulate) {
-#define RB_UMMA(KSTR, GSTR, MASKS)                                                         \
-  asm volatile(                                                                            \
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"                                    \
-      "tcgen05.mma.cta_group::" GSTR ".kind::" KSTR " [%0], %1, %2, %3, " MASKS ", p;\n\t}" \
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u)            \
+#define RB_UMMA(KSTR, GSTR)                                                            \
+  asm volatile(                                                                        \
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"                                \
+      "tcgen05.mma.cta_group::" GSTR ".kind::" KSTR " [%0], %1, %2, %3, p;\n\t}"          \
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)                 \
       : "memory")
   if constexpr (CTAS == 1) {
-    if constexpr (KIND == kKindF16) RB_UMMA("f16", "1", "{%5, %5, %5, %5}");
-    if constexpr (KIND == kKindTF32) RB_UMMA("tf32", "1", "{%5, %5, %5, %5}");
-    if constexpr (KIND == kKindI8) RB_UMMA("i8", "1", "{%5, %5, %5, %5}");
-    if constexpr (KIND == kKindF8) RB_UMMA("f8f6f4", "1", "{%5, %5, %5, %5}");
+    if constexpr (KIND == kKindF16) RB_UMMA("f16", "1");
+    if constexpr (KIND == kKindTF32) RB_UMMA("tf32", "1");
+    if constexpr (KIND == kKindI8) RB_UMMA("i8", "1");
+    if constexpr (KIND == kKindF8) RB_UMMA("f8f6f4", "1");
   } else {
-    if constexpr (KIND == kKindF16) RB_UMMA("f16", "2", "{%5, %5, %5, %5, %5, %5, %5, %5}");
-    if constexpr (KIND == kKindTF32) RB_UMMA("tf32", "2", "{%5, %5, %5, %5, %5, %5, %5, %5}");
-    if constexpr (KIND == kKindI8) RB_UMMA("i8", "2", "{%5, %5, %5, %5, %5, %5, %5, %5}");
-    if constexpr (KIND == kKindF8) RB_UMMA("f8f6f4", "2", "{%5, %5, %5, %5, %5, %5, %5, %5}");
+    if constexpr (KIND == kKindF16) RB_UMMA("f16", "2");
+    if constexpr (KIND == kKindTF32) RB_UMMA("tf32", "2");
+    if constexpr (KIND == kKindI8) RB_UMMA("i8", "2");
+    if constexpr (KIND == kKindF8) RB_UMMA("f8f6f4", "2");
   }
 #undef RB_UMMA
 }
