@@ -389,6 +389,8 @@ struct ConvPlan {
     bool pointwise;                      //   a single tap without padding: A is the output gradient in place
   } cls[16];
   size_t cls_ws_off = 0;
+  bool w_halo = false;      // backward weight on the halo kernel (csrc/conv_wgrad_halo_sm100.cu)
+  HaloConv w_hc;
   bool cls_fused = false;   // every class takes the implicit unit-stride path: one filter pass, one GEMM per class
 };
 
@@ -494,6 +496,17 @@ RbStatus make_plan(const RbConvProblem* p, ConvPlan* pl, int result_type = -1) {
                      p->pad_h < 64 && p->pad_w < 64 && (p->y - 1) * p->dil_h < 256 && (p->x - 1) * p->dil_w < 256 &&
                      p->stride_h <= 8 && p->stride_w <= 8;
     if (pl->b_implicit) pl->b_direct = true;
+    // unit stride, dense NHWK output gradient and KYXC filter gradient: the halo form (input window loaded once per tile)
+    pl->w_halo = false;
+    if (pl->b_implicit && pl->a_direct && pl->c_direct && p->stride_h == 1 && p->stride_w == 1) {
+      HaloConv& h = pl->w_hc;
+      h.is_bf16 = t == RB_BF16;
+      h.N = p->n; h.H = p->h; h.W = p->w; h.C = p->c; h.P = (int)ho; h.Q = (int)wo; h.Kout = p->k;
+      h.Y = p->y; h.X = p->x; h.dil_h = p->dil_h; h.dil_w = p->dil_w;
+      h.pad_h = p->pad_h; h.pad_w = p->pad_w; h.pad_h_r = p->pad_h_r; h.pad_w_r = p->pad_w_r;
+      h.o_n = h.o_p = h.o_q = 0;
+      pl->w_halo = conv_wgrad_halo_applicable(h);
+    }
     pl->a_bytes = pl->a_direct ? 0 : (size_t)G * pix_o * p->k * es;
     pl->b_bytes = pl->b_direct ? 0 : (size_t)G * pix_o * yxc * es;
     pl->c_bytes = pl->c_direct ? 0 : (size_t)G * p->k * yxc * es;
@@ -595,6 +608,7 @@ RbStatus make_plan(const RbConvProblem* p, ConvPlan* pl, int result_type = -1) {
     }
   }
   pl->gemm_ws = gemm_workspace_bytes(&gp, pl->a_implicit ? 0 : pl->b_implicit ? 1 : -1);
+  if (p->direction == 2 && pl->w_halo) pl->gemm_ws = std::max(pl->gemm_ws, conv_wgrad_halo_workspace(pl->w_hc));
   size_t off = 0;
   pl->a_off = off; off += up256(pl->a_bytes);
   pl->b_off = off; off += up256(pl->b_bytes);
@@ -896,6 +910,8 @@ RbStatus rb::conv_run(const RbConvProblem* p, int result_type, void* filter, voi
     if (pl.a_direct) A = output; else { permute(output, ws + pl.a_off, osz, pl.os, act_gmat, true, es); A = ws + pl.a_off; }
     if (pl.b_direct) B = input; else { gather(input, ws + pl.b_off, false, false, ho, wo, p->c); B = ws + pl.b_off; }
     C = pl.c_direct ? filter : static_cast<void*>(ws + pl.c_off);
+    if (pl.w_halo && !capture && !((rbGetGemmVariant() >> 26) & 1))
+      return conv_wgrad_halo_run(pl.w_hc, input, output, filter, ws + pl.gemm_off, pl.gemm_ws, stream_v);
     if (pl.b_implicit) {
       ConvAOperand cv;
       cv.operand = 1;

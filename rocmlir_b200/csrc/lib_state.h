@@ -95,6 +95,12 @@ RbStatus conv_halo_run(const HaloConv& c, const void* image, const void* filter_
 // pixel strides): the CTAs are divided among them in proportion to their work.
 RbStatus conv_halo_run_group(const HaloConv* cs, int count, const void* image, const void* const* filter_matrices,
                              void* const* outs, void* stream, const RbEpilogue* epi = nullptr, int out_type = -1);
+// Backward weight of the same convolution (csrc/conv_wgrad_halo_sm100.cu): image [N][H][W][C], output gradient
+// [N][P][Q][Kout] -> filter gradient [Kout][Y][X][C] in the 16-bit element type. The workspace holds the f32 sums.
+bool conv_wgrad_halo_applicable(const HaloConv& c);
+size_t conv_wgrad_halo_workspace(const HaloConv& c);
+RbStatus conv_wgrad_halo_run(const HaloConv& c, const void* image, const void* out_grad, void* filter_grad, void* workspace,
+                             size_t workspace_bytes, void* stream);
 
 // cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per (device, kernel, size): the call costs microseconds and
 // small problems are bound by the host's launch path.
