@@ -63,6 +63,7 @@ struct AttParams {
   const void* quant_bias;      // first-GEMM-quantised form: device pointers to one i8 and one f16 (else null)
   const void* quant_scale;
   unsigned long long* trace;   // optional [CTAs][16] cycle counters (two-tile kernel), see rbSetTraceBuffer
+  int linear;        // GEMM+GEMM: P = S rounded to the element type (no scale, no softmax, no division by a row sum)
 };
 
 struct AttSmem {
@@ -248,6 +249,21 @@ __global__ void __launch_bounds__(kAttThreads, 1) attention_fwd_kernel(const __g
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld32(tmem_s + c * 32, v + c * 32);
       tmem_ld_wait();
+      if (p.linear) {
+        // GEMM+GEMM: the intermediate is S itself in the element type; columns past the end of N1 are zero
+        const int limit = p.Sk - key0;
+#pragma unroll
+        for (int i = 0; i < 64; ++i)
+          v[i] = pack2((2 * i < limit) ? __uint_as_float(v[2 * i]) : 0.0f, (2 * i + 1 < limit) ? __uint_as_float(v[2 * i + 1]) : 0.0f, p.is_bf16);
+        tmem_st32(tmem_s, v);
+        tmem_st32(tmem_s + 32, v + 32);
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(p_full);
+        l = 1.0f;
+        continue;
+      }
       // f(S) in the log2 domain: scale, bias, masks
       float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
       if (!side_inputs && !edge) {
@@ -641,6 +657,30 @@ __global__ void __launch_bounds__(kAtt2Threads, 1) attention_fwd2_kernel(const _
         }
         return x;
       };
+      if (p.linear) {
+        // GEMM+GEMM: the intermediate is S itself in the element type; columns past the end of N1 are zero
+        const int lim = p.Sk - key0;
+#pragma unroll 1
+        for (int h = 0; h < 2; ++h) {
+          uint32_t v[64];
+          tmem_ld64(tmem_s + h * 64, v);
+          tmem_ld_wait();
+          uint32_t w[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int c0 = h * 64 + 2 * i;
+            w[i] = pack2((c0 < lim) ? __uint_as_float(v[2 * i]) : 0.0f, (c0 + 1 < lim) ? __uint_as_float(v[2 * i + 1]) : 0.0f, p.is_bf16);
+          }
+          tmem_st32(tmem_s + h * 32, w);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_full[t]);
+        l = 1.0f;
+        if (p.trace) sm_busy += clock64() - ts1;
+        continue;
+      }
       // pass 1: row maximum over both halves
       float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
       float m_use = 0.0f;
@@ -1056,6 +1096,27 @@ extern "C" RbStatus rbAttention(const RbAttentionProblem* p, const void* q, cons
   return attention_run(p, q, k, v, o, nullptr, 0, true, stream_v);
 }
 
+namespace rb {
+static thread_local bool t_attention_linear = false;
+
+// O = (A . B1) . B2 on the attention kernels with the softmax taken out: A [g][m][k1] as Q, B1 [g][k1][n1] as K,
+// B2 [g][n1][n2] as V; the intermediate never leaves the SM (S in tensor memory -> rounded to the element type in
+// place -> A operand of the second product). k1 and n2 at most 128 (the kernels' head dimensions).
+bool gemm_gemm_on_chip_applicable(int32_t k1, int32_t n1, int32_t n2, int32_t data_type) {
+  return (data_type == RB_F16 || data_type == RB_BF16) && k1 % 8 == 0 && k1 <= 128 && n2 % 8 == 0 && n2 <= 128 && n1 % 8 == 0;
+}
+RbStatus gemm_gemm_on_chip(int32_t g, int32_t m, int32_t k1, int32_t n1, int32_t n2, int32_t data_type, const void* a,
+                           const void* b1, const void* b2, void* o, void* stream) {
+  RbAttentionProblem p;
+  memset(&p, 0, sizeof(p));
+  p.g = g; p.seq_q = m; p.seq_k = n1; p.head_qk = k1; p.head_v = n2; p.data_type = data_type;
+  t_attention_linear = true;
+  const RbStatus st = attention_run(&p, a, b1, b2, o, nullptr, 0, false, stream);
+  t_attention_linear = false;
+  return st;
+}
+}  // namespace rb
+
 static RbStatus rb::attention_run(const RbAttentionProblem* p, const void* q, const void* k, const void* v, void* o,
                                   void* workspace, size_t workspace_bytes, bool own_scratch, void* stream_v) {
   if (!p) return fail(RB_INVALID_PARAM, "problem is NULL");
@@ -1179,6 +1240,7 @@ static RbStatus rb::attention_run(const RbAttentionProblem* p, const void* q, co
   kp.quant_scale = quantized ? p->quant_scale : nullptr;
   kp.mask = p->mask;
   kp.mask_fill = p->mask_fill;
+  kp.linear = t_attention_linear ? 1 : 0;
   const uint32_t fmt = kp.is_bf16 ? 1u : 0u;
   kp.idesc_s = make_idesc(1, fmt, fmt, 0, p->trans_k ? 0u : 1u, kQT, kKT);
   kp.idesc_pv = make_idesc(1, fmt, fmt, 0, 1u, kQT, (uint32_t)Dvp);

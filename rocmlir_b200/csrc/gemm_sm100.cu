@@ -813,10 +813,15 @@ extern "C" RbStatus rbGemmNoAlloc(const RbGemmProblem* p, const RbEpilogue* epi,
 // ---- rbGemmGemm -------------------------------------------------------------------------------------------
 // O = (A . B1) . B2 with the intermediate rounded to the element type: what rocMLIR's attention skeleton computes
 // with the softmax removed (mlir/lib/Dialect/Rock/Transforms/GridwiseGemmToBlockwise.cpp:1790-1813, 2162-2165).
-// Two launches of the GEMM kernel; the intermediate (M x N1, element type) lives in the caller's workspace and
-// is small enough to stay in L2 between them for the shapes this op is used with.
+// With k1 and n2 at most 128 (the shapes of that skeleton) it runs on the attention kernel in one launch: S = A . B1
+// in tensor memory, rounded to the element type in place, second product straight from there; no workspace. Larger
+// inner extents do not fit the SM (O alone would be 128 x n2 f32 in TMEM): two launches of the GEMM kernel, the
+// intermediate (M x N1, element type) in the caller's workspace, small enough to stay in L2 between them. Variant
+// bit 27 forces the two-launch form.
 extern "C" size_t rbGemmGemmWorkspaceSize(int32_t g, int32_t m, int32_t k1, int32_t n1, int32_t n2, int32_t data_type) {
   if (g <= 0 || m <= 0 || k1 <= 0 || n1 <= 0 || n2 <= 0 || !rb::dtype_bytes(data_type)) return 0;
+  // (the one-launch form needs none of it; the size is reported for the two-launch form so that a caller who sized
+  // its buffer once can switch forms with the variant word)
   RbGemmProblem p1 = {g, m, n1, k1, 0, 0, 0, data_type, data_type, 0};
   RbGemmProblem p2 = {g, m, n2, n1, 0, 0, 0, data_type, data_type, 0};
   const size_t mid = rb::align_up((size_t)g * m * n1 * rb::dtype_bytes(data_type), 256);
@@ -830,6 +835,8 @@ extern "C" RbStatus rbGemmGemm(int32_t g, int32_t m, int32_t k1, int32_t n1, int
     return rb::fail(RB_UNSUPPORTED, "gemm+gemm exists for f16, bf16 and f32");
   const size_t need = rbGemmGemmWorkspaceSize(g, m, k1, n1, n2, data_type);
   if (need == 0) return rb::fail(RB_INVALID_PARAM, "sizes must be positive");
+  if (rb::gemm_gemm_on_chip_applicable(k1, n1, n2, data_type) && !((rbGetGemmVariant() >> 27) & 1))
+    return rb::gemm_gemm_on_chip(g, m, k1, n1, n2, data_type, a, b1, b2, o, stream);
   if (!workspace || workspace_bytes < need)
     return rb::fail(RB_WORKSPACE_TOO_SMALL, "workspace of " + std::to_string(need) + " bytes required");
   RbGemmProblem p1 = {g, m, n1, k1, 0, 0, 0, data_type, data_type, 0};

@@ -97,6 +97,11 @@ RbStatus conv_halo_run_group(const HaloConv* cs, int count, const void* image, c
                              void* const* outs, void* stream, const RbEpilogue* epi = nullptr, int out_type = -1);
 // Backward weight of the same convolution (csrc/conv_wgrad_halo_sm100.cu): image [N][H][W][C], output gradient
 // [N][P][Q][Kout] -> filter gradient [Kout][Y][X][C] in the 16-bit element type. The workspace holds the f32 sums.
+// GEMM+GEMM with the intermediate kept on the SM (csrc/attention_sm100.cu): k1, n2 <= 128, 16-bit types.
+bool gemm_gemm_on_chip_applicable(int32_t k1, int32_t n1, int32_t n2, int32_t data_type);
+RbStatus gemm_gemm_on_chip(int32_t g, int32_t m, int32_t k1, int32_t n1, int32_t n2, int32_t data_type, const void* a,
+                           const void* b1, const void* b2, void* o, void* stream);
+
 bool conv_wgrad_halo_applicable(const HaloConv& c);
 size_t conv_wgrad_halo_workspace(const HaloConv& c);
 RbStatus conv_wgrad_halo_run(const HaloConv& c, const void* image, const void* out_grad, void* filter_grad, void* workspace,

@@ -237,7 +237,9 @@ def test_fp16_gemm_4096_cubed_sampled_rows_and_linearity(cuda_device):
     assert np.abs(colsum - colsum_ref).max() < tol
 
 
-@pytest.mark.parametrize("m,k1,n1,n2", [(256, 192, 320, 128), (4096, 1024, 1024, 1024)])
+@pytest.mark.parametrize("m,k1,n1,n2", [(256, 192, 320, 128), (4096, 1024, 1024, 1024),
+                                        # k1, n2 <= 128: one launch, intermediate on the SM (attention skeleton)
+                                        (256, 64, 320, 128), (4096, 128, 1024, 128), (300, 72, 200, 40), (96, 128, 128, 64)])
 def test_gemm_gemm_matches_oracle(cuda_device, m, k1, n1, n2):
     """O = (A.B1).B2, intermediate rounded to f16 (BASELINE config 5b at full size: M 4096, K1 = N1 = N2 = 1024).
     The full-size oracle is evaluated on a seeded sample of rows (rows are independent)."""
@@ -255,6 +257,35 @@ def test_gemm_gemm_matches_oracle(cuda_device, m, k1, n1, n2):
     ref = oracle.round_to(oracle.gemm_gemm(af[rows], b1f, b2f, oracle.F16, threads=oracle.max_threads()), oracle.F16)
     verdict, info = oracle.verify_float(got[rows], ref, 1e-3, 100.0, 1e30)
     assert verdict == [1, 1, 1], info
+
+
+def test_gemm_gemm_on_chip_equals_two_launches(cuda_device):
+    """Batched bf16 GEMM+GEMM of attention-like extents: the one-launch form (intermediate in tensor memory) against
+    the two-launch form (variant bit 27) on the same inputs - both round the intermediate to bf16 - and the launch count."""
+    import torch
+    from rocmlir_b200 import _lib as L
+    from rocmlir_b200.gemm import gemm_gemm
+    g, m, k1, n1, n2 = 3, 640, 128, 896, 128
+    gen = torch.Generator(device="cuda").manual_seed(77)
+    a = (torch.randn((g, m, k1), device="cuda", generator=gen) * 0.1).bfloat16()
+    b1 = (torch.randn((g, k1, n1), device="cuda", generator=gen) * 0.1).bfloat16()
+    b2 = (torch.randn((g, n1, n2), device="cuda", generator=gen) * 0.1).bfloat16()
+    lib = L.lib()
+    n0 = L.launch_count()
+    fused = gemm_gemm(a, b1, b2)
+    torch.cuda.synchronize()
+    assert L.launch_count() - n0 == 1
+    lib.rbSetGemmVariant(1 << 27)
+    try:
+        plain = gemm_gemm(a, b1, b2)
+        torch.cuda.synchronize()
+    finally:
+        lib.rbSetGemmVariant(0)
+    assert L.kernel_status() == 0
+    ref = (a.float() @ b1.float()).bfloat16().float() @ b2.float()
+    scale = ref.abs().max().item()
+    assert (fused.float() - ref).abs().max().item() <= 2.0 ** -7 * scale
+    assert (fused.float() - plain.float()).abs().max().item() <= 2.0 ** -7 * scale
 
 
 @pytest.mark.parametrize("code,shape", [(oracle.F16, (1, 2304, 2560, 1024)), (oracle.I8, (1, 1300, 3000, 2048)),
