@@ -219,7 +219,7 @@ def build_workload(name, dev, sets, rank=0, world=1, gather=False):
     def rows_of(m, count=8):
         return np.unique(np.concatenate([[0, m - 1], np.random.Generator(np.random.PCG64(9)).choice(m, count - 2, replace=False)]))
 
-    if name.startswith("gemm_") and name != "gemm_gemm_f16":
+    if name.startswith("gemm_") and not name.startswith("gemm_gemm_f16"):
         kind = name[5:]
         if kind in ("f16", "bf16", "f16_bias_relu"):
             dt = torch.bfloat16 if kind == "bf16" else torch.float16
@@ -310,6 +310,26 @@ def build_workload(name, dev, sets, rank=0, world=1, gather=False):
         return dict(step=step, work=(2.0 * m * k1 * n1 + 2.0 * m * n1 * n2) * sets, unit="TFLOP/s",
                     bytes=2.0 * (m * k1 + k1 * n1 + n1 * n2 + m * n2) * sets, bound="tensor", dtype="f16", verify=verify,
                     kernel="gemm_gemm", desc="fp16 GEMM+GEMM M4096 K1 1024 N1 1024 N2 1024")
+    if name == "gemm_gemm_f16_heads":
+        # the attention skeleton without its softmax: 32 problems, inner extents of a head (one launch, intermediate on the SM)
+        G, m_all, k1, n1, n2 = 32, 4096, 128, 4096, 128
+        gl = sharding.shard_range(G, rank, world).size
+        ops = [(randn((gl, m_all, k1), 0.1, torch.float16), randn((gl, k1, n1), 0.1, torch.float16),
+                randn((gl, n1, n2), 0.1, torch.float16), torch.empty((gl, m_all, n2), dtype=torch.float16, device=dev))
+               for _ in range(max(1, sets // 4))]
+        ws = torch.empty(16, dtype=torch.uint8, device=dev)
+        step = lambda: [gemm_gemm(a, b1, b2, out=o, workspace=ws) for a, b1, b2, o in ops]
+
+        def verify():
+            a, b1, b2, o = ops[0]
+            rows = rows_of(m_all)[:16]
+            ref = oracle.round_to(oracle.gemm_gemm(_f32(a[0][rows]), _f32(b1[0]), _f32(b2[0]), oracle.F16, threads=T), oracle.F16)
+            return _verdict(_f32(o[0][rows]), ref, 1e-3)
+        n_ops = len(ops)
+        return dict(step=step, work=2.0 * gl * m_all * n1 * (k1 + n2) * n_ops, unit="TFLOP/s",
+                    bytes=2.0 * gl * (m_all * k1 + k1 * n1 + n1 * n2 + m_all * n2) * n_ops, bound="tensor", dtype="f16",
+                    verify=verify, kernel="attention_fwd2_kernel",
+                    desc="fp16 GEMM+GEMM, 32 problems M4096 K1 128 N1 4096 N2 128 (one launch each, intermediate in tensor memory)")
     if name.startswith("conv_"):
         from rocmlir_b200.conv import ConvConfig, conv, workspace_size as conv_ws
         if name == "conv_f32_nchw":
@@ -404,7 +424,7 @@ def build_workload(name, dev, sets, rank=0, world=1, gather=False):
     raise SystemExit(f"unknown workload {name}")
 
 
-WORKLOADS = (["gemm_f16", "gemm_bf16", "gemm_f16_bias_relu", "gemm_i8", "gemm_i8_requant", "gemm_fp8", "gemm_gemm_f16",
+WORKLOADS = (["gemm_f16", "gemm_bf16", "gemm_f16_bias_relu", "gemm_i8", "gemm_i8_requant", "gemm_fp8", "gemm_gemm_f16", "gemm_gemm_f16_heads",
               "conv_f32_nchw", "attention_f16", "attention_f16_causal"] +
              [f"conv_f16_nhwc_{s}_{d}" for s in "abcd" for d in ("fwd", "bwd_data", "bwd_weight")])
 

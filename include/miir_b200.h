@@ -97,6 +97,11 @@ MIIR_EXPORT MiirStatus miirGetExecutionDims(MiirHandle handle, size_t *global_si
 /* Miir.h:101 */
 MIIR_EXPORT MiirStatus miirDestroyHandle(MiirHandle handle);
 
+/* Bytes of the operation's tensors in argument order (convolution: filter, input, output; GEMM: A, B, C; attention:
+ * Q, K, V and, in sizes[3], O), sizes = size_t[4]. No reference counterpart: the reference's tuning driver reads them
+ * off the kernel's signature (mlir/tools/rocmlir-tuning-driver/rocmlir-tuning-driver.cpp:131-185). */
+MIIR_EXPORT MiirStatus miirGetArgSizes(MiirHandle handle, size_t *sizes);
+
 /* ---- launch (no reference counterpart: the reference's clients load the code object and launch it themselves) ----
  * Arguments in the kernel-argument order of the reference (ConvGenerator.cpp:788-1024): filter, input, output for
  * all three convolution directions; a, b, c for gemm; for attention q, k, v in the first three slots and o in

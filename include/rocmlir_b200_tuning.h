@@ -80,6 +80,25 @@ RB_EXPORT bool rbTuningUpdateTable(RbTuningTable table, const char *problemKey, 
 /* mlirRockTuningSetFromTable (Rock.h:116): false when the table has no entry for the problem's key. */
 RB_EXPORT bool rbTuningSetFromTable(RbTuningTable table, RbProblem problem);
 
+/* The tuning database in the reference's text form (mlir/utils/performance/tuningRunner.py:393-404, read by
+ * perfRunner.py:174-200): `arch <tab> numCUs <tab> problem <tab> perf_config [<tab> TFlops]`, or the legacy
+ * `arch <tab> problem <tab> perf_config`; '#' starts a comment. `arch <tab> numCUs <tab> problem` is exactly the key
+ * rbTuningGetKey returns. Load returns the number of entries taken, Save the number written, -1 when the file
+ * cannot be opened. */
+RB_EXPORT int rbTuningTableLoad(RbTuningTable table, const char *path);
+RB_EXPORT int rbTuningTableSave(RbTuningTable table, const char *path, const char *space_name);
+
+/* Process-wide database: every launch whose variant word is 0 (rbSetGemmVariant) looks its problem key up here and
+ * runs the recorded configuration; workspace queries follow the same rule, so sizes and launches agree. At first
+ * use the library loads the file named by the environment variable RB_TUNING_DB ("none" or empty: no database), or,
+ * when the variable is unset, tuned/sm_100a.tsv beside the shared library (the measured table this package ships;
+ * written by the rocmlir-tuning-driver tool). Rows of other architectures and perf_config strings this library
+ * cannot map are skipped. rbTuningDbLoad adds a file's rows (returns the number taken, -1 = cannot open). */
+RB_EXPORT int rbTuningDbLoad(const char *path);
+RB_EXPORT void rbTuningDbClear(void);
+RB_EXPORT int rbTuningDbSize(void);
+RB_EXPORT uint32_t rbTuningDbLookup(RbProblem problem); /* variant word recorded for the problem, 0 = none */
+
 /* Rock.h:120 */
 #define RB_TUNING_KEY_BUFSZ 2048
 /* mlirRockTuningGetKey (Rock.h:133): "<arch>\t<numCU>\t<problem flags>" in the reference's format

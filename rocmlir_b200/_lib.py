@@ -154,6 +154,8 @@ def lib() -> C.CDLL:
             getattr(l, name).argtypes = [C.c_void_p]
         l.miirBufferGet.restype = C.c_int
         l.miirBufferGet.argtypes = [C.c_void_p, C.c_char_p, C.POINTER(C.c_size_t)]
+        l.miirGetArgSizes.restype = C.c_int
+        l.miirGetArgSizes.argtypes = [C.c_void_p, C.POINTER(C.c_size_t)]
         l.miirGetExecutionDims.restype = C.c_int
         l.miirGetExecutionDims.argtypes = [C.c_void_p, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]
         l.miirDescriptorGet.restype = C.c_int
@@ -215,6 +217,18 @@ def lib() -> C.CDLL:
         l.rbTuningUpdateTable.argtypes = [_Handle, C.c_char_p, C.c_size_t, C.c_char_p, C.c_size_t, C.c_float]
         l.rbTuningSetFromTable.restype = C.c_bool
         l.rbTuningSetFromTable.argtypes = [_Handle, _Handle]
+        l.rbTuningTableLoad.restype = C.c_int
+        l.rbTuningTableLoad.argtypes = [_Handle, C.c_char_p]
+        l.rbTuningTableSave.restype = C.c_int
+        l.rbTuningTableSave.argtypes = [_Handle, C.c_char_p, C.c_char_p]
+        l.rbTuningDbLoad.restype = C.c_int
+        l.rbTuningDbLoad.argtypes = [C.c_char_p]
+        l.rbTuningDbClear.restype = None
+        l.rbTuningDbClear.argtypes = []
+        l.rbTuningDbSize.restype = C.c_int
+        l.rbTuningDbSize.argtypes = []
+        l.rbTuningDbLookup.restype = C.c_uint32
+        l.rbTuningDbLookup.argtypes = [_Handle]
         l.rbTuningGetKey.restype = C.c_size_t
         l.rbTuningGetKey.argtypes = [_Handle, C.c_char_p, C.c_size_t]
         l.rbIsSplitKFaster.restype = C.c_int

@@ -392,6 +392,9 @@ struct ConvPlan {
   bool w_halo = false;      // backward weight on the halo kernel (csrc/conv_wgrad_halo_sm100.cu)
   HaloConv w_hc;
   bool cls_fused = false;   // every class takes the implicit unit-stride path: one filter pass, one GEMM per class
+  bool cls_halo = false;    //   ... and the halo kernel: up to four classes per launch, stored straight into the tensor
+  bool cls_any_empty = false;
+  HaloConv cls_hc[16];
 };
 
 bool is_dense_in_order(const long long* strides, const long long* sizes, const int* order, int n) {
@@ -601,6 +604,23 @@ RbStatus make_plan(const RbConvProblem* p, ConvPlan* pl, int result_type = -1) {
     if (ok) {
       pl->cls_fused = fused;
       pl->n_classes = nc;
+      // Every class is a unit-stride convolution of the output gradient: on the halo kernel each one writes its pixels
+      // straight into the caller's tensor (pixel strides = the convolution's strides), so the class blocks in the
+      // workspace and the interleaving pass fall away.
+      pl->cls_halo = fused && pl->c_direct && es == 2;
+      pl->cls_any_empty = false;
+      for (int i = 0; i < nc && pl->cls_halo; ++i) {
+        const ConvPlan::StrideClass& c = pl->cls[i];
+        if (c.out_off == SIZE_MAX) { pl->cls_any_empty = true; continue; }
+        HaloConv& h = pl->cls_hc[i];
+        h.is_bf16 = p->data_type == RB_BF16;
+        h.N = p->n; h.H = (int)ho; h.W = (int)wo; h.C = p->k; h.P = c.q.h; h.Q = c.q.w; h.Kout = p->c;
+        h.Y = c.q.y; h.X = c.q.x; h.dil_h = h.dil_w = 1;
+        h.pad_h = (c.q.y - 1) - c.q.pad_h; h.pad_w = (c.q.x - 1) - c.q.pad_w;
+        h.pad_h_r = c.q.h - (int)ho - h.pad_h + (c.q.y - 1); h.pad_w_r = c.q.w - (int)wo - h.pad_w + (c.q.x - 1);
+        h.o_q = (long long)p->stride_w * p->c; h.o_p = (long long)p->stride_h * p->w * p->c; h.o_n = (long long)p->h * p->w * p->c;
+        pl->cls_halo = conv_halo_applicable(h);
+      }
       pl->cls_ws_off = off;
       pl->total = off + up256(sub_ws);
       pl->gemm_ws = 0;
@@ -631,6 +651,7 @@ void launch_es(size_t es, int blocks, cudaStream_t st, K k1, K k2, K k4, Args...
 using namespace rb;
 
 size_t rb::conv_workspace_bytes(const RbConvProblem* p, int result_type) {
+  TunedVariantScope tuned(tuned_variant_conv(p));
   ConvPlan pl;
   if (make_plan(p, &pl, result_type) != RB_SUCCESS) return 0;
   return pl.total;
@@ -648,8 +669,16 @@ extern "C" RbStatus rbConvGetGemmProblem(const RbConvProblem* p, RbGemmProblem* 
 }
 
 extern "C" int rbConvKernelCount(const RbConvProblem* p) {
+  TunedVariantScope tuned(tuned_variant_conv(p));
   ConvPlan pl;
   if (make_plan(p, &pl) != RB_SUCCESS) return -1;
+  const bool halo_off = ((rbGetGemmVariant() >> 26) & 1) != 0;
+  if (pl.n_classes > 0 && pl.cls_halo && !halo_off) {
+    int live = 0;
+    for (int i = 0; i < pl.n_classes; ++i) live += pl.cls[i].out_off != SIZE_MAX;
+    return 1 + (live + 3) / 4 + (pl.cls_any_empty ? 1 : 0);   // filter pass, four classes per launch, zero fill
+  }
+  if (p->direction == 2 && pl.w_halo && !halo_off) return 2;   // weight-gradient kernel + the sum of its slabs
   if (pl.n_classes > 0) {
     int n = 1 + (pl.cls_fused ? 1 : 0);   // the interleaving pass (and the one filter pass of the fused form)
     for (int i = 0; i < pl.n_classes; ++i)
@@ -683,6 +712,7 @@ extern "C" RbStatus rbConvEncodeLaunch(const RbConvProblem* p, const RbEpilogue*
 
 RbStatus rb::conv_run(const RbConvProblem* p, int result_type, void* filter, void* input, void* output, void* workspace,
                       size_t workspace_bytes, void* stream_v, const RbEpilogue* epi, RbKernelLaunch* capture) {
+  TunedVariantScope tuned(tuned_variant_conv(p));
   ConvPlan pl;
   RbStatus st = make_plan(p, &pl, result_type);
   if (st != RB_SUCCESS) return st;
@@ -790,49 +820,31 @@ RbStatus rb::conv_run(const RbConvProblem* p, int result_type, void* filter, voi
       else class_filters_kernel<4><<<fb, 256, 0, stream>>>(static_cast<const uint8_t*>(filter), ws, ft);
       count_launch();
     }
-    // Every class is a unit-stride convolution of the output gradient: on the halo kernel each one writes its pixels
-    // straight into the caller's tensor (pixel strides = the convolution's strides), so the class blocks in the
-    // workspace and the interleaving pass fall away.
-    if (pl.cls_fused && pl.c_direct && es == 2 && !((rbGetGemmVariant() >> 26) & 1)) {
-      HaloConv hc[16];
-      bool all = true, any_empty = false;
-      for (int i = 0; i < pl.n_classes && all; ++i) {
-        const ConvPlan::StrideClass& c = pl.cls[i];
-        if (c.out_off == SIZE_MAX) { any_empty = true; continue; }
-        HaloConv& h = hc[i];
-        h.is_bf16 = p->data_type == RB_BF16;
-        h.N = p->n; h.H = (int)ho; h.W = (int)wo; h.C = p->k; h.P = c.q.h; h.Q = c.q.w; h.Kout = p->c;
-        h.Y = c.q.y; h.X = c.q.x; h.dil_h = h.dil_w = 1;
-        h.pad_h = (c.q.y - 1) - c.q.pad_h; h.pad_w = (c.q.x - 1) - c.q.pad_w;
-        h.pad_h_r = c.q.h - (int)ho - h.pad_h + (c.q.y - 1); h.pad_w_r = c.q.w - (int)wo - h.pad_w + (c.q.x - 1);
-        h.o_q = (long long)p->stride_w * p->c; h.o_p = (long long)p->stride_h * p->w * p->c; h.o_n = (long long)p->h * p->w * p->c;
-        all = conv_halo_applicable(h);
+    if (pl.cls_halo && !((rbGetGemmVariant() >> 26) & 1)) {
+      if (pl.cls_any_empty) {   // pixels no tap reaches
+        RB_CUDA_TRY(cudaMemsetAsync(input, 0, (size_t)p->n * p->h * p->w * p->c * es, stream));
+        count_launch();
       }
-      if (all) {
-        if (any_empty) {   // pixels no tap reaches
-          RB_CUDA_TRY(cudaMemsetAsync(input, 0, (size_t)p->n * p->h * p->w * p->c * es, stream));
+      // four classes per launch (a 2 x 2 stride has exactly four)
+      HaloConv group[4];
+      const void* fils[4];
+      void* firsts[4];
+      int n = 0;
+      for (int i = 0; i <= pl.n_classes; ++i) {
+        if (i < pl.n_classes && pl.cls[i].out_off != SIZE_MAX) {
+          const ConvPlan::StrideClass& c = pl.cls[i];
+          group[n] = pl.cls_hc[i];
+          fils[n] = ws + c.fil_off;
+          firsts[n] = static_cast<uint8_t*>(input) + ((size_t)c.ph * p->w + c.pw) * p->c * es;
+          ++n;
         }
-        // four classes per launch (a 2 x 2 stride has exactly four)
-        HaloConv group[4];
-        const void* fils[4];
-        void* firsts[4];
-        int n = 0;
-        for (int i = 0; i <= pl.n_classes; ++i) {
-          if (i < pl.n_classes && pl.cls[i].out_off != SIZE_MAX) {
-            const ConvPlan::StrideClass& c = pl.cls[i];
-            group[n] = hc[i];
-            fils[n] = ws + c.fil_off;
-            firsts[n] = static_cast<uint8_t*>(input) + ((size_t)c.ph * p->w + c.pw) * p->c * es;
-            ++n;
-          }
-          if (n == 4 || (i == pl.n_classes && n > 0)) {
-            st = conv_halo_run_group(group, n, output, fils, firsts, stream_v);
-            if (st != RB_SUCCESS) return st;
-            n = 0;
-          }
+        if (n == 4 || (i == pl.n_classes && n > 0)) {
+          st = conv_halo_run_group(group, n, output, fils, firsts, stream_v);
+          if (st != RB_SUCCESS) return st;
+          n = 0;
         }
-        return RB_SUCCESS;
       }
+      return RB_SUCCESS;
     }
     for (int i = 0; i < pl.n_classes; ++i) {
       const ConvPlan::StrideClass& c = pl.cls[i];

@@ -256,6 +256,33 @@ struct WgradShape {
   int x_plane_bytes, dy_plane_bytes, stage_bytes, stages;
 };
 
+// Units in (tap, channel block) order; consecutive units share an MMA: the half at the lower address comes first and
+// the leading-dimension offset is the (positive) distance to the other. False when a distance does not fit the
+// descriptor's 14-bit field.
+bool wgrad_pairs(const HaloConv& c, const WgradShape& s, uint32_t* off, uint32_t* lbo, int* col0, int* col1) {
+  for (int u = 0; u < s.units; u += 2) {
+    long long o[2] = {0, 0};
+    int col[2] = {-1, -1};
+    for (int h = 0; h < 2 && u + h < s.units; ++h) {
+      const int tap = (u + h) / s.cchunks, cc = (u + h) % s.cchunks;
+      const int y = tap / c.X, x = tap % c.X;
+      o[h] = (long long)cc * s.x_plane_bytes + ((long long)y * c.dil_h * s.Wp + (long long)x * c.dil_w) * 128;
+      col[h] = tap * c.C + cc * 64;
+    }
+    const bool lone = u + 1 >= s.units;
+    const int first = (lone || o[0] < o[1]) ? 0 : 1;
+    const long long d = lone ? 0 : o[1 - first] - o[first];
+    if (!lone && (d <= 0 || (d >> 4) >= 0x4000)) return false;
+    if (off) {
+      off[u / 2] = (uint32_t)(o[first] >> 4);
+      lbo[u / 2] = (uint32_t)(d >> 4);
+      col0[u / 2] = col[first];
+      col1[u / 2] = lone ? -1 : col[1 - first];
+    }
+  }
+  return true;
+}
+
 bool wgrad_shape(const HaloConv& c, WgradShape* s) {
   if (c.C % 64 || c.Kout % 64 || c.Kout > 256 || c.Kout < 64) return false;
   if (c.dil_h < 1 || c.dil_w < 1 || c.pad_h < 0 || c.pad_w < 0 || c.Y * c.X > 49) return false;
@@ -277,8 +304,7 @@ bool wgrad_shape(const HaloConv& c, WgradShape* s) {
   s->dy_plane_bytes = s->ksteps * 16 * 128;
   s->stage_bytes = s->cchunks * s->x_plane_bytes + s->kchunks * s->dy_plane_bytes;
   s->stages = std::min(kWgMaxStages, (232448 - 1024 - kWgSlack - 1024) / s->stage_bytes);
-  // the second window of a pair lies at most one channel plane and the largest tap shift past the first
-  return s->stages >= 2 && ((long long)s->x_plane_bytes * s->cchunks >> 4) < 0x4000;
+  return s->stages >= 2 && wgrad_pairs(c, *s, nullptr, nullptr, nullptr, nullptr);
 }
 
 }  // namespace
@@ -332,24 +358,8 @@ RbStatus conv_wgrad_halo_run(const HaloConv& c, const void* image, const void* o
   p.slabs = static_cast<float*>(workspace);
   p.status = dev->status_word;
   p.wait_cycles = kWaitCycles;
-  // units in (tap, channel block) order; consecutive units share an MMA
-  for (int u = 0; u < s.units; ++u) {
-    const int tap = u / s.cchunks, cc = u % s.cchunks;
-    const int y = tap / c.X, x = tap % c.X;
-    const long long off = (long long)cc * s.x_plane_bytes + ((long long)y * c.dil_h * s.Wp + (long long)x * c.dil_w) * 128;
-    const int col = tap * c.C + cc * 64;
-    if (u % 2 == 0) {
-      p.pair_off[u / 2] = (uint32_t)(off >> 4);
-      p.pair_col0[u / 2] = col;
-      p.pair_col1[u / 2] = -1;
-      p.pair_lbo[u / 2] = 0;
-    } else {
-      const long long lbo = off - ((long long)p.pair_off[u / 2] << 4);
-      if (lbo <= 0 || (lbo >> 4) >= 0x4000) return fail(RB_UNSUPPORTED, "halo weight-gradient kernel: taps too far apart");
-      p.pair_lbo[u / 2] = (uint32_t)(lbo >> 4);
-      p.pair_col1[u / 2] = col;
-    }
-  }
+  if (!wgrad_pairs(c, s, p.pair_off, p.pair_lbo, p.pair_col0, p.pair_col1))
+    return fail(RB_UNSUPPORTED, "halo weight-gradient kernel: taps too far apart");
 
   WgradMaps maps;
   memset(&maps, 0, sizeof(maps));

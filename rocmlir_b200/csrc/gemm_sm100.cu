@@ -129,6 +129,7 @@ struct GemmConfig {
 
 GemmConfig choose_config(const RbGemmProblem* p, int variant, bool epi_vec = false) {
   GemmConfig c;
+  if (variant == 0) variant = (int)tuned_variant_gemm(p);   // the measured table, when it knows the problem
   const int es = (int)dtype_bytes(p->ab_type);
   const bool b_mn = p->ab_type != RB_F32 && p->trans_b == 0;
   const int che = kRowBytes / es;

@@ -97,6 +97,23 @@ RbStatus conv_halo_run_group(const HaloConv* cs, int count, const void* image, c
                              void* const* outs, void* stream, const RbEpilogue* epi = nullptr, int out_type = -1);
 // Backward weight of the same convolution (csrc/conv_wgrad_halo_sm100.cu): image [N][H][W][C], output gradient
 // [N][P][Q][Kout] -> filter gradient [Kout][Y][X][C] in the 16-bit element type. The workspace holds the f32 sums.
+// Tuning database (csrc/tuning.cu): the variant word recorded for a problem, 0 = none.
+uint32_t tuned_variant_gemm(const RbGemmProblem* p);
+uint32_t tuned_variant_conv(const RbConvProblem* p);
+// Runs a call under the recorded variant word when the caller set none (nested calls see the outer one).
+struct TunedVariantScope {
+  int saved;
+  bool active;
+  explicit TunedVariantScope(uint32_t v) : saved(rbGetGemmVariant()), active(saved == 0 && v != 0) {
+    if (active) rbSetGemmVariant((int)v);
+  }
+  ~TunedVariantScope() {
+    if (active) rbSetGemmVariant(saved);
+  }
+  TunedVariantScope(const TunedVariantScope&) = delete;
+  TunedVariantScope& operator=(const TunedVariantScope&) = delete;
+};
+
 // GEMM+GEMM with the intermediate kept on the SM (csrc/attention_sm100.cu): k1, n2 <= 128, 16-bit types.
 bool gemm_gemm_on_chip_applicable(int32_t k1, int32_t n1, int32_t n2, int32_t data_type);
 RbStatus gemm_gemm_on_chip(int32_t g, int32_t m, int32_t k1, int32_t n1, int32_t n2, int32_t data_type, const void* a,

@@ -200,6 +200,36 @@ extern "C" MiirStatus miirDestroyHandle(MiirHandle handle) {
   return MIIR_SUCCESS;
 }
 
+extern "C" MiirStatus miirGetArgSizes(MiirHandle handle, size_t* sizes) {
+  Handle* h = static_cast<Handle*>(handle);
+  if (!h || !sizes) return MIIR_INVALID_PARAM;
+  const std::lock_guard<std::mutex> lock(g_miir_mutex);
+  sizes[0] = sizes[1] = sizes[2] = sizes[3] = 0;
+  if (h->d.kind == kConv) {
+    const RbConvProblem& c = h->d.conv;
+    const size_t es = dtype_bytes(c.data_type);
+    const size_t es_o = c.data_type == RB_I8 ? 4 : (c.data_type == RB_F8E4M3 || c.data_type == RB_F8E5M2) ? 4 : es;
+    sizes[0] = (size_t)c.g * c.k * c.c * c.y * c.x * es;                 // c and k count channels per group
+    sizes[1] = (size_t)c.n * c.g * c.c * c.h * c.w * es;
+    sizes[2] = (size_t)c.n * c.g * c.k * c.ho * c.wo * (c.direction == 0 ? es_o : es);
+  } else if (h->d.kind == kGemm) {
+    const RbGemmProblem& g = h->d.gemm;
+    sizes[0] = (size_t)g.g * g.m * g.k * dtype_bytes(g.ab_type);
+    sizes[1] = (size_t)g.g * g.k * g.n * dtype_bytes(g.ab_type);
+    sizes[2] = (size_t)g.g * g.m * g.n * dtype_bytes(g.c_type);
+  } else if (h->d.kind == kAttention) {
+    const RbAttentionProblem& a = h->d.att;
+    const size_t es = dtype_bytes(a.data_type), es_v = a.data_type == RB_I8 ? 2 : es;
+    sizes[0] = (size_t)a.g * a.seq_q * a.head_qk * es;
+    sizes[1] = (size_t)a.g * a.seq_k * a.head_qk * es;
+    sizes[2] = (size_t)a.g * a.seq_k * a.head_v * es_v;
+    sizes[3] = (size_t)a.g * a.seq_q * a.head_v * es_v;
+  } else {
+    return MIIR_INVALID_MODULE;
+  }
+  return MIIR_SUCCESS;
+}
+
 extern "C" MiirStatus miirLaunch(MiirHandle handle, void* arg0, void* arg1, void* arg2, void* extra, void* workspace,
                                  size_t workspace_bytes, void* stream) {
   Handle* h = static_cast<Handle*>(handle);

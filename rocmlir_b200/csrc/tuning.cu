@@ -1,15 +1,22 @@
 // Tuning surface (include/rocmlir_b200_tuning.h): problem handles, tuning spaces over the GEMM kernel's tile
 // configurations, the best-entry table, problem keys in the reference's text format and the split-K likelihood
 // rule. Counterpart of mlir/lib/CAPI/Dialect/Rock.cpp:31-205 and mlir/lib/Dialect/Rock/Tuning/RockTuningImpl.cpp.
+#include <dlfcn.h>
+
 #include <algorithm>
+#include <atomic>
 #include <cmath>
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
+#include <fstream>
 #include <limits>
 #include <mutex>
 #include <map>
 #include <set>
 #include <shared_mutex>
 #include <string>
+#include <unordered_map>
 #include <vector>
 
 #include "../../include/rocmlir_b200_tuning.h"
@@ -435,6 +442,199 @@ RbSplitKSelectionLikelihood rbIsSplitKFaster(int64_t gDim, int64_t mDim, int64_t
   if (split_values.size() == 1) return RbSplitKNever;
   if (min_imbalance > 1.8) return RbSplitKAlways;
   return RbSplitKMaybe;
+}
+
+// ---- tuning database: the reference's text form, read and written --------------------------------------------
+// A line is `arch <tab> numCUs <tab> problem <tab> perf_config [<tab> TFlops]` (tuningRunner.py:393-404) or the legacy
+// `arch <tab> problem <tab> perf_config`; '#' starts a comment (perfRunner.py:174-200 reads the same three forms).
+// A problem key of this library already is `arch <tab> numCUs <tab> problem`, so a 4/5-column line is key + perf_config.
+
+}  // extern "C"
+
+namespace rb {
+namespace {
+
+struct DbLine { std::string key, perf; float tflops; };
+
+bool split_db_line(const std::string& raw, DbLine* out) {
+  std::string line = raw;
+  while (!line.empty() && (line.back() == '\n' || line.back() == '\r' || line.back() == ' ')) line.pop_back();
+  size_t b = 0;
+  while (b < line.size() && line[b] == ' ') ++b;
+  if (b >= line.size() || line[b] == '#') return false;
+  std::vector<std::string> f;
+  size_t pos = b;
+  while (true) {
+    const size_t t = line.find('\t', pos);
+    f.push_back(line.substr(pos, t == std::string::npos ? std::string::npos : t - pos));
+    if (t == std::string::npos) break;
+    pos = t + 1;
+  }
+  out->tflops = 0.0f;
+  if (f.size() == 3) {
+    out->key = f[0] + "\t" + std::to_string(kDefaultNumCU) + "\t" + f[1];
+    out->perf = f[2];
+  } else if (f.size() == 4 || f.size() == 5) {
+    out->key = f[0] + "\t" + f[1] + "\t" + f[2];
+    out->perf = f[3];
+    if (f.size() == 5) out->tflops = (float)atof(f[4].c_str());
+  } else {
+    return false;
+  }
+  return true;
+}
+
+// Process-wide database consulted by every launch whose variant word is 0.
+struct TuningDb {
+  std::shared_mutex lock;
+  std::unordered_map<std::string, uint32_t> variant_of;
+  std::atomic<int> size{0};
+  std::atomic<int> generation{0};   // bumped by every change (per-thread caches compare it)
+  std::once_flag defaults;
+};
+TuningDb g_db;
+
+int db_add_file(const char* path) {
+  std::ifstream in(path);
+  if (!in) return -1;
+  int taken = 0;
+  std::string raw;
+  std::unique_lock<std::shared_mutex> guard(g_db.lock);
+  while (std::getline(in, raw)) {
+    DbLine l;
+    if (!split_db_line(raw, &l)) continue;
+    if (l.key.compare(0, 6, "sm_100") != 0) continue;   // rows of other architectures (the reference's gfx* rows)
+    uint32_t v = 0;
+    if (!perf_config_to_variant(l.perf.c_str(), &v) || v == 0) continue;
+    g_db.variant_of[l.key] = v;
+    ++taken;
+  }
+  g_db.size.store((int)g_db.variant_of.size());
+  g_db.generation.fetch_add(1);
+  return taken;
+}
+
+// First use: RB_TUNING_DB names the file ("none" or "" = no database); else the table shipped beside the library
+// (tuned/sm_100a.tsv), when present.
+void load_default_db() {
+  std::call_once(g_db.defaults, [] {
+    const char* env = getenv("RB_TUNING_DB");
+    if (env) {
+      if (*env && strcmp(env, "none") != 0) db_add_file(env);
+      return;
+    }
+    Dl_info info;
+    if (dladdr(reinterpret_cast<const void*>(&rbTuningTableCreate), &info) && info.dli_fname) {
+      std::string dir(info.dli_fname);
+      const size_t slash = dir.rfind('/');
+      dir = slash == std::string::npos ? std::string(".") : dir.substr(0, slash);
+      db_add_file((dir + "/tuned/sm_100a.tsv").c_str());
+    }
+  });
+}
+
+uint32_t db_lookup(const ProblemDesc& d) {
+  load_default_db();
+  if (g_db.size.load(std::memory_order_relaxed) == 0) return 0;
+  std::string key;
+  if (!problem_key(d, &key)) return 0;
+  std::shared_lock<std::shared_mutex> guard(g_db.lock);
+  auto it = g_db.variant_of.find(key);
+  return it == g_db.variant_of.end() ? 0u : it->second;
+}
+
+}  // namespace
+
+uint32_t tuned_variant_gemm(const RbGemmProblem* p) {
+  load_default_db();
+  if (!p || g_db.size.load(std::memory_order_relaxed) == 0) return 0;
+  // the last problem asked about, per thread: launches repeat
+  static thread_local RbGemmProblem last_p;
+  static thread_local uint32_t last_v = 0;
+  static thread_local int last_gen = -1;
+  const int gen_now = g_db.generation.load(std::memory_order_relaxed);
+  if (last_gen == gen_now && memcmp(&last_p, p, sizeof(*p)) == 0) return last_v;
+  ProblemDesc d;
+  d.kind = kGemm;
+  d.gemm = *p;
+  last_v = db_lookup(d);
+  last_p = *p;
+  last_gen = gen_now;
+  return last_v;
+}
+
+uint32_t tuned_variant_conv(const RbConvProblem* p) {
+  load_default_db();
+  if (!p || g_db.size.load(std::memory_order_relaxed) == 0) return 0;
+  ProblemDesc d;
+  d.kind = kConv;
+  d.conv = *p;
+  return db_lookup(d);
+}
+
+}  // namespace rb
+
+extern "C" {
+
+int rbTuningDbLoad(const char* path) {
+  load_default_db();
+  if (!path) return -1;
+  return db_add_file(path);
+}
+
+void rbTuningDbClear(void) {
+  load_default_db();
+  std::unique_lock<std::shared_mutex> guard(g_db.lock);
+  g_db.variant_of.clear();
+  g_db.size.store(0);
+  g_db.generation.fetch_add(1);
+}
+
+int rbTuningDbSize(void) {
+  load_default_db();
+  return g_db.size.load();
+}
+
+uint32_t rbTuningDbLookup(RbProblem problem) {
+  if (!problem.ptr) return 0;
+  return db_lookup(*static_cast<ProblemDesc*>(problem.ptr));
+}
+
+int rbTuningTableLoad(RbTuningTable table, const char* path) {
+  if (!table.ptr || !path) return -1;
+  std::ifstream in(path);
+  if (!in) return -1;
+  Table* t = static_cast<Table*>(table.ptr);
+  int taken = 0;
+  std::string raw;
+  while (std::getline(in, raw)) {
+    DbLine l;
+    if (!split_db_line(raw, &l)) continue;
+    // a table keeps the better entry: rank by TFlops when the file has them (stored as a pseudo-time), else keep the first
+    const float time = l.tflops > 0.0f ? 1.0f / l.tflops : std::numeric_limits<float>::max();
+    if (rbTuningUpdateTable(table, l.key.c_str(), l.key.size(), l.perf.c_str(), l.perf.size(), time)) ++taken;
+    else {
+      std::unique_lock<std::shared_mutex> guard(t->lock);
+      if (!t->best.count(l.key)) { t->best[l.key] = std::make_pair(l.perf, time); ++taken; }
+    }
+  }
+  return taken;
+}
+
+int rbTuningTableSave(RbTuningTable table, const char* path, const char* space_name) {
+  if (!table.ptr || !path) return -1;
+  Table* t = static_cast<Table*>(table.ptr);
+  FILE* f = fopen(path, "w");
+  if (!f) return -1;
+  fprintf(f, "# arch\tnumCUs\ttestVector\tperfConfig (%s)\n", space_name ? space_name : "full");
+  std::shared_lock<std::shared_mutex> guard(t->lock);
+  int n = 0;
+  for (const auto& kv : t->best) {
+    fprintf(f, "%s\t%s\n", kv.first.c_str(), kv.second.first.c_str());
+    ++n;
+  }
+  fclose(f);
+  return n;
 }
 
 bool rbIsProblemFusible(RbProblem problem, const char* perfStr, size_t perfLen) {

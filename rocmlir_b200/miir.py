@@ -90,6 +90,14 @@ class Handle:
             raise MiirError(st, "miirGetKernelLaunch (" + L.lib().rbGetLastError().decode() + ")")
         return out
 
+    def arg_sizes(self) -> Tuple[int, int, int, int]:
+        """Bytes of the operation's tensors in argument order (the fourth is attention's O, else 0)."""
+        sizes = (C.c_size_t * 4)()
+        st = L.lib().miirGetArgSizes(self._h, sizes)
+        if st != SUCCESS:
+            raise MiirError(st, "miirGetArgSizes")
+        return tuple(int(v) for v in sizes)
+
     def execution_dims(self) -> Tuple[int, int]:
         g, l = C.c_size_t(0), C.c_size_t(0)
         st = L.lib().miirGetExecutionDims(self._h, C.byref(g), C.byref(l))

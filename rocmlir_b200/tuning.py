@@ -138,6 +138,31 @@ class Table:
         k, p = key.encode(), perf.encode()
         return bool(L.lib().rbTuningUpdateTable(self._t, k, len(k), p, len(p), float(time)))
 
+    def load(self, path: str) -> int:
+        """Reads a tuning database in the reference's 3-, 4- or 5-column text form; returns the entries taken."""
+        return int(L.lib().rbTuningTableLoad(self._t, path.encode()))
+
+    def save(self, path: str, space_name: str = "full") -> int:
+        """Writes `arch <tab> numCUs <tab> problem <tab> perf_config` lines (tuningRunner.py's 4-column form)."""
+        return int(L.lib().rbTuningTableSave(self._t, path.encode(), space_name.encode()))
+
+
+def db_load(path: str) -> int:
+    """Adds a database file to the process-wide table every launch with variant 0 consults."""
+    return int(L.lib().rbTuningDbLoad(path.encode()))
+
+
+def db_clear() -> None:
+    L.lib().rbTuningDbClear()
+
+
+def db_size() -> int:
+    return int(L.lib().rbTuningDbSize())
+
+
+def db_lookup(problem: "Problem") -> int:
+    return int(L.lib().rbTuningDbLookup(problem._p))
+
 
 def is_split_k_faster(g: int, m: int, n: int, k: int, num_cus: int = 148, level: int = FULL) -> int:
     return int(L.lib().rbIsSplitKFaster(g, m, n, k, num_cus, level))

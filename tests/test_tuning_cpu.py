@@ -117,3 +117,72 @@ def test_get_config_reports_the_launch():
     lib.rbSetGemmVariant(0)
     assert (again.tile_n, again.ctas, again.stages, again.splits) == (info.tile_n, info.ctas, info.stages, info.splits)
     assert lib.rbGetGemmVariant() == 0
+
+
+def test_tuning_database_text_forms_and_lookup(tmp_path):
+    """The tuning database in the reference's text forms (tuningRunner.py:393-404 writes 4 or 5 columns, perfRunner.py:
+    174-200 also reads the legacy 3): a table round-trips through a file, the process-wide database takes the rows of
+    this architecture and a launch with variant 0 then plans with the recorded configuration."""
+    import ctypes as C
+    from rocmlir_b200 import _lib as L
+    opts = "--operation gemm --arch sm_100a --t f16 --out_datatype f16 --g 1 --m 4096 --n 4096 --k 4096 --transA false --transB false"
+    prob = tuning.Problem(opts)
+    key = prob.key
+    assert key.split("\t")[:2] == ["sm_100a", "148"]
+    table = tuning.Table()
+    assert table.update(key, "b200:256,128,0,1,0", 2.0)
+    assert table.update(key, "b200:128,256,0,1,0", 1.0)        # faster: replaces
+    assert not table.update(key, "b200:128,64,0,1,0", 3.0)     # slower: kept out
+    path = str(tmp_path / "db.tsv")
+    assert table.save(path, "full") == 1
+    lines = open(path).read().splitlines()
+    assert lines[0].startswith("# arch\tnumCUs\ttestVector\tperfConfig")
+    assert lines[1] == key + "\tb200:128,256,0,1,0"
+    again = tuning.Table()
+    assert again.load(path) == 1
+    fresh = tuning.Problem(opts)
+    assert fresh.set_from_table(again) and fresh.perf_config == "b200:128,256,0,1,0"
+    # the three column counts, a comment, a foreign architecture, an unmappable string
+    problem = key.split("\t", 2)[2]
+    mixed = tmp_path / "mixed.tsv"
+    mixed.write_text("# arch\tnumCUs\ttestVector\tperfConfig\tTFlops (full)\n"
+                     f"sm_100a\t148\t{problem}\tb200:256,128,0,1,0\t1234.5\n"
+                     f"gfx942\t304\t{problem}\tv2:64,64,16,32,32,4,1,1,1\t512.0\n"
+                     f"sm_100a\t{problem.replace('-m 4096', '-m 2048')}\tb200:128,128,0,1,0\n"
+                     f"sm_100a\t148\t{problem.replace('-m 4096', '-m 1024')}\tnot-a-config\n")
+    saved = L.lib().rbGetGemmVariant()
+    tuning.db_clear()
+    try:
+        assert tuning.db_load(str(mixed)) == 2 and tuning.db_size() == 2
+        assert tuning.db_lookup(prob) == prob_variant("b200:256,128,0,1,0", opts)
+        gp = prob_gemm(4096)
+        info = L.RbGemmConfigInfo()
+        L.lib().rbSetGemmVariant(0)
+        assert L.lib().rbGemmGetConfig(C.byref(gp), C.byref(info)) == 0
+        assert (info.ctas, info.tile_n) == (2, 128)                 # the recorded tile, not the rule's 256 columns
+        L.lib().rbSetGemmVariant(prob_variant("b200:128,64,0,1,0", opts))
+        assert L.lib().rbGemmGetConfig(C.byref(gp), C.byref(info)) == 0
+        assert (info.ctas, info.tile_n) == (1, 64)                  # an explicit variant word wins over the database
+        L.lib().rbSetGemmVariant(0)
+        gp2 = prob_gemm(2048)                                   # the legacy 3-column row
+        assert L.lib().rbGemmGetConfig(C.byref(gp2), C.byref(info)) == 0 and (info.ctas, info.tile_n) == (1, 128)
+        tuning.db_clear()
+        assert L.lib().rbGemmGetConfig(C.byref(gp), C.byref(info)) == 0 and info.tile_n == 256
+    finally:
+        tuning.db_clear()
+        L.lib().rbSetGemmVariant(saved)
+
+
+def prob_variant(perf, opts):
+    q = tuning.Problem(opts)
+    assert q.set_from_str(perf)
+    return q.variant
+
+
+def prob_gemm(m):
+    from rocmlir_b200 import _lib as L
+    gp = L.RbGemmProblem()
+    gp.g, gp.m, gp.n, gp.k = 1, m, 4096, 4096
+    gp.trans_a = gp.trans_b = gp.trans_c = 0
+    gp.ab_type = gp.c_type = L.F16
+    return gp
