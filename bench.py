@@ -40,9 +40,9 @@ BYTES_PER_GEMM = 3 * M * N * 2                        # each operand read once, 
 METRIC = "TFLOP/s, fp16 GEMM M=N=K=4096 (rock.gemm, f32 accumulate, f16 out)"
 WORKLOAD = "fp16 GEMM 4096x4096x4096, A,B row-major, f32 accumulate, f16 out, A,B ~ 0.1*N(0,1)"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of gemm_tcgen05_kernel on this workload: a constant taken
-# from the ncu capture summarised in profiles/gemm_f16_4096_ncu.md (89.3 MB read + 15.0 MB written), not measured
+# from the ncu capture summarised in profiles/gemm_f16_4096_ncu.md (two launches: 88.2 + 15.8 and 87.9 + 15.7 MB read + written), not measured
 # by this run.
-NCU_DRAM_BYTES_PER_LAUNCH = 104.3e6
+NCU_DRAM_BYTES_PER_LAUNCH = 103.8e6
 # nominal dense peaks per GPU; f32 runs as three TF32 products per multiply (a third of the 1125 TFLOP/s TF32 figure)
 NOMINAL = {"f16": 2250.0, "bf16": 2250.0, "i8": 4500.0, "fp8": 4500.0, "f32": 375.0, "hbm": 8000.0}
 
@@ -552,6 +552,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (used for ncu captures)")
     ap.add_argument("--no-secondary", action="store_true", help="headline only (used for ncu captures)")
     ap.add_argument("--no-graph", action="store_true", help="secondary workloads: direct launches instead of a CUDA graph")
+    ap.add_argument("--target-ms", type=float, default=1000.0, help="--workload NAME: length of the timed region (short for ncu captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -581,7 +582,7 @@ def main():
 
     if args.workload != "gemm_f16":      # one named workload (or all) as full JSON lines: used for profiling
         for name in (WORKLOADS[1:] if args.workload == "all" else [args.workload]):
-            rec = measure(name, args, dev, rank, world, target_ms=1000.0, sets=args.sets, graph=not args.no_graph)
+            rec = measure(name, args, dev, rank, world, target_ms=args.target_ms, sets=args.sets, graph=not args.no_graph)
             if rank == 0:
                 t0, t1 = rec.pop("host_window")
                 rec["clocks"] = sampler.summary(t0, t1)

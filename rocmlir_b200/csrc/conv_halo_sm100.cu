@@ -38,7 +38,8 @@ constexpr int kHaloMaxTaps = 49;   // up to 7 x 7 filters
 
 struct HaloMaps {
   CUtensorMap in;    // {C, W, H, N} of the NHWC image tensor, box {64, Wp, rows_box, 1}
-  CUtensorMap fil;   // {Y * X * C, Kout, 1} of the K-major filter matrix, box {64, Kout, 1}
+  CUtensorMap fil;   // {Y * X * C, Kout, 1} of the K-major filter matrix, box {64, Kout, 1}; or, for a filter read as it
+                     // lies (b_mn), {Kout, FX, FY, Kfil} of the KYXC filter tensor, box {64, 1, 1, 64}
 };
 
 struct HaloParams {
@@ -48,6 +49,9 @@ struct HaloParams {
   int tiles_per_img, num_tiles;
   int stage_bytes, stages;
   int b_tile_bytes, b_tiles;        // one (tap, channel block) slab of the filter: Kout rows of 128 bytes
+  int b_mn;                         // backward data from the KYXC filter itself: the slab is MN-major (64 rows of the
+                                    // reduction index k, each 64 contiguous input channels; Kout / 64 such chunks)
+  int fy0, fsy, fx0, fsx;           //   filter tap of raster tap (y', x') = (fy0 + fsy * (Y-1-y'), fx0 + fsx * (X-1-x'))
   uint32_t idesc;
   int is_bf16;
   void* out;                        // output pixels of Kout contiguous channels
@@ -120,7 +124,18 @@ conv_halo_kernel(const __grid_constant__ HaloGroup g) {
     if (lane_id() == 0) {
       // the filter, once: slab (tap, cc) = Kout rows x 64 channels
       mbar_expect_tx(bfull_bar, (uint32_t)(p.b_tiles * p.b_tile_bytes));
-      for (int j = 0; j < p.b_tiles; ++j) tma_load_3d(b_smem + (size_t)j * p.b_tile_bytes, &maps.fil, bfull_bar, j * 64, 0, 0);
+      if (!p.b_mn) {
+        for (int j = 0; j < p.b_tiles; ++j) tma_load_3d(b_smem + (size_t)j * p.b_tile_bytes, &maps.fil, bfull_bar, j * 64, 0, 0);
+      } else {
+        // mirrored taps straight from the filter tensor: no rearranged copy of the filter exists
+        for (int j = 0; j < p.b_tiles; ++j) {
+          const int tap = j / p.cchunks, cc = j - tap * p.cchunks;
+          const int ty = tap / p.X, tx = tap - ty * p.X;
+          const int fy = p.fy0 + p.fsy * (p.Y - 1 - ty), fx = p.fx0 + p.fsx * (p.X - 1 - tx);
+          for (int nc = 0; nc < p.Kout / 64; ++nc)
+            tma_load_4d(b_smem + (size_t)j * p.b_tile_bytes + (size_t)nc * 8192, &maps.fil, bfull_bar, nc * 64, fx, fy, cc * 64);
+        }
+      }
       uint32_t s = 0, ph = 0;
       bool ok = true;
       const uint32_t box_bytes = (uint32_t)(p.Wp * p.rows_box * 128);
@@ -139,6 +154,8 @@ conv_halo_kernel(const __grid_constant__ HaloGroup g) {
     // ------------------------------ MMA issuer ------------------------------
     // All 32 lanes run the loop (so that its counters and descriptor addresses are warp-uniform values) and one elected
     // lane issues the tensor-core instructions and their commits.
+    // one lane, chosen once: the commits must come from the thread that issued the MMAs they track
+    const bool leader = elect_one();
     // the loop's invariants, read once (the parameter block is indexed by the group member)
     const int Y = p.Y, X = p.X, cchunks = p.cchunks, num_tiles = p.num_tiles;
     const uint32_t stages = (uint32_t)p.stages, idesc = p.idesc;
@@ -153,7 +170,8 @@ conv_halo_kernel(const __grid_constant__ HaloGroup g) {
     const uint32_t b_slab = (uint32_t)p.b_tile_bytes >> 4, b_tapstep = b_slab * (uint32_t)cchunks;
     long long w_full = 0, w_tempty = 0;
     const long long t_begin = tracing ? clock64() : 0;
-    const uint32_t b_lo0 = smem_desc_lo(smem_u32(b_smem), 16);
+    const uint32_t b_lo0 = smem_desc_lo(smem_u32(b_smem), p.b_mn ? 8192u : 16u);   // MN-major: 8 KB between 64-channel chunks
+    const uint32_t b_kstep = p.b_mn ? 128u : 2u;   // one K step of 16: sixteen 128-byte rows, or 32 bytes along the row
     const uint32_t a_lo0 = smem_desc_lo(smem_u32(smem), 16);
     const uint32_t a_stage = (uint32_t)p.stage_bytes >> 4;
     for (int tile = cta; ok && tile < num_tiles; tile += ctas, ++t) {
@@ -193,10 +211,10 @@ conv_halo_kernel(const __grid_constant__ HaloGroup g) {
               next_ready = f & 1u;
               next_tready = f & 2u;
             }
-            if (elect_one()) {
+            if (leader) {
 #pragma unroll
               for (int k = 0; k < 4; ++k)   // 64 channels = four K steps of 16
-                umma_ss<kKindF16, 1>(tmem_d, desc64(a_lo + k * 2, desc_hi0), desc64(b_lo + k * 2, desc_hi0), idesc, k ? 1u : accum);
+                umma_ss<kKindF16, 1>(tmem_d, desc64(a_lo + k * 2, desc_hi0), desc64(b_lo + k * b_kstep, desc_hi0), idesc, k ? 1u : accum);
             }
             accum = 1;
             a_lo += a_xstep;
@@ -204,12 +222,12 @@ conv_halo_kernel(const __grid_constant__ HaloGroup g) {
           }
           a_row += a_ystep;
         }
-        if (elect_one()) tc_commit_addr1(smem_u32(&empty_bar[s]));
+        if (leader) tc_commit_addr1(smem_u32(&empty_bar[s]));
         s = ns; ph = nph; ready = next_ready;
         if (last_cc) tready = next_tready;
       }
       if (!ok) break;
-      if (elect_one()) tc_commit<1>(&tfull_bar[buf]);
+      if (leader) tc_commit<1>(&tfull_bar[buf]);
     }
     if (tracing && lane_id() == 0) {
       p.trace[blockIdx.x * 16 + 2] = (unsigned long long)w_full;
@@ -322,6 +340,7 @@ conv_halo_kernel(const __grid_constant__ HaloGroup g) {
 
 bool conv_halo_applicable(const HaloConv& c) {
   if (c.C % 64 || c.Kout % 32 || c.Kout > 256 || c.Kout < 32) return false;
+  if (c.b_mn && (c.Kout % 64 || (c.f_sk * 2) % 16 || (c.f_sy * 2) % 16 || (c.f_sx * 2) % 16)) return false;
   if (c.dil_h < 1 || c.dil_w < 1 || c.pad_h < 0 || c.pad_w < 0 || c.Y * c.X > 49) return false;
   const int Wp = c.Q + (c.X - 1) * c.dil_w;
   if (Wp > 128 || Wp != c.W + c.pad_w + c.pad_w_r) return false;
@@ -356,7 +375,9 @@ RbStatus halo_setup(const HaloConv& c, const void* image, const void* filter_mat
   const int fixed = 160 * 128 + p.b_tiles * p.b_tile_bytes + 2048;
   p.stages = std::min(kHaloMaxStages, (232448 - 1024 - fixed) / p.stage_bytes);
   const uint32_t fmt = c.is_bf16 ? 1u : 0u;
-  p.idesc = make_idesc(1, fmt, fmt, 0, 0, 128, (uint32_t)c.Kout);
+  p.idesc = make_idesc(1, fmt, fmt, 0, c.b_mn ? 1u : 0u, 128, (uint32_t)c.Kout);
+  p.b_mn = c.b_mn ? 1 : 0;
+  p.fy0 = c.fy0; p.fsy = c.fsy; p.fx0 = c.fx0; p.fsx = c.fsx;
   p.is_bf16 = c.is_bf16;
   p.out = out;
   p.o_n = c.o_n; p.o_p = c.o_p; p.o_q = c.o_q;
@@ -384,7 +405,14 @@ RbStatus halo_setup(const HaloConv& c, const void* image, const void* filter_mat
     if (!encode_tiled(&maps.in, dt, 4, image, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, &err))
       return fail(RB_UNSUPPORTED, "halo kernel, image: " + err);
   }
-  {
+  if (c.b_mn) {
+    // the filter tensor [Kfil][FY][FX][Kout channels] with its own strides; one box = 64 k x 64 channels of one tap
+    const uint64_t dims[4] = {(uint64_t)c.Kout, (uint64_t)c.FX, (uint64_t)c.FY, (uint64_t)c.C};
+    const uint64_t strides[3] = {(uint64_t)c.f_sx * 2, (uint64_t)c.f_sy * 2, (uint64_t)c.f_sk * 2};
+    const uint32_t box[4] = {64u, 1u, 1u, 64u};
+    if (!encode_tiled(&maps.fil, dt, 4, filter_matrix, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, &err))
+      return fail(RB_UNSUPPORTED, "halo kernel, filter tensor: " + err);
+  } else {
     const uint64_t ktot = (uint64_t)c.Y * c.X * c.C;
     const uint64_t dims[3] = {ktot, (uint64_t)c.Kout, 1};
     const uint64_t strides[2] = {ktot * 2, ktot * c.Kout * 2};

@@ -371,6 +371,7 @@ struct ConvPlan {
   RbGemmProblem gemm;
   // matrices: element counts (0 = operand used as it lies)
   bool a_direct, b_direct, c_direct;
+  bool c_remap = false;   // forward, NKHW-like output: the GEMM epilogue stores channel-major per image (no transposing pass)
   bool a_implicit;   // forward: the A matrix is never built; the GEMM producer loads it from the NHWC input (TMA im2col)
   bool b_implicit;   // backward weight: the same for the B matrix (K = pixels, N = (y,x,c))
   bool a_up;         // backward data with a stride: the output gradient is zero-upsampled into the workspace first
@@ -392,6 +393,7 @@ struct ConvPlan {
   bool w_halo = false;      // backward weight on the halo kernel (csrc/conv_wgrad_halo_sm100.cu)
   HaloConv w_hc;
   bool cls_fused = false;   // every class takes the implicit unit-stride path: one filter pass, one GEMM per class
+  bool fil_in_place = false;   // backward data on the halo kernel reads the KYXC filter as it lies (c contiguous)
   bool cls_halo = false;    //   ... and the halo kernel: up to four classes per launch, stored straight into the tensor
   bool cls_any_empty = false;
   HaloConv cls_hc[16];
@@ -619,12 +621,32 @@ RbStatus make_plan(const RbConvProblem* p, ConvPlan* pl, int result_type = -1) {
         h.pad_h = (c.q.y - 1) - c.q.pad_h; h.pad_w = (c.q.x - 1) - c.q.pad_w;
         h.pad_h_r = c.q.h - (int)ho - h.pad_h + (c.q.y - 1); h.pad_w_r = c.q.w - (int)wo - h.pad_w + (c.q.x - 1);
         h.o_q = (long long)p->stride_w * p->c; h.o_p = (long long)p->stride_h * p->w * p->c; h.o_n = (long long)p->h * p->w * p->c;
+        if (pl->fs[2] == 1 && G == 1 && p->c % 64 == 0) {   // taps come straight from the filter tensor
+          h.b_mn = true;
+          h.FY = p->y; h.FX = p->x; h.f_sk = pl->fs[1]; h.f_sy = pl->fs[3]; h.f_sx = pl->fs[4];
+          h.fy0 = c.y0; h.fsy = p->stride_h; h.fx0 = c.x0; h.fsx = p->stride_w;
+          if (!conv_halo_applicable(h)) h.b_mn = false;
+        }
         pl->cls_halo = conv_halo_applicable(h);
       }
+      pl->fil_in_place = pl->cls_halo;
+      for (int i = 0; i < nc && pl->cls_halo; ++i)
+        if (pl->cls[i].out_off != SIZE_MAX && !pl->cls_hc[i].b_mn) pl->fil_in_place = false;
+      if (!pl->fil_in_place)
+        for (int i = 0; i < nc; ++i) pl->cls_hc[i].b_mn = false;
       pl->cls_ws_off = off;
       pl->total = off + up256(sub_ws);
       pl->gemm_ws = 0;
       return RB_SUCCESS;
+    }
+  }
+  pl->c_remap = false;
+  if (p->direction == 0 && !pl->c_direct && pl->a_implicit && G == 1 && pl->os[4] == 1 && pl->os[3] == wo &&
+      pl->os[2] == ho * wo && pl->os[0] == (long long)p->k * ho * wo) {
+    RbGemmConfigInfo info;
+    if (rbGemmGetConfig(&gp, &info) == RB_SUCCESS && info.splits == 1) {
+      pl->c_remap = true;
+      pl->c_bytes = 0;
     }
   }
   pl->gemm_ws = gemm_workspace_bytes(&gp, pl->a_implicit ? 0 : pl->b_implicit ? 1 : -1);
@@ -649,6 +671,37 @@ void launch_es(size_t es, int blocks, cudaStream_t st, K k1, K k2, K k4, Args...
 }  // namespace rb
 
 using namespace rb;
+
+// Unit-stride 16-bit NHWC forward / backward-data convolutions whose filter fits into shared memory run on the halo
+// kernel: the window of an output tile is loaded once instead of once per tap (csrc/conv_halo_sm100.cu). Backward
+// data is the same kernel over the output gradient with mirrored taps, which it reads straight from a KYXC filter
+// (hc->b_mn) when the layout allows. Variant bit 26 keeps the im2col form.
+static bool unit_halo(const RbConvProblem* p, const ConvPlan& pl, bool has_epi, HaloConv* hc) {
+  if (p->direction > 1 || !pl.a_implicit || pl.a_planes != 0 || pl.a_up || !pl.c_direct || p->stride_h != 1 || p->stride_w != 1 ||
+      !(p->data_type == RB_F16 || p->data_type == RB_BF16) || !(has_epi || pl.gemm.c_type == p->data_type) ||
+      ((rbGetGemmVariant() >> 26) & 1))
+    return false;
+  const int ho = p->ho, wo = p->wo;
+  hc->is_bf16 = p->data_type == RB_BF16;
+  hc->Y = p->y; hc->X = p->x; hc->dil_h = p->dil_h; hc->dil_w = p->dil_w;
+  if (p->direction == 0) {
+    hc->N = p->n; hc->H = p->h; hc->W = p->w; hc->C = p->c; hc->P = ho; hc->Q = wo; hc->Kout = p->k;
+    hc->pad_h = p->pad_h; hc->pad_w = p->pad_w; hc->pad_h_r = p->pad_h_r; hc->pad_w_r = p->pad_w_r;
+  } else {   // backward data: a forward convolution of the output gradient with the mirrored filter
+    hc->N = p->n; hc->H = ho; hc->W = wo; hc->C = p->k; hc->P = p->h; hc->Q = p->w; hc->Kout = p->c;
+    hc->pad_h = (p->y - 1) * p->dil_h - p->pad_h; hc->pad_w = (p->x - 1) * p->dil_w - p->pad_w;
+    hc->pad_h_r = p->h - ho - hc->pad_h + (p->y - 1) * p->dil_h; hc->pad_w_r = p->w - wo - hc->pad_w + (p->x - 1) * p->dil_w;
+  }
+  hc->o_q = hc->Kout; hc->o_p = (long long)hc->Q * hc->Kout; hc->o_n = (long long)hc->P * hc->Q * hc->Kout;
+  if (p->direction == 1 && pl.fs[2] == 1 && p->g == 1 && p->c % 64 == 0) {
+    hc->b_mn = true;
+    hc->FY = p->y; hc->FX = p->x; hc->f_sk = pl.fs[1]; hc->f_sy = pl.fs[3]; hc->f_sx = pl.fs[4];
+    hc->fy0 = 0; hc->fsy = 1; hc->fx0 = 0; hc->fsx = 1;
+    if (conv_halo_applicable(*hc)) return true;
+    hc->b_mn = false;
+  }
+  return conv_halo_applicable(*hc);
+}
 
 size_t rb::conv_workspace_bytes(const RbConvProblem* p, int result_type) {
   TunedVariantScope tuned(tuned_variant_conv(p));
@@ -676,16 +729,20 @@ extern "C" int rbConvKernelCount(const RbConvProblem* p) {
   if (pl.n_classes > 0 && pl.cls_halo && !halo_off) {
     int live = 0;
     for (int i = 0; i < pl.n_classes; ++i) live += pl.cls[i].out_off != SIZE_MAX;
-    return 1 + (live + 3) / 4 + (pl.cls_any_empty ? 1 : 0);   // filter pass, four classes per launch, zero fill
+    return (pl.fil_in_place ? 0 : 1) + (live + 3) / 4 + (pl.cls_any_empty ? 1 : 0);   // filter pass (unless the filter is read in place), four classes per launch, zero fill
   }
   if (p->direction == 2 && pl.w_halo && !halo_off) return 2;   // weight-gradient kernel + the sum of its slabs
+  {
+    HaloConv hc;
+    if (pl.n_classes == 0 && unit_halo(p, pl, false, &hc) && hc.b_mn) return 1;   // backward data, filter read in place
+  }
   if (pl.n_classes > 0) {
     int n = 1 + (pl.cls_fused ? 1 : 0);   // the interleaving pass (and the one filter pass of the fused form)
     for (int i = 0; i < pl.n_classes; ++i)
       if (pl.cls[i].out_off != SIZE_MAX) n += pl.cls_fused ? 1 : 1 + rbConvKernelCount(&pl.cls[i].q);
     return n;
   }
-  return 1 + (pl.a_direct ? 0 : 1) + (pl.b_direct ? 0 : 1) + (pl.c_direct ? 0 : 1);
+  return 1 + (pl.a_direct ? 0 : 1) + (pl.b_direct ? 0 : 1) + ((pl.c_direct || pl.c_remap) ? 0 : 1);
 }
 
 extern "C" RbStatus rbConv(const RbConvProblem* p, void* filter, void* input, void* output, void* workspace,
@@ -801,7 +858,8 @@ RbStatus rb::conv_run(const RbConvProblem* p, int result_type, void* filter, voi
     tb.s_n = pl.is[0]; tb.s_g = pl.is[1]; tb.s_c = pl.is[2]; tb.s_h = pl.is[3]; tb.s_w = pl.is[4];
     tb.sh = p->stride_h; tb.sw = p->stride_w;
     for (int i = 0; i < 16; ++i) { tb.off[i] = -1; tb.hs[i] = tb.wsz[i] = 1; }
-    if (pl.cls_fused) {
+    const bool cls_on_halo = pl.cls_halo && !((rbGetGemmVariant() >> 26) & 1);
+    if (pl.cls_fused && !(cls_on_halo && pl.fil_in_place)) {
       ClassFilters ft;
       ft.s_k = pl.fs[1]; ft.s_c = pl.fs[2]; ft.s_y = pl.fs[3]; ft.s_x = pl.fs[4];
       ft.K = p->k; ft.C = p->c; ft.sh = p->stride_h; ft.sw = p->stride_w;
@@ -820,7 +878,7 @@ RbStatus rb::conv_run(const RbConvProblem* p, int result_type, void* filter, voi
       else class_filters_kernel<4><<<fb, 256, 0, stream>>>(static_cast<const uint8_t*>(filter), ws, ft);
       count_launch();
     }
-    if (pl.cls_halo && !((rbGetGemmVariant() >> 26) & 1)) {
+    if (cls_on_halo) {
       if (pl.cls_any_empty) {   // pixels no tap reaches
         RB_CUDA_TRY(cudaMemsetAsync(input, 0, (size_t)p->n * p->h * p->w * p->c * es, stream));
         count_launch();
@@ -834,7 +892,7 @@ RbStatus rb::conv_run(const RbConvProblem* p, int result_type, void* filter, voi
         if (i < pl.n_classes && pl.cls[i].out_off != SIZE_MAX) {
           const ConvPlan::StrideClass& c = pl.cls[i];
           group[n] = pl.cls_hc[i];
-          fils[n] = ws + c.fil_off;
+          fils[n] = pl.fil_in_place ? static_cast<const void*>(filter) : static_cast<const void*>(ws + c.fil_off);
           firsts[n] = static_cast<uint8_t*>(input) + ((size_t)c.ph * p->w + c.pw) * p->c * es;
           ++n;
         }
@@ -897,6 +955,8 @@ RbStatus rb::conv_run(const RbConvProblem* p, int result_type, void* filter, voi
     return RB_SUCCESS;
   }
 
+  HaloConv uhc;
+  const bool on_halo = !capture && unit_halo(p, pl, epi != nullptr, &uhc);
   const void* A;
   const void* B;
   void* C;
@@ -917,7 +977,7 @@ RbStatus rb::conv_run(const RbConvProblem* p, int result_type, void* filter, voi
   if (p->direction == 0) {
     if (pl.a_direct) A = input; else { gather(input, ws + pl.a_off, false, false, ho, wo, p->c); A = ws + pl.a_off; }
     if (pl.b_direct) B = filter; else { permute(filter, ws + pl.b_off, fsz, pl.fs, fil_kyxc, true, es); B = ws + pl.b_off; }
-    C = pl.c_direct ? output : static_cast<void*>(ws + pl.c_off);
+    C = (pl.c_direct || pl.c_remap) ? output : static_cast<void*>(ws + pl.c_off);
   } else if (p->direction == 2) {
     if (pl.a_direct) A = output; else { permute(output, ws + pl.a_off, osz, pl.os, act_gmat, true, es); A = ws + pl.a_off; }
     if (pl.b_direct) B = input; else { gather(input, ws + pl.b_off, false, false, ho, wo, p->c); B = ws + pl.b_off; }
@@ -939,7 +999,9 @@ RbStatus rb::conv_run(const RbConvProblem* p, int result_type, void* filter, voi
     }
   } else {
     if (pl.a_direct) A = output; else { gather(output, ws + pl.a_off, true, true, p->h, p->w, p->k); A = ws + pl.a_off; }
-    if (pl.a_implicit) {
+    if (on_halo && uhc.b_mn) {
+      B = filter;   // the halo kernel takes the mirrored taps from the filter tensor itself
+    } else if (pl.a_implicit) {
       // B[c][(y',x',k)] = fil[k][c][Y-1-y'][X-1-x']: walk y and x backwards from the last tap
       long long mfs[5] = {pl.fs[0], pl.fs[1], pl.fs[2], -pl.fs[3], -pl.fs[4]};
       const int fil_cyxk[5] = {0, 2, 3, 4, 1};
@@ -949,29 +1011,8 @@ RbStatus rb::conv_run(const RbConvProblem* p, int result_type, void* filter, voi
     } else if (pl.b_direct) B = filter; else { permute(filter, ws + pl.b_off, fsz, pl.fs, fil_yxkc, true, es); B = ws + pl.b_off; }
     C = pl.c_direct ? input : static_cast<void*>(ws + pl.c_off);
   }
-  // Unit-stride 16-bit NHWC convolutions whose filter fits into shared memory run on the halo kernel: the window of an
-  // output tile is loaded once instead of once per tap (csrc/conv_halo_sm100.cu). Variant bit 26 keeps the im2col form.
-  if (pl.a_implicit && !capture && pl.a_planes == 0 && !pl.a_up && pl.c_direct && p->stride_h == 1 && p->stride_w == 1 &&
-      (p->data_type == RB_F16 || p->data_type == RB_BF16) && (epi || pl.gemm.c_type == p->data_type) &&
-      !((rbGetGemmVariant() >> 26) & 1)) {
-    HaloConv hc;
-    hc.is_bf16 = p->data_type == RB_BF16;
-    hc.Y = p->y; hc.X = p->x; hc.dil_h = p->dil_h; hc.dil_w = p->dil_w;
-    const void* image;
-    void* result;
-    if (p->direction == 0) {
-      image = input; result = output;
-      hc.N = p->n; hc.H = p->h; hc.W = p->w; hc.C = p->c; hc.P = (int)ho; hc.Q = (int)wo; hc.Kout = p->k;
-      hc.pad_h = p->pad_h; hc.pad_w = p->pad_w; hc.pad_h_r = p->pad_h_r; hc.pad_w_r = p->pad_w_r;
-    } else {   // backward data: a forward convolution of the output gradient with the mirrored filter matrix B
-      image = output; result = input;
-      hc.N = p->n; hc.H = (int)ho; hc.W = (int)wo; hc.C = p->k; hc.P = p->h; hc.Q = p->w; hc.Kout = p->c;
-      hc.pad_h = (p->y - 1) * p->dil_h - p->pad_h; hc.pad_w = (p->x - 1) * p->dil_w - p->pad_w;
-      hc.pad_h_r = p->h - (int)ho - hc.pad_h + (p->y - 1) * p->dil_h; hc.pad_w_r = p->w - (int)wo - hc.pad_w + (p->x - 1) * p->dil_w;
-    }
-    hc.o_q = hc.Kout; hc.o_p = (long long)hc.Q * hc.Kout; hc.o_n = (long long)hc.P * hc.Q * hc.Kout;
-    if (conv_halo_applicable(hc)) return conv_halo_run(hc, image, B, result, stream_v, epi, pl.gemm.c_type);
-  }
+  if (on_halo)
+    return conv_halo_run(uhc, p->direction == 0 ? input : output, B, p->direction == 0 ? output : input, stream_v, epi, pl.gemm.c_type);
   if (pl.a_implicit) {
     ConvAOperand cv;
     if (p->direction == 0) {
@@ -981,6 +1022,7 @@ RbStatus rb::conv_run(const RbConvProblem* p, int result_type, void* filter, voi
       cv.P = (int)ho; cv.Q = (int)wo; cv.Y = p->y; cv.X = p->x;
       cv.stride_h = p->stride_h; cv.stride_w = p->stride_w; cv.dil_h = p->dil_h; cv.dil_w = p->dil_w;
       cv.pad_h = p->pad_h; cv.pad_w = p->pad_w; cv.pad_h_hi = p->pad_h_r; cv.pad_w_hi = p->pad_w_r;
+      if (pl.c_remap) { cv.c_rows_per_img = (int)(ho * wo); cv.c_img_stride = pl.os[0]; cv.c_col_stride = pl.os[2]; }
     } else {
       // backward data, unit stride: "image" = output gradient (ho x wo x k), "output pixels" = input pixels (h x w)
       const int uh = ((int)ho - 1) * p->stride_h + 1, uw = ((int)wo - 1) * p->stride_w + 1;   // = ho, wo at unit stride
@@ -1005,7 +1047,7 @@ RbStatus rb::conv_run(const RbConvProblem* p, int result_type, void* filter, voi
     st = gemm_run(&pl.gemm, epi, A, B, C, pl.gemm_ws ? ws + pl.gemm_off : nullptr, pl.gemm_ws, stream_v, nullptr, capture);
   }
   if (st != RB_SUCCESS) return st;
-  if (!pl.c_direct) {
+  if (!pl.c_direct && !pl.c_remap) {
     if (p->direction == 0) permute(C, output, osz, pl.os, act_gmat, false, es_c);
     else if (p->direction == 2) permute(C, filter, fsz, pl.fs, fil_kyxc, false, es_c);
     else permute(C, input, isz, pl.is, act_gmat, false, es_c);

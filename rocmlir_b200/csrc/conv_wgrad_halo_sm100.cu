@@ -132,6 +132,8 @@ conv_wgrad_halo_kernel(const __grid_constant__ WgradMaps maps, const __grid_cons
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
     // All 32 lanes run the loop (its counters and descriptor words are warp-uniform); one elected lane issues.
+    // one lane, chosen once: the commits must come from the thread that issued the MMAs they track
+    const bool leader = elect_one();
     const int ksteps = p.ksteps, Kout = p.Kout;
     const uint32_t stages = (uint32_t)p.stages, idesc = p.idesc;
     const bool tracing = p.trace != nullptr;
@@ -157,15 +159,15 @@ conv_wgrad_halo_kernel(const __grid_constant__ WgradMaps maps, const __grid_cons
         const uint32_t accum = (t | ks) ? 1u : 0u;
         for (int j = 0; j < my_pairs; ++j) {
           const uint32_t a_lo = (x_lo + p.pair_off[pair0 + j] + koff) | (p.pair_lbo[pair0 + j] << 16);
-          if (elect_one()) umma_ss<kKindF16, 1>(tmem_base + (uint32_t)(j * Kout), desc64(a_lo, desc_hi), b_desc, idesc, accum);
+          if (leader) umma_ss<kKindF16, 1>(tmem_base + (uint32_t)(j * Kout), desc64(a_lo, desc_hi), b_desc, idesc, accum);
         }
         dy_lo += kStep;
         koff += kStep;
       }
-      if (elect_one()) tc_commit_addr1(smem_u32(&empty_bar[s]));
+      if (leader) tc_commit_addr1(smem_u32(&empty_bar[s]));
       if (++s == stages) { s = 0; ph ^= 1u; }
     }
-    if (elect_one()) tc_commit<1>(done_bar);
+    if (leader) tc_commit<1>(done_bar);
     if (tracing && lane_id() == 0) {
       p.trace[blockIdx.x * 16 + 2] = (unsigned long long)w_full;
       p.trace[blockIdx.x * 16 + 4] = (unsigned long long)(clock64() - t_begin);

@@ -633,6 +633,8 @@ RbStatus rb::gemm_run(const RbGemmProblem* p, const RbEpilogue* epi, const void*
   }
   const size_t es_c = dtype_bytes(p->c_type);
   void* partial = splits > 1 ? static_cast<void*>(wsb + ws.partial_off) : nullptr;
+  if (splits > 1 && conva && conva->c_rows_per_img > 0)
+    return fail(RB_UNSUPPORTED, "a channel-major result cannot be combined with a K split");
   if (splits > 1) {
     // every K range writes raw accumulators into its own plane; the reduction applies the epilogue
     kp.c = partial;
@@ -649,6 +651,14 @@ RbStatus rb::gemm_run(const RbGemmProblem* p, const RbEpilogue* epi, const void*
     kp.c_stride_g = (long long)p->m * p->n;
     kp.vec_ok = (!p->trans_c && ((size_t)p->n * es_c) % 16 == 0 && reinterpret_cast<uintptr_t>(c) % 16 == 0) ? 1 : 0;
     kp.c_tma = (kp.vec_ok && !cfg.plain_stores) ? 1 : 0;
+    if (conva && conva->c_rows_per_img > 0) {   // NKHW result: strided element stores, coalesced along the pixels
+      kp.c_rows_per_img = conva->c_rows_per_img;
+      kp.c_img_stride = conva->c_img_stride;
+      kp.c_stride_m = 1;
+      kp.c_stride_n = conva->c_col_stride;
+      kp.vec_ok = 0;
+      kp.c_tma = 0;
+    }
     kp.epi = ep;
   }
   if (kp.c_tma) {

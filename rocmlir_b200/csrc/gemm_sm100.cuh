@@ -112,6 +112,10 @@ struct GemmParams {
   long long wait_cycles;      // budget of every bounded wait in SM cycles (rbSetWaitLimit; default kWaitCycles)
   int stages;                 // shared-memory ring depth (<= GemmSmemLayout::kMaxStages), a multiple of kpr
   int kpr;                    // K blocks per barrier round (1, 2 or 4): one full/empty barrier pair serves kpr ring slots
+  // Channel-major convolution result (NKHW) written by the epilogue itself: row m = (image, pixel) with c_rows_per_img
+  // pixels per image goes to image * c_img_stride + pixel * c_stride_m, column n adds n * c_stride_n. 0 = plain rows.
+  int c_rows_per_img;
+  long long c_img_stride;
 };
 
 // Implicit B operand: base coordinates of output pixel `pix` (row-major n, p, q) and the tap / channel chunk of
@@ -564,8 +568,11 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
         }
         __syncwarp();
       }
-      const long long c_row_off =
-          (long long)w.split * p.split_stride + (long long)g * p.c_stride_g + row * p.c_stride_m;
+      long long c_row_off = (long long)w.split * p.split_stride + (long long)g * p.c_stride_g + row * p.c_stride_m;
+      if (p.c_rows_per_img) {   // lanes of a warp are consecutive pixels: every column store covers 32 contiguous elements
+        const long long img = row / p.c_rows_per_img;
+        c_row_off = img * p.c_img_stride + (row - img * p.c_rows_per_img) * p.c_stride_m;
+      }
       // what this thread's row contributes to the fused elementwise steps (row / scalar bias, residual address)
       EpiRow erow;
       if ((p.epi.flags & RB_EPI_BIAS) && (p.epi.flags & (RB_EPI_BIAS_ROW | RB_EPI_BIAS_SCALAR)))
@@ -679,9 +686,29 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
           ++nstores;
         }
       }
+      // Channel-major f32 result of a convolution (NKHW): one store per column, the warp's 32 lanes are 32 consecutive
+      // pixels of the column's image plane
+      const bool fast_remap = w.kind == 0 && p.c_rows_per_img && p.epi.flags == 0 && !p.acc_is_int && !probe && p.c_type == RB_F32;
+      if (fast_remap) {
+        const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + buf * kMaxBN;
+#pragma unroll 1
+        for (int c = 0; c < ngroups; ++c) {
+          const int n0 = nb * p.bn + c * 32;
+          if (n0 >= p.N) break;  // warp-uniform
+          uint32_t v[32];
+          tmem_ld32(taddr + c * 32, v);
+          tmem_ld_wait();
+          if (row_ok) {
+            float* d = static_cast<float*>(p.c) + c_row_off + (long long)n0 * p.c_stride_n;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (n0 + j < p.N) d[(long long)j * p.c_stride_n] = __uint_as_float(v[j]);
+          }
+        }
+      }
       // Fused elementwise work (or 1-byte / converted outputs) on whole tiles through TMA stores: the general loop's
       // body without its stream-K and plain-store branches.
-      const bool fast_epi = !fast16 && !fast32 && w.kind == 0 && p.c_tma && !probe && !raw_i32;
+      const bool fast_epi = !fast16 && !fast32 && !fast_remap && w.kind == 0 && p.c_tma && !probe && !raw_i32;
       if (fast_epi) {
         const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + buf * kMaxBN;
 #pragma unroll 1
@@ -726,7 +753,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
         }
       }
 #pragma unroll 1
-      for (int c = 0; c < ngroups && !fast16 && !fast32 && !fast_epi; ++c) {
+      for (int c = 0; c < ngroups && !fast16 && !fast32 && !fast_epi && !fast_remap; ++c) {
         const int n0 = nb * p.bn + c * 32;
         if (n0 >= p.N) break;  // warp-uniform
         if (probe & 2) break;

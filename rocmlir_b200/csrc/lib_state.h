@@ -54,6 +54,10 @@ struct ConvAOperand {
   int stride_h, stride_w, dil_h, dil_w;
   int pad_h, pad_w;          // base pixel of output (p, q) = (p*stride_h - pad_h, q*stride_w - pad_w); may be negative pads
   int pad_h_hi, pad_w_hi;    // upper paddings (bounding box of the base pixel)
+  // Result stored channel-major per image (NKHW) by the epilogue: element (row = image * c_rows_per_img + pixel, col) at
+  // image * c_img_stride + col * c_col_stride + pixel. 0 = the plain [rows][cols] result.
+  int c_rows_per_img = 0;
+  long long c_img_stride = 0, c_col_stride = 0;
 };
 // rbGemm with an optional implicit operand (then `a` (or `b`) is ignored, trans_a (trans_b) must be 0, g must be 1).
 // With `capture` nothing is launched: the call prepares everything as usual and writes the one kernel launch it
@@ -87,6 +91,13 @@ struct HaloConv {
   int pad_h, pad_w, pad_h_r, pad_w_r;
   int is_bf16;
   long long o_n, o_p, o_q;
+  // Backward data reading the KYXC filter tensor as it lies (no rearranged copy): `filter_matrix` is then the filter
+  // itself, [C = conv output channels][FY][FX][Kout = conv input channels, contiguous] with element strides f_sk, f_sy,
+  // f_sx, and tap (y', x') of the raster is filter tap (fy0 + fsy * (Y-1-y'), fx0 + fsx * (X-1-x')).
+  bool b_mn = false;
+  int FY = 0, FX = 0;
+  long long f_sk = 0, f_sy = 0, f_sx = 0;
+  int fy0 = 0, fsy = 1, fx0 = 0, fsx = 1;
 };
 bool conv_halo_applicable(const HaloConv& c);
 RbStatus conv_halo_run(const HaloConv& c, const void* image, const void* filter_matrix, void* out, void* stream,

@@ -53,23 +53,32 @@ def test_folded_depth_needs_the_gathered_input():
 
 
 def test_strided_backward_data_runs_by_pixel_classes():
-    # ResNet 3x3 stride-2 layer, NHWC f16: one filter pass and ONE launch of the halo kernel for the four classes
+    # ResNet 3x3 stride-2 layer, NHWC f16: ONE launch of the halo kernel for the four classes, the mirrored taps read
+    # straight from the KYXC filter (no filter pass)
     c = ConvConfig(n=8, c=128, k=128, h=28, w=28, y=3, x=3, stride_h=2, stride_w=2, pad_h=1, pad_w=1,
                    fil_layout="kyxc", in_layout="nhwc", out_layout="nhwk")
-    assert kernels2(c, 1) == 2
+    assert kernels2(c, 1) == 1
     # the same layer in f32 keeps the class GEMMs and the interleaving pass (the halo kernel is 16-bit)
     assert kernels2(c, 1, torch.float32) > 2
-    # 1x1 stride 2: three of the four classes receive no tap: zero fill, filter pass, one launch
+    # 1x1 stride 2: three of the four classes receive no tap: zero fill, one launch
     p1 = ConvConfig(n=8, c=64, k=128, h=28, w=28, y=1, x=1, stride_h=2, stride_w=2, fil_layout="kyxc",
                     in_layout="nhwc", out_layout="nhwk")
-    assert kernels2(p1, 1) == 3
+    assert kernels2(p1, 1) == 2
     # a 3 x 3 stride has nine classes: three launches of up to four
     s3 = ConvConfig(n=4, c=64, k=64, h=27, w=27, y=3, x=3, stride_h=3, stride_w=3, fil_layout="kyxc",
                     in_layout="nhwc", out_layout="nhwk")
-    assert kernels2(s3, 1) == 1 + 3
-    # unit stride keeps the single implicit GEMM (+ the mirrored filter pass)
-    u = ConvConfig(n=8, c=128, k=128, h=28, w=28, y=3, x=3, pad_h=1, pad_w=1, fil_layout="kyxc", in_layout="nhwc",
+    assert kernels2(s3, 1) == 3
+    # a filter that is not channels-last (KCYX) needs the mirrored sub-filter pass
+    kc = ConvConfig(n=8, c=128, k=128, h=28, w=28, y=3, x=3, stride_h=2, stride_w=2, pad_h=1, pad_w=1,
+                    fil_layout="kcyx", in_layout="nhwc", out_layout="nhwk")
+    assert kernels2(kc, 1) == 2
+    # unit stride: one launch of the halo kernel (mirrored taps read from the filter in place) when the filter fits into
+    # shared memory; a 3x3 filter over 128 x 128 channels does not (288 KB) and keeps the implicit GEMM + filter pass
+    u = ConvConfig(n=8, c=64, k=64, h=28, w=28, y=3, x=3, pad_h=1, pad_w=1, fil_layout="kyxc", in_layout="nhwc",
                    out_layout="nhwk")
-    assert kernels2(u, 1) == 2
+    assert kernels2(u, 1) == 1 and kernels2(u, 0) == 1
+    big = ConvConfig(n=8, c=128, k=128, h=28, w=28, y=3, x=3, pad_h=1, pad_w=1, fil_layout="kyxc", in_layout="nhwc",
+                     out_layout="nhwk")
+    assert kernels2(big, 1) == 2
     # unit-stride backward weight: the halo weight-gradient kernel and the sum of its slabs
     assert kernels2(u, 2) == 2
