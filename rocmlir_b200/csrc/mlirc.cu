@@ -806,7 +806,7 @@ struct Matcher {
   }
 
   // [batch...] x R x C matrix stored row-major (trans = 0) or column-major (trans = 1), batches dense outside
-  bool matrix(const Type* t, int* g, int* rows, int* cols, int* trans) {
+  bool matrix(const Type* t, int* g, int* rows, int* cols, int* trans, bool* batch_shared = nullptr) {
     if (!t || t->kind != Type::Shaped || t->shape.size() < 2) return fail("a dot operand must be a shaped tensor of rank >= 2");
     const size_t n = t->shape.size();
     int64_t G = 1;
@@ -816,11 +816,17 @@ struct Matcher {
     if ((sc == 1 || C == 1) && (sr == C || R == 1)) *trans = 0;
     else if ((sr == 1 || R == 1) && (sc == R || C == 1)) *trans = 1;
     else return fail("a dot operand must be a dense row-major or column-major matrix (strides " + dims_text(t->strides) + ")");
+    // one matrix shared by every batch (a multibroadcast along the batch dimensions: stride 0)
+    bool shared = G > 1;
+    for (size_t i = 0; i + 2 < n; ++i)
+      if (t->shape[i] != 1 && t->strides[i] != 0) shared = false;
+    if (batch_shared) *batch_shared = shared;
     int64_t acc = R * C;
-    for (int i = (int)n - 3; i >= 0; --i) {
-      if (t->shape[i] != 1 && t->strides[i] != acc) return fail("batch dimensions of a dot operand must be dense");
+    for (int i = (int)n - 3; i >= 0 && !shared; --i) {
+      if (t->shape[i] != 1 && t->strides[i] != acc) return fail("batch dimensions of a dot operand must be dense (or broadcast with stride 0)");
       acc *= t->shape[i];
     }
+    if (shared && !batch_shared) return fail("only the second dot operand may be shared between the batches");
     if (G > 0x7fffffff || R > 0x7fffffff || C > 0x7fffffff) return fail("extent exceeds 2^31");
     *g = (int)G; *rows = (int)R; *cols = (int)C;
     return true;
@@ -828,8 +834,22 @@ struct Matcher {
 
   // logical (n, c, h, w)-style tensor -> layout string over `letters` (logical order) with the group letter inserted
   // before the channel letter `ch`
-  bool conv_layout(const Type* t, const char* letters, char ch, int64_t groups, char* out8) {
-    if (!t || t->kind != Type::Shaped || t->shape.size() != 4) return fail("convolution tensors must be shaped tensors of rank 4");
+  // A 1-D convolution (rank-3 tensors n, c, w) is the 2-D one with a unit image height, as MIGraphX itself expands it
+  // (mlir/lib/Conversion/MIGraphXToTosa/MIGraphXToTosa.cpp:241-275): the unit dimension goes in front of the width.
+  static Type with_unit_height(const Type* t) {
+    Type u = *t;
+    if (u.shape.size() == 3) {
+      u.shape.insert(u.shape.begin() + 2, 1);
+      u.strides.insert(u.strides.begin() + 2, t->strides[2] * t->shape[2]);
+    }
+    return u;
+  }
+
+  bool conv_layout(const Type* t0, const char* letters, char ch, int64_t groups, char* out8) {
+    if (!t0 || t0->kind != Type::Shaped || (t0->shape.size() != 4 && t0->shape.size() != 3))
+      return fail("convolution tensors must be shaped tensors of rank 4 (or 3: one image dimension)");
+    const Type expanded = with_unit_height(t0);
+    const Type* t = &expanded;
     const std::vector<int> order = memory_order(t);
     if (!dense_in(t, order)) return fail("convolution tensors must be dense in some dimension order (strides " + dims_text(t->strides) + ")");
     if (groups > 1 && t->shape[strchr(letters, ch) - letters] % groups) return fail("channels are not divisible by the group count");
@@ -913,7 +933,10 @@ struct Matcher {
     if (L->kind == kGemmKind) {
       int g, m, n2, tc;
       if (!matrix(rt, &g, &m, &n2, &tc)) return false;
-      if (g != L->gemm.g || m != L->gemm.m || n2 != L->gemm.n) return fail("the result's shape does not match the dot");
+      const bool folded = (long long)g * m == (long long)L->gemm.g * L->gemm.m && g != L->gemm.g;   // shared second operand
+      if (folded && tc) return fail("a second operand shared between the batches needs a row-major result");
+      if (folded && (L->epi.flags & RB_EPI_BIAS_ROW)) return fail("a per-row bias cannot follow a dot whose batch is folded into its rows");
+      if ((!folded && (g != L->gemm.g || m != L->gemm.m)) || n2 != L->gemm.n) return fail("the result's shape does not match the dot");
       L->gemm.trans_c = tc;
       L->gemm.c_type = L->out_type;
     } else {
@@ -949,9 +972,17 @@ struct Matcher {
       L->kind = kGemmKind;
       RbGemmProblem& p = L->gemm;
       int g1, m, k, ta, g2, k2, n, tb;
-      if (!matrix(x->type, &g1, &m, &k, &ta) || !matrix(y->type, &g2, &k2, &n, &tb)) return false;
+      bool b_shared = false;
+      if (!matrix(x->type, &g1, &m, &k, &ta) || !matrix(y->type, &g2, &k2, &n, &tb, &b_shared)) return false;
       if (g1 != g2 || k != k2) return fail("dot operands do not agree in batch or reduction extent");
       p.g = g1; p.m = m; p.n = n; p.k = k;
+      if (b_shared) {
+        // G x M x K times one K x N matrix is the (G * M) x K x N product on the same bytes when A is stored row by row
+        // (broadcast batch operands: mlir/lib/Conversion/MIGraphXToTosa/MIGraphXToTosa.cpp:393-440)
+        if (ta) return fail("a second operand shared between the batches needs a row-major first operand");
+        if ((long long)g1 * m > 0x7fffffffLL) return fail("extent exceeds 2^31");
+        p.g = 1; p.m = g1 * m;
+      }
       p.trans_a = ta;          // A stored G x K x M when column-major
       p.trans_b = tb;          // B logical K x N: column-major storage is the library's trans_b (G x N x K)
       if (tx == ty) p.ab_type = tx;
@@ -965,13 +996,23 @@ struct Matcher {
     L->kind = kConvKind;
     RbConvProblem& c = L->conv;
     memset(&c, 0, sizeof(c));
-    const Type* in = x->type;
-    const Type* fil = y->type;
-    const Type* out = o->results[0]->type;
-    if (in->shape.size() != 4 || fil->shape.size() != 4 || out->shape.size() != 4) return fail("only 2-D convolutions are matched");
+    const size_t rank = x->type->shape.size();
+    if ((rank != 4 && rank != 3) || y->type->shape.size() != rank || o->results[0]->type->shape.size() != rank)
+      return fail("only 1-D and 2-D convolutions are matched");
+    const Type in_t = with_unit_height(x->type), fil_t = with_unit_height(y->type), out_t = with_unit_height(o->results[0]->type);
+    const Type* in = &in_t;
+    const Type* fil = &fil_t;
+    const Type* out = &out_t;
     std::vector<int64_t> pad, stride, dil;
     if (!ints(o->attr("padding"), &pad) || !ints(o->attr("stride"), &stride) || !ints(o->attr("dilation"), &dil))
       return fail("convolution needs padding, stride and dilation attributes");
+    if (rank == 3) {   // one image dimension: [pad_l, pad_r] (or [pad]), [stride], [dilation]
+      if (pad.size() == 1) pad = {pad[0], pad[0]};
+      if (pad.size() != 2 || stride.size() != 1 || dil.size() != 1) return fail("1-D convolution attributes of the wrong length");
+      pad = {0, pad[0], 0, pad[1]};
+      stride = {1, stride[0]};
+      dil = {1, dil[0]};
+    }
     if (pad.size() == 2) pad = {pad[0], pad[1], pad[0], pad[1]};
     if (pad.size() != 4 || stride.size() != 2 || dil.size() != 2) return fail("convolution attributes of the wrong length");
     const Attr* ga = o->attr("group");

@@ -10,9 +10,10 @@ problems and appends `arch <tab> numCUs <tab> problem <tab> perfConfig [<tab> TF
     python -m rocmlir_b200.tuning_driver -c "--operation gemm --arch sm_100a --t f16 --out_datatype f16 --g 1 --m 4096 --n 4096 --k 4096"
 
 A problem is one line of `--key value` options as miirCreateHandle takes them ('#' starts a comment). Every
-configuration is timed with CUDA events over `--iters` launches after two warm-up launches, operands larger than L2
-are not needed for a ranking (all configurations see the same cache state); operands hold random values of the
-element type, because all-zero data draws less power and runs at clocks real data never sees. The library loads the written file as its
+configuration is timed with CUDA events over `--iters` launches after two warm-up launches, rotating over enough
+operand sets that no launch finds its inputs in L2 (a ranking taken on L2-resident operands picked tiles that lose on
+cold ones); operands hold random values of the element type, because all-zero data draws less power and runs at
+clocks real data never sees. The library loads the written file as its
 default database when it lies at tuned/sm_100a.tsv beside the shared library, or is named by RB_TUNING_DB.
 """
 from __future__ import annotations
@@ -25,6 +26,7 @@ from typing import List, Optional, Tuple
 from . import _lib as L
 from . import miir, tuning
 
+L2_FLUSH_BYTES = 300 << 20
 SPACES = {"quick": tuning.QUICK, "full": tuning.FULL, "exhaustive": tuning.EXHAUSTIVE}
 
 
@@ -62,8 +64,8 @@ def _random_operand(nbytes: int, options: str):
     return x.view(torch.uint8)
 
 
-def tune_one(options: str, space: int, iters: int) -> Tuple[Optional[str], List[Tuple[str, float]]]:
-    """Returns (problem key, [(perf_config, milliseconds)] fastest first)."""
+def tune_one(options: str, space: int, iters: int) -> Tuple[Optional[str], List[Tuple[str, float]], Optional[float]]:
+    """Returns (problem key, [(perf_config, milliseconds)] fastest first, milliseconds of the library's own rule)."""
     import torch
     prob = tuning.Problem(options)
     key = prob.key
@@ -71,33 +73,39 @@ def tune_one(options: str, space: int, iters: int) -> Tuple[Optional[str], List[
     base = re.sub(r"--perf_config\s+\S+", "", options)
     results = []
     bufs = None
-    for perf in configs:
+    for perf in [None] + list(configs):  # None: the library's own rule (what a launch does without a database)
         try:
-            h = miir.Handle(base + " --perf_config " + perf)
+            h = miir.Handle(base if perf is None else base + " --perf_config " + perf)
         except ValueError:
             continue                     # not applicable to this problem
         with h:
             h.lower_tuning_params()
             if bufs is None:
-                bufs = [_random_operand(s, options) if s else None for s in h.arg_sizes()]
+                # enough independent operand sets that consecutive launches never find their inputs in the 126 MB L2
+                sizes = h.arg_sizes()
+                nsets = max(1, min(16, -(-L2_FLUSH_BYTES // max(1, sum(sizes)))))
+                bufs = [[_random_operand(s, options) if s else None for s in sizes] for _ in range(nsets)]
             ws = torch.empty(max(16, h.workspace_size), dtype=torch.uint8, device="cuda")
-            run = lambda: h.launch(bufs[0], bufs[1], bufs[2], extra=bufs[3], workspace=ws)
+            run = lambda b: h.launch(b[0], b[1], b[2], extra=b[3], workspace=ws)
             try:
-                run(); run()
-            except miir.MiirError:
+                for b in bufs[:2]:
+                    run(b)
+            except miir.MiirError as e:
+                print(f"    {perf or 'rule-based choice'}: not runnable ({e})", file=sys.stderr)
                 continue
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda.synchronize()
             e0.record()
-            for _ in range(iters):
-                run()
+            for i in range(iters):
+                run(bufs[i % len(bufs)])
             e1.record()
             torch.cuda.synchronize()
             if L.kernel_status() != 0:
                 raise RuntimeError(f"kernel status {L.kernel_status():#x} under {perf}")
             results.append((perf, e0.elapsed_time(e1) / iters))
-    results.sort(key=lambda r: r[1])
-    return key, results
+    default_ms = next((ms for perf, ms in results if perf is None), None)
+    results = sorted((r for r in results if r[0] is not None), key=lambda r: r[1])
+    return key, results, default_ms
 
 
 def main(argv: Optional[List[str]] = None) -> int:
@@ -107,6 +115,8 @@ def main(argv: Optional[List[str]] = None) -> int:
     ap.add_argument("--tuning-space", default="full", choices=sorted(SPACES))
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--tflops", action="store_true", help="fifth column: TFlops of the winner")
+    ap.add_argument("--min-gain", type=float, default=0.0,
+                    help="write a row only when the winner beats the library's own rule by this fraction (0: always, as tuningRunner.py does)")
     ap.add_argument("-o", "--output", default="-", help="database file to APPEND to ('-': stdout), like tuningRunner.py")
     args = ap.parse_args(argv)
     problems = list(args.config)
@@ -120,7 +130,7 @@ def main(argv: Optional[List[str]] = None) -> int:
         cols = "# arch\tnumCUs\ttestVector\tperfConfig" + ("\tTFlops" if args.tflops else "")
         print(f"{cols} ({args.tuning_space})", file=out)
         for options in problems:
-            key, results = tune_one(options, SPACES[args.tuning_space], args.iters)
+            key, results, default_ms = tune_one(options, SPACES[args.tuning_space], args.iters)
             if not key or not results:
                 print(f"rocmlir-tuning-driver: nothing to tune for: {options}", file=sys.stderr)
                 continue
@@ -128,6 +138,11 @@ def main(argv: Optional[List[str]] = None) -> int:
             tf = flops_of(options) / (ms * 1e-3) / 1e12
             print(f"{key.replace(chr(9), ' | ')}: {perf} {ms * 1e3:.1f} us {tf:.1f} TFlops "
                   f"(of {len(results)} configurations; slowest {results[-1][1] * 1e3:.1f} us)", file=sys.stderr)
+            gain = (default_ms / ms - 1.0) if default_ms else float("inf")
+            if gain < args.min_gain:
+                print(f"    rule-based choice {default_ms * 1e3:.1f} us: winner gains {gain * 100:.1f} % < {args.min_gain * 100:.0f} %, no row written",
+                      file=sys.stderr)
+                continue
             print(f"{key}\t{perf}" + (f"\t{tf:.2f}" if args.tflops else ""), file=out, flush=True)
     return 0
 

@@ -192,3 +192,51 @@ def test_parser_reads_the_references_own_fusion_tests(built):
         m.close()
     assert parsed >= len(files) * 0.6, (parsed, len(files))
     assert must_fuse <= seen, must_fuse - seen
+
+
+CONV_1D = """
+module {
+  func.func @conv1d_bias(%x: !migraphx.shaped<4x64x100xf16, 6400x1x64>, %w: !migraphx.shaped<128x64x5xf16, 320x1x64>,
+                         %bias: !migraphx.shaped<1x128x1xf16, 128x1x1>) -> !migraphx.shaped<4x128x50xf16, 6400x1x128> attributes {kernel, arch = "sm_100a"} {
+    %0 = migraphx.convolution %x, %w {dilation = [1], group = 1 : i64, padding = [2, 2], padding_mode = 0 : i64, stride = [2]} : <4x64x100xf16, 6400x1x64>, <128x64x5xf16, 320x1x64> -> <4x128x50xf16, 6400x1x128>
+    %1 = migraphx.add %0, %bias : <4x128x50xf16, 6400x1x128>, <1x128x1xf16, 128x1x1> -> <4x128x50xf16, 6400x1x128>
+    %2 = migraphx.relu %1 : <4x128x50xf16, 6400x1x128> -> <4x128x50xf16, 6400x1x128>
+    return %2 : !migraphx.shaped<4x128x50xf16, 6400x1x128>
+  }
+}
+"""
+
+
+def test_one_dimensional_convolution_is_the_unit_height_problem(built):
+    """A convolution over rank-3 tensors (n, c, w) is matched as the 2-D problem with a unit image height, the way
+    MIGraphX itself expands it (mlir/lib/Conversion/MIGraphXToTosa/MIGraphXToTosa.cpp:241-275); here channels-last."""
+    from rocmlir_b200.mlirc import Module
+    with Module(CONV_1D) as m:
+        m.high_level()
+        key = m.key
+        assert "convfp16 -F 1" in key and "-n 4 -c 64 -H 1 -W 100 -k 128 -y 1 -x 5 -p 0 -q 2 -u 1 -v 2 -l 1 -j 1 -g 1" in key
+        assert "-I N01GC" in key or "-I N01C" in key or "-I NHWC" in key.upper(), key
+        m.backend("sm_100a")
+        assert m.binary()[:4] == b"\x7fELF"
+
+
+DOT_SHARED_B = """
+func.func @dot_shared_b(%a: !migraphx.shaped<8x96x64xf16, 6144x64x1>, %b: !migraphx.shaped<64x80xf16, 80x1>) -> !migraphx.shaped<8x96x80xf16, 7680x80x1> attributes {kernel, arch = "sm_100a"} {
+  %0 = migraphx.multibroadcast %b {out_dyn_dims = [], out_lens = [8, 64, 80]} : <64x80xf16, 80x1> -> <8x64x80xf16, 0x80x1>
+  %1 = migraphx.dot %a, %0 : <8x96x64xf16, 6144x64x1>, <8x64x80xf16, 0x80x1> -> <8x96x80xf16, 7680x80x1>
+  return %1 : !migraphx.shaped<8x96x80xf16, 7680x80x1>
+}
+"""
+
+
+def test_batched_dot_with_a_shared_second_operand_folds_the_batch_into_m(built):
+    """A B operand broadcast along the batch (stride 0) makes G x M x K . K x N the (G M) x K . K x N product on the same
+    bytes: one group of 768 rows instead of 8 groups of 96."""
+    from rocmlir_b200.mlirc import Module, PipelineError
+    with Module(DOT_SHARED_B) as m:
+        m.high_level()
+        assert "-transA false -transB false -g 1 -m 768 -n 80 -k 64" in m.key
+    col_major_a = DOT_SHARED_B.replace("8x96x64xf16, 6144x64x1", "8x96x64xf16, 6144x1x96")
+    with Module(col_major_a) as m:
+        with pytest.raises(PipelineError, match="row-major first operand"):
+            m.high_level()

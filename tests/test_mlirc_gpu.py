@@ -5,7 +5,7 @@ import pytest
 
 import oracle
 from helpers import from_device, reference_random, to_device, uniform_f32, uniform_int8
-from test_mlirc_cpu import CONV_BIAS_CLIP_NHWC, DOT_ADD, DOT_TRANSB_BIAS_RELU, QUANT_CONV
+from test_mlirc_cpu import CONV_1D, CONV_BIAS_CLIP_NHWC, DOT_ADD, DOT_TRANSB_BIAS_RELU, QUANT_CONV
 
 pytestmark = pytest.mark.gpu
 
@@ -55,6 +55,19 @@ def test_convolution_bias_clip_nhwc_f16(cuda_device):
     ocfg, (braw, xraw, wraw), ref = _conv_case()
     out = torch.zeros(ocfg.numel("out"), dtype=torch.float16, device="cuda")
     _launch(CONV_BIAS_CLIP_NHWC, [to_device(braw, oracle.F16), to_device(xraw, oracle.F16), to_device(wraw, oracle.F16), out])
+    np.testing.assert_array_equal(from_device(out, oracle.F16).ravel(), ref.ravel())
+
+
+def test_one_dimensional_convolution_bias_relu(cuda_device):
+    """Rank-3 tensors (n, c, w), channels last, stride 2, padding 2: the unit-height 2-D problem against the oracle."""
+    import torch
+    ocfg = oracle.Conv(n=4, c=64, k=128, h=1, w=100, y=1, x=5, stride_w=2, pad_w=2, fil_layout="gkyxc", in_layout="nhwgc",
+                       out_layout="nhwgk")
+    (xf, xraw), (wf, wraw), (bf, braw) = reference_random([(ocfg.numel("in"),), (ocfg.numel("fil"),), (128,)], oracle.F16, seed=3)
+    acc = oracle.conv_f32(ocfg, 0, wf, xf, None, threads=oracle.max_threads())
+    ref = oracle.from_f32(oracle.epilogue(acc, 128, bias=bf, relu=True, mid_type=oracle.F16), oracle.F16)
+    out = torch.zeros(ocfg.numel("out"), dtype=torch.float16, device="cuda")
+    _launch(CONV_1D, [to_device(xraw, oracle.F16), to_device(wraw, oracle.F16), to_device(braw, oracle.F16), out])
     np.testing.assert_array_equal(from_device(out, oracle.F16).ravel(), ref.ravel())
 
 
