@@ -286,6 +286,15 @@ RB_EXPORT RbStatus rbAttentionWs(const RbAttentionProblem *p, const void *q, con
 RB_EXPORT RbStatus rbAttention(const RbAttentionProblem *p, const void *q, const void *k, const void *v, void *o,
                                void *stream);
 
+/* int4 operands (migraphx.unpack + dequantizelinear in front of a contraction: mlir/include/mlir/Dialect/MIGraphX/IR/
+ * MIGraphX.td:183-212, mlir/lib/Dialect/MIGraphX/Transforms/RealizeInt4.cpp). `packed` holds two 4-bit values per byte
+ * along the contiguous dimension; out[2i] = (low nibble - zero_point) * scale, out[2i+1] = (high nibble - zero_point) *
+ * scale, rounded once to out_type (RB_F16, RB_BF16, RB_F32), or the plain sign- / zero-extended values for RB_I8
+ * (scale and zero_point unused). `out` has 2 * packed_bytes elements and then is an ordinary operand of rbGemm / rbConv.
+ * The reference fuses this into its operand loads; here it is one pass through memory. */
+RB_EXPORT RbStatus rbUnpackInt4(const void *packed, void *out, int64_t packed_bytes, int32_t is_unsigned, int32_t out_type,
+                                float scale, int32_t zero_point, void *stream);
+
 /* GEMM + GEMM: O[g] = (A[g] . B1[g]) . B2[g], A G x M x K1, B1 G x K1 x N1, B2 G x N1 x N2, O G x M x N2, the
  * intermediate rounded to the element type, both products accumulated in f32 — the attention skeleton of the
  * reference with the softmax removed (mlir/include/mlir/Dialect/Rock/IR/Rock.h:52-56,

@@ -133,6 +133,8 @@ def lib() -> C.CDLL:
         l.rbAttentionWs.restype = C.c_int
         l.rbAttentionWs.argtypes = [C.POINTER(RbAttentionProblem), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                     C.c_void_p, C.c_size_t, C.c_void_p]
+        l.rbUnpackInt4.restype = C.c_int
+        l.rbUnpackInt4.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_float, C.c_int32, C.c_void_p]
         l.rbGemmGemmWorkspaceSize.restype = C.c_size_t
         l.rbGemmGemmWorkspaceSize.argtypes = [C.c_int32] * 6
         l.rbGemmGemm.restype = C.c_int

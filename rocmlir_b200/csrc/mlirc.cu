@@ -118,6 +118,15 @@ struct Lowered {
   EpiRecipe epi;
   int out_type = -1;            // element type of the result after the epilogue
   int arg_a = -1, arg_b = -1;   // function arguments feeding the contraction (gemm: a, b; conv: input, filter)
+  // an operand that arrives as packed int4 (migraphx.unpack, optionally followed by dequantizelinear with a literal
+  // scale / zero point): one pass writes it in the contraction's element type into the workspace first
+  struct Int4Operand {
+    bool on = false;
+    int is_unsigned = 0, out_type = -1, zero = 0;
+    float scale = 1.0f;
+    long long packed_bytes = 0;
+    size_t out_bytes = 0;
+  } int4_a, int4_b;
   int nargs = 0;                // function arguments (the result follows them in the kernel's argument list)
   std::vector<const Type*> arg_types;   // arguments then results
   std::string name, arch, perf_config;
@@ -364,7 +373,12 @@ struct Reader {
       bool is_float;
       if (eat("true")) { a.i = 1; a.f = 1; is_float = false; }
       else if (eat("false")) { a.i = 0; a.f = 0; is_float = false; }
-      else if (!number(&a.f, &a.i, &is_float)) { fail("only splat dense attributes are read"); return nullptr; }
+      else {
+        // a one-element list, dense<[0.25]>, is the same splat (mlir/test/fusion/pr-e2e/mixr-dot-int4-f16.mlir:9)
+        const bool bracket = eat('[');
+        if (!number(&a.f, &a.i, &is_float)) { fail("only splat dense attributes are read"); return nullptr; }
+        if (bracket && !eat(']')) { fail("only splat (one-value) dense attributes are read"); return nullptr; }
+      }
       if (!eat('>')) { fail("only splat dense attributes are read"); return nullptr; }
       if (!eat(':')) { fail("expected ':' after dense<>"); return nullptr; }
       a.kind = Attr::DenseSplat;
@@ -767,6 +781,10 @@ struct Source {
   double lit = 0;
   const Type* type = nullptr;      // the value's own type (after broadcasts)
   const Type* base = nullptr;      // the argument's / literal's type before broadcasting
+  // an argument seen through migraphx.unpack (int4 pairs -> i8) and perhaps dequantizelinear: still kind Arg
+  bool unpacked = false, dequantized = false;
+  int is_unsigned = 0, zero = 0;
+  float scale = 1.0f;
 };
 
 struct Matcher {
@@ -897,6 +915,40 @@ struct Matcher {
         src[o->results[0]] = s;
         continue;
       }
+      if (n == "migraphx.unpack") {
+        // MIGraphX.td:183-212: doubles `axis` by splitting every byte into its two 4-bit values
+        Source s = src[o->operands[0]];
+        const Type* it = o->operands[0]->type;
+        const Type* ot = o->results[0]->type;
+        const Attr* ax = o->attr("axis");
+        const Attr* un = o->attr("isUnsigned");
+        if (s.kind != Source::Arg || s.unpacked || s.type != s.base) return fail("unpack must read a function argument directly");
+        if (!ax || ax->kind != Attr::Int || !it || it->kind != Type::Shaped || ax->i != (int64_t)it->shape.size() - 1 ||
+            it->strides.back() != 1 || !ot || ot->shape.back() != 2 * it->shape.back())
+          return fail("unpack is supported along the last, contiguous dimension");
+        const std::vector<int> order = memory_order(it);
+        if (!dense_in(it, order)) return fail("the packed tensor must be dense");
+        s.unpacked = true;
+        s.is_unsigned = un && ((un->kind == Attr::Int && un->i != 0) || (un->kind == Attr::Raw && un->s == "true") ||
+                               (un->kind == Attr::String && un->s == "true")) ? 1 : 0;
+        s.type = ot;
+        src[o->results[0]] = s;
+        continue;
+      }
+      if (n == "migraphx.dequantizelinear" && !chain && !o->operands.empty() && src[o->operands[0]].kind == Source::Arg &&
+          src[o->operands[0]].unpacked) {
+        Source s = src[o->operands[0]];
+        if (s.dequantized) return fail("an operand is dequantised once");
+        double sc = 1.0, zp = 0.0;
+        if (o->operands.size() < 2 || !literal_of(o->operands[1], &sc)) return fail("the scale of an int4 operand must be a literal");
+        if (o->operands.size() > 2 && !literal_of(o->operands[2], &zp)) return fail("the zero point of an int4 operand must be a literal");
+        s.dequantized = true;
+        s.scale = (float)sc;
+        s.zero = (int)zp;
+        s.type = o->results[0]->type;
+        src[o->results[0]] = s;
+        continue;
+      }
       const bool is_contraction = n == "migraphx.dot" || n == "migraphx.quant_dot" || n == "migraphx.convolution" ||
                                   n == "migraphx.quant_convolution";
       if (is_contraction) {
@@ -991,8 +1043,23 @@ struct Matcher {
       else return fail("dot operands of different element types");
       p.c_type = tr;
       L->arg_a = src[x].arg; L->arg_b = src[y].arg;
+      for (int side = 0; side < 2; ++side) {
+        const Source& s = src[side ? y : x];
+        Lowered::Int4Operand& q = side ? L->int4_b : L->int4_a;
+        q.on = s.unpacked;
+        if (!s.unpacked) continue;
+        const Type* ot = (side ? y : x)->type;
+        q.is_unsigned = s.is_unsigned; q.zero = s.zero; q.scale = s.scale;
+        q.out_type = rb_type_of(ot->elem);
+        if (!s.dequantized && q.out_type != RB_I8) return fail("an unpacked int4 operand without dequantizelinear is i8");
+        long long elems = 1;
+        for (int64_t d : ot->shape) elems *= d;
+        q.packed_bytes = elems / 2;
+        q.out_bytes = (size_t)elems * dtype_bytes(q.out_type);
+      }
       return true;
     }
+    if (src[x].unpacked || src[y].unpacked) return fail("int4 operands are supported for dot, not for convolutions");
     L->kind = kConvKind;
     RbConvProblem& c = L->conv;
     memset(&c, 0, sizeof(c));
@@ -1455,6 +1522,7 @@ bool mlirGetBinary(MlirModule module, size_t* size, char* bin) {
 
 const char* rbModuleGetDiagnostic(MlirModule module) { return module.ptr ? module_of(module)->diagnostic.c_str() : ""; }
 
+static size_t int4_bytes(const Lowered::Int4Operand& q) { return q.on ? (q.out_bytes + 255) / 256 * 256 : 0; }
 static RbStatus module_ready(Operation* mod, size_t nargs) {
   if (!mod || !mod->lowered || !mod->lowered->applicable) return fail(RB_INVALID_PARAM, "run the pipelines on the module first");
   if (nargs != mod->lowered->arg_types.size())
@@ -1469,7 +1537,7 @@ size_t rbModuleGetWorkspaceSize(MlirModule module) {
   rbSetGemmVariant((int)L.variant);
   const size_t n = L.kind == kGemmKind ? rbGemmWorkspaceSize(&L.gemm) : rbConvEpiWorkspaceSize(&L.conv, L.out_type);
   rbSetGemmVariant(saved);
-  return n;
+  return n + int4_bytes(L.int4_a) + int4_bytes(L.int4_b);   // unpacked operands first, the kernel's own workspace behind them
 }
 static RbStatus module_run(MlirModule module, void* const* args, size_t nargs, void* ws, size_t ws_bytes, void* stream, RbKernelLaunch* capture) {
   Operation* mod = module_of(module);
@@ -1482,11 +1550,29 @@ static RbStatus module_run(MlirModule module, void* const* args, size_t nargs, v
   bool have = false;
   build_epilogue(L, args, &e, &have);
   void* result = args[nargs - 1];
+  const void* op_a = args[L.arg_a];
+  const void* op_b = args[L.arg_b];
+  if (L.int4_a.on || L.int4_b.on) {
+    if (capture) return fail(RB_UNSUPPORTED, "a kernel with int4 operands runs an unpacking pass first: it has no single-kernel binary");
+    const size_t need = int4_bytes(L.int4_a) + int4_bytes(L.int4_b);
+    if (!ws || ws_bytes < need) return fail(RB_WORKSPACE_TOO_SMALL, "workspace of " + std::to_string(rbModuleGetWorkspaceSize(module)) + " bytes required");
+    uint8_t* w = static_cast<uint8_t*>(ws);
+    for (int side = 0; side < 2; ++side) {
+      const Lowered::Int4Operand& q = side ? L.int4_b : L.int4_a;
+      if (!q.on) continue;
+      st = rbUnpackInt4(side ? op_b : op_a, w, q.packed_bytes, q.is_unsigned, q.out_type, q.scale, q.zero, stream);
+      if (st != RB_SUCCESS) return st;
+      (side ? op_b : op_a) = w;
+      w += int4_bytes(q);
+    }
+    ws = w;
+    ws_bytes -= need;
+  }
   const int saved = rbGetGemmVariant();
   rbSetGemmVariant((int)L.variant);
   if (L.kind == kGemmKind) {
-    st = capture ? rbGemmEncodeLaunch(&L.gemm, have ? &e : nullptr, args[L.arg_a], args[L.arg_b], result, capture)
-                 : rbGemm(&L.gemm, have ? &e : nullptr, args[L.arg_a], args[L.arg_b], result, ws, ws_bytes, stream);
+    st = capture ? rbGemmEncodeLaunch(&L.gemm, have ? &e : nullptr, op_a, op_b, result, capture)
+                 : rbGemm(&L.gemm, have ? &e : nullptr, op_a, op_b, result, ws, ws_bytes, stream);
   } else {
     // kernel-argument order of the library's convolution: (filter, input, output); migraphx.convolution takes (input, filter)
     st = capture ? rbConvEncodeLaunch(&L.conv, have ? &e : nullptr, L.out_type, args[L.arg_b], args[L.arg_a], result, capture)

@@ -240,3 +240,30 @@ def test_batched_dot_with_a_shared_second_operand_folds_the_batch_into_m(built):
     with Module(col_major_a) as m:
         with pytest.raises(PipelineError, match="row-major first operand"):
             m.high_level()
+
+
+# the shape of mlir/test/fusion/pr-e2e/mixr-dot-int4-f16.mlir at a size the tensor core sees: packed int4 weights as the
+# first operand, unpacked along the reduction dimension and dequantised with a literal scale, then dot
+DOT_INT4 = """
+func.func @mlir_unpack_dequantizelinear_dot(%arg0: !migraphx.shaped<1x96x64xi8, 6144x64x1>, %arg1: !migraphx.shaped<1x128x80xf16, 10240x80x1>) -> !migraphx.shaped<1x96x80xf16, 7680x80x1> attributes {kernel, arch = "sm_100a"} {
+  %0 = migraphx.literal (dense<[0.25]> : tensor<1xf16>) : <1xf16, 0>
+  %1 = migraphx.multibroadcast %0 {out_dyn_dims = [], out_lens = [1, 96, 128]} : <1xf16, 0> -> <1x96x128xf16, 0x0x0>
+  %2 = migraphx.unpack %arg0 {axis = 2 : i64, isUnsigned = false} : <1x96x64xi8, 6144x64x1> -> <1x96x128xi8, 12288x128x1>
+  %3 = migraphx.dequantizelinear %2, %1 : <1x96x128xi8, 12288x128x1>, <1x96x128xf16, 0x0x0> -> <1x96x128xf16, 12288x128x1>
+  %4 = migraphx.dot %3, %arg1 : <1x96x128xf16, 12288x128x1>, <1x128x80xf16, 10240x80x1> -> <1x96x80xf16, 7680x80x1>
+  return %4 : !migraphx.shaped<1x96x80xf16, 7680x80x1>
+}
+"""
+
+
+def test_int4_operand_is_unpacked_into_the_workspace(built):
+    from rocmlir_b200.mlirc import Module, PipelineError
+    with Module(DOT_INT4) as m:
+        m.high_level()
+        assert "-t f16 -out_datatype f16 -transA false -transB false -g 1 -m 96 -n 80 -k 128" in m.key
+        assert m.kernel_info()[0][0] == [1, 96, 64]          # the kernel's first argument is still the packed tensor
+        assert m.workspace_size >= 96 * 128 * 2              # room for the unpacked, dequantised operand
+    along_rows = DOT_INT4.replace("axis = 2 : i64", "axis = 1 : i64")
+    with Module(along_rows) as m:
+        with pytest.raises(PipelineError, match="last, contiguous dimension"):
+            m.high_level()

@@ -5,7 +5,7 @@ import pytest
 
 import oracle
 from helpers import from_device, reference_random, to_device, uniform_f32, uniform_int8
-from test_mlirc_cpu import CONV_1D, CONV_BIAS_CLIP_NHWC, DOT_ADD, DOT_TRANSB_BIAS_RELU, QUANT_CONV
+from test_mlirc_cpu import CONV_1D, CONV_BIAS_CLIP_NHWC, DOT_INT4, DOT_SHARED_B, DOT_ADD, DOT_TRANSB_BIAS_RELU, QUANT_CONV
 
 pytestmark = pytest.mark.gpu
 
@@ -69,6 +69,68 @@ def test_one_dimensional_convolution_bias_relu(cuda_device):
     out = torch.zeros(ocfg.numel("out"), dtype=torch.float16, device="cuda")
     _launch(CONV_1D, [to_device(xraw, oracle.F16), to_device(wraw, oracle.F16), to_device(braw, oracle.F16), out])
     np.testing.assert_array_equal(from_device(out, oracle.F16).ravel(), ref.ravel())
+
+
+def _unpack_int4(packed: np.ndarray, signed: bool) -> np.ndarray:
+    """MIGraphX.td:190-193: out[..., 2i] = in & 0xf, out[..., 2i+1] = in >> 4 (arithmetic when signed)."""
+    b = packed.astype(np.uint8)
+    lo, hi = (b & 0xF).astype(np.int16), (b >> 4).astype(np.int16)
+    if signed:
+        lo = np.where(lo > 7, lo - 16, lo)
+        hi = np.where(hi > 7, hi - 16, hi)
+    out = np.empty(packed.shape[:-1] + (2 * packed.shape[-1],), dtype=np.int16)
+    out[..., 0::2], out[..., 1::2] = lo, hi
+    return out
+
+
+def test_int4_weights_unpack_dequantize_dot(cuda_device):
+    """The graph of mlir/test/fusion/pr-e2e/mixr-dot-int4-f16.mlir: packed signed int4 operand -> unpack along the
+    reduction dimension -> x 0.25 (f16) -> dot with an f16 matrix, against numpy + the GEMM oracle."""
+    import torch
+    from rocmlir_b200 import _lib as L
+    from rocmlir_b200.mlirc import Module
+    rng = np.random.Generator(np.random.PCG64(11))
+    packed = rng.integers(0, 256, size=(1, 96, 64), dtype=np.uint8)
+    (bf, braw), = reference_random([(1, 128, 80)], oracle.F16, seed=2)
+    a = (_unpack_int4(packed, signed=True).astype(np.float32) * np.float32(0.25)).astype(np.float16).astype(np.float32)
+    ref = oracle.from_f32(oracle.gemm_f32(a, bf, 1, 96, 80, 128), oracle.F16)
+    out = torch.zeros((1, 96, 80), dtype=torch.float16, device="cuda")
+    with Module(DOT_INT4) as m:
+        m.high_level()
+        m.backend("sm_100a")
+        ws = torch.empty(m.workspace_size, dtype=torch.uint8, device="cuda")
+        m.launch([torch.from_numpy(packed.view(np.int8)).cuda(), to_device(braw, oracle.F16), out], workspace=ws)
+    torch.cuda.synchronize()
+    assert L.kernel_status() == 0
+    np.testing.assert_array_equal(from_device(out, oracle.F16).reshape(ref.shape), ref)
+
+
+@pytest.mark.parametrize("unsigned,out", [(0, "i8"), (1, "i8"), (0, "f16"), (1, "bf16"), (0, "f32")])
+def test_unpack_int4_entry_point(cuda_device, unsigned, out):
+    import ctypes as C
+    import torch
+    from rocmlir_b200 import _lib as L
+    rng = np.random.Generator(np.random.PCG64(5))
+    packed = rng.integers(0, 256, size=(7, 33), dtype=np.uint8)       # odd sizes: no vector assumptions
+    vals = _unpack_int4(packed, signed=not unsigned).astype(np.float32)
+    dt = {"i8": torch.int8, "f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}[out]
+    code = {"i8": L.I8, "f16": L.F16, "bf16": L.BF16, "f32": L.F32}[out]
+    scale, zero = (1.0, 0) if out == "i8" else (0.37, 3)
+    dst = torch.zeros((7, 66), dtype=dt, device="cuda")
+    src = torch.from_numpy(packed).cuda()
+    L.check(L.lib().rbUnpackInt4(src.data_ptr(), dst.data_ptr(), packed.size, unsigned, code, C.c_float(scale), zero, None))
+    torch.cuda.synchronize()
+    want = torch.from_numpy(vals if out == "i8" else (vals - zero) * np.float32(scale)).to(dt)
+    assert torch.equal(dst.cpu(), want)
+
+
+def test_shared_second_operand_runs_as_one_group(cuda_device):
+    import torch
+    (af, araw), (bf, braw) = reference_random([(8, 96, 64), (1, 64, 80)], oracle.F16, seed=4)
+    out = torch.zeros((8, 96, 80), dtype=torch.float16, device="cuda")
+    _launch(DOT_SHARED_B, [to_device(araw, oracle.F16), to_device(braw, oracle.F16), out])
+    ref = oracle.from_f32(oracle.gemm_f32(af.reshape(1, 768, 64), bf, 1, 768, 80, 64), oracle.F16)
+    np.testing.assert_array_equal(from_device(out, oracle.F16).reshape(ref.shape), ref)
 
 
 def test_client_launches_the_modules_kernel_from_the_binary(cuda_device):
