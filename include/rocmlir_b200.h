@@ -72,6 +72,9 @@ typedef enum RbStatus {
  *                                                       RB_EPI_BIAS_SCALAR it is the single element bias[0]
  *   x = x + residual[g][m][n]     if RB_EPI_RESIDUAL   (a tensor of C's shape and layout: the same-shape add of
  *                                                       mixr-gemm-add; then round_to(mid_type) if ROUND_MID)
+ *   x = f(x)                      if RB_EPI_UNARY      (one of the MIGraphX unary elementwise ops, `unary` = RbUnary:
+ *                                                       mlir/include/mlir/Dialect/MIGraphX/IR/MIGraphX.td:134-181; evaluated in f32,
+ *                                                       then round_to(mid_type) if ROUND_MID)
  *   x = max(x, 0)                 if RB_EPI_RELU
  *   x = min(max(x, lo), hi)       if RB_EPI_CLIP       (migraphx.clip, MIGraphXToTosa.cpp:1089-1101)
  *   x = x * out_recip             if RB_EPI_REQUANT    (out_recip = 1/scale computed by the caller in f32)
@@ -89,8 +92,15 @@ enum {
   RB_EPI_BIAS_ROW = 256,
   RB_EPI_BIAS_SCALAR = 512,
   RB_EPI_ZP_IN = 1024,
-  RB_EPI_ZP_OUT = 2048
+  RB_EPI_ZP_OUT = 2048,
+  RB_EPI_UNARY = 4096
 };
+
+/* RbEpilogue::unary (migraphx.abs / ceil / erf / exp / floor / log / neg / recip / rsqrt / sigmoid / sqrt / tanh) */
+typedef enum RbUnary {
+  RB_UNARY_NONE = 0, RB_UNARY_ABS, RB_UNARY_CEIL, RB_UNARY_ERF, RB_UNARY_EXP, RB_UNARY_FLOOR, RB_UNARY_LOG, RB_UNARY_NEG,
+  RB_UNARY_RECIP, RB_UNARY_RSQRT, RB_UNARY_SIGMOID, RB_UNARY_SQRT, RB_UNARY_TANH
+} RbUnary;
 
 typedef struct RbEpilogue {
   uint32_t flags;
@@ -105,6 +115,7 @@ typedef struct RbEpilogue {
   int32_t out_zero;        /* RB_EPI_ZP_OUT */
   const void *residual;    /* device, C's shape and layout (also under trans_c) */
   int32_t res_type;        /* RbDType of residual[]: RB_F32, RB_F16 or RB_BF16 */
+  int32_t unary;           /* RbUnary, RB_EPI_UNARY (occupies what was tail padding: the struct's size is unchanged) */
 } RbEpilogue;
 
 /* rock.gemm (mlir/include/mlir/Dialect/Rock/IR/RockOps.td:136-181):

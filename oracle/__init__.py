@@ -385,13 +385,16 @@ def gemm_gemm(a, b1, b2, mid_type: int, threads: int = 1) -> np.ndarray:
 # ---- epilogue -------------------------------------------------------------------------------------------------------
 EPI_ALPHA, EPI_COL_SCALE, EPI_BIAS, EPI_RELU, EPI_REQUANT, EPI_ROUND_MID = 1, 2, 4, 8, 16, 32
 EPI_CLIP, EPI_RESIDUAL, EPI_BIAS_ROW, EPI_BIAS_SCALAR, EPI_ZP_IN = 64, 128, 256, 512, 1024
+EPI_UNARY = 4096
+UNARY = {n: i + 1 for i, n in enumerate(("abs", "ceil", "erf", "exp", "floor", "log", "neg", "recip", "rsqrt", "sigmoid",
+                                          "sqrt", "tanh"))}
 
 
 def epilogue(acc: np.ndarray, N: int, *, alpha=None, col_scale=None, bias=None, relu=False, requant_scale=None,
-             mid_type=None, bias_mode: str = "col", residual=None, clip=None, in_zero=None) -> np.ndarray:
+             mid_type=None, bias_mode: str = "col", residual=None, clip=None, in_zero=None, unary=None) -> np.ndarray:
     """acc: f32 or i64 accumulators, last dimension N; `bias_mode` "col" (bias[n]), "row" (bias[row], rows counted
     over all leading dimensions) or "scalar"; `residual` an f32 array of acc's shape; `clip` = (lo, hi); `in_zero` the
-    dequantisation zero point. Returns f32 (convert with from_f32(..., sat_int=True) or quantize_i8)."""
+    dequantisation zero point; `unary` one of UNARY (a name or its code). Returns f32 (convert with from_f32(..., sat_int=True) or quantize_i8)."""
     flags = 0
     if alpha is not None: flags |= EPI_ALPHA
     if col_scale is not None: flags |= EPI_COL_SCALE
@@ -402,6 +405,8 @@ def epilogue(acc: np.ndarray, N: int, *, alpha=None, col_scale=None, bias=None, 
     if residual is not None: flags |= EPI_RESIDUAL
     if clip is not None: flags |= EPI_CLIP
     if in_zero is not None: flags |= EPI_ZP_IN
+    if unary is not None: flags |= EPI_UNARY
+    ucode = UNARY[unary] if isinstance(unary, str) else int(unary or 0)
     rows = acc.size // N
     out = np.empty(acc.shape, np.float32)
     is_int = acc.dtype == np.int64
@@ -415,7 +420,7 @@ def epilogue(acc: np.ndarray, N: int, *, alpha=None, col_scale=None, bias=None, 
     lib().orc_epilogue(None if is_int else _p(accc), _p(accc) if is_int else None, _p(out), C.c_int64(rows),
                        C.c_int64(N), C.c_uint32(flags), C.c_float(np.float32(alpha or 0.0)), _p(cs), _p(bs),
                        C.c_float(recip), C.c_int(mid_type if mid_type is not None else F32), C.c_float(np.float32(lo)),
-                       C.c_float(np.float32(hi)), C.c_float(np.float32(in_zero or 0.0)), _p(rs))
+                       C.c_float(np.float32(hi)), C.c_float(np.float32(in_zero or 0.0)), _p(rs), C.c_int(ucode))
     return out
 
 

@@ -666,10 +666,12 @@ ORC_API void orc_gemm_gemm(const float* a, const float* b1, const float* b2, flo
 // ------------------------------------------------------------------------------------------------
 ORC_API void orc_epilogue(const float* acc_f32, const int64_t* acc_i64, float* out, int64_t rows, int64_t N,
                           uint32_t flags, float alpha, const float* col_scale, const float* bias, float out_recip,
-                          int mid_type, float clip_lo, float clip_hi, float in_zero, const float* residual) {
+                          int mid_type, float clip_lo, float clip_hi, float in_zero, const float* residual, int unary) {
   // flags: 1 alpha, 2 col_scale, 4 bias (256: indexed by the row, 512: a scalar), 8 relu, 16 requant, 32 round to
   // mid_type, 64 clip (tosa.maximum then tosa.minimum, MIGraphXToTosa.cpp:1089-1101), 128 same-shape add,
-  // 1024 dequantisation zero point: (cast(x) - cast(zp)) * scale (MIGraphXToTosa.cpp:879-902)
+  // 1024 dequantisation zero point: (cast(x) - cast(zp)) * scale (MIGraphXToTosa.cpp:879-902),
+  // 4096 one unary elementwise function (MIGraphX.td:134-181; 1 abs 2 ceil 3 erf 4 exp 5 floor 6 log 7 neg 8 recip 9 rsqrt
+  // 10 sigmoid = 1 / (1 + exp(-x)) 11 sqrt 12 tanh) evaluated in f32 with the C library, result rounded to mid_type
   for (int64_t r = 0; r < rows; ++r)
     for (int64_t n = 0; n < N; ++n) {
       float x = acc_i64 ? (float)(int32_t)acc_i64[r * N + n] : acc_f32[r * N + n];
@@ -682,6 +684,24 @@ ORC_API void orc_epilogue(const float* acc_f32, const int64_t* acc_i64, float* o
         if (flags & 32) x = round_to(x, mid_type);
       }
       if (flags & 128) { x = x + residual[r * N + n]; if (flags & 32) x = round_to(x, mid_type); }
+      if (flags & 4096) {
+        switch (unary) {
+          case 1: x = std::fabs(x); break;
+          case 2: x = std::ceil(x); break;
+          case 3: x = std::erf(x); break;
+          case 4: x = std::exp(x); break;
+          case 5: x = std::floor(x); break;
+          case 6: x = std::log(x); break;
+          case 7: x = -x; break;
+          case 8: x = 1.0f / x; break;
+          case 9: x = 1.0f / std::sqrt(x); break;
+          case 10: x = 1.0f / (1.0f + std::exp(-x)); break;
+          case 11: x = std::sqrt(x); break;
+          case 12: x = std::tanh(x); break;
+          default: break;
+        }
+        if (flags & 32) x = round_to(x, mid_type);
+      }
       if (flags & 8) x = x > 0.0f ? x : 0.0f;
       if (flags & 64) { x = x > clip_lo ? x : clip_lo; x = x < clip_hi ? x : clip_hi; }
       if (flags & 16) x = x * out_recip;

@@ -24,13 +24,17 @@ STATUS_NAMES = ["RB_SUCCESS", "RB_INVALID_PARAM", "RB_UNSUPPORTED", "RB_WORKSPAC
 
 EPI_ALPHA, EPI_COL_SCALE, EPI_BIAS, EPI_RELU, EPI_REQUANT, EPI_ROUND_MID = 1, 2, 4, 8, 16, 32
 EPI_CLIP, EPI_RESIDUAL, EPI_BIAS_ROW, EPI_BIAS_SCALAR, EPI_ZP_IN, EPI_ZP_OUT = 64, 128, 256, 512, 1024, 2048
+EPI_UNARY = 4096
+# RbUnary
+UNARY = {n: i + 1 for i, n in enumerate(("abs", "ceil", "erf", "exp", "floor", "log", "neg", "recip", "rsqrt", "sigmoid",
+                                          "sqrt", "tanh"))}
 
 
 class RbEpilogue(C.Structure):
     _fields_ = [("flags", C.c_uint32), ("alpha", C.c_float), ("out_recip", C.c_float), ("mid_type", C.c_int32),
                 ("bias_type", C.c_int32), ("col_scale", C.c_void_p), ("bias", C.c_void_p), ("clip_lo", C.c_float),
                 ("clip_hi", C.c_float), ("in_zero", C.c_float), ("out_zero", C.c_int32), ("residual", C.c_void_p),
-                ("res_type", C.c_int32)]
+                ("res_type", C.c_int32), ("unary", C.c_int32)]
 
 
 class RbGemmProblem(C.Structure):

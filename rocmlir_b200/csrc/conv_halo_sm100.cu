@@ -388,6 +388,7 @@ RbStatus halo_setup(const HaloConv& c, const void* image, const void* filter_mat
     p.epi.clip_lo = epi->clip_lo; p.epi.clip_hi = epi->clip_hi; p.epi.in_zero = epi->in_zero;
     p.epi.out_zero = (epi->flags & RB_EPI_ZP_OUT) ? epi->out_zero : 0;
     p.epi.residual = epi->residual; p.epi.res_type = epi->res_type;
+    p.epi.unary = (epi->flags & RB_EPI_UNARY) ? epi->unary : 0;
   } else if (p.out_type != (c.is_bf16 ? RB_BF16 : RB_F16)) {
     return fail(RB_UNSUPPORTED, "halo kernel: a converted result needs an epilogue");
   }

@@ -26,6 +26,7 @@ struct EpiParams {
   int out_zero;             // RB_EPI_ZP_OUT: zero point added after the rounding cast of the quantisation
   const void* residual;     // RB_EPI_RESIDUAL: tensor of C's shape and layout, element type res_type
   int res_type;
+  int unary;                // RB_EPI_UNARY: RbUnary
 };
 
 // A bias vector indexed by the output column (the per-column vectors are staged in shared memory by the GEMM kernel).
@@ -40,6 +41,26 @@ __device__ __forceinline__ float round_to_type(float x, int t) {
   if (t == RB_F16) return __half2float(__float2half_rn(x));
   if (t == RB_BF16) return __bfloat162float(__float2bfloat16_rn(x));
   return x;
+}
+
+// The MIGraphX unary elementwise ops in f32 (MIGraphX.td:134-181). sigmoid = 1 / (1 + exp(-x)) as
+// MIGraphXToTosa lowers it; recip and rsqrt are correctly rounded divisions / square roots, not the approximate forms.
+__device__ __forceinline__ float epi_unary(float x, int op) {
+  switch (op) {
+    case RB_UNARY_ABS: return fabsf(x);
+    case RB_UNARY_CEIL: return ceilf(x);
+    case RB_UNARY_ERF: return erff(x);
+    case RB_UNARY_EXP: return expf(x);
+    case RB_UNARY_FLOOR: return floorf(x);
+    case RB_UNARY_LOG: return logf(x);
+    case RB_UNARY_NEG: return -x;
+    case RB_UNARY_RECIP: return __fdiv_rn(1.0f, x);
+    case RB_UNARY_RSQRT: return __fdiv_rn(1.0f, __fsqrt_rn(x));
+    case RB_UNARY_SIGMOID: return __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-x)));
+    case RB_UNARY_SQRT: return __fsqrt_rn(x);
+    case RB_UNARY_TANH: return tanhf(x);
+    default: return x;
+  }
 }
 
 __device__ __forceinline__ float load_bias(const void* bias, int bias_type, long long n) {
@@ -63,6 +84,10 @@ __device__ __forceinline__ float epi_apply(float x, const EpiParams& e, long lon
   }
   if (e.flags & RB_EPI_RESIDUAL) {
     x = __fadd_rn(x, load_bias(e.residual, e.res_type, idx));
+    if (e.flags & RB_EPI_ROUND_MID) x = round_to_type(x, e.mid_type);
+  }
+  if (e.flags & RB_EPI_UNARY) {
+    x = epi_unary(x, e.unary);
     if (e.flags & RB_EPI_ROUND_MID) x = round_to_type(x, e.mid_type);
   }
   if (e.flags & RB_EPI_RELU) x = fmaxf(x, 0.0f);
@@ -157,6 +182,14 @@ __device__ __forceinline__ void epi_apply32(float* x, const EpiParams& e, const 
           if (j < r.ncols) x[j] = __fadd_rn(x[j], load_bias(r.res, e.res_type, (long long)j * r.res_stride));
       }
     }
+    if (e.flags & RB_EPI_ROUND_MID) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) x[j] = round_to_type(x[j], e.mid_type);
+    }
+  }
+  if (e.flags & RB_EPI_UNARY) {
+#pragma unroll 4
+    for (int j = 0; j < 32; ++j) x[j] = epi_unary(x[j], e.unary);
     if (e.flags & RB_EPI_ROUND_MID) {
 #pragma unroll
       for (int j = 0; j < 32; ++j) x[j] = round_to_type(x[j], e.mid_type);

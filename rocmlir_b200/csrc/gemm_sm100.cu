@@ -440,6 +440,8 @@ RbStatus rb::gemm_run(const RbGemmProblem* p, const RbEpilogue* epi, const void*
     if ((epi->flags & RB_EPI_RESIDUAL) && !epi->residual) return fail(RB_INVALID_PARAM, "residual is NULL");
     if ((epi->flags & RB_EPI_RESIDUAL) && !(epi->res_type == RB_F32 || epi->res_type == RB_F16 || epi->res_type == RB_BF16))
       return fail(RB_INVALID_PARAM, "res_type must be f32, f16 or bf16");
+    if ((epi->flags & RB_EPI_UNARY) && (epi->unary <= RB_UNARY_NONE || epi->unary > RB_UNARY_TANH))
+      return fail(RB_INVALID_PARAM, "unary must name one of the RbUnary functions");
     if ((flags & RB_EPI_CLIP) && !(epi->clip_lo <= epi->clip_hi)) return fail(RB_INVALID_PARAM, "clip needs lo <= hi");
     if ((flags & RB_EPI_ZP_OUT) && p->c_type != RB_I8) return fail(RB_INVALID_PARAM, "an output zero point needs an i8 result");
   }
@@ -624,6 +626,7 @@ RbStatus rb::gemm_run(const RbGemmProblem* p, const RbEpilogue* epi, const void*
     ep.clip_lo = epi->clip_lo; ep.clip_hi = epi->clip_hi;
     ep.in_zero = epi->in_zero; ep.out_zero = (epi->flags & RB_EPI_ZP_OUT) ? epi->out_zero : 0;
     ep.residual = epi->residual; ep.res_type = epi->res_type;
+    ep.unary = (epi->flags & RB_EPI_UNARY) ? epi->unary : 0;
   }
   if (p->store_method == 1) {
     // the kernel's result is rounded to C's type and added to what C holds, like an atomic add of the stored value

@@ -108,7 +108,7 @@ struct Block { std::vector<Value*> args; std::vector<Operation*> ops; Region* pa
 struct EpiRecipe {
   uint32_t flags = 0;
   float alpha = 0, out_recip = 0, clip_lo = 0, clip_hi = 0, in_zero = 0;
-  int out_zero = 0, mid_type = 0, bias_type = 0, res_type = 0;
+  int out_zero = 0, mid_type = 0, bias_type = 0, res_type = 0, unary = 0;
   int bias_arg = -1, scale_arg = -1, res_arg = -1;   // function-argument indices of the device vectors
 };
 struct Lowered {
@@ -1118,6 +1118,20 @@ struct Matcher {
     EpiRecipe& e = L->epi;
     const Type* rt = o->results[0]->type;
     if (n == "migraphx.relu") { if (!step(60, "relu")) return false; e.flags |= RB_EPI_RELU; *acc_type = rt->elem; return true; }
+    {
+      // the other unary elementwise ops (MIGraphX.td:134-181): one of them, where the rectifier would stand
+      static const char* const kUnary[] = {"", "abs", "ceil", "erf", "exp", "floor", "log", "neg", "recip", "rsqrt", "sigmoid", "sqrt", "tanh"};
+      for (int u = 1; u <= RB_UNARY_TANH; ++u) {
+        if (n != std::string("migraphx.") + kUnary[u]) continue;
+        if (o->operands.size() != 1) return fail(n + " takes one operand");
+        if (rb_type_of(rt->elem) == RB_I8 || rb_type_of(rt->elem) == RB_I32) return fail(n + " is fused on floating-point values only");
+        if (!step(55, kUnary[u])) return false;
+        e.flags |= RB_EPI_UNARY;
+        e.unary = u;
+        *acc_type = rt->elem;
+        return true;
+      }
+    }
     if (n == "migraphx.clip") {
       double lo, hi;
       if (ci != 0 || o->operands.size() != 3 || !literal_of(o->operands[1], &lo) || !literal_of(o->operands[2], &hi))
@@ -1275,7 +1289,7 @@ RbStatus build_epilogue(const Lowered& L, void* const* args, RbEpilogue* e, bool
   memset(e, 0, sizeof(*e));
   const EpiRecipe& r = L.epi;
   e->flags = r.flags; e->alpha = r.alpha; e->out_recip = r.out_recip; e->mid_type = r.mid_type; e->bias_type = r.bias_type;
-  e->clip_lo = r.clip_lo; e->clip_hi = r.clip_hi; e->in_zero = r.in_zero; e->out_zero = r.out_zero; e->res_type = r.res_type;
+  e->clip_lo = r.clip_lo; e->clip_hi = r.clip_hi; e->in_zero = r.in_zero; e->out_zero = r.out_zero; e->res_type = r.res_type; e->unary = r.unary;
   if (r.bias_arg >= 0) e->bias = args[r.bias_arg];
   if (r.scale_arg >= 0) e->col_scale = static_cast<const float*>(args[r.scale_arg]);
   if (r.res_arg >= 0) e->residual = args[r.res_arg];

@@ -44,6 +44,7 @@ class Epilogue:
     clip: Optional[tuple] = None                # (lo, hi): migraphx.clip after the rectifier
     in_zero: Optional[float] = None             # dequantizelinear zero point (subtracted from the accumulator)
     out_zero: Optional[int] = None              # quantizelinear zero point (added after the rounding cast, i8 results)
+    unary: Optional[str] = None                 # one MIGraphX unary function ("sigmoid", "tanh", "erf", ...: _lib.UNARY) before the rectifier
 
     def to_c(self) -> L.RbEpilogue:
         e = L.RbEpilogue()
@@ -75,6 +76,9 @@ class Epilogue:
         if self.out_zero is not None:
             flags |= L.EPI_ZP_OUT
             e.out_zero = int(self.out_zero)
+        if self.unary is not None:
+            flags |= L.EPI_UNARY
+            e.unary = L.UNARY[self.unary]
         if self.relu:
             flags |= L.EPI_RELU
         if self.requant_scale is not None:

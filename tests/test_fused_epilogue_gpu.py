@@ -162,3 +162,44 @@ def test_gemm_accumulate_store_method(cuda_device, code, rms):
         else:
             verdict, info = oracle.verify_float(oracle.to_f32(got, code), oracle.round_to(ref, code), rms, 100.0, 100.0)
             assert verdict == [1, 1, 1], info
+
+
+@pytest.mark.parametrize("code", [oracle.F16, oracle.F32])
+@pytest.mark.parametrize("fn", ["abs", "ceil", "erf", "exp", "floor", "log", "neg", "recip", "rsqrt", "sigmoid", "sqrt", "tanh"])
+def test_gemm_bias_unary(cuda_device, fn, code):
+    """dot -> add(bias) -> one MIGraphX unary elementwise op (MIGraphX.td:134-181), each step in the declared type.
+    Operands are positive so that log / sqrt / rsqrt / recip see their domain. The oracle evaluates the function with
+    the C library in f32; the device's own f32 routines may differ in the last bit, which after the rounding to f16
+    shows as an occasional one-step difference (as does the summation order of the GEMM itself on such data): the
+    reference verifier with its RMS bar decides; ceil / floor are compared exactly away from their steps."""
+    import torch
+    from rocmlir_b200 import _lib as L
+    from rocmlir_b200.gemm import Epilogue, gemm
+    m, n, k = 300, 200, 96
+    rng = np.random.Generator(np.random.PCG64(hash(fn) % 1000))
+    a32 = rng.uniform(0.05, 0.5, size=(m, k)).astype(np.float32)
+    b32 = rng.uniform(0.05, 0.5, size=(k, n)).astype(np.float32)
+    bias32 = rng.uniform(-0.5, 0.5, size=(n,)).astype(np.float32)
+    if fn in ("log", "sqrt", "rsqrt", "recip"):
+        bias32 = np.abs(bias32) + np.float32(0.1)
+    araw, braw, biasraw = (oracle.from_f32(x, code) for x in (a32, b32, bias32))
+    af, bf, biasf = (oracle.to_f32(x, code) for x in (araw, braw, biasraw))
+    mid = None if code == oracle.F32 else code
+    acc = oracle.gemm_f32(af[None], bf[None], 1, m, n, k, threads=oracle.max_threads())
+    ref = oracle.from_f32(oracle.epilogue(acc, n, bias=biasf, mid_type=mid, unary=fn), code)
+    out = gemm(to_device(araw, code), to_device(braw, code), out_dtype=torch_dtype(code),
+               epilogue=Epilogue(bias=to_device(biasraw, code), mid_type=mid, unary=fn), f32_mode=0)
+    torch.cuda.synchronize()
+    assert L.kernel_status() == 0
+    got = from_device(out, code).reshape(ref.shape)
+    bar = 1e-3 if code == oracle.F16 else 3e-5
+    if fn in ("ceil", "floor"):
+        # a step function turns a last-bit difference of the sum into a whole unit: compare where the argument is not
+        # within an f16 step of an integer
+        pre = oracle.to_f32(oracle.from_f32(oracle.epilogue(acc, n, bias=biasf, mid_type=mid), code), code).reshape(ref.shape)
+        keep = np.abs(pre - np.rint(pre)) > 4e-3
+        assert keep.mean() > 0.9
+        np.testing.assert_array_equal(oracle.to_f32(got, code)[keep], oracle.to_f32(ref, code)[keep])
+        return
+    verdict, info = oracle.verify_float(oracle.to_f32(got, code), oracle.to_f32(ref, code), bar, 1e30, 1e30)
+    assert verdict[0] == 1, (fn, info)

@@ -267,3 +267,17 @@ def test_int4_operand_is_unpacked_into_the_workspace(built):
     with Module(along_rows) as m:
         with pytest.raises(PipelineError, match="last, contiguous dimension"):
             m.high_level()
+
+
+def test_unary_elementwise_ops_join_the_fused_tail(built):
+    """dot -> add -> sigmoid (and the other unary ops of MIGraphX.td:134-181) are matched into the epilogue; two of them
+    in a row, or one after the rectifier, are refused by the fixed order."""
+    from rocmlir_b200.mlirc import Module, PipelineError
+    text = DOT_TRANSB_BIAS_RELU.replace("migraphx.relu", "migraphx.sigmoid")
+    with Module(text) as m:
+        m.high_level()
+        m.backend("sm_100a")
+    twice = DOT_TRANSB_BIAS_RELU.replace("%3 = migraphx.relu %2", "%9 = migraphx.tanh %2 : <2x384x520xf16, 199680x520x1> -> <2x384x520xf16, 199680x520x1>\n  %3 = migraphx.erf %9")
+    with Module(twice) as m:
+        with pytest.raises(PipelineError, match="fixed order"):
+            m.high_level()
