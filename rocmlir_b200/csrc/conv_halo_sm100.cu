@@ -45,7 +45,9 @@ struct HaloMaps {
 struct HaloParams {
   int N, P, Q, Kout, cchunks;       // output image P x Q with Kout channels; input channels = cchunks * 64
   int Y, X, dil_h, dil_w, pad_h, pad_w;
-  int Wp, R, rows_box;              // padded raster width, output rows per tile, input rows per box
+  int Wp, R, rows_box;              // padded raster width, output rows per 128-row sub-tile, input rows per box
+  int G;                            // sub-tiles per stage: one window of G * R output rows feeds G accumulators (G * Kout <= 256)
+  int slack_bytes;                  // rows past the last stage that shifted descriptors may touch
   int tiles_per_img, num_tiles;
   int stage_bytes, stages;
   int b_tile_bytes, b_tiles;        // one (tap, channel block) slab of the filter: Kout rows of 128 bytes
@@ -91,8 +93,7 @@ conv_halo_kernel(const __grid_constant__ HaloGroup g) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   // [A ring: stages * stage_bytes][slack: rows that shifted descriptors may touch past the last stage][B][barriers]
-  const int slack = 160 * 128;
-  uint8_t* b_smem = smem + p.stages * p.stage_bytes + slack;
+  uint8_t* b_smem = smem + p.stages * p.stage_bytes + p.slack_bytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(b_smem + p.b_tiles * p.b_tile_bytes);
   uint64_t* full_bar = bars;                      // [stages]
   uint64_t* empty_bar = bars + kHaloMaxStages;    // [stages]
@@ -141,7 +142,7 @@ conv_halo_kernel(const __grid_constant__ HaloGroup g) {
       const uint32_t box_bytes = (uint32_t)(p.Wp * p.rows_box * 128);
       for (int tile = cta; ok && tile < p.num_tiles; tile += ctas) {
         const int n = tile / p.tiles_per_img;
-        const int p0 = (tile - n * p.tiles_per_img) * p.R;
+        const int p0 = (tile - n * p.tiles_per_img) * p.R * p.G;
         for (int cc = 0; cc < p.cchunks; ++cc) {
           if (!mbar_wait(&empty_bar[s], ph ^ 1u, p.status, kStatusTimeoutProducer + s, wait_limit)) { ok = false; break; }
           mbar_expect_tx(&full_bar[s], box_bytes);
@@ -157,7 +158,8 @@ conv_halo_kernel(const __grid_constant__ HaloGroup g) {
     // one lane, chosen once: the commits must come from the thread that issued the MMAs they track
     const bool leader = elect_one();
     // the loop's invariants, read once (the parameter block is indexed by the group member)
-    const int Y = p.Y, X = p.X, cchunks = p.cchunks, num_tiles = p.num_tiles;
+    const int Y = p.Y, X = p.X, cchunks = p.cchunks, num_tiles = p.num_tiles, G = p.G, Kout = p.Kout;
+    const uint32_t g_step = (uint32_t)(p.R * p.Wp) * 8u;   // one sub-tile down the window, in 16-byte units
     const uint32_t stages = (uint32_t)p.stages, idesc = p.idesc;
     const bool tracing = p.trace != nullptr;
     uint32_t* const status = p.status;
@@ -183,7 +185,6 @@ conv_halo_kernel(const __grid_constant__ HaloGroup g) {
       }
       tc_fence_after();
       const uint32_t tmem_d = tmem_base + buf * 256;
-      uint32_t accum = 0;
       for (int cc = 0; cc < cchunks && ok; ++cc) {
         if (!ready) {
           const long long tw = tracing ? clock64() : 0;
@@ -199,12 +200,15 @@ conv_halo_kernel(const __grid_constant__ HaloGroup g) {
         const bool last_cc = cc + 1 == cchunks;
         // every tap is the same window, shifted: the swizzle pattern follows the absolute address, so the shifted
         // start address is all the descriptor needs
-        uint32_t a_row = a_lo0 + s * a_stage;
+        for (int gsub = 0; gsub < G; ++gsub) {
+        uint32_t a_row = a_lo0 + s * a_stage + (uint32_t)gsub * g_step;
         uint32_t b_lo = b_lo0 + (uint32_t)cc * b_slab;
+        const uint32_t tmem_dg = tmem_d + (uint32_t)(gsub * Kout);
+        uint32_t accum = cc ? 1u : 0u;
         for (int y = 0; y < Y; ++y) {
           uint32_t a_lo = a_row;
           for (int x = 0; x < X; ++x) {
-            if (y + 1 == Y && x + 1 == X) {
+            if (gsub + 1 == G && y + 1 == Y && x + 1 == X) {
               uint32_t f = mbar_test_wait(&full_bar[ns], nph) ? 1u : 0u;
               if (last_cc && mbar_test_wait(&tempty_bar[buf ^ 1u], (((t + 1) >> 1) & 1u) ^ 1u)) f |= 2u;
               f = __shfl_sync(0xffffffffu, f, 0);
@@ -214,13 +218,14 @@ conv_halo_kernel(const __grid_constant__ HaloGroup g) {
             if (leader) {
 #pragma unroll
               for (int k = 0; k < 4; ++k)   // 64 channels = four K steps of 16
-                umma_ss<kKindF16, 1>(tmem_d, desc64(a_lo + k * 2, desc_hi0), desc64(b_lo + k * b_kstep, desc_hi0), idesc, k ? 1u : accum);
+                umma_ss<kKindF16, 1>(tmem_dg, desc64(a_lo + k * 2, desc_hi0), desc64(b_lo + k * b_kstep, desc_hi0), idesc, k ? 1u : accum);
             }
             accum = 1;
             a_lo += a_xstep;
             b_lo += b_tapstep;
           }
           a_row += a_ystep;
+        }
         }
         if (leader) tc_commit_addr1(smem_u32(&empty_bar[s]));
         s = ns; ph = nph; ready = next_ready;
@@ -239,7 +244,7 @@ conv_halo_kernel(const __grid_constant__ HaloGroup g) {
     // ------------------------------ epilogue ------------------------------
     const int q4 = warp & 3, lane = lane_id();
     const int m = q4 * 32 + lane;              // position on the tile's padded raster
-    const int Wp = p.Wp, R = p.R, P = p.P, Q = p.Q, Kout = p.Kout, tiles_per_img = p.tiles_per_img, num_tiles = p.num_tiles;
+    const int Wp = p.Wp, R = p.R, P = p.P, Q = p.Q, Kout = p.Kout, tiles_per_img = p.tiles_per_img, num_tiles = p.num_tiles, G = p.G;
     const long long o_n = p.o_n, o_p = p.o_p, o_q = p.o_q;
     const bool is_bf16 = p.is_bf16 != 0, wide = p.wide_store != 0, tracing = p.trace != nullptr;
     uint8_t* const out = static_cast<uint8_t*>(p.out);
@@ -254,10 +259,11 @@ conv_halo_kernel(const __grid_constant__ HaloGroup g) {
       w_tfull += te - tw;
       tc_fence_after();
       const int n = tile / tiles_per_img;
-      const int p0 = (tile - n * tiles_per_img) * R;
+      for (int gsub = 0; gsub < G; ++gsub) {
+      const int p0 = (tile - n * tiles_per_img) * R * G + gsub * R;
       const bool valid = rr < R && qq < Q && p0 + rr < P;
       const long long pix = (long long)n * o_n + (long long)(p0 + rr) * o_p + (long long)qq * o_q;   // elements
-      const uint32_t taddr = tmem_base + (uint32_t(q4 * 32) << 16) + buf * 256;
+      const uint32_t taddr = tmem_base + (uint32_t(q4 * 32) << 16) + buf * 256 + (uint32_t)(gsub * Kout);
       if constexpr (!EPI) {
         uint8_t* dst = out + 2 * pix;
 #pragma unroll 1
@@ -317,6 +323,7 @@ conv_halo_kernel(const __grid_constant__ HaloGroup g) {
           }
         }
       }
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[buf]);
@@ -351,7 +358,8 @@ bool conv_halo_applicable(const HaloConv& c) {
   const long long b_bytes = (long long)c.Y * c.X * (c.C / 64) * c.Kout * 128;
   const int stage_bytes = (Wp * rows_box + 7) / 8 * 8 * 128;
   // the filter stays resident beside at least two stages of the window ring
-  return b_bytes + 2LL * stage_bytes + 160 * 128 + 2048 <= 232448 - 1024;
+  const long long slack = ((128 - R * Wp + (c.X - 1) * c.dil_w + 7) / 8 * 8 + 8) * 128;
+  return b_bytes + 2LL * stage_bytes + slack + 2048 <= 232448 - 1024;
 }
 
 namespace {
@@ -365,15 +373,27 @@ RbStatus halo_setup(const HaloConv& c, const void* image, const void* filter_mat
   p.Y = c.Y; p.X = c.X; p.dil_h = c.dil_h; p.dil_w = c.dil_w; p.pad_h = c.pad_h; p.pad_w = c.pad_w;
   p.Wp = c.Q + (c.X - 1) * c.dil_w;
   p.R = std::min(128 / p.Wp, c.P);
-  p.rows_box = p.R + (c.Y - 1) * c.dil_h;
-  p.tiles_per_img = (c.P + p.R - 1) / p.R;
-  p.num_tiles = c.N * p.tiles_per_img;
-  p.stage_bytes = (p.Wp * p.rows_box + 7) / 8 * 8 * 128;
   p.b_tile_bytes = c.Kout * 128;
   p.b_tiles = c.Y * c.X * p.cchunks;
   if (c.Y * c.X > kHaloMaxTaps) return fail(RB_UNSUPPORTED, "halo kernel: filter larger than 7 x 7");
-  const int fixed = 160 * 128 + p.b_tiles * p.b_tile_bytes + 2048;
-  p.stages = std::min(kHaloMaxStages, (232448 - 1024 - fixed) / p.stage_bytes);
+  // a shifted 128-row view of the last sub-tile may run past the window by the raster's unused rows plus the widest
+  // horizontal tap offset: that many rows (rounded up to the swizzle atom) stay free behind the ring
+  p.slack_bytes = ((128 - p.R * p.Wp + (c.X - 1) * c.dil_w + 7) / 8 * 8 + 8) * 128;
+  int fixed = 0;
+  // Two sub-tiles per stage when two accumulators fit a TMEM buffer and three stages still fit beside the filter:
+  // one window of 2 R output rows shares its halo rows and halves the barrier work per output row.
+  // (measured at C4a: one sub-tile 783, two 825, three 788, four 819 TFLOP/s on the same box)
+  for (p.G = 2; p.G >= 1; --p.G) {
+    if (p.G > 1 && (p.G * c.Kout > 256 || c.P <= (p.G - 1) * p.R)) continue;
+    p.rows_box = p.G * p.R + (c.Y - 1) * c.dil_h;
+    p.stage_bytes = (p.Wp * p.rows_box + 7) / 8 * 8 * 128;
+    fixed = p.slack_bytes + p.b_tiles * p.b_tile_bytes + 2048;
+    p.stages = std::min(kHaloMaxStages, (232448 - 1024 - fixed) / p.stage_bytes);
+    if (p.rows_box <= 256 && p.stages >= (p.G == 2 ? 3 : 2)) break;
+  }
+  if (p.G < 1) return fail(RB_UNSUPPORTED, "halo kernel: the filter leaves no room for the window ring");
+  p.tiles_per_img = (c.P + p.G * p.R - 1) / (p.G * p.R);
+  p.num_tiles = c.N * p.tiles_per_img;
   const uint32_t fmt = c.is_bf16 ? 1u : 0u;
   p.idesc = make_idesc(1, fmt, fmt, 0, c.b_mn ? 1u : 0u, 128, (uint32_t)c.Kout);
   p.b_mn = c.b_mn ? 1 : 0;
@@ -428,8 +448,8 @@ RbStatus halo_setup(const HaloConv& c, const void* image, const void* filter_mat
 // Rough cycles of one tile: its MMAs (shared-memory bound: 128 rows of A and Kout rows of B, 32 bytes each, per MMA at
 // about 100 bytes per clock) or its epilogue, whichever is longer. Only the RATIO between the members of a group matters.
 long long halo_tile_cost(const HaloParams& p) {
-  const long long mma = (long long)p.Y * p.X * p.cchunks * 4 * ((4096 + p.Kout * 32) / 100) + 450;
-  const long long epilogue = (long long)(p.Kout / 32) * 480 + 100;
+  const long long mma = (long long)p.G * p.Y * p.X * p.cchunks * 4 * ((4096 + p.Kout * 32) / 100) + 450;
+  const long long epilogue = (long long)p.G * (p.Kout / 32) * 480 + 100;
   return std::max(mma, epilogue);
 }
 

@@ -146,15 +146,24 @@ conv_wgrad_halo_kernel(const __grid_constant__ WgradMaps maps, const __grid_cons
     long long w_full = 0;
     const long long t_begin = tracing ? clock64() : 0;
     bool ok = true;
+    bool ready = false;
     for (int t = 0; t < my_tiles && ok; ++t) {
-      const long long tw = tracing ? clock64() : 0;
-      if (!mbar_wait_warp(&full_bar[s], ph, p.status, kStatusTimeoutMma + s, wait_limit)) { ok = false; break; }
-      if (tracing) w_full += clock64() - tw;
+      if (!ready) {
+        const long long tw = tracing ? clock64() : 0;
+        if (!mbar_wait_warp(&full_bar[s], ph, p.status, kStatusTimeoutMma + s, wait_limit)) { ok = false; break; }
+        if (tracing) w_full += clock64() - tw;
+      }
       tc_fence_after();
+      // the NEXT stage's barrier is tested before this tile's last reduction step is issued: the answer arrives while
+      // those MMAs queue up, and the wait above is skipped when the stage is already full
+      uint32_t ns = s + 1, nph = ph;
+      if (ns == stages) { ns = 0; nph ^= 1u; }
+      bool next_ready = false;
       const uint32_t x_lo = x_lo0 + s * stage_step;
       uint32_t dy_lo = dy_lo0 + s * stage_step;
       uint32_t koff = 0;
       for (int ks = 0; ks < ksteps; ++ks) {
+        if (ks + 1 == ksteps) next_ready = __shfl_sync(0xffffffffu, mbar_test_wait(&full_bar[ns], nph) ? 1 : 0, 0) != 0;
         const uint64_t b_desc = desc64(dy_lo, desc_hi);
         const uint32_t accum = (t | ks) ? 1u : 0u;
         for (int j = 0; j < my_pairs; ++j) {
@@ -165,7 +174,7 @@ conv_wgrad_halo_kernel(const __grid_constant__ WgradMaps maps, const __grid_cons
         koff += kStep;
       }
       if (leader) tc_commit_addr1(smem_u32(&empty_bar[s]));
-      if (++s == stages) { s = 0; ph ^= 1u; }
+      s = ns; ph = nph; ready = next_ready;
     }
     if (leader) tc_commit<1>(done_bar);
     if (tracing && lane_id() == 0) {
