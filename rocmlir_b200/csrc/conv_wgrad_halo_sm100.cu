@@ -300,12 +300,28 @@ bool wgrad_shape(const HaloConv& c, WgradShape* s) {
   s->Wp = c.Q + (c.X - 1) * c.dil_w;
   if (s->Wp > 128 || s->Wp != c.W + c.pad_w + c.pad_w_r) return false;
   if (c.P + (c.Y - 1) * c.dil_h != c.H + c.pad_h + c.pad_h_r) return false;
-  s->R = std::min(128 / s->Wp, c.P);
+  s->cchunks = c.C / 64;
+  s->kchunks = c.Kout / 64;
+  // Output rows per tile: the reduction runs along the raster, so a tile may be any number of rows long. More rows
+  // share the window's halo rows and waste less of the last 16-pixel step; the ring must still hold three stages.
+  // Among the sizes that fit, the one with the fewest reduction steps per image wins.
+  int best_r = 0;
+  long long best_steps = 0;
+  for (int r = 1; r <= std::min(c.P, 16); ++r) {
+    const int rows_box = r + (c.Y - 1) * c.dil_h;
+    const int ksteps = (r * s->Wp + 15) / 16;
+    const long long stage = (long long)s->cchunks * ((s->Wp * rows_box + 7) / 8 * 8 * 128) + (long long)s->kchunks * ksteps * 16 * 128;
+    if (rows_box > 256 || (232448 - 1024 - kWgSlack - 1024) / stage < 3) continue;
+    const long long steps = (long long)((c.P + r - 1) / r) * (ksteps + 2);   // + the barrier work of a tile, about two steps' worth
+    if (best_r == 0 || steps <= best_steps) { best_r = r; best_steps = steps; }
+  }
+  if (best_r == 0) {   // not even one row with three stages: two stages of the 128-row tile, as before
+    best_r = std::min(128 / s->Wp, c.P);
+  }
+  s->R = best_r;
   s->rows_box = s->R + (c.Y - 1) * c.dil_h;
   if (s->R < 1 || s->rows_box > 256) return false;
   s->ksteps = (s->R * s->Wp + 15) / 16;
-  s->cchunks = c.C / 64;
-  s->kchunks = c.Kout / 64;
   s->units = c.Y * c.X * s->cchunks;
   s->npairs = (s->units + 1) / 2;
   if (s->npairs > kWgMaxPairs) return false;
