@@ -397,7 +397,7 @@ def build_workload(name, dev, sets, rank=0, world=1, gather=False):
         ai = cfg.flops() / (abytes / nsets)
         return dict(step=step, finish=finish, work=cfg.flops() * nsets, unit="TFLOP/s", bytes=abytes,
                     bound=("tensor" if ai > 281 else "hbm"), dtype=("f32" if es == 4 else "f16"), verify=verify, desc=desc,
-                    kernel="gemm_tcgen05_kernel (+ layout / reduction passes)")
+                    kernel="conv_halo_kernel / conv_wgrad_halo_kernel (unit-stride NHWC 16-bit, stride classes) or gemm_tcgen05_kernel (+ layout / reduction passes)")
     if name.startswith("attention_f16"):
         from rocmlir_b200.attention import attention, flops
         causal = name.endswith("causal")
