@@ -617,13 +617,18 @@ def main():
     barrier()
     t_host0 = time.time()
     e0.record()
+    marks = []
     for _ in range(args.steps):
         step_device()
+        m = torch.cuda.Event(enable_timing=True)   # a mark between steps: recorded on the stream, nothing waits for it
+        m.record()
+        marks.append(m)
     e1.record()
     barrier()
     t_host1 = time.time()
     launches = L.launch_count() - launches0
     ms_total = e0.elapsed_time(e1)
+    per_step = sorted(a.elapsed_time(b) for a, b in zip([e0] + marks[:-1], marks))
     status = L.kernel_status()
     clocks = sampler.summary(t_host0, t_host1) if rank == 0 else None
 
@@ -701,6 +706,8 @@ def main():
                              f"{args.passes} passes per step",
                        "parallelism": f"{world} independent replicas of the batch (weak scaling, no collective)",
                        "kernel_variant": args.variant, "kernel_status": status, "timed_region_ms": ms_total,
+                       "ms_per_step_min": per_step[0], "ms_per_step_median": per_step[len(per_step) // 2],
+                       "ms_per_step_max": per_step[-1],
                        "secondary": secondary, "verified": verified, "sharded": sharded},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                          "frac": achieved / peak,
