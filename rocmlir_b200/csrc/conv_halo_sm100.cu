@@ -32,7 +32,7 @@
 namespace rb {
 namespace {
 
-constexpr int kHaloThreads = 256;
+constexpr int kHaloThreads = 384;   // producer, MMA, TMEM and one idle warp, then two epilogue groups of four warps
 constexpr int kHaloMaxStages = 6;
 constexpr int kHaloMaxTaps = 49;   // up to 7 x 7 filters
 
@@ -251,8 +251,13 @@ conv_halo_kernel(const __grid_constant__ HaloGroup g) {
     const int rr = m / Wp, qq = m - rr * Wp;
     uint32_t t = 0;
     long long w_tfull = 0, e_work = 0;
+    // Two epilogue groups (warps 4-7 and 8-11): each serves one of the two accumulator buffers, i.e. every other tile,
+    // so that layers whose tiles have little reduction work per output (few taps, many output channels) are not bound
+    // by one group's drain rate.
+    const uint32_t egroup = (uint32_t)(warp - 4) >> 2;
     for (int tile = cta; tile < num_tiles; tile += ctas, ++t) {
       const uint32_t buf = t & 1u, bph = (t >> 1) & 1u;
+      if (buf != egroup) continue;
       const long long tw = tracing ? clock64() : 0;
       if (!mbar_wait_warp(&tfull_bar[buf], bph, p.status, kStatusTimeoutEpilogue + buf, wait_limit)) break;
       const long long te = tracing ? clock64() : 0;
@@ -329,7 +334,7 @@ conv_halo_kernel(const __grid_constant__ HaloGroup g) {
       if (lane == 0) mbar_arrive(&tempty_bar[buf]);
       if (tracing) e_work += clock64() - te;
     }
-    if (tracing && warp == 4 && lane == 0) {
+    if (tracing && warp == 4 && lane == 0) {   // group 0 only: its waits and work cover every other tile
       p.trace[blockIdx.x * 16 + 6] = (unsigned long long)w_tfull;
       p.trace[blockIdx.x * 16 + 7] = (unsigned long long)e_work;
     }
