@@ -676,11 +676,26 @@ using namespace rb;
 // kernel: the window of an output tile is loaded once instead of once per tap (csrc/conv_halo_sm100.cu). Backward
 // data is the same kernel over the output gradient with mirrored taps, which it reads straight from a KYXC filter
 // (hc->b_mn) when the layout allows. Variant bit 26 keeps the im2col form.
+static void halo_geometry(const RbConvProblem* p, HaloConv* hc);
 static bool unit_halo(const RbConvProblem* p, const ConvPlan& pl, bool has_epi, HaloConv* hc) {
   if (p->direction > 1 || !pl.a_implicit || pl.a_planes != 0 || pl.a_up || !pl.c_direct || p->stride_h != 1 || p->stride_w != 1 ||
       !(p->data_type == RB_F16 || p->data_type == RB_BF16) || !(has_epi || pl.gemm.c_type == p->data_type) ||
       ((rbGetGemmVariant() >> 26) & 1))
     return false;
+  halo_geometry(p, hc);
+  if (p->direction == 1 && pl.fs[2] == 1 && p->g == 1 && p->c % 64 == 0) {
+    hc->b_mn = true;
+    hc->FY = p->y; hc->FX = p->x; hc->f_sk = pl.fs[1]; hc->f_sy = pl.fs[3]; hc->f_sx = pl.fs[4];
+    hc->fy0 = 0; hc->fsy = 1; hc->fx0 = 0; hc->fsx = 1;
+    if (conv_halo_applicable(*hc)) return true;
+    hc->b_mn = false;
+  }
+  return conv_halo_applicable(*hc);
+}
+
+// The unit-stride convolution as the halo kernels see it: forward over the input, or backward data as a forward
+// convolution of the output gradient (channels-last result with dense pixel strides).
+static void halo_geometry(const RbConvProblem* p, HaloConv* hc) {
   const int ho = p->ho, wo = p->wo;
   hc->is_bf16 = p->data_type == RB_BF16;
   hc->Y = p->y; hc->X = p->x; hc->dil_h = p->dil_h; hc->dil_w = p->dil_w;
@@ -693,14 +708,6 @@ static bool unit_halo(const RbConvProblem* p, const ConvPlan& pl, bool has_epi, 
     hc->pad_h_r = p->h - ho - hc->pad_h + (p->y - 1) * p->dil_h; hc->pad_w_r = p->w - wo - hc->pad_w + (p->x - 1) * p->dil_w;
   }
   hc->o_q = hc->Kout; hc->o_p = (long long)hc->Q * hc->Kout; hc->o_n = (long long)hc->P * hc->Q * hc->Kout;
-  if (p->direction == 1 && pl.fs[2] == 1 && p->g == 1 && p->c % 64 == 0) {
-    hc->b_mn = true;
-    hc->FY = p->y; hc->FX = p->x; hc->f_sk = pl.fs[1]; hc->f_sy = pl.fs[3]; hc->f_sx = pl.fs[4];
-    hc->fy0 = 0; hc->fsy = 1; hc->fx0 = 0; hc->fsx = 1;
-    if (conv_halo_applicable(*hc)) return true;
-    hc->b_mn = false;
-  }
-  return conv_halo_applicable(*hc);
 }
 
 size_t rb::conv_workspace_bytes(const RbConvProblem* p, int result_type) {
@@ -1013,6 +1020,33 @@ RbStatus rb::conv_run(const RbConvProblem* p, int result_type, void* filter, voi
   }
   if (on_halo)
     return conv_halo_run(uhc, p->direction == 0 ? input : output, B, p->direction == 0 ? output : input, stream_v, epi, pl.gemm.c_type);
+  // Filters too large to stay in shared memory, and f32 tensors (three TF32 products from two planes of window and
+  // filter): the halo kernel with a streamed filter (csrc/conv_halo_stream_sm100.cu).
+  if (!capture && !epi && pl.a_implicit && !pl.a_up && p->direction <= 1 && p->stride_h == 1 && p->stride_w == 1 &&
+      !((rbGetGemmVariant() >> 26) & 1)) {
+    HaloConv sc;
+    halo_geometry(p, &sc);
+    // (16-bit: up to 128 output channels; at 256 the GEMM kernel's 256-column MMAs run at the math rate and win:
+    //  C = K = 256, 14 x 14, 3 x 3 measured 782 streamed against 970 TFLOP/s)
+    if ((p->data_type == RB_F16 || p->data_type == RB_BF16) && pl.a_planes == 0 && pl.c_direct && pl.gemm.c_type == p->data_type &&
+        sc.Kout <= 128 && conv_halo_stream_applicable(sc, 2, 1))
+      return conv_halo_stream_run(sc, 2, p->direction == 0 ? input : output, nullptr, B, nullptr, p->direction == 0 ? output : input, 1,
+                                  stream_v);
+    const size_t fil_plane = up256((size_t)p->k * p->y * p->x * p->c * 4);
+    if (p->data_type == RB_F32 && p->direction == 0 && pl.a_planes == 2 && (pl.c_direct || pl.c_remap) && pl.gemm.c_type == RB_F32 &&
+        pl.gemm_ws >= 2 * fil_plane) {
+      long long o_k = 1;
+      if (pl.c_remap) { sc.o_n = pl.os[0]; sc.o_p = pl.os[3]; sc.o_q = pl.os[4]; o_k = pl.os[2]; }
+      if (conv_halo_stream_applicable(sc, 4, o_k)) {
+        float* fhi = reinterpret_cast<float*>(ws + pl.gemm_off);
+        float* flo = reinterpret_cast<float*>(ws + pl.gemm_off + fil_plane);
+        const int yxc = p->y * p->x * p->c;
+        st = f32_planes(static_cast<const float*>(B), fhi, flo, 1, p->k, yxc, yxc, false, true, stream_v);
+        if (st != RB_SUCCESS) return st;
+        return conv_halo_stream_run(sc, 4, a_hi, a_lo, fhi, flo, output, o_k, stream_v);
+      }
+    }
+  }
   if (pl.a_implicit) {
     ConvAOperand cv;
     if (p->direction == 0) {

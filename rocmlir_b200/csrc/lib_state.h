@@ -106,6 +106,13 @@ RbStatus conv_halo_run(const HaloConv& c, const void* image, const void* filter_
 // pixel strides): the CTAs are divided among them in proportion to their work.
 RbStatus conv_halo_run_group(const HaloConv* cs, int count, const void* image, const void* const* filter_matrices,
                              void* const* outs, void* stream, const RbEpilogue* epi = nullptr, int out_type = -1);
+// The same forward form with the filter matrix streamed through shared memory (csrc/conv_halo_stream_sm100.cu): any
+// channel count; elem_bytes 2 (f16 / bf16, channels-last result) or 4 (f32 as three TF32 products: hi and lo planes of
+// the NHWC image and of the K-major filter matrix; the result's channel stride o_k may be 1 or a plane size, NKHW).
+bool conv_halo_stream_applicable(const HaloConv& c, int elem_bytes, long long o_k);
+RbStatus conv_halo_stream_run(const HaloConv& c, int elem_bytes, const void* image_hi, const void* image_lo, const void* filter_hi,
+                              const void* filter_lo, void* out, long long o_k, void* stream);
+
 // Backward weight of the same convolution (csrc/conv_wgrad_halo_sm100.cu): image [N][H][W][C], output gradient
 // [N][P][Q][Kout] -> filter gradient [Kout][Y][X][C] in the 16-bit element type. The workspace holds the f32 sums.
 // Tuning database (csrc/tuning.cu): the variant word recorded for a problem, 0 = none.
