@@ -286,7 +286,10 @@ bool stream_shape(const HaloConv& c, int elem_bytes, long long o_k, StreamShape*
   if (s->R < 1) return false;
   s->cchunks = c.C / s->epr;
   s->slab_bytes = c.Kout * 128;
-  s->slack_bytes = ((128 - s->R * s->Wp + (c.X - 1) * c.dil_w + 7) / 8 * 8 + 8) * 128;
+  // The rows of a 128-row MMA beyond R * Wp (shifted by the tap) lie past the end of the window: their results are
+  // discarded and MMA rows do not mix, so they may read whatever follows - the next window stage or, after the last
+  // one, the filter slabs (always more bytes than the overhang). No shared memory is set aside for them.
+  s->slack_bytes = 0;
   const int budget = 232448 - 1024 - 1024 - s->slack_bytes;
   for (s->G = 2; s->G >= 1; --s->G) {
     if (planes * s->G * c.Kout > 256 || (s->G > 1 && c.P <= s->R)) continue;   // f32 keeps two accumulators per sub-tile

@@ -964,6 +964,21 @@ RbStatus rb::conv_run(const RbConvProblem* p, int result_type, void* filter, voi
 
   HaloConv uhc;
   const bool on_halo = !capture && unit_halo(p, pl, epi != nullptr, &uhc);
+  // f32 forward on the streamed-filter halo kernel (csrc/conv_halo_stream_sm100.cu): decided here because a plain KCYX
+  // filter then goes to its two K-major TF32 planes in ONE transposing pass instead of a permutation and a split.
+  HaloConv f32_sc;
+  long long f32_o_k = 1;
+  const size_t fil_plane = up256((size_t)p->k * p->y * p->x * p->c * 4);
+  bool f32_stream = !on_halo && !capture && !epi && pl.a_implicit && !pl.a_up && p->direction == 0 && p->stride_h == 1 &&
+                    p->stride_w == 1 && !((rbGetGemmVariant() >> 26) & 1) && p->data_type == RB_F32 && pl.a_planes == 2 &&
+                    (pl.c_direct || pl.c_remap) && pl.gemm.c_type == RB_F32 && pl.gemm_ws >= 2 * fil_plane;
+  if (f32_stream) {
+    halo_geometry(p, &f32_sc);
+    if (pl.c_remap) { f32_sc.o_n = pl.os[0]; f32_sc.o_p = pl.os[3]; f32_sc.o_q = pl.os[4]; f32_o_k = pl.os[2]; }
+    f32_stream = conv_halo_stream_applicable(f32_sc, 4, f32_o_k);
+  }
+  const bool fil_kcyx = p->g == 1 && pl.fs[4] == 1 && pl.fs[3] == p->x && pl.fs[2] == (long long)p->y * p->x &&
+                        pl.fs[1] == (long long)p->c * p->y * p->x;
   const void* A;
   const void* B;
   void* C;
@@ -983,7 +998,9 @@ RbStatus rb::conv_run(const RbConvProblem* p, int result_type, void* filter, voi
   }
   if (p->direction == 0) {
     if (pl.a_direct) A = input; else { gather(input, ws + pl.a_off, false, false, ho, wo, p->c); A = ws + pl.a_off; }
-    if (pl.b_direct) B = filter; else { permute(filter, ws + pl.b_off, fsz, pl.fs, fil_kyxc, true, es); B = ws + pl.b_off; }
+    if (pl.b_direct) B = filter;
+    else if (f32_stream && fil_kcyx) B = nullptr;   // transposed and split in one pass below
+    else { permute(filter, ws + pl.b_off, fsz, pl.fs, fil_kyxc, true, es); B = ws + pl.b_off; }
     C = (pl.c_direct || pl.c_remap) ? output : static_cast<void*>(ws + pl.c_off);
   } else if (p->direction == 2) {
     if (pl.a_direct) A = output; else { permute(output, ws + pl.a_off, osz, pl.os, act_gmat, true, es); A = ws + pl.a_off; }
@@ -1032,20 +1049,15 @@ RbStatus rb::conv_run(const RbConvProblem* p, int result_type, void* filter, voi
         sc.Kout <= 128 && conv_halo_stream_applicable(sc, 2, 1))
       return conv_halo_stream_run(sc, 2, p->direction == 0 ? input : output, nullptr, B, nullptr, p->direction == 0 ? output : input, 1,
                                   stream_v);
-    const size_t fil_plane = up256((size_t)p->k * p->y * p->x * p->c * 4);
-    if (p->data_type == RB_F32 && p->direction == 0 && pl.a_planes == 2 && (pl.c_direct || pl.c_remap) && pl.gemm.c_type == RB_F32 &&
-        pl.gemm_ws >= 2 * fil_plane) {
-      long long o_k = 1;
-      if (pl.c_remap) { sc.o_n = pl.os[0]; sc.o_p = pl.os[3]; sc.o_q = pl.os[4]; o_k = pl.os[2]; }
-      if (conv_halo_stream_applicable(sc, 4, o_k)) {
-        float* fhi = reinterpret_cast<float*>(ws + pl.gemm_off);
-        float* flo = reinterpret_cast<float*>(ws + pl.gemm_off + fil_plane);
-        const int yxc = p->y * p->x * p->c;
-        st = f32_planes(static_cast<const float*>(B), fhi, flo, 1, p->k, yxc, yxc, false, true, stream_v);
-        if (st != RB_SUCCESS) return st;
-        return conv_halo_stream_run(sc, 4, a_hi, a_lo, fhi, flo, output, o_k, stream_v);
-      }
-    }
+  }
+  if (f32_stream) {
+    float* fhi = reinterpret_cast<float*>(ws + pl.gemm_off);
+    float* flo = reinterpret_cast<float*>(ws + pl.gemm_off + fil_plane);
+    const int yxc = p->y * p->x * p->c;
+    if (B) st = f32_planes(static_cast<const float*>(B), fhi, flo, 1, p->k, yxc, yxc, false, true, stream_v);
+    else st = f32_planes(static_cast<const float*>(filter), fhi, flo, p->k, p->c, p->y * p->x, p->c, true, true, stream_v);   // per k: [C][Y*X] -> [Y*X][C]
+    if (st != RB_SUCCESS) return st;
+    return conv_halo_stream_run(f32_sc, 4, a_hi, a_lo, fhi, flo, output, f32_o_k, stream_v);
   }
   if (pl.a_implicit) {
     ConvAOperand cv;
