@@ -15,6 +15,16 @@ namespace {
 thread_local int t_variant = 0;
 thread_local long long t_wait_cycles = kWaitCycles;   // rbSetWaitLimit
 thread_local int t_stall_launches = 0;                // rbInjectStall: GEMM launches left to stall
+// Chained pair (rbGemmGemm with equal inner extents): the G = 2 problem handed to gemm_run has group 0 = (a, b, c) and
+// group 1 = (c of group 0, b2, c2); gemm_run builds tensor maps whose group stride is the distance between the two
+// tensors and lets the kernel order the groups through flags (GemmParams::chain_flags).
+struct GemmChain {
+  const void* b2;
+  void* c2;
+  unsigned int* flags;
+  size_t flags_bytes;
+};
+thread_local const GemmChain* t_chain = nullptr;
 
 // ---- auxiliary kernels ---------------------------------------------------------------------------
 // Copies `rows` rows of `row_bytes` bytes into rows of `pitch_bytes` bytes, zero-filling the pad.
@@ -480,6 +490,25 @@ RbStatus rb::gemm_run(const RbGemmProblem* p, const RbEpilogue* epi, const void*
     cfg.sk_tiles = 0;
     ws = plan_workspace(p, oa, ob, cfg);
   }
+  const GemmChain* chain = t_chain;
+  // group 1 of a chained pair: A is group 0's C, B and C are the chain's; base = lower address, stride = distance
+  const void* chain_ptr[3][2] = {{a, c}, {b, chain ? chain->b2 : nullptr}, {c, chain ? chain->c2 : nullptr}};
+  uint64_t chain_stride[3] = {0, 0, 0};
+  int chain_flip = 0;
+  if (chain) {
+    if (p->g != 2 || oa.needs_copy || ob.needs_copy || cfg.splits != 1 || conva || epi || capture || p->trans_c ||
+        p->store_method != 0 || p->c_type != abt || p->k != p->n)
+      return fail(RB_UNSUPPORTED, "this pair of products does not run as one chained launch");
+    if (cfg.sk_tiles > 0) { cfg.sk_tiles = 0; ws = plan_workspace(p, oa, ob, cfg); }
+    for (int i = 0; i < 3; ++i) {
+      const uintptr_t x0 = reinterpret_cast<uintptr_t>(chain_ptr[i][0]), x1 = reinterpret_cast<uintptr_t>(chain_ptr[i][1]);
+      const uintptr_t d = x1 > x0 ? x1 - x0 : x0 - x1;
+      if (d == 0 || d % 16 || x0 % 16 || d >= ((uintptr_t)1 << 40))
+        return fail(RB_UNSUPPORTED, "chained launch: the two tensors of an operand must be distinct, 16-byte aligned and within 2^40 bytes");
+      chain_stride[i] = (uint64_t)d;
+      if (x1 < x0) chain_flip |= 1 << i;
+    }
+  }
   if (capture && (oa.needs_copy || ob.needs_copy || cfg.splits > 1))
     return fail(RB_UNSUPPORTED, "this problem runs as several kernels (operand copy, TF32 planes or a K split): it has no "
                                 "single-kernel binary; launch it through the library");
@@ -561,14 +590,17 @@ RbStatus rb::gemm_run(const RbGemmProblem* p, const RbEpilogue* epi, const void*
   auto encode_operand = [&](CUtensorMap* m, const void* base, const OperandPlan& o, int box_rows_kmajor,
                             std::string* err) {
     const bool fused = (&o == &oa) ? a_fused : b_fused;
+    const int ci = (&o == &oa) ? 0 : 1;
+    const uint64_t gstride = chain ? chain_stride[ci] : (uint64_t)o.rows * o.pitch * es;
+    if (chain) base = (chain_flip >> ci) & 1 ? chain_ptr[ci][1] : chain_ptr[ci][0];
     if (fused) {
       const uint64_t dims[4] = {(uint64_t)bke, (uint64_t)o.rows, (uint64_t)(o.cols / bke), (uint64_t)p->g};
-      const uint64_t strides[3] = {(uint64_t)o.pitch * es, (uint64_t)kRowBytes, (uint64_t)o.rows * o.pitch * es};
+      const uint64_t strides[3] = {(uint64_t)o.pitch * es, (uint64_t)kRowBytes, gstride};
       const uint32_t box[4] = {(uint32_t)bke, (uint32_t)bke, (uint32_t)(box_rows_kmajor / bke), 1u};
       return encode_tiled(m, dt, 4, base, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, err);
     }
     const uint64_t dims[3] = {(uint64_t)o.cols, (uint64_t)o.rows, (uint64_t)p->g};
-    const uint64_t strides[2] = {(uint64_t)o.pitch * es, (uint64_t)o.rows * o.pitch * es};
+    const uint64_t strides[2] = {(uint64_t)o.pitch * es, gstride};
     // K-major: box = BKE k-elements x tile rows. MN-major: box = one 128-byte chunk of MN x BKE k-rows.
     const uint32_t box[3] = {(uint32_t)bke, (uint32_t)(o.mn_major ? bke : box_rows_kmajor), 1u};
     return encode_tiled(m, dt, 3, base, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, err);
@@ -652,6 +684,8 @@ RbStatus rb::gemm_run(const RbGemmProblem* p, const RbEpilogue* epi, const void*
     kp.c_type = p->c_type;
     if (p->trans_c) { kp.c_stride_m = 1; kp.c_stride_n = p->m; } else { kp.c_stride_m = p->n; kp.c_stride_n = 1; }
     kp.c_stride_g = (long long)p->m * p->n;
+    if (chain)   // signed distance from group 0's result to group 1's, in elements
+      kp.c_stride_g = (reinterpret_cast<intptr_t>(chain->c2) - reinterpret_cast<intptr_t>(c)) / (intptr_t)es_c;
     kp.vec_ok = (!p->trans_c && ((size_t)p->n * es_c) % 16 == 0 && reinterpret_cast<uintptr_t>(c) % 16 == 0) ? 1 : 0;
     kp.c_tma = (kp.vec_ok && !cfg.plain_stores) ? 1 : 0;
     if (conva && conva->c_rows_per_img > 0) {   // NKHW result: strided element stores, coalesced along the pixels
@@ -673,9 +707,10 @@ RbStatus rb::gemm_run(const RbGemmProblem* p, const RbEpilogue* epi, const void*
                                     : st_type == RB_I32  ? CU_TENSOR_MAP_DATA_TYPE_INT32
                                                          : CU_TENSOR_MAP_DATA_TYPE_UINT8;
     const uint64_t cdims[3] = {(uint64_t)p->n, (uint64_t)p->m, (uint64_t)p->g * splits};
-    const uint64_t cstrides[2] = {(uint64_t)p->n * es_st, (uint64_t)p->m * p->n * es_st};
+    const uint64_t cstrides[2] = {(uint64_t)p->n * es_st, chain ? chain_stride[2] : (uint64_t)p->m * p->n * es_st};
     const uint32_t cbox[3] = {(uint32_t)(kRowBytes / es_st), 32u, 1u};
-    if (!encode_tiled(&maps.c, cdt, 3, kp.c, cdims, cstrides, cbox, CU_TENSOR_MAP_SWIZZLE_128B, &err))
+    void* cbase = (chain && (chain_flip & 4)) ? chain->c2 : kp.c;
+    if (!encode_tiled(&maps.c, cdt, 3, cbase, cdims, cstrides, cbox, CU_TENSOR_MAP_SWIZZLE_128B, &err))
       return fail(RB_UNSUPPORTED, "C: " + err);
   }
   kp.status = dev->status_word;
@@ -693,6 +728,14 @@ RbStatus rb::gemm_run(const RbGemmProblem* p, const RbEpilogue* epi, const void*
   kp.a_fused = a_fused ? 1 : 0;
   kp.b_fused = b_fused ? 1 : 0;
 
+  if (chain) {
+    if ((size_t)kp.tiles_m * kp.tiles_n * ctas * 4 * sizeof(unsigned int) > chain->flags_bytes)
+      return fail(RB_UNSUPPORTED, "chained launch: too many tiles for the flag words");
+    static std::atomic<unsigned int> next_chain_token{0xc4a10001u};
+    kp.chain_flags = chain->flags;
+    kp.chain_token = next_chain_token.fetch_add(1, std::memory_order_relaxed);
+    kp.chain_flip = chain_flip;
+  }
   const long long num_tiles = (long long)kp.G * kp.tiles_m * kp.tiles_n;
   const long long num_items = num_tiles * splits;
   if (num_items > 0x7fffffffLL) return fail(RB_UNSUPPORTED, "too many tiles");
@@ -721,11 +764,11 @@ RbStatus rb::gemm_run(const RbGemmProblem* p, const RbEpilogue* epi, const void*
   lc.dynamicSmemBytes = (size_t)smem;
   lc.stream = stream;
   cudaLaunchAttribute attr[1];
+  lc.attrs = attr;
   if (ctas == 2) {
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-    lc.attrs = attr;
-    lc.numAttrs = 1;
+    attr[lc.numAttrs].id = cudaLaunchAttributeClusterDimension;
+    attr[lc.numAttrs].val.clusterDim.x = 2; attr[lc.numAttrs].val.clusterDim.y = 1; attr[lc.numAttrs].val.clusterDim.z = 1;
+    ++lc.numAttrs;
     const int pairs = dev->sm_count / 2;
     lc.gridDim = dim3((unsigned)(2 * (int)std::min<long long>(num_items, pairs)), 1, 1);
   } else {
@@ -829,9 +872,14 @@ extern "C" RbStatus rbGemmNoAlloc(const RbGemmProblem* p, const RbEpilogue* epi,
 // with the softmax removed (mlir/lib/Dialect/Rock/Transforms/GridwiseGemmToBlockwise.cpp:1790-1813, 2162-2165).
 // With k1 and n2 at most 128 (the shapes of that skeleton) it runs on the attention kernel in one launch: S = A . B1
 // in tensor memory, rounded to the element type in place, second product straight from there; no workspace. Larger
-// inner extents do not fit the SM (O alone would be 128 x n2 f32 in TMEM): two launches of the GEMM kernel, the
-// intermediate (M x N1, element type) in the caller's workspace, small enough to stay in L2 between them. Variant
-// bit 27 forces the two-launch form.
+// inner extents do not fit the SM (O alone would be 128 x n2 f32 in TMEM): the intermediate (M x N1, element type)
+// goes through the caller's workspace, small enough to stay in L2 - as one chained launch of the GEMM kernel when
+// k1 = n1 = n2 (see below), else as two launches. Variant bit 27 forces the two-launch form.
+// Flag words of the chained form: four per (128-row block, tile of columns), for tiles of 32 columns or more.
+static size_t chain_flag_bytes(int m, int n1) {
+  return rb::align_up((size_t)((m + 127) / 128) * ((n1 + 31) / 32) * 4 * sizeof(unsigned int), 256);
+}
+
 extern "C" size_t rbGemmGemmWorkspaceSize(int32_t g, int32_t m, int32_t k1, int32_t n1, int32_t n2, int32_t data_type) {
   if (g <= 0 || m <= 0 || k1 <= 0 || n1 <= 0 || n2 <= 0 || !rb::dtype_bytes(data_type)) return 0;
   // (the one-launch form needs none of it; the size is reported for the two-launch form so that a caller who sized
@@ -839,7 +887,7 @@ extern "C" size_t rbGemmGemmWorkspaceSize(int32_t g, int32_t m, int32_t k1, int3
   RbGemmProblem p1 = {g, m, n1, k1, 0, 0, 0, data_type, data_type, 0};
   RbGemmProblem p2 = {g, m, n2, n1, 0, 0, 0, data_type, data_type, 0};
   const size_t mid = rb::align_up((size_t)g * m * n1 * rb::dtype_bytes(data_type), 256);
-  return mid + std::max(rbGemmWorkspaceSize(&p1), rbGemmWorkspaceSize(&p2));
+  return mid + std::max(rbGemmWorkspaceSize(&p1), rbGemmWorkspaceSize(&p2)) + chain_flag_bytes(m, n1);
 }
 
 extern "C" RbStatus rbGemmGemm(int32_t g, int32_t m, int32_t k1, int32_t n1, int32_t n2, int32_t data_type,
@@ -857,6 +905,19 @@ extern "C" RbStatus rbGemmGemm(int32_t g, int32_t m, int32_t k1, int32_t n1, int
   RbGemmProblem p2 = {g, m, n2, n1, 0, 0, 0, data_type, data_type, 0};
   const size_t mid = rb::align_up((size_t)g * m * n1 * rb::dtype_bytes(data_type), 256);
   uint8_t* ws = static_cast<uint8_t*>(workspace);
+  // Equal inner extents (k1 = n1 = n2), one group, 16-bit: ONE launch of the GEMM kernel over a two-group problem whose
+  // second group reads the first group's result; the tiles of the second product start as soon as the row block of the
+  // intermediate they read is complete, so there is no drain and refill between the products. Variant bit 27 keeps
+  // the two-launch form; shapes or pointers the chained form does not take fall through to it.
+  if (g == 1 && k1 == n1 && n1 == n2 && data_type != RB_F32 && !((rbGetGemmVariant() >> 27) & 1)) {
+    const size_t fb = chain_flag_bytes(m, n1);
+    RbGemmProblem pc = {2, m, n1, k1, 0, 0, 0, data_type, data_type, 0};
+    rb::GemmChain ch = {b2, o, reinterpret_cast<unsigned int*>(ws + need - fb), fb};
+    rb::t_chain = &ch;
+    const RbStatus cst = rbGemm(&pc, nullptr, a, b1, ws, nullptr, 0, stream);
+    rb::t_chain = nullptr;
+    if (cst != RB_UNSUPPORTED) return cst;
+  }
   RbStatus st = rbGemm(&p1, nullptr, a, b1, ws, ws + mid, workspace_bytes - mid, stream);
   if (st != RB_SUCCESS) return st;
   return rbGemm(&p2, nullptr, ws, b2, o, ws + mid, workspace_bytes - mid, stream);

@@ -116,6 +116,14 @@ struct GemmParams {
   // pixels per image goes to image * c_img_stride + pixel * c_stride_m, column n adds n * c_stride_n. 0 = plain rows.
   int c_rows_per_img;
   long long c_img_stride;
+  // Chained pair (G = 2, csrc/gemm_sm100.cu rbGemmGemm): group 1's A operand is group 0's result. The epilogue warps of a
+  // group-0 tile raise chain_flags[m block][(n block, CTA, warp)] = chain_token once their rows are in global memory;
+  // the producer of a group-1 tile waits for every word of its m block before its first load. Tiles are numbered group
+  // 0 first and dealt round-robin, so a waiting CTA has finished all of its own group-0 tiles. chain_flip: bit 0 / 1 /
+  // 2 = the tensor map of A / B / C holds group 1 at the lower address (group coordinate = g ^ 1).
+  unsigned int* chain_flags;
+  unsigned int chain_token;
+  int chain_flip;
 };
 
 // Implicit B operand: base coordinates of output pixel `pix` (row-major n, p, q) and the tap / channel chunk of
@@ -286,7 +294,6 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
-
   if (warp == 0) {
     // ------------------------------ producer ------------------------------
     if (lane_id() == 0) {
@@ -302,6 +309,11 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
         const int n0 = nb * p.bn + (int)rank * bn_cta;
         const int kb_begin = w.kb_begin, kb_end = w.kb_end;
         const int ktotal = (kb_end - kb_begin) * p.nseg;
+        const int ga = g ^ (p.chain_flip & 1), gb = g ^ ((p.chain_flip >> 1) & 1);
+        if (p.chain_flags != nullptr && g == 1) {   // A of this tile is the result of group 0's tiles of the same m block
+          const int nw = p.tiles_n * CTAS * 4;
+          if (!flags_wait(p.chain_flags + (size_t)mb * nw, nw, p.chain_token, p.status, kStatusTimeoutAux + 2, wait_limit)) { ok = false; break; }
+        }
         int img = 0, base_h = 0, base_w = 0;
         if (p.conva.enabled == 1) {
           const int pq = p.conva.P * p.conva.Q;
@@ -341,16 +353,16 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
                 tma_load_im2col_4d(sa, &maps.a[seg], &full_bar[s], cc * BKE, base_w, base_h, img,
                                    (uint16_t)(fx * p.conva.dil_w), (uint16_t)(fy * p.conva.dil_h));
               } else if constexpr (!A_MN) {
-                tma_load_3d(sa, &maps.a[seg], &full_bar[s], k0, m0, g);
+                tma_load_3d(sa, &maps.a[seg], &full_bar[s], k0, m0, ga);
               } else if (p.a_fused) {
-                tma_load_4d(sa, &maps.a[seg], &full_bar[s], 0, k0, m0 / CHE, g);
+                tma_load_4d(sa, &maps.a[seg], &full_bar[s], 0, k0, m0 / CHE, ga);
               } else {
   #pragma unroll
                 for (int c = 0; c < kBM / CHE; ++c)
-                  tma_load_3d(sa + c * CHUNK_BYTES, &maps.a[seg], &full_bar[s], m0 + c * CHE, k0, g);
+                  tma_load_3d(sa + c * CHUNK_BYTES, &maps.a[seg], &full_bar[s], m0 + c * CHE, k0, ga);
               }
               if constexpr (!B_MN) {
-                tma_load_3d(sb, &maps.b[seg], &full_bar[s], k0, n0, g);
+                tma_load_3d(sb, &maps.b[seg], &full_bar[s], k0, n0, gb);
               } else if (p.conva.enabled == 2) {
                 int bi, bh, bw;
                 convb_pixel(p.conva, k0, bi, bh, bw);
@@ -361,10 +373,10 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
                                      (uint16_t)(fx * p.conva.dil_w), (uint16_t)(fy * p.conva.dil_h));
                 }
               } else if (p.b_fused) {
-                tma_load_4d(sb, &maps.b[seg], &full_bar[s], 0, k0, n0 / CHE, g);
+                tma_load_4d(sb, &maps.b[seg], &full_bar[s], 0, k0, n0 / CHE, gb);
               } else {
                 for (int c = 0; c < bn_cta / CHE; ++c)
-                  tma_load_3d(sb + c * CHUNK_BYTES, &maps.b[seg], &full_bar[s], n0 + c * CHE, k0, g);
+                  tma_load_3d(sb + c * CHUNK_BYTES, &maps.b[seg], &full_bar[s], n0 + c * CHE, k0, gb);
               }
             } else {
               // Completion of this CTA's loads is counted on the leader CTA's barrier.
@@ -375,16 +387,16 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
                 tma_load_im2col_4d_bar(sa, &maps.a[seg], lead_full, cc * BKE, base_w, base_h, img,
                                        (uint16_t)(fx * p.conva.dil_w), (uint16_t)(fy * p.conva.dil_h));
               } else if constexpr (!A_MN) {
-                tma_load_3d_bar(sa, &maps.a[seg], lead_full, k0, m0, g);
+                tma_load_3d_bar(sa, &maps.a[seg], lead_full, k0, m0, ga);
               } else if (p.a_fused) {
-                tma_load_4d_bar(sa, &maps.a[seg], lead_full, 0, k0, m0 / CHE, g);
+                tma_load_4d_bar(sa, &maps.a[seg], lead_full, 0, k0, m0 / CHE, ga);
               } else {
   #pragma unroll
                 for (int c = 0; c < kBM / CHE; ++c)
-                  tma_load_3d_bar(sa + c * CHUNK_BYTES, &maps.a[seg], lead_full, m0 + c * CHE, k0, g);
+                  tma_load_3d_bar(sa + c * CHUNK_BYTES, &maps.a[seg], lead_full, m0 + c * CHE, k0, ga);
               }
               if constexpr (!B_MN) {
-                tma_load_3d_bar(sb, &maps.b[seg], lead_full, k0, n0, g);
+                tma_load_3d_bar(sb, &maps.b[seg], lead_full, k0, n0, gb);
               } else if (p.conva.enabled == 2) {
                 int bi, bh, bw;
                 convb_pixel(p.conva, k0, bi, bh, bw);
@@ -395,10 +407,10 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
                                          (uint16_t)(fx * p.conva.dil_w), (uint16_t)(fy * p.conva.dil_h));
                 }
               } else if (p.b_fused) {
-                tma_load_4d_bar(sb, &maps.b[seg], lead_full, 0, k0, n0 / CHE, g);
+                tma_load_4d_bar(sb, &maps.b[seg], lead_full, 0, k0, n0 / CHE, gb);
               } else {
                 for (int c = 0; c < bn_cta / CHE; ++c)
-                  tma_load_3d_bar(sb + c * CHUNK_BYTES, &maps.b[seg], lead_full, n0 + c * CHE, k0, g);
+                  tma_load_3d_bar(sb + c * CHUNK_BYTES, &maps.b[seg], lead_full, n0 + c * CHE, k0, gb);
               }
             }
             if (++kb == kb_end) { kb = kb_begin; ++seg; }
@@ -555,7 +567,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
       const long long row = row0 + lane;
       const bool row_ok = row < p.M;
       const int ngroups = p.bn / 32;
-      const int gz = w.split * p.G + g;   // group coordinate of the store map (K-split planes are stacked groups)
+      const int gz = w.split * p.G + (g ^ ((p.chain_flip >> 2) & 1));   // group coordinate of the store map (K-split planes are stacked groups)
       // Per-column scales / biases of this tile, converted to f32, in this warp's private copy.
       float* vec_scale = epi_vecs + q * (2 * kMaxBN);
       float* vec_bias = vec_scale + kMaxBN;
@@ -865,6 +877,14 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
       if (lane == 0) {
         if constexpr (CTAS == 1) mbar_arrive(&tempty_bar[buf]);
         else mbar_arrive_cluster(&tempty_bar[buf], 0);
+      }
+      if (p.chain_flags != nullptr && g == 0) {
+        // this warp's rows of the intermediate are complete in global memory before its flag says so
+        if (p.c_tma && lane == 0) { bulk_wait<0>(); fence_proxy_async_all(); }
+        __threadfence();
+        __syncwarp();
+        if (lane == 0)
+          *reinterpret_cast<volatile unsigned int*>(p.chain_flags + (size_t)mb * (p.tiles_n * CTAS * 4) + (nb * CTAS + (int)rank) * 4 + q) = p.chain_token;
       }
       if (p.trace) e_work += clock64() - te;
     }

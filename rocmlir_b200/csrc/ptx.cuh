@@ -52,6 +52,29 @@ __device__ __forceinline__ void fence_mbar_init() {
 __device__ __forceinline__ void fence_proxy_async() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
+// Orders generic-proxy and async-proxy (TMA) accesses of this thread in every state space: used where a tile that
+// another CTA wrote to global memory is about to be fetched by TMA, and where TMA stores precede a flag.
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+// Bounded wait until the n words at `flags` all hold `token` (one thread; the loads of a batch are in flight together).
+__device__ __forceinline__ bool flags_wait(const unsigned int* flags, int n, unsigned int token, uint32_t* status, uint32_t code,
+                                           long long limit) {
+  const long long t0 = clock64();
+  for (;;) {
+    bool all = true;
+    for (int i = 0; i < n; i += 8) {
+      unsigned int v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = (i + j < n) ? *reinterpret_cast<const volatile unsigned int*>(flags + i + j) : token;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) all = all && v[j] == token;
+    }
+    if (all) break;
+    if (clock64() - t0 > limit) { atomicCAS(status, 0u, code); return false; }
+  }
+  __threadfence();
+  fence_proxy_async_all();
+  return true;
+}
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
                "r"(bytes)

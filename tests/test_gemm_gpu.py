@@ -288,6 +288,45 @@ def test_gemm_gemm_on_chip_equals_two_launches(cuda_device):
     assert (fused.float() - plain.float()).abs().max().item() <= 2.0 ** -7 * scale
 
 
+@pytest.mark.parametrize("variant", [0, 1 | (3 << 12), 2 | (3 << 12), 1 | (2 << 12), 1 | (1 << 12)])
+@pytest.mark.parametrize("m,k,dtype", [(4096, 1024, "float16"), (1000, 512, "bfloat16"), (300, 192, "float16"),
+                                       (2304, 320, "float16")])
+def test_gemm_gemm_chained_launch_equals_two_launches(cuda_device, m, k, dtype, variant):
+    """k1 = n1 = n2: one launch of the GEMM kernel over two groups, the second reading the first one's result as its
+    tiles' row blocks complete - bit for bit the two-launch form (variant bit 27), with either tensor of each operand
+    at the lower address (the group coordinate of the tensor maps flips), for every tile shape."""
+    import torch
+    from rocmlir_b200 import _lib as L
+    from rocmlir_b200.gemm import gemm_gemm
+    dt = getattr(torch, dtype)
+    gen = torch.Generator(device="cuda").manual_seed(m + k)
+    lib = L.lib()
+    for ws_first in (False, True):
+        ws = torch.empty(32 << 20, dtype=torch.uint8, device="cuda") if ws_first else None
+        a = (torch.randn((m, k), device="cuda", generator=gen) * 0.1).to(dt)
+        bx = (torch.randn((k, k), device="cuda", generator=gen) * 0.1).to(dt)
+        by = (torch.randn((k, k), device="cuda", generator=gen) * 0.1).to(dt)
+        b1, b2 = (by, bx) if ws_first else (bx, by)
+        o = torch.zeros((m, k), device="cuda", dtype=dt)
+        if ws is None:
+            ws = torch.empty(32 << 20, dtype=torch.uint8, device="cuda")
+        try:
+            lib.rbSetGemmVariant(variant)
+            n0 = L.launch_count()
+            chained = gemm_gemm(a, b1, b2, out=o, workspace=ws).clone()
+            torch.cuda.synchronize()
+            assert L.launch_count() - n0 == 1
+            lib.rbSetGemmVariant(variant | (1 << 27))
+            plain = gemm_gemm(a, b1, b2, out=o, workspace=ws)
+            torch.cuda.synchronize()
+        finally:
+            lib.rbSetGemmVariant(0)
+        assert L.kernel_status() == 0
+        assert torch.equal(chained, plain)
+        ref = (a.float() @ b1.float()).to(dt).float() @ b2.float()
+        assert (chained.float() - ref).abs().max().item() <= 2.0 ** -6 * ref.abs().max().item()
+
+
 @pytest.mark.parametrize("code,shape", [(oracle.F16, (1, 2304, 2560, 1024)), (oracle.I8, (1, 1300, 3000, 2048)),
                                         (oracle.F16, (2, 1200, 1100, 640))])
 @pytest.mark.parametrize("ctas", [1, 2])
