@@ -309,7 +309,10 @@ RB_EXPORT RbStatus rbUnpackInt4(const void *packed, void *out, int64_t packed_by
 /* GEMM + GEMM: O[g] = (A[g] . B1[g]) . B2[g], A G x M x K1, B1 G x K1 x N1, B2 G x N1 x N2, O G x M x N2, the
  * intermediate rounded to the element type, both products accumulated in f32 — the attention skeleton of the
  * reference with the softmax removed (mlir/include/mlir/Dialect/Rock/IR/Rock.h:52-56,
- * mlir/lib/Dialect/Rock/Transforms/GridwiseGemmToBlockwise.cpp:1790-1813). The intermediate is kept in `workspace`. */
+ * mlir/lib/Dialect/Rock/Transforms/GridwiseGemmToBlockwise.cpp:1790-1813). With k1, n2 <= 128 the intermediate stays
+ * on the SM (one launch, no workspace use); otherwise it is kept in `workspace` (which must not overlap the operands),
+ * written and read by one chained launch when k1 = n1 = n2 (16-bit types; the workspace then also holds the flag
+ * words that order the two products) and by two launches for other extents. */
 RB_EXPORT size_t rbGemmGemmWorkspaceSize(int32_t g, int32_t m, int32_t k1, int32_t n1, int32_t n2, int32_t data_type);
 RB_EXPORT RbStatus rbGemmGemm(int32_t g, int32_t m, int32_t k1, int32_t n1, int32_t n2, int32_t data_type, const void *a,
                               const void *b1, const void *b2, void *o, void *workspace, size_t workspace_bytes,
