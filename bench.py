@@ -396,8 +396,11 @@ def build_workload(name, dev, sets, rank=0, world=1, gather=False):
         abytes = (cfg.numel("fil") + cfg.numel("in") + cfg.numel("out")) * es * nsets
         ai = cfg.flops() / (abytes / nsets)
         return dict(step=step, finish=finish, work=cfg.flops() * nsets, unit="TFLOP/s", bytes=abytes,
-                    bound=("tensor" if ai > 281 else "hbm"), dtype=("f32" if es == 4 else "f16"), verify=verify, desc=desc,
-                    kernel="conv_halo_kernel / conv_wgrad_halo_kernel (unit-stride NHWC 16-bit, stride classes) or gemm_tcgen05_kernel (+ layout / reduction passes)")
+                    # ridge: 16-bit tensor peak / HBM rate in FLOP per byte; f32 runs as three TF32 products (a sixth of it)
+                    bound=("tensor" if ai > (281 / 6 if es == 4 else 281) else "hbm"), dtype=("f32" if es == 4 else "f16"),
+                    verify=verify, desc=desc,
+                    kernel=("conv_halo_stream_kernel<f32> (+ TF32 plane passes of image and filter)" if es == 4 else
+                            "conv_halo_kernel / conv_wgrad_halo_kernel (unit-stride NHWC 16-bit, stride classes) or gemm_tcgen05_kernel (+ layout / reduction passes)"))
     if name.startswith("attention_f16"):
         from rocmlir_b200.attention import attention, flops
         causal = name.endswith("causal")

@@ -677,6 +677,8 @@ using namespace rb;
 // data is the same kernel over the output gradient with mirrored taps, which it reads straight from a KYXC filter
 // (hc->b_mn) when the layout allows. Variant bit 26 keeps the im2col form.
 static void halo_geometry(const RbConvProblem* p, HaloConv* hc);
+static bool f32_streamed(const RbConvProblem* p, const ConvPlan& pl, HaloConv* sc, long long* o_k);
+static bool filter_is_kcyx(const RbConvProblem* p, const ConvPlan& pl);
 static bool unit_halo(const RbConvProblem* p, const ConvPlan& pl, bool has_epi, HaloConv* hc) {
   if (p->direction > 1 || !pl.a_implicit || pl.a_planes != 0 || pl.a_up || !pl.c_direct || p->stride_h != 1 || p->stride_w != 1 ||
       !(p->data_type == RB_F16 || p->data_type == RB_BF16) || !(has_epi || pl.gemm.c_type == p->data_type) ||
@@ -691,6 +693,24 @@ static bool unit_halo(const RbConvProblem* p, const ConvPlan& pl, bool has_epi, 
     hc->b_mn = false;
   }
   return conv_halo_applicable(*hc);
+}
+
+// f32 forward on the streamed-filter halo kernel (csrc/conv_halo_stream_sm100.cu): unit stride, one group, the image as
+// two TF32 planes; the kernel stores the result with the output tensor's own strides (NHWK, NKHW or any other order).
+static bool f32_streamed(const RbConvProblem* p, const ConvPlan& pl, HaloConv* sc, long long* o_k) {
+  const size_t fil_plane = up256((size_t)p->k * p->y * p->x * p->c * 4);
+  if (!(pl.a_implicit && !pl.a_up && p->direction == 0 && p->stride_h == 1 && p->stride_w == 1 && p->g == 1 &&
+        !((rbGetGemmVariant() >> 26) & 1) && p->data_type == RB_F32 && pl.a_planes == 2 && pl.gemm.c_type == RB_F32 &&
+        pl.gemm_ws >= 2 * fil_plane))
+    return false;
+  halo_geometry(p, sc);
+  *o_k = 1;
+  if (!pl.c_direct) { sc->o_n = pl.os[0]; sc->o_p = pl.os[3]; sc->o_q = pl.os[4]; *o_k = pl.os[2]; }
+  return conv_halo_stream_applicable(*sc, 4, *o_k);
+}
+static bool filter_is_kcyx(const RbConvProblem* p, const ConvPlan& pl) {
+  return p->g == 1 && pl.fs[4] == 1 && pl.fs[3] == p->x && pl.fs[2] == (long long)p->y * p->x &&
+         pl.fs[1] == (long long)p->c * p->y * p->x;
 }
 
 // The unit-stride convolution as the halo kernels see it: forward over the input, or backward data as a forward
@@ -742,6 +762,12 @@ extern "C" int rbConvKernelCount(const RbConvProblem* p) {
   {
     HaloConv hc;
     if (pl.n_classes == 0 && unit_halo(p, pl, false, &hc) && hc.b_mn) return 1;   // backward data, filter read in place
+  }
+  {
+    HaloConv sc;
+    long long o_k;
+    if (pl.n_classes == 0 && f32_streamed(p, pl, &sc, &o_k))   // image planes, filter planes (after a permutation unless KYXC / KCYX), kernel
+      return 3 + ((pl.b_direct || filter_is_kcyx(p, pl)) ? 0 : 1);
   }
   if (pl.n_classes > 0) {
     int n = 1 + (pl.cls_fused ? 1 : 0);   // the interleaving pass (and the one filter pass of the fused form)
@@ -969,16 +995,8 @@ RbStatus rb::conv_run(const RbConvProblem* p, int result_type, void* filter, voi
   HaloConv f32_sc;
   long long f32_o_k = 1;
   const size_t fil_plane = up256((size_t)p->k * p->y * p->x * p->c * 4);
-  bool f32_stream = !on_halo && !capture && !epi && pl.a_implicit && !pl.a_up && p->direction == 0 && p->stride_h == 1 &&
-                    p->stride_w == 1 && !((rbGetGemmVariant() >> 26) & 1) && p->data_type == RB_F32 && pl.a_planes == 2 &&
-                    (pl.c_direct || pl.c_remap) && pl.gemm.c_type == RB_F32 && pl.gemm_ws >= 2 * fil_plane;
-  if (f32_stream) {
-    halo_geometry(p, &f32_sc);
-    if (pl.c_remap) { f32_sc.o_n = pl.os[0]; f32_sc.o_p = pl.os[3]; f32_sc.o_q = pl.os[4]; f32_o_k = pl.os[2]; }
-    f32_stream = conv_halo_stream_applicable(f32_sc, 4, f32_o_k);
-  }
-  const bool fil_kcyx = p->g == 1 && pl.fs[4] == 1 && pl.fs[3] == p->x && pl.fs[2] == (long long)p->y * p->x &&
-                        pl.fs[1] == (long long)p->c * p->y * p->x;
+  const bool f32_stream = !on_halo && !capture && !epi && f32_streamed(p, pl, &f32_sc, &f32_o_k);
+  const bool fil_kcyx = filter_is_kcyx(p, pl);
   const void* A;
   const void* B;
   void* C;

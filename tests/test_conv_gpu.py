@@ -87,6 +87,52 @@ def test_conv_exact_on_reference_integer_data(cuda_device, shape, code, layout, 
     np.testing.assert_array_equal(got.ravel(), ref_raw.ravel())
 
 
+# Shapes of the halo kernel with a streamed filter: 16-bit layers whose filter does not fit into shared memory beside the
+# windows (forward and unit-stride backward data, up to 128 output channels), and f32 forward with reductions of up to
+# 1024 elements (two TF32 planes of window and filter, NHWK or NKHW stored by the kernel): ragged last tiles, one and
+# two sub-tiles per stage, dilation, asymmetric extents, images lower than a tile.
+STREAMED = [
+    (dict(n=3, c=128, k=128, h=13, w=11, y=3, x=3, pad_h=1, pad_w=1), (oracle.F16, oracle.BF16)),
+    (dict(n=2, c=192, k=96, h=9, w=20, y=3, x=3, pad_h=1, pad_w=1), (oracle.F16,)),
+    (dict(n=2, c=256, k=64, h=30, w=30, y=3, x=3, dil_h=2, dil_w=2, pad_h=2, pad_w=2), (oracle.BF16,)),
+    (dict(n=2, c=64, k=64, h=12, w=12, y=3, x=3, pad_h=1, pad_w=1), (oracle.F32,)),
+    (dict(n=1, c=32, k=96, h=10, w=17, y=3, x=3, dil_h=2, dil_w=2, pad_h=2, pad_w=2), (oracle.F32,)),
+    (dict(n=5, c=96, k=32, h=3, w=40, y=3, x=3, pad_h=1, pad_w=1), (oracle.F32,)),
+    (dict(n=2, c=32, k=128, h=20, w=9, y=5, x=5, pad_h=2, pad_w=2), (oracle.F32,)),
+]
+
+
+@pytest.mark.parametrize("direction", [0, 1])
+@pytest.mark.parametrize("layout", ["nhwc", "nchw"])
+@pytest.mark.parametrize("case", STREAMED, ids=lambda c: "x".join(str(v) for v in c[0].values()))
+def test_streamed_filter_halo_kernel_exact(cuda_device, case, layout, direction):
+    """Bit for bit against the oracle on `-rand 1` integer data, and bit for bit against the im2col form of the same
+    library (variant bit 26) - the two differ in kernel, tile order and, for f32, in how the three TF32 products are
+    summed, none of which may show on data whose sums are exact."""
+    from rocmlir_b200 import _lib as L
+    shape, codes = case
+    for code in codes:
+        if layout == "nchw" and code != oracle.F32:
+            continue   # channel-major 16-bit tensors take the gather path: not this kernel
+        cfg, ocfg = make_cfgs(**shape, **LAYOUTS[layout])
+        (ff, fraw), (inf, iraw), (of, oraw) = reference_random([(ocfg.numel("fil"),), (ocfg.numel("in"),),
+                                                               (ocfg.numel("out"),)], code, seed=3)
+        ref_raw = oracle.from_f32(oracle.conv_f32(ocfg, direction, ff, inf, of, threads=oracle.max_threads()), code)
+        n0 = L.launch_count()
+        got = run_conv(cfg, direction, code, {"fil": fraw, "in": iraw, "out": oraw})
+        np.testing.assert_array_equal(got.ravel(), ref_raw.ravel())
+        if code == oracle.F32 and direction == 0:   # image planes, filter planes, kernel: what rbConvKernelCount reports
+            import ctypes
+            import torch
+            assert L.launch_count() - n0 == 3 == L.lib().rbConvKernelCount(ctypes.byref(cfg.to_c(torch.float32, 0, 0)))
+        L.lib().rbSetGemmVariant(1 << 26)
+        try:
+            other = run_conv(cfg, direction, code, {"fil": fraw, "in": iraw, "out": oraw})
+        finally:
+            L.lib().rbSetGemmVariant(0)
+        np.testing.assert_array_equal(got.ravel(), other.ravel())
+
+
 # Backward data with a stride runs as one unit-stride problem per class of input pixels (h mod stride, w mod stride):
 # classes without any tap (1x1 filter, stride 2), more classes than taps (stride 3 under a 2x2 filter), different
 # strides per axis, odd extents, groups, a padding larger than the stride.
