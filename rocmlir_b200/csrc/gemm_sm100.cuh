@@ -622,8 +622,13 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
       // compact loop - 64 columns = one 128-byte staging row per step. The general loop below handles every other
       // case; keeping this one small matters because the general loop's code is far larger than the instruction
       // cache and ran at about 1400 cycles per 32 columns where this one needs about 150.
-      const bool fast16 = w.kind == 0 && p.c_tma && p.epi.flags == 0 && !p.acc_is_int && !probe &&
-                          (p.c_type == RB_F16 || p.c_type == RB_BF16);
+      // The per-column bias add and the rectifier (the GEMM + bias + ReLU of a linear layer) ride along in the same loop:
+      // through the general loop that epilogue took 31k cycles per tile, five times the plain one, and its code
+      // evicted the other roles' instructions (the issue loop waited twice as long for operands).
+      const uint32_t f16_extra = p.epi.flags & ~(uint32_t)(RB_EPI_BIAS | RB_EPI_RELU);
+      const bool f16_bias = epi_col_bias(p.epi.flags), f16_relu = (p.epi.flags & RB_EPI_RELU) != 0;
+      const bool fast16 = w.kind == 0 && p.c_tma && f16_extra == 0 && (f16_bias || !(p.epi.flags & RB_EPI_BIAS)) &&
+                          !p.acc_is_int && !probe && (p.c_type == RB_F16 || p.c_type == RB_BF16);
       // 4-byte C (f32 results, raw i32 results, the raw planes of a K split): 32 columns = one staging row per step
       const bool fast32 = w.kind == 0 && p.c_tma && !probe &&
                           ((p.epi.flags == 0 && !p.acc_is_int && p.c_type == RB_F32) || raw_i32);
@@ -637,10 +642,27 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
           uint32_t v[64];
           tmem_ld32(taddr + cp * 64, v);
           tmem_ld32(taddr + cp * 64 + 32, v + 32);
-          uint8_t* stg = my_staging + (nstores & 1u) * L::kStoreTileBytes;
-          if (lane == 0 && nstores >= 2) bulk_wait_read<1>();  // the store that last used this buffer has read it
+          uint8_t* stg = my_staging + (stg_bufs == 2 ? (nstores & 1u) : 0u) * L::kStoreTileBytes;
+          if (lane == 0 && nstores >= stg_bufs) {   // the store that last used this buffer has read it
+            if (stg_bufs == 2) bulk_wait_read<1>(); else bulk_wait_read<0>();
+          }
           __syncwarp();
           tmem_ld_wait();
+          if (f16_bias) {   // same operations, same order as epi_apply32: add (round to nearest), then the rectifier
+            const float* bs = vec_bias + cp * 64;
+#pragma unroll
+            for (int j = 0; j < 64; j += 4) {
+              const float4 b4 = *reinterpret_cast<const float4*>(bs + j);
+              v[j] = __float_as_uint(__fadd_rn(__uint_as_float(v[j]), b4.x));
+              v[j + 1] = __float_as_uint(__fadd_rn(__uint_as_float(v[j + 1]), b4.y));
+              v[j + 2] = __float_as_uint(__fadd_rn(__uint_as_float(v[j + 2]), b4.z));
+              v[j + 3] = __float_as_uint(__fadd_rn(__uint_as_float(v[j + 3]), b4.w));
+            }
+          }
+          if (f16_relu) {
+#pragma unroll
+            for (int j = 0; j < 64; ++j) v[j] = __float_as_uint(fmaxf(__uint_as_float(v[j]), 0.0f));
+          }
           uint8_t* rowp = stg + lane * kRowBytes;
           if (p.c_type == RB_F16) {
 #pragma unroll
