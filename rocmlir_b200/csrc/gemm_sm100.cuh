@@ -625,8 +625,12 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
       // The per-column bias add and the rectifier (the GEMM + bias + ReLU of a linear layer) ride along in the same loop:
       // through the general loop that epilogue took 31k cycles per tile, five times the plain one, and its code
       // evicted the other roles' instructions (the issue loop waited twice as long for operands).
-      const uint32_t f16_extra = p.epi.flags & ~(uint32_t)(RB_EPI_BIAS | RB_EPI_RELU);
+      // (so does the per-tensor scale of an fp8 product)
+      // and the roundings to a declared 16-bit result type before and after the bias add)
+      const bool f16_mid = (p.epi.flags & RB_EPI_ROUND_MID) && (p.epi.mid_type == RB_F16 || p.epi.mid_type == RB_BF16);
+      const uint32_t f16_extra = p.epi.flags & ~(uint32_t)(RB_EPI_ALPHA | RB_EPI_BIAS | RB_EPI_RELU | (f16_mid ? RB_EPI_ROUND_MID : 0));
       const bool f16_bias = epi_col_bias(p.epi.flags), f16_relu = (p.epi.flags & RB_EPI_RELU) != 0;
+      const bool f16_alpha = (p.epi.flags & RB_EPI_ALPHA) != 0;
       const bool fast16 = w.kind == 0 && p.c_tma && f16_extra == 0 && (f16_bias || !(p.epi.flags & RB_EPI_BIAS)) &&
                           !p.acc_is_int && !probe && (p.c_type == RB_F16 || p.c_type == RB_BF16);
       // 4-byte C (f32 results, raw i32 results, the raw planes of a K split): 32 columns = one staging row per step
@@ -648,6 +652,14 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
           }
           __syncwarp();
           tmem_ld_wait();
+          if (f16_mid) {
+#pragma unroll
+            for (int j = 0; j < 64; ++j) v[j] = __float_as_uint(round_to_type(__uint_as_float(v[j]), p.epi.mid_type));
+          }
+          if (f16_alpha) {
+#pragma unroll
+            for (int j = 0; j < 64; ++j) v[j] = __float_as_uint(__fmul_rn(__uint_as_float(v[j]), p.epi.alpha));
+          }
           if (f16_bias) {   // same operations, same order as epi_apply32: add (round to nearest), then the rectifier
             const float* bs = vec_bias + cp * 64;
 #pragma unroll
@@ -658,6 +670,10 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
               v[j + 2] = __float_as_uint(__fadd_rn(__uint_as_float(v[j + 2]), b4.z));
               v[j + 3] = __float_as_uint(__fadd_rn(__uint_as_float(v[j + 3]), b4.w));
             }
+          }
+          if (f16_bias && f16_mid) {
+#pragma unroll
+            for (int j = 0; j < 64; ++j) v[j] = __float_as_uint(round_to_type(__uint_as_float(v[j]), p.epi.mid_type));
           }
           if (f16_relu) {
 #pragma unroll
@@ -742,7 +758,56 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
       }
       // Fused elementwise work (or 1-byte / converted outputs) on whole tiles through TMA stores: the general loop's
       // body without its stream-K and plain-store branches.
-      const bool fast_epi = !fast16 && !fast32 && !fast_remap && w.kind == 0 && p.c_tma && !probe && !raw_i32;
+      // Quantised linear layer: i32 accumulator x scale[n] x 1 / output scale -> i8 (round half even, saturate, plus the
+      // output zero point). 32 columns are 32 bytes of a staging row; four groups make one 128-byte-wide store.
+      const bool fast8 = !fast16 && !fast32 && !fast_remap && w.kind == 0 && p.c_tma && !probe && p.acc_is_int && p.c_type == RB_I8 &&
+                         (p.epi.flags & ~(uint32_t)RB_EPI_ZP_OUT) == (uint32_t)(RB_EPI_COL_SCALE | RB_EPI_REQUANT);
+      if (fast8) {
+        const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + buf * kMaxBN;
+        const float recip = p.epi.out_recip;
+        const int zp = p.epi.out_zero;
+#pragma unroll 1
+        for (int c = 0; c < ngroups; ++c) {
+          const int n0 = nb * p.bn + c * 32;
+          if (n0 >= p.N) break;  // warp-uniform
+          uint32_t v[32];
+          tmem_ld32(taddr + c * 32, v);
+          const int sub = c & 3;
+          uint8_t* stg = my_staging + (stg_bufs == 2 ? (nstores & 1u) : 0u) * L::kStoreTileBytes;
+          if (sub == 0) {
+            if (lane == 0 && nstores >= stg_bufs) { if (stg_bufs == 2) bulk_wait_read<1>(); else bulk_wait_read<0>(); }
+            __syncwarp();
+          }
+          tmem_ld_wait();
+          const float* cs = vec_scale + c * 32;
+          uint32_t wd[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float4 s4 = *reinterpret_cast<const float4*>(cs + 4 * i);
+            const float sc[4] = {s4.x, s4.y, s4.z, s4.w};
+            uint32_t b = 0;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const float x = __fmul_rn(__fmul_rn(__int2float_rn((int)v[4 * i + k]), sc[k]), recip);
+              b |= (uint32_t)(uint8_t)(int8_t)f32_to_i8_zp(x, zp) << (8 * k);
+            }
+            wd[i] = b;
+          }
+          *reinterpret_cast<uint4*>(stg + lane * kRowBytes + (((sub * 2) ^ (lane & 7)) << 4)) = make_uint4(wd[0], wd[1], wd[2], wd[3]);
+          *reinterpret_cast<uint4*>(stg + lane * kRowBytes + (((sub * 2 + 1) ^ (lane & 7)) << 4)) = make_uint4(wd[4], wd[5], wd[6], wd[7]);
+          const bool last_group = (sub == 3) || (n0 + 32 >= p.N) || (c == ngroups - 1);
+          if (last_group) {
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0 && row0 < p.M) {
+              tma_store_3d(&maps.c, stg, n0 - sub * 32, (int)row0, gz);
+              bulk_commit();
+            }
+            ++nstores;
+          }
+        }
+      }
+      const bool fast_epi = !fast8 && !fast16 && !fast32 && !fast_remap && w.kind == 0 && p.c_tma && !probe && !raw_i32;
       if (fast_epi) {
         const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + buf * kMaxBN;
 #pragma unroll 1
@@ -787,7 +852,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
         }
       }
 #pragma unroll 1
-      for (int c = 0; c < ngroups && !fast16 && !fast32 && !fast_epi && !fast_remap; ++c) {
+      for (int c = 0; c < ngroups && !fast8 && !fast16 && !fast32 && !fast_epi && !fast_remap; ++c) {
         const int n0 = nb * p.bn + c * 32;
         if (n0 >= p.N) break;  // warp-uniform
         if (probe & 2) break;
