@@ -622,21 +622,94 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
       // compact loop - 64 columns = one 128-byte staging row per step. The general loop below handles every other
       // case; keeping this one small matters because the general loop's code is far larger than the instruction
       // cache and ran at about 1400 cycles per 32 columns where this one needs about 150.
-      // The per-column bias add and the rectifier (the GEMM + bias + ReLU of a linear layer) ride along in the same loop:
-      // through the general loop that epilogue took 31k cycles per tile, five times the plain one, and its code
-      // evicted the other roles' instructions (the issue loop waited twice as long for operands).
-      // (so does the per-tensor scale of an fp8 product)
-      // and the roundings to a declared 16-bit result type before and after the bias add)
-      const bool f16_mid = (p.epi.flags & RB_EPI_ROUND_MID) && (p.epi.mid_type == RB_F16 || p.epi.mid_type == RB_BF16);
-      const uint32_t f16_extra = p.epi.flags & ~(uint32_t)(RB_EPI_ALPHA | RB_EPI_BIAS | RB_EPI_RELU | (f16_mid ? RB_EPI_ROUND_MID : 0));
-      const bool f16_bias = epi_col_bias(p.epi.flags), f16_relu = (p.epi.flags & RB_EPI_RELU) != 0;
-      const bool f16_alpha = (p.epi.flags & RB_EPI_ALPHA) != 0;
-      const bool fast16 = w.kind == 0 && p.c_tma && f16_extra == 0 && (f16_bias || !(p.epi.flags & RB_EPI_BIAS)) &&
-                          !p.acc_is_int && !probe && (p.c_type == RB_F16 || p.c_type == RB_BF16);
+      const bool fast16 = w.kind == 0 && p.c_tma && p.epi.flags == 0 && !p.acc_is_int && !probe &&
+                          (p.c_type == RB_F16 || p.c_type == RB_BF16);
       // 4-byte C (f32 results, raw i32 results, the raw planes of a K split): 32 columns = one staging row per step
       const bool fast32 = w.kind == 0 && p.c_tma && !probe &&
                           ((p.epi.flags == 0 && !p.acc_is_int && p.c_type == RB_F32) || raw_i32);
       if (fast16) {
+        const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + buf * kMaxBN;
+        const int nsteps = p.bn / 64;
+#pragma unroll 1
+        for (int cp = 0; cp < nsteps; ++cp) {
+          const int n0 = nb * p.bn + cp * 64;
+          if (n0 >= p.N) break;  // warp-uniform
+          uint32_t v[64];
+          tmem_ld32(taddr + cp * 64, v);
+          tmem_ld32(taddr + cp * 64 + 32, v + 32);
+          uint8_t* stg = my_staging + (nstores & 1u) * L::kStoreTileBytes;
+          if (lane == 0 && nstores >= 2) bulk_wait_read<1>();  // the store that last used this buffer has read it
+          __syncwarp();
+          tmem_ld_wait();
+          uint8_t* rowp = stg + lane * kRowBytes;
+          if (p.c_type == RB_F16) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              uint32_t h[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                __half2 t2 = __floats2half2_rn(__uint_as_float(v[8 * i + 2 * j]), __uint_as_float(v[8 * i + 2 * j + 1]));
+                h[j] = *reinterpret_cast<uint32_t*>(&t2);
+              }
+              *reinterpret_cast<uint4*>(rowp + ((i ^ (lane & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              uint32_t h[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                __nv_bfloat162 t2 = __floats2bfloat162_rn(__uint_as_float(v[8 * i + 2 * j]), __uint_as_float(v[8 * i + 2 * j + 1]));
+                h[j] = *reinterpret_cast<uint32_t*>(&t2);
+              }
+              *reinterpret_cast<uint4*>(rowp + ((i ^ (lane & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
+            }
+          }
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0 && row0 < p.M) {
+            tma_store_3d(&maps.c, stg, n0, (int)row0, gz);
+            bulk_commit();
+          }
+          ++nstores;
+        }
+      } else if (fast32) {
+        const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + buf * kMaxBN;
+#pragma unroll 1
+        for (int c = 0; c < ngroups; ++c) {
+          const int n0 = nb * p.bn + c * 32;
+          if (n0 >= p.N) break;  // warp-uniform
+          uint32_t v[32];
+          tmem_ld32(taddr + c * 32, v);
+          uint8_t* stg = my_staging + (nstores & 1u) * L::kStoreTileBytes;
+          if (lane == 0 && nstores >= 2) bulk_wait_read<1>();
+          __syncwarp();
+          tmem_ld_wait();
+          uint8_t* rowp = stg + lane * kRowBytes;
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            *reinterpret_cast<uint4*>(rowp + ((i ^ (lane & 7)) << 4)) = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0 && row0 < p.M) {
+            tma_store_3d(&maps.c, stg, n0, (int)row0, gz);
+            bulk_commit();
+          }
+          ++nstores;
+        }
+      }
+      // The common float tails - per-tensor alpha (an fp8 product), per-column bias, ReLU, the roundings to a declared
+      // 16-bit result type before and after the bias add - run in a copy of the compact 16-bit loop above. Through the
+      // general loop GEMM + bias + ReLU took 31k cycles per tile, five times the plain store loop, and its code evicted the
+      // other roles' instructions (the issue loop waited twice as long for operands). A copy, not branches inside the
+      // plain loop: with the extra steps inside it the layers with a short K loop lost 20 %.
+      const bool f16_mid = (p.epi.flags & RB_EPI_ROUND_MID) && (p.epi.mid_type == RB_F16 || p.epi.mid_type == RB_BF16);
+      const uint32_t f16_extra = p.epi.flags & ~(uint32_t)(RB_EPI_ALPHA | RB_EPI_BIAS | RB_EPI_RELU | (f16_mid ? RB_EPI_ROUND_MID : 0));
+      const bool f16_bias = epi_col_bias(p.epi.flags), f16_relu = (p.epi.flags & RB_EPI_RELU) != 0;
+      const bool f16_alpha = (p.epi.flags & RB_EPI_ALPHA) != 0;
+      const bool fast16e = p.epi.flags != 0 && w.kind == 0 && p.c_tma && f16_extra == 0 && (f16_bias || !(p.epi.flags & RB_EPI_BIAS)) &&
+                          !p.acc_is_int && !probe && (p.c_type == RB_F16 || p.c_type == RB_BF16);
+      if (fast16e) {
         const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + buf * kMaxBN;
         const int nsteps = p.bn / 64;
 #pragma unroll 1
@@ -711,30 +784,6 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
           }
           ++nstores;
         }
-      } else if (fast32) {
-        const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + buf * kMaxBN;
-#pragma unroll 1
-        for (int c = 0; c < ngroups; ++c) {
-          const int n0 = nb * p.bn + c * 32;
-          if (n0 >= p.N) break;  // warp-uniform
-          uint32_t v[32];
-          tmem_ld32(taddr + c * 32, v);
-          uint8_t* stg = my_staging + (nstores & 1u) * L::kStoreTileBytes;
-          if (lane == 0 && nstores >= 2) bulk_wait_read<1>();
-          __syncwarp();
-          tmem_ld_wait();
-          uint8_t* rowp = stg + lane * kRowBytes;
-#pragma unroll
-          for (int i = 0; i < 8; ++i)
-            *reinterpret_cast<uint4*>(rowp + ((i ^ (lane & 7)) << 4)) = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-          fence_proxy_async();
-          __syncwarp();
-          if (lane == 0 && row0 < p.M) {
-            tma_store_3d(&maps.c, stg, n0, (int)row0, gz);
-            bulk_commit();
-          }
-          ++nstores;
-        }
       }
       // Channel-major f32 result of a convolution (NKHW): one store per column, the warp's 32 lanes are 32 consecutive
       // pixels of the column's image plane
@@ -760,7 +809,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
       // body without its stream-K and plain-store branches.
       // Quantised linear layer: i32 accumulator x scale[n] x 1 / output scale -> i8 (round half even, saturate, plus the
       // output zero point). 32 columns are 32 bytes of a staging row; four groups make one 128-byte-wide store.
-      const bool fast8 = !fast16 && !fast32 && !fast_remap && w.kind == 0 && p.c_tma && !probe && p.acc_is_int && p.c_type == RB_I8 &&
+      const bool fast8 = !fast16 && !fast16e && !fast32 && !fast_remap && w.kind == 0 && p.c_tma && !probe && p.acc_is_int && p.c_type == RB_I8 &&
                          (p.epi.flags & ~(uint32_t)RB_EPI_ZP_OUT) == (uint32_t)(RB_EPI_COL_SCALE | RB_EPI_REQUANT);
       if (fast8) {
         const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + buf * kMaxBN;
@@ -807,7 +856,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
           }
         }
       }
-      const bool fast_epi = !fast8 && !fast16 && !fast32 && !fast_remap && w.kind == 0 && p.c_tma && !probe && !raw_i32;
+      const bool fast_epi = !fast8 && !fast16 && !fast16e && !fast32 && !fast_remap && w.kind == 0 && p.c_tma && !probe && !raw_i32;
       if (fast_epi) {
         const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + buf * kMaxBN;
 #pragma unroll 1
@@ -852,7 +901,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
         }
       }
 #pragma unroll 1
-      for (int c = 0; c < ngroups && !fast8 && !fast16 && !fast32 && !fast_epi && !fast_remap; ++c) {
+      for (int c = 0; c < ngroups && !fast8 && !fast16 && !fast16e && !fast32 && !fast_epi && !fast_remap; ++c) {
         const int n0 = nb * p.bn + c * 32;
         if (n0 >= p.N) break;  // warp-uniform
         if (probe & 2) break;

@@ -176,7 +176,7 @@ def test_gemm_bias_unary(cuda_device, fn, code):
     from rocmlir_b200 import _lib as L
     from rocmlir_b200.gemm import Epilogue, gemm
     m, n, k = 300, 200, 96
-    rng = np.random.Generator(np.random.PCG64(hash(fn) % 1000))
+    rng = np.random.Generator(np.random.PCG64(sum(map(ord, fn))))   # (not hash(): that differs from process to process)
     a32 = rng.uniform(0.05, 0.5, size=(m, k)).astype(np.float32)
     b32 = rng.uniform(0.05, 0.5, size=(k, n)).astype(np.float32)
     bias32 = rng.uniform(-0.5, 0.5, size=(n,)).astype(np.float32)
@@ -195,9 +195,9 @@ def test_gemm_bias_unary(cuda_device, fn, code):
     bar = 1e-3 if code == oracle.F16 else 3e-5
     if fn in ("ceil", "floor"):
         # a step function turns a last-bit difference of the sum into a whole unit: compare where the argument is not
-        # within an f16 step of an integer
+        # within two f16 steps of an integer (the sums reach 16, where a step is 2^-7)
         pre = oracle.to_f32(oracle.from_f32(oracle.epilogue(acc, n, bias=biasf, mid_type=mid), code), code).reshape(ref.shape)
-        keep = np.abs(pre - np.rint(pre)) > 4e-3
+        keep = np.abs(pre - np.rint(pre)) > 0.02
         assert keep.mean() > 0.9
         np.testing.assert_array_equal(oracle.to_f32(got, code)[keep], oracle.to_f32(ref, code)[keep])
         return
