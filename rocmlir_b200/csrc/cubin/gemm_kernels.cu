@@ -7,7 +7,8 @@
 
 namespace rb {
 #define RB_INST(KIND, A, B, C) \
-  template __global__ void gemm_tcgen05_kernel<KIND, A, B, C>(const __grid_constant__ GemmTensorMaps, const GemmParams);
+  template __global__ void gemm_tcgen05_kernel<KIND, A, B, C, false>(const __grid_constant__ GemmTensorMaps, const GemmParams); \
+  template __global__ void gemm_tcgen05_kernel<KIND, A, B, C, true>(const __grid_constant__ GemmTensorMaps, const GemmParams);
 #define RB_INST_MAJORS(KIND, C) RB_INST(KIND, false, false, C) RB_INST(KIND, false, true, C) RB_INST(KIND, true, false, C) RB_INST(KIND, true, true, C)
 RB_INST_MAJORS(kKindF16, 1)
 RB_INST_MAJORS(kKindF16, 2)

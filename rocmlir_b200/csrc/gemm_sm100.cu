@@ -103,20 +103,20 @@ __global__ void f32_prepare_kernel(const float* __restrict__ src, float* __restr
 // ---- dispatch ----------------------------------------------------------------------------------------
 typedef void (*GemmKernel)(const GemmTensorMaps, const GemmParams);
 
-template <int KIND, int CTAS>
+template <int KIND, int CTAS, bool EPI>
 GemmKernel pick_major(bool a_mn, bool b_mn) {
-  if (!a_mn && !b_mn) return gemm_tcgen05_kernel<KIND, false, false, CTAS>;
-  if (!a_mn && b_mn) return gemm_tcgen05_kernel<KIND, false, true, CTAS>;
-  if (a_mn && !b_mn) return gemm_tcgen05_kernel<KIND, true, false, CTAS>;
-  return gemm_tcgen05_kernel<KIND, true, true, CTAS>;
+  if (!a_mn && !b_mn) return gemm_tcgen05_kernel<KIND, false, false, CTAS, EPI>;
+  if (!a_mn && b_mn) return gemm_tcgen05_kernel<KIND, false, true, CTAS, EPI>;
+  if (a_mn && !b_mn) return gemm_tcgen05_kernel<KIND, true, false, CTAS, EPI>;
+  return gemm_tcgen05_kernel<KIND, true, true, CTAS, EPI>;
 }
-template <int CTAS>
+template <int CTAS, bool EPI>
 GemmKernel pick_kernel(int kind, bool a_mn, bool b_mn) {
   switch (kind) {
-    case kKindF16: return pick_major<kKindF16, CTAS>(a_mn, b_mn);
-    case kKindTF32: return gemm_tcgen05_kernel<kKindTF32, false, false, CTAS>;  // f32 operands are made K-major first
-    case kKindI8: return pick_major<kKindI8, CTAS>(a_mn, b_mn);
-    default: return pick_major<kKindF8, CTAS>(a_mn, b_mn);
+    case kKindF16: return pick_major<kKindF16, CTAS, EPI>(a_mn, b_mn);
+    case kKindTF32: return gemm_tcgen05_kernel<kKindTF32, false, false, CTAS, EPI>;  // f32 operands are made K-major first
+    case kKindI8: return pick_major<kKindI8, CTAS, EPI>(a_mn, b_mn);
+    default: return pick_major<kKindF8, CTAS, EPI>(a_mn, b_mn);
   }
 }
 
@@ -403,10 +403,10 @@ extern "C" RbStatus rbGemm(const RbGemmProblem* p, const RbEpilogue* epi, const 
 }
 
 // Name of an instantiation of gemm_tcgen05_kernel inside the cubin image (Itanium mangling of
-// rb::gemm_tcgen05_kernel<KIND, A_MN, B_MN, CTAS>(GemmTensorMaps, GemmParams)).
-static std::string kernel_symbol(int kind, bool a_mn, bool b_mn, int ctas) {
+// rb::gemm_tcgen05_kernel<KIND, A_MN, B_MN, CTAS, EPI>(GemmTensorMaps, GemmParams)).
+static std::string kernel_symbol(int kind, bool a_mn, bool b_mn, int ctas, bool epi) {
   return "_ZN2rb19gemm_tcgen05_kernelILi" + std::to_string(kind) + "ELb" + (a_mn ? "1" : "0") + "ELb" + (b_mn ? "1" : "0") +
-         "ELi" + std::to_string(ctas) + "EEEvNS_14GemmTensorMapsENS_10GemmParamsE";
+         "ELi" + std::to_string(ctas) + "ELb" + (epi ? "1" : "0") + "EEEvNS_14GemmTensorMapsENS_10GemmParamsE";
 }
 
 RbStatus rb::gemm_run(const RbGemmProblem* p, const RbEpilogue* epi, const void* a, const void* b, void* c,
@@ -750,7 +750,10 @@ RbStatus rb::gemm_run(const RbGemmProblem* p, const RbEpilogue* epi, const void*
     kp.sk_token = next_token.fetch_add(1, std::memory_order_relaxed);
   }
 
-  GemmKernel kern = ctas == 2 ? pick_kernel<2>(kind, a_mn, b_mn) : pick_kernel<1>(kind, a_mn, b_mn);
+  // the instantiation with the fused elementwise code only when this launch has such work (see gemm_tcgen05_kernel)
+  const bool epi_kernel = kp.epi.flags != 0;
+  GemmKernel kern = epi_kernel ? (ctas == 2 ? pick_kernel<2, true>(kind, a_mn, b_mn) : pick_kernel<1, true>(kind, a_mn, b_mn))
+                               : (ctas == 2 ? pick_kernel<2, false>(kind, a_mn, b_mn) : pick_kernel<1, false>(kind, a_mn, b_mn));
   const bool kernel_epi_vec = splits == 1 && epi_vec;  // with a K split the reduction kernel applies the epilogue
   const int smem = ctas == 2 ? GemmSmemLayout<2>::total(stages, bn, kernel_epi_vec) : GemmSmemLayout<1>::total(stages, bn, kernel_epi_vec);
   {
@@ -777,7 +780,7 @@ RbStatus rb::gemm_run(const RbGemmProblem* p, const RbEpilogue* epi, const void*
   if (capture) {
     static_assert(sizeof(GemmTensorMaps) + sizeof(GemmParams) + 64 <= sizeof(capture->params), "parameter block too small");
     memset(capture, 0, sizeof(*capture));
-    const std::string sym = kernel_symbol(kind, kind == kKindTF32 ? false : a_mn, kind == kKindTF32 ? false : b_mn, ctas);
+    const std::string sym = kernel_symbol(kind, kind == kKindTF32 ? false : a_mn, kind == kKindTF32 ? false : b_mn, ctas, epi_kernel);
     snprintf(capture->symbol, sizeof(capture->symbol), "%s", sym.c_str());
     capture->grid = lc.gridDim.x;
     capture->block = kGemmThreads;

@@ -231,9 +231,148 @@ struct WorkIter {
   }
 };
 
-template <int KIND, bool A_MN, bool B_MN, int CTAS>
+// ---- Fused epilogue loops kept OUT of the kernel body -------------------------------------------------------------
+// The kernel's per-tile path is latency-critical for problems with a short K loop (a pointwise convolution runs 42
+// tiles of four K blocks per CTA), and its speed follows the size of the code around it: with these loops inlined -
+// never executed by such a problem - the C = 256 -> K = 64 pointwise layers lost 12 % (forward) and 6 % (backward data).
+// They are therefore separate functions, called by the tiles that need them.
+struct EpiStoreCtx {
+  const CUtensorMap* cmap;   // store map of C
+  uint8_t* staging;          // this warp's staging buffers
+  uint32_t stg_bufs;         // 1 or 2
+  uint32_t taddr;            // this warp's quarter of the accumulator buffer
+  int col0;                  // first column of the tile
+  int bn, N, M;
+  int row0, gz, lane;
+};
+
+// 16-bit C from float accumulators with the common float tails: [round to mid] -> [x alpha] -> [+ bias[n], round to mid]
+// -> [ReLU] -> convert; the operations and their order are those of epi_apply32. Returns the updated store count.
+static __device__ __noinline__ uint32_t epi_fused16_tile(const EpiStoreCtx c, uint32_t flags, int mid_type, float alpha,
+                                                         const float* vec_bias, int c_type, uint32_t nstores) {
+  const bool f_mid = (flags & RB_EPI_ROUND_MID) != 0, f_alpha = (flags & RB_EPI_ALPHA) != 0;
+  const bool f_bias = (flags & RB_EPI_BIAS) != 0, f_relu = (flags & RB_EPI_RELU) != 0;
+  const int nsteps = c.bn / 64;
+#pragma unroll 1
+  for (int cp = 0; cp < nsteps; ++cp) {
+    const int n0 = c.col0 + cp * 64;
+    if (n0 >= c.N) break;  // warp-uniform
+    uint32_t v[64];
+    tmem_ld32(c.taddr + cp * 64, v);
+    tmem_ld32(c.taddr + cp * 64 + 32, v + 32);
+    uint8_t* stg = c.staging + (c.stg_bufs == 2 ? (nstores & 1u) : 0u) * (32 * kRowBytes);
+    if (c.lane == 0 && nstores >= c.stg_bufs) {   // the store that last used this buffer has read it
+      if (c.stg_bufs == 2) bulk_wait_read<1>(); else bulk_wait_read<0>();
+    }
+    __syncwarp();
+    tmem_ld_wait();
+    if (f_mid) {
+#pragma unroll
+      for (int j = 0; j < 64; ++j) v[j] = __float_as_uint(round_to_type(__uint_as_float(v[j]), mid_type));
+    }
+    if (f_alpha) {
+#pragma unroll
+      for (int j = 0; j < 64; ++j) v[j] = __float_as_uint(__fmul_rn(__uint_as_float(v[j]), alpha));
+    }
+    if (f_bias) {
+      const float* bs = vec_bias + cp * 64;
+#pragma unroll
+      for (int j = 0; j < 64; j += 4) {
+        const float4 b4 = *reinterpret_cast<const float4*>(bs + j);
+        v[j] = __float_as_uint(__fadd_rn(__uint_as_float(v[j]), b4.x));
+        v[j + 1] = __float_as_uint(__fadd_rn(__uint_as_float(v[j + 1]), b4.y));
+        v[j + 2] = __float_as_uint(__fadd_rn(__uint_as_float(v[j + 2]), b4.z));
+        v[j + 3] = __float_as_uint(__fadd_rn(__uint_as_float(v[j + 3]), b4.w));
+      }
+      if (f_mid) {
+#pragma unroll
+        for (int j = 0; j < 64; ++j) v[j] = __float_as_uint(round_to_type(__uint_as_float(v[j]), mid_type));
+      }
+    }
+    if (f_relu) {
+#pragma unroll
+      for (int j = 0; j < 64; ++j) v[j] = __float_as_uint(fmaxf(__uint_as_float(v[j]), 0.0f));
+    }
+    uint8_t* rowp = stg + c.lane * kRowBytes;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      uint32_t h[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float lo = __uint_as_float(v[8 * i + 2 * j]), hi = __uint_as_float(v[8 * i + 2 * j + 1]);
+        if (c_type == RB_F16) { __half2 t2 = __floats2half2_rn(lo, hi); h[j] = *reinterpret_cast<uint32_t*>(&t2); }
+        else { __nv_bfloat162 t2 = __floats2bfloat162_rn(lo, hi); h[j] = *reinterpret_cast<uint32_t*>(&t2); }
+      }
+      *reinterpret_cast<uint4*>(rowp + ((i ^ (c.lane & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
+    }
+    fence_proxy_async();
+    __syncwarp();
+    if (c.lane == 0 && c.row0 < c.M) {
+      tma_store_3d(c.cmap, stg, n0, c.row0, c.gz);
+      bulk_commit();
+    }
+    ++nstores;
+  }
+  return nstores;
+}
+
+// Quantised linear layer: i32 accumulator x scale[n] x 1 / output scale -> i8 (round half even, saturate, plus the
+// output zero point). 32 columns are 32 bytes of a staging row; four groups make one 128-byte-wide store.
+static __device__ __noinline__ uint32_t epi_requant8_tile(const EpiStoreCtx c, const float* vec_scale, float recip, int zp,
+                                                          uint32_t nstores) {
+  const int ngroups = c.bn / 32;
+#pragma unroll 1
+  for (int g = 0; g < ngroups; ++g) {
+    const int n0 = c.col0 + g * 32;
+    if (n0 >= c.N) break;  // warp-uniform
+    uint32_t v[32];
+    tmem_ld32(c.taddr + g * 32, v);
+    const int sub = g & 3;
+    uint8_t* stg = c.staging + (c.stg_bufs == 2 ? (nstores & 1u) : 0u) * (32 * kRowBytes);
+    if (sub == 0) {
+      if (c.lane == 0 && nstores >= c.stg_bufs) { if (c.stg_bufs == 2) bulk_wait_read<1>(); else bulk_wait_read<0>(); }
+      __syncwarp();
+    }
+    tmem_ld_wait();
+    const float* cs = vec_scale + g * 32;
+    uint32_t wd[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float4 s4 = *reinterpret_cast<const float4*>(cs + 4 * i);
+      const float sc[4] = {s4.x, s4.y, s4.z, s4.w};
+      uint32_t b = 0;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float x = __fmul_rn(__fmul_rn(__int2float_rn((int)v[4 * i + k]), sc[k]), recip);
+        b |= (uint32_t)(uint8_t)(int8_t)f32_to_i8_zp(x, zp) << (8 * k);
+      }
+      wd[i] = b;
+    }
+    *reinterpret_cast<uint4*>(stg + c.lane * kRowBytes + (((sub * 2) ^ (c.lane & 7)) << 4)) = make_uint4(wd[0], wd[1], wd[2], wd[3]);
+    *reinterpret_cast<uint4*>(stg + c.lane * kRowBytes + (((sub * 2 + 1) ^ (c.lane & 7)) << 4)) = make_uint4(wd[4], wd[5], wd[6], wd[7]);
+    const bool last_group = (sub == 3) || (n0 + 32 >= c.N) || (g == ngroups - 1);
+    if (last_group) {
+      fence_proxy_async();
+      __syncwarp();
+      if (c.lane == 0 && c.row0 < c.M) {
+        tma_store_3d(c.cmap, stg, n0 - sub * 32, c.row0, c.gz);
+        bulk_commit();
+      }
+      ++nstores;
+    }
+  }
+  return nstores;
+}
+
+
+// EPI: the instantiation that carries the fused elementwise epilogues (RbEpilogue flags, C += A.B). Launches without
+// one run the EPI = false instantiation, in which every such branch folds away: the per-tile path of problems with a
+// short K loop follows the size of the code around it (measured: the pointwise C = 256 -> K = 64 layers lost 12 % and
+// 6 % when two never-executed fused loops were added to the one kernel, inlined or not).
+template <int KIND, bool A_MN, bool B_MN, int CTAS, bool EPI>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParams p) {
+  const uint32_t eflags = EPI ? p.epi.flags : 0u;   // compile-time zero without EPI
   using KT = KindTraits<KIND>;
   using L = GemmSmemLayout<CTAS>;
   constexpr int ES = KT::ES;
@@ -252,7 +391,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
   const int kpr = p.kpr;               // K blocks per barrier round
   const int rounds = stages / kpr;     // barrier pairs in use
   uint8_t* staging = smem + stages * stage_bytes;  // 1024-byte aligned (stage sizes are multiples of 1024)
-  const bool epi_vec = epi_needs_col_vectors(p.epi.flags);
+  const bool epi_vec = epi_needs_col_vectors(eflags);
   float* epi_vecs = reinterpret_cast<float*>(staging + L::staging_bytes(epi_vec));   // present only when epi_vec
   uint64_t* bars = reinterpret_cast<uint64_t*>(staging + L::staging_bytes(epi_vec) + (epi_vec ? L::kEpiVecBytes : 0));
   uint64_t* full_bar = bars;                       // [stages]
@@ -546,7 +685,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
     const int es_c = dtype_size(p.c_type);
     const int cols_per_store = kRowBytes / es_c;          // columns covered by one 128-byte staging row
     const int groups_per_store = cols_per_store / 32;     // 32-column TMEM loads per staging row: 1, 2 or 4
-    const bool raw_i32 = p.acc_is_int && p.c_type == RB_I32 && p.epi.flags == 0;
+    const bool raw_i32 = p.acc_is_int && p.c_type == RB_I32 && eflags == 0;
     const uint32_t stg_bufs = epi_vec ? 1u : 2u;   // staging buffers per warp
     uint8_t* my_staging = staging + q * stg_bufs * L::kStoreTileBytes;
     uint32_t t = 0, nstores = 0;
@@ -575,8 +714,8 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
         __syncwarp();  // the previous tile's reads of the copy are done
         for (int j = lane; j < p.bn; j += 32) {
           const int n = min(nb * p.bn + j, p.N - 1);
-          if (p.epi.flags & RB_EPI_COL_SCALE) vec_scale[j] = __ldg(p.epi.col_scale + n);
-          if (epi_col_bias(p.epi.flags)) vec_bias[j] = load_bias(p.epi.bias, p.epi.bias_type, n);
+          if (eflags & RB_EPI_COL_SCALE) vec_scale[j] = __ldg(p.epi.col_scale + n);
+          if (epi_col_bias(eflags)) vec_bias[j] = load_bias(p.epi.bias, p.epi.bias_type, n);
         }
         __syncwarp();
       }
@@ -587,14 +726,14 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
       }
       // what this thread's row contributes to the fused elementwise steps (row / scalar bias, residual address)
       EpiRow erow;
-      if ((p.epi.flags & RB_EPI_BIAS) && (p.epi.flags & (RB_EPI_BIAS_ROW | RB_EPI_BIAS_SCALAR)))
+      if ((eflags & RB_EPI_BIAS) && (eflags & (RB_EPI_BIAS_ROW | RB_EPI_BIAS_SCALAR)))
         erow.row_bias = load_bias(p.epi.bias, p.epi.bias_type,
-                                  (p.epi.flags & RB_EPI_BIAS_SCALAR) ? 0 : min(row, (long long)p.M - 1));
+                                  (eflags & RB_EPI_BIAS_SCALAR) ? 0 : min(row, (long long)p.M - 1));
       erow.res_stride = p.c_stride_n;
       const int res_es = p.epi.res_type == RB_F32 ? 4 : 2;
       auto set_res = [&](int n0) {
         erow.ncols = min(32, p.N - n0);
-        erow.res = (row_ok && (p.epi.flags & RB_EPI_RESIDUAL))
+        erow.res = (row_ok && (eflags & RB_EPI_RESIDUAL))
                        ? static_cast<const uint8_t*>(p.epi.residual) + (c_row_off + (long long)n0 * p.c_stride_n) * res_es
                        : nullptr;
       };
@@ -622,11 +761,11 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
       // compact loop - 64 columns = one 128-byte staging row per step. The general loop below handles every other
       // case; keeping this one small matters because the general loop's code is far larger than the instruction
       // cache and ran at about 1400 cycles per 32 columns where this one needs about 150.
-      const bool fast16 = w.kind == 0 && p.c_tma && p.epi.flags == 0 && !p.acc_is_int && !probe &&
+      const bool fast16 = w.kind == 0 && p.c_tma && eflags == 0 && !p.acc_is_int && !probe &&
                           (p.c_type == RB_F16 || p.c_type == RB_BF16);
       // 4-byte C (f32 results, raw i32 results, the raw planes of a K split): 32 columns = one staging row per step
       const bool fast32 = w.kind == 0 && p.c_tma && !probe &&
-                          ((p.epi.flags == 0 && !p.acc_is_int && p.c_type == RB_F32) || raw_i32);
+                          ((eflags == 0 && !p.acc_is_int && p.c_type == RB_F32) || raw_i32);
       if (fast16) {
         const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + buf * kMaxBN;
         const int nsteps = p.bn / 64;
@@ -698,96 +837,28 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
           ++nstores;
         }
       }
-      // The common float tails - per-tensor alpha (an fp8 product), per-column bias, ReLU, the roundings to a declared
-      // 16-bit result type before and after the bias add - run in a copy of the compact 16-bit loop above. Through the
-      // general loop GEMM + bias + ReLU took 31k cycles per tile, five times the plain store loop, and its code evicted the
-      // other roles' instructions (the issue loop waited twice as long for operands). A copy, not branches inside the
-      // plain loop: with the extra steps inside it the layers with a short K loop lost 20 %.
-      const bool f16_mid = (p.epi.flags & RB_EPI_ROUND_MID) && (p.epi.mid_type == RB_F16 || p.epi.mid_type == RB_BF16);
-      const uint32_t f16_extra = p.epi.flags & ~(uint32_t)(RB_EPI_ALPHA | RB_EPI_BIAS | RB_EPI_RELU | (f16_mid ? RB_EPI_ROUND_MID : 0));
-      const bool f16_bias = epi_col_bias(p.epi.flags), f16_relu = (p.epi.flags & RB_EPI_RELU) != 0;
-      const bool f16_alpha = (p.epi.flags & RB_EPI_ALPHA) != 0;
-      const bool fast16e = p.epi.flags != 0 && w.kind == 0 && p.c_tma && f16_extra == 0 && (f16_bias || !(p.epi.flags & RB_EPI_BIAS)) &&
-                          !p.acc_is_int && !probe && (p.c_type == RB_F16 || p.c_type == RB_BF16);
-      if (fast16e) {
-        const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + buf * kMaxBN;
-        const int nsteps = p.bn / 64;
-#pragma unroll 1
-        for (int cp = 0; cp < nsteps; ++cp) {
-          const int n0 = nb * p.bn + cp * 64;
-          if (n0 >= p.N) break;  // warp-uniform
-          uint32_t v[64];
-          tmem_ld32(taddr + cp * 64, v);
-          tmem_ld32(taddr + cp * 64 + 32, v + 32);
-          uint8_t* stg = my_staging + (stg_bufs == 2 ? (nstores & 1u) : 0u) * L::kStoreTileBytes;
-          if (lane == 0 && nstores >= stg_bufs) {   // the store that last used this buffer has read it
-            if (stg_bufs == 2) bulk_wait_read<1>(); else bulk_wait_read<0>();
-          }
-          __syncwarp();
-          tmem_ld_wait();
-          if (f16_mid) {
-#pragma unroll
-            for (int j = 0; j < 64; ++j) v[j] = __float_as_uint(round_to_type(__uint_as_float(v[j]), p.epi.mid_type));
-          }
-          if (f16_alpha) {
-#pragma unroll
-            for (int j = 0; j < 64; ++j) v[j] = __float_as_uint(__fmul_rn(__uint_as_float(v[j]), p.epi.alpha));
-          }
-          if (f16_bias) {   // same operations, same order as epi_apply32: add (round to nearest), then the rectifier
-            const float* bs = vec_bias + cp * 64;
-#pragma unroll
-            for (int j = 0; j < 64; j += 4) {
-              const float4 b4 = *reinterpret_cast<const float4*>(bs + j);
-              v[j] = __float_as_uint(__fadd_rn(__uint_as_float(v[j]), b4.x));
-              v[j + 1] = __float_as_uint(__fadd_rn(__uint_as_float(v[j + 1]), b4.y));
-              v[j + 2] = __float_as_uint(__fadd_rn(__uint_as_float(v[j + 2]), b4.z));
-              v[j + 3] = __float_as_uint(__fadd_rn(__uint_as_float(v[j + 3]), b4.w));
-            }
-          }
-          if (f16_bias && f16_mid) {
-#pragma unroll
-            for (int j = 0; j < 64; ++j) v[j] = __float_as_uint(round_to_type(__uint_as_float(v[j]), p.epi.mid_type));
-          }
-          if (f16_relu) {
-#pragma unroll
-            for (int j = 0; j < 64; ++j) v[j] = __float_as_uint(fmaxf(__uint_as_float(v[j]), 0.0f));
-          }
-          uint8_t* rowp = stg + lane * kRowBytes;
-          if (p.c_type == RB_F16) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              uint32_t h[4];
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                __half2 t2 = __floats2half2_rn(__uint_as_float(v[8 * i + 2 * j]), __uint_as_float(v[8 * i + 2 * j + 1]));
-                h[j] = *reinterpret_cast<uint32_t*>(&t2);
-              }
-              *reinterpret_cast<uint4*>(rowp + ((i ^ (lane & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
-            }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              uint32_t h[4];
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                __nv_bfloat162 t2 = __floats2bfloat162_rn(__uint_as_float(v[8 * i + 2 * j]), __uint_as_float(v[8 * i + 2 * j + 1]));
-                h[j] = *reinterpret_cast<uint32_t*>(&t2);
-              }
-              *reinterpret_cast<uint4*>(rowp + ((i ^ (lane & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
-            }
-          }
-          fence_proxy_async();
-          __syncwarp();
-          if (lane == 0 && row0 < p.M) {
-            tma_store_3d(&maps.c, stg, n0, (int)row0, gz);
-            bulk_commit();
-          }
-          ++nstores;
-        }
+      // The common float tails (per-tensor alpha, per-column bias, ReLU, roundings to a declared 16-bit type) and the
+      // quantised linear layer have compact loops of their own, out of line (epi_fused16_tile, epi_requant8_tile).
+      // Through the general loop GEMM + bias + ReLU took 31k cycles per tile, five times the plain store loop, and its
+      // code evicted the other roles' instructions (the issue loop waited twice as long for operands).
+      const bool f16_mid = (eflags & RB_EPI_ROUND_MID) && (p.epi.mid_type == RB_F16 || p.epi.mid_type == RB_BF16);
+      const uint32_t f16_extra = eflags & ~(uint32_t)(RB_EPI_ALPHA | RB_EPI_BIAS | RB_EPI_RELU | (f16_mid ? RB_EPI_ROUND_MID : 0));
+      const bool fast16e = eflags != 0 && w.kind == 0 && p.c_tma && f16_extra == 0 &&
+                           (epi_col_bias(eflags) || !(eflags & RB_EPI_BIAS)) && !p.acc_is_int && !probe &&
+                           (p.c_type == RB_F16 || p.c_type == RB_BF16);
+      const bool fast8 = !fast16e && w.kind == 0 && p.c_tma && !probe && p.acc_is_int && p.c_type == RB_I8 &&
+                         (eflags & ~(uint32_t)RB_EPI_ZP_OUT) == (uint32_t)(RB_EPI_COL_SCALE | RB_EPI_REQUANT);
+      if (fast16e || fast8) {
+        EpiStoreCtx ec;
+        ec.cmap = &maps.c; ec.staging = my_staging; ec.stg_bufs = stg_bufs;
+        ec.taddr = tmem_base + (uint32_t(q * 32) << 16) + buf * kMaxBN;
+        ec.col0 = nb * p.bn; ec.bn = p.bn; ec.N = p.N; ec.M = p.M; ec.row0 = (int)row0; ec.gz = gz; ec.lane = lane;
+        if (fast16e) nstores = epi_fused16_tile(ec, eflags, p.epi.mid_type, p.epi.alpha, vec_bias, p.c_type, nstores);
+        else nstores = epi_requant8_tile(ec, vec_scale, p.epi.out_recip, p.epi.out_zero, nstores);
       }
       // Channel-major f32 result of a convolution (NKHW): one store per column, the warp's 32 lanes are 32 consecutive
       // pixels of the column's image plane
-      const bool fast_remap = w.kind == 0 && p.c_rows_per_img && p.epi.flags == 0 && !p.acc_is_int && !probe && p.c_type == RB_F32;
+      const bool fast_remap = w.kind == 0 && p.c_rows_per_img && eflags == 0 && !p.acc_is_int && !probe && p.c_type == RB_F32;
       if (fast_remap) {
         const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + buf * kMaxBN;
 #pragma unroll 1
@@ -807,55 +878,6 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
       }
       // Fused elementwise work (or 1-byte / converted outputs) on whole tiles through TMA stores: the general loop's
       // body without its stream-K and plain-store branches.
-      // Quantised linear layer: i32 accumulator x scale[n] x 1 / output scale -> i8 (round half even, saturate, plus the
-      // output zero point). 32 columns are 32 bytes of a staging row; four groups make one 128-byte-wide store.
-      const bool fast8 = !fast16 && !fast16e && !fast32 && !fast_remap && w.kind == 0 && p.c_tma && !probe && p.acc_is_int && p.c_type == RB_I8 &&
-                         (p.epi.flags & ~(uint32_t)RB_EPI_ZP_OUT) == (uint32_t)(RB_EPI_COL_SCALE | RB_EPI_REQUANT);
-      if (fast8) {
-        const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + buf * kMaxBN;
-        const float recip = p.epi.out_recip;
-        const int zp = p.epi.out_zero;
-#pragma unroll 1
-        for (int c = 0; c < ngroups; ++c) {
-          const int n0 = nb * p.bn + c * 32;
-          if (n0 >= p.N) break;  // warp-uniform
-          uint32_t v[32];
-          tmem_ld32(taddr + c * 32, v);
-          const int sub = c & 3;
-          uint8_t* stg = my_staging + (stg_bufs == 2 ? (nstores & 1u) : 0u) * L::kStoreTileBytes;
-          if (sub == 0) {
-            if (lane == 0 && nstores >= stg_bufs) { if (stg_bufs == 2) bulk_wait_read<1>(); else bulk_wait_read<0>(); }
-            __syncwarp();
-          }
-          tmem_ld_wait();
-          const float* cs = vec_scale + c * 32;
-          uint32_t wd[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const float4 s4 = *reinterpret_cast<const float4*>(cs + 4 * i);
-            const float sc[4] = {s4.x, s4.y, s4.z, s4.w};
-            uint32_t b = 0;
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              const float x = __fmul_rn(__fmul_rn(__int2float_rn((int)v[4 * i + k]), sc[k]), recip);
-              b |= (uint32_t)(uint8_t)(int8_t)f32_to_i8_zp(x, zp) << (8 * k);
-            }
-            wd[i] = b;
-          }
-          *reinterpret_cast<uint4*>(stg + lane * kRowBytes + (((sub * 2) ^ (lane & 7)) << 4)) = make_uint4(wd[0], wd[1], wd[2], wd[3]);
-          *reinterpret_cast<uint4*>(stg + lane * kRowBytes + (((sub * 2 + 1) ^ (lane & 7)) << 4)) = make_uint4(wd[4], wd[5], wd[6], wd[7]);
-          const bool last_group = (sub == 3) || (n0 + 32 >= p.N) || (c == ngroups - 1);
-          if (last_group) {
-            fence_proxy_async();
-            __syncwarp();
-            if (lane == 0 && row0 < p.M) {
-              tma_store_3d(&maps.c, stg, n0 - sub * 32, (int)row0, gz);
-              bulk_commit();
-            }
-            ++nstores;
-          }
-        }
-      }
       const bool fast_epi = !fast8 && !fast16 && !fast16e && !fast32 && !fast_remap && w.kind == 0 && p.c_tma && !probe && !raw_i32;
       if (fast_epi) {
         const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + buf * kMaxBN;
@@ -875,7 +897,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
           float x[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) x[j] = p.acc_is_int ? __int2float_rn((int)v[j]) : __uint_as_float(v[j]);
-          if (p.epi.flags) {
+          if (eflags) {
             set_res(n0);
             epi_apply32(x, p.epi, vec_scale + c * 32, vec_bias + c * 32, erow);
           }
@@ -940,7 +962,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmTensorMaps maps, const GemmParam
           nw = 8;
         } else {
           float x[32];
-          if (p.epi.flags == 0) {
+          if (eflags == 0) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) x[j] = p.acc_is_int ? __int2float_rn((int)v[j]) : __uint_as_float(v[j]);
           } else {

@@ -56,7 +56,8 @@ __device__ __forceinline__ void fence_proxy_async() {
 // another CTA wrote to global memory is about to be fetched by TMA, and where TMA stores precede a flag.
 __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 // Bounded wait until the n words at `flags` all hold `token` (one thread; the loads of a batch are in flight together).
-__device__ __forceinline__ bool flags_wait(const unsigned int* flags, int n, unsigned int token, uint32_t* status, uint32_t code,
+// Out of line: it sits in the GEMM producer's per-tile path, which only chained launches take.
+static __device__ __noinline__ bool flags_wait(const unsigned int* flags, int n, unsigned int token, uint32_t* status, uint32_t code,
                                            long long limit) {
   const long long t0 = clock64();
   for (;;) {
