@@ -53,6 +53,19 @@ def test_workspace_size_needs_no_device(lib):
     assert lib.rbGemmWorkspaceSize(C.byref(p)) >= 4 * 64 * 64 * 4
 
 
+def test_gemm_gemm_workspace_holds_intermediate_and_flag_words(lib):
+    """rbGemmGemmWorkspaceSize: the rounded intermediate, the larger of the two products' own workspaces, and the flag
+    words of the chained one-launch form (four per 128-row block and 32-column tile), whatever form then runs."""
+    from rocmlir_b200 import _lib as L
+    m, k1, n1, n2 = 4096, 1024, 1024, 1024
+    need = lib.rbGemmGemmWorkspaceSize(1, m, k1, n1, n2, L.F16)
+    flags = (m // 128) * (n1 // 32) * 4 * 4
+    assert need >= m * n1 * 2 + flags and need % 256 == 0
+    assert lib.rbGemmGemmWorkspaceSize(1, 0, k1, n1, n2, L.F16) == 0          # malformed sizes report 0
+    st = lib.rbGemmGemm(1, m, k1, n1, n2, L.F16, None, None, None, None, None, 0, None)
+    assert st != L.SUCCESS                                                     # no workspace, no device pointers
+
+
 def test_invalid_problem_is_rejected_without_device(lib):
     from rocmlir_b200 import _lib as L
     p = L.RbGemmProblem(1, 0, 512, 64, 0, 0, 0, L.F16, L.F16, 0)
